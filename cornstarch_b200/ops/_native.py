@@ -1,0 +1,115 @@
+"""ctypes binding of ``libcornstarch_b200.so`` (the hand-written sm_100a kernels).
+
+The library has a plain C ABI: raw device pointers, sizes and a CUDA stream handle.  This module
+loads it once, declares the prototypes, and offers small helpers to pass torch tensors.  On a machine
+with a GPU the library is mandatory: :func:`lib` raises if it cannot be loaded, so GPU runs can never
+fall back silently to eager PyTorch.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libcornstarch_b200.so"
+
+vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_long, C.c_float
+
+_PROTOS = {
+    "csb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
+    "csb_norm_bwd_parts": [i32],
+    "csb_norm_fwd": [i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, f32, vp],
+    "csb_norm_bwd": [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, vp],
+    "csb_colsum_parts": [i32],
+    "csb_colsum": [vp, vp, vp, i32, i32, i32, i32, vp],
+    "csb_rope": [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, f32, vp],
+    "csb_glu_fwd": [vp, vp, i64, i32, i32, vp],
+    "csb_glu_bwd": [vp, vp, vp, i64, i32, i32, vp],
+    "csb_act_fwd": [vp, vp, i64, i32, vp],
+    "csb_act_bwd": [vp, vp, vp, i64, i32, vp],
+    "csb_add": [vp, vp, vp, i64, vp],
+    "csb_adamw": [vp, vp, vp, vp, vp, i32, i64, f32, f32, f32, f32, f32, f32, f32, vp, vp, i32, vp],
+    "csb_sumsq": [vp, i32, i64, vp, vp],
+    "csb_clip_scale": [vp, f32, f32, vp, vp, vp, vp],
+    "csb_ce_stats": [vp, i64, vp, i32, i32, vp, vp, vp, i64, vp],
+    "csb_ce_grad": [vp, i64, vp, i32, i32, vp, vp, vp, vp, vp, i64, i64, vp],
+    "csb_gather_merge": [vp, vp, vp, vp, i64, i32, vp],
+    "csb_scatter_merge_bwd": [vp, vp, vp, i32, vp, i64, i32, vp],
+}
+
+
+def lib_path() -> Path:
+    return Path(os.environ.get("CORNSTARCH_B200_LIB", str(_LIB_PATH)))
+
+
+def available() -> bool:
+    """True when the native library exists on disk and a CUDA device is present."""
+    return torch.cuda.is_available() and lib_path().exists()
+
+
+def lib():
+    """Load (once) and return the native library; raises when it is missing."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    p = lib_path()
+    if not p.exists():
+        raise RuntimeError(
+            f"native library {p} not found: run `python -m cornstarch_b200.csrc.build` "
+            "(CUDA tensors never fall back to eager PyTorch)"
+        )
+    _LIB = C.CDLL(str(p))
+    for name, args in _PROTOS.items():
+        if hasattr(_LIB, name):
+            fn = getattr(_LIB, name)
+            fn.argtypes = args
+            fn.restype = C.c_int
+    return _LIB
+
+
+def declare(name: str, argtypes: list) -> None:
+    """Register the prototype of one more exported function (used by optional modules)."""
+    _PROTOS[name] = argtypes
+    if _LIB is not None and hasattr(_LIB, name):
+        fn = getattr(_LIB, name)
+        fn.argtypes = argtypes
+        fn.restype = C.c_int
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"cornstarch_b200 native call {what} failed with code {code}")
+
+
+_STATUS: dict[int, torch.Tensor] = {}
+
+
+def status_word(device: torch.device | None = None) -> torch.Tensor:
+    """Per-device int32 status word that kernels with bounded waits write on a time-out."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    t = _STATUS.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+        _STATUS[idx] = t
+    return t
+
+
+def check_status(device: torch.device | None = None) -> int:
+    """Synchronising read of the status word (call it between steps, not per kernel)."""
+    v = int(status_word(device).item())
+    if v != 0:
+        status_word(device).zero_()
+        raise RuntimeError(f"a device-side bounded wait ran out (status {v}); see csrc/ptx.cuh for codes")
+    return v

@@ -1,0 +1,108 @@
+"""bf16 GEMM on the hand-written tcgen05 kernel (``csrc/gemm.cu``) with a plain-PyTorch CPU path.
+
+``gemm(a, b, trans_a, trans_b)`` computes ``op(a) @ op(b).T`` in the kernel's native orientation:
+
+* ``a_mn_major=False``: ``a`` is ``[M, K]`` (K contiguous);  ``True``: ``a`` is ``[K, M]`` (M contiguous)
+* ``b_mn_major=False``: ``b`` is ``[N, K]`` (K contiguous);  ``True``: ``b`` is ``[K, N]`` (N contiguous)
+
+so the three GEMMs of a linear layer (``y = x W^T``, ``dx = dy W``, ``dW = dy^T x``) need no transpose
+copies.  These are the GEMMs the reference runs through cuBLAS behind ``nn.Linear`` and ColossalAI's
+``Linear1D_Col/Row`` (cornstarch/shardformer/policies/llama.py:192-249).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _native as nat
+
+ACT = {None: 0, "none": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "gelu": 2, "gelu_erf": 2, "silu": 3}
+
+
+def _ref_act(x: torch.Tensor, act) -> torch.Tensor:
+    code = ACT[act]
+    if code == 0:
+        return x
+    if code == 1:
+        return torch.nn.functional.gelu(x, approximate="tanh")
+    if code == 2:
+        return torch.nn.functional.gelu(x)
+    return torch.nn.functional.silu(x)
+
+
+def gemm_reference(a, b, a_mn_major=False, b_mn_major=False, bias=None, act=None, out=None, accumulate=False,
+                   out_dtype=None):
+    """fp32 PyTorch statement of the kernel's contract (CPU path and test oracle)."""
+    A = a.float().t() if a_mn_major else a.float()
+    B = b.float().t() if b_mn_major else b.float()
+    y = A @ B.t()
+    if bias is not None:
+        y = y + bias.float()
+    y = _ref_act(y, act)
+    if out is not None:
+        if accumulate:
+            y = y + out.float()
+        out.copy_(y.to(out.dtype))
+        return out
+    return y.to(out_dtype or a.dtype)
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    a_mn_major: bool = False,
+    b_mn_major: bool = False,
+    bias: torch.Tensor | None = None,
+    act: str | None = None,
+    out: torch.Tensor | None = None,
+    accumulate: bool = False,
+    out_dtype: torch.dtype | None = None,
+    tile_n: int = 0,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """``out (+)= act(op(a) @ op(b).T + bias)``; 2-D row-major operands whose row stride may exceed the width."""
+    if not a.is_cuda:
+        return gemm_reference(a, b, a_mn_major, b_mn_major, bias, act, out, accumulate, out_dtype)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "native GEMM is bf16 x bf16 -> fp32 accumulate"
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    if a_mn_major:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn_major:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    lda, ldb = a.stride(0), b.stride(0)
+    if (lda % 8) or (ldb % 8) or (a.data_ptr() % 16) or (b.data_ptr() % 16):
+        # TMA needs 16-byte aligned rows; repack the rare odd-sized operand
+        if lda % 8 or a.data_ptr() % 16:
+            a = _pad_rows(a)
+            lda = a.stride(0)
+        if ldb % 8 or b.data_ptr() % 16:
+            b = _pad_rows(b)
+            ldb = b.stride(0)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=a.device)
+        accumulate = False
+    assert out.shape == (M, N) and out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.numel() == N
+    st = nat.status_word(a.device)
+    code = nat.lib().csb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), nat.ptr(bias), M, N, K, lda, ldb, out.stride(0),
+        int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate), ACT[act],
+        tile_n, max_ctas, st.data_ptr(), nat.stream(),
+    )
+    nat.check(code, "csb_gemm_bf16")
+    return out
+
+
+def _pad_rows(t: torch.Tensor) -> torch.Tensor:
+    """Copy a 2-D tensor into storage whose row stride is a multiple of 8 elements (16 bytes)."""
+    r, c = t.shape
+    ld = (c + 7) // 8 * 8
+    buf = torch.zeros((r, ld), dtype=t.dtype, device=t.device)
+    buf[:, :c].copy_(t)
+    return buf[:, :c]
