@@ -51,9 +51,15 @@ struct SmemLayout {
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t phase, volatile int* abort_flag) {
+  uint64_t t0 = 0;
   for (uint32_t i = 0; i < CSB_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, phase)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+    if ((i & 511u) == 511u) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > CSB_WAIT_NS) return false;
+    }
   }
   return false;
 }

@@ -22,9 +22,19 @@ enum : int {
   ST_TIMEOUT_MISC = 6,
 };
 
-#ifndef CSB_SPIN_LIMIT
-#define CSB_SPIN_LIMIT (1u << 26)
+// Waits are bounded in wall time: after CSB_WAIT_NS nanoseconds a wait gives up.
+#ifndef CSB_WAIT_NS
+#define CSB_WAIT_NS 2000000000ull
 #endif
+#ifndef CSB_SPIN_LIMIT
+#define CSB_SPIN_LIMIT (1u << 30)
+#endif
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -74,8 +84,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t phase) {
 }
 // Bounded wait; false = gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t phase) {
+  uint64_t t0 = 0;
   for (uint32_t i = 0; i < CSB_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, phase)) return true;
+    if ((i & 511u) == 511u) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > CSB_WAIT_NS) return false;
+    }
   }
   return false;
 }

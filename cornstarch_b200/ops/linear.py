@@ -1,0 +1,186 @@
+"""Linear layers on the tcgen05 GEMM with gradient-accumulation fusion.
+
+``linear(x, weight, bias)`` is ``F.linear`` with a custom backward made of two more native GEMMs.
+When a weight carries a ``main_grad`` attribute (a view into the engine's flat gradient buffer,
+see :mod:`cornstarch_b200.optim.arena`) the weight gradient is accumulated straight into it by the
+GEMM epilogue and autograd receives ``None`` for that weight; otherwise a normal gradient is
+returned.
+
+``multi_linear(x, weights, biases)`` runs several projections of the same input (q/k/v, gate/up) as
+ONE GEMM when the weights sit back to back in memory (which the arena guarantees), and falls back to
+one GEMM per weight otherwise.  The output is the concatenation along the last dimension.
+
+Replaces ``nn.Linear`` / ``Linear1D_Col`` / ``Linear1D_Row`` / ``FusedLinear1D_Col`` used by the
+reference policies (cornstarch/shardformer/policies/llama.py:192-249, policies/phi3.py:181-208).
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+import torch.nn.functional as F
+
+from . import _native as nat
+from .gemm import gemm
+
+
+def _use_native(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype == torch.bfloat16
+
+
+def _as_2d(x: torch.Tensor) -> torch.Tensor:
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(1) != 1 or (x2.stride(0) % 8) or (x2.data_ptr() % 16):
+        x2 = x2.contiguous()
+    return x2
+
+
+def colsum(x2: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """Column sums of a bf16 ``[rows, H]`` matrix (bias gradients) on the native kernel."""
+    rows, H = x2.shape
+    if not _use_native(x2) or H % 8 or not x2.is_contiguous():
+        s = x2.float().sum(0)
+        if out is None:
+            return s.to(x2.dtype)
+        out.copy_((out.float() + s if accumulate else s).to(out.dtype))
+        return out
+    if out is None:
+        out = torch.empty(H, dtype=x2.dtype, device=x2.device)
+        accumulate = False
+    parts = nat.lib().csb_colsum_parts(rows)
+    scratch = torch.empty(parts * H, dtype=torch.float32, device=x2.device)
+    nat.check(
+        nat.lib().csb_colsum(x2.data_ptr(), scratch.data_ptr(), out.data_ptr(), int(out.dtype == torch.float32),
+                             int(accumulate), rows, H, nat.stream()),
+        "csb_colsum",
+    )
+    return out
+
+
+def fuse_adjacent(tensors: Sequence[torch.Tensor]) -> torch.Tensor | None:
+    """If 2-D row-major tensors with equal width sit back to back in one storage, return the stacked view."""
+    t0 = tensors[0]
+    if any(t.dim() != 2 or not t.is_contiguous() or t.shape[1] != t0.shape[1] or t.dtype != t0.dtype for t in tensors):
+        return None
+    end = t0.data_ptr() + t0.numel() * t0.element_size()
+    rows = t0.shape[0]
+    for t in tensors[1:]:
+        if t.data_ptr() != end or t.untyped_storage().data_ptr() != t0.untyped_storage().data_ptr():
+            return None
+        end += t.numel() * t.element_size()
+        rows += t.shape[0]
+    return torch.as_strided(t0, (rows, t0.shape[1]), (t0.shape[1], 1), t0.storage_offset())
+
+
+def fuse_adjacent_1d(tensors: Sequence[torch.Tensor | None]) -> torch.Tensor | None:
+    if any(t is None for t in tensors):
+        return None
+    t0 = tensors[0]
+    end = t0.data_ptr() + t0.numel() * t0.element_size()
+    n = t0.numel()
+    for t in tensors[1:]:
+        if t.data_ptr() != end or t.untyped_storage().data_ptr() != t0.untyped_storage().data_ptr():
+            return None
+        end += t.numel() * t.element_size()
+        n += t.numel()
+    return torch.as_strided(t0, (n,), (1,), t0.storage_offset())
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x W^T + b with native backward; several (weight, bias) pairs share one input."""
+
+    @staticmethod
+    def forward(ctx, x, n_w, act, *params):
+        weights = params[:n_w]
+        biases = params[n_w:]
+        x2 = _as_2d(x)
+        fused_w = fuse_adjacent(weights) if n_w > 1 else weights[0]
+        has_bias = biases[0] is not None
+        fused_b = (fuse_adjacent_1d(biases) if n_w > 1 else biases[0]) if has_bias else None
+        n_total = sum(w.shape[0] for w in weights)
+        if fused_w is not None and (not has_bias or fused_b is not None):
+            y = gemm(x2, fused_w, bias=fused_b, act=act)
+        else:
+            y = torch.empty((x2.shape[0], n_total), dtype=x.dtype, device=x.device)
+            o = 0
+            for w, b in zip(weights, biases):
+                gemm(x2, w, bias=b, act=act, out=y[:, o : o + w.shape[0]])
+                o += w.shape[0]
+        ctx.save_for_backward(x2, *weights)
+        ctx.n_w = n_w
+        ctx.has_bias = has_bias
+        ctx.x_shape = x.shape
+        ctx.biases = biases
+        assert act is None, "activation epilogues are applied outside autograd-tracked linears"
+        return y.view(*x.shape[:-1], n_total)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, *weights = ctx.saved_tensors
+        n_w = ctx.n_w
+        dy2 = _as_2d(dy)
+        fused_w = fuse_adjacent(weights) if n_w > 1 else weights[0]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            if fused_w is not None:
+                dx = gemm(dy2, fused_w, b_mn_major=True)
+            else:
+                o = 0
+                dx = torch.empty_like(x2)
+                for i, w in enumerate(weights):
+                    gemm(dy2[:, o : o + w.shape[0]], w, b_mn_major=True, out=dx, accumulate=i > 0)
+                    o += w.shape[0]
+            dx = dx.view(ctx.x_shape)
+        dws: list = [None] * n_w
+        dbs: list = [None] * n_w
+        need_w = [ctx.needs_input_grad[3 + i] for i in range(n_w)]
+        if any(need_w):
+            mains = [getattr(w, "main_grad", None) for w in weights]
+            fused_main = None
+            if all(m is not None for m in mains):
+                fused_main = fuse_adjacent(mains) if n_w > 1 else mains[0]
+            if fused_main is not None and fused_w is not None:
+                # one GEMM accumulating into the flat gradient buffer
+                gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=fused_main, accumulate=True)
+                for w in weights:
+                    w.grad_added_to_main_grad = True
+            else:
+                o = 0
+                for i, w in enumerate(weights):
+                    n = w.shape[0]
+                    if need_w[i]:
+                        if mains[i] is not None:
+                            gemm(dy2[:, o : o + n], x2, a_mn_major=True, b_mn_major=True, out=mains[i], accumulate=True)
+                            w.grad_added_to_main_grad = True
+                        else:
+                            dws[i] = gemm(dy2[:, o : o + n], x2, a_mn_major=True, b_mn_major=True)
+                    o += n
+        if ctx.has_bias:
+            o = 0
+            for i, (w, b) in enumerate(zip(weights, ctx.biases)):
+                n = w.shape[0]
+                if ctx.needs_input_grad[3 + n_w + i]:
+                    seg = dy2[:, o : o + n]
+                    main = getattr(b, "main_grad", None)
+                    if main is not None:
+                        colsum(seg.contiguous() if not seg.is_contiguous() else seg, out=main, accumulate=True)
+                        b.grad_added_to_main_grad = True
+                    else:
+                        dbs[i] = colsum(seg.contiguous() if not seg.is_contiguous() else seg)
+                o += n
+        return (dx, None, None, *dws, *dbs)
+
+
+def multi_linear(x: torch.Tensor, weights: Sequence[torch.Tensor], biases: Sequence[torch.Tensor | None] | None = None):
+    """Concatenated projections ``[x W_0^T + b_0 | x W_1^T + b_1 | ...]`` of one input."""
+    if biases is None:
+        biases = [None] * len(weights)
+    if not _use_native(x):
+        outs = [F.linear(x, w, b) for w, b in zip(weights, biases)]
+        return outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
+    return _LinearFn.apply(x, len(weights), None, *weights, *biases)
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    return multi_linear(x, [weight], [bias])
