@@ -1,0 +1,498 @@
+// Flash-attention forward for sm_100a with bitfield / causal / full masks, GQA and block skipping.
+//
+//   O = softmax(scale * Q K^T + mask) V,   LSE = log sum exp   (per query row)
+//
+// One CTA = one 128-row query tile of one head.  Both GEMMs run on tcgen05 with TMEM accumulators:
+//   S = Q K^T   : A = Q tile (K-major smem), B = K tile (K-major smem)      -> TMEM S[2] (double buffer)
+//   O += P V    : A = P tile (K-major smem, written by the softmax threads), B = V tile (MN-major smem)
+// Warp roles: warp 0 = TMA producer (Q once, K/V ring of 2 stages), warp 1 = MMA issuer,
+// warps 2..5 = softmax: thread r owns query row r (one TMEM lane), so row max / row sum need no
+// shuffles.  The running maximum is only refreshed when it grows by more than 2^8 (lazy rescale),
+// which keeps the TMEM read-modify-write of O off the common path.
+//
+// Mask handling: a [B][nQ][nK] int8 class map (0 = skip tile, 1 = evaluate the predicate per element,
+// 2 = all allowed) is produced once per step by csb_mask_classify and shared by all layers, heads, the
+// forward and the backward.  Token positions may be given explicitly (context parallelism assigns
+// non-contiguous token sets to ranks), in which case causal order uses those global positions.
+//
+// Replaces the Triton kernels of the reference: cornstarch/kernel/bitfield_attention.py:215-523 (forward,
+// split-KV partials :1279-1436, compressed mask :104-156) and cornstarch/kernel/attention.py:56-345.
+#include "host.h"
+#include "mask.cuh"
+#include "ptx.cuh"
+
+namespace csb {
+
+constexpr int AT_BM = 128;
+constexpr int AT_BN = 128;
+constexpr int CHUNK_BYTES = 128 * 128;  // 128 rows x 64 bf16
+
+struct AttnFwdParams {
+  int B, Sq, Sk, Hq, Hk, D, dk16;
+  int nQ, nK;
+  float scale, scale_log2;
+  int mask_mode;
+  const int64_t* q_bits;
+  const int64_t* k_bits;
+  const int* q_pos;
+  const int* k_pos;
+  const int8_t* cls;
+  __nv_bfloat16* O;
+  long o_stride_b, o_stride_s;  // elements; head stride is D
+  float* lse;                   // [B][Hq][Sq]
+  int* status;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Tile classification: cls[b][qi][kj] = 0 (no pair allowed) / 2 (every pair allowed) / 1 (mixed).
+__global__ void __launch_bounds__(128)
+mask_classify_kernel(int mode, const int64_t* __restrict__ q_bits, const int64_t* __restrict__ k_bits,
+                     const int* __restrict__ q_pos, const int* __restrict__ k_pos, int Sq, int Sk, int bm, int bn,
+                     int nQ, int nK, int8_t* __restrict__ cls, int* __restrict__ row_work) {
+  extern __shared__ uint8_t sm[];
+  int64_t* kb_s = reinterpret_cast<int64_t*>(sm);
+  int* kp_s = reinterpret_cast<int*>(kb_s + bn);
+  const int kj = blockIdx.x, qi = blockIdx.y, b = blockIdx.z;
+  for (int i = threadIdx.x; i < bn; i += blockDim.x) {
+    const int k = kj * bn + i;
+    kb_s[i] = (k < Sk && k_bits) ? k_bits[(long)b * Sk + k] : 0;
+    kp_s[i] = (k < Sk) ? (k_pos ? k_pos[(long)b * Sk + k] : k) : -1;
+  }
+  __syncthreads();
+  int cnt = 0;
+  for (int r = threadIdx.x; r < bm; r += blockDim.x) {
+    const int q = qi * bm + r;
+    if (q >= Sq) continue;
+    const int64_t qb = q_bits ? q_bits[(long)b * Sq + q] : 0;
+    const int qp = q_pos ? q_pos[(long)b * Sq + q] : q;
+    for (int i = 0; i < bn; ++i) {
+      const bool ok = kp_s[i] >= 0 && mask_allowed(mode, qb, kb_s[i], qp, kp_s[i]);
+      cnt += ok ? 1 : 0;
+    }
+  }
+  __shared__ int red[4];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int total = red[0] + red[1] + red[2] + red[3];
+    const int valid_rows = min(bm, Sq - qi * bm);
+    int8_t c = 1;
+    if (total == 0) c = 0;
+    else if (total == valid_rows * bn) c = 2;
+    cls[((long)b * nQ + qi) * nK + kj] = c;
+    // per query block: number of non-empty key blocks (the context-parallel partitioner's workload)
+    if (row_work && c != 0) atomicAdd(&row_work[(long)b * nQ + qi], 1);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+template <int NCH>  // number of 64-wide head-dim chunks held in smem (1: D<=64, 2: D<=128)
+struct AttnSmem {
+  static constexpr int Q_BYTES = NCH * CHUNK_BYTES;
+  static constexpr int KV_BYTES = NCH * CHUNK_BYTES;
+  static constexpr int Q_OFF = 0;
+  static constexpr int K_OFF = Q_OFF + Q_BYTES;
+  static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;
+  static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;
+  static constexpr int KB_OFF = P_OFF + 2 * CHUNK_BYTES;      // int64 k bits  [2][128]
+  static constexpr int KP_OFF = KB_OFF + 2 * 128 * 8;         // int   k pos   [2][128]
+  static constexpr int BAR_OFF = KP_OFF + 2 * 128 * 4;
+  static constexpr int NBAR = 1 + 2 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 1;
+  static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;
+};
+
+__device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t phase, volatile int* abort_flag) {
+  uint64_t t0 = 0;
+  for (uint32_t i = 0; i < CSB_SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, phase)) return true;
+    if ((i & 511u) == 511u) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > CSB_WAIT_NS) return false;
+    }
+  }
+  return false;
+}
+
+template <int NCH>
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
+  using L = AttnSmem<NCH>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;
+  uint64_t* k_empty = bars + 3;
+  uint64_t* v_full = bars + 5;
+  uint64_t* v_empty = bars + 7;
+  uint64_t* s_full = bars + 9;
+  uint64_t* s_empty = bars + 11;
+  uint64_t* p_full = bars + 13;
+  uint64_t* pv_done = bars + 14;
+  uint64_t* kb_full = bars + 15;  // key bits / positions of a partial tile staged by all 128 softmax threads
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int64_t* kb_s = reinterpret_cast<int64_t*>(smem + L::KB_OFF);
+  int* kp_s = reinterpret_cast<int*>(smem + L::KP_OFF);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heaviest (last) query tiles first: under causal masks they have the most key blocks
+  const int qi = p.nQ - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hk);
+  const int q0 = qi * AT_BM;
+  const int8_t* cls_row = p.cls + ((long)b * p.nQ + qi) * p.nK;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    mbar_init(kb_full, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base;        // 2 x 128 columns
+  const uint32_t tmem_O = tmem_base + 256;  // up to 128 columns
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_expect_tx(q_full, L::Q_BYTES);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) tma_load_4d(smem + L::Q_OFF + c * CHUNK_BYTES, &tm_q, q_full, c * 64, h, q0, b);
+      uint32_t it = 0;
+      for (int j = 0; j < p.nK; ++j) {
+        if (cls_row[j] == 0) continue;
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!at_wait(&k_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_EMPTY); *abort_flag = 1; break; }
+        mbar_expect_tx(&k_full[st], L::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+          tma_load_4d(smem + L::K_OFF + st * L::KV_BYTES + c * CHUNK_BYTES, &tm_k, &k_full[st], c * 64, hk, j * AT_BN, b);
+        if (!at_wait(&v_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_EMPTY); *abort_flag = 1; break; }
+        mbar_expect_tx(&v_full[st], L::KV_BYTES);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+          tma_load_4d(smem + L::V_OFF + st * L::KV_BYTES + c * CHUNK_BYTES, &tm_v, &v_full[st], c * 64, hk, j * AT_BN, b);
+        ++it;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(AT_BM, AT_BN, 0, 0);
+      const uint32_t idesc_o = make_idesc_bf16(AT_BM, p.dk16, 0, 1);
+      const uint32_t q_s = smem_u32(smem + L::Q_OFF);
+      const uint32_t p_s = smem_u32(smem + L::P_OFF);
+      const int ksteps_s = p.dk16 / 16;
+      bool ok = at_wait(q_full, 0, abort_flag);
+      if (!ok) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; }
+      // number of non-empty key blocks
+      int n = 0;
+      for (int j = 0; j < p.nK; ++j) n += (cls_row[j] != 0);
+
+      auto issue_s = [&](uint32_t it) -> bool {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!at_wait(&k_full[st], ph, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
+        if (!at_wait(&s_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_TMEM_EMPTY); *abort_flag = 1; return false; }
+        tc_fence_after();
+        const uint32_t k_s = smem_u32(smem + L::K_OFF + st * L::KV_BYTES);
+        for (int kk = 0; kk < ksteps_s; ++kk) {
+          const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
+          umma_f16(tmem_S + st * 128, make_desc_kmajor_sw128(q_s + off), make_desc_kmajor_sw128(k_s + off), idesc_s,
+                   kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&k_empty[st]);
+        umma_commit(&s_full[st]);
+        return true;
+      };
+      if (ok && n > 0) ok = issue_s(0);
+      for (uint32_t it = 0; ok && it < (uint32_t)n; ++it) {
+        if (it + 1 < (uint32_t)n) {
+          ok = issue_s(it + 1);
+          if (!ok) break;
+        }
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!at_wait(&v_full[st], ph, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
+        if (!at_wait(p_full, it & 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
+        tc_fence_after();
+        const uint32_t v_s = smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < AT_BN / 16; ++kk) {
+          const uint32_t a_off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
+          umma_f16(tmem_O, make_desc_kmajor_sw128(p_s + a_off), make_desc_mnmajor_sw128(v_s + kk * 2048, CHUNK_BYTES),
+                   idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(&v_empty[st]);
+        umma_commit(pv_done);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax / correction / epilogue
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
+    const int q = q0 + r;
+    const bool row_valid = q < p.Sq;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    int64_t qb = 0;
+    int qpos = q;
+    if (row_valid) {
+      if (p.q_bits) qb = p.q_bits[(long)b * p.Sq + q];
+      if (p.q_pos) qpos = p.q_pos[(long)b * p.Sq + q];
+    }
+    float m_used = -INFINITY, l_sum = 0.f;
+    uint32_t it = 0, n_partial = 0;
+    bool ok = true;
+    for (int j = 0; j < p.nK && ok; ++j) {
+      const int c = cls_row[j];
+      if (c == 0) continue;
+      const int buf = it & 1;
+      if (c == 1) {
+        const int k = j * AT_BN + r;
+        const bool kv = k < p.Sk;
+        kb_s[buf * 128 + r] = (kv && p.k_bits) ? p.k_bits[(long)b * p.Sk + k] : 0;
+        kp_s[buf * 128 + r] = kv ? (p.k_pos ? p.k_pos[(long)b * p.Sk + k] : k) : -1;
+        mbar_arrive(kb_full);
+        if (!at_wait(kb_full, n_partial & 1, abort_flag)) {
+          if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        ++n_partial;
+      }
+      if (!at_wait(&s_full[buf], (it >> 1) & 1, abort_flag)) {
+        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_TMEM_FULL);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      float s[128];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_S + buf * 128 + cc * 32 + lane_addr, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[cc * 32 + i] = __uint_as_float(v[i]);
+      }
+      tc_fence_before();
+      mbar_arrive(&s_empty[buf]);
+      if (c == 1) {
+        const int64_t* kb = kb_s + buf * 128;
+        const int* kp = kp_s + buf * 128;
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          const int kpos = kp[i];
+          const bool allow = row_valid && kpos >= 0 && mask_allowed(p.mask_mode, qb, kb[i], qpos, kpos);
+          s[i] = allow ? s[i] : -INFINITY;
+        }
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      const float m_new = fmaxf(m_used, mx);
+      const bool need = (m_new - m_used) * p.scale_log2 > 8.f;  // also true when m_used is -inf and m_new is finite
+      if (it > 0) {
+        if (!at_wait(pv_done, (it - 1) & 1, abort_flag)) {
+          if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, need)) {
+          float alpha = 1.f;
+          if (need) alpha = (m_used == -INFINITY) ? 0.f : exp2f((m_used - m_new) * p.scale_log2);
+#pragma unroll
+          for (int cc = 0; cc < NCH * 2; ++cc) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem_O + cc * 32 + lane_addr, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st_32x32(tmem_O + cc * 32 + lane_addr, v);
+          }
+          tmem_st_wait();
+          l_sum *= alpha;
+        }
+      }
+      if (need) m_used = m_new;
+      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used * p.scale_log2;
+      // probabilities -> bf16 -> swizzled K-major smem tile (row r, 16-byte pieces of 8 columns)
+      uint8_t* p_row = smem + L::P_OFF;
+      float lsum = 0.f;
+#pragma unroll
+      for (int piece = 0; piece < 16; ++piece) {
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          e[i] = exp2f(s[piece * 8 + i] * p.scale_log2 - m_eff);
+          lsum += e[i];
+        }
+        uint4 u;
+        u.x = pack_bf16x2(e[0], e[1]);
+        u.y = pack_bf16x2(e[2], e[3]);
+        u.z = pack_bf16x2(e[4], e[5]);
+        u.w = pack_bf16x2(e[6], e[7]);
+        const int chunk = piece >> 3;
+        *reinterpret_cast<uint4*>(p_row + chunk * CHUNK_BYTES + sw128_offset(r, piece & 7)) = u;
+      }
+      l_sum += lsum;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full);
+      ++it;
+    }
+    // ---- epilogue
+    if (ok && it > 0) {
+      if (!at_wait(pv_done, (it - 1) & 1, abort_flag)) {
+        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
+        *abort_flag = 1;
+        ok = false;
+      }
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      __nv_bfloat16* o_row = p.O + (long)b * p.o_stride_b + (long)q * p.o_stride_s + (long)h * p.D;
+#pragma unroll
+      for (int cc = 0; cc < NCH * 2; ++cc) {
+        uint32_t v[32];
+        if (it > 0) {
+          tmem_ld_32x32(tmem_O + cc * 32 + lane_addr, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (row_valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = cc * 32 + g * 8;
+            if (col + 8 <= p.D) {
+              uint4 u;
+              u.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+              u.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+              u.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+              u.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(o_row + col) = u;
+            }
+          }
+        }
+      }
+      if (row_valid)
+        p.lse[((long)b * p.Hq + h) * p.Sq + q] = l_sum > 0.f ? m_used * p.scale + logf(l_sum) : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// 4-D view {D, H, S, B} of a [B][S][H][D]-like bf16 tensor with arbitrary token / batch strides.
+static int make_qkv_tmap(CUtensorMap* tm, const void* base, int D, int H, int S, int B, long stride_s, long stride_b) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)stride_s * 2, (uint64_t)stride_b * 2};
+  uint32_t box[4] = {64, 1, 128, 1};
+  return make_tmap_nd_bf16(tm, base, 4, dims, strides, box);
+}
+
+}  // namespace csb
+
+using namespace csb;
+
+// cls: int8 [B][nQ][nK] with nQ = ceil(Sq/bm), nK = ceil(Sk/bn).  row_work (optional, int32 [B][nQ],
+// zeroed by the caller) receives the number of non-empty key blocks of each query block.
+CSB_API int csb_mask_classify(int mode, const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
+                              int B, int Sq, int Sk, int bm, int bn, signed char* cls, int* row_work, void* stream) {
+  if (bm <= 0 || bn <= 0 || bn > 1024) return CSB_ERR_BAD_ARG;
+  const int nQ = (Sq + bm - 1) / bm, nK = (Sk + bn - 1) / bn;
+  dim3 grid(nK, nQ, B);
+  mask_classify_kernel<<<grid, 128, bn * 12, reinterpret_cast<cudaStream_t>(stream)>>>(
+      mode, reinterpret_cast<const int64_t*>(q_bits), reinterpret_cast<const int64_t*>(k_bits), q_pos, k_pos, Sq, Sk,
+      bm, bn, nQ, nK, reinterpret_cast<int8_t*>(cls), row_work);
+  return launch_result();
+}
+
+// q: [B][Sq][Hq][D], k/v: [B][Sk][Hk][D] bf16 views (head stride D, token stride *_stride_s, batch stride
+// *_stride_b, in elements); out: [B][Sq][Hq][D] view; lse: fp32 [B][Hq][Sq]; cls from csb_mask_classify
+// with bm = bn = 128.
+CSB_API int csb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
+                         int Hq, int Hk, int D, long q_stride_s, long q_stride_b, long k_stride_s, long k_stride_b,
+                         long v_stride_s, long v_stride_b, long o_stride_s, long o_stride_b, float scale, int mask_mode,
+                         const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
+                         const signed char* cls, int* status, void* stream) {
+  if (D % 8 || D > 128 || D < 16 || Hq % Hk) return CSB_ERR_BAD_ARG;
+  if ((q_stride_s % 8) || (k_stride_s % 8) || (v_stride_s % 8) || (o_stride_s % 8)) return CSB_ERR_BAD_ARG;
+  AttnFwdParams p;
+  p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hk = Hk; p.D = D;
+  p.dk16 = (D + 15) / 16 * 16;
+  p.nQ = (Sq + AT_BM - 1) / AT_BM;
+  p.nK = (Sk + AT_BN - 1) / AT_BN;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.mask_mode = mask_mode;
+  p.q_bits = reinterpret_cast<const int64_t*>(q_bits);
+  p.k_bits = reinterpret_cast<const int64_t*>(k_bits);
+  p.q_pos = q_pos; p.k_pos = k_pos;
+  p.cls = reinterpret_cast<const int8_t*>(cls);
+  p.O = reinterpret_cast<__nv_bfloat16*>(out);
+  p.o_stride_b = o_stride_b; p.o_stride_s = o_stride_s;
+  p.lse = lse;
+  p.status = status;
+  CUtensorMap tq, tk, tv;
+  int r;
+  if ((r = make_qkv_tmap(&tq, q, D, Hq, Sq, B, q_stride_s, q_stride_b))) return r;
+  if ((r = make_qkv_tmap(&tk, k, D, Hk, Sk, B, k_stride_s, k_stride_b))) return r;
+  if ((r = make_qkv_tmap(&tv, v, D, Hk, Sk, B, v_stride_s, v_stride_b))) return r;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  dim3 grid(p.nQ, Hq, B);
+  if (D <= 64) {
+    auto kfn = attn_fwd_kernel<1>;
+    static bool set1 = false;
+    if (!set1) { if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<1>::DYN_BYTES) != cudaSuccess) return launch_result(); set1 = true; }
+    kfn<<<grid, 192, AttnSmem<1>::DYN_BYTES, s>>>(tq, tk, tv, p);
+  } else {
+    auto kfn = attn_fwd_kernel<2>;
+    static bool set2 = false;
+    if (!set2) { if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<2>::DYN_BYTES) != cudaSuccess) return launch_result(); set2 = true; }
+    kfn<<<grid, 192, AttnSmem<2>::DYN_BYTES, s>>>(tq, tk, tv, p);
+  }
+  return launch_result();
+}
