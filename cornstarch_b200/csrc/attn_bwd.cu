@@ -1,0 +1,529 @@
+// Flash-attention backward for sm_100a (bitfield / causal / full masks, GQA, tile skipping).
+//
+// One CTA owns one 128-row K/V tile of one KV head and keeps dK and dV for it in TMEM for the
+// whole kernel, looping over the query heads of the GQA group and over 64-row query tiles:
+//
+//   S^T  = K  Q^T              M=128(kv) N=64(q)  contraction D     -> TMEM ST[buf]
+//   dP^T = V  dO^T             M=128     N=64     contraction D     -> TMEM dPT[buf]
+//   P^T  = exp2(S^T*c - LSE),  dS^T = P^T * (dP^T - delta) * scale   (registers -> bf16 smem tiles)
+//   dV  += P^T  dO             M=128     N=D      contraction q=64
+//   dK  += dS^T Q              M=128     N=D      contraction q=64
+//   dQ^T = K^T  dS^T           M=128(d)  N=64(q)  contraction kv=128 -> TMEM (aliases ST[buf])
+//
+// dK/dV need no atomics and are bit-reproducible: every query head that shares the KV head is
+// handled by the same CTA.  dQ^T tiles are added into an fp32 accumulator with coalesced red.add
+// (lanes = consecutive head-dim elements) and converted to bf16 by a final pass.
+//
+// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = 128 compute threads, thread r
+// owning KV row r (TMEM lane r) for S^T/dP^T/dV/dK and head-dim row r for dQ^T.
+//
+// Replaces cornstarch/kernel/bitfield_attention.py:526-929 (T8, T9: fp32 atomics for dQ, dK and dV)
+// and cornstarch/kernel/attention.py:348-852.
+#include "host.h"
+#include "mask.cuh"
+#include "ptx.cuh"
+
+namespace csb {
+
+constexpr int BW_BKV = 128;
+constexpr int BW_BQ = 64;
+constexpr int KV_CHUNK = 128 * 128;  // 128 rows x 128 B
+constexpr int Q_CHUNK = 64 * 128;    // 64 rows x 128 B
+
+struct AttnBwdParams {
+  int B, Sq, Sk, Hq, Hk, D, dk16;
+  int nQ64, nQ128, nK;
+  float scale, scale_log2;
+  int mask_mode;
+  const int64_t* q_bits;
+  const int64_t* k_bits;
+  const int* q_pos;
+  const int* k_pos;
+  const int8_t* cls;  // [B][nQ128][nK]
+  const float* lse;   // [B][Hq][Sq]
+  const float* delta; // [B][Hq][Sq]
+  float* dq_acc;      // [B][Sq][Hq][D] fp32, zeroed by the caller
+  __nv_bfloat16* dK;
+  __nv_bfloat16* dV;
+  long dk_stride_b, dk_stride_s, dv_stride_b, dv_stride_s;
+  int* status;
+};
+
+struct BwdSmem {
+  static constexpr int K_OFF = 0;
+  static constexpr int V_OFF = K_OFF + 2 * KV_CHUNK;
+  static constexpr int Q_OFF = V_OFF + 2 * KV_CHUNK;          // 2 stages x (2 chunks x 8 KB)
+  static constexpr int DO_OFF = Q_OFF + 2 * 2 * Q_CHUNK;
+  static constexpr int PT_OFF = DO_OFF + 2 * 2 * Q_CHUNK;     // [128 kv][64 q] bf16
+  static constexpr int DST_OFF = PT_OFF + KV_CHUNK;
+  static constexpr int META_OFF = DST_OFF + KV_CHUNK;         // per stage: lse2[64] f32, delta[64] f32, qpos[64] i32, qbits[64] i64
+  static constexpr int META_STAGE = 64 * 4 * 3 + 64 * 8;
+  static constexpr int BAR_OFF = META_OFF + 2 * META_STAGE;
+  static constexpr int NBAR = 1 + 2 + 2 + 2 + 2 + 1 + 1 + 2 + 1;
+  static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
+  static constexpr int DYN_BYTES = TOTAL + 1024;
+};
+
+__device__ __forceinline__ bool bw_wait(uint64_t* bar, uint32_t phase, volatile int* abort_flag) {
+  uint64_t t0 = 0;
+  for (uint32_t i = 0; i < CSB_SPIN_LIMIT; ++i) {
+    if (mbar_try_wait(bar, phase)) return true;
+    if ((i & 511u) == 511u) {
+      if (*abort_flag) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > CSB_WAIT_NS) return false;
+    }
+  }
+  return false;
+}
+
+// delta[b][h][q] = sum_d O[b][q][h][d] * dO[b][q][h][d]
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                  float* __restrict__ delta, int B, int Sq, int Hq, int D, long o_sb, long o_ss,
+                                  long do_sb, long do_ss) {
+  const long row = (blockIdx.x * (long)blockDim.x + threadIdx.x) >> 5;  // one warp per (b, q, h)
+  const int lane = threadIdx.x & 31;
+  const long total = (long)B * Sq * Hq;
+  if (row >= total) return;
+  const int h = row % Hq;
+  const long bq = row / Hq;
+  const int q = bq % Sq;
+  const int b = bq / Sq;
+  const __nv_bfloat16* o = O + b * o_sb + (long)q * o_ss + (long)h * D;
+  const __nv_bfloat16* d = dO + b * do_sb + (long)q * do_ss + (long)h * D;
+  float acc = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
+    float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
+    acc += a.x * c.x + a.y * c.y;
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+  if (lane == 0) delta[((long)b * Hq + h) * Sq + q] = acc;
+}
+
+// dq (bf16, strided) = dq_acc (fp32, dense [B][Sq][Hq][D])
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, long n_rows,
+                                       int Sq, int HD, long dq_sb, long dq_ss) {
+  const int vec = HD / 4;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n_rows * vec; i += (long)gridDim.x * blockDim.x) {
+    const long row = i / vec;
+    const int c = (i % vec) * 4;
+    const int q = row % Sq;
+    const long b = row / Sq;
+    const float4 f = *reinterpret_cast<const float4*>(acc + row * HD + c);
+    uint2 u;
+    u.x = pack_bf16x2(f.x, f.y);
+    u.y = pack_bf16x2(f.z, f.w);
+    *reinterpret_cast<uint2*>(dq + b * dq_sb + (long)q * dq_ss + c) = u;
+  }
+}
+
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                const AttnBwdParams p) {
+  using L = BwdSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;    // [2]  Q + dO stage landed
+  uint64_t* q_empty = bars + 3;   // [2]  stage consumed by dV/dK MMAs
+  uint64_t* s_full = bars + 5;    // [2]  S^T and dP^T ready in TMEM
+  uint64_t* st_free = bars + 7;   // [2]  TMEM buffer (S^T/dP^T/dQ^T) drained by the compute threads
+  uint64_t* pds_full = bars + 9;  //      P^T and dS^T tiles written to smem
+  uint64_t* pds_empty = bars + 10;//      ... and consumed by the MMAs
+  uint64_t* dq_full = bars + 11;  // [2]  dQ^T ready in TMEM
+  uint64_t* meta_full = bars + 13;//      per-iteration query metadata staged (128 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBAR);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kj = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int group = p.Hq / p.Hk;
+  const int k0 = kj * BW_BKV;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&st_free[i], 128);
+      mbar_init(&dq_full[i], 1);
+    }
+    mbar_init(pds_full, 128);
+    mbar_init(pds_empty, 1);
+    mbar_init(meta_full, 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: buf0 {ST 0..63, dPT 64..127}, buf1 {ST 128..191, dPT 192..255}, dV 256..383, dK 384..511.
+  // dQ^T of an iteration is written over the ST columns of its own buffer once they have been read.
+  const uint32_t tmem_dV = tmem_base + 256;
+  const uint32_t tmem_dK = tmem_base + 384;
+
+  // every role walks the same (query head, 64-row query tile) list and skips tiles whose class is 0
+  auto tile_class = [&](int i64) -> int { return p.cls[((long)b * p.nQ128 + (i64 >> 1)) * p.nK + kj]; };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_do);
+      mbar_expect_tx(kv_full, 4 * KV_CHUNK);
+      for (int c = 0; c < 2; ++c) {
+        tma_load_4d(smem + L::K_OFF + c * KV_CHUNK, &tm_k, kv_full, c * 64, hk, k0, b);
+        tma_load_4d(smem + L::V_OFF + c * KV_CHUNK, &tm_v, kv_full, c * 64, hk, k0, b);
+      }
+      uint32_t it = 0;
+      bool ok = true;
+      for (int hh = 0; hh < group && ok; ++hh) {
+        const int h = hk * group + hh;
+        for (int i = 0; i < p.nQ64; ++i) {
+          if (tile_class(i) == 0) continue;
+          const int st = it & 1;
+          if (!bw_wait(&q_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) {
+            atomicExch(p.status, ST_TIMEOUT_EMPTY);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&q_full[st], 4 * Q_CHUNK);
+          for (int c = 0; c < 2; ++c) {
+            tma_load_4d(smem + L::Q_OFF + (st * 2 + c) * Q_CHUNK, &tm_q, &q_full[st], c * 64, h, i * BW_BQ, b);
+            tma_load_4d(smem + L::DO_OFF + (st * 2 + c) * Q_CHUNK, &tm_do, &q_full[st], c * 64, h, i * BW_BQ, b);
+          }
+          ++it;
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = make_idesc_bf16(128, BW_BQ, 0, 0);
+      const uint32_t idesc_dkv = make_idesc_bf16(128, p.dk16, 0, 1);
+      const uint32_t idesc_dq = make_idesc_bf16(128, BW_BQ, 1, 1);
+      const uint32_t k_s = smem_u32(smem + L::K_OFF);
+      const uint32_t v_s = smem_u32(smem + L::V_OFF);
+      const uint32_t pt_s = smem_u32(smem + L::PT_OFF);
+      const uint32_t dst_s = smem_u32(smem + L::DST_OFF);
+      const int ksteps_d = p.dk16 / 16;
+      int n = 0;
+      for (int i = 0; i < p.nQ64; ++i) n += (tile_class(i) != 0);
+      n *= group;
+      bool ok = bw_wait(kv_full, 0, abort_flag);
+      if (!ok) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; }
+
+      auto issue_s = [&](uint32_t it) -> bool {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (!bw_wait(&q_full[st], ph, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
+        if (!bw_wait(&st_free[st], ph ^ 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_TMEM_EMPTY); *abort_flag = 1; return false; }
+        tc_fence_after();
+        const uint32_t q_s = smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK);
+        const uint32_t do_s = smem_u32(smem + L::DO_OFF + st * 2 * Q_CHUNK);
+        const uint32_t t_st = tmem_base + st * 128;
+        for (int kk = 0; kk < ksteps_d; ++kk) {
+          const uint32_t a_off = (kk >> 2) * KV_CHUNK + (kk & 3) * 32;
+          const uint32_t b_off = (kk >> 2) * Q_CHUNK + (kk & 3) * 32;
+          umma_f16(t_st, make_desc_kmajor_sw128(k_s + a_off), make_desc_kmajor_sw128(q_s + b_off), idesc_s, kk > 0);
+        }
+        for (int kk = 0; kk < ksteps_d; ++kk) {
+          const uint32_t a_off = (kk >> 2) * KV_CHUNK + (kk & 3) * 32;
+          const uint32_t b_off = (kk >> 2) * Q_CHUNK + (kk & 3) * 32;
+          umma_f16(t_st + 64, make_desc_kmajor_sw128(v_s + a_off), make_desc_kmajor_sw128(do_s + b_off), idesc_s, kk > 0);
+        }
+        umma_commit(&s_full[st]);
+        return true;
+      };
+
+      if (ok && n > 0) ok = issue_s(0);
+      for (uint32_t it = 0; ok && it < (uint32_t)n; ++it) {
+        const int st = it & 1;
+        if (!bw_wait(pds_full, it & 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
+        tc_fence_after();
+        const uint32_t q_s = smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK);
+        const uint32_t do_s = smem_u32(smem + L::DO_OFF + st * 2 * Q_CHUNK);
+        // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows)
+#pragma unroll
+        for (int kk = 0; kk < BW_BQ / 16; ++kk)
+          umma_f16(tmem_dV, make_desc_kmajor_sw128(pt_s + kk * 32), make_desc_mnmajor_sw128(do_s + kk * 2048, Q_CHUNK),
+                   idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < BW_BQ / 16; ++kk)
+          umma_f16(tmem_dK, make_desc_kmajor_sw128(dst_s + kk * 32), make_desc_mnmajor_sw128(q_s + kk * 2048, Q_CHUNK),
+                   idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&q_empty[st]);
+        // dQ^T = K^T dS^T  (contraction over the 128 key rows), into the ST columns of this buffer
+#pragma unroll
+        for (int kk = 0; kk < BW_BKV / 16; ++kk)
+          umma_f16(tmem_base + st * 128, make_desc_mnmajor_sw128(k_s + kk * 2048, KV_CHUNK),
+                   make_desc_mnmajor_sw128(dst_s + kk * 2048, KV_CHUNK), idesc_dq, kk > 0 ? 1u : 0u);
+        umma_commit(pds_empty);
+        umma_commit(&dq_full[st]);
+        if (it + 1 < (uint32_t)n) ok = issue_s(it + 1);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ compute threads
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;  // KV row in the tile == TMEM lane; also head-dim row of dQ^T
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int kidx = k0 + r;
+    const bool k_valid = kidx < p.Sk;
+    const int64_t kb = (k_valid && p.k_bits) ? p.k_bits[(long)b * p.Sk + kidx] : 0;
+    const int kpos = k_valid ? (p.k_pos ? p.k_pos[(long)b * p.Sk + kidx] : kidx) : -1;
+    const float LOG2E = 1.4426950408889634f;
+
+    uint32_t it = 0;
+    bool ok = true;
+    int prev_h = 0, prev_i = 0;
+
+    auto drain_dq = [&](uint32_t pit, int ph, int pi) -> bool {
+      const int st = pit & 1;
+      if (!bw_wait(&dq_full[st], (pit >> 1) & 1, abort_flag)) {
+        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_TMEM_FULL);
+        *abort_flag = 1;
+        return false;
+      }
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + st * 128 + cc * 32 + lane_addr, v);
+        tmem_ld_wait();
+        if (r < p.D) {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            const int q = pi * BW_BQ + cc * 32 + c;
+            if (q < p.Sq) atomicAdd(p.dq_acc + (((long)b * p.Sq + q) * p.Hq + ph) * p.D + r, __uint_as_float(v[c]));
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&st_free[st]);
+      return true;
+    };
+
+    for (int hh = 0; hh < group && ok; ++hh) {
+      const int h = hk * group + hh;
+      for (int i = 0; i < p.nQ64 && ok; ++i) {
+        const int c = tile_class(i);
+        if (c == 0) continue;
+        const int st = it & 1;
+        // ---- stage the per-query metadata of this tile
+        float* m_lse = reinterpret_cast<float*>(smem + L::META_OFF + st * L::META_STAGE);
+        float* m_delta = m_lse + 64;
+        int* m_qpos = reinterpret_cast<int*>(m_delta + 64);
+        int64_t* m_qbits = reinterpret_cast<int64_t*>(m_qpos + 64);
+        if (r < 64) {
+          const int q = i * BW_BQ + r;
+          const bool qv = q < p.Sq;
+          const long idx = ((long)b * p.Hq + h) * p.Sq + q;
+          m_lse[r] = qv ? p.lse[idx] * LOG2E : INFINITY;
+          m_delta[r] = qv ? p.delta[idx] : 0.f;
+          m_qpos[r] = qv ? (p.q_pos ? p.q_pos[(long)b * p.Sq + q] : q) : -1;
+          m_qbits[r] = (qv && p.q_bits) ? p.q_bits[(long)b * p.Sq + q] : 0;
+        }
+        mbar_arrive(meta_full);
+        if (!bw_wait(meta_full, it & 1, abort_flag)) {
+          if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        // ---- S^T and dP^T from TMEM
+        if (!bw_wait(&s_full[st], (it >> 1) & 1, abort_flag)) {
+          if (lane == 0) atomicExch(p.status, ST_TIMEOUT_TMEM_FULL);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        float pv[64], ds[64];
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t sv[32], dv[32];
+          tmem_ld_32x32(tmem_base + st * 128 + cc * 32 + lane_addr, sv);
+          tmem_ld_32x32(tmem_base + st * 128 + 64 + cc * 32 + lane_addr, dv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            const int col = cc * 32 + x;
+            float pr = exp2f(__uint_as_float(sv[x]) * p.scale_log2 - m_lse[col]);
+            if (c == 1) {
+              const bool allow = k_valid && m_qpos[col] >= 0 && mask_allowed(p.mask_mode, m_qbits[col], kb, m_qpos[col], kpos);
+              pr = allow ? pr : 0.f;
+            }
+            pv[col] = pr;
+            ds[col] = pr * (__uint_as_float(dv[x]) - m_delta[col]) * p.scale;
+          }
+        }
+        // ---- P^T / dS^T -> bf16 smem tiles (row r, 8 pieces of 8 query columns)
+        if (it > 0) {
+          if (!bw_wait(pds_empty, (it - 1) & 1, abort_flag)) {
+            if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+        }
+#pragma unroll
+        for (int piece = 0; piece < 8; ++piece) {
+          uint4 u, w;
+          u.x = pack_bf16x2(pv[piece * 8 + 0], pv[piece * 8 + 1]);
+          u.y = pack_bf16x2(pv[piece * 8 + 2], pv[piece * 8 + 3]);
+          u.z = pack_bf16x2(pv[piece * 8 + 4], pv[piece * 8 + 5]);
+          u.w = pack_bf16x2(pv[piece * 8 + 6], pv[piece * 8 + 7]);
+          w.x = pack_bf16x2(ds[piece * 8 + 0], ds[piece * 8 + 1]);
+          w.y = pack_bf16x2(ds[piece * 8 + 2], ds[piece * 8 + 3]);
+          w.z = pack_bf16x2(ds[piece * 8 + 4], ds[piece * 8 + 5]);
+          w.w = pack_bf16x2(ds[piece * 8 + 6], ds[piece * 8 + 7]);
+          const uint32_t off = sw128_offset(r, piece);
+          *reinterpret_cast<uint4*>(smem + L::PT_OFF + off) = u;
+          *reinterpret_cast<uint4*>(smem + L::DST_OFF + off) = w;
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(pds_full);
+        // ---- drain dQ^T of the previous iteration while the MMAs of this one run
+        if (it > 0) ok = drain_dq(it - 1, prev_h, prev_i);
+        prev_h = h;
+        prev_i = i;
+        ++it;
+      }
+    }
+    if (ok && it > 0) ok = drain_dq(it - 1, prev_h, prev_i);
+    // ---- epilogue: dV and dK tiles (every MMA has retired once the last dQ^T was seen)
+    if (ok) {
+      tc_fence_after();
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t t = which == 0 ? tmem_dV : tmem_dK;
+        __nv_bfloat16* base = which == 0 ? p.dV + (long)b * p.dv_stride_b + (long)kidx * p.dv_stride_s + (long)hk * p.D
+                                         : p.dK + (long)b * p.dk_stride_b + (long)kidx * p.dk_stride_s + (long)hk * p.D;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t v[32];
+          if (it > 0) {
+            tmem_ld_32x32(t + cc * 32 + lane_addr, v);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int x = 0; x < 32; ++x) v[x] = 0u;
+          }
+          if (k_valid) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = cc * 32 + g * 8;
+              if (col + 8 <= p.D) {
+                uint4 u;
+                u.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+                u.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+                u.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+                u.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+                *reinterpret_cast<uint4*>(base + col) = u;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+static int make_tmap_4d(CUtensorMap* tm, const void* base, int D, int H, int S, int B, long stride_s, long stride_b,
+                        int box_rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)D * 2, (uint64_t)stride_s * 2, (uint64_t)stride_b * 2};
+  uint32_t box[4] = {64, 1, (uint32_t)box_rows, 1};
+  return make_tmap_nd_bf16(tm, base, 4, dims, strides, box);
+}
+
+}  // namespace csb
+
+using namespace csb;
+
+// All tensors are [B][S][H][D] bf16 views (head stride D; token/batch strides in elements).
+// lse: fp32 [B][Hq][Sq] from the forward; delta: fp32 [B][Hq][Sq] scratch; dq_acc: fp32 dense
+// [B][Sq][Hq][D] scratch that the caller has zeroed.  cls: tile classes for 128x128 tiles.
+CSB_API int csb_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                         const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq,
+                         int Sk, int Hq, int Hk, int D, long q_ss, long q_sb, long k_ss, long k_sb, long v_ss, long v_sb,
+                         long o_ss, long o_sb, long do_ss, long do_sb, long dq_ss, long dq_sb, long dk_ss, long dk_sb,
+                         long dv_ss, long dv_sb, float scale, int mask_mode, const long* q_bits, const long* k_bits,
+                         const int* q_pos, const int* k_pos, const signed char* cls, int* status, void* stream) {
+  if (D % 8 || D > 128 || D < 16 || Hq % Hk) return CSB_ERR_BAD_ARG;
+  if ((q_ss % 8) || (k_ss % 8) || (v_ss % 8) || (do_ss % 8) || (dq_ss % 4) || (dk_ss % 8) || (dv_ss % 8)) return CSB_ERR_BAD_ARG;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  {
+    const long rows = (long)B * Sq * Hq;
+    const int threads = 256;
+    const long blocks = (rows * 32 + threads - 1) / threads;
+    attn_delta_kernel<<<(unsigned)blocks, threads, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(out),
+                                                           reinterpret_cast<const __nv_bfloat16*>(dout), delta, B, Sq, Hq,
+                                                           D, o_sb, o_ss, do_sb, do_ss);
+  }
+  AttnBwdParams p;
+  p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hk = Hk; p.D = D;
+  p.dk16 = (D + 15) / 16 * 16;
+  p.nQ64 = (Sq + BW_BQ - 1) / BW_BQ;
+  p.nQ128 = (Sq + 127) / 128;
+  p.nK = (Sk + BW_BKV - 1) / BW_BKV;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.mask_mode = mask_mode;
+  p.q_bits = reinterpret_cast<const int64_t*>(q_bits);
+  p.k_bits = reinterpret_cast<const int64_t*>(k_bits);
+  p.q_pos = q_pos; p.k_pos = k_pos;
+  p.cls = reinterpret_cast<const int8_t*>(cls);
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
+  p.dK = reinterpret_cast<__nv_bfloat16*>(dk);
+  p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
+  p.dk_stride_b = dk_sb; p.dk_stride_s = dk_ss; p.dv_stride_b = dv_sb; p.dv_stride_s = dv_ss;
+  p.status = status;
+  CUtensorMap tq, tk, tv, tdo;
+  int r;
+  if ((r = make_tmap_4d(&tq, q, D, Hq, Sq, B, q_ss, q_sb, BW_BQ))) return r;
+  if ((r = make_tmap_4d(&tk, k, D, Hk, Sk, B, k_ss, k_sb, BW_BKV))) return r;
+  if ((r = make_tmap_4d(&tv, v, D, Hk, Sk, B, v_ss, v_sb, BW_BKV))) return r;
+  if ((r = make_tmap_4d(&tdo, dout, D, Hq, Sq, B, do_ss, do_sb, BW_BQ))) return r;
+  static bool attr = false;
+  if (!attr) {
+    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::DYN_BYTES) != cudaSuccess)
+      return launch_result();
+    attr = true;
+  }
+  dim3 grid(p.nK, Hk, B);
+  attn_bwd_kernel<<<grid, 192, BwdSmem::DYN_BYTES, s>>>(tq, tk, tv, tdo, p);
+  int e = launch_result();
+  if (e) return e;
+  const long n_rows = (long)B * Sq;
+  const int HD = Hq * D;
+  long work = n_rows * (HD / 4);
+  int blocks = (int)((work + 255) / 256 < (long)sm_count() * 16 ? (work + 255) / 256 : (long)sm_count() * 16);
+  attn_dq_convert_kernel<<<blocks, 256, 0, s>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), n_rows, Sq, HD, dq_sb, dq_ss);
+  return launch_result();
+}

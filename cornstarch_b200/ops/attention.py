@@ -37,8 +37,7 @@ nat.declare(
 )
 nat.declare(
     "csb_attn_bwd",
-    [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i64, i64, i64, i64, i64, i64, i64, i64,
-     i64, i64, i64, i64, i64, i64, f32, i32, vp, vp, vp, vp, vp, vp, vp],
+    [vp] * 11 + [i32] * 6 + [i64] * 16 + [f32, i32, vp, vp, vp, vp, vp, vp, vp],
 )
 
 

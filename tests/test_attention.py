@@ -100,3 +100,76 @@ def test_fwd_strided_qkv_and_cross_lengths():
     ro, rlse = A.attention_reference(q, k, v, mask)
     _close(o, ro)
     _close(lse, rlse, 2e-2)
+
+
+def _ref_grads(q, k, v, mask, do):
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    o, _ = A.attention_reference(qf, kf, vf, mask)
+    o.backward(do.float())
+    return qf.grad, kf.grad, vf.grad
+
+
+@pytest.mark.parametrize("D", [32, 64, 72, 128])
+@pytest.mark.parametrize("S", [57, 128, 283, 512])
+@pytest.mark.parametrize("mode", ["causal", "full"])
+def test_bwd_dense_modes(D, S, mode):
+    q, k, v = _qkv(2, S, S, 4, 2, D, seed=S * 3 + D)
+    mask = A.AttnMask.causal() if mode == "causal" else A.AttnMask.full()
+    do = torch.randn_like(q)
+    o, lse = A.attention_forward(q, k, v, mask)
+    dq, dk, dv = A.attention_backward(do, q, k, v, o, lse, mask)
+    rq, rk, rv = _ref_grads(q, k, v, mask, do)
+    _close(dq, rq)
+    _close(dk, rk)
+    _close(dv, rv)
+
+
+@pytest.mark.parametrize("hk", [1, 2, 3, 6])
+@pytest.mark.parametrize("S", [144, 1024])
+@pytest.mark.parametrize("prefix", [False, True])
+def test_bwd_bitfield_gqa(hk, S, prefix):
+    B, Hq, D = 2, 6, 64
+    q, k, v = _qkv(B, S, S, Hq, hk, D, seed=S + hk + 11)
+    bits = make_bitfield(B, S, seed=S + 1, pad_tail=7).cuda()
+    mask = A.AttnMask.bitfield(bits, prefix_causal=prefix)
+    do = torch.randn_like(q)
+    o, lse = A.attention_forward(q, k, v, mask)
+    dq, dk, dv = A.attention_backward(do, q, k, v, o, lse, mask)
+    rq, rk, rv = _ref_grads(q, k, v, mask, do)
+    _close(dq, rq)
+    _close(dk, rk)
+    _close(dv, rv)
+
+
+def test_bwd_deterministic_dkdv():
+    q, k, v = _qkv(1, 640, 640, 8, 2, 128, seed=9)
+    mask = A.AttnMask.causal()
+    do = torch.randn_like(q)
+    o, lse = A.attention_forward(q, k, v, mask)
+    a = A.attention_backward(do, q, k, v, o, lse, mask)
+    b = A.attention_backward(do, q, k, v, o, lse, mask)
+    assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+
+
+def test_autograd_function_strided():
+    B, S, Hq, Hk, D = 1, 384, 8, 2, 128
+    fused = torch.randn(B, S, (Hq + 2 * Hk) * D, device="cuda").bfloat16().requires_grad_(True)
+    q = fused[..., : Hq * D].view(B, S, Hq, D)
+    k = fused[..., Hq * D : (Hq + Hk) * D].view(B, S, Hk, D)
+    v = fused[..., (Hq + Hk) * D :].view(B, S, Hk, D)
+    o = A.attention(q, k, v, A.AttnMask.causal())
+    w = torch.randn_like(o)
+    (o.float() * w.float()).sum().backward()
+    ff = fused.detach().float().requires_grad_(True)
+    qf = ff[..., : Hq * D].view(B, S, Hq, D)
+    kf = ff[..., Hq * D : (Hq + Hk) * D].view(B, S, Hk, D)
+    vf = ff[..., (Hq + Hk) * D :].view(B, S, Hk, D)
+    ro, _ = A.attention_reference(qf, kf, vf, A.AttnMask.causal())
+    (ro * w.float()).sum().backward()
+    _close(fused.grad, ff.grad)
+
+
+def test_status_clean_after_attention():
+    from cornstarch_b200.ops import _native as nat
+
+    assert nat.check_status() == 0
