@@ -1,0 +1,226 @@
+"""Model base classes: HF-style configs, ``save_pretrained`` / ``from_pretrained``, pipeline hooks.
+
+Models in this package are written from scratch with HF-compatible parameter names and
+``config.json`` fields, so a checkpoint directory produced here (``config.json`` +
+``model.safetensors`` or sharded safetensors + ``model.safetensors.index.json``) has the layout the
+reference produces through HF ``PreTrainedModel`` (tests/test_utils/test_pretrained_projection.py:75-80
+in the reference).  Instead of patching HF forwards per policy (cornstarch/shardformer/modeling/*.py),
+each model natively understands pipeline stages: :meth:`PreTrainedModel.module_names` lists the
+pipeline-assignable units in order (the reference's ``get_all_modules``) and
+:meth:`PreTrainedModel.hold_only` drops everything a stage does not own.
+"""
+
+from __future__ import annotations
+
+import copy
+import json
+import os
+from typing import Any
+
+import torch
+import torch.nn as nn
+
+CONFIG_NAME = "config.json"
+WEIGHTS_NAME = "model.safetensors"
+WEIGHTS_INDEX_NAME = "model.safetensors.index.json"
+
+_MODEL_REGISTRY: dict[str, tuple[type, type]] = {}
+
+
+def register_model(model_type: str, config_cls: type, model_cls: type) -> None:
+    """``AutoConfig`` / ``AutoModel`` style registration keyed by ``model_type``."""
+    _MODEL_REGISTRY[model_type] = (config_cls, model_cls)
+
+
+def registered(model_type: str):
+    return _MODEL_REGISTRY.get(model_type)
+
+
+class PretrainedConfig:
+    """Attribute bag with HF ``config.json`` round-tripping.  Subclasses set ``model_type`` and defaults."""
+
+    model_type: str = ""
+
+    def __init__(self, **kwargs):
+        for k, v in kwargs.items():
+            setattr(self, k, v)
+
+    def to_dict(self) -> dict[str, Any]:
+        out = {}
+        for k, v in self.__dict__.items():
+            if k.startswith("_"):
+                continue
+            if isinstance(v, PretrainedConfig):
+                v = v.to_dict()
+            elif isinstance(v, torch.dtype):
+                v = str(v).replace("torch.", "")
+            out[k] = v
+        out["model_type"] = self.model_type
+        return out
+
+    @classmethod
+    def from_dict(cls, d: dict[str, Any]):
+        d = dict(d)
+        d.pop("model_type", None)
+        return cls(**d)
+
+    @classmethod
+    def from_hf(cls, hf_config):
+        """Build from a ``transformers`` config object (or anything with ``to_dict``)."""
+        d = hf_config.to_dict() if hasattr(hf_config, "to_dict") else dict(hf_config)
+        return cls.from_dict(d)
+
+    def save_pretrained(self, path: str) -> None:
+        os.makedirs(path, exist_ok=True)
+        with open(os.path.join(path, CONFIG_NAME), "w") as f:
+            json.dump(self.to_dict(), f, indent=2, sort_keys=True)
+
+    @classmethod
+    def from_pretrained(cls, path: str):
+        with open(os.path.join(path, CONFIG_NAME)) as f:
+            d = json.load(f)
+        if cls is PretrainedConfig:
+            reg = registered(d.get("model_type", ""))
+            if reg is not None:
+                return reg[0].from_dict(d)
+        return cls.from_dict(d)
+
+    def __repr__(self):
+        return f"{type(self).__name__}({self.to_dict()})"
+
+    def __eq__(self, other):
+        return isinstance(other, PretrainedConfig) and self.to_dict() == other.to_dict()
+
+
+class PreTrainedModel(nn.Module):
+    """Common behaviour of every model: config, (de)serialisation, pipeline-stage pruning."""
+
+    config_class = PretrainedConfig
+    # names of sub-modules that can be placed on a pipeline stage, produced by `module_names(config)`
+    supports_gradient_checkpointing = True
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.gradient_checkpointing = False
+        self._held: set[str] | None = None  # None = everything
+
+    # ---- pipeline -------------------------------------------------------------------------
+    @classmethod
+    def module_names(cls, config) -> list[str]:
+        """Ordered names of the pipeline-assignable units (``PipelineTemplate.get_modules``)."""
+        raise NotImplementedError
+
+    def holds(self, name: str) -> bool:
+        return self._held is None or name in self._held
+
+    def hold_only(self, names: list[str]) -> None:
+        """Release every pipeline unit that is not in ``names`` (its parameters are freed)."""
+        all_names = self.module_names(self.config)
+        unknown = set(names) - set(all_names)
+        assert not unknown, f"unknown module names {sorted(unknown)}"
+        self._held = set(names)
+        for n in all_names:
+            if n in self._held:
+                continue
+            parent, attr = self._resolve_parent(n)
+            if parent is None:
+                continue
+            if isinstance(parent, (nn.ModuleList, nn.Sequential)):
+                parent[int(attr)] = _Released()
+            else:
+                setattr(parent, attr, _Released())
+
+    def _resolve_parent(self, dotted: str):
+        obj = self
+        parts = dotted.split(".")
+        for p in parts[:-1]:
+            if not hasattr(obj, p) and not (isinstance(obj, (nn.ModuleList, nn.Sequential)) and p.isdigit()):
+                return None, None
+            obj = obj[int(p)] if p.isdigit() else getattr(obj, p)
+        last = parts[-1]
+        if isinstance(obj, (nn.ModuleList, nn.Sequential)) and last.isdigit():
+            return obj, last
+        return (obj, last) if hasattr(obj, last) else (None, None)
+
+    # ---- checkpointing of activations -----------------------------------------------------------
+    def gradient_checkpointing_enable(self, gradient_checkpointing_kwargs: dict | None = None):
+        self.gradient_checkpointing = True
+        for m in self.modules():
+            if m is not self and isinstance(m, PreTrainedModel):
+                m.gradient_checkpointing = True
+
+    def gradient_checkpointing_disable(self):
+        self.gradient_checkpointing = False
+        for m in self.modules():
+            if m is not self and isinstance(m, PreTrainedModel):
+                m.gradient_checkpointing = False
+
+    # ---- (de)serialisation ---------------------------------------------------------------------
+    def save_pretrained(self, path: str, max_shard_size: int | None = None, safe_serialization: bool = True):
+        from ..checkpoint.io import save_state_dict_sharded
+
+        os.makedirs(path, exist_ok=True)
+        self.config.save_pretrained(path)
+        sd = {k: v.detach().cpu().contiguous() for k, v in self.state_dict().items()}
+        save_state_dict_sharded(sd, path, max_shard_size=max_shard_size, use_safetensors=safe_serialization)
+
+    @classmethod
+    def from_pretrained(cls, path: str, config=None, dtype=None, device=None, strict: bool = True, **kwargs):
+        from ..checkpoint.io import load_state_dict_any
+
+        if config is None:
+            config = cls.config_class.from_pretrained(path)
+        model = cls(config, **kwargs)
+        sd = load_state_dict_any(path)
+        missing, unexpected = model.load_state_dict(sd, strict=False)
+        if strict and (missing or unexpected):
+            raise RuntimeError(f"from_pretrained: missing={missing} unexpected={unexpected}")
+        if dtype is not None or device is not None:
+            model = model.to(device=device, dtype=dtype)
+        return model
+
+    @property
+    def device(self):
+        try:
+            return next(self.parameters()).device
+        except StopIteration:
+            return torch.device("cpu")
+
+    @property
+    def dtype(self):
+        try:
+            return next(self.parameters()).dtype
+        except StopIteration:
+            return torch.float32
+
+    def num_parameters(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+
+class _Released(nn.Module):
+    """Placeholder left where a pipeline unit was released; calling it is a bug in the stage plan."""
+
+    def forward(self, *a, **k):
+        raise RuntimeError("this module is not held by the current pipeline stage")
+
+
+def is_released(m) -> bool:
+    return isinstance(m, _Released)
+
+
+class ModelOutput(dict):
+    """Dict with attribute access (``out.loss``, ``out["logits"]``), the shape HF models return."""
+
+    def __getattr__(self, k):
+        try:
+            return self[k]
+        except KeyError as e:
+            raise AttributeError(k) from e
+
+    def __setattr__(self, k, v):
+        self[k] = v
+
+
+def clone_config(config):
+    return copy.deepcopy(config)
