@@ -1,0 +1,414 @@
+"""``MultimodalModel``: unimodal encoders + projectors + a language model, composed at run time.
+
+Public classes mirror the reference (cornstarch/models/multimodal_language_model/
+modeling_multimodal_language_model.py:330-1240): :class:`MultimodalProjectorConfig`,
+:class:`MultimodalProjector`, :class:`ModalModuleBase`, :class:`ModalEncoderModule`,
+:class:`ModalDecoderModule`, :class:`MultimodalModel`.
+
+Differences that come from building it for one process per B200 rather than translating it:
+
+* The merge of encoder features into the token embeddings is ONE gather kernel driven by an int32
+  source index computed on the device (``cumsum`` of the placeholder matches); there is no
+  ``masked_scatter`` and no ``.item()`` / ``.tolist()`` round trip per step (the reference syncs twice,
+  :923 and :947).  Counts are only checked on the host when ``check_counts=True``.
+* The attention mask handed to the LLM is always the bitfield mask built from the placeholder ids
+  (text sees everything causally, each modality is bidirectional inside itself); padding positions of
+  the incoming 0/1 mask become 0.
+"""
+
+from __future__ import annotations
+
+import inspect
+from collections import OrderedDict
+from typing import Any, Callable
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from .. import nn as cnn
+from ..kernel.interface import create_bitfield_attention_mask, create_instance_bitfield_attention_mask
+from ..models.base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, register_model
+from ..ops import attention as A
+from ..ops import elementwise as E
+
+_ACTIVATIONS = {"gelu", "gelu_new", "gelu_pytorch_tanh", "gelu_tanh", "quick_gelu", "silu", "swish", "relu"}
+
+
+class MultimodalProjectorConfig(PretrainedConfig):
+    model_type = "multimodal-projector"
+
+    def __init__(self, encoder_config=None, text_config=None, projection_type: str = "linear", activation: str = "gelu",
+                 **kwargs):
+        if projection_type not in ("linear", "mlp", "qformer"):
+            raise ValueError(f"Unsupported projection type: {projection_type}. Supported: 'linear', 'mlp', 'qformer'.")
+        if projection_type != "linear" and activation not in _ACTIVATIONS:
+            raise ValueError(f"Unsupported activation function: {activation}. Supported: {sorted(_ACTIVATIONS)}.")
+        self.projection_type = projection_type
+        self.activation = activation
+        super().__init__(**kwargs)
+        if encoder_config is not None:
+            hidden = getattr(encoder_config, "hidden_size", None) or getattr(encoder_config, "d_model")
+            self.in_features = hidden
+            self.encoder_model_type = getattr(encoder_config, "model_type", "")
+        if text_config is not None:
+            self.out_features = text_config.hidden_size
+            self.language_model_type = getattr(text_config, "model_type", "")
+
+
+class _Activation(nn.Module):
+    def __init__(self, name):
+        super().__init__()
+        self.name = name
+
+    def forward(self, x):
+        return E.activation(x, self.name)
+
+
+class MultimodalProjector(PreTrainedModel):
+    """``projection`` = ``Sequential(linear)`` or ``Sequential(in_proj, activation, out_proj)``.
+
+    State-dict keys: ``projection.linear.*`` / ``projection.in_proj.*``, ``projection.out_proj.*``.
+    ``post_projection`` is an identity hook that context parallelism replaces with a sequence gather.
+    """
+
+    config_class = MultimodalProjectorConfig
+    main_input_name = "inputs_embeds"
+
+    def __init__(self, config: MultimodalProjectorConfig, projection: nn.Module | None = None):
+        super().__init__(config)
+        if projection is not None:
+            self.projection = projection
+        elif config.projection_type == "linear":
+            self.projection = nn.Sequential(OrderedDict([("linear", cnn.Linear(config.in_features, config.out_features))]))
+        elif config.projection_type == "mlp":
+            self.projection = nn.Sequential(OrderedDict([
+                ("in_proj", cnn.Linear(config.in_features, config.out_features)),
+                ("activation", _Activation(config.activation)),
+                ("out_proj", cnn.Linear(config.out_features, config.out_features)),
+            ]))
+        else:
+            raise NotImplementedError("qformer projector is not implemented (nor is it in the reference)")
+        self.post_projection: Callable[[torch.Tensor], torch.Tensor] = lambda x: x
+
+    @classmethod
+    def module_names(cls, config) -> list[str]:
+        if config.projection_type == "linear":
+            return ["projection"]
+        return ["in_proj", "activation", "out_proj"]
+
+    def forward(self, inputs_embeds: torch.Tensor, return_dict: bool = True):
+        def run(x):
+            return self.projection(x)
+
+        if self.gradient_checkpointing and self.training and torch.is_grad_enabled() and inputs_embeds.requires_grad:
+            out = checkpoint(run, inputs_embeds, use_reentrant=False)
+        else:
+            out = run(inputs_embeds)
+        out = self.post_projection(out)
+        return ModelOutput(hidden_states=out) if return_dict else (out,)
+
+
+register_model("multimodal-projector", MultimodalProjectorConfig, MultimodalProjector)
+
+
+class ModalModuleBase(nn.Module):
+    """An encoder/decoder ``module`` plus its ``projector``."""
+
+    def __init__(self, model: nn.Module, projector: MultimodalProjector | None = None):
+        super().__init__()
+        self.module = model
+        self.projector = projector
+        self.config = (model.config, projector.config if projector else None)
+        if projector is not None:
+            hidden = getattr(model.config, "hidden_size", None) or getattr(model.config, "d_model")
+            if isinstance(self, ModalEncoderModule):
+                assert projector.config.in_features == hidden, (
+                    f"Input features of projector ({projector.config.in_features}) should be equal to hidden size of model ({hidden}).")
+            elif isinstance(self, ModalDecoderModule):
+                assert projector.config.out_features == hidden, (
+                    f"Output features of projector ({projector.config.out_features}) should be equal to hidden size of model ({hidden}).")
+            else:
+                raise ValueError("ModalModule should be either ModalEncoderModule or ModalDecoderModule.")
+
+    def train(self, module: bool = True, projector: bool | None = None):
+        projector = module if projector is None else projector
+        self.module.train(module)
+        if self.projector is not None:
+            self.projector.train(projector)
+        self.training = module or projector
+        return self
+
+    def get_modules(self) -> list[nn.Module]:
+        return [self.module] + ([self.projector] if self.projector is not None else [])
+
+
+def _identity_inputs(inputs):
+    return inputs
+
+
+def _identity_output(inputs, output):
+    return output
+
+
+class ModalEncoderModule(ModalModuleBase):
+    """Encoder + projector with three user callbacks; returns ``None`` when its main input is absent from the batch."""
+
+    def __init__(self, model: nn.Module, projector: MultimodalProjector | None = None, additional_args: list[str] = (),
+                 preprocess_callback: Callable[[dict[str, Any]], dict[str, Any]] = _identity_inputs,
+                 postprocess_module_callback: Callable = _identity_output,
+                 postprocess_projector_callback: Callable = _identity_output):
+        super().__init__(model, projector)
+        self.additional_args = list(additional_args)
+        self.preprocess_callback = preprocess_callback
+        self.postprocess_module_callback = postprocess_module_callback
+        self.postprocess_projector_callback = postprocess_projector_callback
+
+    def forward_arg_names(self) -> list[str]:
+        return [k for k in inspect.signature(self.module.forward).parameters.keys() if k not in ("self", "kw", "kwargs")]
+
+    def forward(self, return_dict: bool | None = None, output_attentions=None, output_hidden_states=None, **kwargs):
+        kwargs = self.preprocess_callback(inputs=kwargs)
+        params = self.forward_arg_names()
+        if params[0] not in kwargs or kwargs[params[0]] is None:
+            return None  # this batch carries no input for the modality
+        outputs = self.module(**{k: v for k, v in kwargs.items() if k in params})
+        if isinstance(outputs, torch.Tensor):
+            outputs = ModelOutput(last_hidden_state=outputs)
+        outputs = self.postprocess_module_callback(inputs=kwargs, output=outputs)
+        if self.projector is None:
+            return outputs
+        first = outputs[0] if isinstance(outputs, (tuple, list)) else next(iter(outputs.values()))
+        outputs = self.projector(first, return_dict=True)
+        return self.postprocess_projector_callback(inputs=kwargs, output=outputs)
+
+
+class ModalDecoderModule(ModalModuleBase):
+    def __init__(self, model: nn.Module, projector: MultimodalProjector):
+        super().__init__(model, projector)
+
+    def forward(self, *args, return_dict: bool | None = None, **kwargs):
+        if self.projector is None:
+            return self.module(*args, **kwargs)
+        projected = self.projector(*args, **kwargs)
+        return self.module(_first_tensor(projected))
+
+
+def _first_tensor(output) -> torch.Tensor:
+    if isinstance(output, torch.Tensor):
+        return output
+    if isinstance(output, (tuple, list)):
+        return output[0]
+    return next(iter(output.values()))
+
+
+class MultimodalModel(nn.Module):
+    """Encoders (``<key>_encoder`` sub-modules) + ``language_model``."""
+
+    def __init__(self, encoders: dict[str, ModalEncoderModule] | None = None, language_model: nn.Module | None = None,
+                 preprocess_llm_callback: Callable | None = None, init_projector_type: str = "linear",
+                 init_activation: str = "gelu", mask_mode: str = "modality"):
+        super().__init__()
+        encoders = encoders or {}
+        self.encoders_keys = list(encoders.keys())
+        for key, enc in encoders.items():
+            if enc.projector is None and language_model is not None:
+                pc = MultimodalProjectorConfig(encoder_config=enc.module.config, text_config=language_model.config,
+                                               projection_type=init_projector_type, activation=init_activation)
+                enc.projector = MultimodalProjector(pc)
+                enc.config = (enc.module.config, pc)
+            if enc.projector is not None and language_model is not None:
+                hidden = getattr(enc.module.config, "hidden_size", None) or getattr(enc.module.config, "d_model")
+                assert enc.projector.config.in_features == hidden, "projector input size must equal the encoder hidden size"
+                assert enc.projector.config.out_features == language_model.config.hidden_size, (
+                    "projector output size must equal the language model hidden size")
+            setattr(self, f"{key}_encoder", enc)
+        self.language_model = language_model
+        self.preprocess_llm_callback = preprocess_llm_callback
+        self.token_ids: dict[str, int] | None = None
+        # "modality": one bit per modality (reference rule); "instance": one bit per image/audio instance + prefix-causal
+        self.mask_mode = mask_mode
+        self.check_counts = False
+
+    # ------------------------------------------------------------------ structure helpers
+    @property
+    def encoders(self) -> dict[str, ModalEncoderModule]:
+        return {k: getattr(self, f"{k}_encoder") for k in self.encoders_keys}
+
+    def get_input_embeddings(self):
+        return self.language_model.get_input_embeddings()
+
+    def gradient_checkpointing_enable(self, gradient_checkpointing_kwargs: dict | None = None):
+        """Always non-reentrant (the reference forces ``use_reentrant=False``, :774-792)."""
+        for enc in self.encoders.values():
+            if hasattr(enc.module, "gradient_checkpointing_enable"):
+                enc.module.gradient_checkpointing_enable()
+            if enc.projector is not None:
+                enc.projector.gradient_checkpointing_enable()
+        if self.language_model is not None and hasattr(self.language_model, "gradient_checkpointing_enable"):
+            self.language_model.gradient_checkpointing_enable()
+
+    def train(self, encoders_mode: dict[str, tuple[bool, bool]] | bool | None = None, llm_mode: bool | None = True):
+        """Freeze / unfreeze by ``requires_grad``: ``encoders_mode = {key: (encoder, projector)}``; ``None`` leaves a part as is."""
+        if isinstance(encoders_mode, bool):
+            # nn.Module.train(mode) / .eval() compatibility
+            mode = encoders_mode
+            nn.Module.train(self, mode)
+            return self
+        nn.Module.train(self, True)
+        if encoders_mode is not None:
+            for key, (enc_mode, proj_mode) in encoders_mode.items():
+                enc = getattr(self, f"{key}_encoder")
+                enc.train(enc_mode, proj_mode)
+                for p in enc.module.parameters():
+                    p.requires_grad_(bool(enc_mode) and p.dtype.is_floating_point and not getattr(p, "_always_frozen", False))
+                if enc.projector is not None:
+                    for p in enc.projector.parameters():
+                        p.requires_grad_(bool(proj_mode))
+        if llm_mode is not None and self.language_model is not None:
+            self.language_model.train(llm_mode)
+            for p in self.language_model.parameters():
+                p.requires_grad_(bool(llm_mode))
+        return self
+
+    def eval(self):
+        nn.Module.train(self, False)
+        return self
+
+    def set_modality_token_ids(self, token_ids: dict[str, int], new_num_tokens: int = 0):
+        """Called by :class:`MultimodalProcessor`; maps modality key -> placeholder token id."""
+        self.token_ids = dict(token_ids)
+
+    # ------------------------------------------------------------------ mask + merge
+    def create_bitfield_attention_mask(self, input_ids: torch.Tensor, padding_mask: torch.Tensor | None = None):
+        ordered = {k: self.token_ids[k] for k in self.token_ids}
+        if self.mask_mode == "instance":
+            return create_instance_bitfield_attention_mask(input_ids, ordered, padding_mask)
+        return create_bitfield_attention_mask(input_ids, ordered, padding_mask)
+
+    def build_attn_mask(self, input_ids, padding_mask=None) -> A.AttnMask:
+        bits = self.create_bitfield_attention_mask(input_ids, padding_mask)
+        return A.AttnMask.bitfield(bits, prefix_causal=(self.mask_mode == "instance"))
+
+    def merge_source_index(self, input_ids: torch.Tensor, feature_counts: dict[str, int]) -> torch.Tensor:
+        """int32 ``[B*S]``: ``>= 0`` = embedding row (token id), ``< 0`` = ``-(row of the concatenated features) - 1``."""
+        flat = input_ids.reshape(-1)
+        src = flat.to(torch.int32)
+        offset = 0
+        for key, n in feature_counts.items():
+            tid = self.token_ids[key]
+            is_m = flat == tid
+            rank = torch.cumsum(is_m.to(torch.int32), dim=0) - 1
+            src = torch.where(is_m, -(rank + offset) - 1, src)
+            if self.check_counts:
+                got = int(is_m.sum().item())
+                if got != n:
+                    raise ValueError(f"Number of {key} tokens {got} should be equal to number of {key} features {n}.")
+            offset += n
+        return src
+
+    def merge_encoder_outputs(self, encoders_outputs: dict[str, Any], input_ids: torch.Tensor,
+                              inputs_embeds: torch.Tensor | None = None, attention_mask: torch.Tensor | None = None):
+        """Scatter encoder features into the token embeddings at the placeholder positions.
+
+        Returns ``(inputs_embeds [B,S,H], bitfield_mask [B,S] int64)``.  When ``inputs_embeds`` is ``None`` the
+        embedding lookup and the scatter run as one kernel.
+        """
+        if self.token_ids is None:
+            raise ValueError("token_ids must be set before merging encoder outputs. Call `MultimodalModel.set_modality_token_ids()`.")
+        feats, counts = [], OrderedDict()
+        hidden = self.language_model.config.hidden_size
+        for key in self.token_ids:  # bit order == token_ids order; feature order must match merge_source_index
+            if key not in encoders_outputs or encoders_outputs[key] is None:
+                continue
+            out = _first_tensor(encoders_outputs[key])
+            out = out.reshape(-1, out.shape[-1])
+            if out.shape[-1] != hidden:
+                raise ValueError(f"Expected encoder output hidden_size {out.shape[-1]} to be equal to inputs_embeds hidden_size {hidden}.")
+            feats.append(out)
+            counts[key] = out.shape[0]
+        for key in encoders_outputs:
+            if encoders_outputs[key] is not None and key not in self.token_ids:
+                raise ValueError(f"Token ID for {key} is not set. Call `MultimodalModel.set_modality_token_ids()`.")
+        emb = self.language_model.get_input_embeddings()
+        B, S = input_ids.shape
+        if feats:
+            allf = feats[0] if len(feats) == 1 else torch.cat(feats, dim=0)
+            src = self.merge_source_index(input_ids, counts)
+            sharded_vocab = isinstance(emb, cnn.VocabParallelEmbedding) and cnn._ws(emb.process_group) > 1
+            if inputs_embeds is None and sharded_vocab:
+                # vocab-parallel lookup first (placeholder ids masked to 0), features scattered in afterwards
+                inputs_embeds = emb(torch.where(src.view(B, S) < 0, torch.zeros_like(input_ids), input_ids))
+            if inputs_embeds is None:
+                merged = emb(input_ids, allf.to(emb.weight.dtype), src)
+            else:
+                flat = inputs_embeds.reshape(B * S, -1)
+                is_f = (src < 0)[:, None]
+                merged = torch.where(is_f, allf.to(flat.dtype)[(-src.long() - 1).clamp(min=0)], flat).view(B, S, -1)
+        else:
+            merged = inputs_embeds if inputs_embeds is not None else emb(input_ids)
+        bits = self.create_bitfield_attention_mask(input_ids, attention_mask)
+        return merged, bits
+
+    # ------------------------------------------------------------------ forward
+    def encode(self, **kwargs) -> dict[str, Any]:
+        outs = {}
+        for key in self.encoders_keys:
+            enc = getattr(self, f"{key}_encoder")
+            names = set(enc.forward_arg_names()) | set(enc.additional_args)
+            outs[key] = enc(**{k: v for k, v in kwargs.items() if k in names})
+        return outs
+
+    def forward(self, input_ids: torch.Tensor | None = None, attention_mask: torch.Tensor | None = None,
+                position_ids: torch.Tensor | None = None, inputs_embeds: torch.Tensor | None = None,
+                labels: torch.Tensor | None = None, **kwargs):
+        enc_out = self.encode(**kwargs)
+        if self.language_model is None:
+            return enc_out
+        have = {k: v for k, v in enc_out.items() if v is not None}
+        if labels is not None and self.token_ids:
+            # placeholder positions never contribute to the loss
+            ignore = torch.zeros_like(labels, dtype=torch.bool)
+            for tid in self.token_ids.values():
+                ignore |= input_ids == tid
+            labels = torch.where(ignore, torch.full_like(labels, -100), labels)
+        if self.token_ids:
+            embeds, bits = self.merge_encoder_outputs(have, input_ids, inputs_embeds, attention_mask)
+            mask = A.AttnMask.bitfield(bits, prefix_causal=(self.mask_mode == "instance"))
+        else:
+            embeds = inputs_embeds if inputs_embeds is not None else self.language_model.get_input_embeddings()(input_ids)
+            mask = attention_mask
+        llm_inputs = dict(input_ids=None, inputs_embeds=embeds, attention_mask=mask, position_ids=position_ids,
+                          labels=labels, **kwargs)
+        if self.preprocess_llm_callback is not None:
+            llm_inputs = self.preprocess_llm_callback(llm_inputs)
+        params = inspect.signature(self.language_model.forward).parameters
+        accepts_kw = any(p.kind == inspect.Parameter.VAR_KEYWORD for p in params.values())
+        enc_args = set()
+        for enc in self.encoders.values():
+            enc_args |= set(enc.forward_arg_names()) | set(enc.additional_args)
+        llm_inputs = {k: v for k, v in llm_inputs.items()
+                      if (k in params) or (accepts_kw and k not in enc_args)}
+        return self.language_model(**llm_inputs)
+
+    @torch.no_grad()
+    def generate(self, input_ids: torch.Tensor, max_new_tokens: int = 16, attention_mask=None, eos_token_id=None, **kwargs):
+        """Greedy decoding without a KV cache (each step re-runs the prefix; enough for evaluation-sized prompts)."""
+        ids = input_ids
+        enc_out = {k: v for k, v in self.encode(**kwargs).items() if v is not None}
+        finished = torch.zeros(ids.shape[0], dtype=torch.bool, device=ids.device)
+        for _ in range(max_new_tokens):
+            if self.token_ids:
+                embeds, bits = self.merge_encoder_outputs(enc_out, ids, None, None)
+                mask = A.AttnMask.bitfield(bits, prefix_causal=(self.mask_mode == "instance"))
+            else:
+                embeds, mask = self.language_model.get_input_embeddings()(ids), None
+            out = self.language_model(inputs_embeds=embeds, attention_mask=mask)
+            nxt = out.logits[:, -1].argmax(-1)
+            if eos_token_id is not None:
+                nxt = torch.where(finished, torch.full_like(nxt, eos_token_id), nxt)
+                finished |= nxt == eos_token_id
+            ids = torch.cat([ids, nxt[:, None]], dim=1)
+            if eos_token_id is not None and bool(finished.all()):
+                break
+        return ids

@@ -62,20 +62,48 @@ def lib():
             f"native library {p} not found: run `python -m cornstarch_b200.csrc.build` "
             "(CUDA tensors never fall back to eager PyTorch)"
         )
-    _LIB = C.CDLL(str(p))
+    raw = C.CDLL(str(p))
     for name, args in _PROTOS.items():
-        if hasattr(_LIB, name):
-            fn = getattr(_LIB, name)
+        if hasattr(raw, name):
+            fn = getattr(raw, name)
             fn.argtypes = args
             fn.restype = C.c_int
+    _LIB = _CountingLib(raw)
     return _LIB
+
+
+class _CountingLib:
+    """Forwards attribute access to the CDLL and counts calls of kernel-launching entry points."""
+
+    _NO_LAUNCH = {"csb_norm_bwd_parts", "csb_colsum_parts"}
+
+    def __init__(self, raw):
+        self._raw = raw
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            target = getattr(self._raw, name)
+            if name in self._NO_LAUNCH:
+                fn = target
+            else:
+                def fn(*a, _t=target):
+                    global launch_count
+                    launch_count += 1
+                    return _t(*a)
+            self._cache[name] = fn
+        return fn
+
+
+launch_count = 0
 
 
 def declare(name: str, argtypes: list) -> None:
     """Register the prototype of one more exported function (used by optional modules)."""
     _PROTOS[name] = argtypes
-    if _LIB is not None and hasattr(_LIB, name):
-        fn = getattr(_LIB, name)
+    if _LIB is not None and hasattr(_LIB._raw, name):
+        fn = getattr(_LIB._raw, name)
         fn.argtypes = argtypes
         fn.restype = C.c_int
 

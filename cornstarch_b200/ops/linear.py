@@ -99,10 +99,12 @@ class _LinearFn(torch.autograd.Function):
         has_bias = biases[0] is not None
         fused_b = (fuse_adjacent_1d(biases) if n_w > 1 else biases[0]) if has_bias else None
         n_total = sum(w.shape[0] for w in weights)
+        # the returned tensor owns its storage (callers such as RoPE modify it in place)
+        out = torch.empty((*x.shape[:-1], n_total), dtype=x.dtype, device=x.device)
+        y = out.view(-1, n_total)
         if fused_w is not None and (not has_bias or fused_b is not None):
-            y = gemm(x2, fused_w, bias=fused_b, act=act)
+            gemm(x2, fused_w, bias=fused_b, act=act, out=y)
         else:
-            y = torch.empty((x2.shape[0], n_total), dtype=x.dtype, device=x.device)
             o = 0
             for w, b in zip(weights, biases):
                 gemm(x2, w, bias=b, act=act, out=y[:, o : o + w.shape[0]])
@@ -113,7 +115,7 @@ class _LinearFn(torch.autograd.Function):
         ctx.x_shape = x.shape
         ctx.biases = biases
         assert act is None, "activation epilogues are applied outside autograd-tracked linears"
-        return y.view(*x.shape[:-1], n_total)
+        return out
 
     @staticmethod
     def backward(ctx, dy):

@@ -1,0 +1,312 @@
+"""Fused AdamW over flat parameter / gradient / state buffers ("arena"), with optional ZeRO-1 sharding.
+
+On CUDA with bf16 parameters the optimizer re-homes every parameter into one contiguous bf16 buffer per
+weight-decay group (in module order, so q/k/v and gate/up weights end up adjacent and can run as one
+GEMM), gives every parameter a ``main_grad`` view into a flat gradient buffer (the linear / norm /
+embedding backward kernels accumulate straight into it) and keeps fp32 master weights and Adam moments
+flat as well.  One kernel launch per group then does: unscale / clip, Adam moments, decoupled weight
+decay, master update, bf16 write-back and gradient zeroing.  The global gradient norm is a reduction
+kernel plus a 1-thread kernel that turns it into the clip factor on the device, so a step has no host
+synchronisation.
+
+With ``zero_stage=1`` and a data-parallel group each rank keeps the master weights and moments of its
+1/dp slice only: gradients are reduce-scattered (or all-reduced by the caller), the slice is updated, the
+bf16 parameters are all-gathered.
+
+On CPU (or non-bf16 parameters) the same math runs in PyTorch on ordinary ``.grad`` tensors; this is
+the oracle of the GPU test and the path of the CPU/gloo tests.
+
+Stands in for ``torch.optim.Adam(fused=True)`` plus ColossalAI's ``HybridParallelAMPOptimizer`` /
+``HybridParallelNaiveOptimizer`` (master weights, gradient clipping across tp/pp, dynamic loss scale),
+used at cornstarch/plugin/multimodal_parallel_plugin/multimodal_parallel_plugin.py:627-654.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Iterable
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _native as nat
+
+ALIGN = 64  # elements; keeps every parameter 128-byte aligned inside the arena
+
+
+class _Region:
+    """One weight-decay group laid out flat."""
+
+    def __init__(self, params: list[torch.nn.Parameter], grad_dtype: torch.dtype, shard: tuple[int, int] | None):
+        dev = params[0].device
+        self.params = params
+        self.offsets = []
+        n = 0
+        for p in params:
+            self.offsets.append(n)
+            n += (p.numel() + ALIGN - 1) // ALIGN * ALIGN
+        ws = shard[1] if shard else 1
+        pad_to = ALIGN * ws
+        self.numel = (n + pad_to - 1) // pad_to * pad_to
+        self.flat_param = torch.zeros(self.numel, dtype=torch.bfloat16, device=dev)
+        self.flat_grad = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
+        for p, off in zip(params, self.offsets):
+            view = self.flat_param[off : off + p.numel()].view(p.shape)
+            view.copy_(p.data)
+            p.data = view
+            p.main_grad = self.flat_grad[off : off + p.numel()].view(p.shape)
+            p.grad_added_to_main_grad = False
+        if shard:
+            r, ws = shard
+            per = self.numel // ws
+            self.lo, self.hi = r * per, (r + 1) * per
+        else:
+            self.lo, self.hi = 0, self.numel
+        k = self.hi - self.lo
+        self.master = self.flat_param[self.lo : self.hi].float()
+        self.exp_avg = torch.zeros(k, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(k, dtype=torch.float32, device=dev)
+
+
+class FusedAdamW(torch.optim.Optimizer):
+    def __init__(self, params: Iterable, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.01, max_norm: float = 0.0, grad_dtype: torch.dtype = torch.bfloat16,
+                 zero_stage: int = 0, dp_group=None, norm_groups: list | None = None, use_arena: bool | None = None):
+        defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
+        super().__init__(params, defaults)
+        self.max_norm = max_norm
+        self.grad_dtype = grad_dtype
+        self.zero_stage = zero_stage
+        self.dp_group = dp_group
+        self.norm_groups = norm_groups or []  # extra groups (tp, pp) over which the squared norm is summed
+        self.loss_scale = 1.0
+        self._step = 0
+        self._regions: list[tuple[dict, _Region]] = []
+        all_params = [p for g in self.param_groups for p in g["params"]]
+        cuda_bf16 = bool(all_params) and all(p.is_cuda and p.dtype == torch.bfloat16 for p in all_params)
+        self.use_arena = cuda_bf16 if use_arena is None else (use_arena and cuda_bf16)
+        if self.use_arena:
+            self._build_arena()
+
+    # ------------------------------------------------------------------ arena path
+    def _build_arena(self):
+        shard = None
+        if self.zero_stage >= 1 and self.dp_group is not None and dist.get_world_size(self.dp_group) > 1:
+            shard = (dist.get_rank(self.dp_group), dist.get_world_size(self.dp_group))
+        for g in self.param_groups:
+            ps = [p for p in g["params"] if p.requires_grad]
+            if ps:
+                self._regions.append((g, _Region(ps, self.grad_dtype, shard)))
+        dev = self._regions[0][1].flat_param.device
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._scale = torch.ones(1, dtype=torch.float32, device=dev)
+        self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._skip = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._sharded = shard is not None
+
+    def flat_grads(self) -> list[torch.Tensor]:
+        """The flat gradient buffers (what data-parallel reduction works on)."""
+        return [r.flat_grad for _, r in self._regions]
+
+    def flat_params(self) -> list[torch.Tensor]:
+        return [r.flat_param for _, r in self._regions]
+
+    def _fold_stray_grads(self):
+        """Gradients autograd left in ``.grad`` (ops without main_grad fusion) are added to ``main_grad``."""
+        for _, r in self._regions:
+            for p in r.params:
+                if p.grad is not None:
+                    p.main_grad.add_(p.grad.to(p.main_grad.dtype))
+                    p.grad = None
+
+    def _step_arena(self):
+        lib = nat.lib()
+        st = nat.stream()
+        self._fold_stray_grads()
+        if self._sharded:
+            ws = dist.get_world_size(self.dp_group)
+            for _, r in self._regions:
+                if not getattr(self, "grads_already_reduced", False):
+                    out = r.flat_grad[r.lo : r.hi]
+                    dist.reduce_scatter_tensor(out, r.flat_grad, op=dist.ReduceOp.AVG, group=self.dp_group)
+        inv_scale = 1.0 / self.loss_scale
+        need_norm = self.max_norm > 0 or self.loss_scale != 1.0
+        if need_norm:
+            self._sumsq.zero_()
+            for _, r in self._regions:
+                g = r.flat_grad[r.lo : r.hi]
+                nat.check(lib.csb_sumsq(g.data_ptr(), int(g.dtype == torch.float32), g.numel(), self._sumsq.data_ptr(), st), "csb_sumsq")
+            groups = list(self.norm_groups) + ([self.dp_group] if self._sharded else [])
+            for grp in groups:
+                if grp is not None and dist.get_world_size(grp) > 1:
+                    dist.all_reduce(self._sumsq, group=grp)
+            nat.check(lib.csb_clip_scale(self._sumsq.data_ptr(), float(self.max_norm), inv_scale, self._scale.data_ptr(),
+                                         self._norm.data_ptr(), self._skip.data_ptr(), st), "csb_clip_scale")
+        self._step += 1
+        for g, r in self._regions:
+            b1, b2 = g["betas"]
+            bc1 = 1.0 - b1 ** self._step
+            bc2 = 1.0 - b2 ** self._step
+            grad = r.flat_grad[r.lo : r.hi]
+            param = r.flat_param[r.lo : r.hi]
+            nat.check(
+                lib.csb_adamw(param.data_ptr(), r.master.data_ptr(), r.exp_avg.data_ptr(), r.exp_avg_sq.data_ptr(),
+                              grad.data_ptr(), int(grad.dtype == torch.float32), grad.numel(), float(g["lr"]), b1, b2,
+                              float(g["eps"]), float(g["weight_decay"]), bc1, bc2,
+                              self._scale.data_ptr() if need_norm else None, self._skip.data_ptr() if need_norm else None,
+                              1, st),
+                "csb_adamw",
+            )
+            if self._sharded:
+                if r.lo > 0:
+                    r.flat_grad[: r.lo].zero_()
+                if r.hi < r.numel:
+                    r.flat_grad[r.hi :].zero_()
+                dist.all_gather_into_tensor(r.flat_param, param.clone(), group=self.dp_group)
+            for p in r.params:
+                p.grad_added_to_main_grad = False
+
+    # ------------------------------------------------------------------ plain path (CPU / fp32)
+    @torch.no_grad()
+    def _step_plain(self):
+        params = [p for g in self.param_groups for p in g["params"] if p.grad is not None]
+        inv_scale = 1.0 / self.loss_scale
+        scale = inv_scale
+        if self.max_norm > 0 or self.loss_scale != 1.0:
+            sq = torch.zeros((), dtype=torch.float32, device=params[0].device if params else "cpu")
+            for p in params:
+                sq = sq + p.grad.float().pow(2).sum()
+            for grp in self.norm_groups:
+                if grp is not None and dist.get_world_size(grp) > 1:
+                    dist.all_reduce(sq, group=grp)
+            norm = sq.sqrt() * inv_scale
+            self._last_norm = norm
+            if not torch.isfinite(norm):
+                return
+            if self.max_norm > 0:
+                scale = inv_scale * min(1.0, self.max_norm / (float(norm) + 1e-6))
+        self._step += 1
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            bc1, bc2 = 1.0 - b1 ** self._step, 1.0 - b2 ** self._step
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["master"] = p.detach().float().clone()
+                    st["exp_avg"] = torch.zeros_like(st["master"])
+                    st["exp_avg_sq"] = torch.zeros_like(st["master"])
+                gr = p.grad.float() * scale
+                st["exp_avg"].mul_(b1).add_(gr, alpha=1 - b1)
+                st["exp_avg_sq"].mul_(b2).addcmul_(gr, gr, value=1 - b2)
+                denom = (st["exp_avg_sq"] / bc2).sqrt().add_(g["eps"])
+                st["master"].mul_(1 - g["lr"] * g["weight_decay"]).addcdiv_(st["exp_avg"] / bc1, denom, value=-g["lr"])
+                p.copy_(st["master"].to(p.dtype))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        if self.use_arena:
+            self._step_arena()
+        else:
+            self._step_plain()
+        return loss
+
+    def zero_grad(self, set_to_none: bool = True):
+        if self.use_arena:
+            # the fused step already cleared the flat gradient buffer; only stray .grad tensors remain
+            for _, r in self._regions:
+                for p in r.params:
+                    p.grad = None
+            return
+        super().zero_grad(set_to_none)
+
+    def clear_main_grads(self):
+        for _, r in self._regions:
+            r.flat_grad.zero_()
+
+    def grad_norm(self) -> torch.Tensor | None:
+        """Global gradient norm of the last step (device scalar; reading it synchronises)."""
+        if self.use_arena:
+            return self._norm
+        return getattr(self, "_last_norm", None)
+
+    # ------------------------------------------------------------------ state dict in the per-parameter layout
+    def state_dict(self):
+        if not self.use_arena:
+            sd = super().state_dict()
+            sd["fused_step"] = self._step
+            return sd
+        # expose flat state as per-parameter tensors (ids follow param_groups order, like torch)
+        state, idx = {}, 0
+        index_of = {}
+        for g in self.param_groups:
+            for p in g["params"]:
+                index_of[id(p)] = idx
+                idx += 1
+        for _, r in self._regions:
+            for p, off in zip(r.params, r.offsets):
+                lo, hi = off, off + p.numel()
+                if lo >= r.lo and hi <= r.hi:
+                    s = slice(lo - r.lo, hi - r.lo)
+                    state[index_of[id(p)]] = {
+                        "master": r.master[s].view(p.shape).clone(),
+                        "exp_avg": r.exp_avg[s].view(p.shape).clone(),
+                        "exp_avg_sq": r.exp_avg_sq[s].view(p.shape).clone(),
+                    }
+        groups = []
+        start = 0
+        for g in self.param_groups:
+            d = {k: v for k, v in g.items() if k != "params"}
+            d["params"] = list(range(start, start + len(g["params"])))
+            start += len(g["params"])
+            groups.append(d)
+        return {"state": state, "param_groups": groups, "fused_step": self._step}
+
+    def load_state_dict(self, sd):
+        self._step = int(sd.get("fused_step", 0))
+        if not self.use_arena:
+            sd = {k: v for k, v in sd.items() if k != "fused_step"}
+            return super().load_state_dict(sd)
+        index_of, idx = {}, 0
+        for g in self.param_groups:
+            for p in g["params"]:
+                index_of[id(p)] = idx
+                idx += 1
+        for g, saved in zip(self.param_groups, sd["param_groups"]):
+            for k, v in saved.items():
+                if k != "params":
+                    g[k] = v
+        for _, r in self._regions:
+            for p, off in zip(r.params, r.offsets):
+                st = sd["state"].get(index_of[id(p)])
+                if st is None:
+                    continue
+                lo, hi = off, off + p.numel()
+                if lo >= r.lo and hi <= r.hi:
+                    s = slice(lo - r.lo, hi - r.lo)
+                    r.master[s].copy_(st["master"].reshape(-1))
+                    r.exp_avg[s].copy_(st["exp_avg"].reshape(-1))
+                    r.exp_avg_sq[s].copy_(st["exp_avg_sq"].reshape(-1))
+
+    def update_master_params(self):
+        """Re-read master weights from the (just loaded) bf16 parameters."""
+        for _, r in self._regions:
+            r.master.copy_(r.flat_param[r.lo : r.hi].float())
+
+
+def split_decay_groups(model: torch.nn.Module, weight_decay: float = 0.01) -> list[dict]:
+    """Two param groups in module order: matrices (decayed) and vectors (norm weights, biases; not decayed)."""
+    decay, no_decay, seen = [], [], set()
+    for p in model.parameters():
+        if not p.requires_grad or id(p) in seen:
+            continue
+        seen.add(id(p))
+        (decay if p.dim() >= 2 else no_decay).append(p)
+    groups = []
+    if decay:
+        groups.append({"params": decay, "weight_decay": weight_decay})
+    if no_decay:
+        groups.append({"params": no_decay, "weight_decay": 0.0})
+    return groups
