@@ -3,19 +3,24 @@
 // One CTA owns one 128-row K/V tile of one KV head and keeps dK and dV for it in TMEM for the
 // whole kernel, looping over the query heads of the GQA group and over 64-row query tiles:
 //
-//   S^T  = K  Q^T              M=128(kv) N=64(q)  contraction D     -> TMEM ST[buf]
-//   dP^T = V  dO^T             M=128     N=64     contraction D     -> TMEM dPT[buf]
+//   S^T  = K  Q^T              M=128(kv) N=64(q)  contraction D     -> TMEM S^T[2] (double buffer)
+//   dP^T = V  dO^T             M=128     N=64     contraction D     -> TMEM dP^T
 //   P^T  = exp2(S^T*c - LSE),  dS^T = P^T * (dP^T - delta) * scale   (registers -> bf16 smem tiles)
 //   dV  += P^T  dO             M=128     N=D      contraction q=64
 //   dK  += dS^T Q              M=128     N=D      contraction q=64
-//   dQ^T = K^T  dS^T           M=128(d)  N=64(q)  contraction kv=128 -> TMEM (aliases ST[buf])
+//   dQ^T = K^T  dS^T           M=128(d)  N=64(q)  contraction kv=128 -> TMEM dQ^T
 //
 // dK/dV need no atomics and are bit-reproducible: every query head that shares the KV head is
 // handled by the same CTA.  dQ^T tiles are added into an fp32 accumulator with coalesced red.add
 // (lanes = consecutive head-dim elements) and converted to bf16 by a final pass.
 //
-// Warp roles: warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 = 128 compute threads, thread r
-// owning KV row r (TMEM lane r) for S^T/dP^T/dV/dK and head-dim row r for dQ^T.
+// Warp roles (320 threads): warp 0 = TMA producer (K/V once, Q/dO ring of 3 stages), warp 1 = MMA
+// issuer, warps 2..9 = 256 compute threads.  Thread (r, half) owns KV row r (TMEM lane r) and 32 of
+// the 64 query columns of S^T / dP^T, and head-dim row r of dQ^T.  The pipeline keeps S^T one
+// iteration ahead: while the compute warps turn S^T(i), dP^T(i) into P^T, dS^T, the tensor core
+// already holds S^T(i+1); dP^T(i+1) is issued as soon as dP^T(i) has been read, before the
+// dV/dK/dQ^T MMAs of iteration i, so the next exponentials overlap those MMAs.  Per-tile query
+// metadata (LSE, delta, positions, bitfields) is prefetched into registers one iteration early.
 //
 // Replaces cornstarch/kernel/bitfield_attention.py:526-929 (T8, T9: fp32 atomics for dQ, dK and dV)
 // and cornstarch/kernel/attention.py:348-852.
@@ -50,19 +55,25 @@ struct AttnBwdParams {
 };
 
 struct BwdSmem {
+  static constexpr int QSTAGES = 3;
   static constexpr int K_OFF = 0;
   static constexpr int V_OFF = K_OFF + 2 * KV_CHUNK;
-  static constexpr int Q_OFF = V_OFF + 2 * KV_CHUNK;          // 2 stages x (2 chunks x 8 KB)
-  static constexpr int DO_OFF = Q_OFF + 2 * 2 * Q_CHUNK;
-  static constexpr int PT_OFF = DO_OFF + 2 * 2 * Q_CHUNK;     // [128 kv][64 q] bf16
+  static constexpr int Q_OFF = V_OFF + 2 * KV_CHUNK;          // QSTAGES x (2 chunks x 8 KB)
+  static constexpr int DO_OFF = Q_OFF + QSTAGES * 2 * Q_CHUNK;
+  static constexpr int PT_OFF = DO_OFF + QSTAGES * 2 * Q_CHUNK;  // [128 kv][64 q] bf16
   static constexpr int DST_OFF = PT_OFF + KV_CHUNK;
-  static constexpr int META_OFF = DST_OFF + KV_CHUNK;         // per stage: lse2[64] f32, delta[64] f32, qpos[64] i32, qbits[64] i64
+  static constexpr int META_OFF = DST_OFF + KV_CHUNK;         // per buffer: lse2[64] f32, delta[64] f32, qpos[64] i32, qbits[64] i64
   static constexpr int META_STAGE = 64 * 4 * 3 + 64 * 8;
-  static constexpr int BAR_OFF = META_OFF + 2 * META_STAGE;
-  static constexpr int NBAR = 1 + 2 + 2 + 2 + 2 + 1 + 1 + 2 + 1;
-  static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
+  static constexpr int LIST_OFF = META_OFF + 2 * META_STAGE;  // valid 64-row query tiles of this key block: int16 index, int8 class
+  static constexpr int MAX_TILES = 1024;                      // sequences up to 65536 tokens
+  static constexpr int BAR_OFF = LIST_OFF + MAX_TILES * 4;
+  static constexpr int NBAR = 1 + QSTAGES + QSTAGES + 1 + 1 + 1 + 1 + 1 + 1;
+  static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 32;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
+
+constexpr int BW_COMPUTE_THREADS = 256;
+constexpr int BW_THREADS = 64 + BW_COMPUTE_THREADS;
 
 __device__ __forceinline__ bool bw_wait(uint64_t* bar, uint32_t phase, volatile int* abort_flag) {
   uint64_t t0 = 0;
@@ -120,25 +131,29 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloa
   }
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
                 const AttnBwdParams p) {
   using L = BwdSmem;
+  constexpr int QS = L::QSTAGES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* kv_full = bars;
-  uint64_t* q_full = bars + 1;    // [2]  Q + dO stage landed
-  uint64_t* q_empty = bars + 3;   // [2]  stage consumed by dV/dK MMAs
-  uint64_t* s_full = bars + 5;    // [2]  S^T and dP^T ready in TMEM
-  uint64_t* st_free = bars + 7;   // [2]  TMEM buffer (S^T/dP^T/dQ^T) drained by the compute threads
-  uint64_t* pds_full = bars + 9;  //      P^T and dS^T tiles written to smem
-  uint64_t* pds_empty = bars + 10;//      ... and consumed by the MMAs
-  uint64_t* dq_full = bars + 11;  // [2]  dQ^T ready in TMEM
-  uint64_t* meta_full = bars + 13;//      per-iteration query metadata staged (128 arrivals)
+  uint64_t* q_full = bars + 1;            // [QS]  Q + dO stage landed
+  uint64_t* q_empty = q_full + QS;        // [QS]  stage consumed by the dV/dK MMAs
+  uint64_t* sdp_full = q_empty + QS;      //       S^T and dP^T of an iteration ready in TMEM
+  uint64_t* pds_full = sdp_full + 1;      //       P^T and dS^T tiles written to smem (256 arrivals)
+  uint64_t* pds_empty = pds_full + 1;     //       ... and consumed by the MMAs
+  uint64_t* dq_full = pds_empty + 1;      //       dQ^T ready in TMEM
+  uint64_t* dq_free = dq_full + 1;        //       dQ^T drained (256 arrivals)
+  uint64_t* meta_full = dq_free + 1;      //       per-iteration query metadata staged (256 arrivals)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* n_valid_slot = reinterpret_cast<int*>(tmem_slot + 2);
+  int16_t* tile_idx = reinterpret_cast<int16_t*>(smem + L::LIST_OFF);
+  int8_t* tile_cls = reinterpret_cast<int8_t*>(smem + L::LIST_OFF + L::MAX_TILES * 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kj = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
@@ -147,17 +162,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < QS; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&st_free[i], 128);
-      mbar_init(&dq_full[i], 1);
     }
-    mbar_init(pds_full, 128);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, BW_COMPUTE_THREADS);
     mbar_init(pds_empty, 1);
-    mbar_init(meta_full, 128);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_free, BW_COMPUTE_THREADS);
+    mbar_init(meta_full, BW_COMPUTE_THREADS);
     *abort_flag = 0;
+    // list of the 64-row query tiles that have at least one allowed pair with this key block
+    int n = 0;
+    for (int i = 0; i < p.nQ64 && n < L::MAX_TILES; ++i) {
+      const int8_t c = p.cls[((long)b * p.nQ128 + (i >> 1)) * p.nK + kj];
+      if (c != 0) {
+        tile_idx[n] = static_cast<int16_t>(i);
+        tile_cls[n] = c;
+        ++n;
+      }
+    }
+    *n_valid_slot = n;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -168,13 +194,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM columns: buf0 {ST 0..63, dPT 64..127}, buf1 {ST 128..191, dPT 192..255}, dV 256..383, dK 384..511.
-  // dQ^T of an iteration is written over the ST columns of its own buffer once they have been read.
+  const int n_valid = *n_valid_slot;
+  const int n_iter = n_valid * group;
+  // TMEM columns: S^T[0] 0..63, S^T[1] 64..127, dP^T 128..191, dQ^T 192..255, dV 256..383, dK 384..511
+  const uint32_t tmem_dPT = tmem_base + 128;
+  const uint32_t tmem_dQT = tmem_base + 192;
   const uint32_t tmem_dV = tmem_base + 256;
   const uint32_t tmem_dK = tmem_base + 384;
-
-  // every role walks the same (query head, 64-row query tile) list and skips tiles whose class is 0
-  auto tile_class = [&](int i64) -> int { return p.cls[((long)b * p.nQ128 + (i64 >> 1)) * p.nK + kj]; };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -188,25 +214,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tma_load_4d(smem + L::K_OFF + c * KV_CHUNK, &tm_k, kv_full, c * 64, hk, k0, b);
         tma_load_4d(smem + L::V_OFF + c * KV_CHUNK, &tm_v, kv_full, c * 64, hk, k0, b);
       }
-      uint32_t it = 0;
-      bool ok = true;
-      for (int hh = 0; hh < group && ok; ++hh) {
-        const int h = hk * group + hh;
-        for (int i = 0; i < p.nQ64; ++i) {
-          if (tile_class(i) == 0) continue;
-          const int st = it & 1;
-          if (!bw_wait(&q_empty[st], ((it >> 1) & 1) ^ 1, abort_flag)) {
-            atomicExch(p.status, ST_TIMEOUT_EMPTY);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          mbar_expect_tx(&q_full[st], 4 * Q_CHUNK);
-          for (int c = 0; c < 2; ++c) {
-            tma_load_4d(smem + L::Q_OFF + (st * 2 + c) * Q_CHUNK, &tm_q, &q_full[st], c * 64, h, i * BW_BQ, b);
-            tma_load_4d(smem + L::DO_OFF + (st * 2 + c) * Q_CHUNK, &tm_do, &q_full[st], c * 64, h, i * BW_BQ, b);
-          }
-          ++it;
+      for (int it = 0; it < n_iter; ++it) {
+        const int h = hk * group + it / n_valid;
+        const int i = tile_idx[it % n_valid];
+        const int st = it % QS;
+        if (!bw_wait(&q_empty[st], ((it / QS) & 1) ^ 1, abort_flag)) {
+          atomicExch(p.status, ST_TIMEOUT_EMPTY);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_expect_tx(&q_full[st], 4 * Q_CHUNK);
+        for (int c = 0; c < 2; ++c) {
+          tma_load_4d(smem + L::Q_OFF + (st * 2 + c) * Q_CHUNK, &tm_q, &q_full[st], c * 64, h, i * BW_BQ, b);
+          tma_load_4d(smem + L::DO_OFF + (st * 2 + c) * Q_CHUNK, &tm_do, &q_full[st], c * 64, h, i * BW_BQ, b);
         }
       }
     }
@@ -222,40 +242,45 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t pt_s = smem_u32(smem + L::PT_OFF);
       const uint32_t dst_s = smem_u32(smem + L::DST_OFF);
       const int ksteps_d = p.dk16 / 16;
-      int n = 0;
-      for (int i = 0; i < p.nQ64; ++i) n += (tile_class(i) != 0);
-      n *= group;
       bool ok = bw_wait(kv_full, 0, abort_flag);
       if (!ok) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; }
 
-      auto issue_s = [&](uint32_t it) -> bool {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!bw_wait(&q_full[st], ph, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
-        if (!bw_wait(&st_free[st], ph ^ 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_TMEM_EMPTY); *abort_flag = 1; return false; }
+      // S^T(it) = K Q^T into ST[it & 1]; waits for the Q/dO stage of that iteration
+      auto issue_st = [&](int it) -> bool {
+        const int st = it % QS;
+        if (!bw_wait(&q_full[st], (it / QS) & 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
         tc_fence_after();
         const uint32_t q_s = smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK);
-        const uint32_t do_s = smem_u32(smem + L::DO_OFF + st * 2 * Q_CHUNK);
-        const uint32_t t_st = tmem_base + st * 128;
+        const uint32_t t_st = tmem_base + (it & 1) * 64;
         for (int kk = 0; kk < ksteps_d; ++kk) {
           const uint32_t a_off = (kk >> 2) * KV_CHUNK + (kk & 3) * 32;
           const uint32_t b_off = (kk >> 2) * Q_CHUNK + (kk & 3) * 32;
           umma_f16(t_st, make_desc_kmajor_sw128(k_s + a_off), make_desc_kmajor_sw128(q_s + b_off), idesc_s, kk > 0);
         }
+        return true;
+      };
+      // dP^T(it) = V dO^T; its commit also covers S^T(it), issued earlier
+      auto issue_dpt = [&](int it) {
+        const int st = it % QS;
+        const uint32_t do_s = smem_u32(smem + L::DO_OFF + st * 2 * Q_CHUNK);
         for (int kk = 0; kk < ksteps_d; ++kk) {
           const uint32_t a_off = (kk >> 2) * KV_CHUNK + (kk & 3) * 32;
           const uint32_t b_off = (kk >> 2) * Q_CHUNK + (kk & 3) * 32;
-          umma_f16(t_st + 64, make_desc_kmajor_sw128(v_s + a_off), make_desc_kmajor_sw128(do_s + b_off), idesc_s, kk > 0);
+          umma_f16(tmem_dPT, make_desc_kmajor_sw128(v_s + a_off), make_desc_kmajor_sw128(do_s + b_off), idesc_s, kk > 0);
         }
-        umma_commit(&s_full[st]);
-        return true;
+        umma_commit(sdp_full);
       };
 
-      if (ok && n > 0) ok = issue_s(0);
-      for (uint32_t it = 0; ok && it < (uint32_t)n; ++it) {
-        const int st = it & 1;
+      if (ok && n_iter > 0) {
+        ok = issue_st(0);
+        if (ok) issue_dpt(0);
+        if (ok && n_iter > 1) ok = issue_st(1);
+      }
+      for (int it = 0; ok && it < n_iter; ++it) {
+        const int st = it % QS;
         if (!bw_wait(pds_full, it & 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
         tc_fence_after();
+        if (it + 1 < n_iter) issue_dpt(it + 1);  // dP^T columns were read before pds_full(it)
         const uint32_t q_s = smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK);
         const uint32_t do_s = smem_u32(smem + L::DO_OFF + st * 2 * Q_CHUNK);
         // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows)
@@ -268,148 +293,156 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_f16(tmem_dK, make_desc_kmajor_sw128(dst_s + kk * 32), make_desc_mnmajor_sw128(q_s + kk * 2048, Q_CHUNK),
                    idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&q_empty[st]);
-        // dQ^T = K^T dS^T  (contraction over the 128 key rows), into the ST columns of this buffer
+        if (it > 0) {
+          if (!bw_wait(dq_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_TMEM_EMPTY); *abort_flag = 1; break; }
+          tc_fence_after();
+        }
+        // dQ^T = K^T dS^T  (contraction over the 128 key rows)
 #pragma unroll
         for (int kk = 0; kk < BW_BKV / 16; ++kk)
-          umma_f16(tmem_base + st * 128, make_desc_mnmajor_sw128(k_s + kk * 2048, KV_CHUNK),
+          umma_f16(tmem_dQT, make_desc_mnmajor_sw128(k_s + kk * 2048, KV_CHUNK),
                    make_desc_mnmajor_sw128(dst_s + kk * 2048, KV_CHUNK), idesc_dq, kk > 0 ? 1u : 0u);
         umma_commit(pds_empty);
-        umma_commit(&dq_full[st]);
-        if (it + 1 < (uint32_t)n) ok = issue_s(it + 1);
+        umma_commit(dq_full);
+        if (it + 2 < n_iter) ok = issue_st(it + 2);  // ST[it & 1] was read before pds_full(it)
       }
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ compute threads
-    const int quarter = warp & 3;
+    // ------------------------------------------------------------------ compute threads (8 warps)
+    const int cw = warp - 2;
+    const int quarter = warp & 3;       // TMEM lane quarter this warp may touch
+    const int half = cw >> 2;           // which 32 of the 64 query columns this warp handles
     const int r = quarter * 32 + lane;  // KV row in the tile == TMEM lane; also head-dim row of dQ^T
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const int col0 = half * 32;
     const int kidx = k0 + r;
     const bool k_valid = kidx < p.Sk;
     const int64_t kb = (k_valid && p.k_bits) ? p.k_bits[(long)b * p.Sk + kidx] : 0;
     const int kpos = k_valid ? (p.k_pos ? p.k_pos[(long)b * p.Sk + kidx] : kidx) : -1;
     const float LOG2E = 1.4426950408889634f;
+    // the 64 threads with half == 0 and r < 64 stage the metadata of query row (tile * 64 + r)
+    const bool stager = (half == 0) && (r < 64);
 
-    uint32_t it = 0;
+    float pf_lse = 0.f, pf_delta = 0.f;
+    int pf_qpos = -1;
+    int64_t pf_qbits = 0;
+    auto prefetch_meta = [&](int it) {
+      if (!stager || it >= n_iter) return;
+      const int h = hk * group + it / n_valid;
+      const int q = tile_idx[it % n_valid] * BW_BQ + r;
+      const bool qv = q < p.Sq;
+      const long idx = ((long)b * p.Hq + h) * p.Sq + q;
+      pf_lse = qv ? p.lse[idx] * LOG2E : INFINITY;
+      pf_delta = qv ? p.delta[idx] : 0.f;
+      pf_qpos = qv ? (p.q_pos ? p.q_pos[(long)b * p.Sq + q] : q) : -1;
+      pf_qbits = (qv && p.q_bits) ? p.q_bits[(long)b * p.Sq + q] : 0;
+    };
+
     bool ok = true;
-    int prev_h = 0, prev_i = 0;
-
-    auto drain_dq = [&](uint32_t pit, int ph, int pi) -> bool {
-      const int st = pit & 1;
-      if (!bw_wait(&dq_full[st], (pit >> 1) & 1, abort_flag)) {
+    auto drain_dq = [&](int pit) -> bool {
+      if (!bw_wait(dq_full, pit & 1, abort_flag)) {
         if (lane == 0) atomicExch(p.status, ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
         return false;
       }
       tc_fence_after();
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_base + st * 128 + cc * 32 + lane_addr, v);
-        tmem_ld_wait();
-        if (r < p.D) {
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            const int q = pi * BW_BQ + cc * 32 + c;
-            if (q < p.Sq) atomicAdd(p.dq_acc + (((long)b * p.Sq + q) * p.Hq + ph) * p.D + r, __uint_as_float(v[c]));
-          }
-        }
-      }
+      const int ph = hk * group + pit / n_valid;
+      const int pi = tile_idx[pit % n_valid];
+      uint32_t v[32];
+      tmem_ld_32x32(tmem_dQT + col0 + lane_addr, v);
+      tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&st_free[st]);
+      mbar_arrive(dq_free);
+      if (r < p.D) {
+        float* base = p.dq_acc + (((long)b * p.Sq + (long)pi * BW_BQ + col0) * p.Hq + ph) * p.D + r;
+        const long qstride = (long)p.Hq * p.D;
+        const int qlim = p.Sq - (pi * BW_BQ + col0);
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          if (c < qlim) atomicAdd(base + c * qstride, __uint_as_float(v[c]));
+      }
       return true;
     };
 
-    for (int hh = 0; hh < group && ok; ++hh) {
-      const int h = hk * group + hh;
-      for (int i = 0; i < p.nQ64 && ok; ++i) {
-        const int c = tile_class(i);
-        if (c == 0) continue;
-        const int st = it & 1;
-        // ---- stage the per-query metadata of this tile
-        float* m_lse = reinterpret_cast<float*>(smem + L::META_OFF + st * L::META_STAGE);
-        float* m_delta = m_lse + 64;
-        int* m_qpos = reinterpret_cast<int*>(m_delta + 64);
-        int64_t* m_qbits = reinterpret_cast<int64_t*>(m_qpos + 64);
-        if (r < 64) {
-          const int q = i * BW_BQ + r;
-          const bool qv = q < p.Sq;
-          const long idx = ((long)b * p.Hq + h) * p.Sq + q;
-          m_lse[r] = qv ? p.lse[idx] * LOG2E : INFINITY;
-          m_delta[r] = qv ? p.delta[idx] : 0.f;
-          m_qpos[r] = qv ? (p.q_pos ? p.q_pos[(long)b * p.Sq + q] : q) : -1;
-          m_qbits[r] = (qv && p.q_bits) ? p.q_bits[(long)b * p.Sq + q] : 0;
+    prefetch_meta(0);
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int c = tile_cls[it % n_valid];
+      const int mb = it & 1;
+      float* m_lse = reinterpret_cast<float*>(smem + L::META_OFF + mb * L::META_STAGE);
+      float* m_delta = m_lse + 64;
+      int* m_qpos = reinterpret_cast<int*>(m_delta + 64);
+      int64_t* m_qbits = reinterpret_cast<int64_t*>(m_qpos + 64);
+      if (stager) {
+        m_lse[r] = pf_lse;
+        m_delta[r] = pf_delta;
+        m_qpos[r] = pf_qpos;
+        m_qbits[r] = pf_qbits;
+      }
+      mbar_arrive(meta_full);
+      prefetch_meta(it + 1);  // global loads for the next tile fly while this one is processed
+      if (!bw_wait(meta_full, it & 1, abort_flag)) {
+        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      if (!bw_wait(sdp_full, it & 1, abort_flag)) {
+        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_TMEM_FULL);
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(tmem_base + (it & 1) * 64 + col0 + lane_addr, sv);
+      tmem_ld_32x32(tmem_dPT + col0 + lane_addr, dv);
+      tmem_ld_wait();
+      float pv[32], ds[32];
+#pragma unroll
+      for (int x = 0; x < 32; ++x) {
+        const int col = col0 + x;
+        float pr = exp2f(__uint_as_float(sv[x]) * p.scale_log2 - m_lse[col]);
+        if (c == 1) {
+          const bool allow = k_valid && m_qpos[col] >= 0 && mask_allowed(p.mask_mode, m_qbits[col], kb, m_qpos[col], kpos);
+          pr = allow ? pr : 0.f;
         }
-        mbar_arrive(meta_full);
-        if (!bw_wait(meta_full, it & 1, abort_flag)) {
+        pv[x] = pr;
+        ds[x] = pr * (__uint_as_float(dv[x]) - m_delta[col]) * p.scale;
+      }
+      if (it > 0) {
+        if (!bw_wait(pds_empty, (it - 1) & 1, abort_flag)) {
           if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
           *abort_flag = 1;
           ok = false;
           break;
         }
-        // ---- S^T and dP^T from TMEM
-        if (!bw_wait(&s_full[st], (it >> 1) & 1, abort_flag)) {
-          if (lane == 0) atomicExch(p.status, ST_TIMEOUT_TMEM_FULL);
-          *abort_flag = 1;
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        float pv[64], ds[64];
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t sv[32], dv[32];
-          tmem_ld_32x32(tmem_base + st * 128 + cc * 32 + lane_addr, sv);
-          tmem_ld_32x32(tmem_base + st * 128 + 64 + cc * 32 + lane_addr, dv);
-          tmem_ld_wait();
-#pragma unroll
-          for (int x = 0; x < 32; ++x) {
-            const int col = cc * 32 + x;
-            float pr = exp2f(__uint_as_float(sv[x]) * p.scale_log2 - m_lse[col]);
-            if (c == 1) {
-              const bool allow = k_valid && m_qpos[col] >= 0 && mask_allowed(p.mask_mode, m_qbits[col], kb, m_qpos[col], kpos);
-              pr = allow ? pr : 0.f;
-            }
-            pv[col] = pr;
-            ds[col] = pr * (__uint_as_float(dv[x]) - m_delta[col]) * p.scale;
-          }
-        }
-        // ---- P^T / dS^T -> bf16 smem tiles (row r, 8 pieces of 8 query columns)
-        if (it > 0) {
-          if (!bw_wait(pds_empty, (it - 1) & 1, abort_flag)) {
-            if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-        }
-#pragma unroll
-        for (int piece = 0; piece < 8; ++piece) {
-          uint4 u, w;
-          u.x = pack_bf16x2(pv[piece * 8 + 0], pv[piece * 8 + 1]);
-          u.y = pack_bf16x2(pv[piece * 8 + 2], pv[piece * 8 + 3]);
-          u.z = pack_bf16x2(pv[piece * 8 + 4], pv[piece * 8 + 5]);
-          u.w = pack_bf16x2(pv[piece * 8 + 6], pv[piece * 8 + 7]);
-          w.x = pack_bf16x2(ds[piece * 8 + 0], ds[piece * 8 + 1]);
-          w.y = pack_bf16x2(ds[piece * 8 + 2], ds[piece * 8 + 3]);
-          w.z = pack_bf16x2(ds[piece * 8 + 4], ds[piece * 8 + 5]);
-          w.w = pack_bf16x2(ds[piece * 8 + 6], ds[piece * 8 + 7]);
-          const uint32_t off = sw128_offset(r, piece);
-          *reinterpret_cast<uint4*>(smem + L::PT_OFF + off) = u;
-          *reinterpret_cast<uint4*>(smem + L::DST_OFF + off) = w;
-        }
-        fence_proxy_async_smem();
-        tc_fence_before();
-        mbar_arrive(pds_full);
-        // ---- drain dQ^T of the previous iteration while the MMAs of this one run
-        if (it > 0) ok = drain_dq(it - 1, prev_h, prev_i);
-        prev_h = h;
-        prev_i = i;
-        ++it;
       }
+      // P^T / dS^T -> bf16 smem tiles: row r, this warp's four 16-byte pieces (8 query columns each)
+#pragma unroll
+      for (int pc = 0; pc < 4; ++pc) {
+        uint4 u, w;
+        u.x = pack_bf16x2(pv[pc * 8 + 0], pv[pc * 8 + 1]);
+        u.y = pack_bf16x2(pv[pc * 8 + 2], pv[pc * 8 + 3]);
+        u.z = pack_bf16x2(pv[pc * 8 + 4], pv[pc * 8 + 5]);
+        u.w = pack_bf16x2(pv[pc * 8 + 6], pv[pc * 8 + 7]);
+        w.x = pack_bf16x2(ds[pc * 8 + 0], ds[pc * 8 + 1]);
+        w.y = pack_bf16x2(ds[pc * 8 + 2], ds[pc * 8 + 3]);
+        w.z = pack_bf16x2(ds[pc * 8 + 4], ds[pc * 8 + 5]);
+        w.w = pack_bf16x2(ds[pc * 8 + 6], ds[pc * 8 + 7]);
+        const uint32_t off = sw128_offset(r, half * 4 + pc);
+        *reinterpret_cast<uint4*>(smem + L::PT_OFF + off) = u;
+        *reinterpret_cast<uint4*>(smem + L::DST_OFF + off) = w;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+      // drain dQ^T of the previous iteration while the MMAs of this one run
+      if (it > 0) ok = drain_dq(it - 1);
     }
-    if (ok && it > 0) ok = drain_dq(it - 1, prev_h, prev_i);
-    // ---- epilogue: dV and dK tiles (every MMA has retired once the last dQ^T was seen)
+    if (ok && n_iter > 0) ok = drain_dq(n_iter - 1);
+    // ---- epilogue: dV and dK tiles (every MMA has retired once the last dQ^T was seen);
+    //      the two warps of a lane quarter split the head-dim columns
     if (ok) {
       tc_fence_after();
 #pragma unroll
@@ -418,9 +451,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __nv_bfloat16* base = which == 0 ? p.dV + (long)b * p.dv_stride_b + (long)kidx * p.dv_stride_s + (long)hk * p.D
                                          : p.dK + (long)b * p.dk_stride_b + (long)kidx * p.dk_stride_s + (long)hk * p.D;
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
+        for (int c2 = 0; c2 < 2; ++c2) {
+          const int cc = half * 2 + c2;
           uint32_t v[32];
-          if (it > 0) {
+          if (n_iter > 0) {
             tmem_ld_32x32(t + cc * 32 + lane_addr, v);
             tmem_ld_wait();
           } else {
@@ -476,6 +510,7 @@ CSB_API int csb_attn_bwd(const void* q, const void* k, const void* v, const void
                          long dv_ss, long dv_sb, float scale, int mask_mode, const long* q_bits, const long* k_bits,
                          const int* q_pos, const int* k_pos, const signed char* cls, int* status, void* stream) {
   if (D % 8 || D > 128 || D < 16 || Hq % Hk) return CSB_ERR_BAD_ARG;
+  if ((Sq + BW_BQ - 1) / BW_BQ > BwdSmem::MAX_TILES) return CSB_ERR_TOO_LARGE;
   if ((q_ss % 8) || (k_ss % 8) || (v_ss % 8) || (do_ss % 8) || (dq_ss % 4) || (dk_ss % 8) || (dv_ss % 8)) return CSB_ERR_BAD_ARG;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   {
@@ -517,7 +552,7 @@ CSB_API int csb_attn_bwd(const void* q, const void* k, const void* v, const void
     attr = true;
   }
   dim3 grid(p.nK, Hk, B);
-  attn_bwd_kernel<<<grid, 192, BwdSmem::DYN_BYTES, s>>>(tq, tk, tv, tdo, p);
+  attn_bwd_kernel<<<grid, BW_THREADS, BwdSmem::DYN_BYTES, s>>>(tq, tk, tv, tdo, p);
   int e = launch_result();
   if (e) return e;
   const long n_rows = (long)B * Sq;

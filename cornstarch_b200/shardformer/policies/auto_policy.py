@@ -1,0 +1,81 @@
+"""Fully-qualified model class name -> policy class (``get_autopolicy`` / ``get_policy_type`` / ``import_policy``).
+
+Keys cover this package's model classes and, as aliases, the HF ``transformers`` class names the
+reference registers (cornstarch/shardformer/policies/auto_policy.py:12-248), so a template written for
+``transformers.models.llama.modeling_llama.LlamaForCausalLM`` resolves to the same pipeline units.
+"""
+
+from __future__ import annotations
+
+from . import models as P
+
+_NATIVE = {
+    "cornstarch_b200.models.llama.DecoderModel": P.DecoderModelPolicy,
+    "cornstarch_b200.models.llama.DecoderForCausalLM": P.DecoderForCausalLMPolicy,
+    "cornstarch_b200.models.moe.MoeForCausalLM": P.MoeForCausalLMPolicy,
+    "cornstarch_b200.models.vision.SiglipVisionModel": P.SiglipVisionModelPolicy,
+    "cornstarch_b200.models.vision.CLIPVisionModel": P.CLIPVisionModelPolicy,
+    "cornstarch_b200.models.vision.ViTModel": P.ViTModelPolicy,
+    "cornstarch_b200.models.whisper.WhisperEncoder": P.WhisperEncoderPolicy,
+    "cornstarch_b200.models.whisper.Qwen2AudioEncoder": P.Qwen2AudioEncoderPolicy,
+    "cornstarch_b200.multimodal.modeling.MultimodalProjector": P.MultimodalProjectorPolicy,
+}
+
+
+def _hf(family: str, module: str, base: str, causal: str):
+    pre = f"transformers.models.{family}.modeling_{module}."
+    return {pre + base: P.DecoderModelPolicy, pre + causal: P.DecoderForCausalLMPolicy}
+
+
+_HF_ALIASES = {}
+for fam, base, causal in (("llama", "LlamaModel", "LlamaForCausalLM"), ("mistral", "MistralModel", "MistralForCausalLM"),
+                          ("qwen2", "Qwen2Model", "Qwen2ForCausalLM"), ("qwen3", "Qwen3Model", "Qwen3ForCausalLM"),
+                          ("gemma", "GemmaModel", "GemmaForCausalLM"), ("gemma2", "Gemma2Model", "Gemma2ForCausalLM"),
+                          ("gemma3", "Gemma3TextModel", "Gemma3ForCausalLM"), ("phi3", "Phi3Model", "Phi3ForCausalLM")):
+    _HF_ALIASES.update(_hf(fam, fam, base, causal))
+_HF_ALIASES.update({
+    "transformers.models.mixtral.modeling_mixtral.MixtralModel": P.DecoderModelPolicy,
+    "transformers.models.mixtral.modeling_mixtral.MixtralForCausalLM": P.MoeForCausalLMPolicy,
+    "transformers.models.qwen3_moe.modeling_qwen3_moe.Qwen3MoeModel": P.DecoderModelPolicy,
+    "transformers.models.qwen3_moe.modeling_qwen3_moe.Qwen3MoeForCausalLM": P.MoeForCausalLMPolicy,
+    "transformers.models.siglip.modeling_siglip.SiglipVisionModel": P.SiglipVisionModelPolicy,
+    "transformers.models.clip.modeling_clip.CLIPVisionModel": P.CLIPVisionModelPolicy,
+    "transformers.models.vit.modeling_vit.ViTModel": P.ViTModelPolicy,
+    "transformers.models.whisper.modeling_whisper.WhisperEncoder": P.WhisperEncoderPolicy,
+    "transformers.models.qwen2_audio.modeling_qwen2_audio.Qwen2AudioEncoder": P.Qwen2AudioEncoderPolicy,
+    "cornstarch.models.multimodal_language_model.modeling_multimodal_language_model.MultimodalProjector": P.MultimodalProjectorPolicy,
+})
+
+_POLICY_LIST = {**_NATIVE, **_HF_ALIASES}
+
+
+def register_policy(fullname: str, policy_cls) -> None:
+    _POLICY_LIST[fullname] = policy_cls
+
+
+def import_policy(fullname: str):
+    return get_policy_type(fullname)
+
+
+def get_policy_type(fullname: str):
+    pol = _POLICY_LIST.get(fullname)
+    if pol is None:
+        # subclasses of registered model classes (e.g. LlamaForCausalLM = DecoderForCausalLM) resolve by MRO
+        raise NotImplementedError(f"Auto policy for {fullname} is not implemented. Supported: {sorted(_POLICY_LIST)}")
+    return pol
+
+
+def get_autopolicy(fullname: str):
+    """Instance of the policy registered for the fully-qualified class name."""
+    return get_policy_type(fullname)()
+
+
+def policy_for_model(model):
+    """Policy instance for a model object, walking its class MRO."""
+    for klass in type(model).__mro__:
+        name = f"{klass.__module__}.{klass.__qualname__}"
+        if name in _POLICY_LIST:
+            pol = _POLICY_LIST[name]()
+            pol.set_model(model)
+            return pol
+    raise NotImplementedError(f"no policy for {type(model)}")

@@ -1,0 +1,158 @@
+"""Policies of the model zoo (one small class per model class).
+
+Pipeline unit names per model follow Appendix-style lists of the reference policies, e.g.
+cornstarch/shardformer/policies/llama.py:38-49 (``embed_tokens, rotary_emb, layers.i, norm`` and the
+``model.`` prefix + ``lm_head`` for the causal-LM class), policies/siglip.py:34-46, policies/clip.py:33-44,
+policies/vit.py:31-39, policies/whisper.py:36-47, policies/multimodal.py:33-44.
+"""
+
+from __future__ import annotations
+
+from ...models import llama as L
+from ...models import moe as M
+from ...models import vision as V
+from ...models import whisper as W
+from ...multimodal.modeling import MultimodalProjector
+from .base_policy import ModelPolicy, TPRule
+
+_DEC_LAYER = r"(model\.)?layers\.\d+\."
+
+
+class DecoderModelPolicy(ModelPolicy):
+    model_cls = L.DecoderModel
+    first_stage_modules = ["embed_tokens", "rotary_emb", "rotary_emb_local"]
+    last_stage_modules = ["norm"]
+    supported_sp_modes = ("all_to_all", "ring_attn")
+    head_modules = _DEC_LAYER + r"self_attn"
+    tp_rules = [
+        TPRule(_DEC_LAYER + r"self_attn\.(q_proj|k_proj|v_proj)", "col"),
+        TPRule(_DEC_LAYER + r"self_attn\.qkv_proj", "col", "qkv"),
+        TPRule(_DEC_LAYER + r"self_attn\.o_proj", "row"),
+        TPRule(_DEC_LAYER + r"mlp\.(gate_proj|up_proj)", "col"),
+        TPRule(_DEC_LAYER + r"mlp\.gate_up_proj", "col", "gate_up"),
+        TPRule(_DEC_LAYER + r"mlp\.down_proj", "row"),
+        TPRule(_DEC_LAYER + r"(block_sparse_moe|mlp)\.experts\.\d+\.(w1|w3|gate_proj|up_proj)", "col"),
+        TPRule(_DEC_LAYER + r"(block_sparse_moe|mlp)\.experts\.\d+\.(w2|down_proj)", "row"),
+        TPRule(r"(model\.)?embed_tokens", "vocab"),
+        TPRule(r"lm_head", "lm_head"),
+    ]
+
+    def split_sizes(self, path, module):
+        cfg = self.model.config
+        if path.endswith("qkv_proj"):
+            d = cfg.head_dim
+            return [cfg.num_attention_heads * d, cfg.num_key_value_heads * d, cfg.num_key_value_heads * d]
+        if path.endswith("gate_up_proj"):
+            return [cfg.intermediate_size, cfg.intermediate_size]
+        return None
+
+    def config_sanity_check(self):
+        super().config_sanity_check()
+        sc, cfg = self.shard_config, self.model.config
+        if sc is None:
+            return
+        tp = sc.tensor_parallel_size
+        assert cfg.num_attention_heads % tp == 0 and cfg.num_key_value_heads % tp == 0, (
+            "The number of attention heads and key/value heads must be divisible by the tensor parallel size.")
+        if sc.sequence_parallelism_mode == "all_to_all":
+            sp = sc.sequence_parallel_size
+            assert (cfg.num_attention_heads // tp) % sp == 0 and (cfg.num_key_value_heads // tp) % sp == 0, (
+                "Ulysses needs the per-tp-rank head counts to be divisible by the sequence parallel size.")
+
+
+class DecoderForCausalLMPolicy(DecoderModelPolicy):
+    model_cls = L.DecoderForCausalLM
+    first_stage_modules = ["model.embed_tokens", "model.rotary_emb", "model.rotary_emb_local"]
+    last_stage_modules = ["model.norm", "lm_head"]
+
+    def get_shared_params(self):
+        cfg = self.model.config
+        if getattr(cfg, "tie_word_embeddings", False):
+            return [{"first": "model.embed_tokens.weight", "last": "lm_head.weight"}]
+        return []
+
+
+class MoeForCausalLMPolicy(DecoderForCausalLMPolicy):
+    model_cls = M.MoeForCausalLM
+
+    def config_sanity_check(self):
+        super().config_sanity_check()
+        if getattr(self.model.config, "model_type", "") == "qwen3_moe":
+            sc = self.shard_config
+            if sc is not None and sc.enable_sequence_parallelism and sc.sequence_parallel_size > 1:
+                raise ValueError("Qwen3-MoE does not support sequence parallelism")
+
+
+_ENC_ATTN_COL = r"(q_proj|k_proj|v_proj|query|key|value)"
+
+
+class SiglipVisionModelPolicy(ModelPolicy):
+    model_cls = V.SiglipVisionModel
+    first_stage_modules = ["vision_model.embeddings"]
+    last_stage_modules = ["vision_model.post_layernorm", "vision_model.head"]
+    supported_sp_modes = ("ring_attn",)
+    head_modules = r"vision_model\.encoder\.layers\.\d+\.self_attn"
+    tp_rules = [
+        TPRule(r"vision_model\.encoder\.layers\.\d+\.self_attn\." + _ENC_ATTN_COL, "col"),
+        TPRule(r"vision_model\.encoder\.layers\.\d+\.self_attn\.out_proj", "row"),
+        TPRule(r"vision_model\.encoder\.layers\.\d+\.mlp\.fc1", "col"),
+        TPRule(r"vision_model\.encoder\.layers\.\d+\.mlp\.fc2", "row"),
+        TPRule(r"vision_model\.head\.mlp\.fc1", "col"),
+        TPRule(r"vision_model\.head\.mlp\.fc2", "row"),
+    ]
+
+
+class CLIPVisionModelPolicy(SiglipVisionModelPolicy):
+    model_cls = V.CLIPVisionModel
+    first_stage_modules = ["vision_model.embeddings", "vision_model.pre_layrnorm"]
+    last_stage_modules = ["vision_model.post_layernorm"]
+
+
+class ViTModelPolicy(ModelPolicy):
+    model_cls = V.ViTModel
+    first_stage_modules = ["embeddings"]
+    last_stage_modules = ["layernorm", "pooler"]
+    supported_sp_modes = ("ring_attn",)
+    head_modules = r"encoder\.layer\.\d+"
+    tp_rules = [
+        TPRule(r"encoder\.layer\.\d+\.attention\.attention\." + _ENC_ATTN_COL, "col"),
+        TPRule(r"encoder\.layer\.\d+\.attention\.output\.dense", "row"),
+        TPRule(r"encoder\.layer\.\d+\.intermediate\.dense", "col"),
+        TPRule(r"encoder\.layer\.\d+\.output\.dense", "row"),
+    ]
+
+
+class WhisperEncoderPolicy(ModelPolicy):
+    model_cls = W.WhisperEncoder
+    first_stage_modules = ["conv1", "conv2", "embed_positions"]
+    last_stage_modules = ["layer_norm", "avg_pooler"]
+    supported_sp_modes = ("ring_attn",)
+    head_modules = r"layers\.\d+\.self_attn"
+    tp_rules = [
+        TPRule(r"layers\.\d+\.self_attn\." + _ENC_ATTN_COL, "col"),
+        TPRule(r"layers\.\d+\.self_attn\.out_proj", "row"),
+        TPRule(r"layers\.\d+\.fc1", "col"),
+        TPRule(r"layers\.\d+\.fc2", "row"),
+    ]
+
+
+class Qwen2AudioEncoderPolicy(WhisperEncoderPolicy):
+    model_cls = W.Qwen2AudioEncoder
+
+
+class MultimodalProjectorPolicy(ModelPolicy):
+    """``linear`` -> column-parallel with gathered output; ``in_proj`` column, ``out_proj`` row."""
+
+    model_cls = MultimodalProjector
+    tp_rules = [
+        TPRule(r"projection\.linear", "col_gather"),
+        TPRule(r"projection\.in_proj", "col"),
+        TPRule(r"projection\.out_proj", "row"),
+    ]
+
+    @classmethod
+    def get_all_modules(cls, config) -> list[str]:
+        return MultimodalProjector.module_names(config)
+
+    def pipeline_template_sanity_check(self, template) -> None:
+        return None
