@@ -126,6 +126,9 @@ class PreTrainedModel(nn.Module):
             parent, attr = self._resolve_parent(n)
             if parent is None:
                 continue
+            target = parent[int(attr)] if isinstance(parent, (nn.ModuleList, nn.Sequential)) else getattr(parent, attr)
+            if isinstance(target, nn.Module) and not any(True for _ in target.parameters()):
+                continue  # stateless helpers (rotary tables, activations, poolers) cost nothing to keep
             if isinstance(parent, (nn.ModuleList, nn.Sequential)):
                 parent[int(attr)] = _Released()
             else:

@@ -446,7 +446,12 @@ class DecoderForCausalLM(PreTrainedModel):
             if shift_labels:
                 tgt = torch.full_like(labels, -100)
                 tgt[:, :-1] = labels[:, 1:]
-            loss_sum, n_valid = linear_cross_entropy(h, self.lm_head.weight, tgt, tp_group=tp_group,
+            w = self.lm_head.weight
+            valid = getattr(self, "valid_vocab", None)
+            if valid is not None and valid < w.shape[0]:
+                w = w[:valid]  # rows beyond the real vocabulary are padding of the vocab-parallel shard
+            h_in = comm.reduce_backward(h, tp_group) if tp_group is not None else h  # each vocab shard yields a partial dh
+            loss_sum, n_valid = linear_cross_entropy(h_in, w, tgt, tp_group=tp_group,
                                                      vocab_start=self.vocab_start, reduction="sum_and_count")
             result["loss_sum"], result["num_valid"] = loss_sum, n_valid
             result["loss"] = loss_sum / n_valid.clamp(min=1).to(loss_sum.dtype)

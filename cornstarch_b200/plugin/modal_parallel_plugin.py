@@ -1,0 +1,106 @@
+"""``ModalParallelPlugin``: the parallel plan of ONE modality (an encoder or the language model).
+
+Constructor arguments follow the reference (cornstarch/plugin/multimodal_parallel_plugin/
+modal_parallel_plugin.py:72-101): ``tp_size``, ``sp_size``, ``sequence_parallelism_mode``
+(``"ring_attn"`` = context parallelism, ``"all_to_all"`` = Ulysses), ``pipeline_template``,
+``context_parallel_distribution_mode``, ``custom_policy``.  ``configure`` shards the modality's module(s)
+with :class:`ShardFormer`.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch.nn as nn
+
+from ..multimodal.modeling import ModalModuleBase
+from ..pipeline_template import PipelineTemplate
+from ..shardformer.policies.auto_policy import policy_for_model
+from ..shardformer.shard.shard_config import ContextParallelDistributionMode, ShardConfig
+from ..shardformer.shard.shardformer import ShardFormer
+
+
+class ModalParallelPlugin:
+    def __init__(self, tp_size: int = 1, sp_size: int = 1, sequence_parallelism_mode: Optional[str] = None,
+                 pipeline_template: Optional[PipelineTemplate] = None,
+                 context_parallel_distribution_mode: ContextParallelDistributionMode | str = ContextParallelDistributionMode.MAKESPAN_MIN,
+                 cpu_offload: bool = False, custom_policy=None, ep_size: int = 1):
+        if sp_size > 1:
+            assert sequence_parallelism_mode in ("ring_attn", "all_to_all"), (
+                "sequence_parallelism_mode must be 'ring_attn' or 'all_to_all' when sp_size > 1")
+        self.tp_size = tp_size
+        self.sp_size = sp_size
+        self.ep_size = ep_size
+        self.sequence_parallelism_mode = sequence_parallelism_mode if sp_size > 1 else None
+        self.pipeline_template = pipeline_template
+        self.context_parallel_distribution_mode = (
+            ContextParallelDistributionMode(context_parallel_distribution_mode)
+            if isinstance(context_parallel_distribution_mode, str) else context_parallel_distribution_mode)
+        self.cpu_offload = cpu_offload
+        self.custom_policy = custom_policy
+        self.shard_config: ShardConfig | None = None
+
+    def make_shard_config(self, tp_group, sp_group, stage_manager, device=None, dtype=None, ep_group=None, **flags) -> ShardConfig:
+        self.shard_config = ShardConfig(
+            tensor_parallel_process_group=tp_group,
+            sequence_parallel_process_group=sp_group,
+            pipeline_stage_manager=stage_manager,
+            pipeline_template=self.pipeline_template,
+            enable_tensor_parallelism=self.tp_size > 1,
+            enable_sequence_parallelism=self.sp_size > 1,
+            sequence_parallelism_mode=self.sequence_parallelism_mode,
+            context_parallel_distribution_mode=self.context_parallel_distribution_mode,
+            expert_parallel_process_group=ep_group,
+            extra_kwargs={"device": device, "dtype": dtype},
+            **flags,
+        )
+        return self.shard_config
+
+    def configure(self, model: nn.Module, shard_config: ShardConfig | None = None, stage_manager=None):
+        """Shard ``model`` (a ``ModalModuleBase`` or a language model) in place and return it."""
+        sc = shard_config or self.shard_config
+        assert sc is not None, "call make_shard_config first"
+        former = ShardFormer(sc)
+        if isinstance(model, ModalModuleBase):
+            held = stage_manager.held_module_names() if stage_manager is not None else None
+            self._configure_modal_module(model, sc, former, held)
+        else:
+            former.optimize(model, self.custom_policy or policy_for_model(model))
+        return model
+
+    def _configure_modal_module(self, modal: ModalModuleBase, sc: ShardConfig, former: ShardFormer, held: list[str] | None):
+        """Encoder units are named ``module.<unit>``; the projector's ``projector.<unit>`` (last stage only)."""
+        import copy
+
+        enc_held = None if held is None else [h[len("module."):] for h in held if h.startswith("module.")]
+        proj_held = None if held is None else [h for h in held if h.startswith("projector.")]
+        enc_sc = copy.copy(sc)
+        if enc_held is not None:
+            enc_sc.pipeline_stage_manager = _FixedHeld(enc_held)
+            enc_sc.pipeline_template = None
+        ShardFormer(enc_sc).optimize(modal.module, policy_for_model(modal.module))
+        if modal.projector is not None:
+            if proj_held is not None and not proj_held:
+                modal.projector = None  # the projector lives on the encoder's last stage only
+            else:
+                proj_sc = copy.copy(sc)
+                proj_sc.pipeline_stage_manager = None
+                proj_sc.pipeline_template = None
+                proj_sc.enable_sequence_parallelism = False
+                proj_sc.sequence_parallelism_mode = None
+                ShardFormer(proj_sc).optimize(modal.projector, policy_for_model(modal.projector))
+                if sc.enable_sequence_parallelism and sc.sequence_parallel_size > 1:
+                    from ..parallel.comm import gather_forward_split_backward
+
+                    sp_group, sp = sc.sequence_parallel_process_group, sc.sequence_parallel_size
+                    modal.projector.post_projection = lambda x: gather_forward_split_backward(x, 1, sp_group, float(sp))
+
+
+class _FixedHeld:
+    """Minimal stage-manager stand-in that reports a fixed list of held units."""
+
+    def __init__(self, names):
+        self._names = list(names)
+
+    def held_module_names(self):
+        return self._names

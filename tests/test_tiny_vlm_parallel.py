@@ -1,0 +1,129 @@
+"""Tiny VLM on CPU / gloo, fp32: data-parallel (world 2) and modality-parallel pipeline (encoder stage + LLM
+stage, world 2; encoder stage + 2 LLM stages x TP 2, world 6...) must reproduce the loss and the
+post-step weights of the single-process model."""
+
+import copy
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from tests.dist_utils import run_distributed
+
+
+def _build(seed=0):
+    from cornstarch_b200.zoo import build_model
+
+    torch.manual_seed(seed)
+    m = build_model("tiny")
+    m.train()
+    return m
+
+
+def _batch(n, seed=1):
+    from cornstarch_b200.zoo import synthetic_batch
+
+    return synthetic_batch("tiny", n, seed=seed)
+
+
+def _single_process_reference(n_samples, n_micro, lr=1e-2, steps=2):
+    from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
+
+    model = _build()
+    opt = FusedAdamW(split_decay_groups(model, 0.0), lr=lr)
+    batch = _batch(n_samples)
+    losses = []
+    mb = n_samples // n_micro
+    for _ in range(steps):
+        total = 0.0
+        for i in range(n_micro):
+            sub = {k: v[i * mb : (i + 1) * mb] for k, v in batch.items()}
+            loss = model(**sub).loss / n_micro
+            loss.backward()
+            total += loss.item()
+        opt.step()
+        opt.zero_grad()
+        losses.append(total)
+    return losses, {k: v.detach().clone() for k, v in model.state_dict().items()}
+
+
+def _dp_worker(rank, world):
+    from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
+
+    ref_losses, ref_sd = _single_process_reference(4, 2)
+    model = _build()
+    opt = FusedAdamW(split_decay_groups(model, 0.0), lr=1e-2)
+    batch = _batch(4)
+    mine = {k: v[rank * 2 : (rank + 1) * 2] for k, v in batch.items()}
+    for step in range(2):
+        loss = model(**mine).loss
+        loss.backward()
+        for p in model.parameters():
+            if p.grad is not None:
+                dist.all_reduce(p.grad)
+                p.grad.div_(world)
+        opt.step()
+        opt.zero_grad()
+        tot = loss.detach().clone()
+        dist.all_reduce(tot)
+        assert abs(tot.item() / world - ref_losses[step]) < 1e-4, (tot.item() / world, ref_losses[step])
+    for k, v in model.state_dict().items():
+        assert torch.allclose(v, ref_sd[k], atol=1e-5, rtol=1e-4), k
+
+
+def test_dp2_matches_single_process():
+    run_distributed(_dp_worker, 2)
+
+
+def _pp_worker(rank, world, llm_stages, tp, n_micro):
+    from cornstarch_b200.booster import Booster
+    from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
+    from cornstarch_b200.pipeline_template import PipelineTemplate
+    from cornstarch_b200.plugin.modal_parallel_plugin import ModalParallelPlugin
+    from cornstarch_b200.plugin.multimodal_parallel_plugin import MultimodalParallelPlugin
+
+    n_samples = 4
+    ref_losses, ref_sd = _single_process_reference(n_samples, n_micro)
+    model = _build()
+    enc_tpl = PipelineTemplate.even_split(model.vision_encoder, 1)
+    llm_tpl = PipelineTemplate.even_split(model.language_model, llm_stages)
+    plugin = MultimodalParallelPlugin(
+        encoder_plugins={"vision": ModalParallelPlugin(tp_size=tp, pipeline_template=enc_tpl)},
+        language_model_plugin=ModalParallelPlugin(tp_size=tp, pipeline_template=llm_tpl),
+        num_microbatches=n_micro, precision=None, device=torch.device("cpu"))
+    booster = Booster(plugin=plugin)
+    opt = FusedAdamW(split_decay_groups(model, 0.0), lr=1e-2)
+    pmodel, popt, criterion, *_ = booster.boost(model, opt, criterion=lambda out, batch: out.loss)
+    batch = _batch(n_samples)
+    sm = plugin.stage_manager
+    for step in range(2):
+        out = booster.execute_pipeline(iter([batch]), pmodel, criterion, popt, return_loss=True)
+        popt.step()
+        popt.zero_grad()
+        if sm.is_last_stage(check_only_in_modal=False):
+            assert abs(out["loss"].item() - ref_losses[step]) < 1e-4, (out["loss"].item(), ref_losses[step])
+    # post-step weights of the layers this rank holds equal the single-process ones (TP shards compared by slice)
+    mine = getattr(pmodel.module, pmodel.my_modal_name)
+    from cornstarch_b200 import nn as cnn
+
+    prefix = pmodel.my_modal_name + "."
+    tp_rank = dist.get_rank(plugin.tp_group) if tp > 1 else 0
+    for name, mod in mine.named_modules():
+        for pn, p in mod.named_parameters(recurse=False):
+            full = ref_sd[prefix + (name + "." if name else "") + pn]
+            if isinstance(mod, cnn.ColumnParallelLinear) and hasattr(mod, "full_vocab_size"):
+                local = mod.weight.shape[0]
+                full = torch.cat([full, full.new_zeros(local * tp - full.shape[0], full.shape[1])])[tp_rank * local : (tp_rank + 1) * local]
+            elif isinstance(mod, cnn.ColumnParallelLinear):
+                full = full.chunk(tp, dim=0)[tp_rank]
+            elif isinstance(mod, cnn.RowParallelLinear) and pn == "weight":
+                full = full.chunk(tp, dim=1)[tp_rank]
+            elif isinstance(mod, cnn.VocabParallelEmbedding):
+                pad = mod.padded_num_embeddings - full.shape[0]
+                full = torch.cat([full, full.new_zeros(pad, full.shape[1])])[mod.vocab_start : mod.vocab_end]
+            assert torch.allclose(p.detach(), full, atol=2e-3, rtol=5e-3), (name, pn, (p.detach() - full).abs().max())
+
+
+@pytest.mark.parametrize("llm_stages,tp,n_micro,world", [(1, 1, 2, 2), (2, 1, 4, 3), (1, 2, 2, 4)])
+def test_modality_parallel_pipeline_matches_single_process(llm_stages, tp, n_micro, world):
+    run_distributed(_pp_worker, world, llm_stages, tp, n_micro)
