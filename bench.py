@@ -181,11 +181,17 @@ def main():
         sync()
         ms_e2e = t0.elapsed_time(t1)
     else:
-        ms_e2e = ms
+        ms_e2e, last = ms, None
     if world > 1:
         t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
+        lt = torch.tensor([last if (last is not None and last == last) else -1e30], device="cuda", dtype=torch.float64)
+        dist.all_reduce(lt, op=dist.ReduceOp.MAX)  # only the last pipeline stage knows the loss
+        last = float(lt[0])
+        lc = torch.tensor([launches], device="cuda", dtype=torch.int64)
+        dist.all_reduce(lc)
+        launches = int(lc[0])
     nat.check_status()
 
     tokens_per_step = trainer.tokens_per_step
