@@ -352,6 +352,14 @@ class DecoderModel(PreTrainedModel):
         B, S, _ = hidden_states.shape
         mask = as_attn_mask(attention_mask, B, S, hidden_states.device)
         pos = position_ids
+        cp_state = None
+        if self.pc is not None and self.pc.sp_mode == "ring_attn" and self.pc.sp_size > 1:
+            hidden_states, pos, mask, cp_state, S_full = self._context_parallel_split(hidden_states, mask, kwargs)
+            B, S, _ = hidden_states.shape
+            kwargs = dict(kwargs, rope_len=max(int(kwargs.get("rope_len", 0) or 0), S_full))
+        elif self.pc is not None and self.pc.sp_mode == "all_to_all" and self.pc.sp_size > 1 and first:
+            # Ulysses: every rank keeps a contiguous 1/sp slice of the sequence between attention layers
+            hidden_states = comm.split_forward_gather_backward(hidden_states, 1, self.pc.sp_group, 1.0 / self.pc.sp_size)
         # positions beyond max_position_embeddings (context-parallel shards of a long sequence) need `rope_len`
         max_pos = max(S, int(kwargs.get("rope_len", 0) or 0))
         rope = self.rotary_emb(hidden_states.device, max_pos)
@@ -375,9 +383,28 @@ class DecoderModel(PreTrainedModel):
                 out = self.norm(delta)
             else:
                 out, _ = self.norm(delta, residual)
+            if self.pc is not None and self.pc.sp_mode == "all_to_all" and self.pc.sp_size > 1:
+                # Ulysses: back to the full sequence for the LM head (the loss is computed identically on every sp rank)
+                out = comm.gather_forward_split_backward(out, 1, self.pc.sp_group, float(self.pc.sp_size))
         else:
             out = delta if residual is None else delta + residual
-        return ModelOutput(last_hidden_state=out, router_logits=tuple(aux_losses) if aux_losses else None)
+        return ModelOutput(last_hidden_state=out, router_logits=tuple(aux_losses) if aux_losses else None, cp_state=cp_state)
+
+    def _context_parallel_split(self, hidden_states, mask, kwargs):
+        """Pick this rank's tokens (first stage) and express the mask through global positions."""
+        from ..parallel.cp import ContextParallelBatchSplitUtils as U, ContextParallelState
+
+        B, S, _ = hidden_states.shape
+        S_full = mask.q_bits.shape[1] if mask.q_bits is not None else int(kwargs.get("full_seq_len", 0) or S)
+        offsets = U.create_context_parallel_split(mask if mask.q_bits is not None else None, self.pc.sp_group,
+                                                  self.pc.cp_dist_mode, seq_len=S_full, batch=B, device=hidden_states.device)
+        if offsets is None:
+            return hidden_states, None, mask, None, S_full
+        state = ContextParallelState(self.pc.sp_group, offsets, mask, hidden_states.device)
+        if S == S_full:
+            hidden_states = hidden_states.index_select(1, state.mine)
+        pos = state.mine.int()[None].expand(B, -1).contiguous()
+        return hidden_states, pos, state.local_mask, state, S_full
 
 
 def as_attn_mask(attention_mask, B: int, S: int, device) -> A.AttnMask:
@@ -441,11 +468,14 @@ class DecoderForCausalLM(PreTrainedModel):
         result = ModelOutput(router_logits=out.router_logits)
         tp_group = self.pc.tp_group if self.pc is not None else None
         softcap = self.model.spec.final_softcap
+        cp_state = out.get("cp_state")
         if labels is not None and not softcap:
             tgt = labels
             if shift_labels:
                 tgt = torch.full_like(labels, -100)
                 tgt[:, :-1] = labels[:, 1:]
+            if cp_state is not None and cp_state.mine is not None and tgt.shape[1] != h.shape[1]:
+                tgt = tgt.index_select(1, cp_state.mine)
             w = self.lm_head.weight
             valid = getattr(self, "valid_vocab", None)
             if valid is not None and valid < w.shape[0]:
@@ -453,8 +483,17 @@ class DecoderForCausalLM(PreTrainedModel):
             h_in = comm.reduce_backward(h, tp_group) if tp_group is not None else h  # each vocab shard yields a partial dh
             loss_sum, n_valid = linear_cross_entropy(h_in, w, tgt, tp_group=tp_group,
                                                      vocab_start=self.vocab_start, reduction="sum_and_count")
-            result["loss_sum"], result["num_valid"] = loss_sum, n_valid
-            result["loss"] = loss_sum / n_valid.clamp(min=1).to(loss_sum.dtype)
+            if cp_state is not None:
+                # every context-parallel rank sees a token subset: normalise by the global token count and
+                # pre-multiply by sp so that the dp x sp gradient average yields d(sum / count)
+                total = n_valid.clone().float()
+                torch.distributed.all_reduce(total, group=cp_state.group)
+                sp = torch.distributed.get_world_size(cp_state.group)
+                result["loss_sum"], result["num_valid"] = loss_sum, total
+                result["loss"] = loss_sum * sp / total.clamp(min=1).to(loss_sum.dtype)
+            else:
+                result["loss_sum"], result["num_valid"] = loss_sum, n_valid
+                result["loss"] = loss_sum / n_valid.clamp(min=1).to(loss_sum.dtype)
         if return_logits or (labels is None) or softcap:
             logits = linear(comm.reduce_backward(h, tp_group) if tp_group is not None else h, self.lm_head.weight)
             if tp_group is not None and comm._world(tp_group) > 1 and not (self.pc and self.pc.parallel_output and labels is not None):

@@ -196,7 +196,22 @@ class _VisionBase(PreTrainedModel):
         if hidden_states is not None:
             return hidden_states
         assert self.holds(embed_name), "this stage has no embeddings: pass hidden_states"
-        return embed_fn(pixel_values)
+        x = embed_fn(pixel_values)
+        group = getattr(self, "_cp_group", None)
+        if group is not None:
+            from ..parallel import comm
+
+            x = comm.split_forward_gather_backward(x, 1, group)  # contiguous uniform token chunks
+        return x
+
+    def _attn_mask(self, device):
+        """Full attention; under context parallelism the mask carries the gather state."""
+        group = getattr(self, "_cp_group", None)
+        if group is None:
+            return A.AttnMask.full()
+        from ..parallel.cp import ContextParallelState
+
+        return ContextParallelState(group, None, None, device).local_mask
 
 
 class SiglipVisionModel(_VisionBase):
@@ -216,7 +231,7 @@ class SiglipVisionModel(_VisionBase):
     def forward(self, pixel_values=None, hidden_states=None, output_hidden_states=False, **kw):
         vm = self.vision_model
         x = self._stage_input(pixel_values, hidden_states, "vision_model.embeddings", lambda p: vm.embeddings(p))
-        x = vm.encoder.run(x, A.AttnMask.full(), self.gradient_checkpointing and self.training)
+        x = vm.encoder.run(x, self._attn_mask(x.device), self.gradient_checkpointing and self.training)
         if not self.holds("vision_model.post_layernorm"):
             return ModelOutput(hidden_states=x)
         last = vm.post_layernorm(x)
@@ -272,7 +287,7 @@ class CLIPVisionModel(_VisionBase):
         vm = self.vision_model
         x = self._stage_input(pixel_values, hidden_states, "vision_model.embeddings",
                               lambda p: vm.pre_layrnorm(vm.embeddings(p)))
-        x = vm.encoder.run(x, A.AttnMask.full(), self.gradient_checkpointing and self.training)
+        x = vm.encoder.run(x, self._attn_mask(x.device), self.gradient_checkpointing and self.training)
         if not self.holds("vision_model.post_layernorm"):
             return ModelOutput(hidden_states=x)
         pooled = vm.post_layernorm(x[:, 0])
@@ -371,7 +386,7 @@ class ViTModel(_VisionBase):
 
     def forward(self, pixel_values=None, hidden_states=None, **kw):
         x = self._stage_input(pixel_values, hidden_states, "embeddings", lambda p: self.embeddings(p))
-        x = self.encoder.run(x, A.AttnMask.full(), self.gradient_checkpointing and self.training)
+        x = self.encoder.run(x, self._attn_mask(x.device), self.gradient_checkpointing and self.training)
         if not self.holds("layernorm"):
             return ModelOutput(hidden_states=x)
         last = self.layernorm(x)

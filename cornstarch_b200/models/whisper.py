@@ -119,8 +119,16 @@ class WhisperEncoder(PreTrainedModel):
         if hidden_states is None:
             assert self.holds("conv1"), "this stage has no front-end: pass hidden_states"
             hidden_states = self.embed(input_features)
+            if getattr(self, "_cp_group", None) is not None:
+                from ..parallel import comm
+
+                hidden_states = comm.split_forward_gather_backward(hidden_states, 1, self._cp_group)
         x = hidden_states
         mask = A.AttnMask.full()
+        if getattr(self, "_cp_group", None) is not None:
+            from ..parallel.cp import ContextParallelState
+
+            mask = ContextParallelState(self._cp_group, None, None, x.device).local_mask
         for layer in self.layers:
             if is_released(layer):
                 continue

@@ -179,3 +179,48 @@ def _all_to_all(x, scatter_dim, gather_dim, group):
 def all_to_all_comm(x, group, scatter_dim: int = 2, gather_dim: int = 1):
     """``[B, S/sp, H] <-> [B, S, H/sp]`` exchange of Ulysses sequence parallelism (equal shards)."""
     return x if _world(group) == 1 else _AllToAll.apply(x, scatter_dim, gather_dim, group)
+
+
+def reduce_scatter_uneven(x: torch.Tensor, dim: int, group, sizes: list[int]) -> torch.Tensor:
+    """Sum ``x`` over the group and return this rank's slice of ``dim`` (slices may differ in size)."""
+    ws, rank = dist.get_world_size(group), dist.get_rank(group)
+    x = x.contiguous()
+    if dist.get_backend(group) != "gloo" and len(set(sizes)) == 1 and dim == 0:
+        out = torch.empty((sizes[0], *x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x, group=group)
+        return out
+    if dist.get_backend(group) != "gloo":
+        # pad every rank's slice to the largest one so that a plain reduce_scatter applies
+        mx = max(sizes)
+        chunks, start = [], 0
+        for s in sizes:
+            c = x.narrow(dim, start, s)
+            if s < mx:
+                pad_shape = list(c.shape)
+                pad_shape[dim] = mx - s
+                c = torch.cat([c, c.new_zeros(pad_shape)], dim=dim)
+            chunks.append(c.contiguous())
+            start += s
+        out = torch.empty_like(chunks[0])
+        dist.reduce_scatter(out, chunks, group=group)
+        return out.narrow(dim, 0, sizes[rank]).contiguous()
+    dist.all_reduce(x, group=group)
+    return x.narrow(dim, sum(sizes[:rank]), sizes[rank]).contiguous()
+
+
+class _GatherFwdReduceScatterBwd(torch.autograd.Function):
+    """All-gather (uneven) in forward, reduce-scatter of the gradient in backward: K/V under context parallelism."""
+
+    @staticmethod
+    def forward(ctx, x, dim, group, sizes):
+        out, sizes = all_gather_uneven(x, dim, group, sizes)
+        ctx.dim, ctx.group, ctx.sizes = dim, group, sizes
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return reduce_scatter_uneven(g, ctx.dim, ctx.group, ctx.sizes), None, None, None
+
+
+def gather_forward_reduce_scatter_backward(x, dim: int, group, sizes: list[int] | None = None):
+    return x if _world(group) == 1 else _GatherFwdReduceScatterBwd.apply(x, dim, group, sizes)
