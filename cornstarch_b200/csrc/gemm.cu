@@ -36,6 +36,12 @@ struct GemmParams {
   int act;
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int* status;
+  // ---- fused all-reduce through peer memory (ar_world > 1): the epilogue publishes this rank's partial
+  // tile in its own staging buffer and raises a per-tile flag on every rank; reducer CTAs of the same
+  // launch sum the partial tiles of all ranks (peer loads over NVLink) into C as tiles become ready.
+  int ar_world, ar_rank, ar_epoch, n_gemm_ctas, ar_max_tiles;
+  __nv_bfloat16* ar_part[8];   // staging buffer [M][N] of every rank (index = rank), peer-mapped
+  int* ar_flags[8];            // flag array [world][max_tiles] of every rank, peer-mapped
 };
 
 template <int BN>
@@ -91,6 +97,76 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   }
 }
 
+// Reducer CTAs of a fused GEMM + all-reduce launch: for every output tile (strided over the reducer
+// CTAs) wait (bounded) until each rank has raised the tile's flag for this epoch, then add up the
+// partial tiles of all ranks, read straight from their staging buffers, and store the sum into C.
+template <int BN>
+__device__ void ar_reducer(const GemmParams& p, int num_tiles, int rid, int nred) {
+  __shared__ int s_ok;
+  const int tid = threadIdx.x;
+  for (int tile = rid; tile < num_tiles; tile += nred) {
+    if (tid == 0) s_ok = 1;
+    __syncthreads();
+    if (tid < p.ar_world) {
+      const int* flag = p.ar_flags[p.ar_rank] + tid * p.ar_max_tiles + tile;
+      uint64_t t0 = 0;
+      bool seen = false;
+      for (uint32_t i = 0; i < CSB_SPIN_LIMIT; ++i) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v >= p.ar_epoch) { seen = true; break; }
+        if ((i & 255u) == 255u) {
+          const uint64_t now = global_timer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > CSB_WAIT_NS) break;
+        }
+      }
+      if (!seen) {
+        atomicExch(p.status, ST_TIMEOUT_PEER_FLAG);
+        s_ok = 0;
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;  // a peer never delivered: leave the rest of C untouched, the status word says why
+    int m_blk, n_blk;
+    tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+    const int row0 = m_blk * BM, col0 = n_blk * BN;
+    const int rows = min(BM, p.M - row0), cols = min(BN, p.N - col0);
+    const int vec_per_row = (cols + 7) / 8;
+    for (int i = tid; i < rows * vec_per_row; i += blockDim.x) {
+      const int r = i / vec_per_row, c = (i % vec_per_row) * 8;
+      const size_t off = static_cast<size_t>(row0 + r) * p.N + col0 + c;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (c + 8 <= cols) {
+        for (int src = 0; src < p.ar_world; ++src) {
+          const uint4 u = *reinterpret_cast<const uint4*>(p.ar_part[src] + off);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
+        }
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row0 + r) * p.ldc + col0 + c;
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]);
+        o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]);
+        o.w = pack_bf16x2(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(dst) = o;
+      } else {
+        for (int j = 0; c + j < cols; ++j) {
+          float a = 0.f;
+          for (int src = 0; src < p.ar_world; ++src) a += __bfloat162float(p.ar_part[src][off + j]);
+          reinterpret_cast<__nv_bfloat16*>(p.C)[static_cast<size_t>(row0 + r) * p.ldc + col0 + c + j] = __float2bfloat16(a);
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
@@ -108,6 +184,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+
+  if (p.ar_world > 1 && static_cast<int>(blockIdx.x) >= p.n_gemm_ctas) {
+    ar_reducer<BN>(p, num_tiles, blockIdx.x - p.n_gemm_ctas, gridDim.x - p.n_gemm_ctas);
+    return;
+  }
+  const int gemm_ctas = p.ar_world > 1 ? p.n_gemm_ctas : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; ++s) {
@@ -139,7 +221,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas) {
         int m_blk, n_blk;
         tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
         for (int kb = 0; kb < p.num_k_blocks; ++kb, ++it) {
@@ -179,7 +261,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t it = 0;
       uint32_t local_tile = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas, ++local_tile) {
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!wait_or_abort(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) {
@@ -221,7 +303,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
     uint32_t local_tile = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas, ++local_tile) {
       int m_blk, n_blk;
       tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
       const uint32_t acc = local_tile & 1;
@@ -235,7 +317,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const int row = m_blk * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      const bool vec_ok = (p.ldc & 7) == 0;
+      const bool vec_ok = ((p.ar_world > 1 ? p.N : p.ldc) & 7) == 0;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
@@ -273,7 +355,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = p.accumulate ? dst[j] + f[j] : f[j];
             }
           } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+            __nv_bfloat16* dst = (p.ar_world > 1)
+                                     ? p.ar_part[p.ar_rank] + static_cast<size_t>(row) * p.N + col0
+                                     : reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
             if (full && vec_ok) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
@@ -306,6 +390,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
+      if (p.ar_world > 1) {
+        // all 128 epilogue threads have written their rows of the partial tile: publish it
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (warp == 2 && lane < p.ar_world) {
+          __threadfence_system();
+          int* flag = p.ar_flags[lane] + p.ar_rank * p.ar_max_tiles + tile;
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.ar_epoch) : "memory");
+        }
+      }
     }
   }
 
@@ -344,7 +437,18 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
   int tiles = p.num_m_blocks * p.num_n_blocks;
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-  kfn<<<grid, 192, L::DYN_BYTES, stream>>>(ta, tb, p);
+  GemmParams q = p;
+  if (q.ar_world > 1) {
+    // reducer CTAs ride in the same launch; every CTA must be resident at once (1 CTA per SM)
+    int nred = q.n_gemm_ctas > 0 ? q.n_gemm_ctas : 16;  // on entry n_gemm_ctas carries the requested reducer count
+    if (nred > sm_count() / 2) nred = sm_count() / 2;
+    int ngemm = sm_count() - nred;
+    if (ngemm > tiles) ngemm = tiles;
+    if (max_ctas > 0 && ngemm > max_ctas) ngemm = max_ctas;
+    q.n_gemm_ctas = ngemm;
+    grid = ngemm + nred;
+  }
+  kfn<<<grid, 192, L::DYN_BYTES, stream>>>(ta, tb, q);
   return launch_result();
 }
 
@@ -378,6 +482,8 @@ CSB_API int csb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   p.num_n_blocks = (N + bn - 1) / bn;
   p.num_k_blocks = (K + BK - 1) / BK;
   p.status = status;
+  p.ar_world = 1; p.ar_rank = 0; p.ar_epoch = 0; p.n_gemm_ctas = 0; p.ar_max_tiles = 0;
+  for (int i = 0; i < 8; ++i) { p.ar_part[i] = nullptr; p.ar_flags[i] = nullptr; }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define CSB_DISPATCH(BNV)                                                                       \
   if (!a_mn_major && !b_mn_major) return launch_gemm<BNV, false, false>(A, B, p, lda, ldb, max_ctas, s); \
@@ -387,4 +493,43 @@ CSB_API int csb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   if (bn == 256) { CSB_DISPATCH(256) }
   CSB_DISPATCH(128)
 #undef CSB_DISPATCH
+}
+
+
+// Fused GEMM + all-reduce across `world` ranks through peer-mapped memory:
+//   C = sum over ranks of op(A_rank) * op(B_rank)^T      (bf16 out, every rank ends with the full sum)
+// part_ptrs[r]  : staging buffer of rank r (>= M*N bf16), flags_ptrs[r]: int32 [world][max_tiles] of rank r;
+// both arrays hold `world` device pointers valid on THIS rank (own buffer + peer mappings).
+// epoch must grow by one per call on a given (staging, flags) pair and be the same on all ranks; callers
+// alternate between two pairs so that a rank never overwrites a partial tile a slower peer still reads.
+CSB_API int csb_gemm_allreduce_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                    int a_mn_major, int b_mn_major, int world, int rank, void* const* part_ptrs,
+                                    void* const* flags_ptrs, int max_tiles, int epoch, int n_reducers, int tile_n,
+                                    int* status, void* stream) {
+  using namespace csb;
+  if (M <= 0 || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || (N & 7) || world < 2 || world > 8) return CSB_ERR_BAD_ARG;
+  int bn = (tile_n == 128 || tile_n == 256) ? tile_n : ((N >= 256) ? 256 : 128);
+  GemmParams p;
+  p.C = C; p.bias = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.out_fp32 = 0; p.accumulate = 0; p.act = 0;
+  p.num_m_blocks = (M + BM - 1) / BM;
+  p.num_n_blocks = (N + bn - 1) / bn;
+  p.num_k_blocks = (K + BK - 1) / BK;
+  if (p.num_m_blocks * p.num_n_blocks > max_tiles) return CSB_ERR_TOO_LARGE;
+  p.status = status;
+  p.ar_world = world; p.ar_rank = rank; p.ar_epoch = epoch; p.n_gemm_ctas = n_reducers; p.ar_max_tiles = max_tiles;
+  for (int i = 0; i < 8; ++i) {
+    p.ar_part[i] = i < world ? reinterpret_cast<__nv_bfloat16*>(part_ptrs[i]) : nullptr;
+    p.ar_flags[i] = i < world ? reinterpret_cast<int*>(flags_ptrs[i]) : nullptr;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+#define CSB_DISPATCH_AR(BNV)                                                                       \
+  if (!a_mn_major && !b_mn_major) return launch_gemm<BNV, false, false>(A, B, p, lda, ldb, 0, s); \
+  if (!a_mn_major && b_mn_major) return launch_gemm<BNV, false, true>(A, B, p, lda, ldb, 0, s);   \
+  if (a_mn_major && !b_mn_major) return launch_gemm<BNV, true, false>(A, B, p, lda, ldb, 0, s);   \
+  return launch_gemm<BNV, true, true>(A, B, p, lda, ldb, 0, s);
+  if (bn == 256) { CSB_DISPATCH_AR(256) }
+  CSB_DISPATCH_AR(128)
+#undef CSB_DISPATCH_AR
 }

@@ -1,0 +1,65 @@
+"""Fused GEMM + all-reduce through peer memory on 2 GPUs (child processes, NCCL only for bootstrap):
+result equals the fp32 sum of the per-rank products; repeated calls exercise the epoch / double-buffer logic."""
+
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        from cornstarch_b200.ops import _native as nat
+        from cornstarch_b200.parallel.symm import FusedTensorParallel
+
+        ftp = FusedTensorParallel.get(dist.group.WORLD)
+        assert ftp is not None
+        for it, (M, N, K, amn, bmn) in enumerate([(512, 1024, 256, 0, 0), (1000, 776, 520, 0, 1), (2048, 4096, 1024, 0, 0),
+                                                  (512, 1024, 256, 0, 0), (384, 512, 640, 1, 1)]):
+            g = torch.Generator().manual_seed(100 * it + rank)
+            a = torch.randn((K, M) if amn else (M, K), generator=g).cuda().bfloat16()
+            b = torch.randn((K, N) if bmn else (N, K), generator=g).cuda().bfloat16()
+            out = ftp.gemm_allreduce(a, b, bool(amn), bool(bmn))
+            A_ = a.float().t() if amn else a.float()
+            B_ = b.float().t() if bmn else b.float()
+            ref = A_ @ B_.t()
+            dist.all_reduce(ref)
+            torch.cuda.synchronize()
+            err = (out.float() - ref).abs().max().item()
+            assert err <= 2e-2 * ref.abs().max().item() + 0.5, (it, err)
+        nat.check_status()
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_gemm_allreduce_two_gpus():
+    from tests.dist_utils import free_port
+
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+    results = []
+    while not q.empty():
+        results.append(q.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert len(results) == 2 and all(r[1] == "ok" for r in results), results
