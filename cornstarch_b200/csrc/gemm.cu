@@ -36,13 +36,33 @@ struct GemmParams {
   int act;
   int num_m_blocks, num_n_blocks, num_k_blocks;
   int* status;
-  // ---- fused all-reduce through peer memory (ar_world > 1): the epilogue publishes this rank's partial
-  // tile in its own staging buffer and raises a per-tile flag on every rank; reducer CTAs of the same
-  // launch sum the partial tiles of all ranks (peer loads over NVLink) into C as tiles become ready.
-  int ar_world, ar_rank, ar_epoch, n_gemm_ctas, ar_max_tiles;
-  __nv_bfloat16* ar_part[8];   // staging buffer [M][N] of every rank (index = rank), peer-mapped
-  int* ar_flags[8];            // flag array [world][max_tiles] of every rank, peer-mapped
+  int tma_epi;  // epilogue through shared memory + TMA stores (needs a 16-byte aligned C with 16-byte row pitch)
+  // ---- fused all-reduce through peer memory (ar_world > 1).  Tile rows are owned by ranks in contiguous
+  // ranges; every rank walks the ranges starting after its own and ends with its own.  For a tile it does
+  // not own, the epilogue PUSHES the bf16 partial into its slot of the owner's inbox (posted NVLink
+  // stores) and bumps an arrival counter there.  For a tile it owns, the epilogue waits (bounded) for the
+  // peers' partials, adds them to its TMEM accumulator in registers, stores the sum into C and pushes it
+  // into the `final` buffer of every peer.  No extra CTAs, no extra pass over the local partial.
+  int ar_world, ar_rank;
+  int ar_base;                 // value of every arrival counter of this context before this call
+  long ar_slot_elems;          // elements per inbox slot
+  __nv_bfloat16* ar_inbox[8];  // inbox of every rank (peer-mapped): [world slots][M][N]; slot s = partial of rank s
+  __nv_bfloat16* ar_final[8];  // final buffer [M][N] of every rank (peer-mapped): rows owned by others land here
+  int* ar_cnt_part[8];         // per rank: int32 [world][512 tile rows], bumped by the sender of a partial tile
+  int* ar_cnt_final[8];        // per rank: int32 [world][512 tile rows], bumped by the owner after pushing a final tile
 };
+
+constexpr int AR_MAX_ROWS = 512;
+
+__host__ __device__ __forceinline__ int ar_range_start(int range, int num_m, int world) {
+  return static_cast<int>((static_cast<long>(range) * num_m) / world);
+}
+__host__ __device__ __forceinline__ int ar_owner(int m_blk, int num_m, int world) {
+  int o = static_cast<int>((static_cast<long>(m_blk) * world) / num_m);
+  while (o + 1 < world && ar_range_start(o + 1, num_m, world) <= m_blk) ++o;
+  while (o > 0 && ar_range_start(o, num_m, world) > m_blk) --o;
+  return o;
+}
 
 template <int BN>
 struct SmemLayout {
@@ -50,7 +70,9 @@ struct SmemLayout {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;  // two 16 KB output slabs (128 rows x 128 B, swizzled)
+  static constexpr int EPI_SLAB_BYTES = 128 * 128;
+  static constexpr int BAR_OFFSET = EPI_OFFSET + 2 * EPI_SLAB_BYTES;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem_addr, abort
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;  // slack for 1024-byte alignment
@@ -81,6 +103,29 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
   n_blk = in_group / gsz;
 }
 
+// Rotated order for the fused all-reduce: the tile-row index is shifted so that a rank starts with the
+// rows owned by the next rank and finishes with its own.
+__device__ __forceinline__ void tile_coords_rot(int tile, int num_m, int num_n, int rot, int& m_blk, int& n_blk) {
+  tile_coords(tile, num_m, num_n, m_blk, n_blk);
+  m_blk += rot;
+  if (m_blk >= num_m) m_blk -= num_m;
+}
+
+__device__ __forceinline__ bool spin_until_ge(const int* addr, int target) {
+  uint64_t t0 = 0;
+  for (uint32_t i = 0; i < CSB_SPIN_LIMIT; ++i) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    if (v >= target) return true;
+    if ((i & 63u) == 63u) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > CSB_WAIT_NS) return false;
+    }
+  }
+  return false;
+}
+
 __device__ __forceinline__ float apply_act(float x, int act) {
   switch (act) {
     case ACT_GELU_TANH: {
@@ -97,80 +142,149 @@ __device__ __forceinline__ float apply_act(float x, int act) {
   }
 }
 
-// Reducer CTAs of a fused GEMM + all-reduce launch: for every output tile (strided over the reducer
-// CTAs) wait (bounded) until each rank has raised the tile's flag for this epoch, then add up the
-// partial tiles of all ranks, read straight from their staging buffers, and store the sum into C.
+// Tensor maps of the output side: C itself and, for the fused all-reduce, this rank's slot in every
+// rank's inbox and every rank's final buffer (128-byte swizzled boxes of 128 rows x 128 bytes).
+struct EpiMaps {
+  CUtensorMap c;
+  CUtensorMap inbox[8];
+  CUtensorMap fin[8];
+};
+
+// Epilogue of one tile through shared memory: every thread owns one accumulator row; 128-byte row pieces
+// (64 bf16 or 32 fp32 columns) are staged in a swizzled slab and written with ONE TMA store per slab and
+// destination, so global and NVLink writes are full 128-byte lines.  `accumulate` uses the TMA reduce-add.
 template <int BN>
-__device__ void ar_reducer(const GemmParams& p, int num_tiles, int rid, int nred) {
-  __shared__ int s_ok;
-  const int tid = threadIdx.x;
-  for (int tile = rid; tile < num_tiles; tile += nred) {
-    if (tid == 0) s_ok = 1;
-    __syncthreads();
-    if (tid < p.ar_world) {
-      const int* flag = p.ar_flags[p.ar_rank] + tid * p.ar_max_tiles + tile;
-      uint64_t t0 = 0;
-      bool seen = false;
-      for (uint32_t i = 0; i < CSB_SPIN_LIMIT; ++i) {
-        int v;
-        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-        if (v >= p.ar_epoch) { seen = true; break; }
-        if ((i & 255u) == 255u) {
-          const uint64_t now = global_timer_ns();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > CSB_WAIT_NS) break;
-        }
-      }
-      if (!seen) {
-        atomicExch(p.status, ST_TIMEOUT_PEER_FLAG);
-        s_ok = 0;
+__device__ __forceinline__ void epilogue_tile_tma(const GemmParams& p, const EpiMaps& maps, uint8_t* epi_smem,
+                                                  uint32_t t_row, int m_blk, int n_blk, int quarter, int lane, int warp,
+                                                  uint32_t& slab_ctr, uint64_t* tmem_empty_bar, bool ar, int owner,
+                                                  bool mine) {
+  const int r = quarter * 32 + lane;
+  const int row = m_blk * BM + r;
+  const bool e0 = (warp == 2 && lane == 0);
+  const int cps = p.out_fp32 ? 32 : 64;  // columns per 128-byte slab row
+  const int n_slabs = BN / cps;
+  for (int s = 0; s < n_slabs; ++s, ++slab_ctr) {
+    const int col0 = n_blk * BN + s * cps;
+    const bool last = (s == n_slabs - 1) || (col0 + cps >= p.N);
+    float f[64];
+    {
+      uint32_t v[32];
+      tmem_ld_32x32(t_row + s * cps, v);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+      if (cps == 64) {
+        tmem_ld_32x32(t_row + s * cps + 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[32 + j] = __uint_as_float(v[j]);
       }
     }
-    __syncthreads();
-    if (!s_ok) return;  // a peer never delivered: leave the rest of C untouched, the status word says why
-    int m_blk, n_blk;
-    tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
-    const int row0 = m_blk * BM, col0 = n_blk * BN;
-    const int rows = min(BM, p.M - row0), cols = min(BN, p.N - col0);
-    const int vec_per_row = (cols + 7) / 8;
-    for (int i = tid; i < rows * vec_per_row; i += blockDim.x) {
-      const int r = i / vec_per_row, c = (i % vec_per_row) * 8;
-      const size_t off = static_cast<size_t>(row0 + r) * p.N + col0 + c;
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      if (c + 8 <= cols) {
-        for (int src = 0; src < p.ar_world; ++src) {
-          const uint4 u = *reinterpret_cast<const uint4*>(p.ar_part[src] + off);
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    if (last) {
+      tc_fence_before();
+      mbar_arrive(tmem_empty_bar);  // the accumulator buffer can be overwritten by the next tile's MMAs
+    }
+    if (p.bias) {
+      const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(h[j]);
-            acc[2 * j] += f.x;
-            acc[2 * j + 1] += f.y;
+      for (int j = 0; j < 64; ++j)
+        if (j < cps && col0 + j < p.N) f[j] += __bfloat162float(b[j]);
+    }
+    if (p.act != ACT_NONE) {
+#pragma unroll
+      for (int j = 0; j < 64; ++j)
+        if (j < cps) f[j] = apply_act(f[j], p.act);
+    }
+    if (mine) {
+      // bf16-round my partial like the peers', then add theirs (they sit in my own inbox: local reads)
+#pragma unroll
+      for (int j = 0; j < 64; ++j) f[j] = __bfloat162float(__float2bfloat16(f[j]));
+      if (row < p.M) {
+        const size_t off = static_cast<size_t>(row) * p.N + col0;
+        for (int src = 0; src < p.ar_world; ++src) {
+          if (src == p.ar_rank) continue;
+          const __nv_bfloat16* in = p.ar_inbox[p.ar_rank] + static_cast<size_t>(src) * p.ar_slot_elems + off;
+          if (col0 + 64 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 64; j += 8) {
+              const uint4 u = *reinterpret_cast<const uint4*>(in + j);
+              const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                f[j + 2 * q] += __uint_as_float(w[q] << 16);
+                f[j + 2 * q + 1] += __uint_as_float(w[q] & 0xffff0000u);
+              }
+            }
+          } else {
+            for (int j = 0; j < 64 && col0 + j < p.N; ++j) f[j] += __bfloat162float(in[j]);
           }
         }
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row0 + r) * p.ldc + col0 + c;
-        uint4 o;
-        o.x = pack_bf16x2(acc[0], acc[1]);
-        o.y = pack_bf16x2(acc[2], acc[3]);
-        o.z = pack_bf16x2(acc[4], acc[5]);
-        o.w = pack_bf16x2(acc[6], acc[7]);
-        *reinterpret_cast<uint4*>(dst) = o;
-      } else {
-        for (int j = 0; c + j < cols; ++j) {
-          float a = 0.f;
-          for (int src = 0; src < p.ar_world; ++src) a += __bfloat162float(p.ar_part[src][off + j]);
-          reinterpret_cast<__nv_bfloat16*>(p.C)[static_cast<size_t>(row0 + r) * p.ldc + col0 + c + j] = __float2bfloat16(a);
-        }
       }
     }
-    __syncthreads();
+    uint8_t* buf = epi_smem + (slab_ctr & 1) * SmemLayout<BN>::EPI_SLAB_BYTES;
+    if (e0) tma_store_wait_read<1>();  // the store that last used this slab has finished reading it
+    asm volatile("bar.sync 2, 128;" ::: "memory");
+    if (p.out_fp32) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 u = make_uint4(__float_as_uint(f[4 * j]), __float_as_uint(f[4 * j + 1]), __float_as_uint(f[4 * j + 2]),
+                                   __float_as_uint(f[4 * j + 3]));
+        *reinterpret_cast<uint4*>(buf + sw128_offset(r, j)) = u;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint4 u;
+        u.x = pack_bf16x2(f[8 * j + 0], f[8 * j + 1]);
+        u.y = pack_bf16x2(f[8 * j + 2], f[8 * j + 3]);
+        u.z = pack_bf16x2(f[8 * j + 4], f[8 * j + 5]);
+        u.w = pack_bf16x2(f[8 * j + 6], f[8 * j + 7]);
+        *reinterpret_cast<uint4*>(buf + sw128_offset(r, j)) = u;
+      }
+    }
+    fence_proxy_async_smem();
+    asm volatile("bar.sync 2, 128;" ::: "memory");
+    if (e0) {
+      const int y = m_blk * BM;
+      if (!ar) {
+        if (p.accumulate) tma_reduce_add_2d(&maps.c, buf, col0, y);
+        else tma_store_2d(&maps.c, buf, col0, y);
+      } else if (!mine) {
+        tma_store_2d(&maps.inbox[owner], buf, col0, y);
+      } else {
+        tma_store_2d(&maps.c, buf, col0, y);
+        for (int d = 0; d < p.ar_world; ++d)
+          if (d != p.ar_rank) tma_store_2d(&maps.fin[d], buf, col0, y);
+      }
+      tma_store_commit();
+    }
+    if (last) {
+      slab_ctr += 1;
+      break;
+    }
+  }
+  if (ar && e0) {
+    // the tile's stores must have landed before the tile is counted on the receiving side
+    tma_store_wait<0>();
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence_system();
+    if (!mine) {
+      int* cnt = p.ar_cnt_part[owner] + p.ar_rank * AR_MAX_ROWS + m_blk;
+      asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+    } else {
+      for (int d = 0; d < p.ar_world; ++d) {
+        if (d == p.ar_rank) continue;
+        int* cnt = p.ar_cnt_final[d] + p.ar_rank * AR_MAX_ROWS + m_blk;
+        asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+      }
+    }
   }
 }
 
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const GemmParams p) {
+                 const __grid_constant__ EpiMaps epi_maps, const GemmParams p) {
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -184,12 +298,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = p.num_m_blocks * p.num_n_blocks;
-
-  if (p.ar_world > 1 && static_cast<int>(blockIdx.x) >= p.n_gemm_ctas) {
-    ar_reducer<BN>(p, num_tiles, blockIdx.x - p.n_gemm_ctas, gridDim.x - p.n_gemm_ctas);
-    return;
-  }
-  const int gemm_ctas = p.ar_world > 1 ? p.n_gemm_ctas : static_cast<int>(gridDim.x);
+  const int rot = p.ar_world > 1 ? ar_range_start((p.ar_rank + 1) % p.ar_world, p.num_m_blocks, p.ar_world) : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; ++s) {
@@ -221,9 +330,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+        tile_coords_rot(tile, p.num_m_blocks, p.num_n_blocks, rot, m_blk, n_blk);
         for (int kb = 0; kb < p.num_k_blocks; ++kb, ++it) {
           const int s = it % L::STAGES;
           const uint32_t ph = (it / L::STAGES) & 1;
@@ -261,7 +370,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t it = 0;
       uint32_t local_tile = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas, ++local_tile) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!wait_or_abort(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) {
@@ -302,10 +411,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // ------------------------------------------------------------------ epilogue warps (2..5)
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
     uint32_t local_tile = 0;
+    uint32_t slab_ctr = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gemm_ctas, ++local_tile) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
       int m_blk, n_blk;
-      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, m_blk, n_blk);
+      tile_coords_rot(tile, p.num_m_blocks, p.num_n_blocks, rot, m_blk, n_blk);
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!wait_or_abort(&tmem_full[acc], acc_ph, abort_flag)) {
@@ -317,7 +427,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       const int row = m_blk * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      const bool vec_ok = ((p.ar_world > 1 ? p.N : p.ldc) & 7) == 0;
+      const bool vec_ok = (p.ldc & 7) == 0;
+      const bool ar = p.ar_world > 1;
+      const int owner = ar ? ar_owner(m_blk, p.num_m_blocks, p.ar_world) : 0;
+      const bool mine = ar && owner == p.ar_rank;
+      if (p.tma_epi) {
+        if (mine) {
+          bool arrived = true;
+          if (lane < p.ar_world && lane != p.ar_rank)
+            arrived = spin_until_ge(p.ar_cnt_part[p.ar_rank] + lane * AR_MAX_ROWS + m_blk, p.ar_base + p.num_n_blocks);
+          if (!__all_sync(0xffffffffu, arrived) && lane == 0) atomicExch(p.status, ST_TIMEOUT_PEER_FLAG);
+        }
+        epilogue_tile_tma<BN>(p, epi_maps, smem + L::EPI_OFFSET, t_row, m_blk, n_blk, quarter, lane, warp, slab_ctr,
+                              &tmem_empty[acc], ar, owner, mine);
+        continue;
+      }
+      if (mine) {
+        // the peers computed my rows first; by now their partials normally sit in my inbox already
+        bool arrived = true;
+        if (lane < p.ar_world && lane != p.ar_rank)
+          arrived = spin_until_ge(p.ar_cnt_part[p.ar_rank] + lane * AR_MAX_ROWS + m_blk, p.ar_base + p.num_n_blocks);
+        if (!__all_sync(0xffffffffu, arrived)) {
+          if (lane == 0) atomicExch(p.status, ST_TIMEOUT_PEER_FLAG);  // the sum below is then incomplete; the host sees the status
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
@@ -339,7 +472,74 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int j = 0; j < 32; ++j) f[j] = apply_act(f[j], p.act);
           }
           const bool full = (col0 + 32 <= p.N);
-          if (p.out_fp32) {
+          if (ar) {
+            const size_t off = static_cast<size_t>(row) * p.N + col0;
+            if (!mine) {
+              // partial tile -> my slot of the owner's inbox
+              __nv_bfloat16* dst = p.ar_inbox[owner] + static_cast<size_t>(p.ar_rank) * p.ar_slot_elems + off;
+              if (full) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 o;
+                  o.x = pack_bf16x2(f[j], f[j + 1]);
+                  o.y = pack_bf16x2(f[j + 2], f[j + 3]);
+                  o.z = pack_bf16x2(f[j + 4], f[j + 5]);
+                  o.w = pack_bf16x2(f[j + 6], f[j + 7]);
+                  *reinterpret_cast<uint4*>(dst + j) = o;
+                }
+              } else {
+                for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = __float2bfloat16(f[j]);
+              }
+            } else {
+              // my own partial is rounded to bf16 like the peers' so that the sum does not depend on who owns the row
+#pragma unroll
+              for (int j = 0; j < 32; ++j) f[j] = __bfloat162float(__float2bfloat16(f[j]));
+              for (int src = 0; src < p.ar_world; ++src) {
+                if (src == p.ar_rank) continue;
+                const __nv_bfloat16* in = p.ar_inbox[p.ar_rank] + static_cast<size_t>(src) * p.ar_slot_elems + off;
+                if (full) {
+#pragma unroll
+                  for (int j = 0; j < 32; j += 8) {
+                    const uint4 u = *reinterpret_cast<const uint4*>(in + j);
+                    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                      f[j + 2 * q] += __uint_as_float(w[q] << 16);
+                      f[j + 2 * q + 1] += __uint_as_float(w[q] & 0xffff0000u);
+                    }
+                  }
+                } else {
+                  for (int j = 0; j < 32 && col0 + j < p.N; ++j) f[j] += __bfloat162float(in[j]);
+                }
+              }
+              // final values: into my C and into every peer's `final` buffer
+              uint4 o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                o[j].x = pack_bf16x2(f[8 * j + 0], f[8 * j + 1]);
+                o[j].y = pack_bf16x2(f[8 * j + 2], f[8 * j + 3]);
+                o[j].z = pack_bf16x2(f[8 * j + 4], f[8 * j + 5]);
+                o[j].w = pack_bf16x2(f[8 * j + 6], f[8 * j + 7]);
+              }
+              __nv_bfloat16* cdst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+              if (full && vec_ok) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(cdst + 8 * j) = o[j];
+              } else {
+                for (int j = 0; j < 32 && col0 + j < p.N; ++j) cdst[j] = __float2bfloat16(f[j]);
+              }
+              for (int d = 0; d < p.ar_world; ++d) {
+                if (d == p.ar_rank) continue;
+                __nv_bfloat16* fdst = p.ar_final[d] + off;
+                if (full) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(fdst + 8 * j) = o[j];
+                } else {
+                  for (int j = 0; j < 32 && col0 + j < p.N; ++j) fdst[j] = __float2bfloat16(f[j]);
+                }
+              }
+            }
+          } else if (p.out_fp32) {
             float* dst = reinterpret_cast<float*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
             if (full && (p.ldc & 3) == 0) {
 #pragma unroll
@@ -355,9 +555,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
               for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = p.accumulate ? dst[j] + f[j] : f[j];
             }
           } else {
-            __nv_bfloat16* dst = (p.ar_world > 1)
-                                     ? p.ar_part[p.ar_rank] + static_cast<size_t>(row) * p.N + col0
-                                     : reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<size_t>(row) * p.ldc + col0;
             if (full && vec_ok) {
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
@@ -390,15 +588,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
-      if (p.ar_world > 1) {
-        // all 128 epilogue threads have written their rows of the partial tile: publish it
+      if (ar) {
+        // all 128 epilogue threads have issued their stores for this tile: make them visible, then count the tile
         asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (warp == 2 && lane < p.ar_world) {
-          __threadfence_system();
-          int* flag = p.ar_flags[lane] + p.ar_rank * p.ar_max_tiles + tile;
-          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(p.ar_epoch) : "memory");
+        if (warp == 2) {
+          if (!mine && lane == 0) {
+            __threadfence_system();
+            int* cnt = p.ar_cnt_part[owner] + p.ar_rank * AR_MAX_ROWS + m_blk;
+            asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+          } else if (mine && lane < p.ar_world && lane != p.ar_rank) {
+            __threadfence_system();
+            int* cnt = p.ar_cnt_final[lane] + p.ar_rank * AR_MAX_ROWS + m_blk;
+            asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
+          }
         }
       }
+    }
+    if (p.tma_epi && warp == 2 && lane == 0) tma_store_wait<0>();  // shared memory must outlive the bulk stores
+    if (p.ar_world > 1 && ok && blockIdx.x == 0) {
+      // before the launch completes, the final tiles that the other owners push into my `final` buffer must have
+      // landed: each epilogue thread of CTA 0 checks a share of the (tile row, owner) counters
+      const int t = (warp - 2) * 32 + lane;
+      bool all_in = true;
+      for (int mb = t; mb < p.num_m_blocks; mb += 128) {
+        const int o = ar_owner(mb, p.num_m_blocks, p.ar_world);
+        if (o == p.ar_rank) continue;
+        all_in = all_in && spin_until_ge(p.ar_cnt_final[p.ar_rank] + o * AR_MAX_ROWS + mb, p.ar_base + p.num_n_blocks);
+      }
+      if (!all_in) atomicExch(p.status, ST_TIMEOUT_PEER_FLAG);
     }
   }
 
@@ -438,17 +655,22 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   GemmParams q = p;
-  if (q.ar_world > 1) {
-    // reducer CTAs ride in the same launch; every CTA must be resident at once (1 CTA per SM)
-    int nred = q.n_gemm_ctas > 0 ? q.n_gemm_ctas : 16;  // on entry n_gemm_ctas carries the requested reducer count
-    if (nred > sm_count() / 2) nred = sm_count() / 2;
-    int ngemm = sm_count() - nred;
-    if (ngemm > tiles) ngemm = tiles;
-    if (max_ctas > 0 && ngemm > max_ctas) ngemm = max_ctas;
-    q.n_gemm_ctas = ngemm;
-    grid = ngemm + nred;
+  static EpiMaps em;
+  const int eb = q.out_fp32 ? 4 : 2;
+  const int cps = 128 / eb;
+  q.tma_epi = ((reinterpret_cast<uintptr_t>(q.C) & 15) == 0 && ((size_t)q.ldc * eb) % 16 == 0) ? 1 : 0;
+  if (q.ar_world > 1 && !q.tma_epi) return CSB_ERR_BAD_ARG;
+  if (q.tma_epi) {
+    r = make_tmap_2d_out(&em.c, q.C, q.M, q.N, q.ldc, q.out_fp32, cps, BM);
+    if (r) return r;
+    for (int d = 0; d < q.ar_world && q.ar_world > 1; ++d) {
+      r = make_tmap_2d_out(&em.inbox[d], q.ar_inbox[d] + (size_t)q.ar_rank * q.ar_slot_elems, q.M, q.N, q.N, 0, cps, BM);
+      if (r) return r;
+      r = make_tmap_2d_out(&em.fin[d], q.ar_final[d], q.M, q.N, q.N, 0, cps, BM);
+      if (r) return r;
+    }
   }
-  kfn<<<grid, 192, L::DYN_BYTES, stream>>>(ta, tb, q);
+  kfn<<<grid, 192, L::DYN_BYTES, stream>>>(ta, tb, em, q);
   return launch_result();
 }
 
@@ -482,8 +704,9 @@ CSB_API int csb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   p.num_n_blocks = (N + bn - 1) / bn;
   p.num_k_blocks = (K + BK - 1) / BK;
   p.status = status;
-  p.ar_world = 1; p.ar_rank = 0; p.ar_epoch = 0; p.n_gemm_ctas = 0; p.ar_max_tiles = 0;
-  for (int i = 0; i < 8; ++i) { p.ar_part[i] = nullptr; p.ar_flags[i] = nullptr; }
+  p.tma_epi = 0;
+  p.ar_world = 1; p.ar_rank = 0; p.ar_base = 0; p.ar_slot_elems = 0;
+  for (int i = 0; i < 8; ++i) { p.ar_inbox[i] = nullptr; p.ar_final[i] = nullptr; p.ar_cnt_part[i] = nullptr; p.ar_cnt_final[i] = nullptr; }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define CSB_DISPATCH(BNV)                                                                       \
   if (!a_mn_major && !b_mn_major) return launch_gemm<BNV, false, false>(A, B, p, lda, ldb, max_ctas, s); \
@@ -496,16 +719,21 @@ CSB_API int csb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
 }
 
 
-// Fused GEMM + all-reduce across `world` ranks through peer-mapped memory:
-//   C = sum over ranks of op(A_rank) * op(B_rank)^T      (bf16 out, every rank ends with the full sum)
-// part_ptrs[r]  : staging buffer of rank r (>= M*N bf16), flags_ptrs[r]: int32 [world][max_tiles] of rank r;
-// both arrays hold `world` device pointers valid on THIS rank (own buffer + peer mappings).
-// epoch must grow by one per call on a given (staging, flags) pair and be the same on all ranks; callers
-// alternate between two pairs so that a rank never overwrites a partial tile a slower peer still reads.
+// Fused GEMM + all-reduce across `world` ranks (2..8, one node) through peer-mapped memory:
+//   C = sum over ranks of op(A_rank) * op(B_rank)^T      (bf16)
+// On return of the launch, C holds the rows this rank owns (contiguous ranges of 128-row tile rows, range r for
+// rank r, see csb_ar_owned_rows) and `final` (this rank's buffer in final_ptrs) holds every other row; the
+// caller copies those rows from `final` into C (a plain device copy, stream-ordered after the launch).
+//   inbox_ptrs[r] : inbox of rank r, `world` slots of slot_elems bf16          (>= M*N each)
+//   final_ptrs[r] : final buffer of rank r, slot_elems bf16
+//   cnt_part_ptrs[r], cnt_final_ptrs[r] : int32 [world][512] arrival counters of rank r (monotonic, zero at start)
+// all four arrays hold `world` device pointers valid on THIS rank (own buffers + peer mappings).
+// `base` = num_n_blocks(of this shape) * number of earlier calls on this set of buffers; a set of buffers serves one
+// (M, N, tile_n) shape, and callers alternate between two sets so a rank never overwrites data a slower peer still reads.
 CSB_API int csb_gemm_allreduce_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                                    int a_mn_major, int b_mn_major, int world, int rank, void* const* part_ptrs,
-                                    void* const* flags_ptrs, int max_tiles, int epoch, int n_reducers, int tile_n,
-                                    int* status, void* stream) {
+                                    int a_mn_major, int b_mn_major, int world, int rank, void* const* inbox_ptrs,
+                                    void* const* final_ptrs, void* const* cnt_part_ptrs, void* const* cnt_final_ptrs,
+                                    long slot_elems, int base, int tile_n, int* status, void* stream) {
   using namespace csb;
   if (M <= 0 || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || (N & 7) || world < 2 || world > 8) return CSB_ERR_BAD_ARG;
   int bn = (tile_n == 128 || tile_n == 256) ? tile_n : ((N >= 256) ? 256 : 128);
@@ -516,12 +744,15 @@ CSB_API int csb_gemm_allreduce_bf16(const void* A, const void* B, void* C, int M
   p.num_m_blocks = (M + BM - 1) / BM;
   p.num_n_blocks = (N + bn - 1) / bn;
   p.num_k_blocks = (K + BK - 1) / BK;
-  if (p.num_m_blocks * p.num_n_blocks > max_tiles) return CSB_ERR_TOO_LARGE;
+  if (p.num_m_blocks > AR_MAX_ROWS || p.num_m_blocks < world || (long)M * N > slot_elems) return CSB_ERR_TOO_LARGE;
   p.status = status;
-  p.ar_world = world; p.ar_rank = rank; p.ar_epoch = epoch; p.n_gemm_ctas = n_reducers; p.ar_max_tiles = max_tiles;
+  p.tma_epi = 0;
+  p.ar_world = world; p.ar_rank = rank; p.ar_base = base; p.ar_slot_elems = slot_elems;
   for (int i = 0; i < 8; ++i) {
-    p.ar_part[i] = i < world ? reinterpret_cast<__nv_bfloat16*>(part_ptrs[i]) : nullptr;
-    p.ar_flags[i] = i < world ? reinterpret_cast<int*>(flags_ptrs[i]) : nullptr;
+    p.ar_inbox[i] = i < world ? reinterpret_cast<__nv_bfloat16*>(inbox_ptrs[i]) : nullptr;
+    p.ar_final[i] = i < world ? reinterpret_cast<__nv_bfloat16*>(final_ptrs[i]) : nullptr;
+    p.ar_cnt_part[i] = i < world ? reinterpret_cast<int*>(cnt_part_ptrs[i]) : nullptr;
+    p.ar_cnt_final[i] = i < world ? reinterpret_cast<int*>(cnt_final_ptrs[i]) : nullptr;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define CSB_DISPATCH_AR(BNV)                                                                       \
@@ -532,4 +763,17 @@ CSB_API int csb_gemm_allreduce_bf16(const void* A, const void* B, void* C, int M
   if (bn == 256) { CSB_DISPATCH_AR(256) }
   CSB_DISPATCH_AR(128)
 #undef CSB_DISPATCH_AR
+}
+
+// Rows [row_begin, row_end) of an M-row output that rank `rank` of `world` owns in the fused all-reduce,
+// and the tile width / tile-row count the launch will use for N columns.
+CSB_API int csb_ar_layout(int M, int N, int world, int rank, int tile_n, int* row_begin, int* row_end, int* num_n_blocks) {
+  using namespace csb;
+  int bn = (tile_n == 128 || tile_n == 256) ? tile_n : ((N >= 256) ? 256 : 128);
+  const int num_m = (M + BM - 1) / BM;
+  *row_begin = ar_range_start(rank, num_m, world) * BM;
+  int e = ar_range_start(rank + 1, num_m, world) * BM;
+  *row_end = e < M ? e : M;
+  *num_n_blocks = (N + bn - 1) / bn;
+  return 0;
 }

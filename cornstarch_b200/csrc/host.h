@@ -54,6 +54,27 @@ inline int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, 
   return 0;
 }
 
+// Row-major 2-D tensor of 2- or 4-byte elements (bf16 / fp32) for epilogue stores: box_cols * elem_bytes must be 128.
+inline int make_tmap_2d_out(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int fp32,
+                            uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return CSB_ERR_NO_DRIVER_SYMBOL;
+  const uint64_t eb = fp32 ? 4 : 2;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * eb};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "[cornstarch_b200] cuTensorMapEncodeTiled(out) failed: %d (base=%p rows=%llu cols=%llu ld=%llu)\n",
+            (int)r, base, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld);
+    return CSB_ERR_TENSORMAP;
+  }
+  return 0;
+}
+
 // General N-d bf16 tensor map (dims/strides innermost first; strides in BYTES for dims 1..n-1).
 inline int make_tmap_nd_bf16(CUtensorMap* out, const void* base, int nd, const uint64_t* dims_in,
                              const uint64_t* strides_bytes, const uint32_t* box_in,

@@ -191,7 +191,7 @@ class Attention(nn.Module):
         else:
             xin = self.q_proj.input_hook(x)
             biases = [self.q_proj.bias, self.k_proj.bias, self.v_proj.bias] if self.spec.qkv_bias else None
-            qkv = multi_linear(xin, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], biases)
+            qkv = multi_linear(xin, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], biases, tp=self.q_proj.tp_spec(x))
         ulysses = self.pc is not None and self.pc.sp_mode == "all_to_all" and self.pc.sp_size > 1
         if ulysses:
             # [B, S/sp, heads*D] -> [B, S, heads/sp*D] separately for q, k, v
@@ -241,7 +241,7 @@ class MLP(nn.Module):
         else:
             xin = self.gate_proj.input_hook(x)
             biases = [self.gate_proj.bias, self.up_proj.bias] if self.gate_proj.bias is not None else None
-            gu = multi_linear(xin, [self.gate_proj.weight, self.up_proj.weight], biases)
+            gu = multi_linear(xin, [self.gate_proj.weight, self.up_proj.weight], biases, tp=self.gate_proj.tp_spec(x))
         return self.down_proj(E.glu(gu, self.act))
 
 

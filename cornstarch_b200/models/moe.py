@@ -63,7 +63,7 @@ class _SwiGLUExpert(nn.Module):
 
     def forward(self, x, act="silu"):
         g, u, d = (getattr(self, n) for n in self.names)
-        gu = multi_linear(g.input_hook(x), [g.weight, u.weight])
+        gu = multi_linear(g.input_hook(x), [g.weight, u.weight], tp=g.tp_spec(x))
         return d(E.glu(gu, act))
 
 

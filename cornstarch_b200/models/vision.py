@@ -76,7 +76,7 @@ def encoder_block(x, ln1, q, k, v, o, ln2, fc1, fc2, act: str, num_heads: int, m
     h = ln1(x)
     hin = q.input_hook(h)
     biases = [q.bias, k.bias, v.bias] if (q.bias is not None or k.bias is not None or v.bias is not None) else None
-    qkv = multi_linear(hin, [q.weight, k.weight, v.weight], biases)
+    qkv = multi_linear(hin, [q.weight, k.weight, v.weight], biases, tp=q.tp_spec(h))
     nh = q.weight.shape[0] // D
     qh = qkv[..., : nh * D].view(B, S, nh, D)
     kh = qkv[..., nh * D : 2 * nh * D].view(B, S, nh, D)

@@ -55,6 +55,10 @@ class Linear(nn.Module):
     def input_hook(self, x):
         return x
 
+    def tp_spec(self, x):
+        """``("col" | "row", FusedTensorParallel)`` when the tensor-parallel reduce can be fused into the GEMM."""
+        return None
+
     def output_hook(self, y):
         return y
 
@@ -88,12 +92,20 @@ class ColumnParallelLinear(Linear):
         new.split_sizes = split_sizes
         return new
 
+    def tp_spec(self, x):
+        ftp = _fused_tp(self.process_group, x)
+        return ("col", ftp) if ftp is not None else None
+
     def input_hook(self, x):
+        if self.tp_spec(x) is not None:
+            return x  # the backward all-reduce of dx happens inside the fused GEMM
         return comm.reduce_backward(x, self.process_group)
 
     def forward(self, x):
-        x = comm.reduce_backward(x, self.process_group)
-        y = linear(x, self.weight, self.bias)
+        spec = self.tp_spec(x)
+        if spec is None:
+            x = comm.reduce_backward(x, self.process_group)
+        y = linear(x, self.weight, self.bias, tp=spec)
         if self.gather_output:
             y = comm.gather_forward_split_backward(y, -1 % y.dim(), self.process_group)
         return y
@@ -127,8 +139,28 @@ class RowParallelLinear(Linear):
             y = y + self.bias
         return y
 
+    def tp_spec(self, x):
+        ftp = _fused_tp(self.process_group, x)
+        return ("row", ftp) if ftp is not None else None
+
     def forward(self, x):
+        spec = self.tp_spec(x)
+        if spec is not None:
+            y = linear(x, self.weight, None, tp=spec)
+            return y + self.bias if self.bias is not None else y
         return self.output_hook(linear(x, self.weight, None))
+
+
+FUSED_TP_ENABLED = True
+
+
+def _fused_tp(group, x):
+    """The fused GEMM + all-reduce context of ``group`` for bf16 CUDA inputs (``None`` = use NCCL collectives)."""
+    if not FUSED_TP_ENABLED or group is None or not x.is_cuda or x.dtype != torch.bfloat16:
+        return None
+    from .parallel.symm import FusedTensorParallel
+
+    return FusedTensorParallel.get(group)
 
 
 def shard_rows(t: torch.Tensor, tp: int, rank: int, split_sizes: list[int] | None = None) -> torch.Tensor:
@@ -250,7 +282,8 @@ class DropoutForReplicatedInput(nn.Dropout):
 
 def qkv_linear(x, q: Linear, k: Linear, v: Linear):
     """The three attention projections as one GEMM when their weights are adjacent in memory."""
-    return multi_linear(x, [q.weight, k.weight, v.weight], [q.bias, k.bias, v.bias] if q.bias is not None or v.bias is not None else None)
+    return multi_linear(x, [q.weight, k.weight, v.weight], [q.bias, k.bias, v.bias] if q.bias is not None or v.bias is not None else None,
+                        tp=q.tp_spec(x))
 
 
 def init_std(hidden: int) -> float:

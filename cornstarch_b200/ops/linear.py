@@ -91,10 +91,11 @@ class _LinearFn(torch.autograd.Function):
     """y = x W^T + b with native backward; several (weight, bias) pairs share one input."""
 
     @staticmethod
-    def forward(ctx, x, n_w, act, *params):
+    def forward(ctx, x, n_w, act, tp, *params):
         weights = params[:n_w]
         biases = params[n_w:]
         x2 = _as_2d(x)
+        ctx.tp = tp
         fused_w = fuse_adjacent(weights) if n_w > 1 else weights[0]
         has_bias = biases[0] is not None
         fused_b = (fuse_adjacent_1d(biases) if n_w > 1 else biases[0]) if has_bias else None
@@ -102,7 +103,11 @@ class _LinearFn(torch.autograd.Function):
         # the returned tensor owns its storage (callers such as RoPE modify it in place)
         out = torch.empty((*x.shape[:-1], n_total), dtype=x.dtype, device=x.device)
         y = out.view(-1, n_total)
-        if fused_w is not None and (not has_bias or fused_b is not None):
+        assert not (tp is not None and tp[0] == "row" and (has_bias or n_w != 1)), "row-parallel: one weight, bias added after the reduce"
+        if tp is not None and tp[0] == "row" and fused_w is not None and not has_bias:
+            # row-parallel: partial products of all ranks are summed by the fused GEMM + all-reduce kernel
+            tp[1].gemm_allreduce(x2, fused_w, out=y)
+        elif fused_w is not None and (not has_bias or fused_b is not None):
             gemm(x2, fused_w, bias=fused_b, act=act, out=y)
         else:
             o = 0
@@ -125,7 +130,10 @@ class _LinearFn(torch.autograd.Function):
         fused_w = fuse_adjacent(weights) if n_w > 1 else weights[0]
         dx = None
         if ctx.needs_input_grad[0]:
-            if fused_w is not None:
+            if fused_w is not None and ctx.tp is not None and ctx.tp[0] == "col":
+                # column-parallel: dx is a partial sum over the output shards -> fused GEMM + all-reduce
+                dx = ctx.tp[1].gemm_allreduce(dy2, fused_w, b_mn_major=True)
+            elif fused_w is not None:
                 dx = gemm(dy2, fused_w, b_mn_major=True)
             else:
                 o = 0
@@ -133,10 +141,15 @@ class _LinearFn(torch.autograd.Function):
                 for i, w in enumerate(weights):
                     gemm(dy2[:, o : o + w.shape[0]], w, b_mn_major=True, out=dx, accumulate=i > 0)
                     o += w.shape[0]
+                if ctx.tp is not None and ctx.tp[0] == "col":
+                    # weights not adjacent in memory (no parameter arena): plain GEMMs, then the NCCL all-reduce
+                    import torch.distributed as dist
+
+                    dist.all_reduce(dx, group=ctx.tp[1].group)
             dx = dx.view(ctx.x_shape)
         dws: list = [None] * n_w
         dbs: list = [None] * n_w
-        need_w = [ctx.needs_input_grad[3 + i] for i in range(n_w)]
+        need_w = [ctx.needs_input_grad[4 + i] for i in range(n_w)]
         if any(need_w):
             mains = [getattr(w, "main_grad", None) for w in weights]
             fused_main = None
@@ -162,7 +175,7 @@ class _LinearFn(torch.autograd.Function):
             o = 0
             for i, (w, b) in enumerate(zip(weights, ctx.biases)):
                 n = w.shape[0]
-                if ctx.needs_input_grad[3 + n_w + i]:
+                if ctx.needs_input_grad[4 + n_w + i]:
                     seg = dy2[:, o : o + n]
                     main = getattr(b, "main_grad", None)
                     if main is not None:
@@ -171,18 +184,24 @@ class _LinearFn(torch.autograd.Function):
                     else:
                         dbs[i] = colsum(seg.contiguous() if not seg.is_contiguous() else seg)
                 o += n
-        return (dx, None, None, *dws, *dbs)
+        return (dx, None, None, None, *dws, *dbs)
 
 
-def multi_linear(x: torch.Tensor, weights: Sequence[torch.Tensor], biases: Sequence[torch.Tensor | None] | None = None):
-    """Concatenated projections ``[x W_0^T + b_0 | x W_1^T + b_1 | ...]`` of one input."""
+def multi_linear(x: torch.Tensor, weights: Sequence[torch.Tensor], biases: Sequence[torch.Tensor | None] | None = None,
+                 tp=None):
+    """Concatenated projections ``[x W_0^T + b_0 | x W_1^T + b_1 | ...]`` of one input.
+
+    ``tp = ("col" | "row", FusedTensorParallel)`` fuses the tensor-parallel all-reduce into the GEMM: for a
+    row-parallel weight in the forward, for column-parallel weights in the input-gradient GEMM of the backward.
+    """
     if biases is None:
         biases = [None] * len(weights)
     if not _use_native(x):
+        assert tp is None
         outs = [F.linear(x, w, b) for w, b in zip(weights, biases)]
         return outs[0] if len(outs) == 1 else torch.cat(outs, dim=-1)
-    return _LinearFn.apply(x, len(weights), None, *weights, *biases)
+    return _LinearFn.apply(x, len(weights), None, tp, *weights, *biases)
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
-    return multi_linear(x, [weight], [bias])
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, tp=None) -> torch.Tensor:
+    return multi_linear(x, [weight], [bias], tp)

@@ -4,11 +4,12 @@
 single-node group, exchanges CUDA IPC handles through the group and maps every peer's buffer, so a
 kernel on any rank can load from / store to any rank's buffer over NVLink (``csrc/symm.cu``).
 
-``FusedTensorParallel`` owns two staging buffers and two flag arrays per rank (alternated call by call)
-and runs ``csb_gemm_allreduce_bf16``: the GEMM epilogue publishes this rank's partial tile and raises a
-per-tile flag on every rank; reducer CTAs of the same launch add up the partial tiles of all ranks by
-peer loads as soon as their flags are up, so the NVLink transfer overlaps the remaining MMA work tile
-by tile.  This is the row-parallel forward (o_proj / down_proj / fc2) and the column-parallel backward
+``FusedTensorParallel`` runs ``csb_gemm_allreduce_bf16``, a two-shot all-reduce folded into the GEMM
+epilogue: output tile rows are owned by ranks in contiguous ranges and every rank computes the ranges in
+rotated order, its own last.  A tile of a foreign range is pushed as a bf16 partial into the owner's
+inbox (posted NVLink stores); a tile of the own range adds the partials that the peers pushed earlier,
+stores the sum locally and pushes it into every peer's final buffer.  All 148 SMs keep doing MMA work,
+transfers overlap the math tile by tile, and no rank ever waits on a remote load.  This is the row-parallel forward (o_proj / down_proj / fc2) and the column-parallel backward
 (dX of q|k|v, gate|up, fc1) of Megatron-1D tensor parallelism, which the reference runs as a cuBLAS GEMM
 followed by a blocking NCCL all-reduce (ColossalAI ``Linear1D_Row`` / ``Linear1D_Col``,
 cornstarch/shardformer/policies/llama.py:192-249).
@@ -32,8 +33,9 @@ nat.declare("csb_ipc_close", [vp])
 nat.declare("csb_ipc_handle_size", [])
 nat.declare(
     "csb_gemm_allreduce_bf16",
-    [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, i32, i32, i32, i32, vp, vp],
+    [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, i64, i32, i32, vp, vp],
 )
+nat.declare("csb_ar_layout", [i32, i32, i32, i32, i32, vp, vp, vp])
 
 
 class _RawCudaBuffer:
@@ -95,10 +97,35 @@ class SymmetricMemory:
             self._own = 0
 
 
+class _ARContext:
+    """Symmetric buffers of one output shape: inbox (one slot per source rank), final buffer, arrival counters."""
+
+    ROWS = 512
+
+    def __init__(self, group, M: int, N: int, tile_n: int):
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.M, self.N = M, N
+        self.slot = M * N
+        cnt_bytes = self.world * self.ROWS * 4
+        self.off_final = self.world * self.slot * 2
+        self.off_cnt_part = self.off_final + self.slot * 2
+        self.off_cnt_final = self.off_cnt_part + cnt_bytes
+        total = self.off_cnt_final + cnt_bytes
+        self.mem = SymmetricMemory(total, group)
+        self.inbox = self.mem.offset_ptr_array(0)
+        self.final = self.mem.offset_ptr_array(self.off_final)
+        self.cnt_part = self.mem.offset_ptr_array(self.off_cnt_part)
+        self.cnt_final = self.mem.offset_ptr_array(self.off_cnt_final)
+        self.final_local = self.mem.local_tensor(torch.bfloat16, self.off_final, self.slot).view(M, N)
+        rb, re, nn = C.c_int(), C.c_int(), C.c_int()
+        nat.lib().csb_ar_layout(M, N, self.world, self.rank, tile_n, C.byref(rb), C.byref(re), C.byref(nn))
+        self.row_begin, self.row_end, self.num_n = rb.value, re.value, nn.value
+        self.calls = 0
+
+
 class FusedTensorParallel:
     """GEMM + all-reduce through peer memory for one tensor-parallel group (world size 2..8, one node)."""
 
-    MAX_TILES = 16384
     _by_group: dict = {}
 
     @classmethod
@@ -114,50 +141,39 @@ class FusedTensorParallel:
             cls._by_group[key] = cls(group)
         return cls._by_group[key]
 
-    def __init__(self, group, elems: int = 8192 * 4096):
+    def __init__(self, group):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self.elems = 0
-        self.mem: SymmetricMemory | None = None
-        self.epoch = [0, 0]
-        self.calls = 0
-        self._alloc(elems)
-
-    def _alloc(self, elems: int):
-        if self.mem is not None:
-            self.mem.close()
-        self.elems = elems
-        self.part_bytes = elems * 2
-        self.flag_bytes = self.world * self.MAX_TILES * 4
-        total = 2 * self.part_bytes + 2 * self.flag_bytes
-        self.mem = SymmetricMemory(total, self.group)
-        self.part_ptrs = [self.mem.offset_ptr_array(i * self.part_bytes) for i in range(2)]
-        self.flag_ptrs = [self.mem.offset_ptr_array(2 * self.part_bytes + i * self.flag_bytes) for i in range(2)]
-        self.epoch = [0, 0]
+        self.contexts: dict[tuple[int, int, int], _ARContext] = {}
 
     def gemm_allreduce(self, a: torch.Tensor, b: torch.Tensor, a_mn_major=False, b_mn_major=False,
-                       out: torch.Tensor | None = None, n_reducers: int = 16, tile_n: int = 0) -> torch.Tensor:
+                       out: torch.Tensor | None = None, tile_n: int = 0) -> torch.Tensor:
         """``out = sum_ranks op(a) @ op(b).T`` (bf16); every rank of the group must make the same call."""
         if a_mn_major:
             K, M = a.shape
         else:
             M, K = a.shape
         N = b.shape[1] if b_mn_major else b.shape[0]
-        if M * N > self.elems:
-            self._alloc(M * N)  # collective: every rank sees the same shapes
+        key = (M, N, tile_n)
+        ctx = self.contexts.get(key)
+        if ctx is None:
+            ctx = self.contexts[key] = _ARContext(self.group, M, N, tile_n)  # collective: all ranks see the same shapes
         if out is None:
             out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
-        which = self.calls & 1
-        self.calls += 1
-        self.epoch[which] += 1
         st = nat.status_word(a.device)
         nat.check(
             nat.lib().csb_gemm_allreduce_bf16(
                 a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
-                int(a_mn_major), int(b_mn_major), self.world, self.rank, C.cast(self.part_ptrs[which], vp),
-                C.cast(self.flag_ptrs[which], vp), self.MAX_TILES, self.epoch[which], n_reducers, tile_n,
+                int(a_mn_major), int(b_mn_major), self.world, self.rank, C.cast(ctx.inbox, vp), C.cast(ctx.final, vp),
+                C.cast(ctx.cnt_part, vp), C.cast(ctx.cnt_final, vp), ctx.slot, ctx.calls * ctx.num_n, tile_n,
                 st.data_ptr(), nat.stream()),
             "csb_gemm_allreduce_bf16",
         )
+        ctx.calls += 1
+        # rows owned by the other ranks arrived in the final buffer: move them next to the rows computed here
+        if ctx.row_begin > 0:
+            out[: ctx.row_begin].copy_(ctx.final_local[: ctx.row_begin])
+        if ctx.row_end < M:
+            out[ctx.row_end :].copy_(ctx.final_local[ctx.row_end :])
         return out

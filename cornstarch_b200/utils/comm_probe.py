@@ -1,0 +1,93 @@
+"""Multi-GPU micro-benchmarks of the fused compute+collective kernels against the NCCL baseline.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29533 \
+        -m cornstarch_b200.utils.comm_probe gemm_allreduce
+
+For each shape it reports (device-timed with CUDA events, max over ranks): the fused GEMM + all-reduce
+kernel, the baseline (same GEMM kernel followed by an NCCL all-reduce), and the roofline of the fused op:
+the slower of FLOPs / measured bf16 GEMM peak and NVLink bytes / 770 GB/s (each rank pushes
+(world-1)/world of the output as partials and the same amount again as final tiles).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops.gemm import gemm
+from .kernel_probe import peaks
+
+NVLINK_BPS = 770e9
+
+
+def timeit(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def gemm_allreduce(args):
+    from ..parallel.symm import FusedTensorParallel
+
+    ftp = FusedTensorParallel.get(dist.group.WORLD)
+    world, rank = dist.get_world_size(), dist.get_rank()
+    _, flops_peak, src = peaks()
+    T, H, I, QKV = 8192, 4096, 14336, 6144
+    shapes = [("o_proj fwd", T, H, H // world, 0), ("down_proj fwd", T, H, I // world, 0),
+              ("qkv dX", T, H, QKV // world, 1), ("gate_up dX", T, H, 2 * I // world, 1)]
+    for name, M, N, K, bmn in shapes:
+        a = torch.randn(M, K, device="cuda").bfloat16()
+        b = torch.randn((K, N) if bmn else (N, K), device="cuda").bfloat16()
+        out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        for nred in args.reducers:
+            ms_f = timeit(lambda: ftp.gemm_allreduce(a, b, False, bool(bmn), out=out))
+
+            def base():
+                gemm(a, b, False, bool(bmn), out=out)
+                dist.all_reduce(out)
+
+            ms_b = timeit(base)
+            ms_g = timeit(lambda: gemm(a, b, False, bool(bmn), out=out))
+            flops = 2.0 * M * N * K
+            link_bytes = 2 * (world - 1) / world * M * N * 2
+            roof_ms = max(flops / flops_peak, link_bytes / NVLINK_BPS) * 1e3
+            if rank == 0:
+                print(json.dumps({"op": name, "M": M, "N": N, "K": K, "world": world, "reducer_ctas": nred,
+                                  "fused_ms": round(ms_f, 4), "gemm_then_nccl_ms": round(ms_b, 4), "gemm_only_ms": round(ms_g, 4),
+                                  "roofline_ms": round(roof_ms, 4), f"frac_of_roofline_{src}": round(roof_ms / ms_f, 3),
+                                  "speedup_vs_nccl": round(ms_b / ms_f, 3)}), flush=True)
+    from ..ops import _native as nat
+
+    nat.check_status()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm_allreduce"])
+    ap.add_argument("--reducers", type=int, nargs="+", default=[16])
+    args = ap.parse_args()
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    {"gemm_allreduce": gemm_allreduce}[args.what](args)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

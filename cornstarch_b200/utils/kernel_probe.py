@@ -123,9 +123,49 @@ def probe_elementwise(a, flush):
     report("swiglu_fwd", ms, bytes_=3 * T * I * 2)
 
 
+def probe_gemm_ar_local(a, flush):
+    """The fused GEMM + all-reduce kernel on ONE GPU: rank 0 of an emulated world of 2 whose peer inbox is this
+    GPU's own buffer and whose peer flags are pre-set, so that the reducer path can be timed and profiled alone."""
+    import ctypes as C
+
+    from ..ops import _native as nat
+    from ..parallel import symm  # noqa: F401  (declares the prototype)
+
+    M, N, K = a.m, a.n, a.k
+    A_ = torch.randn(M, K, device="cuda").bfloat16()
+    B_ = torch.randn(N, K, device="cuda").bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    slot = M * N
+    inbox = torch.zeros(2 * slot, device="cuda", dtype=torch.bfloat16)
+    final = torch.zeros(slot, device="cuda", dtype=torch.bfloat16)
+    cnt_part = torch.zeros(2 * 512, device="cuda", dtype=torch.int32)
+    cnt_final = torch.zeros(2 * 512, device="cuda", dtype=torch.int32)
+    cnt_part[512:] = 1 << 30   # the emulated peer has "already delivered" every partial tile of every call
+    cnt_final[512:] = 1 << 30  # ... and every final tile
+    arr = lambda t: C.cast((C.c_void_p * 2)(t.data_ptr(), t.data_ptr()), C.c_void_p)  # noqa: E731
+    st = nat.status_word()
+    rb, re, nn = C.c_int(), C.c_int(), C.c_int()
+    nat.lib().csb_ar_layout(M, N, 2, 0, 0, C.byref(rb), C.byref(re), C.byref(nn))
+    calls = [0]
+
+    def run():
+        nat.check(nat.lib().csb_gemm_allreduce_bf16(
+            A_.data_ptr(), B_.data_ptr(), out.data_ptr(), M, N, K, K, K, N, 0, 0, 2, 0, arr(inbox), arr(final),
+            arr(cnt_part), arr(cnt_final), slot, calls[0] * nn.value, 0, st.data_ptr(), nat.stream()), "gemm_ar")
+        calls[0] += 1
+
+    ms = timeit(run, a.iters, a.warmup, flush)
+    ref = A_.float() @ B_.float().t()
+    own = slice(rb.value, re.value)  # rows owned by the emulated rank 0 hold the sum with the (zero) peer partial
+    err = (out.float()[own] - ref[own]).abs().max().item() / ref.abs().max().item()
+    report("gemm_allreduce[emulated world 2 on one GPU]", ms, flops=2.0 * M * N * K, M=M, N=N, K=K, reducers=a.reducers,
+           rel_err=round(err, 5))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "elementwise", "all"])
+    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "elementwise", "gemm_ar_local", "all"])
+    ap.add_argument("--reducers", type=int, default=16)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -142,7 +182,8 @@ def main():
     flush = Flusher(not a.no_flush)
     todo = ["gemm", "attn_fwd", "attn_bwd", "elementwise"] if a.what == "all" else [a.what]
     for t in todo:
-        {"gemm": probe_gemm, "attn_fwd": probe_attn_fwd, "attn_bwd": probe_attn_bwd, "elementwise": probe_elementwise}[t](a, flush)
+        {"gemm": probe_gemm, "attn_fwd": probe_attn_fwd, "attn_bwd": probe_attn_bwd, "elementwise": probe_elementwise,
+         "gemm_ar_local": probe_gemm_ar_local}[t](a, flush)
     from ..ops import _native as nat
 
     nat.check_status()

@@ -63,3 +63,66 @@ def test_gemm_allreduce_two_gpus():
         if p.is_alive():
             p.terminate()
     assert len(results) == 2 and all(r[1] == "ok" for r in results), results
+
+
+def _tp_model_worker(rank, world, port, q):
+    """Tiny Llama with TP=2 in bf16: the fused GEMM+all-reduce path must match the NCCL all-reduce path."""
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        from cornstarch_b200 import nn as cnn
+        from cornstarch_b200.models.llama import DecoderConfig, DecoderForCausalLM
+        from cornstarch_b200.ops import _native as nat
+        from cornstarch_b200.shardformer.shard.shard_config import ShardConfig
+        from cornstarch_b200.shardformer.shard.shardformer import ShardFormer
+
+        cfg = DecoderConfig(vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                            num_attention_heads=8, num_key_value_heads=4, max_position_embeddings=1024)
+        results = {}
+        for fused in (False, True):
+            cnn.FUSED_TP_ENABLED = fused
+            torch.manual_seed(0)
+            model = DecoderForCausalLM(cfg).cuda().bfloat16()
+            sc = ShardConfig(tensor_parallel_process_group=dist.group.WORLD, extra_kwargs={"device": "cuda"})
+            ShardFormer(sc).optimize(model)
+            ids = torch.randint(0, 2048, (2, 384), generator=torch.Generator().manual_seed(1)).cuda()
+            out = model(input_ids=ids, labels=ids)
+            out.loss.backward()
+            results[fused] = (out.loss.item(), {n: p.grad.float().clone() for n, p in model.named_parameters() if p.grad is not None})
+        nat.check_status()
+        l0, g0 = results[False]
+        l1, g1 = results[True]
+        assert abs(l0 - l1) < 2e-2, (l0, l1)
+        for n in g0:
+            d = (g0[n] - g1[n]).abs().max().item()
+            cos = torch.nn.functional.cosine_similarity(g0[n].flatten(), g1[n].flatten(), dim=0).item()
+            assert cos > 0.995, (n, d, g0[n].abs().max().item(), cos)
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_tp2_model_fused_matches_nccl():
+    from tests.dist_utils import free_port
+
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = free_port()
+    procs = [ctx.Process(target=_tp_model_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    results = []
+    while not q.empty():
+        results.append(q.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert len(results) == 2 and all(r[1] == "ok" for r in results), results
