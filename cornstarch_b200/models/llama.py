@@ -74,7 +74,7 @@ Qwen3Config = _cfg_cls("qwen3")
 GemmaConfig = _cfg_cls("gemma", hidden_act="gelu_pytorch_tanh", tie_word_embeddings=True)
 Gemma2Config = _cfg_cls("gemma2", hidden_act="gelu_pytorch_tanh", tie_word_embeddings=True)
 Gemma3TextConfig = _cfg_cls("gemma3_text", hidden_act="gelu_pytorch_tanh", tie_word_embeddings=True)
-Phi3Config = _cfg_cls("phi3")
+Phi3Config = _cfg_cls("phi3", rms_norm_eps=1e-5)
 
 
 @dataclass

@@ -33,6 +33,8 @@ class MixtralConfig(DecoderConfig):
         self.router_aux_loss_coef = router_aux_loss_coef
         self.output_router_logits = output_router_logits
         kw.setdefault("intermediate_size", 14336)
+        kw.setdefault("rms_norm_eps", 1e-5)
+        kw.setdefault("rope_theta", 1e6)
         super().__init__(**kw)
 
 

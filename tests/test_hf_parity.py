@@ -1,0 +1,132 @@
+"""Model math against the Hugging Face implementations with identical weights (CPU, fp32): a state dict produced by
+``transformers`` must load unchanged and give the same logits / hidden states."""
+
+import pytest
+import torch
+
+tf = pytest.importorskip("transformers")
+
+
+def _load(mine, hf):
+    missing, unexpected = mine.load_state_dict(hf.state_dict(), strict=False)
+    missing = [m for m in missing if "rotary" not in m and "embed_positions" not in m]
+    assert not missing and not unexpected, (missing, unexpected)
+
+
+DEC = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+           max_position_embeddings=128)
+
+
+@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "gemma", "phi3", "mixtral", "qwen3_moe"])
+def test_decoder_families_match_hf(family):
+    from cornstarch_b200.models import llama as L
+    from cornstarch_b200.models import moe as M
+
+    torch.manual_seed(0)
+    kw = dict(DEC)
+    if family == "llama":
+        hf_cfg, cfg, cls = tf.LlamaConfig(**kw), L.LlamaConfig(**kw), L.DecoderForCausalLM
+        hf_cls = tf.LlamaForCausalLM
+    elif family == "mistral":
+        hf_cfg, cfg, cls, hf_cls = tf.MistralConfig(**kw, sliding_window=None), L.MistralConfig(**kw), L.DecoderForCausalLM, tf.MistralForCausalLM
+    elif family == "qwen2":
+        hf_cfg, cfg, cls, hf_cls = tf.Qwen2Config(**kw), L.Qwen2Config(**kw), L.DecoderForCausalLM, tf.Qwen2ForCausalLM
+    elif family == "qwen3":
+        kw["head_dim"] = 16
+        hf_cfg, cfg, cls, hf_cls = tf.Qwen3Config(**kw), L.Qwen3Config(**kw), L.DecoderForCausalLM, tf.Qwen3ForCausalLM
+    elif family == "gemma":
+        kw["head_dim"] = 16
+        hf_cfg = tf.GemmaConfig(**kw, hidden_activation="gelu_pytorch_tanh")
+        cfg, cls, hf_cls = L.GemmaConfig(**kw), L.DecoderForCausalLM, tf.GemmaForCausalLM
+    elif family == "phi3":
+        hf_cfg, cfg, cls, hf_cls = tf.Phi3Config(**kw, pad_token_id=0), L.Phi3Config(**kw), L.DecoderForCausalLM, tf.Phi3ForCausalLM
+    elif family == "mixtral":
+        hf_cfg = tf.MixtralConfig(**kw, num_local_experts=4, num_experts_per_tok=2, sliding_window=None)
+        cfg, cls, hf_cls = M.MixtralConfig(**kw, num_local_experts=4, num_experts_per_tok=2), M.MoeForCausalLM, tf.MixtralForCausalLM
+    else:
+        kw["head_dim"] = 16
+        moe = dict(num_experts=4, num_experts_per_tok=2, moe_intermediate_size=48, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[])
+        hf_cfg = tf.Qwen3MoeConfig(**kw, **moe)
+        cfg, cls, hf_cls = M.Qwen3MoeConfig(**kw, **moe), M.MoeForCausalLM, tf.Qwen3MoeForCausalLM
+    hf_cfg._attn_implementation = "eager"
+    hf = hf_cls(hf_cfg).eval()
+    mine = cls(cfg).eval()
+    sd = hf.state_dict()
+    if family in ("mixtral", "qwen3_moe"):
+        sd = _unfuse_hf_experts(sd, family)
+    missing, unexpected = mine.load_state_dict(sd, strict=False)
+    assert not unexpected and not [m for m in missing if "rotary" not in m], (missing, unexpected)
+    ids = torch.randint(0, 320, (2, 40))
+    with torch.no_grad():
+        ref = hf(input_ids=ids).logits
+        out = mine(input_ids=ids).logits
+    assert torch.allclose(out, ref, atol=2e-4, rtol=1e-3), (out - ref).abs().max()
+
+
+def _unfuse_hf_experts(sd, family):
+    """transformers >= 5 stores MoE experts as stacked 3-D tensors; the classic per-expert names are what checkpoints on the hub use."""
+    out = {}
+    for k, v in sd.items():
+        if k.endswith("experts.gate_up_proj") and v.dim() == 3:
+            pre = k[: -len("gate_up_proj")]
+            E, two_i, _h = v.shape
+            for e in range(E):
+                g, u = v[e][: two_i // 2], v[e][two_i // 2 :]
+                if family == "mixtral":
+                    out[f"{pre}{e}.w1.weight"], out[f"{pre}{e}.w3.weight"] = g, u
+                else:
+                    out[f"{pre}{e}.gate_proj.weight"], out[f"{pre}{e}.up_proj.weight"] = g, u
+        elif k.endswith("experts.down_proj") and v.dim() == 3:
+            pre = k[: -len("down_proj")]
+            for e in range(v.shape[0]):
+                out[f"{pre}{e}.{'w2' if family == 'mixtral' else 'down_proj'}.weight"] = v[e]
+        elif ".mlp.gate.weight" in k and family == "mixtral":
+            out[k.replace(".mlp.gate.weight", ".block_sparse_moe.gate.weight")] = v
+        else:
+            out[k] = v
+    if family == "mixtral":
+        out = {k.replace(".mlp.experts.", ".block_sparse_moe.experts."): v for k, v in out.items()}
+    return out
+
+
+def test_siglip_clip_vit_match_hf():
+    from cornstarch_b200.models import vision as V
+
+    torch.manual_seed(0)
+    common = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=28, patch_size=14)
+    px = torch.randn(2, 3, 28, 28)
+    hf = tf.SiglipVisionModel(tf.SiglipVisionConfig(**common)).eval()
+    mine = V.SiglipVisionModel(V.SiglipVisionConfig(**common)).eval()
+    _load(mine, hf)
+    with torch.no_grad():
+        a, b = hf(pixel_values=px), mine(pixel_values=px)
+    assert torch.allclose(b.last_hidden_state, a.last_hidden_state, atol=1e-4)
+    assert torch.allclose(b.pooler_output, a.pooler_output, atol=1e-4)
+    hf = tf.CLIPVisionModel(tf.CLIPVisionConfig(**common)).eval()
+    mine = V.CLIPVisionModel(V.CLIPVisionConfig(**common)).eval()
+    _load(mine, hf)
+    with torch.no_grad():
+        a, b = hf(pixel_values=px), mine(pixel_values=px)
+    assert torch.allclose(b.last_hidden_state, a.last_hidden_state, atol=1e-4)
+    hf = tf.ViTModel(tf.ViTConfig(**common)).eval()
+    mine = V.ViTModel(V.ViTConfig(**common)).eval()
+    _load(mine, hf)
+    with torch.no_grad():
+        a, b = hf(pixel_values=px), mine(pixel_values=px)
+    assert torch.allclose(b.last_hidden_state, a.last_hidden_state, atol=1e-4)
+    assert torch.allclose(b.pooler_output, a.pooler_output, atol=1e-4)
+
+
+def test_whisper_encoder_matches_hf():
+    from cornstarch_b200.models import whisper as W
+
+    torch.manual_seed(0)
+    kw = dict(num_mel_bins=16, d_model=64, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=128, max_source_positions=50)
+    hf = tf.WhisperModel(tf.WhisperConfig(**kw, decoder_layers=1, decoder_attention_heads=4, decoder_ffn_dim=64, vocab_size=100, pad_token_id=0, bos_token_id=1, eos_token_id=2, decoder_start_token_id=1)).encoder.eval()
+    mine = W.WhisperEncoder(W.WhisperConfig(**kw)).eval()
+    missing, unexpected = mine.load_state_dict(hf.state_dict(), strict=False)
+    assert not missing and not unexpected
+    x = torch.randn(2, 16, 100)
+    with torch.no_grad():
+        a, b = hf(x).last_hidden_state, mine(input_features=x).last_hidden_state
+    assert torch.allclose(b, a, atol=1e-4), (a - b).abs().max()
