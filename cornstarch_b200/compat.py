@@ -1,0 +1,70 @@
+"""Import-path compatibility with the reference package.
+
+``import cornstarch_b200.compat`` (or ``cornstarch_b200.compat.install()``) registers aliases in
+``sys.modules`` so that user scripts written against the reference keep their imports::
+
+    from cornstarch.models.multimodal_language_model import MultimodalModel, ModalEncoderModule, MultimodalProjector
+    from cornstarch.pipeline_template import PipelineTemplate
+    from cornstarch.plugin.multimodal_parallel_plugin import ModalParallelPlugin, MultimodalParallelPlugin
+    from cornstarch.shardformer.shard.shard_config import ShardConfig, ContextParallelDistributionMode
+    from cornstarch.kernel.interface import create_bitfield_attention_mask
+    from colossalai.booster import Booster
+
+Nothing is aliased when a real ``cornstarch`` package is already imported.
+"""
+
+from __future__ import annotations
+
+import importlib
+import sys
+import types
+
+_ALIASES = {
+    "cornstarch": "cornstarch_b200",
+    "cornstarch.pipeline_template": "cornstarch_b200.pipeline_template",
+    "cornstarch.models": "cornstarch_b200.models",
+    "cornstarch.models.multimodal_language_model": "cornstarch_b200.multimodal",
+    "cornstarch.kernel": "cornstarch_b200.kernel",
+    "cornstarch.kernel.interface": "cornstarch_b200.kernel.interface",
+    "cornstarch.kernel.bitfield_attention": "cornstarch_b200.kernel.bitfield_attention",
+    "cornstarch.kernel.attention": "cornstarch_b200.kernel.attention",
+    "cornstarch.plugin": "cornstarch_b200.plugin",
+    "cornstarch.plugin.multimodal_parallel_plugin": "cornstarch_b200.plugin.multimodal_api",
+    "cornstarch.plugin.encoders_colocated_plugin": "cornstarch_b200.plugin.encoders_colocated_plugin",
+    "cornstarch.plugin.encoders_colocated_plugin.encoders_colocated_plugin": "cornstarch_b200.plugin.encoders_colocated_plugin",
+    "cornstarch.plugin.heterogeneous_parallel_plugin": "cornstarch_b200.plugin.heterogeneous_parallel_plugin",
+    "cornstarch.shardformer": "cornstarch_b200.shardformer",
+    "cornstarch.shardformer.shard": "cornstarch_b200.shardformer.shard",
+    "cornstarch.shardformer.shard.shard_config": "cornstarch_b200.shardformer.shard.shard_config",
+    "cornstarch.shardformer.shard.shardformer": "cornstarch_b200.shardformer.shard.shardformer",
+    "cornstarch.shardformer.policies": "cornstarch_b200.shardformer.policies",
+    "cornstarch.shardformer.policies.auto_policy": "cornstarch_b200.shardformer.policies.auto_policy",
+    "cornstarch.shardformer.layers": "cornstarch_b200.shardformer.layers",
+    "cornstarch.shardformer.layers.utils": "cornstarch_b200.shardformer.layers.utils",
+    "cornstarch.shardformer.layers.operation": "cornstarch_b200.shardformer.layers.operation",
+    "cornstarch.testing": "cornstarch_b200.testing",
+    "cornstarch.testing.timer": "cornstarch_b200.testing.timer",
+    "cornstarch.testing.dcgm": "cornstarch_b200.testing.dcgm",
+}
+
+
+def install(force: bool = False) -> None:
+    if "cornstarch" in sys.modules and not force and getattr(sys.modules["cornstarch"], "__name__", "") != "cornstarch_b200":
+        return
+    for alias, target in _ALIASES.items():
+        try:
+            sys.modules[alias] = importlib.import_module(target)
+        except ImportError:
+            continue
+    if "colossalai" not in sys.modules:
+        col = types.ModuleType("colossalai")
+        booster = types.ModuleType("colossalai.booster")
+        from .booster import Booster
+
+        booster.Booster = Booster
+        col.booster = booster
+        sys.modules["colossalai"] = col
+        sys.modules["colossalai.booster"] = booster
+
+
+install()

@@ -127,3 +127,33 @@ def _pp_worker(rank, world, llm_stages, tp, n_micro):
 @pytest.mark.parametrize("llm_stages,tp,n_micro,world", [(1, 1, 2, 2), (2, 1, 4, 3), (1, 2, 2, 4)])
 def test_modality_parallel_pipeline_matches_single_process(llm_stages, tp, n_micro, world):
     run_distributed(_pp_worker, world, llm_stages, tp, n_micro)
+
+
+def _colocated_worker(rank, world):
+    from cornstarch_b200.booster import Booster
+    from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
+    from cornstarch_b200.pipeline_template import PipelineTemplate
+    from cornstarch_b200.plugin.encoders_colocated_plugin import EncodersColocatedMultimodalParallelPlugin
+    from cornstarch_b200.plugin.modal_parallel_plugin import ModalParallelPlugin
+
+    n_micro = 2
+    ref_losses, ref_sd = _single_process_reference(4, n_micro)
+    model = _build()
+    plugin = EncodersColocatedMultimodalParallelPlugin(
+        encoder_plugins={"vision": ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.vision_encoder, 1))},
+        language_model_plugin=ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.language_model, 2)),
+        num_microbatches=n_micro, device=torch.device("cpu"))
+    booster = Booster(plugin=plugin)
+    opt = FusedAdamW(split_decay_groups(model, 0.0), lr=1e-2)
+    pmodel, popt, criterion, *_ = booster.boost(model, opt, criterion=lambda out, batch: out.loss)
+    batch = _batch(4)
+    for step in range(2):
+        out = booster.execute_pipeline(iter([batch]), pmodel, criterion, popt, return_loss=True)
+        popt.step()
+        popt.zero_grad()
+        if plugin.stage_manager.is_last_stage(check_only_in_modal=False):
+            assert abs(out["loss"].item() - ref_losses[step]) < 1e-4, (out["loss"].item(), ref_losses[step])
+
+
+def test_encoders_colocated_pipeline_matches_single_process():
+    run_distributed(_colocated_worker, 3)
