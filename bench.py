@@ -118,7 +118,22 @@ def parse_args():
     ap.add_argument("--microbatch", type=int, default=1)
     ap.add_argument("--parallelism", default="auto", help="auto | dp | e.g. 'pp4xtp2'")
     ap.add_argument("--no-e2e", action="store_true")
-    return ap.parse_args()
+    ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
+                    help="benchmark configuration: 1 VLM (headline), 2 vision+audio VALM, 3 long-context CP, 4 MoE EP+ZeRO-1")
+    args = ap.parse_args()
+    # presets of the other configurations (explicit flags win)
+    preset = {2: dict(shape="valm", samples_per_gpu=2, parallelism={8: "enc1+llm2xtp2", 4: "enc1+llm2xtp1"}),
+              3: dict(shape="long", samples_per_gpu=8, parallelism="cp"),
+              4: dict(shape="moe", samples_per_gpu=2, parallelism="ep")}.get(args.config)
+    if preset:
+        if args.shape == "vlm":
+            args.shape = preset["shape"]
+        if args.samples_per_gpu == SAMPLES_PER_GPU:
+            args.samples_per_gpu = preset["samples_per_gpu"]
+        if args.parallelism == "auto":
+            plan = preset["parallelism"]
+            args.parallelism = plan.get(args.gpus, "auto") if isinstance(plan, dict) else plan
+    return args
 
 
 def main():
@@ -209,7 +224,7 @@ def main():
                        "parallelism": trainer.parallelism, "microbatch": args.microbatch,
                        "l2": "no flush needed: every step streams >16 GB of weights and activations, far above the 126 MB L2",
                        "optimizer": "fused AdamW, fp32 master + moments, bf16 grads", "activation_checkpointing": "per layer"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "native",
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": "native", "benchmark_config": args.config,
         }
         print(json.dumps(out))
     if world > 1:

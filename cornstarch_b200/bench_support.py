@@ -18,7 +18,7 @@ class SingleDeviceTrainer:
     parallelism = "single"
 
     def __init__(self, shape: str, samples_per_step: int, microbatch: int, device, lr: float = 1e-4, seed: int = 0,
-                 dp_group=None):
+                 dp_group=None, mask_mode: str = "modality", dtype=torch.bfloat16):
         self.shape = SHAPES[shape]
         self.model_name = _model_name(shape)
         self.seq_len = self.shape.seq_len
@@ -28,13 +28,13 @@ class SingleDeviceTrainer:
         self.dp_group = dp_group
         self.world = dist.get_world_size(dp_group) if dp_group is not None else 1
         torch.manual_seed(seed)
-        self.model = build_model(shape, device=device, dtype=torch.bfloat16)
+        self.model = build_model(shape, device=device, dtype=dtype, mask_mode=mask_mode)
         self.model.gradient_checkpointing_enable()
         self.model.train()
-        self.opt = FusedAdamW(split_decay_groups(self.model, 0.01), lr=lr, max_norm=1.0)
+        self.opt = self.make_optimizer(lr)
         self.n_micro = samples_per_step // microbatch
-        rank = dist.get_rank(dp_group) if dp_group is not None else 0
-        self.host = [synthetic_batch(shape, microbatch, seed=1000 * rank + i, dtype=torch.bfloat16, pin=True)
+        rank = self.data_rank()
+        self.host = [synthetic_batch(shape, microbatch, seed=1000 * rank + i, dtype=dtype, pin=True)
                      for i in range(self.n_micro)]
         self.dev = [{k: v.to(device) for k, v in b.items()} for b in self.host]
         self.global_batch = samples_per_step * self.world
@@ -44,6 +44,20 @@ class SingleDeviceTrainer:
         if self.world > 1:
             self.parallelism = f"dp{self.world}"
 
+    def make_optimizer(self, lr):
+        return FusedAdamW(split_decay_groups(self.model, 0.01), lr=lr, max_norm=1.0)
+
+    def data_rank(self) -> int:
+        return dist.get_rank(self.dp_group) if self.dp_group is not None else 0
+
+    def reduce_grads(self):
+        if self.world > 1:
+            for g in self.opt.flat_grads() if self.opt.use_arena else [p.grad for p in self.model.parameters() if p.grad is not None]:
+                dist.all_reduce(g, op=dist.ReduceOp.SUM if dist.get_backend(self.dp_group) == "gloo" else dist.ReduceOp.AVG,
+                                group=self.dp_group)
+                if dist.get_backend(self.dp_group) == "gloo":
+                    g.div_(self.world)
+
     def _run(self, batches):
         total = None
         for b in batches:
@@ -51,9 +65,7 @@ class SingleDeviceTrainer:
             loss = out.loss / self.n_micro
             loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
-        if self.world > 1:
-            for g in self.opt.flat_grads():
-                dist.all_reduce(g, op=dist.ReduceOp.AVG, group=self.dp_group)
+        self.reduce_grads()
         self.opt.step()
         self.opt.zero_grad()
         return total
@@ -66,11 +78,74 @@ class SingleDeviceTrainer:
         return float(self._run(batches).item())
 
 
+class ExpertParallelTrainer(SingleDeviceTrainer):
+    """Data parallel over all ranks; the experts of every MoE layer are sharded over the same ranks (expert parallel,
+    dispatch / combine all-to-all); replicated parameters use ZeRO-1 (optimizer state sharded, gradients reduce-scattered)."""
+
+    def __init__(self, shape, samples_per_step, microbatch, device, group, **kw):
+        self.group = group
+        super().__init__(shape, samples_per_step, microbatch, device, dp_group=group, **kw)
+        self.parallelism = f"dp{self.world} + ep{self.world} (expert all-to-all) + ZeRO-1"
+
+    def make_optimizer(self, lr):
+        from .parallel.ep import shard_experts
+
+        shard_experts(self.model.language_model, self.group)
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+        return FusedAdamW(split_decay_groups(self.model, 0.01), lr=lr, max_norm=1.0, zero_stage=1, dp_group=self.group,
+                          expert_group=self.group)
+
+    def reduce_grads(self):
+        if self.opt.use_arena:
+            return  # ZeRO-1 reduce-scatters inside the step; expert gradients are not replicated
+        ws = self.world
+        for p in self.model.parameters():
+            if p.grad is None:
+                continue
+            if getattr(p, "expert_parallel", False):
+                p.grad.div_(ws)
+            else:
+                dist.all_reduce(p.grad, group=self.group)
+                p.grad.div_(ws)
+
+
+class ContextParallelTrainer(SingleDeviceTrainer):
+    """One replica over all ranks: every rank holds the whole model and 1/cp of every sequence (gathered-KV context
+    parallelism with makespan-balanced token assignment); gradients are averaged over the context-parallel ranks, which
+    is also where ZeRO-1 shards the optimizer state."""
+
+    def __init__(self, shape, samples_per_step, microbatch, device, group, **kw):
+        self.group = group
+        super().__init__(shape, samples_per_step, microbatch, device, dp_group=group, mask_mode="instance", **kw)
+        self.global_batch = samples_per_step  # all ranks work on the same samples
+        self.tokens_per_step = self.global_batch * self.seq_len
+        self.parallelism = f"cp{self.world} (gathered-KV ring attention, makespan_min) + ZeRO-1"
+
+    def data_rank(self) -> int:
+        return 0  # same data on every rank
+
+    def make_optimizer(self, lr):
+        from .models.llama import ParallelContext
+        from .parallel.cp import install_context_parallel_attention
+
+        install_context_parallel_attention(self.model.language_model, self.group)
+        self.model.language_model.set_parallel_context(
+            ParallelContext(sp_group=self.group, sp_mode="ring_attn", cp_dist_mode="makespan_min"))
+        return FusedAdamW(split_decay_groups(self.model, 0.01), lr=lr, max_norm=1.0, zero_stage=1, dp_group=self.group)
+
+    def reduce_grads(self):
+        if self.opt.use_arena:
+            return
+        super().reduce_grads()
+
+
 def _model_name(shape: str) -> str:
     return {
         "vlm": "SigLIP-so400m-shape (27L,h1152) + MLP projector + Llama-3.1-8B-shape (32L,h4096,vocab 128256)",
         "valm": "SigLIP-so400m-shape + Whisper-large-v3-shape + Llama-3.1-8B-shape",
         "moe": "SigLIP-so400m-shape + Mixtral-8x7B-shape",
+        "long": "SigLIP-so400m-shape + Llama-3.1-8B-shape, 8 images per 65536-token sample",
     }.get(shape, shape)
 
 
@@ -79,6 +154,10 @@ def build_trainer(args, rank: int, world: int, local_rank: int):
     plan = args.parallelism
     if world == 1:
         return SingleDeviceTrainer(args.shape, args.samples_per_gpu, args.microbatch, device)
+    if plan == "ep" or (plan == "auto" and SHAPES[args.shape].moe):
+        return ExpertParallelTrainer(args.shape, args.samples_per_gpu, args.microbatch, device, dist.group.WORLD)
+    if plan == "cp" or (plan == "auto" and SHAPES[args.shape].images_per_sample > 1):
+        return ContextParallelTrainer(args.shape, args.samples_per_gpu, args.microbatch, device, dist.group.WORLD)
     if plan == "dp":
         return SingleDeviceTrainer(args.shape, args.samples_per_gpu, args.microbatch, device, dp_group=dist.group.WORLD)
     from .bench_parallel import PipelineTrainer

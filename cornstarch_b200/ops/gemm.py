@@ -74,6 +74,13 @@ def gemm(
     else:
         N, Kb = b.shape
     assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    if M == 0 or N == 0 or K == 0:
+        # empty operand (an expert that received no token): nothing to launch
+        if out is None:
+            return torch.zeros((M, N), dtype=out_dtype or torch.bfloat16, device=a.device)
+        if not accumulate and K == 0:
+            out.zero_()
+        return out
     lda, ldb = a.stride(0), b.stride(0)
     if (lda % 8) or (ldb % 8) or (a.data_ptr() % 16) or (b.data_ptr() % 16):
         # TMA needs 16-byte aligned rows; repack the rare odd-sized operand

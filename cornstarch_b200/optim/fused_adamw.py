@@ -71,7 +71,8 @@ class _Region:
 class FusedAdamW(torch.optim.Optimizer):
     def __init__(self, params: Iterable, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.01, max_norm: float = 0.0, grad_dtype: torch.dtype = torch.bfloat16,
-                 zero_stage: int = 0, dp_group=None, norm_groups: list | None = None, use_arena: bool | None = None):
+                 zero_stage: int = 0, dp_group=None, norm_groups: list | None = None, use_arena: bool | None = None,
+                 expert_group=None):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.max_norm = max_norm
@@ -79,6 +80,9 @@ class FusedAdamW(torch.optim.Optimizer):
         self.zero_stage = zero_stage
         self.dp_group = dp_group
         self.norm_groups = norm_groups or []  # extra groups (tp, pp) over which the squared norm is summed
+        # param groups flagged {"expert_parallel": True} hold parameters that are NOT replicated over the data-parallel
+        # group (each rank owns different experts): never ZeRO-sharded; their squared norm is summed over expert_group
+        self.expert_group = expert_group
         self.loss_scale = 1.0
         self._step = 0
         self._regions: list[tuple[dict, _Region]] = []
@@ -96,17 +100,21 @@ class FusedAdamW(torch.optim.Optimizer):
         for g in self.param_groups:
             ps = [p for p in g["params"] if p.requires_grad]
             if ps:
-                self._regions.append((g, _Region(ps, self.grad_dtype, shard)))
+                region = _Region(ps, self.grad_dtype, None if g.get("expert_parallel") else shard)
+                region.sharded = shard is not None and not g.get("expert_parallel")
+                region.expert = bool(g.get("expert_parallel"))
+                self._regions.append((g, region))
         dev = self._regions[0][1].flat_param.device
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
         self._scale = torch.ones(1, dtype=torch.float32, device=dev)
         self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self._skip = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._sumsq_expert = torch.zeros(1, dtype=torch.float32, device=dev)
         self._sharded = shard is not None
 
     def flat_grads(self) -> list[torch.Tensor]:
-        """The flat gradient buffers (what data-parallel reduction works on)."""
-        return [r.flat_grad for _, r in self._regions]
+        """The flat gradient buffers of replicated parameters (what data-parallel reduction works on)."""
+        return [r.flat_grad for _, r in self._regions if not r.expert]
 
     def flat_params(self) -> list[torch.Tensor]:
         return [r.flat_param for _, r in self._regions]
@@ -123,21 +131,35 @@ class FusedAdamW(torch.optim.Optimizer):
         lib = nat.lib()
         st = nat.stream()
         self._fold_stray_grads()
-        if self._sharded:
-            ws = dist.get_world_size(self.dp_group)
+        if self.dp_group is not None and dist.get_world_size(self.dp_group) > 1:
+            # expert gradients hold the contributions of every data-parallel rank's tokens, each taken from that
+            # rank's own mean loss: the mean over ranks is 1/dp of the sum
             for _, r in self._regions:
-                if not getattr(self, "grads_already_reduced", False):
+                if r.expert:
+                    r.flat_grad.mul_(1.0 / dist.get_world_size(self.dp_group))
+        if self._sharded:
+            for _, r in self._regions:
+                if r.sharded and not getattr(self, "grads_already_reduced", False):
                     out = r.flat_grad[r.lo : r.hi]
                     dist.reduce_scatter_tensor(out, r.flat_grad, op=dist.ReduceOp.AVG, group=self.dp_group)
         inv_scale = 1.0 / self.loss_scale
         need_norm = self.max_norm > 0 or self.loss_scale != 1.0
         if need_norm:
             self._sumsq.zero_()
+            self._sumsq_expert.zero_()
+            any_expert = False
             for _, r in self._regions:
                 g = r.flat_grad[r.lo : r.hi]
-                nat.check(lib.csb_sumsq(g.data_ptr(), int(g.dtype == torch.float32), g.numel(), self._sumsq.data_ptr(), st), "csb_sumsq")
-            groups = list(self.norm_groups) + ([self.dp_group] if self._sharded else [])
-            for grp in groups:
+                acc = self._sumsq_expert if r.expert else self._sumsq
+                any_expert |= r.expert
+                nat.check(lib.csb_sumsq(g.data_ptr(), int(g.dtype == torch.float32), g.numel(), acc.data_ptr(), st), "csb_sumsq")
+            if self._sharded and dist.get_world_size(self.dp_group) > 1:
+                dist.all_reduce(self._sumsq, group=self.dp_group)  # every rank summed its slice only
+            if any_expert:
+                if self.expert_group is not None and dist.get_world_size(self.expert_group) > 1:
+                    dist.all_reduce(self._sumsq_expert, group=self.expert_group)
+                self._sumsq.add_(self._sumsq_expert)
+            for grp in self.norm_groups:
                 if grp is not None and dist.get_world_size(grp) > 1:
                     dist.all_reduce(self._sumsq, group=grp)
             nat.check(lib.csb_clip_scale(self._sumsq.data_ptr(), float(self.max_norm), inv_scale, self._scale.data_ptr(),
@@ -157,7 +179,7 @@ class FusedAdamW(torch.optim.Optimizer):
                               1, st),
                 "csb_adamw",
             )
-            if self._sharded:
+            if r.sharded:
                 if r.lo > 0:
                     r.flat_grad[: r.lo].zero_()
                 if r.hi < r.numel:
@@ -298,15 +320,20 @@ class FusedAdamW(torch.optim.Optimizer):
 
 def split_decay_groups(model: torch.nn.Module, weight_decay: float = 0.01) -> list[dict]:
     """Two param groups in module order: matrices (decayed) and vectors (norm weights, biases; not decayed)."""
-    decay, no_decay, seen = [], [], set()
+    decay, no_decay, expert, seen = [], [], [], set()
     for p in model.parameters():
         if not p.requires_grad or id(p) in seen:
             continue
         seen.add(id(p))
-        (decay if p.dim() >= 2 else no_decay).append(p)
+        if getattr(p, "expert_parallel", False):
+            expert.append(p)  # sharded over an expert-parallel group: its own region, never ZeRO-sharded or DP-reduced
+        else:
+            (decay if p.dim() >= 2 else no_decay).append(p)
     groups = []
     if decay:
         groups.append({"params": decay, "weight_decay": weight_decay})
     if no_decay:
         groups.append({"params": no_decay, "weight_decay": 0.0})
+    if expert:
+        groups.append({"params": expert, "weight_decay": weight_decay, "expert_parallel": True})
     return groups

@@ -1,0 +1,155 @@
+"""Expert parallelism: every rank of an expert-parallel group owns ``num_experts / ep`` experts; tokens travel
+to the owners of their top-k experts (dispatch), run through the expert MLPs there, and travel back (combine).
+
+The reference has no expert parallelism (its Mixtral / Qwen3-MoE experts are tensor-parallel only,
+cornstarch/shardformer/policies/mixtral.py:216-234, and every rank loops over all experts,
+cornstarch/shardformer/modeling/mixtral.py); this is the capability its MoE configuration needs on a
+multi-GPU node.
+
+Data movement per MoE layer::
+
+    sort (token, k) pairs by expert            -> rows grouped by destination rank
+    counts[ep, local] --all-to-all-->           recv_counts[src, local]
+    rows   --uneven all-to-all-->               rows grouped by (src, local expert)
+    regroup by local expert, one SwiGLU per contiguous segment (three tcgen05 GEMMs each)
+    results --uneven all-to-all back-->         rows in the sender's sorted order
+    scale by routing weight, index_add into the token order
+
+Both all-to-alls are autograd functions whose backward is the reverse exchange.  On NCCL they are
+``all_to_all_single`` with split sizes; on gloo (CPU tests) they are emulated with a padded all-gather.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def _a2a_uneven(x: torch.Tensor, send: list[int], recv: list[int], group) -> torch.Tensor:
+    out = x.new_empty((sum(recv), *x.shape[1:]))
+    if dist.get_backend(group) != "gloo":
+        dist.all_to_all_single(out, x.contiguous(), recv, send, group=group)
+        return out
+    ws, rank = dist.get_world_size(group), dist.get_rank(group)
+    mx = torch.tensor([max(send) if send else 0], dtype=torch.int64)
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX, group=group)
+    mx = int(mx.item())
+    buf = x.new_zeros((ws, mx, *x.shape[1:]))
+    start = 0
+    for d, n in enumerate(send):
+        buf[d, :n] = x[start : start + n]
+        start += n
+    everyone = [torch.empty_like(buf) for _ in range(ws)]
+    dist.all_gather(everyone, buf, group=group)
+    start = 0
+    for s, n in enumerate(recv):
+        out[start : start + n] = everyone[s][rank, :n]
+        start += n
+    return out
+
+
+class _AllToAllUneven(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, send, recv, group):
+        ctx.send, ctx.recv, ctx.group = send, recv, group
+        return _a2a_uneven(x, send, recv, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _a2a_uneven(g.contiguous(), ctx.recv, ctx.send, ctx.group), None, None, None
+
+
+def all_to_all_uneven(x, send_splits: list[int], recv_splits: list[int], group):
+    return _AllToAllUneven.apply(x, send_splits, recv_splits, group)
+
+
+class ExpertParallel:
+    """Attached to a sparse MoE block as ``block.ep``; the block then holds only this rank's experts."""
+
+    def __init__(self, group, num_experts: int):
+        self.group = group
+        self.ws = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        assert num_experts % self.ws == 0, f"{num_experts} experts cannot be split over {self.ws} ranks"
+        self.num_experts = num_experts
+        self.local = num_experts // self.ws
+        self.first = self.rank * self.local
+        self.last_recv_tokens = 0  # tokens this rank's experts processed in the last call (load statistics)
+
+    def local_expert_ids(self) -> range:
+        return range(self.first, self.first + self.local)
+
+    def exchange_counts(self, counts: torch.Tensor) -> torch.Tensor:
+        """``counts[E]`` rows I send per expert -> ``recv[src, local]`` rows I receive per source and local expert."""
+        send = counts.view(self.ws, self.local).contiguous()
+        if dist.get_backend(self.group) == "gloo":
+            everyone = [torch.empty_like(send) for _ in range(self.ws)]
+            dist.all_gather(everyone, send, group=self.group)
+            return torch.stack([e[self.rank] for e in everyone], dim=0)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        return recv
+
+    def forward(self, x2: torch.Tensor, weights: torch.Tensor, experts_idx: torch.Tensor, experts, act: str) -> torch.Tensor:
+        T, H = x2.shape
+        k = experts_idx.shape[1]
+        flat_e = experts_idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        token_of = torch.div(order, k, rounding_mode="floor")
+        counts = torch.bincount(flat_e, minlength=self.num_experts)
+        recv_counts = self.exchange_counts(counts)
+        # one host read for both directions' split sizes
+        both = torch.cat([counts.view(self.ws, self.local).sum(1), recv_counts.reshape(-1)]).tolist()
+        send_splits = both[: self.ws]
+        rc = [both[self.ws + s * self.local : self.ws + (s + 1) * self.local] for s in range(self.ws)]
+        recv_splits = [sum(r) for r in rc]
+        rows = all_to_all_uneven(x2[token_of], send_splits, recv_splits, self.group)  # grouped by (src, local expert)
+        self.last_recv_tokens = rows.shape[0]
+        if self.local > 1:
+            # permutation to (local expert, src) order
+            starts, pos = [], 0
+            for s in range(self.ws):
+                for e in range(self.local):
+                    starts.append(pos)
+                    pos += rc[s][e]
+            perm = torch.cat([torch.arange(starts[s * self.local + e], starts[s * self.local + e] + rc[s][e])
+                              for e in range(self.local) for s in range(self.ws)]).to(rows.device)
+            rows = rows[perm]
+        outs, start = [], 0
+        for e in range(self.local):
+            n = sum(rc[s][e] for s in range(self.ws))
+            seg = rows[start : start + n]
+            # an expert that received nothing still takes part in autograd (its weights get zero gradients)
+            outs.append(experts[e](seg, act))
+            start += n
+        y = torch.cat(outs, dim=0) if len(outs) > 1 else outs[0]
+        if self.local > 1:
+            inv = torch.empty_like(perm)
+            inv[perm] = torch.arange(perm.numel(), device=perm.device)
+            y = y[inv]
+        back = all_to_all_uneven(y, recv_splits, send_splits, self.group)
+        back = back * weights.reshape(-1)[order].unsqueeze(-1).to(back.dtype)
+        out = torch.zeros_like(x2)
+        out.index_add_(0, token_of, back)
+        return out
+
+
+def shard_experts(model, group) -> list[torch.nn.Parameter]:
+    """Keep only this rank's experts in every sparse MoE block of ``model`` and attach the exchange.
+
+    Returns the expert parameters (they are NOT replicated over the group: no data-parallel reduction, and an
+    optimizer must not shard them again)."""
+    import torch.nn as nn
+
+    expert_params = []
+    for m in model.modules():
+        if hasattr(m, "experts") and hasattr(m, "ep") and isinstance(m.experts, nn.ModuleList):
+            if m.ep is not None:
+                continue
+            ep = ExpertParallel(group, len(m.experts))
+            m.experts = nn.ModuleList([m.experts[i] for i in ep.local_expert_ids()])
+            m.ep = ep
+            expert_params += list(m.experts.parameters())
+    for p in expert_params:
+        p.expert_parallel = True
+    return expert_params

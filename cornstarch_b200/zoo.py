@@ -5,6 +5,8 @@
 ``valm``      ``vlm`` plus a Whisper-large-v3-shaped audio encoder (1500 audio tokens).
 ``moe``       SigLIP-so400m-shaped encoder + Mixtral-8x7B-shaped LLM, sequence 4096.
 ``vlm_small`` a 4-layer cut of ``vlm`` (same layer shapes) for smoke tests and profiler captures.
+``long``      ``vlm`` at sequence 65536 with 8 images per sample at random positions (context parallelism).
+``long_tiny`` / ``moe_tiny``  CPU-sized versions of ``long`` and ``moe`` for the gloo tests.
 
 Weights are random-initialised; data is synthetic (pixels ~ N(0,1), token ids uniform), as there is no
 network access for datasets or checkpoints.
@@ -37,6 +39,7 @@ class Shape:
     vision: dict = field(default_factory=dict)
     audio: dict = field(default_factory=dict)
     moe: bool = False
+    images_per_sample: int = 1
 
 
 SIGLIP_SO400M = dict(hidden_size=1152, intermediate_size=4304, num_hidden_layers=27, num_attention_heads=16,
@@ -61,6 +64,19 @@ SHAPES = {
                        llm={**LLAMA31_8B, "num_hidden_layers": 4}, vision={**SIGLIP_SO400M, "num_hidden_layers": 3}),
     "valm": Shape("valm", seq_len=8192, image_tokens=729, audio_tokens=1500, image_size=384, mel_bins=128, mel_frames=3000,
                   vocab=128256, llm=LLAMA31_8B, vision=SIGLIP_SO400M, audio=WHISPER_LARGE_V3),
+    "long": Shape("long", seq_len=65536, image_tokens=729, image_size=384, vocab=128256, images_per_sample=8,
+                  llm={**LLAMA31_8B, "max_position_embeddings": 65536}, vision=SIGLIP_SO400M),
+    "long_tiny": Shape("long_tiny", seq_len=1024, image_tokens=16, image_size=56, vocab=1000, images_per_sample=4,
+                       llm=dict(vocab_size=1000, hidden_size=128, intermediate_size=352, num_hidden_layers=2,
+                                num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=1024),
+                       vision=dict(hidden_size=64, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                   image_size=56, patch_size=14, hidden_act="gelu", vit=True)),
+    "moe_tiny": Shape("moe_tiny", seq_len=256, image_tokens=16, image_size=56, vocab=1000, moe=True,
+                      llm=dict(vocab_size=1000, hidden_size=128, intermediate_size=192, num_hidden_layers=2,
+                               num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512,
+                               num_local_experts=4, num_experts_per_tok=2),
+                      vision=dict(hidden_size=64, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                  image_size=56, patch_size=14, hidden_act="gelu", vit=True)),
     "moe": Shape("moe", seq_len=4096, image_tokens=729, image_size=384, vocab=32000, llm=MIXTRAL_8X7B, vision=SIGLIP_SO400M,
                  moe=True),
 }
@@ -125,7 +141,15 @@ def synthetic_batch(shape: Shape | str, batch: int, seed: int = 0, device="cpu",
     ids = torch.randint(0, sh.vocab - n_special, (batch, sh.seq_len), generator=g)
     pos = 0
     out = {}
-    if sh.vision:
+    if sh.vision and sh.images_per_sample > 1:
+        # one image somewhere inside each of `images_per_sample` equal segments of the sequence
+        seg = sh.seq_len // sh.images_per_sample
+        for b in range(batch):
+            for i in range(sh.images_per_sample):
+                start = i * seg + int(torch.randint(0, seg - sh.image_tokens, (1,), generator=g))
+                ids[b, start : start + sh.image_tokens] = sh.vocab - 1
+        out["pixel_values"] = torch.randn(batch * sh.images_per_sample, 3, sh.image_size, sh.image_size, generator=g).to(dtype)
+    elif sh.vision:
         ids[:, pos : pos + sh.image_tokens] = sh.vocab - 1
         pos += sh.image_tokens
         out["pixel_values"] = torch.randn(batch, 3, sh.image_size, sh.image_size, generator=g).to(dtype)

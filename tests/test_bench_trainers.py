@@ -1,0 +1,53 @@
+"""The benchmark's expert-parallel and context-parallel trainers on CPU-sized shapes: loss of the first step equals
+the single-process model on the same data, and a step updates the weights."""
+
+import torch
+import torch.distributed as dist
+
+from tests.dist_utils import run_distributed
+
+
+def _ep_worker(rank, world):
+    from cornstarch_b200.bench_support import ExpertParallelTrainer, SingleDeviceTrainer
+
+    dev = torch.device("cpu")
+    ref = SingleDeviceTrainer("moe_tiny", 2, 1, dev, dtype=torch.float32)
+    ref.host = None
+    tr = ExpertParallelTrainer("moe_tiny", 2, 1, dev, dist.group.WORLD, dtype=torch.float32)
+    assert len(tr.model.language_model.model.layers[0].block_sparse_moe.experts) == 4 // world
+    # loss on this rank's data against the unsharded model with the same seed
+    from cornstarch_b200.zoo import build_model
+
+    torch.manual_seed(0)
+    full = build_model("moe_tiny", dtype=torch.float32)
+    want = sum(full(**b).loss.item() for b in tr.dev) / tr.n_micro
+    got = float(tr.step_device())
+    assert abs(got - want) < 1e-4, (got, want)
+    l2 = float(tr.step_device())
+    assert l2 < got  # the step trained
+    assert "ep" in tr.parallelism and tr.global_batch == 2 * world
+
+
+def _cp_worker(rank, world):
+    from cornstarch_b200.bench_support import ContextParallelTrainer
+    from cornstarch_b200.zoo import build_model
+
+    dev = torch.device("cpu")
+    tr = ContextParallelTrainer("long_tiny", 2, 1, dev, dist.group.WORLD, dtype=torch.float32)
+    torch.manual_seed(0)
+    full = build_model("long_tiny", dtype=torch.float32, mask_mode="instance")
+    want = sum(full(**b).loss.item() for b in tr.dev) / tr.n_micro
+    # every rank reports sp * (its local token loss sum) / global count: the mean over ranks is the global loss
+    got = tr.step_device().clone()
+    dist.all_reduce(got)
+    got = float(got) / world
+    assert abs(got - want) < 1e-4, (got, want)
+    assert tr.tokens_per_step == 2 * 1024
+
+
+def test_expert_parallel_trainer():
+    run_distributed(_ep_worker, 2)
+
+
+def test_context_parallel_trainer():
+    run_distributed(_cp_worker, 2)

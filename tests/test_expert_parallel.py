@@ -1,0 +1,50 @@
+"""Expert parallelism: dispatch / combine all-to-all with experts sharded over ranks equals the local MoE block."""
+
+import torch
+import torch.distributed as dist
+
+from tests.dist_utils import run_distributed
+
+
+def _worker(rank, world, num_experts):
+    from cornstarch_b200.models.moe import MixtralConfig, MixtralSparseMoeBlock
+    from cornstarch_b200.parallel.ep import shard_experts
+
+    cfg = MixtralConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=4,
+                        num_key_value_heads=2, num_local_experts=num_experts, num_experts_per_tok=2)
+    torch.manual_seed(0)
+    full = MixtralSparseMoeBlock(cfg)
+    torch.manual_seed(0)
+    sharded = MixtralSparseMoeBlock(cfg)
+    expert_params = shard_experts(sharded, dist.group.WORLD)
+    assert len(sharded.experts) == num_experts // world and all(p.expert_parallel for p in expert_params)
+    # every rank has its own tokens (data parallel over the same group)
+    g = torch.Generator().manual_seed(10 + rank)
+    x = torch.randn(2, 9 + rank, 32, generator=g)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya, la = full(xa)
+    yb, lb = sharded(xb)
+    assert torch.allclose(ya, yb, atol=1e-5), (ya - yb).abs().max()
+    assert torch.allclose(la, lb)
+    ya.square().sum().backward()
+    yb.square().sum().backward()
+    assert torch.allclose(xa.grad, xb.grad, atol=1e-5)
+    assert torch.allclose(full.gate.weight.grad, sharded.gate.weight.grad, atol=1e-5)
+    # expert weights: the sharded gradient holds contributions of ALL ranks' tokens, the local block only mine
+    per = num_experts // world
+    zero = torch.zeros_like(full.experts[0].w1.weight)
+    mine = torch.stack([e.w1.weight.grad if e.w1.weight.grad is not None else zero for e in full.experts])
+    everyone = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine)
+    total = sum(everyone)
+    for j in range(per):
+        got = sharded.experts[j].w1.weight.grad
+        assert torch.allclose(got, total[rank * per + j], atol=1e-4), (rank, j, (got - total[rank * per + j]).abs().max())
+
+
+def test_ep2_four_experts():
+    run_distributed(_worker, 2, 4)
+
+
+def test_ep4_four_experts():
+    run_distributed(_worker, 4, 4)
