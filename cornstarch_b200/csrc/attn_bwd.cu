@@ -5,14 +5,15 @@
 //
 //   S^T  = K  Q^T              M=128(kv) N=64(q)  contraction D     -> TMEM S^T[2] (double buffer)
 //   dP^T = V  dO^T             M=128     N=64     contraction D     -> TMEM dP^T
-//   P^T  = exp2(S^T*c - LSE),  dS^T = P^T * (dP^T - delta) * scale   (registers -> bf16 smem tiles)
+//   P^T  = exp2(S^T*c - LSE),  dS^T = P^T * (dP^T - delta) * scale   (P^T -> bf16 pairs in TMEM over S^T;
+//                                                                     dS^T -> bf16 smem tile)
 //   dV  += P^T  dO             M=128     N=D      contraction q=64
 //   dK  += dS^T Q              M=128     N=D      contraction q=64
 //   dQ^T = K^T  dS^T           M=128(d)  N=64(q)  contraction kv=128 -> TMEM dQ^T
 //
 // dK/dV need no atomics and are bit-reproducible: every query head that shares the KV head is
-// handled by the same CTA.  dQ^T tiles are added into an fp32 accumulator with coalesced red.add
-// (lanes = consecutive head-dim elements) and converted to bf16 by a final pass.
+// handled by the same CTA.  dQ^T tiles are staged in shared memory as [q][d] rows and added into an fp32
+// accumulator by TMA reduce-add (one 32x32 block per warp), then converted to bf16 by a final pass.
 //
 // Warp roles (320 threads): warp 0 = TMA producer (K/V once, Q/dO ring of 3 stages), warp 1 = MMA
 // issuer, warps 2..9 = 256 compute threads.  Thread (r, half) owns KV row r (TMEM lane r) and 32 of
@@ -60,9 +61,9 @@ struct BwdSmem {
   static constexpr int V_OFF = K_OFF + 2 * KV_CHUNK;
   static constexpr int Q_OFF = V_OFF + 2 * KV_CHUNK;          // QSTAGES x (2 chunks x 8 KB)
   static constexpr int DO_OFF = Q_OFF + QSTAGES * 2 * Q_CHUNK;
-  static constexpr int PT_OFF = DO_OFF + QSTAGES * 2 * Q_CHUNK;  // [128 kv][64 q] bf16
-  static constexpr int DST_OFF = PT_OFF + KV_CHUNK;
-  static constexpr int META_OFF = DST_OFF + KV_CHUNK;         // per buffer: lse2[64] f32, delta[64] f32, qpos[64] i32, qbits[64] i64
+  static constexpr int DST_OFF = DO_OFF + QSTAGES * 2 * Q_CHUNK;  // dS^T [128 kv][64 q] bf16
+  static constexpr int DQ_OFF = DST_OFF + KV_CHUNK;           // dQ staging: 8 warps x [32 q][32 d] fp32 (row-major, 4 KB each)
+  static constexpr int META_OFF = DQ_OFF + 8 * 4096;          // per buffer: lse2[64] f32, delta*scale[64] f32, qpos[64] i32, qbits[64] i64
   static constexpr int META_STAGE = 64 * 4 * 3 + 64 * 8;
   static constexpr int LIST_OFF = META_OFF + 2 * META_STAGE;  // valid 64-row query tiles of this key block: int16 index, int8 class
   static constexpr int MAX_TILES = 1024;                      // sequences up to 65536 tokens
@@ -134,7 +135,7 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloa
 __global__ void __launch_bounds__(BW_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const AttnBwdParams p) {
+                const __grid_constant__ CUtensorMap tm_dq, const AttnBwdParams p) {
   using L = BwdSmem;
   constexpr int QS = L::QSTAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -173,18 +174,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(dq_free, BW_COMPUTE_THREADS);
     mbar_init(meta_full, BW_COMPUTE_THREADS);
     *abort_flag = 0;
-    // list of the 64-row query tiles that have at least one allowed pair with this key block
-    int n = 0;
-    for (int i = 0; i < p.nQ64 && n < L::MAX_TILES; ++i) {
-      const int8_t c = p.cls[((long)b * p.nQ128 + (i >> 1)) * p.nK + kj];
-      if (c != 0) {
-        tile_idx[n] = static_cast<int16_t>(i);
-        tile_cls[n] = c;
-        ++n;
-      }
-    }
-    *n_valid_slot = n;
     mbar_fence_init();
+  }
+  if (warp == 0) {
+    // list of the 64-row query tiles that have at least one allowed pair with this key block (ordered compaction)
+    int n = 0;
+    for (int base = 0; base < p.nQ64 && n < L::MAX_TILES; base += 32) {
+      const int i = base + lane;
+      const int8_t c = (i < p.nQ64) ? p.cls[((long)b * p.nQ128 + (i >> 1)) * p.nK + kj] : int8_t(0);
+      const uint32_t m = __ballot_sync(0xffffffffu, c != 0);
+      const int pos = n + __popc(m & ((1u << lane) - 1u));
+      if (c != 0 && pos < L::MAX_TILES) {
+        tile_idx[pos] = static_cast<int16_t>(i);
+        tile_cls[pos] = c;
+      }
+      n += __popc(m);
+    }
+    if (lane == 0) *n_valid_slot = n < L::MAX_TILES ? n : L::MAX_TILES;
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -239,7 +245,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t idesc_dq = make_idesc_bf16(128, BW_BQ, 1, 1);
       const uint32_t k_s = smem_u32(smem + L::K_OFF);
       const uint32_t v_s = smem_u32(smem + L::V_OFF);
-      const uint32_t pt_s = smem_u32(smem + L::PT_OFF);
       const uint32_t dst_s = smem_u32(smem + L::DST_OFF);
       const int ksteps_d = p.dk16 / 16;
       bool ok = bw_wait(kv_full, 0, abort_flag);
@@ -286,8 +291,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows)
 #pragma unroll
         for (int kk = 0; kk < BW_BQ / 16; ++kk)
-          umma_f16(tmem_dV, make_desc_kmajor_sw128(pt_s + kk * 32), make_desc_mnmajor_sw128(do_s + kk * 2048, Q_CHUNK),
-                   idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_f16_ts(tmem_dV, tmem_base + (it & 1) * 64 + (kk >> 1) * 32 + (kk & 1) * 8,
+                      make_desc_mnmajor_sw128(do_s + kk * 2048, Q_CHUNK), idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < BW_BQ / 16; ++kk)
           umma_f16(tmem_dK, make_desc_kmajor_sw128(dst_s + kk * 32), make_desc_mnmajor_sw128(q_s + kk * 2048, Q_CHUNK),
@@ -334,7 +339,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const bool qv = q < p.Sq;
       const long idx = ((long)b * p.Hq + h) * p.Sq + q;
       pf_lse = qv ? p.lse[idx] * LOG2E : INFINITY;
-      pf_delta = qv ? p.delta[idx] : 0.f;
+      pf_delta = qv ? p.delta[idx] * p.scale : 0.f;
       pf_qpos = qv ? (p.q_pos ? p.q_pos[(long)b * p.Sq + q] : q) : -1;
       pf_qbits = (qv && p.q_bits) ? p.q_bits[(long)b * p.Sq + q] : 0;
     };
@@ -354,13 +359,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_free);
-      if (r < p.D) {
-        float* base = p.dq_acc + (((long)b * p.Sq + (long)pi * BW_BQ + col0) * p.Hq + ph) * p.D + r;
-        const long qstride = (long)p.Hq * p.D;
-        const int qlim = p.Sq - (pi * BW_BQ + col0);
+      // this warp's [32 d][32 q] block -> shared memory as [q][d] rows of 128 B -> one TMA reduce-add into dq_acc
+      if (lane == 0) tma_store_wait_read<0>();  // the previous block has left the staging buffer
+      __syncwarp();
+      float* stage = reinterpret_cast<float*>(smem + L::DQ_OFF + cw * 4096);
 #pragma unroll
-        for (int c = 0; c < 32; ++c)
-          if (c < qlim) atomicAdd(base + c * qstride, __uint_as_float(v[c]));
+      for (int c = 0; c < 32; ++c) stage[c * 32 + lane] = __uint_as_float(v[c]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && quarter * 32 < p.D) {
+        tma_reduce_add_4d(&tm_dq, stage, quarter * 32, ph, pi * BW_BQ + col0, b);
+        tma_store_commit();
       }
       return true;
     };
@@ -400,15 +409,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_wait();
       float pv[32], ds[32];
 #pragma unroll
-      for (int x = 0; x < 32; ++x) {
-        const int col = col0 + x;
-        float pr = exp2f(__uint_as_float(sv[x]) * p.scale_log2 - m_lse[col]);
-        if (c == 1) {
+      for (int x4 = 0; x4 < 8; ++x4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(m_lse + col0 + x4 * 4);
+        const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+        for (int y = 0; y < 4; ++y)
+          pv[x4 * 4 + y] = fast_exp2(fmaf(__uint_as_float(sv[x4 * 4 + y]), p.scale_log2, -ls[y]));
+      }
+      if (c == 1) {
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+          const int col = col0 + x;
           const bool allow = k_valid && m_qpos[col] >= 0 && mask_allowed(p.mask_mode, m_qbits[col], kb, m_qpos[col], kpos);
-          pr = allow ? pr : 0.f;
+          pv[x] = allow ? pv[x] : 0.f;
         }
-        pv[x] = pr;
-        ds[x] = pr * (__uint_as_float(dv[x]) - m_delta[col]) * p.scale;
+      }
+#pragma unroll
+      for (int x4 = 0; x4 < 8; ++x4) {
+        const float4 d4 = *reinterpret_cast<const float4*>(m_delta + col0 + x4 * 4);
+        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+#pragma unroll
+        for (int y = 0; y < 4; ++y)
+          ds[x4 * 4 + y] = pv[x4 * 4 + y] * fmaf(__uint_as_float(dv[x4 * 4 + y]), p.scale, -dl[y]);
       }
       if (it > 0) {
         if (!bw_wait(pds_empty, (it - 1) & 1, abort_flag)) {
@@ -418,22 +440,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           break;
         }
       }
-      // P^T / dS^T -> bf16 smem tiles: row r, this warp's four 16-byte pieces (8 query columns each)
+      // P^T -> packed bf16 pairs in tensor memory, over this thread's own S^T columns (first 16 of its 32);
+      // dS^T -> bf16 smem tile: row r, this warp's four 16-byte pieces (8 query columns each)
+      {
+        uint32_t pk[16];
+#pragma unroll
+        for (int x = 0; x < 16; ++x) pk[x] = pack_bf16x2(pv[2 * x], pv[2 * x + 1]);
+        tmem_st_32x16(tmem_base + (it & 1) * 64 + col0 + lane_addr, pk);
+      }
 #pragma unroll
       for (int pc = 0; pc < 4; ++pc) {
-        uint4 u, w;
-        u.x = pack_bf16x2(pv[pc * 8 + 0], pv[pc * 8 + 1]);
-        u.y = pack_bf16x2(pv[pc * 8 + 2], pv[pc * 8 + 3]);
-        u.z = pack_bf16x2(pv[pc * 8 + 4], pv[pc * 8 + 5]);
-        u.w = pack_bf16x2(pv[pc * 8 + 6], pv[pc * 8 + 7]);
+        uint4 w;
         w.x = pack_bf16x2(ds[pc * 8 + 0], ds[pc * 8 + 1]);
         w.y = pack_bf16x2(ds[pc * 8 + 2], ds[pc * 8 + 3]);
         w.z = pack_bf16x2(ds[pc * 8 + 4], ds[pc * 8 + 5]);
         w.w = pack_bf16x2(ds[pc * 8 + 6], ds[pc * 8 + 7]);
-        const uint32_t off = sw128_offset(r, half * 4 + pc);
-        *reinterpret_cast<uint4*>(smem + L::PT_OFF + off) = u;
-        *reinterpret_cast<uint4*>(smem + L::DST_OFF + off) = w;
+        *reinterpret_cast<uint4*>(smem + L::DST_OFF + sw128_offset(r, half * 4 + pc)) = w;
       }
+      tmem_st_wait();
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(pds_full);
@@ -441,6 +465,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (it > 0) ok = drain_dq(it - 1);
     }
     if (ok && n_iter > 0) ok = drain_dq(n_iter - 1);
+    if (lane == 0) tma_store_wait<0>();  // every reduce-add of this warp has completed
+    __syncwarp();
     // ---- epilogue: dV and dK tiles (every MMA has retired once the last dQ^T was seen);
     //      the two warps of a lane quarter split the head-dim columns
     if (ok) {
@@ -545,6 +571,14 @@ CSB_API int csb_attn_bwd(const void* q, const void* k, const void* v, const void
   if ((r = make_tmap_4d(&tk, k, D, Hk, Sk, B, k_ss, k_sb, BW_BKV))) return r;
   if ((r = make_tmap_4d(&tv, v, D, Hk, Sk, B, v_ss, v_sb, BW_BKV))) return r;
   if ((r = make_tmap_4d(&tdo, dout, D, Hq, Sq, B, do_ss, do_sb, BW_BQ))) return r;
+  CUtensorMap tdq;
+  {
+    // dq_acc is dense fp32 [B][Sq][Hq][D]; a block is 32 head-dim elements (128 B) x 32 query rows
+    uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hq, (uint64_t)Sq, (uint64_t)B};
+    uint64_t strides[3] = {(uint64_t)D * 4, (uint64_t)Hq * D * 4, (uint64_t)Sq * Hq * D * 4};
+    uint32_t box[4] = {32, 1, 32, 1};
+    if ((r = make_tmap_nd_f32(&tdq, dq_acc, 4, dims, strides, box))) return r;
+  }
   static bool attr = false;
   if (!attr) {
     if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::DYN_BYTES) != cudaSuccess)
@@ -552,7 +586,7 @@ CSB_API int csb_attn_bwd(const void* q, const void* k, const void* v, const void
     attr = true;
   }
   dim3 grid(p.nK, Hk, B);
-  attn_bwd_kernel<<<grid, BW_THREADS, BwdSmem::DYN_BYTES, s>>>(tq, tk, tv, tdo, p);
+  attn_bwd_kernel<<<grid, BW_THREADS, BwdSmem::DYN_BYTES, s>>>(tq, tk, tv, tdo, tdq, p);
   int e = launch_result();
   if (e) return e;
   const long n_rows = (long)B * Sq;

@@ -4,10 +4,11 @@
 //
 // One CTA = one 128-row query tile of one head.  Both GEMMs run on tcgen05 with TMEM accumulators:
 //   S = Q K^T   : A = Q tile (K-major smem), B = K tile (K-major smem)      -> TMEM S[2] (double buffer)
-//   O += P V    : A = P tile (K-major smem, written by the softmax threads), B = V tile (MN-major smem)
+//   O += P V    : A = P tile in TMEM (bf16 pairs written by the softmax threads over the columns of S), B = V tile
+//                 (MN-major smem)
 // Warp roles: warp 0 = TMA producer (Q once, K/V ring of 2 stages), warp 1 = MMA issuer,
-// warps 2..5 = softmax: thread r owns query row r (one TMEM lane), so row max / row sum need no
-// shuffles.  The running maximum is only refreshed when it grows by more than 2^8 (lazy rescale),
+// warps 2..9 = softmax: two threads per query row (one TMEM lane), each owning 64 of a tile's 128 key
+// columns; the pair exchanges its row maximum through shared memory.  The running maximum is only refreshed when it grows by more than 2^8 (lazy rescale),
 // which keeps the TMEM read-modify-write of O off the common path.
 //
 // Mask handling: a [B][nQ][nK] int8 class map (0 = skip tile, 1 = evaluate the predicate per element,
@@ -95,11 +96,13 @@ struct AttnSmem {
   static constexpr int Q_OFF = 0;
   static constexpr int K_OFF = Q_OFF + Q_BYTES;
   static constexpr int V_OFF = K_OFF + 2 * KV_BYTES;
-  static constexpr int P_OFF = V_OFF + 2 * KV_BYTES;
-  static constexpr int KB_OFF = P_OFF + 2 * CHUNK_BYTES;      // int64 k bits  [2][128]
+  static constexpr int KB_OFF = V_OFF + 2 * KV_BYTES;         // int64 k bits  [2][128]
   static constexpr int KP_OFF = KB_OFF + 2 * 128 * 8;         // int   k pos   [2][128]
-  static constexpr int BAR_OFF = KP_OFF + 2 * 128 * 4;
-  static constexpr int NBAR = 1 + 2 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 1;
+  static constexpr int XM_OFF = KP_OFF + 2 * 128 * 4;         // float row-max exchange [2 buffers][2 halves][128]
+  static constexpr int CLS_OFF = XM_OFF + 6 * 128 * 4;        // + row-sum exchange [2 halves][128]; then the tile classes
+  static constexpr int MAX_NK = 1024;                         // key blocks per row of the class map (131072 keys)
+  static constexpr int BAR_OFF = CLS_OFF + MAX_NK;
+  static constexpr int NBAR = 1 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 1 + 4 + 1;
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
@@ -119,7 +122,7 @@ __device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t phase, volatile 
 }
 
 template <int NCH>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
   using L = AttnSmem<NCH>;
@@ -132,10 +135,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* v_full = bars + 5;
   uint64_t* v_empty = bars + 7;
   uint64_t* s_full = bars + 9;
-  uint64_t* s_empty = bars + 11;
-  uint64_t* p_full = bars + 13;
-  uint64_t* pv_done = bars + 14;
-  uint64_t* kb_full = bars + 15;  // key bits / positions of a partial tile staged by all 128 softmax threads
+  uint64_t* p_full = bars + 11;
+  uint64_t* pv_done = bars + 12;
+  uint64_t* kb_full = bars + 13;  // key bits / positions of a partial tile staged by the softmax threads
+  uint64_t* pair_bar = bars + 14; // [4] one per lane quarter: the two warps that share its query rows
+  uint64_t* o_done = bars + 18;   // the last P V has retired: O is final
+  float* xm_s = reinterpret_cast<float*>(smem + L::XM_OFF);
+  int8_t* cls_s = reinterpret_cast<int8_t*>(smem + L::CLS_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int64_t* kb_s = reinterpret_cast<int64_t*>(smem + L::KB_OFF);
@@ -147,7 +153,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hk);
   const int q0 = qi * AT_BM;
-  const int8_t* cls_row = p.cls + ((long)b * p.nQ + qi) * p.nK;
+  {
+    // this query tile's row of the class map, read once (every role walks it)
+    const int8_t* cls_g = p.cls + ((long)b * p.nQ + qi) * p.nK;
+    for (int j = threadIdx.x; j < p.nK; j += blockDim.x) cls_s[j] = cls_g[j];
+  }
+  const int8_t* cls_row = cls_s;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -157,11 +168,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
     }
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 256);
     mbar_init(pv_done, 1);
-    mbar_init(kb_full, 128);
+    mbar_init(o_done, 1);
+    mbar_init(kb_full, 256);
+    for (int i = 0; i < 4; ++i) mbar_init(&pair_bar[i], 64);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -210,7 +222,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t idesc_s = make_idesc_bf16(AT_BM, AT_BN, 0, 0);
       const uint32_t idesc_o = make_idesc_bf16(AT_BM, p.dk16, 0, 1);
       const uint32_t q_s = smem_u32(smem + L::Q_OFF);
-      const uint32_t p_s = smem_u32(smem + L::P_OFF);
       const int ksteps_s = p.dk16 / 16;
       bool ok = at_wait(q_full, 0, abort_flag);
       if (!ok) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; }
@@ -218,11 +229,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       int n = 0;
       for (int j = 0; j < p.nK; ++j) n += (cls_row[j] != 0);
 
+      // tcgen05.mma operations of one CTA execute in issue order.  S(it+1) is issued after P(it-1) V(it-1), the last
+      // reader of the TMEM buffer it overwrites (P(it-1) lives in the columns of S(it-1)); the softmax threads are done
+      // with that buffer because their p_full(it-1) arrival preceded that MMA.
       auto issue_s = [&](uint32_t it) -> bool {
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         if (!at_wait(&k_full[st], ph, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
-        if (!at_wait(&s_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_TMEM_EMPTY); *abort_flag = 1; return false; }
         tc_fence_after();
         const uint32_t k_s = smem_u32(smem + L::K_OFF + st * L::KV_BYTES);
         for (int kk = 0; kk < ksteps_s; ++kk) {
@@ -246,20 +259,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!at_wait(p_full, it & 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
         tc_fence_after();
         const uint32_t v_s = smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
+        // O += P V with P read from tensor memory: 16 keys of a row = 8 packed 32-bit columns per step
 #pragma unroll
-        for (int kk = 0; kk < AT_BN / 16; ++kk) {
-          const uint32_t a_off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
-          umma_f16(tmem_O, make_desc_kmajor_sw128(p_s + a_off), make_desc_mnmajor_sw128(v_s + kk * 2048, CHUNK_BYTES),
-                   idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < AT_BN / 16; ++kk)
+          umma_f16_ts(tmem_O, tmem_S + st * 128 + kk * 8, make_desc_mnmajor_sw128(v_s + kk * 2048, CHUNK_BYTES), idesc_o,
+                      (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&v_empty[st]);
         umma_commit(pv_done);
+        if (it + 1 == (uint32_t)n) umma_commit(o_done);
       }
     }
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax / correction / epilogue
+    // Two threads per query row: warps 2..5 take key columns 0..63 of a tile, warps 6..9 columns 64..127 (a warp
+    // may only touch the TMEM lane quarter warp%4).  The pair exchanges its row maximum through shared memory.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;  // row inside the tile == TMEM lane
     const int q = q0 + r;
     const bool row_valid = q < p.Sq;
@@ -271,127 +287,142 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (p.q_pos) qpos = p.q_pos[(long)b * p.Sq + q];
     }
     float m_used = -INFINITY, l_sum = 0.f;
-    uint32_t it = 0, n_partial = 0;
+    uint32_t it = 0, n_partial = 0, n_pair = 0;
     bool ok = true;
+    auto fail = [&](int code) {
+      if (lane == 0) atomicExch(p.status, code);
+      *abort_flag = 1;
+      ok = false;
+    };
     for (int j = 0; j < p.nK && ok; ++j) {
       const int c = cls_row[j];
       if (c == 0) continue;
       const int buf = it & 1;
-      if (c == 1) {
-        const int k = j * AT_BN + r;
-        const bool kv = k < p.Sk;
-        kb_s[buf * 128 + r] = (kv && p.k_bits) ? p.k_bits[(long)b * p.Sk + k] : 0;
-        kp_s[buf * 128 + r] = kv ? (p.k_pos ? p.k_pos[(long)b * p.Sk + k] : k) : -1;
-        mbar_arrive(kb_full);
-        if (!at_wait(kb_full, n_partial & 1, abort_flag)) {
-          if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
-          *abort_flag = 1;
-          ok = false;
-          break;
-        }
-        ++n_partial;
-      }
-      if (!at_wait(&s_full[buf], (it >> 1) & 1, abort_flag)) {
-        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_TMEM_FULL);
-        *abort_flag = 1;
-        ok = false;
-        break;
-      }
+      if (!at_wait(&s_full[buf], (it >> 1) & 1, abort_flag)) { fail(ST_TIMEOUT_TMEM_FULL); break; }
       tc_fence_after();
-      float s[128];
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_S + buf * 128 + cc * 32 + lane_addr, v);
+      float s[64];
+      {
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32(tmem_S + buf * 128 + half * 64 + lane_addr, v0);
+        tmem_ld_32x32(tmem_S + buf * 128 + half * 64 + 32 + lane_addr, v1);
+        // Key metadata of a partial tile is staged only now: S(it) being ready means P(it-2) V(it-2) was issued, i.e.
+        // every thread has finished the tile that used this staging buffer before.
+        if (c == 1) {
+          if (half == 0) {
+            const int k = j * AT_BN + r;
+            const bool kv = k < p.Sk;
+            kb_s[buf * 128 + r] = (kv && p.k_bits) ? p.k_bits[(long)b * p.Sk + k] : 0;
+            kp_s[buf * 128 + r] = kv ? (p.k_pos ? p.k_pos[(long)b * p.Sk + k] : k) : -1;
+          }
+          mbar_arrive(kb_full);
+          if (!at_wait(kb_full, n_partial & 1, abort_flag)) {
+            tmem_ld_wait();
+            fail(ST_TIMEOUT_MISC);
+            break;
+          }
+          ++n_partial;
+        }
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[cc * 32 + i] = __uint_as_float(v[i]);
+        for (int i = 0; i < 32; ++i) {
+          s[i] = __uint_as_float(v0[i]);
+          s[32 + i] = __uint_as_float(v1[i]);
+        }
       }
-      tc_fence_before();
-      mbar_arrive(&s_empty[buf]);
       if (c == 1) {
-        const int64_t* kb = kb_s + buf * 128;
-        const int* kp = kp_s + buf * 128;
+        const int64_t* kb = kb_s + buf * 128 + half * 64;
+        const int* kp = kp_s + buf * 128 + half * 64;
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
+        for (int i = 0; i < 64; ++i) {
           const int kpos = kp[i];
           const bool allow = row_valid && kpos >= 0 && mask_allowed(p.mask_mode, qb, kb[i], qpos, kpos);
           s[i] = allow ? s[i] : -INFINITY;
         }
       }
-      float mx = s[0];
+      float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
 #pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 4; i < 64; i += 4) {
+        mx0 = fmaxf(mx0, s[i]);
+        mx1 = fmaxf(mx1, s[i + 1]);
+        mx2 = fmaxf(mx2, s[i + 2]);
+        mx3 = fmaxf(mx3, s[i + 3]);
+      }
+      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      // exchange with the thread that holds the other 64 columns of this row
+      xm_s[(buf * 2 + half) * 128 + r] = mx;
+      mbar_arrive(&pair_bar[quarter]);
+      if (!at_wait(&pair_bar[quarter], n_pair & 1, abort_flag)) { fail(ST_TIMEOUT_MISC); break; }
+      ++n_pair;
+      mx = fmaxf(mx, xm_s[(buf * 2 + (half ^ 1)) * 128 + r]);
       const float m_new = fmaxf(m_used, mx);
       const bool need = (m_new - m_used) * p.scale_log2 > 8.f;  // also true when m_used is -inf and m_new is finite
-      if (it > 0) {
-        if (!at_wait(pv_done, (it - 1) & 1, abort_flag)) {
-          if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
-          *abort_flag = 1;
-          ok = false;
-          break;
-        }
+      if (it > 0 && __any_sync(0xffffffffu, need)) {
+        // rare (lazy rescale): O is only touched once the previous P V has retired.  The barrier is at most one
+        // phase ahead of the one awaited here, because P V(it) cannot be issued before this thread's p_full arrival.
+        if (!at_wait(pv_done, (it - 1) & 1, abort_flag)) { fail(ST_TIMEOUT_MISC); break; }
         tc_fence_after();
-        if (__any_sync(0xffffffffu, need)) {
-          float alpha = 1.f;
-          if (need) alpha = (m_used == -INFINITY) ? 0.f : exp2f((m_used - m_new) * p.scale_log2);
+        float alpha = 1.f;
+        if (need) alpha = (m_used == -INFINITY) ? 0.f : fast_exp2((m_used - m_new) * p.scale_log2);
 #pragma unroll
-          for (int cc = 0; cc < NCH * 2; ++cc) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem_O + cc * 32 + lane_addr, v);
-            tmem_ld_wait();
+        for (int cc = 0; cc < NCH; ++cc) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_O + (half * NCH + cc) * 32 + lane_addr, v);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-            tmem_st_32x32(tmem_O + cc * 32 + lane_addr, v);
-          }
-          tmem_st_wait();
-          l_sum *= alpha;
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+          tmem_st_32x32(tmem_O + (half * NCH + cc) * 32 + lane_addr, v);
         }
+        tmem_st_wait();
+        l_sum *= alpha;
       }
       if (need) m_used = m_new;
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used * p.scale_log2;
-      // probabilities -> bf16 -> swizzled K-major smem tile (row r, 16-byte pieces of 8 columns)
-      uint8_t* p_row = smem + L::P_OFF;
-      float lsum = 0.f;
+      // probabilities -> packed bf16 pairs -> tensor memory, over the first 64 columns of this tile's S buffer (the
+      // partner's S values there were read before the pair barrier above): thread (r, half) writes keys 64*half.. of row r
+      uint32_t pk[32];
+      float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
 #pragma unroll
-      for (int piece = 0; piece < 16; ++piece) {
-        float e[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          e[i] = exp2f(s[piece * 8 + i] * p.scale_log2 - m_eff);
-          lsum += e[i];
-        }
-        uint4 u;
-        u.x = pack_bf16x2(e[0], e[1]);
-        u.y = pack_bf16x2(e[2], e[3]);
-        u.z = pack_bf16x2(e[4], e[5]);
-        u.w = pack_bf16x2(e[6], e[7]);
-        const int chunk = piece >> 3;
-        *reinterpret_cast<uint4*>(p_row + chunk * CHUNK_BYTES + sw128_offset(r, piece & 7)) = u;
+      for (int i = 0; i < 64; i += 4) {
+        const float e0 = fast_exp2(fmaf(s[i], p.scale_log2, -m_eff));
+        const float e1 = fast_exp2(fmaf(s[i + 1], p.scale_log2, -m_eff));
+        const float e2 = fast_exp2(fmaf(s[i + 2], p.scale_log2, -m_eff));
+        const float e3 = fast_exp2(fmaf(s[i + 3], p.scale_log2, -m_eff));
+        ls0 += e0;
+        ls1 += e1;
+        ls2 += e2;
+        ls3 += e3;
+        pk[i / 2] = pack_bf16x2(e0, e1);
+        pk[i / 2 + 1] = pack_bf16x2(e2, e3);
       }
-      l_sum += lsum;
-      fence_proxy_async_smem();
+      tmem_st_32x32(tmem_S + buf * 128 + half * 32 + lane_addr, pk);
+      tmem_st_wait();
+      l_sum += (ls0 + ls1) + (ls2 + ls3);
       tc_fence_before();
       mbar_arrive(p_full);
       ++it;
     }
     // ---- epilogue
     if (ok && it > 0) {
-      if (!at_wait(pv_done, (it - 1) & 1, abort_flag)) {
-        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
-        *abort_flag = 1;
-        ok = false;
-      }
+      // (pv_done cannot be used here: two phases may still be pending, which a parity wait cannot tell from none)
+      if (!at_wait(o_done, 0, abort_flag)) fail(ST_TIMEOUT_MISC);
     }
     if (ok) {
+      // total row sum = this thread's columns + the partner's
+      xm_s[(4 + half) * 128 + r] = l_sum;
+      mbar_arrive(&pair_bar[quarter]);
+      if (!at_wait(&pair_bar[quarter], n_pair & 1, abort_flag)) fail(ST_TIMEOUT_MISC);
+    }
+    if (ok) {
+      l_sum += xm_s[(4 + (half ^ 1)) * 128 + r];
       tc_fence_after();
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
       __nv_bfloat16* o_row = p.O + (long)b * p.o_stride_b + (long)q * p.o_stride_s + (long)h * p.D;
 #pragma unroll
-      for (int cc = 0; cc < NCH * 2; ++cc) {
+      for (int cc = 0; cc < NCH; ++cc) {
+        const int col0 = (half * NCH + cc) * 32;
         uint32_t v[32];
         if (it > 0) {
-          tmem_ld_32x32(tmem_O + cc * 32 + lane_addr, v);
+          tmem_ld_32x32(tmem_O + col0 + lane_addr, v);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -400,7 +431,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (row_valid) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const int col = cc * 32 + g * 8;
+            const int col = col0 + g * 8;
             if (col + 8 <= p.D) {
               uint4 u;
               u.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
@@ -412,7 +443,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
-      if (row_valid)
+      if (row_valid && half == 0)
         p.lse[((long)b * p.Hq + h) * p.Sq + q] = l_sum > 0.f ? m_used * p.scale + logf(l_sum) : -INFINITY;
     }
   }
@@ -459,6 +490,7 @@ CSB_API int csb_attn_fwd(const void* q, const void* k, const void* v, void* out,
                          const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
                          const signed char* cls, int* status, void* stream) {
   if (D % 8 || D > 128 || D < 16 || Hq % Hk) return CSB_ERR_BAD_ARG;
+  if ((Sk + AT_BN - 1) / AT_BN > AttnSmem<2>::MAX_NK) return CSB_ERR_TOO_LARGE;
   if ((q_stride_s % 8) || (k_stride_s % 8) || (v_stride_s % 8) || (o_stride_s % 8)) return CSB_ERR_BAD_ARG;
   AttnFwdParams p;
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hk = Hk; p.D = D;
@@ -487,12 +519,12 @@ CSB_API int csb_attn_fwd(const void* q, const void* k, const void* v, void* out,
     auto kfn = attn_fwd_kernel<1>;
     static bool set1 = false;
     if (!set1) { if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<1>::DYN_BYTES) != cudaSuccess) return launch_result(); set1 = true; }
-    kfn<<<grid, 192, AttnSmem<1>::DYN_BYTES, s>>>(tq, tk, tv, p);
+    kfn<<<grid, 320, AttnSmem<1>::DYN_BYTES, s>>>(tq, tk, tv, p);
   } else {
     auto kfn = attn_fwd_kernel<2>;
     static bool set2 = false;
     if (!set2) { if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<2>::DYN_BYTES) != cudaSuccess) return launch_result(); set2 = true; }
-    kfn<<<grid, 192, AttnSmem<2>::DYN_BYTES, s>>>(tq, tk, tv, p);
+    kfn<<<grid, 320, AttnSmem<2>::DYN_BYTES, s>>>(tq, tk, tv, p);
   }
   return launch_result();
 }

@@ -97,6 +97,27 @@ inline int make_tmap_nd_bf16(CUtensorMap* out, const void* base, int nd, const u
   return 0;
 }
 
+// General N-d fp32 tensor map without swizzle (rows of the staged tile are plain row-major in shared memory).
+inline int make_tmap_nd_f32(CUtensorMap* out, const void* base, int nd, const uint64_t* dims_in,
+                            const uint64_t* strides_bytes, const uint32_t* box_in) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return CSB_ERR_NO_DRIVER_SYMBOL;
+  cuuint64_t dims[5];
+  cuuint64_t strides[4];
+  cuuint32_t box[5];
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  for (int i = 0; i < nd; ++i) { dims[i] = dims_in[i]; box[i] = box_in[i]; }
+  for (int i = 0; i + 1 < nd; ++i) strides[i] = strides_bytes[i];
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, nd, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "[cornstarch_b200] cuTensorMapEncodeTiled(f32, nd=%d) failed: %d\n", nd, (int)r);
+    return CSB_ERR_TENSORMAP;
+  }
+  return 0;
+}
+
 inline int launch_result() {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {

@@ -19,7 +19,7 @@ from dataclasses import dataclass
 
 import torch
 import torch.nn as nn
-from torch.utils.checkpoint import checkpoint
+from ..utils.recompute import checkpoint_layer
 
 from .. import nn as cnn
 from ..ops import attention as A
@@ -373,7 +373,7 @@ class DecoderModel(PreTrainedModel):
                 if self.config.layer_types[layer.self_attn.layer_idx] == "sliding_attention":
                     lrope = self.rotary_emb_local(hidden_states.device, max_pos)
             if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
-                delta, residual, aux = checkpoint(layer, delta, residual, lrope, pos, mask, use_reentrant=False)
+                delta, residual, aux = checkpoint_layer(layer, delta, residual, lrope, pos, mask)
             else:
                 delta, residual, aux = layer(delta, residual, lrope, pos, mask)
             if aux is not None:

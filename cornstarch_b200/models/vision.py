@@ -16,7 +16,7 @@ import math
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
-from torch.utils.checkpoint import checkpoint
+from ..utils.recompute import checkpoint_layer
 
 from .. import nn as cnn
 from ..ops import attention as A
@@ -139,7 +139,7 @@ class _Encoder(nn.Module):
             if is_released(layer):
                 continue
             if ckpt and torch.is_grad_enabled():
-                x = checkpoint(layer, x, mask, use_reentrant=False)
+                x = checkpoint_layer(layer, x, mask)
             else:
                 x = layer(x, mask)
         return x

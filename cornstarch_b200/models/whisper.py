@@ -14,7 +14,7 @@ import math
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
-from torch.utils.checkpoint import checkpoint
+from ..utils.recompute import checkpoint_layer
 
 from .. import nn as cnn
 from ..ops import attention as A
@@ -135,7 +135,7 @@ class WhisperEncoder(PreTrainedModel):
             if self.training and self.layerdrop > 0 and torch.rand(()) < self.layerdrop:
                 continue  # LayerDrop, kept from the reference (cornstarch/shardformer/modeling/whisper.py:108-116)
             if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
-                x = checkpoint(layer, x, mask, use_reentrant=False)
+                x = checkpoint_layer(layer, x, mask)
             else:
                 x = layer(x, mask)
         if not self.holds("layer_norm"):

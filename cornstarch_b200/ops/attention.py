@@ -20,6 +20,8 @@ import ctypes as C
 import math
 from dataclasses import dataclass, field
 
+import threading
+
 import torch
 
 from . import _native as nat
@@ -229,10 +231,61 @@ class _AttnFn(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+class _AttnReplayFn(torch.autograd.Function):
+    """Forward = an output computed earlier (kept across an activation recomputation); backward = the real one."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, mask, scale, out, lse):
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.mask, ctx.scale = mask, scale
+        return out.view_as(out)
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = attention_backward(do, q, k, v, out, lse, ctx.mask, ctx.scale)
+        return dq, dk, dv, None, None, None, None
+
+
+_TAPE = threading.local()
+
+
+class attention_tape:
+    """Context manager used by activation recomputation that keeps attention outputs.
+
+    ``record``: every :func:`attention` call appends its ``(out, lse)`` to ``items`` (the caller runs under
+    ``torch.no_grad``).  ``replay``: calls pop their entry in the same order and skip the forward kernel; the
+    backward kernel runs as usual.  ``out`` + ``lse`` cost ``S * H * (2 D + 4)`` bytes per layer, far less than the
+    layer's other activations, while the forward kernel is the most expensive part of a recomputation at long
+    sequence lengths.
+    """
+
+    def __init__(self, items: list, mode: str):
+        assert mode in ("record", "replay")
+        self.items, self.mode = items, mode
+
+    def __enter__(self):
+        self.prev = getattr(_TAPE, "cur", None)
+        _TAPE.cur = self
+        return self
+
+    def __exit__(self, *exc):
+        _TAPE.cur = self.prev
+        return False
+
+
 def attention(q, k, v, mask: AttnMask | None = None, scale: float | None = None) -> torch.Tensor:
     """``softmax(scale q k^T + mask) v`` for ``[B, S, H, D]`` tensors (GQA when ``Hq > Hk``)."""
     mask = mask or AttnMask.causal()
     if q.is_cuda and q.dtype == torch.bfloat16:
+        tape = getattr(_TAPE, "cur", None)
+        if tape is not None and tape.mode == "record" and not torch.is_grad_enabled():
+            out, lse = attention_forward(q, k, v, mask, scale)
+            tape.items.append((out, lse))
+            return out
+        if tape is not None and tape.mode == "replay" and tape.items:
+            out, lse = tape.items.pop(0)
+            return _AttnReplayFn.apply(q, k, v, mask, scale, out, lse)
         return _AttnFn.apply(q, k, v, mask, scale)
     o, _ = attention_reference(q, k, v, mask, scale)
     return o
