@@ -397,6 +397,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_st_32x32(tmem_S + buf * 128 + half * 32 + lane_addr, pk);
       tmem_st_wait();
       l_sum += (ls0 + ls1) + (ls2 + ls3);
+      // S(it+1) is issued before the MMA warp waits for p_full(it), so nothing else keeps a fast thread from arriving
+      // twice in one phase (its second arrival would stand in for a slow thread's first): wait until every thread has
+      // arrived for the previous tile.
+      if (it > 0 && !at_wait(p_full, (it - 1) & 1, abort_flag)) { fail(ST_TIMEOUT_MISC); break; }
       tc_fence_before();
       mbar_arrive(p_full);
       ++it;

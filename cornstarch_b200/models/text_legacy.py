@@ -119,7 +119,7 @@ class _GPT2MLP(nn.Module):
 class GPT2Block(nn.Module):
     def __init__(self, config):
         super().__init__()
-        self.nh = config.n_head
+        self.num_heads, self.head_dim = config.n_head, config.n_embd // config.n_head
         self.act = config.activation_function
         self.ln_1 = cnn.LayerNorm(config.n_embd, config.layer_norm_epsilon)
         self.attn = _GPT2Attention(config)
@@ -128,8 +128,7 @@ class GPT2Block(nn.Module):
 
     def forward(self, x, mask):
         B, S, H = x.shape
-        D = H // self.nh
-        qkv = self.attn.c_attn(self.ln_1(x)).view(B, S, 3, self.nh, D)
+        qkv = self.attn.c_attn(self.ln_1(x)).view(B, S, 3, self.num_heads, self.head_dim)
         a = A.attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], mask)
         a = self.attn.c_proj(a.reshape(B, S, H))
         h2, x = self.ln_2(a, x)
@@ -254,18 +253,18 @@ class BertLayer(nn.Module):
 
     def __init__(self, config):
         super().__init__()
-        self.nh, self.act = config.num_attention_heads, config.hidden_act
+        self.num_heads, self.head_dim, self.act = config.num_attention_heads, config.hidden_size // config.num_attention_heads, config.hidden_act
         self.attention = _BertAttention(config)
         self.intermediate = _BertIntermediate(config)
         self.output = _BertOut(config.intermediate_size, config.hidden_size, config.layer_norm_eps)
 
     def forward(self, x, mask):
-        B, S, H = x.shape
-        D = H // self.nh
+        B, S, _ = x.shape
         s = self.attention.self
-        qkv = multi_linear(x, [s.query.weight, s.key.weight, s.value.weight], [s.query.bias, s.key.bias, s.value.bias])
-        q, k, v = (qkv[..., i * H : (i + 1) * H].view(B, S, self.nh, D) for i in range(3))
-        a = self.attention.output.dense(A.attention(q, k, v, mask).reshape(B, S, H))
+        W = self.num_heads * self.head_dim
+        qkv = multi_linear(s.query.input_hook(x), [s.query.weight, s.key.weight, s.value.weight], [s.query.bias, s.key.bias, s.value.bias])
+        q, k, v = (qkv[..., i * W : (i + 1) * W].view(B, S, self.num_heads, self.head_dim) for i in range(3))
+        a = self.attention.output.dense(A.attention(q, k, v, mask).reshape(B, S, W))
         x, _ = self.attention.output.LayerNorm(a, x)  # LN(x + a)
         m = self.output.dense(E.activation(self.intermediate.dense(x), self.act))
         x, _ = self.output.LayerNorm(m, x)
@@ -395,7 +394,8 @@ class OPTDecoderLayer(nn.Module):
     def __init__(self, config):
         super().__init__()
         H = config.hidden_size
-        self.nh, self.act, self.pre_ln = config.num_attention_heads, config.activation_function, config.do_layer_norm_before
+        self.num_heads, self.head_dim = config.num_attention_heads, H // config.num_attention_heads
+        self.act, self.pre_ln = config.activation_function, config.do_layer_norm_before
         self.self_attn = _OPTAttention(H, config.enable_bias)
         self.self_attn_layer_norm = cnn.LayerNorm(H, 1e-5)
         self.fc1 = cnn.Linear(H, config.ffn_dim, bias=config.enable_bias)
@@ -403,14 +403,14 @@ class OPTDecoderLayer(nn.Module):
         self.final_layer_norm = cnn.LayerNorm(H, 1e-5)
 
     def forward(self, x, mask):
-        B, S, H = x.shape
-        D = H // self.nh
+        B, S, _ = x.shape
         a = self.self_attn
+        W = self.num_heads * self.head_dim
         h = self.self_attn_layer_norm(x) if self.pre_ln else x
         biases = [a.q_proj.bias, a.k_proj.bias, a.v_proj.bias] if a.q_proj.bias is not None else None
-        qkv = multi_linear(h, [a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], biases)
-        q, k, v = (qkv[..., i * H : (i + 1) * H].view(B, S, self.nh, D) for i in range(3))
-        o = a.out_proj(A.attention(q, k, v, mask).reshape(B, S, H))
+        qkv = multi_linear(a.q_proj.input_hook(h), [a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], biases)
+        q, k, v = (qkv[..., i * W : (i + 1) * W].view(B, S, self.num_heads, self.head_dim) for i in range(3))
+        o = a.out_proj(A.attention(q, k, v, mask).reshape(B, S, W))
         if self.pre_ln:
             h2, x = self.final_layer_norm(o, x)
             return x + self.fc2(E.activation(self.fc1(h2), self.act))

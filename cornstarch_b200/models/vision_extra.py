@@ -88,7 +88,8 @@ class Dinov2Layer(nn.Module):
     def __init__(self, config):
         super().__init__()
         H = config.hidden_size
-        self.nh, self.act, self.swiglu = config.num_attention_heads, config.hidden_act, config.use_swiglu_ffn
+        self.num_heads, self.head_dim = config.num_attention_heads, H // config.num_attention_heads
+        self.act, self.swiglu = config.hidden_act, config.use_swiglu_ffn
         self.norm1 = cnn.LayerNorm(H, config.layer_norm_eps)
         self.attention = _DinoAttention(H, config.qkv_bias)
         self.layer_scale1 = _LayerScale(H, config.layerscale_value)
@@ -101,7 +102,7 @@ class Dinov2Layer(nn.Module):
         a = self.attention.attention
         biases = [a.query.bias, a.key.bias, a.value.bias] if a.query.bias is not None else None
         qkv = multi_linear(self.norm1(x), [a.query.weight, a.key.weight, a.value.weight], biases)
-        o = self.attention.output.dense(_attend(qkv, self.nh, x.shape[-1] // self.nh, mask, self.attn_impl))
+        o = self.attention.output.dense(_attend(qkv, self.num_heads, self.head_dim, mask, self.attn_impl))
         x = x + self.layer_scale1(o)
         h = self.norm2(x)
         if self.swiglu:
@@ -194,7 +195,8 @@ class EvaCLIPEncoderLayer(nn.Module):
 
     def __init__(self, config):
         super().__init__()
-        self.nh, self.act, self.post = config.num_attention_heads, config.hidden_act, bool(config.post_layernorm)
+        self.num_heads, self.head_dim = config.num_attention_heads, config.hidden_size // config.num_attention_heads
+        self.act, self.post = config.hidden_act, bool(config.post_layernorm)
         self.self_attn = _EvaAttention(config)
         self.layer_norm1 = _eva_norm(config)
         self.mlp = _EvaMLP(config)
@@ -203,16 +205,15 @@ class EvaCLIPEncoderLayer(nn.Module):
 
     def _qkv(self, h):
         a = self.self_attn
-        H = h.shape[-1]
+        H = a.q_proj.weight.shape[0]
         zero = lambda: torch.zeros(H, dtype=h.dtype, device=h.device)  # noqa: E731
         bs = [a.q_proj.bias, a.k_proj.bias, a.v_proj.bias]
         biases = None if all(b is None for b in bs) else [b if b is not None else zero() for b in bs]
         return multi_linear(h, [a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], biases)
 
     def forward(self, x, mask):
-        D = x.shape[-1] // self.nh
         h = x if self.post else self.layer_norm1(x)
-        o = self.self_attn.out_proj(_attend(self._qkv(h), self.nh, D, mask, self.attn_impl))
+        o = self.self_attn.out_proj(_attend(self._qkv(h), self.num_heads, self.head_dim, mask, self.attn_impl))
         x = x + (self.layer_norm1(o) if self.post else o)
         h = x if self.post else self.layer_norm2(x)
         m = self.mlp.fc2(E.activation(self.mlp.fc1(h), self.act))
@@ -298,7 +299,7 @@ class InternVisionEncoderLayer(nn.Module):
     def __init__(self, config):
         super().__init__()
         H = config.hidden_size
-        self.nh, self.act = config.num_attention_heads, config.hidden_act
+        self.num_heads, self.head_dim, self.act = config.num_attention_heads, H // config.num_attention_heads, config.hidden_act
         self.attn = _InternAttention(config)
         self.mlp = _InternMLP(config)
         self.norm1 = cnn.RMSNorm(H, config.layer_norm_eps)
@@ -308,13 +309,11 @@ class InternVisionEncoderLayer(nn.Module):
         self.attn_impl = None
 
     def forward(self, x, mask):
-        B, S, H = x.shape
-        D = H // self.nh
         qkv = self.attn.qkv(self.norm1(x))
         if self.attn.qk_normalization:
-            q, k, v = qkv.split(H, dim=-1)
+            q, k, v = qkv.split(qkv.shape[-1] // 3, dim=-1)
             qkv = torch.cat([self.attn.q_norm(q.contiguous()), self.attn.k_norm(k.contiguous()), v], dim=-1)
-        o = self.attn.proj(_attend(qkv, self.nh, D, mask, self.attn_impl))
+        o = self.attn.proj(_attend(qkv, self.num_heads, self.head_dim, mask, self.attn_impl))
         x = x + o * self.ls1.to(x.dtype)
         m = self.mlp.fc2(E.activation(self.mlp.fc1(self.norm2(x)), self.act))
         return x + m * self.ls2.to(x.dtype)
@@ -411,7 +410,7 @@ class PixtralAttentionLayer(nn.Module):
     def __init__(self, config):
         super().__init__()
         H = config.hidden_size
-        self.nh, self.D, self.act = config.num_attention_heads, config.head_dim, config.hidden_act
+        self.num_heads, self.head_dim, self.act = config.num_attention_heads, config.head_dim, config.hidden_act
         self.attention_norm = cnn.RMSNorm(H, 1e-5)
         self.feed_forward = _PixtralMLP(H, config.intermediate_size)
         self.attention = _PixtralAttention(H)
@@ -422,8 +421,8 @@ class PixtralAttentionLayer(nn.Module):
         a, f = self.attention, self.feed_forward
         qkv = multi_linear(self.attention_norm(x), [a.q_proj.weight, a.k_proj.weight, a.v_proj.weight])
         if rope is not None:
-            qkv = E.rope_(qkv, rope[0], rope[1], pos, 2 * self.nh, self.D)
-        x = x + a.o_proj(_attend(qkv, self.nh, self.D, mask, self.attn_impl))
+            qkv = E.rope_(qkv, rope[0], rope[1], pos, 2 * self.num_heads, self.head_dim)
+        x = x + a.o_proj(_attend(qkv, self.num_heads, self.head_dim, mask, self.attn_impl))
         gu = multi_linear(self.ffn_norm(x), [f.gate_proj.weight, f.up_proj.weight])
         return x + f.down_proj(E.glu(gu, self.act))
 
@@ -519,16 +518,15 @@ class Qwen2VLVisionBlock(nn.Module):
     def __init__(self, config):
         super().__init__()
         H = config.embed_dim
-        self.nh, self.act = config.num_heads, config.hidden_act
+        self.num_heads, self.head_dim, self.act = config.num_heads, H // config.num_heads, config.hidden_act
         self.norm1, self.norm2 = cnn.LayerNorm(H, 1e-6), cnn.LayerNorm(H, 1e-6)
         self.attn = _QwenVisionAttention(H)
         self.mlp = _QwenVisionMLP(H, int(H * config.mlp_ratio))
         self.attn_impl = None
 
     def forward(self, x, mask, rope, pos):
-        D = x.shape[-1] // self.nh
-        qkv = E.rope_(self.attn.qkv(self.norm1(x)), rope[0], rope[1], pos, 2 * self.nh, D)
-        x = x + self.attn.proj(_attend(qkv, self.nh, D, mask, self.attn_impl))
+        qkv = E.rope_(self.attn.qkv(self.norm1(x)), rope[0], rope[1], pos, 2 * self.num_heads, self.head_dim)
+        x = x + self.attn.proj(_attend(qkv, self.num_heads, self.head_dim, mask, self.attn_impl))
         return x + self.mlp.fc2(E.activation(self.mlp.fc1(self.norm2(x)), self.act))
 
 

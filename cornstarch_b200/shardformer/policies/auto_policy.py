@@ -19,6 +19,17 @@ _NATIVE = {
     "cornstarch_b200.models.whisper.WhisperEncoder": P.WhisperEncoderPolicy,
     "cornstarch_b200.models.whisper.Qwen2AudioEncoder": P.Qwen2AudioEncoderPolicy,
     "cornstarch_b200.multimodal.modeling.MultimodalProjector": P.MultimodalProjectorPolicy,
+    "cornstarch_b200.models.vision_extra.Dinov2Model": P.Dinov2ModelPolicy,
+    "cornstarch_b200.models.vision_extra.EvaCLIPVisionModel": P.EvaCLIPVisionModelPolicy,
+    "cornstarch_b200.models.vision_extra.InternVisionModel": P.InternVisionModelPolicy,
+    "cornstarch_b200.models.vision_extra.PixtralVisionModel": P.PixtralVisionModelPolicy,
+    "cornstarch_b200.models.vision_extra.Qwen2VisionTransformerPretrainedModel": P.Qwen2VisionTransformerPolicy,
+    "cornstarch_b200.models.text_legacy.GPT2Model": P.GPT2ModelPolicy,
+    "cornstarch_b200.models.text_legacy.GPT2LMHeadModel": P.GPT2LMHeadModelPolicy,
+    "cornstarch_b200.models.text_legacy.BertModel": P.BertModelPolicy,
+    "cornstarch_b200.models.text_legacy.BertForMaskedLM": P.BertForMaskedLMPolicy,
+    "cornstarch_b200.models.text_legacy.OPTModel": P.OPTModelPolicy,
+    "cornstarch_b200.models.text_legacy.OPTForCausalLM": P.OPTForCausalLMPolicy,
 }
 
 
@@ -44,6 +55,17 @@ _HF_ALIASES.update({
     "transformers.models.whisper.modeling_whisper.WhisperEncoder": P.WhisperEncoderPolicy,
     "transformers.models.qwen2_audio.modeling_qwen2_audio.Qwen2AudioEncoder": P.Qwen2AudioEncoderPolicy,
     "cornstarch.models.multimodal_language_model.modeling_multimodal_language_model.MultimodalProjector": P.MultimodalProjectorPolicy,
+    "transformers.models.dinov2.modeling_dinov2.Dinov2Model": P.Dinov2ModelPolicy,
+    "cornstarch.models.evaclip.modeling_evaclip.EvaCLIPVisionModel": P.EvaCLIPVisionModelPolicy,
+    "cornstarch.models.intern_vit.modeling_intern_vit.InternVisionModel": P.InternVisionModelPolicy,
+    "transformers.models.pixtral.modeling_pixtral.PixtralVisionModel": P.PixtralVisionModelPolicy,
+    "transformers.models.qwen2_vl.modeling_qwen2_vl.Qwen2VisionTransformerPretrainedModel": P.Qwen2VisionTransformerPolicy,
+    "transformers.models.gpt2.modeling_gpt2.GPT2Model": P.GPT2ModelPolicy,
+    "transformers.models.gpt2.modeling_gpt2.GPT2LMHeadModel": P.GPT2LMHeadModelPolicy,
+    "transformers.models.bert.modeling_bert.BertModel": P.BertModelPolicy,
+    "transformers.models.bert.modeling_bert.BertForMaskedLM": P.BertForMaskedLMPolicy,
+    "transformers.models.opt.modeling_opt.OPTModel": P.OPTModelPolicy,
+    "transformers.models.opt.modeling_opt.OPTForCausalLM": P.OPTForCausalLMPolicy,
 })
 
 _POLICY_LIST = {**_NATIVE, **_HF_ALIASES}

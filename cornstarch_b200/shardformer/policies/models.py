@@ -9,6 +9,8 @@ policies/vit.py:31-39, policies/whisper.py:36-47, policies/multimodal.py:33-44.
 from __future__ import annotations
 
 from ...models import llama as L
+from ...models import text_legacy as T
+from ...models import vision_extra as X
 from ...models import moe as M
 from ...models import vision as V
 from ...models import whisper as W
@@ -156,3 +158,144 @@ class MultimodalProjectorPolicy(ModelPolicy):
 
     def pipeline_template_sanity_check(self, template) -> None:
         return None
+
+
+class Dinov2ModelPolicy(ViTModelPolicy):
+    model_cls = X.Dinov2Model
+    last_stage_modules = ["layernorm"]
+    tp_rules = [
+        TPRule(r"encoder\.layer\.\d+\.attention\.attention\." + _ENC_ATTN_COL, "col"),
+        TPRule(r"encoder\.layer\.\d+\.attention\.output\.dense", "row"),
+        TPRule(r"encoder\.layer\.\d+\.mlp\.fc1", "col"),
+        TPRule(r"encoder\.layer\.\d+\.mlp\.fc2", "row"),
+    ]
+
+
+class EvaCLIPVisionModelPolicy(SiglipVisionModelPolicy):
+    model_cls = X.EvaCLIPVisionModel
+    last_stage_modules = ["vision_model.post_layernorm"]
+    head_modules = r"vision_model\.encoder\.layers\.\d+"
+    tp_rules = SiglipVisionModelPolicy.tp_rules[:4]
+
+
+class InternVisionModelPolicy(ModelPolicy):
+    """Pipeline only when q/k are RMS-normalised over the full width (that norm cannot be sharded); otherwise the
+    fused qkv is column parallel (cornstarch/shardformer/policies/intern_vit.py:35-45)."""
+
+    model_cls = X.InternVisionModel
+    first_stage_modules = ["embeddings"]
+    last_stage_modules = []
+    head_modules = r"encoder\.layers\.\d+"
+    tp_rules = [
+        TPRule(r"encoder\.layers\.\d+\.attn\.qkv", "col", "qkv"),
+        TPRule(r"encoder\.layers\.\d+\.attn\.proj", "row"),
+        TPRule(r"encoder\.layers\.\d+\.mlp\.fc1", "col"),
+        TPRule(r"encoder\.layers\.\d+\.mlp\.fc2", "row"),
+    ]
+
+    def split_sizes(self, path, module):
+        H = self.model.config.hidden_size
+        return [H, H, H] if path.endswith("qkv") else None
+
+    def config_sanity_check(self):
+        super().config_sanity_check()
+        sc = self.shard_config
+        if sc is not None and sc.tensor_parallel_size > 1 and self.model.config.qk_normalization:
+            raise ValueError("InternViT with qk_normalization cannot be tensor parallel: q_norm/k_norm span all heads")
+
+
+class PixtralVisionModelPolicy(ModelPolicy):
+    model_cls = X.PixtralVisionModel
+    first_stage_modules = ["patch_conv", "ln_pre", "patch_positional_embedding"]
+    last_stage_modules = []
+    supported_sp_modes = ("ring_attn",)
+    head_modules = r"transformer\.layers\.\d+"
+    tp_rules = [
+        TPRule(r"transformer\.layers\.\d+\.attention\.(q_proj|k_proj|v_proj)", "col"),
+        TPRule(r"transformer\.layers\.\d+\.attention\.o_proj", "row"),
+        TPRule(r"transformer\.layers\.\d+\.feed_forward\.(gate_proj|up_proj)", "col"),
+        TPRule(r"transformer\.layers\.\d+\.feed_forward\.down_proj", "row"),
+    ]
+
+
+class Qwen2VisionTransformerPolicy(ModelPolicy):
+    model_cls = X.Qwen2VisionTransformerPretrainedModel
+    first_stage_modules = ["patch_embed", "rotary_pos_emb"]
+    last_stage_modules = ["merger"]
+    supported_sp_modes = ("ring_attn",)
+    head_modules = r"blocks\.\d+"
+    tp_rules = [
+        TPRule(r"blocks\.\d+\.attn\.qkv", "col", "qkv"),
+        TPRule(r"blocks\.\d+\.attn\.proj", "row"),
+        TPRule(r"blocks\.\d+\.mlp\.fc1", "col"),
+        TPRule(r"blocks\.\d+\.mlp\.fc2", "row"),
+    ]
+
+    def split_sizes(self, path, module):
+        H = self.model.config.embed_dim
+        return [H, H, H] if path.endswith("qkv") else None
+
+
+class GPT2ModelPolicy(ModelPolicy):
+    """Pipeline parallel only: GPT-2 stores its projection weights transposed (``Conv1D``)
+    (module list cornstarch/shardformer/policies/gpt2.py:44-55)."""
+
+    model_cls = T.GPT2Model
+    first_stage_modules = ["wte", "wpe", "drop"]
+    last_stage_modules = ["ln_f"]
+    tp_rules = []
+
+    def config_sanity_check(self):
+        super().config_sanity_check()
+        sc = self.shard_config
+        if sc is not None and sc.tensor_parallel_size > 1:
+            raise ValueError("GPT-2 (Conv1D weights) supports pipeline and data parallelism only")
+
+
+class GPT2LMHeadModelPolicy(GPT2ModelPolicy):
+    model_cls = T.GPT2LMHeadModel
+    first_stage_modules = ["transformer.wte", "transformer.wpe", "transformer.drop"]
+    last_stage_modules = ["transformer.ln_f", "lm_head"]
+
+    def get_shared_params(self):
+        if getattr(self.model.config, "tie_word_embeddings", False):
+            return [{"first": "transformer.wte.weight", "last": "lm_head.weight"}]
+        return []
+
+
+class BertModelPolicy(ModelPolicy):
+    model_cls = T.BertModel
+    first_stage_modules = ["embeddings"]
+    last_stage_modules = ["pooler"]
+    head_modules = r"(bert\.)?encoder\.layer\.\d+"
+    tp_rules = [
+        TPRule(r"(bert\.)?encoder\.layer\.\d+\.attention\.self\.(query|key|value)", "col"),
+        TPRule(r"(bert\.)?encoder\.layer\.\d+\.attention\.output\.dense", "row"),
+        TPRule(r"(bert\.)?encoder\.layer\.\d+\.intermediate\.dense", "col"),
+        TPRule(r"(bert\.)?encoder\.layer\.\d+\.output\.dense", "row"),
+    ]
+
+
+class BertForMaskedLMPolicy(BertModelPolicy):
+    model_cls = T.BertForMaskedLM
+    first_stage_modules = ["bert.embeddings"]
+    last_stage_modules = ["cls"]
+
+
+class OPTModelPolicy(ModelPolicy):
+    model_cls = T.OPTModel
+    first_stage_modules = ["decoder.embed_tokens", "decoder.embed_positions", "decoder.project_in"]
+    last_stage_modules = ["decoder.final_layer_norm", "decoder.project_out"]
+    head_modules = r"(model\.)?decoder\.layers\.\d+"
+    tp_rules = [
+        TPRule(r"(model\.)?decoder\.layers\.\d+\.self_attn\.(q_proj|k_proj|v_proj)", "col"),
+        TPRule(r"(model\.)?decoder\.layers\.\d+\.self_attn\.out_proj", "row"),
+        TPRule(r"(model\.)?decoder\.layers\.\d+\.fc1", "col"),
+        TPRule(r"(model\.)?decoder\.layers\.\d+\.fc2", "row"),
+    ]
+
+
+class OPTForCausalLMPolicy(OPTModelPolicy):
+    model_cls = T.OPTForCausalLM
+    first_stage_modules = ["model.decoder.embed_tokens", "model.decoder.embed_positions", "model.decoder.project_in"]
+    last_stage_modules = ["model.decoder.final_layer_norm", "model.decoder.project_out", "lm_head"]
