@@ -26,6 +26,7 @@
 // Replaces cornstarch/kernel/bitfield_attention.py:526-929 (T8, T9: fp32 atomics for dQ, dK and dV)
 // and cornstarch/kernel/attention.py:348-852.
 #include "host.h"
+#include "kv_segments.h"
 #include "mask.cuh"
 #include "ptx.cuh"
 
@@ -49,10 +50,11 @@ struct AttnBwdParams {
   const float* lse;   // [B][Hq][Sq]
   const float* delta; // [B][Hq][Sq]
   float* dq_acc;      // [B][Sq][Hq][D] fp32, zeroed by the caller
-  __nv_bfloat16* dK;
-  __nv_bfloat16* dV;
-  long dk_stride_b, dk_stride_s, dv_stride_b, dv_stride_s;
+  __nv_bfloat16* dK[CSB_MAX_SEG];  // per key segment: where its dK / dV tiles go (possibly a peer's inbox)
+  __nv_bfloat16* dV[CSB_MAX_SEG];
+  long dk_stride_b[CSB_MAX_SEG], dk_stride_s[CSB_MAX_SEG], dv_stride_b[CSB_MAX_SEG], dv_stride_s[CSB_MAX_SEG];
   int* status;
+  SegInfo seg;
 };
 
 struct BwdSmem {
@@ -133,9 +135,9 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloa
 }
 
 __global__ void __launch_bounds__(BW_THREADS, 1)
-attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
-                const __grid_constant__ CUtensorMap tm_dq, const AttnBwdParams p) {
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ KvMaps kvm,
+                const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
+                const AttnBwdParams p) {
   using L = BwdSmem;
   constexpr int QS = L::QSTAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -153,13 +155,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* n_valid_slot = reinterpret_cast<int*>(tmem_slot + 2);
+  int* peer_ok_slot = reinterpret_cast<int*>(tmem_slot + 3);
   int16_t* tile_idx = reinterpret_cast<int16_t*>(smem + L::LIST_OFF);
   int8_t* tile_cls = reinterpret_cast<int8_t*>(smem + L::LIST_OFF + L::MAX_TILES * 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kj = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int group = p.Hq / p.Hk;
-  const int k0 = kj * BW_BKV;
+  const int k0 = kj * BW_BKV;                              // index into k_bits / k_pos (padded gathered space)
+  const int sg = seg_of_tile(p.seg, kj);                   // which K/V segment (rank) this key block belongs to
+  const int row0 = (kj - p.seg.tile_start[sg]) * BW_BKV;   // first row of the block inside that segment
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -190,7 +195,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       n += __popc(m);
     }
-    if (lane == 0) *n_valid_slot = n < L::MAX_TILES ? n : L::MAX_TILES;
+    if (lane == 0) {
+      *n_valid_slot = n < L::MAX_TILES ? n : L::MAX_TILES;
+      // A key block of a peer: nothing of this CTA may touch that rank's memory (loads of K/V, stores of dK/dV
+      // into its inbox) before the rank has staged its K/V, which also means it is done with its previous inbox.
+      int ok = 1;
+      if (p.seg.ready_flags != nullptr && sg != p.seg.my_seg) {
+        ok = wait_peer_flag(p.seg.ready_flags + sg, p.seg.ready_value) ? 1 : 0;
+        if (!ok) atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG);
+      }
+      *peer_ok_slot = ok;
+    }
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
@@ -201,7 +216,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int n_valid = *n_valid_slot;
-  const int n_iter = n_valid * group;
+  const bool peer_ready = *peer_ok_slot != 0;
+  const int n_iter = peer_ready ? n_valid * group : 0;
   // TMEM columns: S^T[0] 0..63, S^T[1] 64..127, dP^T 128..191, dQ^T 192..255, dV 256..383, dK 384..511
   const uint32_t tmem_dPT = tmem_base + 128;
   const uint32_t tmem_dQT = tmem_base + 192;
@@ -212,20 +228,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
       tma_prefetch_desc(&tm_do);
-      mbar_expect_tx(kv_full, 4 * KV_CHUNK);
-      for (int c = 0; c < 2; ++c) {
-        tma_load_4d(smem + L::K_OFF + c * KV_CHUNK, &tm_k, kv_full, c * 64, hk, k0, b);
-        tma_load_4d(smem + L::V_OFF + c * KV_CHUNK, &tm_v, kv_full, c * 64, hk, k0, b);
+      const bool peer_ok = peer_ready;
+      if (peer_ok) {
+        mbar_expect_tx(kv_full, 4 * KV_CHUNK);
+        for (int c = 0; c < 2; ++c) {
+          tma_load_4d(smem + L::K_OFF + c * KV_CHUNK, &kvm.k[sg], kv_full, c * 64, hk, row0, b);
+          tma_load_4d(smem + L::V_OFF + c * KV_CHUNK, &kvm.v[sg], kv_full, c * 64, hk, row0, b);
+        }
       }
-      for (int it = 0; it < n_iter; ++it) {
+      for (int it = 0; peer_ok && it < n_iter; ++it) {
         const int h = hk * group + it / n_valid;
         const int i = tile_idx[it % n_valid];
         const int st = it % QS;
         if (!bw_wait(&q_empty[st], ((it / QS) & 1) ^ 1, abort_flag)) {
-          atomicExch(p.status, ST_TIMEOUT_EMPTY);
+          atomicCAS(p.status, 0, ST_TIMEOUT_EMPTY);
           *abort_flag = 1;
           break;
         }
@@ -248,12 +265,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t dst_s = smem_u32(smem + L::DST_OFF);
       const int ksteps_d = p.dk16 / 16;
       bool ok = bw_wait(kv_full, 0, abort_flag);
-      if (!ok) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; }
+      if (!ok) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; }
 
       // S^T(it) = K Q^T into ST[it & 1]; waits for the Q/dO stage of that iteration
       auto issue_st = [&](int it) -> bool {
         const int st = it % QS;
-        if (!bw_wait(&q_full[st], (it / QS) & 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
+        if (!bw_wait(&q_full[st], (it / QS) & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
         tc_fence_after();
         const uint32_t q_s = smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK);
         const uint32_t t_st = tmem_base + (it & 1) * 64;
@@ -283,7 +300,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       for (int it = 0; ok && it < n_iter; ++it) {
         const int st = it % QS;
-        if (!bw_wait(pds_full, it & 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
+        if (!bw_wait(pds_full, it & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
         tc_fence_after();
         if (it + 1 < n_iter) issue_dpt(it + 1);  // dP^T columns were read before pds_full(it)
         const uint32_t q_s = smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK);
@@ -299,7 +316,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                    idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&q_empty[st]);
         if (it > 0) {
-          if (!bw_wait(dq_free, (it - 1) & 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_TMEM_EMPTY); *abort_flag = 1; break; }
+          if (!bw_wait(dq_free, (it - 1) & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_TMEM_EMPTY); *abort_flag = 1; break; }
           tc_fence_after();
         }
         // dQ^T = K^T dS^T  (contraction over the 128 key rows)
@@ -322,7 +339,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const int col0 = half * 32;
     const int kidx = k0 + r;
-    const bool k_valid = kidx < p.Sk;
+    const int krow = row0 + r;  // row inside the segment
+    const bool k_valid = krow < p.seg.rows[sg];
     const int64_t kb = (k_valid && p.k_bits) ? p.k_bits[(long)b * p.Sk + kidx] : 0;
     const int kpos = k_valid ? (p.k_pos ? p.k_pos[(long)b * p.Sk + kidx] : kidx) : -1;
     const float LOG2E = 1.4426950408889634f;
@@ -347,7 +365,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     bool ok = true;
     auto drain_dq = [&](int pit) -> bool {
       if (!bw_wait(dq_full, pit & 1, abort_flag)) {
-        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_TMEM_FULL);
+        if (lane == 0) atomicCAS(p.status, 0, ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
         return false;
       }
@@ -391,13 +409,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_arrive(meta_full);
       prefetch_meta(it + 1);  // global loads for the next tile fly while this one is processed
       if (!bw_wait(meta_full, it & 1, abort_flag)) {
-        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
+        if (lane == 0) atomicCAS(p.status, 0, ST_TIMEOUT_MISC);
         *abort_flag = 1;
         ok = false;
         break;
       }
       if (!bw_wait(sdp_full, it & 1, abort_flag)) {
-        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_TMEM_FULL);
+        if (lane == 0) atomicCAS(p.status, 0, ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
         ok = false;
         break;
@@ -434,7 +452,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       if (it > 0) {
         if (!bw_wait(pds_empty, (it - 1) & 1, abort_flag)) {
-          if (lane == 0) atomicExch(p.status, ST_TIMEOUT_MISC);
+          if (lane == 0) atomicCAS(p.status, 0, ST_TIMEOUT_MISC);
           *abort_flag = 1;
           ok = false;
           break;
@@ -469,13 +487,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncwarp();
     // ---- epilogue: dV and dK tiles (every MMA has retired once the last dQ^T was seen);
     //      the two warps of a lane quarter split the head-dim columns
-    if (ok) {
+    if (ok && peer_ready) {
       tc_fence_after();
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const uint32_t t = which == 0 ? tmem_dV : tmem_dK;
-        __nv_bfloat16* base = which == 0 ? p.dV + (long)b * p.dv_stride_b + (long)kidx * p.dv_stride_s + (long)hk * p.D
-                                         : p.dK + (long)b * p.dk_stride_b + (long)kidx * p.dk_stride_s + (long)hk * p.D;
+        __nv_bfloat16* base = which == 0
+                                  ? p.dV[sg] + (long)b * p.dv_stride_b[sg] + (long)krow * p.dv_stride_s[sg] + (long)hk * p.D
+                                  : p.dK[sg] + (long)b * p.dk_stride_b[sg] + (long)krow * p.dk_stride_s[sg] + (long)hk * p.D;
 #pragma unroll
         for (int c2 = 0; c2 < 2; ++c2) {
           const int cc = half * 2 + c2;
@@ -526,18 +545,19 @@ static int make_tmap_4d(CUtensorMap* tm, const void* base, int D, int H, int S, 
 
 using namespace csb;
 
-// All tensors are [B][S][H][D] bf16 views (head stride D; token/batch strides in elements).
-// lse: fp32 [B][Hq][Sq] from the forward; delta: fp32 [B][Hq][Sq] scratch; dq_acc: fp32 dense
-// [B][Sq][Hq][D] scratch that the caller has zeroed.  cls: tile classes for 128x128 tiles.
-CSB_API int csb_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
-                         const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq,
-                         int Sk, int Hq, int Hk, int D, long q_ss, long q_sb, long k_ss, long k_sb, long v_ss, long v_sb,
-                         long o_ss, long o_sb, long do_ss, long do_sb, long dq_ss, long dq_sb, long dk_ss, long dk_sb,
-                         long dv_ss, long dv_sb, float scale, int mask_mode, const long* q_bits, const long* k_bits,
-                         const int* q_pos, const int* k_pos, const signed char* cls, int* status, void* stream) {
+// q / out / dout / dq are [B][Sq][Hq][D] bf16 views (head stride D; token / batch strides in elements); keys and values
+// come as segments (kv_segments.h) and the dK / dV tiles of segment r are written to kv->dk[r] / kv->dv[r].
+// lse: fp32 [B][Hq][Sq] from the forward; delta: fp32 [B][Hq][Sq] scratch; dq_acc: fp32 dense [B][Sq][Hq][D] scratch
+// that the caller has zeroed.  Sk = padded gathered length; cls: tile classes for 128x128 tiles.
+CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void* out, const void* dout, const float* lse,
+                             float* delta, float* dq_acc, void* dq, int B, int Sq, int Sk, int Hq, int Hk, int D, long q_ss,
+                             long q_sb, long o_ss, long o_sb, long do_ss, long do_sb, long dq_ss, long dq_sb, float scale,
+                             int mask_mode, const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
+                             const signed char* cls, int* status, void* stream) {
   if (D % 8 || D > 128 || D < 16 || Hq % Hk) return CSB_ERR_BAD_ARG;
+  if (kv == nullptr || kv->n_seg < 1 || kv->n_seg > CSB_MAX_SEG) return CSB_ERR_BAD_ARG;
   if ((Sq + BW_BQ - 1) / BW_BQ > BwdSmem::MAX_TILES) return CSB_ERR_TOO_LARGE;
-  if ((q_ss % 8) || (k_ss % 8) || (v_ss % 8) || (do_ss % 8) || (dq_ss % 4) || (dk_ss % 8) || (dv_ss % 8)) return CSB_ERR_BAD_ARG;
+  if ((q_ss % 8) || (do_ss % 8) || (dq_ss % 4)) return CSB_ERR_BAD_ARG;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   {
     const long rows = (long)B * Sq * Hq;
@@ -561,16 +581,24 @@ CSB_API int csb_attn_bwd(const void* q, const void* k, const void* v, const void
   p.q_pos = q_pos; p.k_pos = k_pos;
   p.cls = reinterpret_cast<const int8_t*>(cls);
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
-  p.dK = reinterpret_cast<__nv_bfloat16*>(dk);
-  p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
-  p.dk_stride_b = dk_sb; p.dk_stride_s = dk_ss; p.dv_stride_b = dv_sb; p.dv_stride_s = dv_ss;
   p.status = status;
-  CUtensorMap tq, tk, tv, tdo;
+  fill_seg_info(&p.seg, kv, BW_BKV);
+  if (p.seg.tile_start[kv->n_seg] != p.nK) return CSB_ERR_BAD_ARG;
+  CUtensorMap tq, tdo;
+  KvMaps kvm;
   int r;
   if ((r = make_tmap_4d(&tq, q, D, Hq, Sq, B, q_ss, q_sb, BW_BQ))) return r;
-  if ((r = make_tmap_4d(&tk, k, D, Hk, Sk, B, k_ss, k_sb, BW_BKV))) return r;
-  if ((r = make_tmap_4d(&tv, v, D, Hk, Sk, B, v_ss, v_sb, BW_BKV))) return r;
   if ((r = make_tmap_4d(&tdo, dout, D, Hq, Sq, B, do_ss, do_sb, BW_BQ))) return r;
+  for (int i = 0; i < CSB_MAX_SEG; ++i) {
+    const int g = i < kv->n_seg ? i : 0;
+    if ((kv->k_stride_s[g] % 8) || (kv->v_stride_s[g] % 8) || (kv->dk_stride_s[g] % 8) || (kv->dv_stride_s[g] % 8)) return CSB_ERR_BAD_ARG;
+    if ((r = make_tmap_4d(&kvm.k[i], kv->k[g], D, Hk, kv->rows[g], B, kv->k_stride_s[g], kv->k_stride_b[g], BW_BKV))) return r;
+    if ((r = make_tmap_4d(&kvm.v[i], kv->v[g], D, Hk, kv->rows[g], B, kv->v_stride_s[g], kv->v_stride_b[g], BW_BKV))) return r;
+    p.dK[i] = reinterpret_cast<__nv_bfloat16*>(kv->dk[g]);
+    p.dV[i] = reinterpret_cast<__nv_bfloat16*>(kv->dv[g]);
+    p.dk_stride_s[i] = kv->dk_stride_s[g]; p.dk_stride_b[i] = kv->dk_stride_b[g];
+    p.dv_stride_s[i] = kv->dv_stride_s[g]; p.dv_stride_b[i] = kv->dv_stride_b[g];
+  }
   CUtensorMap tdq;
   {
     // dq_acc is dense fp32 [B][Sq][Hq][D]; a block is 32 head-dim elements (128 B) x 32 query rows
@@ -586,7 +614,7 @@ CSB_API int csb_attn_bwd(const void* q, const void* k, const void* v, const void
     attr = true;
   }
   dim3 grid(p.nK, Hk, B);
-  attn_bwd_kernel<<<grid, BW_THREADS, BwdSmem::DYN_BYTES, s>>>(tq, tk, tv, tdo, tdq, p);
+  attn_bwd_kernel<<<grid, BW_THREADS, BwdSmem::DYN_BYTES, s>>>(tq, kvm, tdo, tdq, p);
   int e = launch_result();
   if (e) return e;
   const long n_rows = (long)B * Sq;
@@ -594,5 +622,120 @@ CSB_API int csb_attn_bwd(const void* q, const void* k, const void* v, const void
   long work = n_rows * (HD / 4);
   int blocks = (int)((work + 255) / 256 < (long)sm_count() * 16 ? (work + 255) / 256 : (long)sm_count() * 16);
   attn_dq_convert_kernel<<<blocks, 256, 0, s>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), n_rows, Sq, HD, dq_sb, dq_ss);
+  return launch_result();
+}
+
+// One local K/V tensor ([B][Sk][Hk][D] views) with dK / dV of the same shape.
+CSB_API int csb_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                         const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq,
+                         int Sk, int Hq, int Hk, int D, long q_ss, long q_sb, long k_ss, long k_sb, long v_ss, long v_sb,
+                         long o_ss, long o_sb, long do_ss, long do_sb, long dq_ss, long dq_sb, long dk_ss, long dk_sb,
+                         long dv_ss, long dv_sb, float scale, int mask_mode, const long* q_bits, const long* k_bits,
+                         const int* q_pos, const int* k_pos, const signed char* cls, int* status, void* stream) {
+  CsbKvSegments kv = {};
+  kv.n_seg = 1;
+  kv.my_seg = 0;
+  kv.rows[0] = Sk;
+  kv.k[0] = k; kv.v[0] = v;
+  kv.k_stride_s[0] = k_ss; kv.k_stride_b[0] = k_sb; kv.v_stride_s[0] = v_ss; kv.v_stride_b[0] = v_sb;
+  kv.dk[0] = dk; kv.dv[0] = dv;
+  kv.dk_stride_s[0] = dk_ss; kv.dk_stride_b[0] = dk_sb; kv.dv_stride_s[0] = dv_ss; kv.dv_stride_b[0] = dv_sb;
+  kv.ready_flags = nullptr;
+  return csb_attn_bwd_seg(q, &kv, out, dout, lse, delta, dq_acc, dq, B, Sq, Sk, Hq, Hk, D, q_ss, q_sb, o_ss, o_sb, do_ss,
+                          do_sb, dq_ss, dq_sb, scale, mask_mode, q_bits, k_bits, q_pos, k_pos, cls, status, stream);
+}
+
+// --------------------------------------------------------------------------------------------- context-parallel glue
+namespace csb {
+
+// Tell every peer that this rank's event counter reached `value` (its K/V are staged, or its dK/dV tiles delivered):
+// peer r's flag array has one int per source rank.  Ordered after all earlier work of the stream; the fence makes
+// this rank's earlier stores (also those to peer memory) visible before the flag.
+__global__ void cp_signal_kernel(int* const* flag_arrays, int world, int me, int value) {
+  const int r = threadIdx.x;
+  if (r >= world) return;
+  __threadfence_system();
+  int* f = flag_arrays[r] + me;
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(f), "r"(value) : "memory");
+}
+
+// Stream-ordered (bounded) wait until every rank's counter in the local flag array reached `value`.
+__global__ void cp_wait_kernel(const int* flags, int world, int value, int* status) {
+  if (threadIdx.x != 0) return;
+  for (int r = 0; r < world; ++r)
+    if (!wait_peer_flag(flags + r, value)) {
+      atomicCAS(status, 0, ST_TIMEOUT_PEER_FLAG);
+      return;
+    }
+}
+
+struct CpReduceParams {
+  const __nv_bfloat16* src[CSB_MAX_SEG];  // one inbox slot per source rank, all [n] elements
+  int world;
+  const int* flags;  // local flag array: flags[r] >= value once rank r delivered its tiles
+  int value;
+  int* status;
+};
+
+// out = sum over source ranks of their bf16 partial tiles (fp32 accumulation).
+__global__ void __launch_bounds__(256) cp_reduce_kernel(CpReduceParams p, __nv_bfloat16* out, long n8) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) {
+    int ok = 1;
+    for (int r = 0; r < p.world && ok; ++r)
+      if (!wait_peer_flag(p.flags + r, p.value)) ok = 0;
+    if (!ok) atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG);
+    ok_s = ok;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n8; i += (long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < p.world; ++r) {
+      const uint4 u = reinterpret_cast<const uint4*>(p.src[r])[i];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        acc[2 * k] += f.x;
+        acc[2 * k + 1] += f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16x2(acc[0], acc[1]);
+    o.y = pack_bf16x2(acc[2], acc[3]);
+    o.z = pack_bf16x2(acc[4], acc[5]);
+    o.w = pack_bf16x2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+}
+
+}  // namespace csb
+
+// flag_arrays: device array of `world` pointers, entry r = rank r's flag array (peer-mapped), each int[world].
+CSB_API int csb_cp_signal(void* flag_arrays, int world, int me, int value, void* stream) {
+  if (world < 1 || world > CSB_MAX_SEG) return CSB_ERR_BAD_ARG;
+  cp_signal_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<int* const*>(flag_arrays), world, me, value);
+  return launch_result();
+}
+
+CSB_API int csb_cp_wait(const int* flags, int world, int value, int* status, void* stream) {
+  if (world < 1 || world > CSB_MAX_SEG) return CSB_ERR_BAD_ARG;
+  cp_wait_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flags, world, value, status);
+  return launch_result();
+}
+
+// out[n] = sum_r src[r][n] once every rank's counter in `flags` reached `value` (n a multiple of 8).
+CSB_API int csb_cp_reduce(const void* const* src, int world, const int* flags, int value, void* out, long n, int* status,
+                          void* stream) {
+  if (world < 1 || world > CSB_MAX_SEG || (n % 8)) return CSB_ERR_BAD_ARG;
+  CpReduceParams p;
+  for (int r = 0; r < CSB_MAX_SEG; ++r) p.src[r] = reinterpret_cast<const __nv_bfloat16*>(src[r < world ? r : 0]);
+  p.world = world; p.flags = flags; p.value = value; p.status = status;
+  const long n8 = n / 8;
+  long blocks = (n8 + 255) / 256;
+  if (blocks > (long)sm_count() * 8) blocks = (long)sm_count() * 8;
+  if (blocks < 1) blocks = 1;
+  cp_reduce_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p, reinterpret_cast<__nv_bfloat16*>(out), n8);
   return launch_result();
 }

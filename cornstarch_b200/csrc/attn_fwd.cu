@@ -19,6 +19,7 @@
 // Replaces the Triton kernels of the reference: cornstarch/kernel/bitfield_attention.py:215-523 (forward,
 // split-KV partials :1279-1436, compressed mask :104-156) and cornstarch/kernel/attention.py:56-345.
 #include "host.h"
+#include "kv_segments.h"
 #include "mask.cuh"
 #include "ptx.cuh"
 
@@ -42,6 +43,8 @@ struct AttnFwdParams {
   long o_stride_b, o_stride_s;  // elements; head stride is D
   float* lse;                   // [B][Hq][Sq]
   int* status;
+  int j_start;  // key tiles are visited in rotated order starting here (own segment first)
+  SegInfo seg;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -123,8 +126,7 @@ __device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t phase, volatile 
 
 template <int NCH>
 __global__ void __launch_bounds__(320, 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const AttnFwdParams p) {
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ KvMaps kvm, const AttnFwdParams p) {
   using L = AttnSmem<NCH>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -192,26 +194,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
-      tma_prefetch_desc(&tm_k);
-      tma_prefetch_desc(&tm_v);
       mbar_expect_tx(q_full, L::Q_BYTES);
 #pragma unroll
       for (int c = 0; c < NCH; ++c) tma_load_4d(smem + L::Q_OFF + c * CHUNK_BYTES, &tm_q, q_full, c * 64, h, q0, b);
       uint32_t it = 0;
-      for (int j = 0; j < p.nK; ++j) {
+      uint32_t opened = p.seg.my_seg >= 0 ? (1u << p.seg.my_seg) : 0u;
+      if (p.seg.ready_flags == nullptr) opened = 0xffu;
+      for (int t = 0; t < p.nK; ++t) {
+        int j = t + p.j_start;
+        if (j >= p.nK) j -= p.nK;
         if (cls_row[j] == 0) continue;
+        const int sg = seg_of_tile(p.seg, j);
+        const int row0 = (j - p.seg.tile_start[sg]) * AT_BN;
+        if (!((opened >> sg) & 1u)) {
+          // first tile from this peer: its K/V must have been staged (bounded wait on the counter it stores here)
+          if (!wait_peer_flag(p.seg.ready_flags + sg, p.seg.ready_value)) { atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG); *abort_flag = 1; break; }
+          opened |= 1u << sg;
+        }
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!at_wait(&k_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_EMPTY); *abort_flag = 1; break; }
+        if (!at_wait(&k_empty[st], ph ^ 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_EMPTY); *abort_flag = 1; break; }
         mbar_expect_tx(&k_full[st], L::KV_BYTES);
 #pragma unroll
         for (int c = 0; c < NCH; ++c)
-          tma_load_4d(smem + L::K_OFF + st * L::KV_BYTES + c * CHUNK_BYTES, &tm_k, &k_full[st], c * 64, hk, j * AT_BN, b);
-        if (!at_wait(&v_empty[st], ph ^ 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_EMPTY); *abort_flag = 1; break; }
+          tma_load_4d(smem + L::K_OFF + st * L::KV_BYTES + c * CHUNK_BYTES, &kvm.k[sg], &k_full[st], c * 64, hk, row0, b);
+        if (!at_wait(&v_empty[st], ph ^ 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_EMPTY); *abort_flag = 1; break; }
         mbar_expect_tx(&v_full[st], L::KV_BYTES);
 #pragma unroll
         for (int c = 0; c < NCH; ++c)
-          tma_load_4d(smem + L::V_OFF + st * L::KV_BYTES + c * CHUNK_BYTES, &tm_v, &v_full[st], c * 64, hk, j * AT_BN, b);
+          tma_load_4d(smem + L::V_OFF + st * L::KV_BYTES + c * CHUNK_BYTES, &kvm.v[sg], &v_full[st], c * 64, hk, row0, b);
         ++it;
       }
     }
@@ -224,7 +235,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t q_s = smem_u32(smem + L::Q_OFF);
       const int ksteps_s = p.dk16 / 16;
       bool ok = at_wait(q_full, 0, abort_flag);
-      if (!ok) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; }
+      if (!ok) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; }
       // number of non-empty key blocks
       int n = 0;
       for (int j = 0; j < p.nK; ++j) n += (cls_row[j] != 0);
@@ -235,7 +246,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       auto issue_s = [&](uint32_t it) -> bool {
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!at_wait(&k_full[st], ph, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
+        if (!at_wait(&k_full[st], ph, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
         tc_fence_after();
         const uint32_t k_s = smem_u32(smem + L::K_OFF + st * L::KV_BYTES);
         for (int kk = 0; kk < ksteps_s; ++kk) {
@@ -255,8 +266,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!at_wait(&v_full[st], ph, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
-        if (!at_wait(p_full, it & 1, abort_flag)) { atomicExch(p.status, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
+        if (!at_wait(&v_full[st], ph, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
+        if (!at_wait(p_full, it & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
         tc_fence_after();
         const uint32_t v_s = smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
         // O += P V with P read from tensor memory: 16 keys of a row = 8 packed 32-bit columns per step
@@ -290,11 +301,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     uint32_t it = 0, n_partial = 0, n_pair = 0;
     bool ok = true;
     auto fail = [&](int code) {
-      if (lane == 0) atomicExch(p.status, code);
+      if (lane == 0) atomicCAS(p.status, 0, code);
       *abort_flag = 1;
       ok = false;
     };
-    for (int j = 0; j < p.nK && ok; ++j) {
+    for (int t = 0; t < p.nK && ok; ++t) {
+      int j = t + p.j_start;
+      if (j >= p.nK) j -= p.nK;
       const int c = cls_row[j];
       if (c == 0) continue;
       const int buf = it & 1;
@@ -357,8 +370,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const float m_new = fmaxf(m_used, mx);
       const bool need = (m_new - m_used) * p.scale_log2 > 8.f;  // also true when m_used is -inf and m_new is finite
       if (it > 0 && __any_sync(0xffffffffu, need)) {
-        // rare (lazy rescale): O is only touched once the previous P V has retired.  The barrier is at most one
-        // phase ahead of the one awaited here, because P V(it) cannot be issued before this thread's p_full arrival.
+        // rare (lazy rescale): O is only touched once the previous P V has retired
         if (!at_wait(pv_done, (it - 1) & 1, abort_flag)) { fail(ST_TIMEOUT_MISC); break; }
         tc_fence_after();
         float alpha = 1.f;
@@ -397,10 +409,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_st_32x32(tmem_S + buf * 128 + half * 32 + lane_addr, pk);
       tmem_st_wait();
       l_sum += (ls0 + ls1) + (ls2 + ls3);
-      // S(it+1) is issued before the MMA warp waits for p_full(it), so nothing else keeps a fast thread from arriving
-      // twice in one phase (its second arrival would stand in for a slow thread's first): wait until every thread has
-      // arrived for the previous tile.
-      if (it > 0 && !at_wait(p_full, (it - 1) & 1, abort_flag)) { fail(ST_TIMEOUT_MISC); break; }
+      // Arrive for tile `it` only once P V(it-1) has retired.  Without this, nothing bounds how far the softmax threads
+      // run ahead of the MMA warp (S(it+1) is issued before it waits for p_full(it)): while it waits for a slow V tile,
+      // p_full could complete two phases, which its parity wait cannot tell from none; a fast thread could also arrive
+      // twice within one phase.  The exponentials above are already done, so the wait is normally free.
+      if (it > 0 && !at_wait(pv_done, (it - 1) & 1, abort_flag)) { fail(ST_TIMEOUT_MISC); break; }
       tc_fence_before();
       mbar_arrive(p_full);
       ++it;
@@ -485,17 +498,18 @@ CSB_API int csb_mask_classify(int mode, const long* q_bits, const long* k_bits, 
   return launch_result();
 }
 
-// q: [B][Sq][Hq][D], k/v: [B][Sk][Hk][D] bf16 views (head stride D, token stride *_stride_s, batch stride
-// *_stride_b, in elements); out: [B][Sq][Hq][D] view; lse: fp32 [B][Hq][Sq]; cls from csb_mask_classify
-// with bm = bn = 128.
-CSB_API int csb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
-                         int Hq, int Hk, int D, long q_stride_s, long q_stride_b, long k_stride_s, long k_stride_b,
-                         long v_stride_s, long v_stride_b, long o_stride_s, long o_stride_b, float scale, int mask_mode,
-                         const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
-                         const signed char* cls, int* status, void* stream) {
+// q: [B][Sq][Hq][D]; keys / values as segments (see kv_segments.h), each a [B][rows][Hk][D] bf16 view (head stride D,
+// token / batch strides in elements); Sk = sum of the segments' rows rounded up to 128 each (the padded gathered
+// length that k_bits / k_pos / cls are indexed by); out: [B][Sq][Hq][D] view; lse: fp32 [B][Hq][Sq]; cls from
+// csb_mask_classify with bm = bn = 128.
+CSB_API int csb_attn_fwd_seg(const void* q, const CsbKvSegments* kv, void* out, float* lse, int B, int Sq, int Sk, int Hq,
+                             int Hk, int D, long q_stride_s, long q_stride_b, long o_stride_s, long o_stride_b, float scale,
+                             int mask_mode, const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
+                             const signed char* cls, int* status, void* stream) {
   if (D % 8 || D > 128 || D < 16 || Hq % Hk) return CSB_ERR_BAD_ARG;
+  if (kv == nullptr || kv->n_seg < 1 || kv->n_seg > CSB_MAX_SEG) return CSB_ERR_BAD_ARG;
   if ((Sk + AT_BN - 1) / AT_BN > AttnSmem<2>::MAX_NK) return CSB_ERR_TOO_LARGE;
-  if ((q_stride_s % 8) || (k_stride_s % 8) || (v_stride_s % 8) || (o_stride_s % 8)) return CSB_ERR_BAD_ARG;
+  if ((q_stride_s % 8) || (o_stride_s % 8)) return CSB_ERR_BAD_ARG;
   AttnFwdParams p;
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hk = Hk; p.D = D;
   p.dk16 = (D + 15) / 16 * 16;
@@ -512,23 +526,51 @@ CSB_API int csb_attn_fwd(const void* q, const void* k, const void* v, void* out,
   p.o_stride_b = o_stride_b; p.o_stride_s = o_stride_s;
   p.lse = lse;
   p.status = status;
-  CUtensorMap tq, tk, tv;
+  fill_seg_info(&p.seg, kv, AT_BN);
+  if (p.seg.tile_start[kv->n_seg] != p.nK) return CSB_ERR_BAD_ARG;  // Sk must be the padded gathered length
+  p.j_start = (kv->my_seg >= 0 && kv->my_seg < kv->n_seg) ? p.seg.tile_start[kv->my_seg] : 0;
+  if (p.j_start >= p.nK) p.j_start = 0;
+  CUtensorMap tq;
+  KvMaps kvm;
   int r;
   if ((r = make_qkv_tmap(&tq, q, D, Hq, Sq, B, q_stride_s, q_stride_b))) return r;
-  if ((r = make_qkv_tmap(&tk, k, D, Hk, Sk, B, k_stride_s, k_stride_b))) return r;
-  if ((r = make_qkv_tmap(&tv, v, D, Hk, Sk, B, v_stride_s, v_stride_b))) return r;
+  for (int i = 0; i < CSB_MAX_SEG; ++i) {
+    const int g = i < kv->n_seg ? i : 0;  // unused slots repeat segment 0 (never dereferenced)
+    if ((kv->k_stride_s[g] % 8) || (kv->v_stride_s[g] % 8)) return CSB_ERR_BAD_ARG;
+    if ((r = make_qkv_tmap(&kvm.k[i], kv->k[g], D, Hk, kv->rows[g], B, kv->k_stride_s[g], kv->k_stride_b[g]))) return r;
+    if ((r = make_qkv_tmap(&kvm.v[i], kv->v[g], D, Hk, kv->rows[g], B, kv->v_stride_s[g], kv->v_stride_b[g]))) return r;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   dim3 grid(p.nQ, Hq, B);
   if (D <= 64) {
     auto kfn = attn_fwd_kernel<1>;
     static bool set1 = false;
     if (!set1) { if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<1>::DYN_BYTES) != cudaSuccess) return launch_result(); set1 = true; }
-    kfn<<<grid, 320, AttnSmem<1>::DYN_BYTES, s>>>(tq, tk, tv, p);
+    kfn<<<grid, 320, AttnSmem<1>::DYN_BYTES, s>>>(tq, kvm, p);
   } else {
     auto kfn = attn_fwd_kernel<2>;
     static bool set2 = false;
     if (!set2) { if (cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, AttnSmem<2>::DYN_BYTES) != cudaSuccess) return launch_result(); set2 = true; }
-    kfn<<<grid, 320, AttnSmem<2>::DYN_BYTES, s>>>(tq, tk, tv, p);
+    kfn<<<grid, 320, AttnSmem<2>::DYN_BYTES, s>>>(tq, kvm, p);
   }
   return launch_result();
+}
+
+// One local K/V tensor: q: [B][Sq][Hq][D], k/v: [B][Sk][Hk][D] bf16 views.
+CSB_API int csb_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
+                         int Hq, int Hk, int D, long q_stride_s, long q_stride_b, long k_stride_s, long k_stride_b,
+                         long v_stride_s, long v_stride_b, long o_stride_s, long o_stride_b, float scale, int mask_mode,
+                         const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
+                         const signed char* cls, int* status, void* stream) {
+  CsbKvSegments kv = {};
+  kv.n_seg = 1;
+  kv.my_seg = 0;
+  kv.rows[0] = Sk;
+  kv.k[0] = k; kv.v[0] = v;
+  kv.k_stride_s[0] = k_stride_s; kv.k_stride_b[0] = k_stride_b;
+  kv.v_stride_s[0] = v_stride_s; kv.v_stride_b[0] = v_stride_b;
+  kv.ready_flags = nullptr;
+  // the kernel indexes k_bits / k_pos / cls by the unpadded Sk when there is a single segment
+  return csb_attn_fwd_seg(q, &kv, out, lse, B, Sq, Sk, Hq, Hk, D, q_stride_s, q_stride_b, o_stride_s, o_stride_b, scale,
+                          mask_mode, q_bits, k_bits, q_pos, k_pos, cls, status, stream);
 }

@@ -119,10 +119,7 @@ def classify_mask(mask: AttnMask, B: int, Sq: int, Sk: int, device, bm: int = BL
         return cls
     cls = torch.empty(B, nQ, nK, dtype=torch.int8, device=dev)
     work = torch.zeros(B, nQ, dtype=torch.int32, device=dev) if with_work else None
-    qb = mask.q_bits.contiguous() if mask.q_bits is not None else None
-    kb = mask.k_bits.contiguous() if mask.k_bits is not None else None
-    qp = mask.q_pos.int().contiguous() if mask.q_pos is not None else None
-    kp = mask.k_pos.int().contiguous() if mask.k_pos is not None else None
+    qb, kb, qp, kp = _mask_ptrs(mask, B)
     nat.check(
         nat.lib().csb_mask_classify(mask.mode, nat.ptr(qb), nat.ptr(kb), nat.ptr(qp), nat.ptr(kp), B, Sq, Sk, bm, bn,
                                     cls.data_ptr(), nat.ptr(work), nat.stream()),
@@ -155,12 +152,19 @@ def _check_layout(t: torch.Tensor, name: str):
     assert t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0, f"{name}: token stride / base must be 16-byte aligned"
 
 
-def _mask_ptrs(mask: AttnMask):
-    qb = mask.q_bits.contiguous() if mask.q_bits is not None else None
-    kb = mask.k_bits.contiguous() if mask.k_bits is not None else None
-    qp = mask.q_pos.int().contiguous() if mask.q_pos is not None else None
-    kp = mask.k_pos.int().contiguous() if mask.k_pos is not None else None
-    return qb, kb, qp, kp
+def _rows(t, B, to_int=False):
+    """Per-token mask metadata as a contiguous ``[B, S]`` tensor (a single row is shared by the whole batch)."""
+    if t is None:
+        return None
+    if to_int:
+        t = t.int()
+    if B is not None and t.shape[0] == 1 and B > 1:
+        t = t.expand(B, -1)
+    return t.contiguous()
+
+
+def _mask_ptrs(mask: AttnMask, B: int | None = None):
+    return _rows(mask.q_bits, B), _rows(mask.k_bits, B), _rows(mask.q_pos, B, True), _rows(mask.k_pos, B, True)
 
 
 def attention_forward(q, k, v, mask: AttnMask, scale: float | None = None):
@@ -173,7 +177,7 @@ def attention_forward(q, k, v, mask: AttnMask, scale: float | None = None):
     out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
     cls = mask.classes(B, Sq, Sk, q.device)
-    qb, kb, qp, kp = _mask_ptrs(mask)
+    qb, kb, qp, kp = _mask_ptrs(mask, B)
     st = nat.status_word(q.device)
     nat.check(
         nat.lib().csb_attn_fwd(
@@ -200,7 +204,7 @@ def attention_backward(do, q, k, v, out, lse, mask: AttnMask, scale: float | Non
     dq_acc = torch.zeros((B, Sq, Hq, D), dtype=torch.float32, device=q.device)
     delta = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
     cls = mask.classes(B, Sq, Sk, q.device)
-    qb, kb, qp, kp = _mask_ptrs(mask)
+    qb, kb, qp, kp = _mask_ptrs(mask, B)
     st = nat.status_word(q.device)
     nat.check(
         nat.lib().csb_attn_bwd(

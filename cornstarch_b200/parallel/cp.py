@@ -172,8 +172,26 @@ class ContextParallelState:
         return A.AttnMask(mode=m.mode, q_bits=qb, k_bits=kb, q_pos=q_pos, k_pos=k_pos)
 
 
+FUSED_CP_ENABLED = True  # stream K/V tiles from the peers inside the attention kernels instead of gathering with NCCL
+
+
+def _fused_for(state: "ContextParallelState", q):
+    if not FUSED_CP_ENABLED or state.sizes is None or not q.is_cuda or q.dtype != torch.bfloat16:
+        return None
+    from .cp_fused import FusedContextParallelAttention
+
+    return FusedContextParallelAttention.get(state.group)
+
+
 def context_parallel_attention(q, k, v, state: ContextParallelState, scale=None, mask: A.AttnMask | None = None):
     """Local queries against the gathered keys/values (``[B, S_local, H, D]`` in, same out)."""
+    fused = _fused_for(state, q)
+    if fused is not None:
+        from .cp_fused import fused_context_parallel_attention, padded_mask
+
+        if getattr(state, "fused_mask", None) is None:
+            state.fused_mask = padded_mask(mask or state.local_mask, state.sizes)
+        return fused_context_parallel_attention(q, k, v, fused, state.sizes, state.fused_mask, scale)
     kv = torch.stack([k, v], dim=0)  # one collective for both
     kv_all = comm.gather_forward_reduce_scatter_backward(kv, 2, state.group, state.sizes)
     return A.attention(q, kv_all[0], kv_all[1], mask or state.local_mask, scale)

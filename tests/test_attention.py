@@ -173,3 +173,40 @@ def test_status_clean_after_attention():
     from cornstarch_b200.ops import _native as nat
 
     assert nat.check_status() == 0
+
+
+@pytest.mark.parametrize("sizes,my_seg", [([512, 512], 1), ([300, 180, 420], 0), ([128, 640], 1)])
+@pytest.mark.parametrize("mode", ["causal", "bitfield"])
+def test_kv_segments_local(sizes, my_seg, mode):
+    """K/V given as several tensors (the layout of context parallelism, here all on one GPU): forward and backward
+    equal the single-tensor kernels on the concatenation; the mask lives in the padded gathered index space."""
+    from cornstarch_b200.parallel.cp_fused import attention_segments_local, padded_layout
+
+    B, Hq, Hk, D = 2, 4, 2, 128
+    S = sum(sizes)
+    q, k, v = _qkv(B, S, S, Hq, Hk, D, seed=S)
+    do = torch.randn(B, S, Hq, D, generator=torch.Generator().manual_seed(1)).cuda().bfloat16()
+    pos = torch.arange(S, dtype=torch.int32).cuda()[None].expand(B, -1).contiguous()
+    bits = make_bitfield(B, S, seed=S, pad_tail=3).cuda() if mode == "bitfield" else None
+    ref_mask = A.AttnMask(mode=A.MASK_BITFIELD if bits is not None else A.MASK_CAUSAL, q_bits=bits, k_bits=bits, q_pos=pos, k_pos=pos)
+    ro, rlse = A.attention_forward(q, k, v, ref_mask)
+    rdq, rdk, rdv = A.attention_backward(do, q, k, v, ro, rlse, ref_mask)
+    starts, total = padded_layout(sizes)
+    kp = torch.full((B, total), -1, dtype=torch.int32, device="cuda")
+    kb = torch.zeros((B, total), dtype=torch.int64, device="cuda") if bits is not None else None
+    ks, vs, off = [], [], 0
+    for s0, n in zip(starts, sizes):
+        kp[:, s0 : s0 + n] = pos[:, off : off + n]
+        if kb is not None:
+            kb[:, s0 : s0 + n] = bits[:, off : off + n]
+        ks.append(k[:, off : off + n].contiguous())
+        vs.append(v[:, off : off + n].contiguous())
+        off += n
+    mask = A.AttnMask(mode=ref_mask.mode, q_bits=bits, k_bits=kb, q_pos=pos, k_pos=kp)
+    o, lse, dq, dks, dvs = attention_segments_local(q, ks, vs, mask, my_seg=my_seg, do=do)
+    _close(o, ro)
+    fin = torch.isfinite(rlse)
+    _close(lse[fin], rlse[fin], 2e-2)
+    _close(dq, rdq)
+    _close(torch.cat(dks, dim=1), rdk)
+    _close(torch.cat(dvs, dim=1), rdv)

@@ -1,0 +1,98 @@
+"""Context-parallel attention with K/V streamed from the peer inside the kernels (2 GPUs, child processes) against
+the all-gather / reduce-scatter path on the same inputs: outputs and dq / dk / dv agree; several calls in a row
+exercise the double-buffered staging slots, the event counters and uneven shard lengths."""
+
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(B, S, seed):
+    g = torch.Generator().manual_seed(seed)
+    text = (1 << 62) | 1 | 2 | 4
+    bits = torch.full((B, S), text, dtype=torch.int64)
+    for b in range(B):
+        a = int(torch.randint(0, S // 2, (1,), generator=g))
+        bits[b, a : a + S // 6] = 2
+        c = int(torch.randint(S // 2, S - S // 6, (1,), generator=g))
+        bits[b, c : c + S // 8] = 4
+    return bits
+
+
+def _worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        from cornstarch_b200.ops import _native as nat
+        from cornstarch_b200.ops import attention as A
+        from cornstarch_b200.parallel import cp as CP
+
+        B, Hq, Hk, D = 2, 8, 2, 128
+        for it, (S, mode, dist_mode) in enumerate([(1024, "causal", "zigzag"), (1536, "bitfield", "makespan_min"),
+                                                   (1200, "bitfield", "uniform"), (2048, "causal", "uniform")]):
+            g = torch.Generator().manual_seed(7 + it)  # same tensors on both ranks; each keeps its shard
+            q_full = torch.randn(B, S, Hq, D, generator=g).cuda().bfloat16()
+            k_full = torch.randn(B, S, Hk, D, generator=g).cuda().bfloat16()
+            v_full = torch.randn(B, S, Hk, D, generator=g).cuda().bfloat16()
+            do_full = torch.randn(B, S, Hq, D, generator=g).cuda().bfloat16()
+            full_mask = A.AttnMask.causal() if mode == "causal" else A.AttnMask.bitfield(_bits(B, S, it).cuda())
+            offsets = CP.ContextParallelBatchSplitUtils.create_context_parallel_split(
+                full_mask if mode != "causal" else None, dist.group.WORLD, dist_mode, seq_len=S, batch=B, device="cuda")
+            assert offsets is not None
+            state = CP.ContextParallelState(dist.group.WORLD, offsets, full_mask, "cuda")
+            mine = state.mine
+            results = {}
+            for fused in (False, True):
+                CP.FUSED_CP_ENABLED = fused
+                state.fused_mask = None
+                qs = q_full[:, mine].clone().requires_grad_()
+                ks = k_full[:, mine].clone().requires_grad_()
+                vs = v_full[:, mine].clone().requires_grad_()
+                for _rep in range(3 if fused else 1):  # repeated calls walk through both staging slots
+                    qs.grad = ks.grad = vs.grad = None
+                    o = CP.context_parallel_attention(qs, ks, vs, state)
+                    o.backward(do_full[:, mine])
+                torch.cuda.synchronize()
+                results[fused] = (o.detach().float(), qs.grad.float(), ks.grad.float(), vs.grad.float())
+            for name, a, b in zip(("o", "dq", "dk", "dv"), results[True], results[False]):
+                err = (a - b).abs().max().item()
+                assert err <= 3e-2 * max(1.0, b.abs().max().item()), (it, name, err)
+            # and against the unsharded reference on this rank's rows
+            ro, _ = A.attention_reference(q_full, k_full, v_full, full_mask)
+            err = (results[True][0] - ro[:, mine].float()).abs().max().item()
+            assert err <= 3e-2, (it, "ref", err)
+        nat.check_status()
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_context_parallel_attention_two_gpus():
+    from tests.dist_utils import free_port
+
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+    results = []
+    while not q.empty():
+        results.append(q.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert len(results) == 2 and all(r[1] == "ok" for r in results), results
