@@ -1,10 +1,12 @@
 """Multi-GPU trainer for ``bench.py``: the modality-parallel pipeline through ``Booster`` / ``MultimodalParallelPlugin``.
 
 Plans per GPU count (``--parallelism auto``): the headline configuration is 8 GPUs = one encoder stage plus
-three LLM stages with tensor parallelism 2 in every stage; smaller counts keep the same pipeline shape:
+three LLM stages with tensor parallelism 2 in every stage:
 
-    2 GPUs: encoder stage + 1 LLM stage,  tp 1          4 GPUs: encoder stage + 3 LLM stages, tp 1
-    8 GPUs: encoder stage + 3 LLM stages, tp 2
+    8 GPUs: encoder stage + 3 LLM stages, tp 2 (the named configuration)
+    2 / 4 GPUs: data parallel (every GPU holds the whole model; gradients reduced by the peer-memory kernel), which is
+    faster there than a pipeline whose encoder stage would leave a GPU almost idle; the pipeline shapes remain
+    available as explicit plans (``enc1+llm1xtp1``, ``enc1+llm3xtp1``).
 
 An explicit plan is written ``enc<E>+llm<L>xtp<T>`` (e.g. ``enc1+llm3xtp2``); remaining ranks become data parallel.
 """

@@ -45,12 +45,14 @@ class SingleDeviceTrainer:
             self.parallelism = f"dp{self.world}"
 
     def make_optimizer(self, lr):
-        return FusedAdamW(split_decay_groups(self.model, 0.01), lr=lr, max_norm=1.0)
+        return FusedAdamW(split_decay_groups(self.model, 0.01), lr=lr, max_norm=1.0, dp_group=self.dp_group)
 
     def data_rank(self) -> int:
         return dist.get_rank(self.dp_group) if self.dp_group is not None else 0
 
     def reduce_grads(self):
+        if self.world > 1 and self.opt.use_arena and self.opt.reduce_dp_grads():
+            return
         if self.world > 1:
             for g in self.opt.flat_grads() if self.opt.use_arena else [p.grad for p in self.model.parameters() if p.grad is not None]:
                 dist.all_reduce(g, op=dist.ReduceOp.SUM if dist.get_backend(self.dp_group) == "gloo" else dist.ReduceOp.AVG,
@@ -158,6 +160,8 @@ def build_trainer(args, rank: int, world: int, local_rank: int):
         return ExpertParallelTrainer(args.shape, args.samples_per_gpu, args.microbatch, device, dist.group.WORLD)
     if plan == "cp" or (plan == "auto" and SHAPES[args.shape].images_per_sample > 1):
         return ContextParallelTrainer(args.shape, args.samples_per_gpu, args.microbatch, device, dist.group.WORLD)
+    if plan == "auto" and world in (2, 4):
+        plan = "dp"
     if plan == "dp":
         return SingleDeviceTrainer(args.shape, args.samples_per_gpu, args.microbatch, device, dp_group=dist.group.WORLD)
     from .bench_parallel import PipelineTrainer

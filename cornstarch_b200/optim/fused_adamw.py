@@ -37,7 +37,8 @@ ALIGN = 64  # elements; keeps every parameter 128-byte aligned inside the arena
 class _Region:
     """One weight-decay group laid out flat."""
 
-    def __init__(self, params: list[torch.nn.Parameter], grad_dtype: torch.dtype, shard: tuple[int, int] | None):
+    def __init__(self, params: list[torch.nn.Parameter], grad_dtype: torch.dtype, shard: tuple[int, int] | None,
+                 grad_alloc=None):
         dev = params[0].device
         self.params = params
         self.offsets = []
@@ -49,7 +50,8 @@ class _Region:
         pad_to = ALIGN * ws
         self.numel = (n + pad_to - 1) // pad_to * pad_to
         self.flat_param = torch.zeros(self.numel, dtype=torch.bfloat16, device=dev)
-        self.flat_grad = torch.zeros(self.numel, dtype=grad_dtype, device=dev)
+        # gradients may live in peer-mapped memory so that the data-parallel reduction kernel can reach them
+        self.flat_grad = grad_alloc(self.numel) if grad_alloc is not None else torch.zeros(self.numel, dtype=grad_dtype, device=dev)
         for p, off in zip(params, self.offsets):
             view = self.flat_param[off : off + p.numel()].view(p.shape)
             view.copy_(p.data)
@@ -72,7 +74,7 @@ class FusedAdamW(torch.optim.Optimizer):
     def __init__(self, params: Iterable, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.01, max_norm: float = 0.0, grad_dtype: torch.dtype = torch.bfloat16,
                  zero_stage: int = 0, dp_group=None, norm_groups: list | None = None, use_arena: bool | None = None,
-                 expert_group=None):
+                 expert_group=None, fused_dp: bool = True):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         self.max_norm = max_norm
@@ -83,6 +85,8 @@ class FusedAdamW(torch.optim.Optimizer):
         # param groups flagged {"expert_parallel": True} hold parameters that are NOT replicated over the data-parallel
         # group (each rank owns different experts): never ZeRO-sharded; their squared norm is summed over expert_group
         self.expert_group = expert_group
+        self.fused_dp = fused_dp  # reduce data-parallel gradients with this package's peer-memory kernel when possible
+        self.reducer = None
         self.loss_scale = 1.0
         self._step = 0
         self._regions: list[tuple[dict, _Region]] = []
@@ -97,10 +101,15 @@ class FusedAdamW(torch.optim.Optimizer):
         shard = None
         if self.zero_stage >= 1 and self.dp_group is not None and dist.get_world_size(self.dp_group) > 1:
             shard = (dist.get_rank(self.dp_group), dist.get_world_size(self.dp_group))
+        if self.fused_dp and self.dp_group is not None and self.grad_dtype == torch.bfloat16:
+            from ..parallel.dp_fused import FusedGradReducer
+
+            self.reducer = FusedGradReducer.get(self.dp_group)
         for g in self.param_groups:
             ps = [p for p in g["params"] if p.requires_grad]
             if ps:
-                region = _Region(ps, self.grad_dtype, None if g.get("expert_parallel") else shard)
+                alloc = self.reducer.allocate if (self.reducer is not None and not g.get("expert_parallel")) else None
+                region = _Region(ps, self.grad_dtype, None if g.get("expert_parallel") else shard, alloc)
                 region.sharded = shard is not None and not g.get("expert_parallel")
                 region.expert = bool(g.get("expert_parallel"))
                 self._regions.append((g, region))
@@ -115,6 +124,21 @@ class FusedAdamW(torch.optim.Optimizer):
     def flat_grads(self) -> list[torch.Tensor]:
         """The flat gradient buffers of replicated parameters (what data-parallel reduction works on)."""
         return [r.flat_grad for _, r in self._regions if not r.expert]
+
+    def reduce_dp_grads(self, bucket_bytes: int = 256 << 20) -> bool:
+        """Average the replicated gradients over the data-parallel group.  Returns False when there is nothing to do
+        here (no group, ZeRO-1 reduces inside ``step``, or the plain per-parameter path is in use)."""
+        if not self.use_arena or self.dp_group is None or dist.get_world_size(self.dp_group) == 1 or self._sharded:
+            return False
+        bufs = self.flat_grads()
+        if self.reducer is not None:
+            self.reducer.reduce(bufs)
+            return True
+        for flat in bufs:
+            step = max(1, bucket_bytes // flat.element_size())
+            for s in range(0, flat.numel(), step):
+                dist.all_reduce(flat[s : s + step], op=dist.ReduceOp.AVG, group=self.dp_group)
+        return True
 
     def flat_params(self) -> list[torch.Tensor]:
         return [r.flat_param for _, r in self._regions]
@@ -137,9 +161,13 @@ class FusedAdamW(torch.optim.Optimizer):
             for _, r in self._regions:
                 if r.expert:
                     r.flat_grad.mul_(1.0 / dist.get_world_size(self.dp_group))
-        if self._sharded:
-            for _, r in self._regions:
-                if r.sharded and not getattr(self, "grads_already_reduced", False):
+        if self._sharded and not getattr(self, "grads_already_reduced", False):
+            todo = [r for _, r in self._regions if r.sharded]
+            if self.reducer is not None and todo:
+                # reduce-scatter by the peer-memory kernel: every rank ends up with the mean of its own slice
+                self.reducer.reduce([r.flat_grad for r in todo], all_reduce=False)
+            else:
+                for r in todo:
                     out = r.flat_grad[r.lo : r.hi]
                     dist.reduce_scatter_tensor(out, r.flat_grad, op=dist.ReduceOp.AVG, group=self.dp_group)
         inv_scale = 1.0 / self.loss_scale

@@ -227,6 +227,8 @@ class HeterogeneousDataLoader(DataLoader):
             "inconsistent global batch size and numbers of micro-batches")
         sampler = HeterogeneousBatchSampler(self._dataset, pipeline_index, self.microbatch_size, num_microbatches,
                                             self._shuffle, self._seed)
+        # (re-)binding after a re-plan: DataLoader refuses attribute changes once initialised
+        object.__setattr__(self, "_DataLoader__initialized", False)
         super().__init__(self._dataset, batch_sampler=sampler, **self._kwargs)
         self._configured = True
 
@@ -374,14 +376,11 @@ class HeterogeneousParallelPlugin:
 
     def execute_pipeline(self, data_iter: Iterator, model: HeterogeneousParallelModule, criterion: Callable, optimizer=None,
                          return_loss: bool = True, return_outputs: bool = False) -> dict:
-        weight = model.loss_weight * len(self.pipelines)  # schedule divides by this pipeline's micro-batch count
-
         def weighted(out, batch):
             return criterion(out, batch) * (model.loss_weight)
 
         # loss per micro-batch / my micro-batches * (my micro-batches / all) = 1 / all micro-batches
         out = self.schedule.forward_backward_step(model, data_iter, weighted, optimizer, return_loss, return_outputs)
-        del weight
         if torch.is_grad_enabled() and optimizer is not None:
             model.sync_shared_params()
             model.sync_dp_grads()

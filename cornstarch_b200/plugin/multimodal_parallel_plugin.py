@@ -151,11 +151,9 @@ class MultimodalParallelModule(nn.Module):
         if isinstance(opt, FusedAdamW) and opt.use_arena:
             if opt._sharded:
                 return  # ZeRO-1: the reduce-scatter happens inside the optimizer step
-            for flat in opt.flat_grads():
-                n = flat.numel()
-                step = max(1, bucket_bytes // flat.element_size())
-                for s in range(0, n, step):
-                    dist.all_reduce(flat[s : s + step], op=dist.ReduceOp.AVG, group=g)
+            if opt.dp_group is None:
+                opt.dp_group = g
+            opt.reduce_dp_grads(bucket_bytes)  # peer-memory kernel when the buffers are peer-mapped, else NCCL buckets
             return
         grads = [p.grad for p in getattr(self.module, self.my_modal_name).parameters() if p.grad is not None]
         ws = dist.get_world_size(g)

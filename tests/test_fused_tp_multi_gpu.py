@@ -126,3 +126,66 @@ def test_tp2_model_fused_matches_nccl():
         if p.is_alive():
             p.terminate()
     assert len(results) == 2 and all(r[1] == "ok" for r in results), results
+
+
+def _grad_reduce_worker(rank, world, port, q):
+    """The peer-memory gradient reduction kernel (all-reduce and reduce-scatter) against a fp32 mean, several rounds."""
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        from cornstarch_b200.ops import _native as nat
+        from cornstarch_b200.parallel.dp_fused import FusedGradReducer
+
+        red = FusedGradReducer.get(dist.group.WORLD)
+        assert red is not None
+        sizes = [1 << 20, 8 * 1000 * world, 64 * world]
+        bufs = [red.allocate(n) for n in sizes]
+        for rnd in range(3):
+            refs = []
+            for i, b in enumerate(bufs):
+                g = torch.Generator().manual_seed(1000 * rnd + 10 * i + rank)
+                b.copy_(torch.randn(b.numel(), generator=g).cuda().bfloat16())
+                ref = b.float().clone()
+                dist.all_reduce(ref)
+                refs.append(ref / world)
+            all_reduce = rnd != 1
+            red.reduce(bufs, all_reduce=all_reduce)
+            torch.cuda.synchronize()
+            for b, ref in zip(bufs, refs):
+                if all_reduce:
+                    lo, hi = 0, b.numel()
+                else:
+                    per = b.numel() // world
+                    lo, hi = rank * per, (rank + 1) * per
+                err = (b.float()[lo:hi] - ref[lo:hi]).abs().max().item()
+                assert err <= 2e-2, (rnd, err)
+            dist.barrier()
+        nat.check_status()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fused_gradient_reduce_two_gpus():
+    from tests.dist_utils import free_port
+
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = free_port()
+    procs = [ctx.Process(target=_grad_reduce_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+    results = []
+    while not q.empty():
+        results.append(q.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert len(results) == 2 and all(r[1] == "ok" for r in results), results
