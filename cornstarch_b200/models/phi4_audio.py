@@ -1,0 +1,229 @@
+"""Phi-4-multimodal audio encoder (conformer blocks) with HF parameter names.
+
+Pipeline units as in the reference's policy (cornstarch/shardformer/policies/phi4_multimodal.py:37-47):
+``encoder_embedding, embed, relative_attention_bias_layer, encoders.i``.  Block structure (patched forward
+cornstarch/shardformer/modeling/phi4_multimodal.py): half-step GLU feed-forward, self-attention with a learned
+relative-position bias per head, a convolution module (point-wise GLU conv, depth-wise separable conv, point-wise
+conv), second half-step feed-forward, final LayerNorm.
+
+Linear layers, LayerNorms and the GLU run on this package's kernels.  The attention adds a dense ``[heads, T, T]``
+bias to the scores, which the flash-attention kernels of this package do not take, so it goes through PyTorch's
+scaled-dot-product attention; the audio sequences are short (T = frames / time_reduction), and the 1-D / 2-D
+convolutions use cuDNN through PyTorch like the other front-ends.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import nn as cnn
+from ..ops import elementwise as E
+from ..ops.linear import multi_linear
+from ..utils.recompute import checkpoint_layer
+from .base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, register_model
+
+
+class Phi4MultimodalAudioConfig(PretrainedConfig):
+    model_type = "phi4_multimodal_audio"
+
+    def __init__(self, hidden_size=1024, intermediate_size=1536, num_blocks=24, num_attention_heads=16, activation="swish",
+                 chunk_size=-1, left_chunk=18, conv_activation="swish", conv_glu_type="swish", depthwise_multiplier=1,
+                 depthwise_separable_out_channel=1024, ext_pw_out_channel=1024, input_size=80, kernel_size=3,
+                 nemo_conv_channels=1024, nemo_final_size=None, time_reduction=8, bias_max_distance=1000, bias_symmetric=False,
+                 nemo_activation="relu", **kw):
+        self.hidden_size, self.intermediate_size, self.num_blocks = hidden_size, intermediate_size, num_blocks
+        self.num_attention_heads, self.activation = num_attention_heads, activation
+        self.conv_activation, self.conv_glu_type, self.depthwise_multiplier = conv_activation, conv_glu_type, depthwise_multiplier
+        self.depthwise_separable_out_channel, self.ext_pw_out_channel = depthwise_separable_out_channel, ext_pw_out_channel
+        self.input_size, self.kernel_size, self.nemo_conv_channels, self.time_reduction = input_size, kernel_size, nemo_conv_channels, time_reduction
+        self.bias_max_distance, self.bias_symmetric, self.nemo_activation = bias_max_distance, bias_symmetric, nemo_activation
+        self.chunk_size, self.left_chunk = chunk_size, left_chunk
+        if nemo_final_size is None:
+            length = input_size
+            for _ in range(int(math.log2(time_reduction))):
+                length = math.floor((length - 1) / 2 + 1)
+            nemo_final_size = length
+        self.nemo_final_size = nemo_final_size
+        kw.pop("depthwise_seperable_out_channel", None)
+        super().__init__(**kw)
+
+    num_hidden_layers = property(lambda self: self.num_blocks)
+
+
+_ACT = {"swish": "silu", "silu": "silu", "relu": "relu", "gelu": "gelu"}
+
+
+class _MeanVarNorm(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.register_buffer("global_mean", torch.zeros(config.input_size))
+        self.register_buffer("global_invstd", torch.ones(config.input_size))
+
+    def forward(self, x):
+        return (x - self.global_mean.to(x.dtype)) * self.global_invstd.to(x.dtype)
+
+
+class _NemoConvSubsampling(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        c = config.nemo_conv_channels
+        act = nn.ReLU() if config.nemo_activation == "relu" else nn.SiLU()
+        layers = [nn.Conv2d(1, c, 3, 2, 1), act]
+        for _ in range(int(math.log2(config.time_reduction)) - 1):
+            layers += [nn.Conv2d(c, c, 3, 2, 1, groups=c), nn.Conv2d(c, c, 1, 1, 0), act]
+        self.conv = nn.Sequential(*layers)
+        self.out = cnn.Linear(c * config.nemo_final_size, config.hidden_size)
+
+    def forward(self, x):
+        h = self.conv(x.unsqueeze(1).to(self.conv[0].weight.dtype))
+        b, _, t, _ = h.shape
+        return self.out(h.transpose(1, 2).reshape(b, t, -1))
+
+
+class _RelativeAttentionBias(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.max_distance, self.symmetric = config.bias_max_distance, config.bias_symmetric
+        self.num_buckets = self.max_distance * (1 if self.symmetric else 2)
+        self.bias_values = nn.Embedding(self.num_buckets, config.num_attention_heads)
+
+    def forward(self, T: int, device):
+        pos = torch.arange(T, device=device)
+        rel = (pos[None, :] - pos[:, None]).clamp(-self.max_distance, self.max_distance - 1)
+        idx = rel.abs() if self.symmetric else rel + self.num_buckets // 2
+        return self.bias_values(idx).permute(2, 0, 1).unsqueeze(0)  # [1, heads, T, T]
+
+
+class _AudioMLP(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.layer_norm = cnn.LayerNorm(config.hidden_size, 1e-5)
+        self.gate_up_proj = cnn.Linear(config.hidden_size, 2 * config.intermediate_size)
+        self.down_proj = cnn.Linear(config.intermediate_size, config.hidden_size)
+        self.act = _ACT[config.activation]
+
+    def forward(self, x):
+        up, gate = self.gate_up_proj(self.layer_norm(x)).chunk(2, dim=-1)  # HF order: value first, gate second
+        return self.down_proj(E.glu(torch.cat([gate, up], dim=-1), self.act))
+
+
+class _AudioAttention(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        H = config.hidden_size
+        self.num_heads, self.head_dim = config.num_attention_heads, H // config.num_attention_heads
+        self.q_proj, self.k_proj, self.v_proj, self.o_proj = cnn.Linear(H, H), cnn.Linear(H, H), cnn.Linear(H, H), cnn.Linear(H, H)
+
+    def forward(self, x, bias):
+        B, T, _ = x.shape
+        W = self.num_heads * self.head_dim
+        qkv = multi_linear(self.q_proj.input_hook(x), [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight],
+                           [self.q_proj.bias, self.k_proj.bias, self.v_proj.bias])
+        q, k, v = (qkv[..., i * W : (i + 1) * W].view(B, T, self.num_heads, self.head_dim).transpose(1, 2) for i in range(3))
+        o = F.scaled_dot_product_attention(q, k, v, attn_mask=bias.to(q.dtype))
+        return self.o_proj(o.transpose(1, 2).reshape(B, T, W))
+
+
+class _GluPointWiseConv(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.out_dim = config.ext_pw_out_channel
+        self.ext_pw_conv_1d = nn.Conv1d(config.hidden_size, 2 * self.out_dim, 1)
+        self.b1 = nn.Parameter(torch.zeros(1, self.out_dim, 1))
+        self.b2 = nn.Parameter(torch.zeros(1, self.out_dim, 1))
+        self.act = _ACT[config.conv_glu_type]
+
+    def forward(self, x):  # [B, T, H] -> [B, T, out]: a 1x1 convolution is a linear layer over channels
+        w = self.ext_pw_conv_1d.weight.squeeze(-1)
+        h = cnn.linear(x, w, self.ext_pw_conv_1d.bias)
+        a = h[..., : self.out_dim] + self.b1.view(1, 1, -1).to(h.dtype)
+        g = h[..., self.out_dim :] + self.b2.view(1, 1, -1).to(h.dtype)
+        return E.glu(torch.cat([g, a], dim=-1), self.act)
+
+
+class _DepthWiseSeparableConv1d(nn.Module):
+    def __init__(self, config, padding):
+        super().__init__()
+        H = config.hidden_size
+        self.dw_conv = nn.Conv1d(H, H * config.depthwise_multiplier, config.kernel_size, 1, padding=padding, groups=H)
+        self.pw_conv = nn.Conv1d(H * config.depthwise_multiplier, config.depthwise_separable_out_channel, 1)
+
+    def forward(self, x):
+        return self.pw_conv(self.dw_conv(x))
+
+
+class _ConvModule(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.kernel_size = config.kernel_size
+        self.layer_norm = cnn.LayerNorm(config.hidden_size, 1e-5)
+        self.glu = _GluPointWiseConv(config)
+        self.dw_sep_conv_1d = _DepthWiseSeparableConv1d(config, padding=config.kernel_size - 1)
+        self.ext_pw_conv_1d = nn.Conv1d(config.hidden_size, config.ext_pw_out_channel, 1)
+        self.act = _ACT[config.conv_activation]
+
+    def forward(self, x):
+        h = self.glu(self.layer_norm(x)).permute(0, 2, 1)
+        h = self.dw_sep_conv_1d(h.to(self.dw_sep_conv_1d.dw_conv.weight.dtype))
+        if self.kernel_size > 1:
+            h = h[:, :, : -(self.kernel_size - 1)]  # causal: drop the look-ahead the symmetric padding added
+        h = E.activation(h.permute(0, 2, 1).contiguous(), self.act)
+        return cnn.linear(h, self.ext_pw_conv_1d.weight.squeeze(-1), self.ext_pw_conv_1d.bias)
+
+
+class Phi4MultimodalAudioConformerEncoderLayer(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.feed_forward_in = _AudioMLP(config)
+        self.self_attn = _AudioAttention(config)
+        self.conv = _ConvModule(config)
+        self.feed_forward_out = _AudioMLP(config)
+        self.layer_norm_att = cnn.LayerNorm(config.hidden_size, 1e-5)
+        self.layer_norm = cnn.LayerNorm(config.hidden_size, 1e-5)
+
+    def forward(self, x, bias):
+        r = x + 0.5 * self.feed_forward_in(x)
+        x = r + self.self_attn(self.layer_norm_att(r), bias)
+        x = x + self.conv(x)
+        x = x + 0.5 * self.feed_forward_out(x)
+        return self.layer_norm(x)
+
+
+class Phi4MultimodalAudioModel(PreTrainedModel):
+    config_class = Phi4MultimodalAudioConfig
+    main_input_name = "audio_input_features"
+
+    def __init__(self, config):
+        super().__init__(config)
+        self.encoder_embedding = _MeanVarNorm(config)
+        self.embed = _NemoConvSubsampling(config)
+        self.relative_attention_bias_layer = _RelativeAttentionBias(config)
+        self.encoders = nn.ModuleList([Phi4MultimodalAudioConformerEncoderLayer(config) for _ in range(config.num_blocks)])
+
+    @classmethod
+    def module_names(cls, config):
+        return ["encoder_embedding", "embed", "relative_attention_bias_layer"] + [f"encoders.{i}" for i in range(config.num_blocks)]
+
+    def forward(self, audio_input_features=None, hidden_states=None, **kw):
+        if hidden_states is None:
+            x = self.embed(self.encoder_embedding(audio_input_features))
+        else:
+            x = hidden_states
+        bias = self.relative_attention_bias_layer(x.shape[1], x.device)
+        for layer in self.encoders:
+            if is_released(layer):
+                continue
+            if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
+                x = checkpoint_layer(layer, x, bias)
+            else:
+                x = layer(x, bias)
+        if is_released(self.encoders[-1]):
+            return ModelOutput(hidden_states=x)
+        return ModelOutput(last_hidden_state=x)
+
+
+register_model("phi4_multimodal_audio", Phi4MultimodalAudioConfig, Phi4MultimodalAudioModel)

@@ -63,6 +63,9 @@ def all_to_all_uneven(x, send_splits: list[int], recv_splits: list[int], group):
     return _AllToAllUneven.apply(x, send_splits, recv_splits, group)
 
 
+FUSED_EP_ENABLED = True  # exchange tokens with this package's peer-memory kernel instead of NCCL all_to_all
+
+
 class ExpertParallel:
     """Attached to a sparse MoE block as ``block.ep``; the block then holds only this rank's experts."""
 
@@ -97,6 +100,9 @@ class ExpertParallel:
         order = torch.argsort(flat_e, stable=True)
         token_of = torch.div(order, k, rounding_mode="floor")
         counts = torch.bincount(flat_e, minlength=self.num_experts)
+        fused = self._fused(x2)
+        if fused is not None:
+            return self._forward_fused(fused, x2, weights, order, token_of, counts, experts, act)
         recv_counts = self.exchange_counts(counts)
         # one host read for both directions' split sizes
         both = torch.cat([counts.view(self.ws, self.local).sum(1), recv_counts.reshape(-1)]).tolist()
@@ -132,6 +138,65 @@ class ExpertParallel:
         out = torch.zeros_like(x2)
         out.index_add_(0, token_of, back)
         return out
+
+
+def _ep_fused_methods():
+    def _fused(self, x2):
+        if not FUSED_EP_ENABLED or not x2.is_cuda or x2.dtype != torch.bfloat16 or x2.shape[1] % 8:
+            return None
+        from .ep_fused import FusedExpertExchange
+
+        return FusedExpertExchange.get(self.group)
+
+    def _forward_fused(self, ex, x2, weights, order, token_of, counts, experts, act):
+        """Same data flow as ``forward`` with both exchanges done by the peer-memory push kernel."""
+        from .ep_fused import fused_all_to_all
+
+        T, H = x2.shape
+        k = order.numel() // T
+        everyone = [torch.empty_like(counts) for _ in range(self.ws)]
+        dist.all_gather(everyone, counts, group=self.group)  # counts[src][expert]: placement of every rank's rows
+        mat = torch.stack(everyone).view(self.ws, self.ws, self.local).tolist()  # [src][dst][local expert]
+        send = [[sum(mat[s][d]) for d in range(self.ws)] for s in range(self.ws)]
+        # every rank may receive at most all (token, k) pairs of the group; sized once from the first call's total
+        total_pairs = sum(sum(r) for r in send)
+        ex.ensure(max(ex.capacity_rows, total_pairs), H)
+        rows = fused_all_to_all(x2, token_of, send, ex)  # gather by token fused into the push
+        me = self.rank
+        rc = [mat[s][me] for s in range(self.ws)]
+        self.last_recv_tokens = rows.shape[0]
+        perm = None
+        if self.local > 1:
+            starts, pos = [], 0
+            for s in range(self.ws):
+                for e in range(self.local):
+                    starts.append(pos)
+                    pos += rc[s][e]
+            perm = torch.cat([torch.arange(starts[s * self.local + e], starts[s * self.local + e] + rc[s][e])
+                              for e in range(self.local) for s in range(self.ws)]).to(rows.device)
+            rows = rows[perm]
+        outs, start = [], 0
+        for e in range(self.local):
+            n = sum(rc[s][e] for s in range(self.ws))
+            outs.append(experts[e](rows[start : start + n], act))
+            start += n
+        y = torch.cat(outs, dim=0) if len(outs) > 1 else outs[0]
+        if perm is not None:
+            inv = torch.empty_like(perm)
+            inv[perm] = torch.arange(perm.numel(), device=perm.device)
+            y = y[inv]
+        rev = [[send[d][s] for d in range(self.ws)] for s in range(self.ws)]
+        back = fused_all_to_all(y, None, rev, ex)
+        back = back * weights.reshape(-1)[order].unsqueeze(-1).to(back.dtype)
+        out = torch.zeros_like(x2)
+        out.index_add_(0, token_of, back)
+        return out
+
+    ExpertParallel._fused = _fused
+    ExpertParallel._forward_fused = _forward_fused
+
+
+_ep_fused_methods()
 
 
 def shard_experts(model, group) -> list[torch.nn.Parameter]:

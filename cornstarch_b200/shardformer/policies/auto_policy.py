@@ -24,6 +24,9 @@ _NATIVE = {
     "cornstarch_b200.models.vision_extra.InternVisionModel": P.InternVisionModelPolicy,
     "cornstarch_b200.models.vision_extra.PixtralVisionModel": P.PixtralVisionModelPolicy,
     "cornstarch_b200.models.vision_extra.Qwen2VisionTransformerPretrainedModel": P.Qwen2VisionTransformerPolicy,
+    "cornstarch_b200.models.llama4.Llama4TextModel": P.Llama4TextModelPolicy,
+    "cornstarch_b200.models.llama4.Llama4ForCausalLM": P.Llama4ForCausalLMPolicy,
+    "cornstarch_b200.models.phi4_audio.Phi4MultimodalAudioModel": P.Phi4MultimodalAudioModelPolicy,
     "cornstarch_b200.models.text_legacy.GPT2Model": P.GPT2ModelPolicy,
     "cornstarch_b200.models.text_legacy.GPT2LMHeadModel": P.GPT2LMHeadModelPolicy,
     "cornstarch_b200.models.text_legacy.BertModel": P.BertModelPolicy,
@@ -60,6 +63,9 @@ _HF_ALIASES.update({
     "cornstarch.models.intern_vit.modeling_intern_vit.InternVisionModel": P.InternVisionModelPolicy,
     "transformers.models.pixtral.modeling_pixtral.PixtralVisionModel": P.PixtralVisionModelPolicy,
     "transformers.models.qwen2_vl.modeling_qwen2_vl.Qwen2VisionTransformerPretrainedModel": P.Qwen2VisionTransformerPolicy,
+    "transformers.models.llama4.modeling_llama4.Llama4TextModel": P.Llama4TextModelPolicy,
+    "transformers.models.llama4.modeling_llama4.Llama4ForCausalLM": P.Llama4ForCausalLMPolicy,
+    "transformers.models.phi4_multimodal.modeling_phi4_multimodal.Phi4MultimodalAudioModel": P.Phi4MultimodalAudioModelPolicy,
     "transformers.models.gpt2.modeling_gpt2.GPT2Model": P.GPT2ModelPolicy,
     "transformers.models.gpt2.modeling_gpt2.GPT2LMHeadModel": P.GPT2LMHeadModelPolicy,
     "transformers.models.bert.modeling_bert.BertModel": P.BertModelPolicy,

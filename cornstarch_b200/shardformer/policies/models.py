@@ -9,6 +9,8 @@ policies/vit.py:31-39, policies/whisper.py:36-47, policies/multimodal.py:33-44.
 from __future__ import annotations
 
 from ...models import llama as L
+from ...models import llama4 as L4
+from ...models import phi4_audio as PA
 from ...models import text_legacy as T
 from ...models import vision_extra as X
 from ...models import moe as M
@@ -299,3 +301,48 @@ class OPTForCausalLMPolicy(OPTModelPolicy):
     model_cls = T.OPTForCausalLM
     first_stage_modules = ["model.decoder.embed_tokens", "model.decoder.embed_positions", "model.decoder.project_in"]
     last_stage_modules = ["model.decoder.final_layer_norm", "model.decoder.project_out", "lm_head"]
+
+
+_L4_LAYER = r"(model\.)?layers\.\d+\."
+
+
+class Llama4TextModelPolicy(ModelPolicy):
+    """Attention and the shared expert / dense MLP are tensor parallel; the stacked routed experts stay replicated
+    (cornstarch/shardformer/policies/llama4.py:188-218 shards attention + shared_expert the same way)."""
+
+    model_cls = L4.Llama4TextModel
+    first_stage_modules = ["embed_tokens", "rotary_emb"]
+    last_stage_modules = ["norm"]
+    supported_sp_modes = ()
+    head_modules = _L4_LAYER + r"self_attn"
+    tp_rules = [
+        TPRule(_L4_LAYER + r"self_attn\.(q_proj|k_proj|v_proj)", "col"),
+        TPRule(_L4_LAYER + r"self_attn\.o_proj", "row"),
+        TPRule(_L4_LAYER + r"feed_forward\.(shared_expert\.)?(gate_proj|up_proj)", "col"),
+        TPRule(_L4_LAYER + r"feed_forward\.(shared_expert\.)?down_proj", "row"),
+        TPRule(r"(model\.)?embed_tokens", "vocab"),
+        TPRule(r"lm_head", "lm_head"),
+    ]
+
+
+class Llama4ForCausalLMPolicy(Llama4TextModelPolicy):
+    model_cls = L4.Llama4ForCausalLM
+    first_stage_modules = ["model.embed_tokens", "model.rotary_emb"]
+    last_stage_modules = ["model.norm", "lm_head"]
+
+
+class Phi4MultimodalAudioModelPolicy(ModelPolicy):
+    model_cls = PA.Phi4MultimodalAudioModel
+    first_stage_modules = ["encoder_embedding", "embed", "relative_attention_bias_layer"]
+    last_stage_modules = []
+    head_modules = r"encoders\.\d+\.self_attn"
+    tp_rules = [
+        TPRule(r"encoders\.\d+\.self_attn\.(q_proj|k_proj|v_proj)", "col"),
+        TPRule(r"encoders\.\d+\.self_attn\.o_proj", "row"),
+    ]
+
+    def config_sanity_check(self):
+        super().config_sanity_check()
+        sc = self.shard_config
+        if sc is not None and sc.tensor_parallel_size > 1:
+            raise ValueError("the relative attention bias is indexed by global head: tensor parallelism is not supported for this encoder")

@@ -6,7 +6,8 @@
 ``moe``       SigLIP-so400m-shaped encoder + Mixtral-8x7B-shaped LLM, sequence 4096.
 ``vlm_small`` a 4-layer cut of ``vlm`` (same layer shapes) for smoke tests and profiler captures.
 ``long``      ``vlm`` at sequence 65536 with 8 images per sample at random positions (context parallelism).
-``long_tiny`` / ``moe_tiny``  CPU-sized versions of ``long`` and ``moe`` for the gloo tests.
+``long_tiny`` / ``moe_tiny``  CPU-sized versions of ``long`` and ``moe`` for the gloo tests;
+``long_small`` / ``moe_small``  4-layer cuts at the real layer shapes for multi-GPU smoke runs.
 
 Weights are random-initialised; data is synthetic (pixels ~ N(0,1), token ids uniform), as there is no
 network access for datasets or checkpoints.
@@ -66,6 +67,11 @@ SHAPES = {
                   vocab=128256, llm=LLAMA31_8B, vision=SIGLIP_SO400M, audio=WHISPER_LARGE_V3),
     "long": Shape("long", seq_len=65536, image_tokens=729, image_size=384, vocab=128256, images_per_sample=8,
                   llm={**LLAMA31_8B, "max_position_embeddings": 65536}, vision=SIGLIP_SO400M),
+    "long_small": Shape("long_small", seq_len=16384, image_tokens=729, image_size=384, vocab=128256, images_per_sample=8,
+                        llm={**LLAMA31_8B, "num_hidden_layers": 4, "max_position_embeddings": 16384},
+                        vision={**SIGLIP_SO400M, "num_hidden_layers": 3}),
+    "moe_small": Shape("moe_small", seq_len=4096, image_tokens=729, image_size=384, vocab=32000, moe=True,
+                       llm={**MIXTRAL_8X7B, "num_hidden_layers": 4}, vision={**SIGLIP_SO400M, "num_hidden_layers": 3}),
     "long_tiny": Shape("long_tiny", seq_len=1024, image_tokens=16, image_size=56, vocab=1000, images_per_sample=4,
                        llm=dict(vocab_size=1000, hidden_size=128, intermediate_size=352, num_hidden_layers=2,
                                 num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=1024),

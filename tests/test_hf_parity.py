@@ -17,7 +17,7 @@ DEC = dict(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_lay
            max_position_embeddings=128)
 
 
-@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "gemma", "phi3", "mixtral", "qwen3_moe"])
+@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "phi3", "mixtral", "qwen3_moe"])
 def test_decoder_families_match_hf(family):
     from cornstarch_b200.models import llama as L
     from cornstarch_b200.models import moe as M
@@ -38,6 +38,18 @@ def test_decoder_families_match_hf(family):
         kw["head_dim"] = 16
         hf_cfg = tf.GemmaConfig(**kw, hidden_activation="gelu_pytorch_tanh")
         cfg, cls, hf_cls = L.GemmaConfig(**kw), L.DecoderForCausalLM, tf.GemmaForCausalLM
+    elif family == "gemma2":
+        # attention soft-capping and the sliding window are not applied (as in the reference's bitfield attention adapter,
+        # cornstarch/kernel/interface.py:56-67): switched off on the HF side for the comparison
+        kw["head_dim"] = 16
+        extra = dict(query_pre_attn_scalar=16, final_logit_softcapping=30.0)
+        hf_cfg = tf.Gemma2Config(**kw, **extra, attn_logit_softcapping=None, sliding_window=4096)
+        cfg, cls, hf_cls = L.Gemma2Config(**kw, **extra), L.DecoderForCausalLM, tf.Gemma2ForCausalLM
+    elif family == "gemma3":
+        kw["head_dim"] = 16
+        extra = dict(query_pre_attn_scalar=16, rope_local_base_freq=10000.0)
+        hf_cfg = tf.Gemma3TextConfig(**kw, **extra, sliding_window=4096)
+        cfg, cls, hf_cls = L.Gemma3TextConfig(**kw, **extra, layer_types=list(hf_cfg.layer_types)), L.DecoderForCausalLM, tf.Gemma3ForCausalLM
     elif family == "phi3":
         hf_cfg, cfg, cls, hf_cls = tf.Phi3Config(**kw, pad_token_id=0), L.Phi3Config(**kw), L.DecoderForCausalLM, tf.Phi3ForCausalLM
     elif family == "mixtral":

@@ -89,3 +89,27 @@ def test_recompute_keeps_gradients():
     m(input_ids=ids, labels=ids).loss.backward()
     for n, p in m.named_parameters():
         assert torch.allclose(p.grad, ref[n], atol=1e-6), n
+
+
+def test_llama4_text_matches_hf():
+    from transformers import Llama4TextConfig as HC
+    from transformers.models.llama4.modeling_llama4 import Llama4ForCausalLM as HM
+
+    from cornstarch_b200.models.llama4 import Llama4ForCausalLM, Llama4TextConfig
+
+    kw = dict(vocab_size=100, hidden_size=32, intermediate_size=48, intermediate_size_mlp=64, num_hidden_layers=4,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=8, num_local_experts=4, num_experts_per_tok=1,
+              interleave_moe_layer_step=2, max_position_embeddings=64, attention_chunk_size=64)
+    torch.manual_seed(0)
+    hfc = HC(**kw)
+    hfc._attn_implementation = "eager"
+    hf = HM(hfc).eval()
+    ours = Llama4ForCausalLM(Llama4TextConfig(**kw, rope_theta=hfc.rope_parameters["rope_theta"] if getattr(hfc, "rope_parameters", None) else 500000.0)).eval()
+    _load(ours, hf)
+    ids = torch.randint(0, 100, (2, 24))
+    want = hf(input_ids=ids, labels=ids)
+    got = ours(input_ids=ids, labels=ids)
+    assert torch.allclose(got.loss, want.loss, atol=1e-4), (got.loss, want.loss)
+    assert torch.allclose(ours(input_ids=ids).logits, want.logits, atol=2e-3)
+    assert Llama4ForCausalLM.module_names(ours.config)[:3] == ["model.embed_tokens", "model.rotary_emb", "model.layers.0"]
+    assert ours.config.moe_layers == [1, 3] and ours.config.no_rope_layers == [1, 1, 1, 0]

@@ -123,3 +123,25 @@ def test_evaclip_block_math(post):
     x = x + (n2(mm) if post else mm)
     assert torch.allclose(out.last_hidden_state, x, atol=1e-5)
     assert EvaCLIPVisionModel.module_names(cfg) == ["vision_model.embeddings", "vision_model.encoder.layers.0", "vision_model.post_layernorm"]
+
+
+def test_phi4_audio_matches_hf():
+    from transformers.models.phi4_multimodal.configuration_phi4_multimodal import Phi4MultimodalAudioConfig as HC
+    from transformers.models.phi4_multimodal.modeling_phi4_multimodal import Phi4MultimodalAudioModel as HM
+
+    from cornstarch_b200.models.phi4_audio import Phi4MultimodalAudioConfig, Phi4MultimodalAudioModel
+
+    kw = dict(hidden_size=32, intermediate_size=48, num_blocks=2, num_attention_heads=4, input_size=16, nemo_conv_channels=32,
+              ext_pw_out_channel=32, kernel_size=3, time_reduction=8)
+    torch.manual_seed(0)
+    hf = HM(HC(depthwise_separable_out_channel=32, **kw)).eval()
+    ours = Phi4MultimodalAudioModel(Phi4MultimodalAudioConfig(depthwise_separable_out_channel=32, **kw)).eval()
+    _load(ours, hf.state_dict())
+    x = torch.randn(2, 64, 16)
+    want = hf(x, mask=None)
+    want = want if isinstance(want, torch.Tensor) else want[0]
+    got = ours(audio_input_features=x).last_hidden_state
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert torch.allclose(got, want, atol=1e-4), (got - want).abs().max()
+    assert Phi4MultimodalAudioModel.module_names(ours.config) == ["encoder_embedding", "embed", "relative_attention_bias_layer",
+                                                                    "encoders.0", "encoders.1"]
