@@ -230,6 +230,14 @@ class MultimodalModel(nn.Module):
         self.mask_mode = mask_mode
         self.check_counts = False
 
+    @classmethod
+    def from_pretrained_multimodal_model(cls, pretrained_model_path: str, dtype=None, device=None) -> "MultimodalModel":
+        """Cut a composite HF checkpoint directory (``llava_next``, ``qwen2_vl``) into encoder, projector and LLM
+        (cornstarch/models/multimodal_language_model/modeling_multimodal_language_model.py:752-772)."""
+        from .adapters import from_pretrained_multimodal_model
+
+        return from_pretrained_multimodal_model(pretrained_model_path, dtype=dtype, device=device)
+
     # ------------------------------------------------------------------ structure helpers
     @property
     def encoders(self) -> dict[str, ModalEncoderModule]:
