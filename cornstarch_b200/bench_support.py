@@ -45,6 +45,10 @@ class SingleDeviceTrainer:
             self.parallelism = f"dp{self.world}"
 
     def make_optimizer(self, lr):
+        from .ops import _native as nat
+
+        if nat.LIBRARY_MODE:
+            return _TorchAdamW(self.model, lr)
         return FusedAdamW(split_decay_groups(self.model, 0.01), lr=lr, max_norm=1.0, dp_group=self.dp_group)
 
     def data_rank(self) -> int:
@@ -78,6 +82,26 @@ class SingleDeviceTrainer:
     def step_e2e(self) -> float:
         batches = [{k: v.to(self.device, non_blocking=True) for k, v in b.items()} for b in self.host]
         return float(self._run(batches).item())
+
+
+class _TorchAdamW(torch.optim.AdamW):
+    """Library baseline optimizer: ``torch.optim.AdamW(fused=True)`` with global-norm clipping, no flat arena."""
+
+    use_arena = False
+
+    def __init__(self, model, lr):
+        self._params = [p for p in model.parameters() if p.requires_grad]
+        super().__init__(split_decay_groups(model, 0.01), lr=lr, fused=True)
+
+    def step(self, closure=None):
+        torch.nn.utils.clip_grad_norm_(self._params, 1.0)
+        return super().step(closure)
+
+    def reduce_dp_grads(self):
+        return False
+
+    def flat_grads(self):
+        return [p.grad for p in self._params if p.grad is not None]
 
 
 class ExpertParallelTrainer(SingleDeviceTrainer):

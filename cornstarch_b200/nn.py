@@ -20,6 +20,8 @@ import torch.distributed as dist
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .ops import _native as nat
+
 from .ops import elementwise as E
 from .ops.linear import linear, multi_linear
 from .parallel import comm
@@ -156,7 +158,7 @@ FUSED_TP_ENABLED = True
 
 def _fused_tp(group, x):
     """The fused GEMM + all-reduce context of ``group`` for bf16 CUDA inputs (``None`` = use NCCL collectives)."""
-    if not FUSED_TP_ENABLED or group is None or not x.is_cuda or x.dtype != torch.bfloat16:
+    if not FUSED_TP_ENABLED or nat.LIBRARY_MODE or group is None or not x.is_cuda or x.dtype != torch.bfloat16:
         return None
     from .parallel.symm import FusedTensorParallel
 
@@ -198,7 +200,7 @@ class Embedding(nn.Module):
         if src is not None:
             out = E.embed_merge(self.weight, src.reshape(-1), feats)
             return out.view(*ids.shape, self.embedding_dim)
-        if self.weight.is_cuda and self.weight.dtype == torch.bfloat16:
+        if self.weight.is_cuda and self.weight.dtype == torch.bfloat16 and not nat.LIBRARY_MODE:
             out = E.embed_merge(self.weight, ids.reshape(-1).int(), None)
             return out.view(*ids.shape, self.embedding_dim)
         return F.embedding(ids, self.weight)

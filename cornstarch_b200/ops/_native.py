@@ -14,6 +14,9 @@ from pathlib import Path
 
 import torch
 
+# Library baseline: route every op to PyTorch / cuBLAS / cuDNN instead of this package's kernels (what the reference's
+# call sites use); selected with CORNSTARCH_B200_LIBRARY_OPS=1 (bench.py --impl baseline) for same-box comparisons.
+LIBRARY_MODE = os.environ.get("CORNSTARCH_B200_LIBRARY_OPS", "0") == "1"
 _LIB = None
 _LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libcornstarch_b200.so"
 
@@ -88,15 +91,39 @@ class _CountingLib:
             if name in self._NO_LAUNCH:
                 fn = target
             else:
-                def fn(*a, _t=target):
-                    global launch_count
-                    launch_count += 1
-                    return _t(*a)
+                if KERNEL_TIMES:
+                    def fn(*a, _t=target, _n=name):
+                        global launch_count
+                        launch_count += 1
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                        r = _t(*a)
+                        e1.record()
+                        _TIMES.setdefault(_n, []).append((e0, e1))
+                        return r
+                else:
+                    def fn(*a, _t=target):
+                        global launch_count
+                        launch_count += 1
+                        return _t(*a)
             self._cache[name] = fn
         return fn
 
 
 launch_count = 0
+# CORNSTARCH_B200_KERNEL_TIMES=1: bracket every native call with a CUDA event pair on the launching stream and sum the
+# device time per entry point (kernel_times()); a few microseconds of host time per call, for in-situ breakdowns.
+KERNEL_TIMES = os.environ.get("CORNSTARCH_B200_KERNEL_TIMES", "0") == "1"
+_TIMES: dict = {}
+
+
+def kernel_times(reset: bool = True) -> dict:
+    """``{entry point: (calls, total ms)}`` since the last reset (synchronises the device)."""
+    torch.cuda.synchronize()
+    out = {k: (len(v), sum(a.elapsed_time(b) for a, b in v)) for k, v in _TIMES.items()}
+    if reset:
+        _TIMES.clear()
+    return out
 
 
 def declare(name: str, argtypes: list) -> None:

@@ -23,6 +23,7 @@ from dataclasses import dataclass, field
 import threading
 
 import torch
+import torch.nn.functional as F
 
 from . import _native as nat
 
@@ -278,9 +279,33 @@ class attention_tape:
         return False
 
 
+def attention_library(q, k, v, mask: AttnMask, scale=None) -> torch.Tensor:
+    """PyTorch scaled-dot-product attention (flash / cuDNN / memory-efficient kernels): the library baseline.  Causal and
+    full masks without explicit positions use the fused flags; everything else gets a dense boolean mask."""
+    B, Sq = q.shape[:2]
+    Sk = k.shape[1]
+    qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    gqa = q.shape[2] != k.shape[2]
+    plain = mask.q_pos is None and mask.k_pos is None
+    if mask.mode == MASK_CAUSAL and plain and Sq == Sk:
+        o = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, scale=scale, enable_gqa=gqa)
+    elif mask.mode == MASK_FULL:
+        o = F.scaled_dot_product_attention(qh, kh, vh, scale=scale, enable_gqa=gqa)
+    else:
+        cache = mask._cls.get(("dense", B, Sq, Sk))
+        if cache is None:
+            cache = dense_mask(mask, B, Sq, Sk, q.device)[:, None]
+            mask._cls[("dense", B, Sq, Sk)] = cache
+        o = F.scaled_dot_product_attention(qh, kh, vh, attn_mask=cache, scale=scale, enable_gqa=gqa)
+        o = torch.nan_to_num(o)  # fully masked (padding) rows
+    return o.transpose(1, 2)
+
+
 def attention(q, k, v, mask: AttnMask | None = None, scale: float | None = None) -> torch.Tensor:
     """``softmax(scale q k^T + mask) v`` for ``[B, S, H, D]`` tensors (GQA when ``Hq > Hk``)."""
     mask = mask or AttnMask.causal()
+    if nat.LIBRARY_MODE and q.is_cuda:
+        return attention_library(q, k, v, mask, scale)
     if q.is_cuda and q.dtype == torch.bfloat16:
         tape = getattr(_TAPE, "cur", None)
         if tape is not None and tape.mode == "record" and not torch.is_grad_enabled():

@@ -123,7 +123,7 @@ def linear_cross_entropy(hidden, weight, labels, ignore_index: int = -100, chunk
     h2 = hidden.reshape(-1, H)
     lab = labels.reshape(-1)
     n_valid = (lab != ignore_index).sum()
-    if hidden.is_cuda and hidden.dtype == torch.bfloat16 and weight.shape[0] % 8 == 0:
+    if hidden.is_cuda and hidden.dtype == torch.bfloat16 and weight.shape[0] % 8 == 0 and not nat.LIBRARY_MODE:
         h2 = h2 if h2.is_contiguous() else h2.contiguous()
         loss_sum = _LinearCEFn.apply(h2, weight, lab, ignore_index, chunk, tp_group, vocab_start)
     else:

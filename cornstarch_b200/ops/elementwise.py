@@ -24,11 +24,16 @@ from . import _native as nat
 
 
 def _native_ok(x: torch.Tensor) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16
+    return x.is_cuda and x.dtype == torch.bfloat16 and not nat.LIBRARY_MODE
 
 
 # --------------------------------------------------------------------------------------- norms
 def _norm_ref(x, w, b, eps, is_ln, w_offset):
+    if nat.LIBRARY_MODE and x.is_cuda:
+        wt = w if not w_offset else (w.float() + w_offset).to(w.dtype)
+        if is_ln:
+            return F.layer_norm(x, (x.shape[-1],), wt, b, eps)
+        return F.rms_norm(x, (x.shape[-1],), wt, eps)
     xf = x.float()
     if is_ln:
         mean = xf.mean(-1, keepdim=True)

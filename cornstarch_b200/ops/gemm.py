@@ -47,6 +47,23 @@ def gemm_reference(a, b, a_mn_major=False, b_mn_major=False, bias=None, act=None
     return y.to(out_dtype or a.dtype)
 
 
+def gemm_library(a, b, a_mn_major=False, b_mn_major=False, bias=None, act=None, out=None, accumulate=False, out_dtype=None):
+    """The same contract on cuBLAS (``torch.matmul`` in the operands' dtype): the library baseline."""
+    A = a.t() if a_mn_major else a
+    B = b if b_mn_major else b.t()
+    y = torch.matmul(A, B)
+    if bias is not None:
+        y = y + bias
+    y = _ref_act(y, act)
+    if out is not None:
+        if accumulate:
+            out.add_(y.to(out.dtype))
+        else:
+            out.copy_(y)
+        return out
+    return y.to(out_dtype or a.dtype)
+
+
 def gemm(
     a: torch.Tensor,
     b: torch.Tensor,
@@ -63,6 +80,8 @@ def gemm(
     """``out (+)= act(op(a) @ op(b).T + bias)``; 2-D row-major operands whose row stride may exceed the width."""
     if not a.is_cuda:
         return gemm_reference(a, b, a_mn_major, b_mn_major, bias, act, out, accumulate, out_dtype)
+    if nat.LIBRARY_MODE:
+        return gemm_library(a, b, a_mn_major, b_mn_major, bias, act, out, accumulate, out_dtype)
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "native GEMM is bf16 x bf16 -> fp32 accumulate"
     assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
     if a_mn_major:

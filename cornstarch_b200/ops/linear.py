@@ -26,7 +26,7 @@ from .gemm import gemm
 
 
 def _use_native(x: torch.Tensor) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16
+    return x.is_cuda and x.dtype == torch.bfloat16 and not nat.LIBRARY_MODE
 
 
 def _as_2d(x: torch.Tensor) -> torch.Tensor:

@@ -176,7 +176,9 @@ FUSED_CP_ENABLED = True  # stream K/V tiles from the peers inside the attention 
 
 
 def _fused_for(state: "ContextParallelState", q):
-    if not FUSED_CP_ENABLED or state.sizes is None or not q.is_cuda or q.dtype != torch.bfloat16:
+    from ..ops import _native as nat
+
+    if nat.LIBRARY_MODE or not FUSED_CP_ENABLED or state.sizes is None or not q.is_cuda or q.dtype != torch.bfloat16:
         return None
     from .cp_fused import FusedContextParallelAttention
 

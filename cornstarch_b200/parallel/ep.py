@@ -142,7 +142,9 @@ class ExpertParallel:
 
 def _ep_fused_methods():
     def _fused(self, x2):
-        if not FUSED_EP_ENABLED or not x2.is_cuda or x2.dtype != torch.bfloat16 or x2.shape[1] % 8:
+        from ..ops import _native as nat
+
+        if nat.LIBRARY_MODE or not FUSED_EP_ENABLED or not x2.is_cuda or x2.dtype != torch.bfloat16 or x2.shape[1] % 8:
             return None
         from .ep_fused import FusedExpertExchange
 
