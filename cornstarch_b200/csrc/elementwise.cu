@@ -165,46 +165,68 @@ __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_b
 // One pass over a flat shard: fp32 master/exp_avg/exp_avg_sq, bf16 (or fp32) grads, bf16 params.
 // grad_scale (device scalar, optional) carries 1/loss_scale * clip factor; `skip` (device int,
 // optional) non-zero turns the whole update into a no-op (inf/nan step under dynamic loss scaling).
+constexpr int ADAMW_UNROLL = 4;
 template <typename GradT>
-__global__ void adamw_kernel(__nv_bfloat16* __restrict__ param, float* __restrict__ master, float* __restrict__ m,
-                             float* __restrict__ v, GradT* __restrict__ grad, long n, float lr, float b1, float b2,
-                             float eps, float wd, float bc1, float bc2, const float* __restrict__ grad_scale,
-                             const int* __restrict__ skip, int zero_grad) {
+__global__ void __launch_bounds__(256)
+adamw_kernel(__nv_bfloat16* __restrict__ param, float* __restrict__ master, float* __restrict__ m,
+             float* __restrict__ v, GradT* __restrict__ grad, long n, float lr, float b1, float b2,
+             float eps, float wd, float bc1, float bc2, const float* __restrict__ grad_scale,
+             const int* __restrict__ skip, int zero_grad) {
   if (skip && *skip) return;
   const float gs = grad_scale ? *grad_scale : 1.f;
+  const float inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2, decay = 1.f - lr * wd;
   const long n4 = n / 4;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
-    float4 w = reinterpret_cast<float4*>(master)[i];
-    float4 mm = reinterpret_cast<float4*>(m)[i];
-    float4 vv = reinterpret_cast<float4*>(v)[i];
-    float g[4];
-    if constexpr (sizeof(GradT) == 4) {
-      float4 gg = reinterpret_cast<float4*>(grad)[i];
-      g[0] = gg.x; g[1] = gg.y; g[2] = gg.z; g[3] = gg.w;
-      if (zero_grad) reinterpret_cast<float4*>(grad)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-    } else {
-      uint2 gg = reinterpret_cast<uint2*>(grad)[i];
-      float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&gg.x));
-      float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&gg.y));
-      g[0] = a.x; g[1] = a.y; g[2] = b.x; g[3] = b.y;
-      if (zero_grad) reinterpret_cast<uint2*>(grad)[i] = make_uint2(0u, 0u);
-    }
-    float wv[4] = {w.x, w.y, w.z, w.w}, mv[4] = {mm.x, mm.y, mm.z, mm.w}, sv[4] = {vv.x, vv.y, vv.z, vv.w};
+  // A CTA works on ADAMW_UNROLL consecutive chunks of blockDim vectors per pass; all loads of a pass are issued before the
+  // first use, which is what keeps enough bytes in flight (one vector per thread left HBM at a third of its bandwidth).
+  // Every element is read once and written once: streaming (evict-first) accesses keep the L2 out of the way.
+  const long pass = (long)blockDim.x * ADAMW_UNROLL;
+  for (long base = blockIdx.x * pass; base < n4; base += (long)gridDim.x * pass) {
+    float4 w[ADAMW_UNROLL], mm[ADAMW_UNROLL], vv[ADAMW_UNROLL];
+    float g[ADAMW_UNROLL][4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float gj = g[j] * gs;
-      mv[j] = b1 * mv[j] + (1.f - b1) * gj;
-      sv[j] = b2 * sv[j] + (1.f - b2) * gj * gj;
-      const float denom = sqrtf(sv[j] / bc2) + eps;
-      wv[j] = wv[j] * (1.f - lr * wd) - lr * (mv[j] / bc1) / denom;
+    for (int u = 0; u < ADAMW_UNROLL; ++u) {
+      const long i = base + u * blockDim.x + threadIdx.x;
+      if (i < n4) {
+        w[u] = __ldcs(reinterpret_cast<const float4*>(master) + i);
+        mm[u] = __ldcs(reinterpret_cast<const float4*>(m) + i);
+        vv[u] = __ldcs(reinterpret_cast<const float4*>(v) + i);
+        if constexpr (sizeof(GradT) == 4) {
+          const float4 gg = __ldcs(reinterpret_cast<const float4*>(grad) + i);
+          g[u][0] = gg.x; g[u][1] = gg.y; g[u][2] = gg.z; g[u][3] = gg.w;
+        } else {
+          uint2 gg = __ldcs(reinterpret_cast<const uint2*>(grad) + i);
+          const float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&gg.x));
+          const float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&gg.y));
+          g[u][0] = a.x; g[u][1] = a.y; g[u][2] = b.x; g[u][3] = b.y;
+        }
+      }
     }
-    reinterpret_cast<float4*>(master)[i] = make_float4(wv[0], wv[1], wv[2], wv[3]);
-    reinterpret_cast<float4*>(m)[i] = make_float4(mv[0], mv[1], mv[2], mv[3]);
-    reinterpret_cast<float4*>(v)[i] = make_float4(sv[0], sv[1], sv[2], sv[3]);
-    uint2 o;
-    o.x = pack_bf16x2(wv[0], wv[1]);
-    o.y = pack_bf16x2(wv[2], wv[3]);
-    reinterpret_cast<uint2*>(param)[i] = o;
+#pragma unroll
+    for (int u = 0; u < ADAMW_UNROLL; ++u) {
+      const long i = base + u * blockDim.x + threadIdx.x;
+      if (i >= n4) continue;
+      float wv[4] = {w[u].x, w[u].y, w[u].z, w[u].w}, mv[4] = {mm[u].x, mm[u].y, mm[u].z, mm[u].w};
+      float sv[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float gj = g[u][j] * gs;
+        mv[j] = b1 * mv[j] + (1.f - b1) * gj;
+        sv[j] = b2 * sv[j] + (1.f - b2) * gj * gj;
+        const float denom = sqrtf(sv[j] * inv_bc2) + eps;
+        wv[j] = wv[j] * decay - lr * (mv[j] * inv_bc1) / denom;
+      }
+      __stcs(reinterpret_cast<float4*>(master) + i, make_float4(wv[0], wv[1], wv[2], wv[3]));
+      __stcs(reinterpret_cast<float4*>(m) + i, make_float4(mv[0], mv[1], mv[2], mv[3]));
+      __stcs(reinterpret_cast<float4*>(v) + i, make_float4(sv[0], sv[1], sv[2], sv[3]));
+      uint2 o;
+      o.x = pack_bf16x2(wv[0], wv[1]);
+      o.y = pack_bf16x2(wv[2], wv[3]);
+      reinterpret_cast<uint2*>(param)[i] = o;
+      if (zero_grad) {
+        if constexpr (sizeof(GradT) == 4) __stcs(reinterpret_cast<float4*>(grad) + i, make_float4(0.f, 0.f, 0.f, 0.f));
+        else __stcs(reinterpret_cast<uint2*>(grad) + i, make_uint2(0u, 0u));
+      }
+    }
   }
 }
 
@@ -464,7 +486,7 @@ CSB_API int csb_adamw(void* param, float* master, float* m, float* v, void* grad
                       const int* skip, int zero_grad, void* stream) {
   if (n % 4) return CSB_ERR_BAD_ARG;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = ew_grid(n / 4, 256);
+  const int grid = ew_grid(n / 4 / ADAMW_UNROLL + 1, 256);
   if (grad_fp32)
     adamw_kernel<float><<<grid, 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(param), master, m, v,
                                              reinterpret_cast<float*>(grad), n, lr, b1, b2, eps, wd, bc1, bc2,

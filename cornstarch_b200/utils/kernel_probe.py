@@ -123,6 +123,18 @@ def probe_elementwise(a, flush):
     report("swiglu_fwd", ms, bytes_=3 * T * I * 2)
 
 
+def probe_adamw(a, flush):
+    """Fused AdamW over a flat arena of ``--m * 1e6`` bf16 parameters (fp32 master + two moments, bf16 gradients)."""
+    from ..optim.fused_adamw import FusedAdamW
+
+    n = int(a.m) * 1_000_000
+    p = torch.nn.Parameter(torch.randn(n, device="cuda").bfloat16())
+    opt = FusedAdamW([{"params": [p], "weight_decay": 0.01}], lr=1e-4)
+    p.main_grad.normal_()
+    ms = timeit(opt.step, a.iters, a.warmup, flush)
+    report("adamw", ms, bytes_=30.0 * n, params=n)
+
+
 def probe_gemm_ar_local(a, flush):
     """The fused GEMM + all-reduce kernel on ONE GPU: rank 0 of an emulated world of 2 whose peer inbox is this
     GPU's own buffer and whose peer flags are pre-set, so that the reducer path can be timed and profiled alone."""
@@ -164,7 +176,7 @@ def probe_gemm_ar_local(a, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "elementwise", "gemm_ar_local", "all"])
+    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "elementwise", "gemm_ar_local", "adamw", "all"])
     ap.add_argument("--reducers", type=int, default=16)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
@@ -183,7 +195,7 @@ def main():
     todo = ["gemm", "attn_fwd", "attn_bwd", "elementwise"] if a.what == "all" else [a.what]
     for t in todo:
         {"gemm": probe_gemm, "attn_fwd": probe_attn_fwd, "attn_bwd": probe_attn_bwd, "elementwise": probe_elementwise,
-         "gemm_ar_local": probe_gemm_ar_local}[t](a, flush)
+         "gemm_ar_local": probe_gemm_ar_local, "adamw": probe_adamw}[t](a, flush)
     from ..ops import _native as nat
 
     nat.check_status()
