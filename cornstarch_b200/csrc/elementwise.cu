@@ -234,7 +234,28 @@ adamw_kernel(__nv_bfloat16* __restrict__ param, float* __restrict__ master, floa
 template <typename GradT>
 __global__ void sumsq_kernel(const GradT* __restrict__ g, long n, float* __restrict__ out) {
   float acc = 0.f;
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+  // 16-byte streaming loads, two per thread and pass (the base pointer is 16-byte aligned: arena slices and torch
+  // allocations are); the tail that does not fill a vector is read element-wise
+  constexpr int PER = 16 / sizeof(GradT);
+  const long nvec = n / PER;
+  const long stride = (long)gridDim.x * blockDim.x;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < nvec; i += 2 * stride) {
+    uint4 u0 = __ldcs(reinterpret_cast<const uint4*>(g) + i);
+    uint4 u1 = make_uint4(0u, 0u, 0u, 0u);
+    if (i + stride < nvec) u1 = __ldcs(reinterpret_cast<const uint4*>(g) + i + stride);
+    const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if constexpr (sizeof(GradT) == 4) {
+        const float x = __uint_as_float(w[k]);
+        acc += x * x;
+      } else {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[k]));
+        acc += f.x * f.x + f.y * f.y;
+      }
+    }
+  }
+  for (long i = nvec * PER + blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += stride) {
     float x;
     if constexpr (sizeof(GradT) == 4) x = g[i]; else x = __bfloat162float(g[i]);
     acc += x * x;
@@ -499,7 +520,7 @@ CSB_API int csb_adamw(void* param, float* master, float* m, float* v, void* grad
 }
 CSB_API int csb_sumsq(const void* g, int grad_fp32, long n, float* out, void* stream) {
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = ew_grid(n, 512);
+  const int grid = ew_grid(n / 16 + 1, 512);
   if (grad_fp32)
     sumsq_kernel<float><<<grid, 512, 0, s>>>(reinterpret_cast<const float*>(g), n, out);
   else

@@ -135,8 +135,22 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   }
 }
 
+__device__ __forceinline__ Vec8 unpack8(const uint4& u) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+  Vec8 v;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    v.f[2 * i] = t.x;
+    v.f[2 * i + 1] = t.y;
+  }
+  return v;
+}
+
 // dx = rstd * (g - xhat * mean(g*xhat) [- mean(g)])  with g = dy * w;  dw += dy * xhat;  db += dy
-template <bool IS_LN>
+// NVEC = 16-byte vectors per thread (H <= NVEC * 2048).  The raw vectors of the CTA's next row are fetched before the
+// current row is reduced, so that loads stay in flight across the block-wide reduction.
+template <bool IS_LN, int NVEC>
 __global__ void __launch_bounds__(NORM_THREADS)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
                 const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean_in,
@@ -145,18 +159,18 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
                 int rows, int H, float w_offset) {
   __shared__ float sh[32];
   const int nvec = H / 8;
-  float dw_acc[NORM_MAX_VEC][8];
-  float db_acc[NORM_MAX_VEC][8];
+  float dw_acc[NVEC][8];
+  float db_acc[NVEC][8];
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i)
+  for (int i = 0; i < NVEC; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       dw_acc[i][j] = 0.f;
       db_acc[i][j] = 0.f;
     }
-  Vec8 wv[NORM_MAX_VEC];
+  Vec8 wv[NVEC];
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+  for (int i = 0; i < NVEC; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
     if (c < nvec) {
       wv[i] = load8(w + c * 8);
@@ -164,18 +178,40 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
       for (int j = 0; j < 8; ++j) wv[i].f[j] += w_offset;
     }
   }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  uint4 n_dy[NVEC], n_h[NVEC], n_dr[NVEC];
+  auto fetch = [&](int row) {
     const size_t base = static_cast<size_t>(row) * H;
-    const float mean = IS_LN ? mean_in[row] : 0.f;
-    const float rstd = rstd_in[row];
-    Vec8 g[NORM_MAX_VEC], xh[NORM_MAX_VEC];
-    float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nvec) {
-        Vec8 d = load8(dy + base + c * 8);
-        Vec8 hv = load8(h + base + c * 8);
+        n_dy[i] = __ldcs(reinterpret_cast<const uint4*>(dy + base + c * 8));
+        n_h[i] = __ldcs(reinterpret_cast<const uint4*>(h + base + c * 8));
+        if (dres) n_dr[i] = __ldcs(reinterpret_cast<const uint4*>(dres + base + c * 8));
+      }
+    }
+  };
+  if (blockIdx.x < rows) fetch(blockIdx.x);
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const size_t base = static_cast<size_t>(row) * H;
+    uint4 c_dy[NVEC], c_h[NVEC], c_dr[NVEC];
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      c_dy[i] = n_dy[i];
+      c_h[i] = n_h[i];
+      c_dr[i] = n_dr[i];
+    }
+    if (row + (int)gridDim.x < rows) fetch(row + gridDim.x);
+    const float mean = IS_LN ? mean_in[row] : 0.f;
+    const float rstd = rstd_in[row];
+    Vec8 g[NVEC], xh[NVEC];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < NVEC; ++i) {
+      const int c = threadIdx.x + i * NORM_THREADS;
+      if (c < nvec) {
+        const Vec8 d = unpack8(c_dy[i]);
+        const Vec8 hv = unpack8(c_h[i]);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i].f[j] = (hv.f[j] - mean) * rstd;
@@ -190,14 +226,14 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     const float m1 = block_sum(s1, sh) / H;
     const float m2 = IS_LN ? block_sum(s2, sh) / H : 0.f;
 #pragma unroll
-    for (int i = 0; i < NORM_MAX_VEC; ++i) {
+    for (int i = 0; i < NVEC; ++i) {
       const int c = threadIdx.x + i * NORM_THREADS;
       if (c < nvec) {
         Vec8 o;
 #pragma unroll
         for (int j = 0; j < 8; ++j) o.f[j] = rstd * (g[i].f[j] - xh[i].f[j] * m1 - m2);
         if (dres) {
-          Vec8 r = load8(dres + base + c * 8);
+          const Vec8 r = unpack8(c_dr[i]);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o.f[j] += r.f[j];
         }
@@ -206,7 +242,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     }
   }
 #pragma unroll
-  for (int i = 0; i < NORM_MAX_VEC; ++i) {
+  for (int i = 0; i < NVEC; ++i) {
     const int c = threadIdx.x + i * NORM_THREADS;
     if (c < nvec) {
       float* pw = dw_partial + static_cast<size_t>(blockIdx.x) * H + c * 8;
@@ -222,18 +258,28 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
 }
 
 // out[c] (+)= sum_r partial[r][c]; out is fp32 (main-grad accumulation) or bf16.
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, void* __restrict__ out, int nparts, int H,
-                                       int out_fp32, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+// One CTA = 32 columns x 8 row groups: every warp reads 128 contiguous bytes of a row, the 8 groups are summed in
+// shared memory (a column-per-thread loop over all rows left the partial buffer to 16 CTAs).
+__global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __restrict__ partial, void* __restrict__ out,
+                                                              int nparts, int H, int out_fp32, int accumulate) {
+  __shared__ float sh[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int r = 0; r < nparts; ++r) s += partial[static_cast<size_t>(r) * H + c];
-  if (out_fp32) {
-    float* o = reinterpret_cast<float*>(out);
-    o[c] = accumulate ? o[c] + s : s;
-  } else {
-    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
-    o[c] = __float2bfloat16(accumulate ? __bfloat162float(o[c]) + s : s);
+  if (c < H)
+    for (int r = ty; r < nparts; r += 8) s += partial[static_cast<size_t>(r) * H + c];
+  sh[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < H) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) s += sh[k][tx];
+    if (out_fp32) {
+      float* o = reinterpret_cast<float*>(out);
+      o[c] = accumulate ? o[c] + s : s;
+    } else {
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+      o[c] = __float2bfloat16(accumulate ? __bfloat162float(o[c]) + s : s);
+    }
   }
 }
 
@@ -298,15 +344,20 @@ CSB_API int csb_norm_bwd(int is_layernorm, const void* dy, const void* h, const 
   auto W = reinterpret_cast<const __nv_bfloat16*>(w);
   auto DR = reinterpret_cast<const __nv_bfloat16*>(dres);
   auto DX = reinterpret_cast<__nv_bfloat16*>(dx);
-  if (is_layernorm)
-    norm_bwd_kernel<true><<<grid, NORM_THREADS, 0, s>>>(DY, Hh, W, mean, rstd, DR, DX, dw_partial, db_partial, rows, H, w_offset);
-  else
-    norm_bwd_kernel<false><<<grid, NORM_THREADS, 0, s>>>(DY, Hh, W, mean, rstd, DR, DX, dw_partial, db_partial, rows, H, w_offset);
+#define CSB_NORM_BWD(LN, NV) \
+  norm_bwd_kernel<LN, NV><<<grid, NORM_THREADS, 0, s>>>(DY, Hh, W, mean, rstd, DR, DX, dw_partial, db_partial, rows, H, w_offset)
+  const int nv = H <= 2048 ? 1 : (H <= 4096 ? 2 : 4);
+  if (is_layernorm) {
+    if (nv == 1) CSB_NORM_BWD(true, 1); else if (nv == 2) CSB_NORM_BWD(true, 2); else CSB_NORM_BWD(true, 4);
+  } else {
+    if (nv == 1) CSB_NORM_BWD(false, 1); else if (nv == 2) CSB_NORM_BWD(false, 2); else CSB_NORM_BWD(false, 4);
+  }
+#undef CSB_NORM_BWD
   int r = launch_result();
   if (r) return r;
-  if (dw_out) reduce_partials_kernel<<<(H + 255) / 256, 256, 0, s>>>(dw_partial, dw_out, grid, H, grads_fp32, accumulate);
+  if (dw_out) reduce_partials_kernel<<<(H + 31) / 32, 256, 0, s>>>(dw_partial, dw_out, grid, H, grads_fp32, accumulate);
   if (is_layernorm && db_out && db_partial)
-    reduce_partials_kernel<<<(H + 255) / 256, 256, 0, s>>>(db_partial, db_out, grid, H, grads_fp32, accumulate);
+    reduce_partials_kernel<<<(H + 31) / 32, 256, 0, s>>>(db_partial, db_out, grid, H, grads_fp32, accumulate);
   return launch_result();
 }
 
@@ -321,6 +372,6 @@ CSB_API int csb_colsum(const void* x, float* partial, void* out, int out_fp32, i
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int grid = csb_colsum_parts(rows);
   colsum_partial_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), partial, rows, H);
-  reduce_partials_kernel<<<(H + 255) / 256, 256, 0, s>>>(partial, out, grid, H, out_fp32, accumulate);
+  reduce_partials_kernel<<<(H + 31) / 32, 256, 0, s>>>(partial, out, grid, H, out_fp32, accumulate);
   return launch_result();
 }

@@ -118,6 +118,16 @@ def probe_elementwise(a, flush):
     w = torch.ones(H, device="cuda").bfloat16()
     ms = timeit(lambda: E.rms_norm(x, w, 1e-5, r), a.iters, a.warmup, flush)
     report("rmsnorm_residual_fwd", ms, bytes_=4 * T * H * 2)
+    xg = x.clone().requires_grad_()
+    wg = torch.ones(H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y, hsum = E.rms_norm(xg, wg, 1e-5, r)
+    dy = torch.randn_like(y)
+
+    def bwd():
+        torch.autograd.grad((y, hsum), (xg, wg), (dy, dy), retain_graph=True)
+
+    ms = timeit(bwd, a.iters, a.warmup, flush)
+    report("rmsnorm_residual_bwd", ms, bytes_=4 * T * H * 2)
     gu = torch.randn(T, 2 * I, device="cuda").bfloat16()
     ms = timeit(lambda: E.glu(gu), a.iters, a.warmup, flush)
     report("swiglu_fwd", ms, bytes_=3 * T * I * 2)
