@@ -1,0 +1,135 @@
+"""MultimodalModel behaviour on CPU: merging encoder outputs into the text, the bitfield mask rule, freezing by
+``train(...)``, skipped modalities, projector save/load, the processor's token expansion, the timer aid and the
+import-path aliases of the reference."""
+
+import importlib
+
+import pytest
+import torch
+
+from cornstarch_b200.zoo import build_model, synthetic_batch
+
+
+def test_merge_places_features_and_builds_bitfield_mask():
+    model = build_model("tiny", dtype=torch.float32)
+    tid = model.token_ids["vision"]
+    ids = torch.randint(0, 900, (2, 40))
+    ids[:, 3:19] = tid
+    feats = torch.randn(2, 16, model.language_model.config.hidden_size)
+    embeds, bits = model.merge_encoder_outputs({"vision": (feats,)}, ids)
+    assert torch.allclose(embeds[:, 3:19], feats)
+    want_text = model.language_model.get_input_embeddings()(ids[:, :3])
+    assert torch.allclose(embeds[:, :3], want_text)
+    text_bits = (1 << 62) | 1 | 2
+    assert bits[0, 0].item() == text_bits and bits[0, 5].item() == 2  # text sees every modality; the image has bit 1
+    with pytest.raises(ValueError):
+        model.check_counts = True
+        model.merge_encoder_outputs({"vision": (feats[:, :5],)}, ids)
+
+
+def test_labels_at_modality_positions_are_ignored_and_missing_modality_is_skipped():
+    model = build_model("tiny", dtype=torch.float32)
+    batch = synthetic_batch("tiny", 2, seed=1)
+    out = model(**batch)
+    assert torch.isfinite(out.loss)
+    # text-only batch: the encoder has no input and is skipped
+    ids = torch.randint(0, 900, (2, 32))
+    out2 = model(input_ids=ids, labels=ids)
+    assert torch.isfinite(out2.loss)
+
+
+def test_train_modes_toggle_requires_grad():
+    model = build_model("tiny", dtype=torch.float32)
+    model.train(encoders_mode={"vision": (False, True)}, llm_mode=False)
+    enc = model.vision_encoder
+    assert not any(p.requires_grad for p in enc.module.parameters())
+    assert all(p.requires_grad for p in enc.projector.parameters())
+    assert not any(p.requires_grad for p in model.language_model.parameters())
+    model.train(encoders_mode=None, llm_mode=True)
+    assert all(p.requires_grad for p in model.language_model.parameters())
+    assert not any(p.requires_grad for p in enc.module.parameters())  # None leaves a part as it was
+
+
+def test_projector_save_and_load(tmp_path):
+    from cornstarch_b200.multimodal import MultimodalProjector
+
+    model = build_model("tiny", dtype=torch.float32)
+    proj = model.vision_encoder.projector
+    proj.save_pretrained(str(tmp_path))
+    assert (tmp_path / "config.json").exists() and (tmp_path / "model.safetensors").exists()
+    again = MultimodalProjector.from_pretrained(str(tmp_path))
+    assert set(again.state_dict()) == set(proj.state_dict()) == {"projection.in_proj.weight", "projection.in_proj.bias",
+                                                                  "projection.out_proj.weight", "projection.out_proj.bias"}
+    for k, v in proj.state_dict().items():
+        assert torch.equal(v, again.state_dict()[k])
+
+
+class _Tok:
+    """Whitespace tokenizer with special tokens kept whole."""
+
+    def __init__(self):
+        self.vocab = {"<pad>": 0}
+
+    def __len__(self):
+        return 1000
+
+    def add_special_tokens(self, d):
+        for t in d["additional_special_tokens"]:
+            self.vocab.setdefault(t, 990 + len(self.vocab))
+
+    def convert_tokens_to_ids(self, t):
+        return self.vocab[t]
+
+    def __call__(self, text, return_tensors="pt", **kw):
+        rows = []
+        for s in text:
+            for sp in list(self.vocab):
+                s = s.replace(sp, f" {sp} ")
+            rows.append([self.vocab.get(w, 1 + (hash(w) % 900)) for w in s.split()])
+        n = max(len(r) for r in rows)
+        ids = torch.tensor([r + [0] * (n - len(r)) for r in rows])
+        return {"input_ids": ids, "attention_mask": (ids != 0).long()}
+
+
+class _ImageProc:
+    def __call__(self, images=None, return_tensors="pt"):
+        return {"pixel_values": torch.stack(images)}
+
+
+def test_processor_expands_modality_tokens():
+    from cornstarch_b200.multimodal import MultimodalProcessor
+
+    model = build_model("tiny", dtype=torch.float32)
+    proc = MultimodalProcessor({"vision": _ImageProc()}, _Tok(), model, predefined_tokens={"vision": "<image>"},
+                               num_feature_calculation_funcs={"vision": lambda inputs, outputs: [16] * len(outputs["pixel_values"])})
+    imgs = [torch.randn(3, 56, 56), torch.randn(3, 56, 56)]
+    batch = proc(encoder_inputs={"vision": {"images": imgs}}, llm_inputs={"text": ["<image> a b c", "x <image> y"]})
+    assert list(batch.keys())[0] == "input_ids"
+    tid = model.token_ids["vision"]
+    assert (batch["input_ids"] == tid).sum(dim=1).tolist() == [16, 16]
+    out = model(input_ids=batch["input_ids"], pixel_values=batch["pixel_values"], labels=batch["input_ids"])
+    assert torch.isfinite(out.loss)
+
+
+def test_timer_context_manager_restores_functions():
+    from cornstarch_b200.testing.timer import TimerContextManager
+
+    import torch.nn.functional as F
+
+    orig = F.gelu
+    with TimerContextManager("torch.nn.functional.gelu") as t:
+        assert F.gelu is not orig
+        F.gelu(torch.randn(8))
+        F.gelu(torch.randn(8))
+    assert F.gelu is orig
+    times = t.get_elapsed_times()
+    assert len(times["torch.nn.functional.gelu"]) == 2 and all(x >= 0 for x in times["torch.nn.functional.gelu"])
+
+
+def test_reference_import_paths_resolve():
+    import cornstarch_b200.compat  # noqa: F401
+
+    m = importlib.import_module("cornstarch.models.multimodal_language_model")
+    assert hasattr(m, "MultimodalModel") and hasattr(m, "ModalEncoderModule")
+    p = importlib.import_module("cornstarch.plugin.multimodal_parallel_plugin")
+    assert hasattr(p, "MultimodalParallelPlugin")
