@@ -25,7 +25,7 @@ from .. import nn as cnn
 from ..ops import attention as A
 from ..ops import elementwise as E
 from ..ops.cross_entropy import linear_cross_entropy
-from ..ops.linear import linear, multi_linear
+from ..ops.linear import add_adapter_deltas, linear, multi_linear
 from ..parallel import comm
 from .base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, register_model
 
@@ -192,6 +192,7 @@ class Attention(nn.Module):
             xin = self.q_proj.input_hook(x)
             biases = [self.q_proj.bias, self.k_proj.bias, self.v_proj.bias] if self.spec.qkv_bias else None
             qkv = multi_linear(xin, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], biases, tp=self.q_proj.tp_spec(x))
+            qkv = add_adapter_deltas(qkv, xin, (self.q_proj, self.k_proj, self.v_proj))
         ulysses = self.pc is not None and self.pc.sp_mode == "all_to_all" and self.pc.sp_size > 1
         if ulysses:
             # [B, S/sp, heads*D] -> [B, S, heads/sp*D] separately for q, k, v
@@ -242,6 +243,7 @@ class MLP(nn.Module):
             xin = self.gate_proj.input_hook(x)
             biases = [self.gate_proj.bias, self.up_proj.bias] if self.gate_proj.bias is not None else None
             gu = multi_linear(xin, [self.gate_proj.weight, self.up_proj.weight], biases, tp=self.gate_proj.tp_spec(x))
+            gu = add_adapter_deltas(gu, xin, (self.gate_proj, self.up_proj))
         return self.down_proj(E.glu(gu, self.act))
 
 

@@ -205,3 +205,19 @@ def multi_linear(x: torch.Tensor, weights: Sequence[torch.Tensor], biases: Seque
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, tp=None) -> torch.Tensor:
     return multi_linear(x, [weight], [bias], tp)
+
+
+def add_adapter_deltas(y: torch.Tensor, x: torch.Tensor, projections) -> torch.Tensor:
+    """``y`` = fused output of several projections of ``x`` (concatenated on the last dim).  Projections that carry an
+    adapter (a ``delta(x)`` method returning their additive update, e.g. LoRA) get it added to their slice."""
+    if not any(hasattr(p, "delta") for p in projections):
+        return y
+    parts, lo = [], 0
+    for p in projections:
+        n = p.weight.shape[0]
+        piece = y[..., lo : lo + n]
+        if hasattr(p, "delta"):
+            piece = piece + p.delta(x)
+        parts.append(piece)
+        lo += n
+    return torch.cat(parts, dim=-1)

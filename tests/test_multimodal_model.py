@@ -133,3 +133,29 @@ def test_reference_import_paths_resolve():
     assert hasattr(m, "MultimodalModel") and hasattr(m, "ModalEncoderModule")
     p = importlib.import_module("cornstarch.plugin.multimodal_parallel_plugin")
     assert hasattr(p, "MultimodalParallelPlugin")
+
+
+def test_lora_adapters_train_only_low_rank_and_merge():
+    from cornstarch_b200.lora import LoRALinear, add_lora, merge_lora
+    from cornstarch_b200.models.llama import DecoderConfig, DecoderForCausalLM
+
+    torch.manual_seed(0)
+    cfg = DecoderConfig(vocab_size=100, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2)
+    m = DecoderForCausalLM(cfg)
+    ids = torch.randint(0, 100, (2, 16))
+    base = m(input_ids=ids).logits.detach()
+    wrapped = add_lora(m, r=4, alpha=8, target=("q_proj", "v_proj", "down_proj"))
+    assert len(wrapped) == 6
+    assert torch.allclose(m(input_ids=ids).logits, base, atol=1e-6)  # B starts at zero
+    for mod in m.modules():
+        if isinstance(mod, LoRALinear):
+            torch.nn.init.normal_(mod.lora_B, std=0.05)
+    changed = m(input_ids=ids, labels=ids)
+    assert not torch.allclose(changed.logits if "logits" in changed else m(input_ids=ids).logits, base, atol=1e-4)
+    changed.loss.backward()
+    q = m.model.layers[0].self_attn.q_proj
+    assert q.base.weight.grad is None and q.lora_A.grad is not None and q.lora_A.grad.abs().sum() > 0
+    adapted = m(input_ids=ids).logits.detach()
+    merge_lora(m)
+    assert not any(isinstance(x, LoRALinear) for x in m.modules())
+    assert torch.allclose(m(input_ids=ids).logits, adapted, atol=1e-4)
