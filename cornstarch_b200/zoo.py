@@ -67,6 +67,13 @@ SHAPES = {
                   vocab=128256, llm=LLAMA31_8B, vision=SIGLIP_SO400M, audio=WHISPER_LARGE_V3),
     "long": Shape("long", seq_len=65536, image_tokens=729, image_size=384, vocab=128256, images_per_sample=8,
                   llm={**LLAMA31_8B, "max_position_embeddings": 65536}, vision=SIGLIP_SO400M),
+    "valm_tiny": Shape("valm_tiny", seq_len=256, image_tokens=16, audio_tokens=24, image_size=56, mel_bins=16, mel_frames=48, vocab=1000,
+                       llm=dict(vocab_size=1000, hidden_size=128, intermediate_size=352, num_hidden_layers=2,
+                                num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512),
+                       vision=dict(hidden_size=64, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                   image_size=56, patch_size=14, hidden_act="gelu", vit=True),
+                       audio=dict(num_mel_bins=16, d_model=64, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=128,
+                                  max_source_positions=24)),
     "long_small": Shape("long_small", seq_len=16384, image_tokens=729, image_size=384, vocab=128256, images_per_sample=8,
                         llm={**LLAMA31_8B, "num_hidden_layers": 4, "max_position_embeddings": 16384},
                         vision={**SIGLIP_SO400M, "num_hidden_layers": 3}),

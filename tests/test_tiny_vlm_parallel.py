@@ -157,3 +157,42 @@ def _colocated_worker(rank, world):
 
 def test_encoders_colocated_pipeline_matches_single_process():
     run_distributed(_colocated_worker, 3)
+
+
+def _valm_worker(rank, world):
+    """Vision and audio encoders as parallel pipeline branches feeding one LLM stage (3 ranks)."""
+    from cornstarch_b200.booster import Booster
+    from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
+    from cornstarch_b200.pipeline_template import PipelineTemplate
+    from cornstarch_b200.plugin.modal_parallel_plugin import ModalParallelPlugin
+    from cornstarch_b200.plugin.multimodal_parallel_plugin import MultimodalParallelPlugin
+    from cornstarch_b200.zoo import build_model, synthetic_batch
+
+    n_micro = 2
+    torch.manual_seed(0)
+    ref = build_model("valm_tiny")
+    ref.train()
+    batch = synthetic_batch("valm_tiny", 4, seed=1)
+    ref_loss = 0.0
+    for i in range(n_micro):
+        sub = {k: v[2 * i : 2 * i + 2] for k, v in batch.items()}
+        ref_loss += (ref(**sub).loss / n_micro).item()
+    torch.manual_seed(0)
+    model = build_model("valm_tiny")
+    model.train()
+    plugin = MultimodalParallelPlugin(
+        encoder_plugins={"vision": ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.vision_encoder, 1)),
+                         "audio": ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.audio_encoder, 1))},
+        language_model_plugin=ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.language_model, 1)),
+        num_microbatches=n_micro, device=torch.device("cpu"))
+    booster = Booster(plugin=plugin)
+    opt = FusedAdamW(split_decay_groups(model, 0.0), lr=1e-2)
+    pmodel, popt, criterion, *_ = booster.boost(model, opt, criterion=lambda out, b: out.loss)
+    out = booster.execute_pipeline(iter([batch]), pmodel, criterion, popt, return_loss=True)
+    if plugin.stage_manager.is_last_stage(check_only_in_modal=False):
+        assert abs(out["loss"].item() - ref_loss) < 1e-4, (out["loss"].item(), ref_loss)
+    popt.step()
+
+
+def test_two_encoder_branches_match_single_process():
+    run_distributed(_valm_worker, 3)
