@@ -75,16 +75,91 @@ def gemm_allreduce(args):
     nat.check_status()
 
 
+def cp_attention(args):
+    """Context-parallel attention forward + backward: K/V streamed from the peers inside the kernels against
+    NCCL all-gather / reduce-scatter around the local kernels.  Llama-8B heads, ``--seq`` tokens per rank."""
+    from ..ops import attention as A
+    from ..parallel import cp as CP
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    _, flops_peak, src = peaks()
+    B, Hq, Hk, D = 1, 32, 8, 128
+    S = args.seq * world
+    g = torch.Generator().manual_seed(0)
+    full = A.AttnMask.causal()
+    offs = CP.ContextParallelBatchSplitUtils.create_context_parallel_split(None, dist.group.WORLD, "zigzag", seq_len=S, batch=B, device="cuda")
+    state = CP.ContextParallelState(dist.group.WORLD, offs, full, "cuda")
+    n = state.mine.numel()
+    q = torch.randn(B, n, Hq, D, generator=g).cuda().bfloat16().requires_grad_()
+    k = torch.randn(B, n, Hk, D, generator=g).cuda().bfloat16().requires_grad_()
+    v = torch.randn(B, n, Hk, D, generator=g).cuda().bfloat16().requires_grad_()
+    do = torch.randn(B, n, Hq, D, generator=g).cuda().bfloat16()
+
+    def run():
+        q.grad = k.grad = v.grad = None
+        CP.context_parallel_attention(q, k, v, state).backward(do)
+
+    res = {}
+    for fused in (True, False):
+        CP.FUSED_CP_ENABLED = fused
+        state.fused_mask = None
+        res[fused] = timeit(run, iters=5, warmup=2)
+    # causal zigzag: every rank computes 1/world of the S x S / 2 score matrix; forward 4 S^2 H D / 2, backward 2.5x
+    flops = 3.5 * 4.0 * S * S * Hq * D * 0.5 / world
+    kv_bytes = (world - 1) * n * Hk * D * 2 * 2          # K and V shards of the peers, read once per pass
+    link_bytes = 2 * kv_bytes + kv_bytes                  # forward + backward reads, dK/dV tiles written to the owners
+    roof_ms = max(flops / flops_peak, link_bytes / NVLINK_BPS) * 1e3
+    if rank == 0:
+        print(json.dumps({"op": "cp_attention fwd+bwd", "world": world, "tokens_per_rank": n, "S": S,
+                          "fused_ms": round(res[True], 3), "nccl_gather_then_kernels_ms": round(res[False], 3),
+                          "roofline_ms": round(roof_ms, 3), f"frac_of_roofline_{src}": round(roof_ms / res[True], 3),
+                          "speedup_vs_nccl": round(res[False] / res[True], 3)}), flush=True)
+    from ..ops import _native as nat
+
+    nat.check_status()
+
+
+def grad_reduce(args):
+    """Flat-gradient all-reduce (mean) of ``--mb`` MiB of bf16: the peer-memory kernel against NCCL all_reduce + div."""
+    from ..parallel.dp_fused import FusedGradReducer
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    red = FusedGradReducer.get(dist.group.WORLD)
+    n = args.mb * (1 << 20) // 2
+    buf = red.allocate(n)
+    buf.normal_()
+    plain = torch.randn(n, device="cuda").bfloat16()
+    ms_f = timeit(lambda: red.reduce([buf]), iters=5, warmup=2)
+
+    def base():
+        dist.all_reduce(plain)
+        plain.mul_(1.0 / world)
+
+    ms_b = timeit(base, iters=5, warmup=2)
+    link_bytes = 2 * (world - 1) / world * n * 2
+    roof_ms = link_bytes / NVLINK_BPS * 1e3
+    if rank == 0:
+        print(json.dumps({"op": "grad all-reduce (mean)", "world": world, "MiB": args.mb, "fused_ms": round(ms_f, 3),
+                          "nccl_allreduce_then_scale_ms": round(ms_b, 3), "roofline_ms": round(roof_ms, 3),
+                          "frac_of_roofline": round(roof_ms / ms_f, 3), "bus_GBps": round(link_bytes / ms_f / 1e6, 1),
+                          "speedup_vs_nccl": round(ms_b / ms_f, 3)}), flush=True)
+    from ..ops import _native as nat
+
+    nat.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm_allreduce"])
+    ap.add_argument("what", choices=["gemm_allreduce", "cp_attention", "grad_reduce"])
+    ap.add_argument("--seq", type=int, default=8192, help="cp_attention: tokens per rank")
+    ap.add_argument("--mb", type=int, default=1024, help="grad_reduce: buffer size in MiB")
     ap.add_argument("--reducers", type=int, nargs="+", default=[16])
     args = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    {"gemm_allreduce": gemm_allreduce}[args.what](args)
+    {"gemm_allreduce": gemm_allreduce, "cp_attention": cp_attention, "grad_reduce": grad_reduce}[args.what](args)
     dist.barrier()
     dist.destroy_process_group()
 
