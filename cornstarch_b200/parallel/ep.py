@@ -217,6 +217,50 @@ def shard_experts(model, group) -> list[torch.nn.Parameter]:
             m.experts = nn.ModuleList([m.experts[i] for i in ep.local_expert_ids()])
             m.ep = ep
             expert_params += list(m.experts.parameters())
+            _install_global_expert_names(m, ep)
     for p in expert_params:
         p.expert_parallel = True
     return expert_params
+
+
+def _install_global_expert_names(block, ep: ExpertParallel) -> None:
+    """Checkpoints name experts by their global index: ``experts.<local>`` <-> ``experts.<first + local>`` on save / load."""
+    import re
+
+    first, local = ep.first, ep.local
+
+    def on_save(module, state_dict, prefix, local_metadata):
+        pat = re.compile(re.escape(prefix) + r"experts\.(\d+)\.")
+        for k in [k for k in state_dict if pat.match(k)]:
+            j = int(pat.match(k).group(1))
+            state_dict[pat.sub(f"{prefix}experts.{first + j}.", k, count=1)] = state_dict.pop(k)
+        return state_dict
+
+    def on_load(module, state_dict, prefix, *args):
+        pat = re.compile(re.escape(prefix) + r"experts\.(\d+)\.")
+        renamed = {}
+        for k in [k for k in state_dict if pat.match(k)]:
+            e = int(pat.match(k).group(1))
+            v = state_dict.pop(k)
+            if first <= e < first + local:
+                renamed[pat.sub(f"{prefix}experts.{e - first}.", k, count=1)] = v
+        state_dict.update(renamed)
+
+    block._register_state_dict_hook(on_save)
+    block.register_load_state_dict_pre_hook(on_load)
+
+
+def gather_full_state_dict(model, group, dst: int = 0) -> dict | None:
+    """The unsharded state dict (all experts, global names) on rank ``dst`` of the group, ``None`` elsewhere.
+    Replicated parameters are taken from ``dst``; expert parameters travel as CPU tensors through the group."""
+    import re
+
+    sd = {k: v.detach().cpu() for k, v in model.state_dict().items()}
+    mine = {k: v for k, v in sd.items() if re.search(r"\.experts\.\d+\.", k)}
+    everyone = [None] * dist.get_world_size(group)
+    dist.all_gather_object(everyone, mine, group=group)
+    if dist.get_rank(group) != dst:
+        return None
+    for part in everyone:
+        sd.update(part)
+    return dict(sorted(sd.items()))

@@ -48,3 +48,36 @@ def test_ep2_four_experts():
 
 def test_ep4_four_experts():
     run_distributed(_worker, 4, 4)
+
+
+def _ckpt_worker(rank, world):
+    from cornstarch_b200.models.moe import MixtralConfig, MoeForCausalLM
+    from cornstarch_b200.parallel.ep import gather_full_state_dict, shard_experts
+
+    cfg = MixtralConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2)
+    torch.manual_seed(0)
+    full = MoeForCausalLM(cfg)
+    torch.manual_seed(0)
+    sharded = MoeForCausalLM(cfg)
+    shard_experts(sharded, dist.group.WORLD)
+    # the sharded model names its experts globally and reassembles to the unsharded state dict
+    names = [k for k in sharded.state_dict() if ".experts." in k]
+    per = 4 // world
+    assert all(int(k.split(".experts.")[1].split(".")[0]) in range(rank * per, (rank + 1) * per) for k in names)
+    sd = gather_full_state_dict(sharded, dist.group.WORLD)
+    if rank == 0:
+        ref = full.state_dict()
+        assert set(sd) == set(ref)
+        assert all(torch.equal(sd[k], ref[k]) for k in ref)
+    # loading a full state dict into a sharded model keeps only the local experts
+    torch.manual_seed(1)
+    other = MoeForCausalLM(cfg)
+    missing, unexpected = sharded.load_state_dict(other.state_dict(), strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    e = rank * per
+    assert torch.equal(sharded.model.layers[1].block_sparse_moe.experts[0].w1.weight, other.model.layers[1].block_sparse_moe.experts[e].w1.weight)
+
+
+def test_expert_sharded_state_dict_round_trip():
+    run_distributed(_ckpt_worker, 2)
