@@ -150,9 +150,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   int* kp_s = reinterpret_cast<int*>(smem + L::KP_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The grid is one-dimensional so that thread blocks start in index order.  The first pull_ctas blocks bring the
+  // remote K / V segments into local memory; they are resident before any block that waits for their counters.
+  const int n_pull = p.seg.pull_ctas;
+  if ((int)blockIdx.x < n_pull) {
+    if (!pull_remote_segments(p.seg, blockIdx.x, n_pull, reinterpret_cast<int*>(smem)) && threadIdx.x == 0)
+      atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG);
+    return;
+  }
+  const int lin = blockIdx.x - n_pull;
   // heaviest (last) query tiles first: under causal masks they have the most key blocks
-  const int qi = p.nQ - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int qi = p.nQ - 1 - lin % p.nQ;
+  const int h = (lin / p.nQ) % p.Hq, b = lin / (p.nQ * p.Hq);
   const int hk = h / (p.Hq / p.Hk);
   const int q0 = qi * AT_BM;
   {
@@ -208,7 +217,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int row0 = (j - p.seg.tile_start[sg]) * AT_BN;
         if (!((opened >> sg) & 1u)) {
           // first tile from this peer: its K/V must have been staged (bounded wait on the counter it stores here)
-          if (!wait_peer_flag(p.seg.ready_flags + sg, p.seg.ready_value)) { atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG); *abort_flag = 1; break; }
+          const bool arrived = n_pull > 0 ? wait_local_count(p.seg.pulled + sg, p.seg.pull_target)
+                                          : wait_peer_flag(p.seg.ready_flags + sg, p.seg.ready_value);
+          if (!arrived) { atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG); *abort_flag = 1; break; }
+          // the copy was written with ordinary stores by other blocks; the loads below go through the async proxy
+          asm volatile("fence.proxy.async.global;" ::: "memory");
           opened |= 1u << sg;
         }
         const int st = it & 1;
@@ -537,11 +550,18 @@ CSB_API int csb_attn_fwd_seg(const void* q, const CsbKvSegments* kv, void* out, 
   for (int i = 0; i < CSB_MAX_SEG; ++i) {
     const int g = i < kv->n_seg ? i : 0;  // unused slots repeat segment 0 (never dereferenced)
     if ((kv->k_stride_s[g] % 8) || (kv->v_stride_s[g] % 8)) return CSB_ERR_BAD_ARG;
-    if ((r = make_qkv_tmap(&kvm.k[i], kv->k[g], D, Hk, kv->rows[g], B, kv->k_stride_s[g], kv->k_stride_b[g]))) return r;
-    if ((r = make_qkv_tmap(&kvm.v[i], kv->v[g], D, Hk, kv->rows[g], B, kv->v_stride_s[g], kv->v_stride_b[g]))) return r;
+    // with pulling blocks the tiles of a remote segment are read from its local copy
+    const bool local_copy = p.seg.pull_ctas > 0 && g != kv->my_seg;
+    if (local_copy && (kv->pull_k[g] == nullptr || kv->pull_v[g] == nullptr || (kv->pull_elems[g] % 8))) return CSB_ERR_BAD_ARG;
+    const void* kb = local_copy ? kv->pull_k[g] : kv->k[g];
+    const void* vb = local_copy ? kv->pull_v[g] : kv->v[g];
+    if ((r = make_qkv_tmap(&kvm.k[i], kb, D, Hk, kv->rows[g], B, kv->k_stride_s[g], kv->k_stride_b[g]))) return r;
+    if ((r = make_qkv_tmap(&kvm.v[i], vb, D, Hk, kv->rows[g], B, kv->v_stride_s[g], kv->v_stride_b[g]))) return r;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  dim3 grid(p.nQ, Hq, B);
+  const long n_blocks = (long)p.nQ * Hq * B + p.seg.pull_ctas;
+  if (n_blocks > 0x7fffffffL) return CSB_ERR_TOO_LARGE;
+  dim3 grid((unsigned)n_blocks);
   if (D <= 64) {
     auto kfn = attn_fwd_kernel<1>;
     static bool set1 = false;

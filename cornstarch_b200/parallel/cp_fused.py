@@ -24,6 +24,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -48,6 +49,8 @@ class KvSegments(C.Structure):
         ("dk", vp * MAX_SEG), ("dv", vp * MAX_SEG),
         ("dk_stride_s", i64 * MAX_SEG), ("dk_stride_b", i64 * MAX_SEG),
         ("dv_stride_s", i64 * MAX_SEG), ("dv_stride_b", i64 * MAX_SEG),
+        ("pull_ctas", i32), ("pull_k", vp * MAX_SEG), ("pull_v", vp * MAX_SEG), ("pull_elems", i64 * MAX_SEG),
+        ("pulled", vp), ("pull_target", i32),
     ]
 
 
@@ -57,6 +60,10 @@ nat.declare("csb_attn_bwd_seg", [vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, 
 nat.declare("csb_cp_signal", [vp, i32, i32, i32, vp])
 nat.declare("csb_cp_reduce", [vp, i32, vp, i32, vp, i64, vp, vp])
 nat.declare("csb_cp_wait", [vp, i32, i32, vp, vp])
+
+
+# thread blocks of the forward kernel that copy remote K / V into local memory (0: every tile is read from its owner)
+PULL_CTAS = int(os.environ.get("CORNSTARCH_B200_CP_PULL_CTAS", "24"))
 
 
 def padded_layout(sizes: list[int], tile: int = 128):
@@ -88,6 +95,10 @@ class _Buffers:
         self.dkv_flag_ptrs = torch.tensor([p + self.off_flags + 128 for p in self.mem.ptrs], dtype=torch.int64, device="cuda")
         self.kv_events = 0
         self.dkv_events = 0
+        # forward: local copies of the peers' K / V (filled by the kernel's pulling blocks) and their completion counters
+        self.pull = torch.empty((self.world, 2, B, smax, Hk, D), dtype=torch.bfloat16, device="cuda")
+        self.pulled = torch.zeros(MAX_SEG, dtype=torch.int32, device="cuda")
+        self.pull_calls = 0
         torch.cuda.synchronize()
         dist.barrier(group)
 
@@ -163,6 +174,17 @@ class FusedContextParallelAttention:
                 seg.dk_stride_b[r] = seg.dv_stride_b[r] = sb
         seg.ready_flags = bufs.flags.data_ptr()
         seg.ready_value = value
+        if not with_grads and PULL_CTAS > 0:
+            # forward: a query tile needs most key tiles, so remote K / V are copied once into local memory by the
+            # first thread blocks of the kernel instead of being fetched over NVLink by every query tile
+            bufs.pull_calls += 1
+            seg.pull_ctas = PULL_CTAS
+            seg.pulled = bufs.pulled.data_ptr()
+            seg.pull_target = PULL_CTAS * bufs.pull_calls
+            for r in range(self.world):
+                seg.pull_k[r] = bufs.pull[r, 0].data_ptr()
+                seg.pull_v[r] = bufs.pull[r, 1].data_ptr()
+                seg.pull_elems[r] = (sizes[r] if bufs.B == 1 else bufs.smax) * bufs.B * bufs.Hk * bufs.D
         return seg
 
     # ------------------------------------------------------------------ forward / backward
@@ -303,9 +325,12 @@ def local_segments(ks: list[torch.Tensor], vs: list[torch.Tensor], my_seg: int =
     return seg
 
 
-def attention_segments_local(q, ks, vs, mask: A.AttnMask, scale=None, my_seg: int = 0, do=None):
+def attention_segments_local(q, ks, vs, mask: A.AttnMask, scale=None, my_seg: int = 0, do=None, pull_ctas: int = 0):
     """Forward (and backward when ``do`` is given) over K/V given as several local tensors; ``mask`` is indexed in the
-    padded gathered space of ``[k.shape[1] for k in ks]``.  Returns ``(out, lse)`` or ``(out, lse, dq, dks, dvs)``."""
+    padded gathered space of ``[k.shape[1] for k in ks]``.  Returns ``(out, lse)`` or ``(out, lse, dq, dks, dvs)``.
+
+    ``pull_ctas > 0`` runs the forward the way the multi-GPU path does: the first thread blocks copy every segment but
+    ``my_seg`` into a second buffer (the ready counters are already set) and the query tiles read those copies."""
     B, Sq, Hq, D = q.shape
     Hk = ks[0].shape[2]
     sizes = [k.shape[1] for k in ks]
@@ -317,6 +342,15 @@ def attention_segments_local(q, ks, vs, mask: A.AttnMask, scale=None, my_seg: in
     qb, kb, qp, kp = A._mask_ptrs(mask, B)
     st = nat.status_word(q.device)
     seg = local_segments(ks, vs, my_seg)
+    if pull_ctas > 0:
+        assert all(k.is_contiguous() and v.is_contiguous() for k, v in zip(ks, vs))
+        keep = [torch.ones(MAX_SEG, dtype=torch.int32, device=q.device), torch.zeros(MAX_SEG, dtype=torch.int32, device=q.device)]
+        seg.ready_flags, seg.ready_value = keep[0].data_ptr(), 1
+        seg.pull_ctas, seg.pulled, seg.pull_target = pull_ctas, keep[1].data_ptr(), pull_ctas
+        for r, (k, v) in enumerate(zip(ks, vs)):
+            ck, cv = torch.full_like(k, float("nan")), torch.full_like(v, float("nan"))
+            keep += [ck, cv]
+            seg.pull_k[r], seg.pull_v[r], seg.pull_elems[r] = ck.data_ptr(), cv.data_ptr(), k.numel()
     nat.check(nat.lib().csb_attn_fwd_seg(
         q.data_ptr(), C.addressof(seg), out.data_ptr(), lse.data_ptr(), B, Sq, Sk, Hq, Hk, D, q.stride(1), q.stride(0),
         out.stride(1), out.stride(0), scale, mask.mode, nat.ptr(qb), nat.ptr(kb), nat.ptr(qp), nat.ptr(kp), cls.data_ptr(),

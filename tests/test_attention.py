@@ -210,3 +210,30 @@ def test_kv_segments_local(sizes, my_seg, mode):
     _close(dq, rdq)
     _close(torch.cat(dks, dim=1), rdk)
     _close(torch.cat(dvs, dim=1), rdv)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("sizes,my_seg,pull", [((256, 384), 1, 3), ((200, 128, 333), 0, 8), ((1024, 1024), 1, 24)])
+def test_kv_segments_pulled(sizes, my_seg, pull):
+    """The forward with pulling thread blocks (the first blocks copy every other segment once, the query tiles read the
+    copies) equals the forward that reads the segments where they are."""
+    from cornstarch_b200.parallel.cp_fused import attention_segments_local, padded_layout
+
+    B, Hq, Hk, D = 2, 4, 2, 128
+    S = sum(sizes)
+    q, k, v = _qkv(B, S, S, Hq, Hk, D, seed=S + 1)
+    pos = torch.arange(S, dtype=torch.int32).cuda()[None].expand(B, -1).contiguous()
+    starts, total = padded_layout(sizes)
+    kp = torch.full((B, total), -1, dtype=torch.int32, device="cuda")
+    ks, vs, off = [], [], 0
+    for s0, n in zip(starts, sizes):
+        kp[:, s0 : s0 + n] = pos[:, off : off + n]
+        ks.append(k[:, off : off + n].contiguous())
+        vs.append(v[:, off : off + n].contiguous())
+        off += n
+    mask = A.AttnMask(mode=A.MASK_CAUSAL, q_pos=pos, k_pos=kp)
+    ro, rlse = attention_segments_local(q, ks, vs, mask, my_seg=my_seg)
+    o, lse = attention_segments_local(q, ks, vs, mask, my_seg=my_seg, pull_ctas=pull)
+    torch.cuda.synchronize()
+    assert torch.equal(o, ro)
+    assert torch.equal(lse, rlse)
