@@ -195,6 +195,11 @@ class ModalParallelCheckpointIO:
             if fn.startswith("pytorch_optim-stage-") and fn.endswith(".bin"):
                 flat.update(torch.load(os.path.join(path, fn), map_location="cpu", weights_only=True))
         gfile = os.path.join(path, f"pytorch_optim_group-stage-{self.stage + 1:05d}.bin")
+        if not os.path.isfile(gfile):
+            # written by a pipeline with fewer stages: the hyper-parameters are the same in every stage's file
+            others = sorted(fn for fn in os.listdir(path) if fn.startswith("pytorch_optim_group-stage-"))
+            if others:
+                gfile = os.path.join(path, others[0])
         meta = torch.load(gfile, weights_only=False) if os.path.isfile(gfile) else {"param_groups": [], "fused_step": 0}
         state, idx = {}, 0
         for g in opt.param_groups:

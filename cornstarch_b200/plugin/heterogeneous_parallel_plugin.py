@@ -436,13 +436,11 @@ class _HeteroCheckpointIO:
         return model
 
     def save_optimizer(self, optimizer, checkpoint, shard=True, size_per_shard=1024):
-        import os
-
-        self._io(optimizer.model).save_sharded_optimizer(optimizer, optimizer.model.module, os.path.join(checkpoint, f"pipeline-{self.plugin._pipeline_index}"), size_per_shard)
+        # the replicas hold the same optimizer state after every step; pipeline 0 (all stages of it) writes, keyed by
+        # parameter name, so a pipeline with another stage layout can read it back
+        self._io(optimizer.model).save_sharded_optimizer(optimizer, optimizer.model.module, checkpoint, size_per_shard)
         dist.barrier()
 
     def load_optimizer(self, optimizer, checkpoint):
-        import os
-
-        self._io(optimizer.model).load_sharded_optimizer(optimizer, optimizer.model.module, os.path.join(checkpoint, f"pipeline-{self.plugin._pipeline_index}"))
+        self._io(optimizer.model).load_sharded_optimizer(optimizer, optimizer.model.module, checkpoint)
         dist.barrier()
