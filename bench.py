@@ -112,6 +112,8 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=4)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--recompute", choices=["auto", "full"], default="auto",
+                    help="auto: after the first warm-up step, decoder layers that fit in free memory keep their activations")
     ap.add_argument("--impl", default="native", choices=["native", "reference", "baseline"])
     ap.add_argument("--shape", default="vlm", help="named shape from cornstarch_b200.zoo (default: the headline VLM)")
     ap.add_argument("--samples-per-gpu", type=int, default=SAMPLES_PER_GPU)
@@ -170,8 +172,12 @@ def main():
     from cornstarch_b200.ops import _native as nat
 
     # ---- device-timed region: inputs already on the device
-    for _ in range(W):
+    for i in range(W):
         trainer.step_device()
+        if i == 0 and args.recompute == "auto" and hasattr(trainer, "tune_recompute"):
+            # the first step ran with every layer recomputed and shows how much memory is left: layers that fit stop
+            # being recomputed; the remaining (>= 2) warm-up steps run with the final setting
+            trainer.tune_recompute()
     sync()
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -236,7 +242,8 @@ def main():
                        "l2": "no flush needed: every step streams >16 GB of weights and activations, far above the 126 MB L2",
                        "optimizer": ("fused AdamW, fp32 master + moments, bf16 grads" if args.impl == "native"
                                      else "torch.optim.AdamW(fused=True) on bf16 parameters, clip_grad_norm_"),
-                       "kernels": ("this package (sm_100a)" if args.impl == "native" else "library: cuBLAS, PyTorch SDPA, PyTorch elementwise, NCCL"), "activation_checkpointing": "per layer"},
+                       "kernels": ("this package (sm_100a)" if args.impl == "native" else "library: cuBLAS, PyTorch SDPA, PyTorch elementwise, NCCL"), "activation_checkpointing": getattr(trainer, "recompute", "every layer"),
+                       "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1)},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": args.impl, "benchmark_config": args.config,
         }
         print(json.dumps(out))

@@ -148,10 +148,16 @@ class PreTrainedModel(nn.Module):
 
     # ---- checkpointing of activations -----------------------------------------------------------
     def gradient_checkpointing_enable(self, gradient_checkpointing_kwargs: dict | None = None):
+        """``gradient_checkpointing_kwargs={"keep_last_layers": k}``: the last ``k`` decoder layers this rank holds keep
+        their activations (no recomputation) - for when memory is left over; other keys (``use_reentrant``) are accepted
+        and ignored."""
+        keep = int((gradient_checkpointing_kwargs or {}).get("keep_last_layers", 0))
         self.gradient_checkpointing = True
+        self.recompute_keep_layers = keep
         for m in self.modules():
             if m is not self and isinstance(m, PreTrainedModel):
                 m.gradient_checkpointing = True
+                m.recompute_keep_layers = keep
 
     def gradient_checkpointing_disable(self):
         self.gradient_checkpointing = False

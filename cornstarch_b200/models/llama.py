@@ -367,14 +367,18 @@ class DecoderModel(PreTrainedModel):
         rope = self.rotary_emb(hidden_states.device, max_pos)
         delta, residual = hidden_states, None
         aux_losses = []
+        recompute = self.gradient_checkpointing and self.training and torch.is_grad_enabled()
+        n_recompute = sum(not is_released(l) for l in self.layers) - int(getattr(self, "recompute_keep_layers", 0))
+        seen = 0
         for layer in self.layers:
             if is_released(layer):
                 continue
+            seen += 1
             lrope = rope
             if self.spec.local_rope and getattr(self.config, "layer_types", None):
                 if self.config.layer_types[layer.self_attn.layer_idx] == "sliding_attention":
                     lrope = self.rotary_emb_local(hidden_states.device, max_pos)
-            if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
+            if recompute and seen <= n_recompute:
                 delta, residual, aux = checkpoint_layer(layer, delta, residual, lrope, pos, mask)
             else:
                 delta, residual, aux = layer(delta, residual, lrope, pos, mask)
@@ -459,6 +463,7 @@ class DecoderForCausalLM(PreTrainedModel):
     def gradient_checkpointing_enable(self, gradient_checkpointing_kwargs=None):
         super().gradient_checkpointing_enable(gradient_checkpointing_kwargs)
         self.model.gradient_checkpointing = True
+        self.model.recompute_keep_layers = self.recompute_keep_layers
 
     def forward(self, input_ids=None, inputs_embeds=None, attention_mask=None, position_ids=None, labels=None,
                 hidden_states=None, return_logits: bool | None = None, shift_labels: bool = True, **kwargs):

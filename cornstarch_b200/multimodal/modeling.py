@@ -247,14 +247,15 @@ class MultimodalModel(nn.Module):
         return self.language_model.get_input_embeddings()
 
     def gradient_checkpointing_enable(self, gradient_checkpointing_kwargs: dict | None = None):
-        """Always non-reentrant (the reference forces ``use_reentrant=False``, :774-792)."""
+        """Always non-reentrant (the reference forces ``use_reentrant=False``, :774-792).  ``{"keep_last_layers": k}`` is
+        passed on to the language model (its last ``k`` held layers keep their activations)."""
         for enc in self.encoders.values():
             if hasattr(enc.module, "gradient_checkpointing_enable"):
                 enc.module.gradient_checkpointing_enable()
             if enc.projector is not None:
                 enc.projector.gradient_checkpointing_enable()
         if self.language_model is not None and hasattr(self.language_model, "gradient_checkpointing_enable"):
-            self.language_model.gradient_checkpointing_enable()
+            self.language_model.gradient_checkpointing_enable(gradient_checkpointing_kwargs)
 
     def train(self, encoders_mode: dict[str, tuple[bool, bool]] | bool | None = None, llm_mode: bool | None = True):
         """Freeze / unfreeze by ``requires_grad``: ``encoders_mode = {key: (encoder, projector)}``; ``None`` leaves a part as is."""

@@ -159,3 +159,23 @@ def test_lora_adapters_train_only_low_rank_and_merge():
     merge_lora(m)
     assert not any(isinstance(x, LoRALinear) for x in m.modules())
     assert torch.allclose(m(input_ids=ids).logits, adapted, atol=1e-4)
+
+
+def test_recompute_keep_last_layers_same_gradients():
+    """Keeping the activations of the last k decoder layers (no recomputation there) changes no gradient."""
+    from cornstarch_b200 import zoo
+
+    batch = zoo.synthetic_batch("tiny", 2, seed=3)
+    grads = []
+    for keep in (None, 0, 1, 99):
+        torch.manual_seed(0)
+        model = zoo.build_model("tiny", device="cpu", dtype=torch.float32)
+        if keep is not None:
+            model.gradient_checkpointing_enable({"keep_last_layers": keep})
+        model.train()
+        model(**batch).loss.backward()
+        grads.append({n: p.grad.clone() for n, p in model.named_parameters() if p.grad is not None})
+    for g in grads[1:]:
+        assert g.keys() == grads[0].keys()
+        for n in g:
+            assert torch.allclose(g[n], grads[0][n], atol=1e-6), n
