@@ -75,8 +75,14 @@ struct BwdSmem {
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
 
-constexpr int BW_COMPUTE_THREADS = 256;
-constexpr int BW_THREADS = 64 + BW_COMPUTE_THREADS;
+// NCW compute warps (8 or 16): NCW / 4 warps share a TMEM lane quarter and split the 64 query columns between them.
+template <int NCW>
+struct BwdCfg {
+  static constexpr int COMPUTE_THREADS = NCW * 32;
+  static constexpr int THREADS = 64 + COMPUTE_THREADS;
+  static constexpr int GROUPS = NCW / 4;       // column groups
+  static constexpr int COLS = BW_BQ / GROUPS;  // query columns of S^T / dP^T / dQ^T per thread: 32 or 16
+};
 
 __device__ __forceinline__ bool bw_wait(uint64_t* bar, uint32_t phase, volatile int* abort_flag) {
   uint64_t t0 = 0;
@@ -134,12 +140,15 @@ __global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloa
   }
 }
 
-__global__ void __launch_bounds__(BW_THREADS, 1)
+template <int NCW>
+__global__ void __launch_bounds__(BwdCfg<NCW>::THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ KvMaps kvm,
                 const __grid_constant__ CUtensorMap tm_do, const __grid_constant__ CUtensorMap tm_dq,
                 const AttnBwdParams p) {
   using L = BwdSmem;
+  using CFG = BwdCfg<NCW>;
   constexpr int QS = L::QSTAGES;
+  constexpr int COLS = CFG::COLS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
@@ -173,11 +182,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&q_empty[i], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, BW_COMPUTE_THREADS);
+    mbar_init(pds_full, CFG::COMPUTE_THREADS);
     mbar_init(pds_empty, 1);
     mbar_init(dq_full, 1);
-    mbar_init(dq_free, BW_COMPUTE_THREADS);
-    mbar_init(meta_full, BW_COMPUTE_THREADS);
+    mbar_init(dq_free, CFG::COMPUTE_THREADS);
+    mbar_init(meta_full, CFG::COMPUTE_THREADS);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -308,7 +317,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows)
 #pragma unroll
         for (int kk = 0; kk < BW_BQ / 16; ++kk)
-          umma_f16_ts(tmem_dV, tmem_base + (it & 1) * 64 + (kk >> 1) * 32 + (kk & 1) * 8,
+          umma_f16_ts(tmem_dV, tmem_base + (it & 1) * 64 + (kk / (COLS / 16)) * COLS + (kk % (COLS / 16)) * 8,
                       make_desc_mnmajor_sw128(do_s + kk * 2048, Q_CHUNK), idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < BW_BQ / 16; ++kk)
@@ -331,13 +340,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ compute threads (8 warps)
+    // ------------------------------------------------------------------ compute threads (NCW warps)
     const int cw = warp - 2;
     const int quarter = warp & 3;       // TMEM lane quarter this warp may touch
-    const int half = cw >> 2;           // which 32 of the 64 query columns this warp handles
+    const int half = cw >> 2;           // which group of COLS query columns (of 64) this warp handles
     const int r = quarter * 32 + lane;  // KV row in the tile == TMEM lane; also head-dim row of dQ^T
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const int col0 = half * 32;
+    const int col0 = half * COLS;
     const int kidx = k0 + r;
     const int krow = row0 + r;  // row inside the segment
     const bool k_valid = krow < p.seg.rows[sg];
@@ -372,21 +381,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tc_fence_after();
       const int ph = hk * group + pit / n_valid;
       const int pi = tile_idx[pit % n_valid];
-      uint32_t v[32];
-      tmem_ld_32x32(tmem_dQT + col0 + lane_addr, v);
+      uint32_t v[COLS];
+      tmem_ld_cols<COLS>(tmem_dQT + col0 + lane_addr, v);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_free);
-      // this warp's [32 d][32 q] block -> shared memory as [q][d] rows of 128 B -> one TMA reduce-add into dq_acc
+      // this warp's [32 d][COLS q] block -> shared memory as [q][d] rows of 128 B -> one TMA reduce-add into dq_acc
       if (lane == 0) tma_store_wait_read<0>();  // the previous block has left the staging buffer
       __syncwarp();
-      float* stage = reinterpret_cast<float*>(smem + L::DQ_OFF + cw * 4096);
+      float* stage = reinterpret_cast<float*>(smem + L::DQ_OFF + cw * (COLS * 128));
 #pragma unroll
-      for (int c = 0; c < 32; ++c) stage[c * 32 + lane] = __uint_as_float(v[c]);
+      for (int c = 0; c < COLS; ++c) stage[c * 32 + lane] = __uint_as_float(v[c]);
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0 && quarter * 32 < p.D) {
-        tma_reduce_add_4d(&tm_dq, stage, quarter * 32, ph, pi * BW_BQ + col0, b);
+        tma_reduce_add_4d(&tm_dq, stage, quarter * 32, ph, pi * BW_BQ + col0, b);  // box: 32 d x COLS q
         tma_store_commit();
       }
       return true;
@@ -421,13 +430,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         break;
       }
       tc_fence_after();
-      uint32_t sv[32], dv[32];
-      tmem_ld_32x32(tmem_base + (it & 1) * 64 + col0 + lane_addr, sv);
-      tmem_ld_32x32(tmem_dPT + col0 + lane_addr, dv);
+      uint32_t sv[COLS], dv[COLS];
+      tmem_ld_cols<COLS>(tmem_base + (it & 1) * 64 + col0 + lane_addr, sv);
+      tmem_ld_cols<COLS>(tmem_dPT + col0 + lane_addr, dv);
       tmem_ld_wait();
-      float pv[32], ds[32];
+      float pv[COLS], ds[COLS];
 #pragma unroll
-      for (int x4 = 0; x4 < 8; ++x4) {
+      for (int x4 = 0; x4 < COLS / 4; ++x4) {
         const float4 l4 = *reinterpret_cast<const float4*>(m_lse + col0 + x4 * 4);
         const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
@@ -436,14 +445,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       if (c == 1) {
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
+        for (int x = 0; x < COLS; ++x) {
           const int col = col0 + x;
           const bool allow = k_valid && m_qpos[col] >= 0 && mask_allowed(p.mask_mode, m_qbits[col], kb, m_qpos[col], kpos);
           pv[x] = allow ? pv[x] : 0.f;
         }
       }
 #pragma unroll
-      for (int x4 = 0; x4 < 8; ++x4) {
+      for (int x4 = 0; x4 < COLS / 4; ++x4) {
         const float4 d4 = *reinterpret_cast<const float4*>(m_delta + col0 + x4 * 4);
         const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
 #pragma unroll
@@ -458,22 +467,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           break;
         }
       }
-      // P^T -> packed bf16 pairs in tensor memory, over this thread's own S^T columns (first 16 of its 32);
-      // dS^T -> bf16 smem tile: row r, this warp's four 16-byte pieces (8 query columns each)
+      // P^T -> packed bf16 pairs in tensor memory, over this thread's own S^T columns (the first half of them);
+      // dS^T -> bf16 smem tile: row r, this warp's 16-byte pieces (8 query columns each)
       {
-        uint32_t pk[16];
+        uint32_t pk[COLS / 2];
 #pragma unroll
-        for (int x = 0; x < 16; ++x) pk[x] = pack_bf16x2(pv[2 * x], pv[2 * x + 1]);
-        tmem_st_32x16(tmem_base + (it & 1) * 64 + col0 + lane_addr, pk);
+        for (int x = 0; x < COLS / 2; ++x) pk[x] = pack_bf16x2(pv[2 * x], pv[2 * x + 1]);
+        tmem_st_cols<COLS / 2>(tmem_base + (it & 1) * 64 + col0 + lane_addr, pk);
       }
 #pragma unroll
-      for (int pc = 0; pc < 4; ++pc) {
+      for (int pc = 0; pc < COLS / 8; ++pc) {
         uint4 w;
         w.x = pack_bf16x2(ds[pc * 8 + 0], ds[pc * 8 + 1]);
         w.y = pack_bf16x2(ds[pc * 8 + 2], ds[pc * 8 + 3]);
         w.z = pack_bf16x2(ds[pc * 8 + 4], ds[pc * 8 + 5]);
         w.w = pack_bf16x2(ds[pc * 8 + 6], ds[pc * 8 + 7]);
-        *reinterpret_cast<uint4*>(smem + L::DST_OFF + sw128_offset(r, half * 4 + pc)) = w;
+        *reinterpret_cast<uint4*>(smem + L::DST_OFF + sw128_offset(r, half * (COLS / 8) + pc)) = w;
       }
       tmem_st_wait();
       fence_proxy_async_smem();
@@ -486,7 +495,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (lane == 0) tma_store_wait<0>();  // every reduce-add of this warp has completed
     __syncwarp();
     // ---- epilogue: dV and dK tiles (every MMA has retired once the last dQ^T was seen);
-    //      the two warps of a lane quarter split the head-dim columns
+    //      the warps of a lane quarter split the head-dim columns
     if (ok && peer_ready) {
       tc_fence_after();
 #pragma unroll
@@ -496,8 +505,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                   ? p.dV[sg] + (long)b * p.dv_stride_b[sg] + (long)krow * p.dv_stride_s[sg] + (long)hk * p.D
                                   : p.dK[sg] + (long)b * p.dk_stride_b[sg] + (long)krow * p.dk_stride_s[sg] + (long)hk * p.D;
 #pragma unroll
-        for (int c2 = 0; c2 < 2; ++c2) {
-          const int cc = half * 2 + c2;
+        for (int c2 = 0; c2 < 4 / CFG::GROUPS; ++c2) {
+          const int cc = half * (4 / CFG::GROUPS) + c2;
           uint32_t v[32];
           if (n_iter > 0) {
             tmem_ld_32x32(t + cc * 32 + lane_addr, v);
@@ -599,22 +608,31 @@ CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void*
     p.dk_stride_s[i] = kv->dk_stride_s[g]; p.dk_stride_b[i] = kv->dk_stride_b[g];
     p.dv_stride_s[i] = kv->dv_stride_s[g]; p.dv_stride_b[i] = kv->dv_stride_b[g];
   }
+  // 16 compute warps (two more per scheduler to hide the tensor-memory load latency) unless the environment says 8
+  static const bool wide = []() {
+    const char* e = getenv("CORNSTARCH_B200_ATTN_BWD_WARPS");
+    return !(e && atoi(e) == 8);
+  }();
   CUtensorMap tdq;
   {
-    // dq_acc is dense fp32 [B][Sq][Hq][D]; a block is 32 head-dim elements (128 B) x 32 query rows
+    // dq_acc is dense fp32 [B][Sq][Hq][D]; a block is 32 head-dim elements (128 B) x 32 or 16 query rows
     uint64_t dims[4] = {(uint64_t)D, (uint64_t)Hq, (uint64_t)Sq, (uint64_t)B};
     uint64_t strides[3] = {(uint64_t)D * 4, (uint64_t)Hq * D * 4, (uint64_t)Sq * Hq * D * 4};
-    uint32_t box[4] = {32, 1, 32, 1};
+    uint32_t box[4] = {32, 1, (uint32_t)(wide ? BwdCfg<16>::COLS : BwdCfg<8>::COLS), 1};
     if ((r = make_tmap_nd_f32(&tdq, dq_acc, 4, dims, strides, box))) return r;
   }
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::DYN_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_bwd_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::DYN_BYTES) != cudaSuccess ||
+        cudaFuncSetAttribute(attn_bwd_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem::DYN_BYTES) != cudaSuccess)
       return launch_result();
     attr = true;
   }
   dim3 grid(p.nK, Hk, B);
-  attn_bwd_kernel<<<grid, BW_THREADS, BwdSmem::DYN_BYTES, s>>>(tq, kvm, tdo, tdq, p);
+  if (wide)
+    attn_bwd_kernel<16><<<grid, BwdCfg<16>::THREADS, BwdSmem::DYN_BYTES, s>>>(tq, kvm, tdo, tdq, p);
+  else
+    attn_bwd_kernel<8><<<grid, BwdCfg<8>::THREADS, BwdSmem::DYN_BYTES, s>>>(tq, kvm, tdo, tdq, p);
   int e = launch_result();
   if (e) return e;
   const long n_rows = (long)B * Sq;

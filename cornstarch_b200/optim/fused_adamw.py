@@ -256,6 +256,12 @@ class FusedAdamW(torch.optim.Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None):
+        from ..utils.trace import nvtx_range
+
+        with nvtx_range("optimizer/fused_adamw_step"):
+            return self._step_impl(closure)
+
+    def _step_impl(self, closure=None):
         loss = closure() if closure is not None else None
         if self.use_arena:
             self._step_arena()

@@ -17,6 +17,8 @@ from typing import Any, Callable, Iterable
 import torch
 from torch.utils._pytree import tree_flatten, tree_map
 
+from ..utils.trace import nvtx_range
+
 from .p2p import MultimodalPipelineP2PCommunication
 
 
@@ -152,7 +154,8 @@ class MultimodalEncoderTrainingOneForwardOneBackwardSchedule:
                 kwargs.update(input_obj)
             else:
                 kwargs["hidden_states"] = input_obj
-        output_obj = model(**kwargs)
+        with nvtx_range("pipeline/forward_microbatch"):
+            output_obj = model(**kwargs)
         if self.stage_manager.is_last_stage(check_only_in_modal=False):
             loss = criterion(output_obj, micro_batch) / self.num_microbatches
             if accum_loss is not None:
@@ -170,7 +173,8 @@ class MultimodalEncoderTrainingOneForwardOneBackwardSchedule:
                 if isinstance(leaf, torch.Tensor) and leaf.requires_grad:
                     leaf.retain_grad()
         if output_obj_grad is None:
-            _backward(optimizer, output_obj, None)
+            with nvtx_range("pipeline/backward_microbatch"):
+                _backward(optimizer, output_obj, None)
         else:
             outs, grads = [], []
             o_leaves = tree_flatten(output_obj)[0] if not isinstance(output_obj, dict) else None
@@ -187,7 +191,8 @@ class MultimodalEncoderTrainingOneForwardOneBackwardSchedule:
                         outs.append(o)
                         grads.append(g)
             if outs:
-                _backward(optimizer, outs, grads)
+                with nvtx_range("pipeline/backward_microbatch"):
+                    _backward(optimizer, outs, grads)
 
     # ------------------------------------------------------------------ the schedule
     def num_warmup(self) -> int:

@@ -184,9 +184,89 @@ def probe_gemm_ar_local(a, flush):
            rel_err=round(err, 5))
 
 
+def probe_grad_reduce_local(a, flush):
+    """The gradient all-reduce kernel on ONE GPU: rank 0 of an emulated world of 2 whose peer buffer is a second
+    buffer of this GPU and whose "gradients complete" counter is pre-set.  ``--m`` = MiB per buffer.  Rank 0 owns the
+    first half: it reads that half of both buffers and writes the mean into both."""
+    import ctypes as C
+
+    from ..ops import _native as nat
+    from ..parallel import dp_fused  # noqa: F401  (declares the prototype)
+
+    n = int(a.m) * (1 << 20) // 2
+    mine = torch.randn(n, device="cuda").bfloat16()
+    peer = torch.randn(n, device="cuda").bfloat16()
+    want = ((mine[: n // 2].float() + peer[: n // 2].float()) * 0.5).bfloat16()
+    ready = torch.full((64,), 1 << 30, dtype=torch.int32, device="cuda")
+    bufs = (C.c_void_p * 8)(mine.data_ptr(), peer.data_ptr(), 0, 0, 0, 0, 0, 0)
+    st = nat.status_word()
+
+    def run():
+        nat.check(nat.lib().csb_grad_reduce(C.cast(bufs, C.c_void_p), 2, 0, n, 0.5, 1, ready.data_ptr(), 1, 0, st.data_ptr(),
+                                            nat.stream()), "csb_grad_reduce")
+
+    run()
+    torch.cuda.synchronize()
+    ok = bool(torch.equal(mine[: n // 2], want) and torch.equal(peer[: n // 2], want))
+    ms = timeit(run, a.iters, a.warmup, flush)
+    # per launch: half a buffer read twice (own + peer copy) and written twice
+    report("grad_reduce[emulated world 2 on one GPU]", ms, bytes_=4.0 * (n // 2) * 2, buffer_MiB=a.m, correct=ok)
+
+
+def probe_moe_push_local(a, flush):
+    """The MoE dispatch push on ONE GPU: ``--m`` token rows of width ``--n`` gathered through a random (token, k) order
+    and stored into 8 destination buffers that all live on this GPU."""
+    import ctypes as C
+
+    from ..ops import _native as nat
+    from ..parallel import ep_fused  # noqa: F401  (declares the prototype)
+
+    rows, H, ws = a.m, a.n, 8
+    src = torch.randn(rows, H, device="cuda").bfloat16()
+    index = torch.randperm(rows, device="cuda").int()
+    per = rows // ws
+    seg = [min(i * per, rows) for i in range(ws)] + [rows]
+    dst = [torch.empty(seg[d + 1] - seg[d], H, device="cuda", dtype=torch.bfloat16) for d in range(ws)]
+    seg_arr = (C.c_int * (ws + 1))(*seg)
+    dst_arr = (C.c_void_p * ws)(*[t.data_ptr() for t in dst])
+
+    def run():
+        nat.check(nat.lib().csb_moe_push(src.data_ptr(), index.data_ptr(), rows, H, C.cast(seg_arr, C.c_void_p),
+                                         C.cast(dst_arr, C.c_void_p), ws, nat.stream()), "csb_moe_push")
+
+    run()
+    torch.cuda.synchronize()
+    ok = bool(torch.equal(torch.cat(dst), src[index.long()]))
+    ms = timeit(run, a.iters, a.warmup, flush)
+    report("moe_push[8 destinations on one GPU]", ms, bytes_=2.0 * rows * H * 2, rows=rows, H=H, correct=ok)
+
+
+def probe_attn_fwd_pulled(a, flush):
+    """The context-parallel forward on ONE GPU: K / V in two segments, the query rows of the later half; the first
+    ``--reducers`` thread blocks copy the other segment, the query tiles read the copy (all memory local)."""
+    from ..parallel.cp_fused import attention_segments_local, padded_layout
+
+    B, S, Hq, Hk, D = a.batch, a.seq, a.heads, a.kv_heads, a.head_dim
+    half = S // 2
+    q = torch.randn(B, half, Hq, D, device="cuda").bfloat16()
+    ks = [torch.randn(B, half, Hk, D, device="cuda").bfloat16() for _ in range(2)]
+    vs = [torch.randn(B, half, Hk, D, device="cuda").bfloat16() for _ in range(2)]
+    _, total = padded_layout([half, half])
+    qp = (half + torch.arange(half, dtype=torch.int32, device="cuda"))[None].expand(B, -1).contiguous()
+    kp = torch.arange(total, dtype=torch.int32, device="cuda")[None].expand(B, -1).contiguous()
+    mask = A.AttnMask(mode=A.MASK_CAUSAL, q_pos=qp, k_pos=kp)
+    mask.classes(B, half, total, q.device)
+    ms_direct = timeit(lambda: attention_segments_local(q, ks, vs, mask, my_seg=1), a.iters, a.warmup, flush)
+    ms = timeit(lambda: attention_segments_local(q, ks, vs, mask, my_seg=1, pull_ctas=a.reducers), a.iters, a.warmup, flush)
+    flops = 4.0 * B * Hq * half * D * (half + half / 2)
+    report("attn_fwd_seg[2 segments on one GPU, pulled]", ms, flops=flops, S=S, pull_ctas=a.reducers,
+           direct_ms=round(ms_direct, 4))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "elementwise", "gemm_ar_local", "adamw", "all"])
+    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "elementwise", "gemm_ar_local", "adamw", "grad_reduce_local",
+                                     "moe_push_local", "attn_fwd_pulled", "all"])
     ap.add_argument("--reducers", type=int, default=16)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
@@ -205,7 +285,8 @@ def main():
     todo = ["gemm", "attn_fwd", "attn_bwd", "elementwise"] if a.what == "all" else [a.what]
     for t in todo:
         {"gemm": probe_gemm, "attn_fwd": probe_attn_fwd, "attn_bwd": probe_attn_bwd, "elementwise": probe_elementwise,
-         "gemm_ar_local": probe_gemm_ar_local, "adamw": probe_adamw}[t](a, flush)
+         "gemm_ar_local": probe_gemm_ar_local, "adamw": probe_adamw, "grad_reduce_local": probe_grad_reduce_local,
+         "moe_push_local": probe_moe_push_local, "attn_fwd_pulled": probe_attn_fwd_pulled}[t](a, flush)
     from ..ops import _native as nat
 
     nat.check_status()
