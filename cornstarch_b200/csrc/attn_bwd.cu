@@ -608,10 +608,10 @@ CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void*
     p.dk_stride_s[i] = kv->dk_stride_s[g]; p.dk_stride_b[i] = kv->dk_stride_b[g];
     p.dv_stride_s[i] = kv->dv_stride_s[g]; p.dv_stride_b[i] = kv->dv_stride_b[g];
   }
-  // 16 compute warps (two more per scheduler to hide the tensor-memory load latency) unless the environment says 8
+  // 8 compute warps, or 16 (two more per scheduler to hide the tensor-memory load latency) when the environment asks
   static const bool wide = []() {
     const char* e = getenv("CORNSTARCH_B200_ATTN_BWD_WARPS");
-    return !(e && atoi(e) == 8);
+    return e && atoi(e) == 16;
   }();
   CUtensorMap tdq;
   {
