@@ -103,9 +103,12 @@ class ExpertParallel:
         fused = self._fused(x2)
         if fused is not None:
             return self._forward_fused(fused, x2, weights, order, token_of, counts, experts, act)
-        recv_counts = self.exchange_counts(counts)
-        # one host read for both directions' split sizes
-        both = torch.cat([counts.view(self.ws, self.local).sum(1), recv_counts.reshape(-1)]).tolist()
+        both = _replayed_counts()
+        if both is None:
+            recv_counts = self.exchange_counts(counts)
+            # one host read for both directions' split sizes
+            both = torch.cat([counts.view(self.ws, self.local).sum(1), recv_counts.reshape(-1)]).tolist()
+            _record_counts(both)
         send_splits = both[: self.ws]
         rc = [both[self.ws + s * self.local : self.ws + (s + 1) * self.local] for s in range(self.ws)]
         recv_splits = [sum(r) for r in rc]
@@ -140,6 +143,27 @@ class ExpertParallel:
         return out
 
 
+def _replayed_counts():
+    """Inside the recomputation of a layer the routing is the one of the first forward pass: the token counts that pass
+    exchanged (a collective plus a host read) are taken from the recomputation tape instead of being exchanged again."""
+    from ..ops.attention import _TAPE
+
+    tape = getattr(_TAPE, "cur", None)
+    if tape is None or tape.mode != "replay":
+        return None
+    tag, value = tape.items.pop(0)
+    assert tag == "ep_counts", "recomputation tape out of order"
+    return value
+
+
+def _record_counts(value) -> None:
+    from ..ops.attention import _TAPE
+
+    tape = getattr(_TAPE, "cur", None)
+    if tape is not None and tape.mode == "record":
+        tape.items.append(("ep_counts", value))
+
+
 def _ep_fused_methods():
     def _fused(self, x2):
         from ..ops import _native as nat
@@ -156,9 +180,12 @@ def _ep_fused_methods():
 
         T, H = x2.shape
         k = order.numel() // T
-        everyone = [torch.empty_like(counts) for _ in range(self.ws)]
-        dist.all_gather(everyone, counts, group=self.group)  # counts[src][expert]: placement of every rank's rows
-        mat = torch.stack(everyone).view(self.ws, self.ws, self.local).tolist()  # [src][dst][local expert]
+        mat = _replayed_counts()
+        if mat is None:
+            everyone = [torch.empty_like(counts) for _ in range(self.ws)]
+            dist.all_gather(everyone, counts, group=self.group)  # counts[src][expert]: placement of every rank's rows
+            mat = torch.stack(everyone).view(self.ws, self.ws, self.local).tolist()  # [src][dst][local expert]
+            _record_counts(mat)
         send = [[sum(mat[s][d]) for d in range(self.ws)] for s in range(self.ws)]
         # every rank may receive at most all (token, k) pairs of the group; sized once from the first call's total
         total_pairs = sum(sum(r) for r in send)
