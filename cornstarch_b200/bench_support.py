@@ -101,11 +101,16 @@ class SingleDeviceTrainer:
                     g.div_(self.world)
 
     def _run(self, batches):
+        import contextlib
+
         total = None
-        for b in batches:
-            out = self.model(**b)
-            loss = out.loss / self.n_micro
-            loss.backward()
+        for i, b in enumerate(batches):
+            # the last micro-batch's backward pass overlaps the gradient reduction of the layers it has finished
+            last = i == len(batches) - 1 and self.world > 1 and self.overlap_reduce and hasattr(self.opt, "overlapped_reduce")
+            with (self.opt.overlapped_reduce() if last else contextlib.nullcontext()):
+                out = self.model(**b)
+                loss = out.loss / self.n_micro
+                loss.backward()
             total = loss.detach() if total is None else total + loss.detach()
         self.reduce_grads()
         self.opt.step()
@@ -113,6 +118,7 @@ class SingleDeviceTrainer:
         return total
 
     recompute = "every layer"
+    overlap_reduce = True
 
     def tune_recompute(self):
         """Call after one step: layers that fit in the memory left over stop being recomputed."""

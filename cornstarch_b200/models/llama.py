@@ -27,6 +27,7 @@ from ..ops import elementwise as E
 from ..ops.cross_entropy import linear_cross_entropy
 from ..ops.linear import add_adapter_deltas, linear, multi_linear
 from ..parallel import comm
+from ..parallel.dp_fused import layer_input as grad_sync_layer_input
 from .base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, register_model
 
 
@@ -378,6 +379,7 @@ class DecoderModel(PreTrainedModel):
             if self.spec.local_rope and getattr(self.config, "layer_types", None):
                 if self.config.layer_types[layer.self_attn.layer_idx] == "sliding_attention":
                     lrope = self.rotary_emb_local(hidden_states.device, max_pos)
+            grad_sync_layer_input(layer, delta)
             if recompute and seen <= n_recompute:
                 delta, residual, aux = checkpoint_layer(layer, delta, residual, lrope, pos, mask)
             else:

@@ -98,6 +98,7 @@ class FusedAdamW(torch.optim.Optimizer):
 
     # ------------------------------------------------------------------ arena path
     def _build_arena(self):
+        self._overlap, self._overlap_used = None, False
         shard = None
         if self.zero_stage >= 1 and self.dp_group is not None and dist.get_world_size(self.dp_group) > 1:
             shard = (dist.get_rank(self.dp_group), dist.get_world_size(self.dp_group))
@@ -125,6 +126,23 @@ class FusedAdamW(torch.optim.Optimizer):
         """The flat gradient buffers of replicated parameters (what data-parallel reduction works on)."""
         return [r.flat_grad for _, r in self._regions if not r.expert]
 
+    def overlapped_reduce(self, max_ctas: int = 16):
+        """Context manager for the forward + backward pass of a step's LAST micro-batch: the gradients of each decoder
+        layer are averaged over the data-parallel group while the backward pass of the earlier layers still runs;
+        ``reduce_dp_grads()`` afterwards reduces the rest and closes the exchange.  A null context when the peer-memory
+        reducer is not in use (single rank, NCCL path, ZeRO-1)."""
+        import contextlib
+
+        if (not self.use_arena or self.reducer is None or self._sharded or self.dp_group is None
+                or dist.get_world_size(self.dp_group) == 1):
+            return contextlib.nullcontext()
+        from ..parallel.dp_fused import OverlappedGradReduce
+
+        if self._overlap is None:
+            self._overlap = OverlappedGradReduce(self.reducer, self.flat_grads(), max_ctas)
+        self._overlap_used = True
+        return self._overlap
+
     def reduce_dp_grads(self, bucket_bytes: int = 256 << 20) -> bool:
         """Average the replicated gradients over the data-parallel group.  Returns False when there is nothing to do
         here (no group, ZeRO-1 reduces inside ``step``, or the plain per-parameter path is in use)."""
@@ -132,7 +150,11 @@ class FusedAdamW(torch.optim.Optimizer):
             return False
         bufs = self.flat_grads()
         if self.reducer is not None:
-            self.reducer.reduce(bufs)
+            if self._overlap is not None and self._overlap_used:
+                self._overlap.finish()  # part of the buffers was reduced during the backward pass
+                self._overlap_used = False
+            else:
+                self.reducer.reduce(bufs)
             return True
         for flat in bufs:
             step = max(1, bucket_bytes // flat.element_size())

@@ -82,3 +82,116 @@ class FusedGradReducer:
                                           self.flags.data_ptr(), self.events, max_ctas, status.data_ptr(), st), "csb_grad_reduce")
         nat.check(lib.csb_cp_signal(self.done_ptrs.data_ptr(), self.world, self.rank, self.events, st), "csb_cp_signal")
         nat.check(lib.csb_cp_wait(self.flags.data_ptr() + 128, self.world, self.events, status.data_ptr(), st), "csb_cp_wait")
+
+
+class OverlappedGradReduce:
+    """Reduce the gradients of a transformer layer as soon as the layer's backward pass has been enqueued, on a side
+    stream with a few thread blocks, while the backward pass of the layers before it keeps the rest of the GPU busy.
+
+    Used for the last micro-batch of a step (earlier micro-batches only accumulate).  The decoder loop announces every
+    layer's input tensor through :func:`layer_input`; a hook on that tensor fires once the gradient with respect to it
+    exists, i.e. after every backward node of the layer - and with it every weight-gradient kernel - has been issued.
+    ``finish`` reduces what no hook covered (embeddings, head, encoders, norms outside the layers) and closes the
+    exchange; after it the main stream sees averaged gradients everywhere.
+
+    The reference reduces per parameter after the whole step
+    (cornstarch/plugin/multimodal_parallel_plugin/multimodal_parallel_plugin.py:362-384)."""
+
+    current: "OverlappedGradReduce | None" = None
+
+    def __init__(self, reducer: FusedGradReducer, flat_grads: list[torch.Tensor], max_ctas: int = 16):
+        self.reducer, self.flat_grads, self.max_ctas = reducer, flat_grads, max_ctas
+        self.side = torch.cuda.Stream()
+        self.done: list[list[tuple[int, int]]] = [[] for _ in flat_grads]  # reduced element ranges per buffer
+        self.launches = 0
+
+    # ---- context: active while the last micro-batch runs forward and backward
+    def __enter__(self):
+        OverlappedGradReduce.current = self
+        return self
+
+    def __exit__(self, *exc):
+        OverlappedGradReduce.current = None
+        return False
+
+    def _ranges_of(self, layer) -> list[tuple[int, int, int]]:
+        cached = getattr(layer, "_csb_grad_ranges", None)
+        if cached is not None:
+            return cached
+        spans: dict[int, list[int]] = {}
+        for p in layer.parameters():
+            g = getattr(p, "main_grad", None)
+            if g is None:
+                continue
+            for bi, flat in enumerate(self.flat_grads):
+                off = (g.data_ptr() - flat.data_ptr()) // flat.element_size()
+                if 0 <= off < flat.numel() and g.data_ptr() >= flat.data_ptr():
+                    lo = off // 64 * 64
+                    hi = min(flat.numel(), (off + g.numel() + 63) // 64 * 64)
+                    cur = spans.setdefault(bi, [lo, hi])
+                    cur[0], cur[1] = min(cur[0], lo), max(cur[1], hi)
+        out = [(bi, lo, hi) for bi, (lo, hi) in spans.items()]
+        layer._csb_grad_ranges = out
+        return out
+
+    def layer_input(self, layer, tensor: torch.Tensor) -> None:
+        if isinstance(tensor, torch.Tensor) and tensor.requires_grad:
+            tensor.register_hook(lambda grad, layer=layer: self._layer_done(layer))
+
+    def _layer_done(self, layer) -> None:
+        ranges = [r for r in self._ranges_of(layer) if r[2] > r[1]]
+        if not ranges:
+            return
+        ev = torch.cuda.Event()
+        ev.record()
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev)
+            for bi, lo, hi in ranges:
+                self._reduce_range(bi, lo, hi)
+
+    def _reduce_range(self, bi: int, lo: int, hi: int) -> None:
+        r = self.reducer
+        lib, st = nat.lib(), nat.stream()
+        flat = self.flat_grads[bi]
+        mem = r._find(flat)
+        status = nat.status_word(flat.device)
+        r.events += 1
+        nat.check(lib.csb_cp_signal(r.ready_ptrs.data_ptr(), r.world, r.rank, r.events, st), "csb_cp_signal")
+        ptrs = (vp * 8)(*([p + lo * 2 for p in mem.ptrs] + [0] * (8 - r.world)))
+        nat.check(lib.csb_grad_reduce(C.cast(ptrs, vp), r.world, r.rank, hi - lo, 1.0 / r.world, 1, r.flags.data_ptr(), r.events,
+                                      self.max_ctas, status.data_ptr(), st), "csb_grad_reduce")
+        self.done[bi].append((lo, hi))
+        self.launches += 1
+
+    def finish(self) -> None:
+        """Reduce every range no layer hook covered, then wait until all ranks' pushes have landed here."""
+        r = self.reducer
+        ev = torch.cuda.Event()
+        ev.record()
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev)
+            saved, self.max_ctas = self.max_ctas, 0  # the backward pass is over: use the whole GPU
+            for bi, flat in enumerate(self.flat_grads):
+                pos = 0
+                for lo, hi in sorted(self.done[bi]):
+                    if lo > pos:
+                        self._reduce_range(bi, pos, lo)
+                    pos = max(pos, hi)
+                if pos < flat.numel():
+                    self._reduce_range(bi, pos, flat.numel())
+            self.max_ctas = saved
+            lib, st = nat.lib(), nat.stream()
+            status = nat.status_word(self.flat_grads[0].device)
+            nat.check(lib.csb_cp_signal(r.done_ptrs.data_ptr(), r.world, r.rank, r.events, st), "csb_cp_signal")
+            nat.check(lib.csb_cp_wait(r.flags.data_ptr() + 128, r.world, r.events, status.data_ptr(), st), "csb_cp_wait")
+            end = torch.cuda.Event()
+            end.record()
+        torch.cuda.current_stream().wait_event(end)
+        self.done = [[] for _ in self.flat_grads]
+
+
+def layer_input(layer, tensor) -> None:
+    """Called by a model's layer loop: lets an active :class:`OverlappedGradReduce` hook the layer's input."""
+    cur = OverlappedGradReduce.current
+    if cur is not None:
+        cur.layer_input(layer, tensor)

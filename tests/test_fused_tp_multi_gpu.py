@@ -189,3 +189,70 @@ def test_fused_gradient_reduce_two_gpus():
         if p.is_alive():
             p.terminate()
     assert len(results) == 2 and all(r[1] == "ok" for r in results), results
+
+
+def _overlap_worker(rank, world, port, q):
+    """Data-parallel training step of a small decoder: gradients reduced layer by layer during the backward pass equal the
+    gradients reduced by one call after it."""
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        from cornstarch_b200.models.llama import LlamaConfig, LlamaForCausalLM
+        from cornstarch_b200.ops import _native as nat
+        from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
+
+        cfg = LlamaConfig(vocab_size=1024, hidden_size=256, intermediate_size=512, num_hidden_layers=4, num_attention_heads=4,
+                          num_key_value_heads=2, max_position_embeddings=256)
+        ids = torch.randint(0, 1024, (2, 256), generator=torch.Generator().manual_seed(rank)).cuda()
+        grads = {}
+        for mode in ("after", "overlapped"):
+            torch.manual_seed(0)
+            model = LlamaForCausalLM(cfg).cuda().bfloat16()
+            model.gradient_checkpointing_enable({"keep_last_layers": 1})
+            model.train()
+            opt = FusedAdamW(split_decay_groups(model, 0.01), lr=1e-3, dp_group=dist.group.WORLD)
+            assert opt.reducer is not None
+            for step in range(2):  # the second round checks that the counters line up across steps
+                opt.clear_main_grads()
+                if mode == "overlapped":
+                    with opt.overlapped_reduce(max_ctas=8) as sess:
+                        model(input_ids=ids, labels=ids).loss.backward()
+                    assert sess.launches >= 4 * (step + 1), sess.launches
+                else:
+                    model(input_ids=ids, labels=ids).loss.backward()
+                assert opt.reduce_dp_grads()
+                torch.cuda.synchronize()
+            grads[mode] = [g.float().clone() for g in opt.flat_grads()]
+            dist.barrier()
+        for a, b in zip(grads["after"], grads["overlapped"]):
+            assert torch.isfinite(a).all() and a.abs().max() > 0
+            assert torch.equal(a, b), (a - b).abs().max().item()
+        nat.check_status()
+        dist.destroy_process_group()
+        q.put((rank, "ok"))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, traceback.format_exc()))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_overlapped_gradient_reduce_two_gpus():
+    from tests.dist_utils import free_port
+
+    ctx = mp.get_context("spawn")
+    q = ctx.SimpleQueue()
+    port = free_port()
+    procs = [ctx.Process(target=_overlap_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(240)
+    results = []
+    while not q.empty():
+        results.append(q.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+    assert len(results) == 2 and all(r[1] == "ok" for r in results), results
