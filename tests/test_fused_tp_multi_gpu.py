@@ -227,7 +227,8 @@ def _overlap_worker(rank, world, port, q):
             dist.barrier()
         for a, b in zip(grads["after"], grads["overlapped"]):
             assert torch.isfinite(a).all() and a.abs().max() > 0
-            assert torch.equal(a, b), (a - b).abs().max().item()
+            # two backward passes differ in the last bits (the dQ reduce-adds of the attention kernel are unordered)
+            assert (a - b).abs().max().item() <= 5e-3 * a.abs().max().item(), ((a - b).abs().max().item(), a.abs().max().item())
         nat.check_status()
         dist.destroy_process_group()
         q.put((rank, "ok"))
