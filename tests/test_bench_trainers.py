@@ -51,3 +51,25 @@ def test_expert_parallel_trainer():
 
 def test_context_parallel_trainer():
     run_distributed(_cp_worker, 2)
+
+
+def _pipeline_worker(rank, world):
+    """The benchmark's modality-parallel pipeline trainer (encoder stage + LLM stage, tp 2) steps, tunes recomputation
+    (a no-op without a GPU, but through the same group logic) and steps again."""
+    from types import SimpleNamespace
+
+    from cornstarch_b200.bench_parallel import PipelineTrainer
+
+    args = SimpleNamespace(shape="tiny", parallelism="enc1+llm1xtp2", samples_per_gpu=1, microbatch=1)
+    tr = PipelineTrainer(args, rank, world, torch.device("cpu"))
+    l1 = tr.step_device()
+    keep = tr.tune_recompute()
+    assert keep == 0 and "decoder layers kept" in tr.recompute
+    l2 = tr.step_device()
+    if tr.is_last:
+        assert torch.isfinite(l1) and torch.isfinite(l2)
+    assert tr.global_batch == world
+
+
+def test_pipeline_trainer_with_recompute_tuning():
+    run_distributed(_pipeline_worker, 4)
