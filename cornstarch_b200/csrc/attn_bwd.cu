@@ -54,6 +54,7 @@ struct AttnBwdParams {
   __nv_bfloat16* dV[CSB_MAX_SEG];
   long dk_stride_b[CSB_MAX_SEG], dk_stride_s[CSB_MAX_SEG], dv_stride_b[CSB_MAX_SEG], dv_stride_s[CSB_MAX_SEG];
   int* status;
+  int dbg;  // timing experiments only (results are wrong when set): bit 0 no reduce-add, 1 no dQ staging, 2 no exp, 3 no dS^T store, 4 no P^T store
   SegInfo seg;
 };
 
@@ -390,11 +391,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (lane == 0) tma_store_wait_read<0>();  // the previous block has left the staging buffer
       __syncwarp();
       float* stage = reinterpret_cast<float*>(smem + L::DQ_OFF + cw * (COLS * 128));
+      if (!(p.dbg & 2)) {
 #pragma unroll
-      for (int c = 0; c < COLS; ++c) stage[c * 32 + lane] = __uint_as_float(v[c]);
+        for (int c = 0; c < COLS; ++c) stage[c * 32 + lane] = __uint_as_float(v[c]);
+      }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0 && quarter * 32 < p.D) {
+      if (lane == 0 && quarter * 32 < p.D && !(p.dbg & 3)) {
         tma_reduce_add_4d(&tm_dq, stage, quarter * 32, ph, pi * BW_BQ + col0, b);  // box: 32 d x COLS q
         tma_store_commit();
       }
@@ -441,7 +444,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
         for (int y = 0; y < 4; ++y)
-          pv[x4 * 4 + y] = fast_exp2(fmaf(__uint_as_float(sv[x4 * 4 + y]), p.scale_log2, -ls[y]));
+          pv[x4 * 4 + y] = (p.dbg & 4) ? fmaf(__uint_as_float(sv[x4 * 4 + y]), p.scale_log2, -ls[y])
+                                       : fast_exp2(fmaf(__uint_as_float(sv[x4 * 4 + y]), p.scale_log2, -ls[y]));
       }
       if (c == 1) {
 #pragma unroll
@@ -473,7 +477,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t pk[COLS / 2];
 #pragma unroll
         for (int x = 0; x < COLS / 2; ++x) pk[x] = pack_bf16x2(pv[2 * x], pv[2 * x + 1]);
-        tmem_st_cols<COLS / 2>(tmem_base + (it & 1) * 64 + col0 + lane_addr, pk);
+        if (!(p.dbg & 16)) tmem_st_cols<COLS / 2>(tmem_base + (it & 1) * 64 + col0 + lane_addr, pk);
       }
 #pragma unroll
       for (int pc = 0; pc < COLS / 8; ++pc) {
@@ -482,7 +486,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         w.y = pack_bf16x2(ds[pc * 8 + 2], ds[pc * 8 + 3]);
         w.z = pack_bf16x2(ds[pc * 8 + 4], ds[pc * 8 + 5]);
         w.w = pack_bf16x2(ds[pc * 8 + 6], ds[pc * 8 + 7]);
-        *reinterpret_cast<uint4*>(smem + L::DST_OFF + sw128_offset(r, half * (COLS / 8) + pc)) = w;
+        if (!(p.dbg & 8)) *reinterpret_cast<uint4*>(smem + L::DST_OFF + sw128_offset(r, half * (COLS / 8) + pc)) = w;
       }
       tmem_st_wait();
       fence_proxy_async_smem();
@@ -591,6 +595,8 @@ CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void*
   p.cls = reinterpret_cast<const int8_t*>(cls);
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
   p.status = status;
+  static const int dbg = []() { const char* e = getenv("CORNSTARCH_B200_ATTN_BWD_DEBUG"); return e ? atoi(e) : 0; }();
+  p.dbg = dbg;
   fill_seg_info(&p.seg, kv, BW_BKV);
   if (p.seg.tile_start[kv->n_seg] != p.nK) return CSB_ERR_BAD_ARG;
   CUtensorMap tq, tdo;
