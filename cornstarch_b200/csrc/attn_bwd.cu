@@ -54,6 +54,7 @@ struct AttnBwdParams {
   __nv_bfloat16* dV[CSB_MAX_SEG];
   long dk_stride_b[CSB_MAX_SEG], dk_stride_s[CSB_MAX_SEG], dv_stride_b[CSB_MAX_SEG], dv_stride_s[CSB_MAX_SEG];
   int* status;
+  int kj_slowest;  // block order: 1 = key block slowest (masks that leave key blocks unequal work), 0 = key block fastest
   int dbg;  // timing experiments only (results are wrong when set): bit 0 no reduce-add, 1 no dQ staging, 2 no exp, 3 no dS^T store, 4 no P^T store
   SegInfo seg;
 };
@@ -170,7 +171,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   int8_t* tile_cls = reinterpret_cast<int8_t*>(smem + L::LIST_OFF + L::MAX_TILES * 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kj = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  // One-dimensional grid, key block slowest: under causal masks the first key blocks meet the most query tiles, so
+  // the heavy blocks of every head start first and the light ones fill the tail.
+  // (With a full mask every block is equally heavy; key block fastest then keeps the Q / dO tiles of few heads in L2.)
+  const int n_hb = p.Hk * p.B;
+  const int hb = p.kj_slowest ? blockIdx.x % n_hb : blockIdx.x / p.nK;
+  const int kj = p.kj_slowest ? blockIdx.x / n_hb : blockIdx.x % p.nK;
+  const int hk = hb % p.Hk, b = hb / p.Hk;
   const int group = p.Hq / p.Hk;
   const int k0 = kj * BW_BKV;                              // index into k_bits / k_pos (padded gathered space)
   const int sg = seg_of_tile(p.seg, kj);                   // which K/V segment (rank) this key block belongs to
@@ -597,6 +604,7 @@ CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void*
   p.status = status;
   static const int dbg = []() { const char* e = getenv("CORNSTARCH_B200_ATTN_BWD_DEBUG"); return e ? atoi(e) : 0; }();
   p.dbg = dbg;
+  p.kj_slowest = mask_mode != MASK_FULL;
   fill_seg_info(&p.seg, kv, BW_BKV);
   if (p.seg.tile_start[kv->n_seg] != p.nK) return CSB_ERR_BAD_ARG;
   CUtensorMap tq, tdo;
@@ -634,7 +642,9 @@ CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void*
       return launch_result();
     attr = true;
   }
-  dim3 grid(p.nK, Hk, B);
+  const long n_blocks = (long)p.nK * Hk * B;
+  if (n_blocks > 0x7fffffffL) return CSB_ERR_TOO_LARGE;
+  dim3 grid((unsigned)n_blocks);
   if (wide)
     attn_bwd_kernel<16><<<grid, BwdCfg<16>::THREADS, BwdSmem::DYN_BYTES, s>>>(tq, kvm, tdo, tdq, p);
   else

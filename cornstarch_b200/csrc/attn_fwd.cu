@@ -159,9 +159,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     return;
   }
   const int lin = blockIdx.x - n_pull;
-  // heaviest (last) query tiles first: under causal masks they have the most key blocks
-  const int qi = p.nQ - 1 - lin % p.nQ;
-  const int h = (lin / p.nQ) % p.Hq, b = lin / (p.nQ * p.Hq);
+  // Heaviest (last) query tiles first, over all heads and batch entries: under causal masks they have the most key
+  // blocks, and the lightest tiles of every head fill the tail of the grid.
+  const int hb = lin % (p.Hq * p.B);
+  const int qi = p.nQ - 1 - lin / (p.Hq * p.B);
+  const int h = hb % p.Hq, b = hb / p.Hq;
   const int hk = h / (p.Hq / p.Hk);
   const int q0 = qi * AT_BM;
   {
