@@ -118,3 +118,20 @@ class OptimizerWrapper:
 
     def unwrap(self):
         return self.optim
+
+
+class HybridParallelNaiveOptimizer(OptimizerWrapper):
+    """The wrapper under the name the reference's plugin uses for fp32 / bf16 training."""
+
+    def __init__(self, optim, model=None, max_norm: float = 0.0, tp_group=None, pp_group=None, **kw):
+        super().__init__(optim, model, max_norm, None, tp_group, pp_group)
+
+
+class HybridParallelAMPOptimizer(OptimizerWrapper):
+    """The wrapper under the name the reference's plugin uses for mixed precision: ``precision="fp16"`` turns the dynamic
+    loss scale on (``initial_scale``, ``min_scale``, ``growth_factor``, ``backoff_factor``, ``growth_interval``,
+    ``hysteresis``, ``max_scale`` as in the reference's constructor)."""
+
+    def __init__(self, optim, model=None, precision: str = "fp16", max_norm: float = 0.0, tp_group=None, pp_group=None,
+                 **scaler_kwargs):
+        super().__init__(optim, model, max_norm, precision, tp_group, pp_group, scaler_kwargs or None)
