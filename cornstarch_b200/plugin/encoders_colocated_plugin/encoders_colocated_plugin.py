@@ -14,13 +14,13 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
-from ..multimodal.modeling import ModalEncoderModule, MultimodalModel, _first_tensor
-from ..parallel.mesh import MultiModalProcessGroupMesh
-from ..parallel.schedule import MultimodalEncoderTrainingOneForwardOneBackwardSchedule
-from ..parallel.stage_manager import MultiModalPipelineStageManager
-from ..pipeline_template import PipelineTemplate
-from .modal_parallel_plugin import ModalParallelPlugin, _FixedHeld
-from .multimodal_parallel_plugin import PRECISION, MultimodalParallelModule, MultimodalParallelPlugin, _Dropped, _DroppedLM
+from ...multimodal.modeling import ModalEncoderModule, MultimodalModel, _first_tensor
+from ...parallel.mesh import MultiModalProcessGroupMesh
+from ...parallel.schedule import MultimodalEncoderTrainingOneForwardOneBackwardSchedule
+from ...parallel.stage_manager import MultiModalPipelineStageManager
+from ...pipeline_template import PipelineTemplate
+from ..modal_parallel_plugin import ModalParallelPlugin, _FixedHeld
+from ..multimodal_parallel_plugin import PRECISION, MultimodalParallelModule, MultimodalParallelPlugin, _Dropped, _DroppedLM
 
 
 class EncodersColocatedProcessGroupMesh(MultiModalProcessGroupMesh):

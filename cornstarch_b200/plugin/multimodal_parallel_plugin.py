@@ -26,6 +26,7 @@ from ..ops import attention as A
 from ..optim.fused_adamw import FusedAdamW, split_decay_groups
 from ..optim.wrapper import OptimizerWrapper
 from ..parallel.mesh import MultiModalProcessGroupMesh
+from ..parallel.p2p import MultimodalPipelineP2PCommunication  # noqa: F401  (part of this module's public names)
 from ..parallel.schedule import MultimodalEncoderTrainingOneForwardOneBackwardSchedule
 from ..parallel.stage_manager import MultiModalPipelineStageManager
 from ..pipeline_template import PipelineTemplate
