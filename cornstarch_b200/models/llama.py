@@ -337,6 +337,10 @@ class DecoderModel(PreTrainedModel):
         for layer in self.layers:
             if not is_released(layer):
                 layer.self_attn.pc = pc
+                if layer.self_attn.spec.qk_norm and pc is not None and pc.tp_size > 1:
+                    # q_norm / k_norm weights are shared by all heads but see only this rank's heads
+                    layer.self_attn.q_norm.grad_sum_group = pc.tp_group
+                    layer.self_attn.k_norm.grad_sum_group = pc.tp_group
 
     def embed(self, input_ids, feats=None, src=None):
         h = self.embed_tokens(input_ids, feats, src)

@@ -248,9 +248,15 @@ class RMSNorm(nn.Module):
         self.eps, self.weight_offset = eps, weight_offset
         init = torch.zeros if weight_offset else torch.ones
         self.weight = nn.Parameter(init(hidden_size, device=device, dtype=dtype))
+        # A norm over the head dimension applied to the heads of ONE tensor-parallel rank (q_norm / k_norm) sees only
+        # part of the heads: its weight gradient is the sum over the group.  The owner sets the group.
+        self.grad_sum_group = None
 
     def forward(self, x, residual=None):
-        return E.rms_norm(x, self.weight, self.eps, residual, self.weight_offset)
+        w = self.weight
+        if self.grad_sum_group is not None:
+            w = comm.reduce_backward(w, self.grad_sum_group)  # identity forward, all-reduce of the gradient
+        return E.rms_norm(x, w, self.eps, residual, self.weight_offset)
 
 
 class LayerNorm(nn.Module):
