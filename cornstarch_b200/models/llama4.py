@@ -27,6 +27,7 @@ from ..ops import elementwise as E
 from ..ops.cross_entropy import linear_cross_entropy
 from ..ops.gemm import gemm
 from ..ops.linear import linear, multi_linear
+from ..parallel import comm
 from ..utils.recompute import checkpoint_layer
 from .base import ModelOutput, PreTrainedModel, is_released, register_model
 from .llama import DecoderConfig
@@ -256,6 +257,14 @@ class Llama4ForCausalLM(PreTrainedModel):
         super().__init__(config)
         self.model = Llama4TextModel(config)
         self.lm_head = cnn.Linear(config.hidden_size, config.vocab_size, bias=False)
+        self.vocab_start = 0    # first vocabulary id of the local LM-head shard under tensor parallelism
+        self.valid_vocab = None  # rows of the local shard that are real vocabulary (the rest is padding)
+        self.tp_group = None
+
+    def set_parallel_context(self, pc):
+        self.tp_group = pc.tp_group if pc is not None else None
+        if hasattr(self.model, "set_parallel_context"):
+            self.model.set_parallel_context(pc)
 
     @classmethod
     def module_names(cls, config):
@@ -274,9 +283,16 @@ class Llama4ForCausalLM(PreTrainedModel):
         if labels is not None:
             tgt = torch.full_like(labels, -100)
             tgt[:, :-1] = labels[:, 1:]
-            res["loss"] = linear_cross_entropy(h, self.lm_head.weight, tgt)
+            w = self.lm_head.weight
+            if self.valid_vocab is not None and self.valid_vocab < w.shape[0]:
+                w = w[: self.valid_vocab]
+            tp = self.tp_group if (self.tp_group is not None and comm._world(self.tp_group) > 1) else None
+            h_in = comm.reduce_backward(h, tp) if tp is not None else h  # each vocabulary shard yields a partial dh
+            res["loss"] = linear_cross_entropy(h_in, w, tgt, tp_group=tp, vocab_start=self.vocab_start)
         else:
-            res["logits"] = linear(h, self.lm_head.weight)
+            tp = self.tp_group if (self.tp_group is not None and comm._world(self.tp_group) > 1) else None
+            logits = linear(comm.reduce_backward(h, tp) if tp is not None else h, self.lm_head.weight)
+            res["logits"] = comm.gather_forward_split_backward(logits, logits.dim() - 1, tp) if tp is not None else logits
         return res
 
 

@@ -101,7 +101,7 @@ class Dinov2Layer(nn.Module):
     def forward(self, x, mask):
         a = self.attention.attention
         biases = [a.query.bias, a.key.bias, a.value.bias] if a.query.bias is not None else None
-        qkv = multi_linear(self.norm1(x), [a.query.weight, a.key.weight, a.value.weight], biases)
+        qkv = multi_linear(a.query.input_hook(self.norm1(x)), [a.query.weight, a.key.weight, a.value.weight], biases)
         o = self.attention.output.dense(_attend(qkv, self.num_heads, self.head_dim, mask, self.attn_impl))
         x = x + self.layer_scale1(o)
         h = self.norm2(x)
@@ -209,7 +209,7 @@ class EvaCLIPEncoderLayer(nn.Module):
         zero = lambda: torch.zeros(H, dtype=h.dtype, device=h.device)  # noqa: E731
         bs = [a.q_proj.bias, a.k_proj.bias, a.v_proj.bias]
         biases = None if all(b is None for b in bs) else [b if b is not None else zero() for b in bs]
-        return multi_linear(h, [a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], biases)
+        return multi_linear(a.q_proj.input_hook(h), [a.q_proj.weight, a.k_proj.weight, a.v_proj.weight], biases)
 
     def forward(self, x, mask):
         h = x if self.post else self.layer_norm1(x)
@@ -419,11 +419,11 @@ class PixtralAttentionLayer(nn.Module):
 
     def forward(self, x, mask, rope=None, pos=None):
         a, f = self.attention, self.feed_forward
-        qkv = multi_linear(self.attention_norm(x), [a.q_proj.weight, a.k_proj.weight, a.v_proj.weight])
+        qkv = multi_linear(a.q_proj.input_hook(self.attention_norm(x)), [a.q_proj.weight, a.k_proj.weight, a.v_proj.weight])
         if rope is not None:
             qkv = E.rope_(qkv, rope[0], rope[1], pos, 2 * self.num_heads, self.head_dim)
         x = x + a.o_proj(_attend(qkv, self.num_heads, self.head_dim, mask, self.attn_impl))
-        gu = multi_linear(self.ffn_norm(x), [f.gate_proj.weight, f.up_proj.weight])
+        gu = multi_linear(f.gate_proj.input_hook(self.ffn_norm(x)), [f.gate_proj.weight, f.up_proj.weight])
         return x + f.down_proj(E.glu(gu, self.act))
 
 

@@ -49,6 +49,28 @@ def _build(family):
     if family == "whisper":
         return W.WhisperEncoder(W.WhisperConfig(num_mel_bins=8, d_model=64, encoder_layers=2, encoder_attention_heads=4,
                                                 encoder_ffn_dim=128, max_source_positions=10)), "audio"
+    if family == "gemma3":
+        return L.DecoderForCausalLM(L.Gemma3TextConfig(**KW, head_dim=16, query_pre_attn_scalar=16,
+                                                       layer_types=["sliding_attention", "full_attention"])), "text"
+    if family == "qwen3_moe":
+        return M.MoeForCausalLM(M.Qwen3MoeConfig(**KW, head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32)), "text"
+    if family == "llama4":
+        from cornstarch_b200.models.llama4 import Llama4ForCausalLM, Llama4TextConfig
+
+        return Llama4ForCausalLM(Llama4TextConfig(vocab_size=128, hidden_size=64, intermediate_size=48, intermediate_size_mlp=128,
+                                                  num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                                                  num_local_experts=4, num_experts_per_tok=1, interleave_moe_layer_step=2,
+                                                  max_position_embeddings=64, attention_chunk_size=64)), "text"
+    if family == "internvit":
+        return X.InternVisionModel(X.InternVisionConfig(**vis, qk_normalization=False)), "image"
+    if family == "evaclip":
+        return X.EvaCLIPVisionModel(X.EvaCLIPVisionConfig(**vis)), "image"
+    if family == "pixtral":
+        return X.PixtralVisionModel(X.PixtralVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                                          num_attention_heads=4, image_size=56, patch_size=14, head_dim=16)), "image56"
+    if family == "qwen2_audio":
+        return W.Qwen2AudioEncoder(W.Qwen2AudioEncoderConfig(num_mel_bins=8, d_model=64, encoder_layers=2, encoder_attention_heads=4,
+                                                             encoder_ffn_dim=128, max_source_positions=10)), "audio"
     raise KeyError(family)
 
 
@@ -56,7 +78,7 @@ def _run(model, kind, x):
     if kind == "text":
         out = model(input_ids=x, labels=x)
         return out.loss
-    if kind == "image":
+    if kind in ("image", "image56"):
         out = model(pixel_values=x)
     else:
         out = model(input_features=x)
@@ -78,6 +100,8 @@ def _worker(rank, world, family):
         x = torch.randint(0, 128, (2, 24), generator=g)
     elif kind == "image":
         x = torch.randn(2, 3, 28, 28, generator=g, requires_grad=True)
+    elif kind == "image56":
+        x = torch.randn(2, 3, 56, 56, generator=g, requires_grad=True)
     else:
         x = torch.randn(2, 8, 20, generator=g, requires_grad=True)
     xr = x.detach().clone().requires_grad_(x.requires_grad) if x.is_floating_point() else x
@@ -93,7 +117,7 @@ def _worker(rank, world, family):
     assert abs(loss.item() - ref_loss.item()) < 2e-4 * max(1.0, abs(ref_loss.item())), (family, loss.item(), ref_loss.item())
     loss.backward()
     if x.is_floating_point():
-        assert torch.allclose(x.grad, xr.grad, atol=1e-5, rtol=1e-3), (x.grad - xr.grad).abs().max()
+        assert torch.allclose(x.grad, xr.grad, atol=5e-5, rtol=1e-3), (x.grad - xr.grad).abs().max()
     checked = 0
     ref_params = dict(ref.named_parameters())
     for n, p in model.named_parameters():
@@ -106,6 +130,7 @@ def _worker(rank, world, family):
 
 
 @pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "phi3", "mixtral", "opt", "bert",
-                                    "siglip", "clip", "vit", "dinov2", "whisper"])
+                                    "siglip", "clip", "vit", "dinov2", "whisper", "gemma3", "qwen3_moe", "llama4", "internvit",
+                                    "evaclip", "qwen2_audio", "pixtral"])
 def test_tp2_matches_unsharded(family):
     run_distributed(_worker, 2, family)
