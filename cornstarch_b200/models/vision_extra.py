@@ -459,6 +459,15 @@ class PixtralVisionModel(_VisionBase):
             side = self.patch_positional_embedding.side
             hh, ww = torch.meshgrid(torch.arange(gh, device=x.device), torch.arange(gw, device=x.device), indexing="ij")
             position_ids = (hh * side + ww).reshape(1, -1).expand(B, -1).int().contiguous()
+            group = getattr(self, "_cp_group", None)
+            if group is not None:
+                # context parallelism: contiguous token chunks per rank, and with them their 2-D rotary positions
+                import torch.distributed as dist
+
+                from ..parallel import comm
+
+                x = comm.split_forward_gather_backward(x, 1, group)
+                position_ids = torch.tensor_split(position_ids, dist.get_world_size(group), dim=1)[dist.get_rank(group)].contiguous()
         else:
             x = hidden_states
         rope = self.patch_positional_embedding.tables(x.device)

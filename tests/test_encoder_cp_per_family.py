@@ -1,0 +1,77 @@
+"""Context parallelism of the encoders per family (2 gloo ranks): tokens split uniformly after the embeddings, K/V gathered
+for full attention; the gathered output equals the unsharded encoder's, and so does the gradient of the input."""
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from tests.dist_utils import run_distributed
+
+FAMILIES = ["siglip", "clip", "vit", "dinov2", "evaclip", "pixtral", "whisper", "qwen2_audio"]
+
+
+def _features(model, kind, x):
+    out = model(pixel_values=x) if kind.startswith("image") else model(input_features=x)
+    return out["last_hidden_state"] if isinstance(out, dict) else out[0]
+
+
+def _check(ref, model, kind, x, world):
+    from cornstarch_b200.parallel import comm
+    from cornstarch_b200.shardformer.shard.shard_config import ShardConfig
+    from cornstarch_b200.shardformer.shard.shardformer import ShardFormer
+
+    xr = x.clone().requires_grad_(True)
+    want = _features(ref, kind, xr)
+    wgt = torch.randn(want.shape, generator=torch.Generator().manual_seed(9))
+    (want.float() * wgt).sum().backward()
+    sc = ShardConfig(sequence_parallel_process_group=dist.group.WORLD, enable_sequence_parallelism=True,
+                     sequence_parallelism_mode="ring_attn", enable_tensor_parallelism=False, extra_kwargs={"device": "cpu"})
+    ShardFormer(sc).optimize(model)
+    xs = x.clone().requires_grad_(True)
+    local = _features(model, kind, xs)
+    assert local.shape[1] < want.shape[1], "the encoder did not split its tokens"
+    full = comm.gather_forward_split_backward(local, 1, dist.group.WORLD)
+    assert torch.allclose(full, want, atol=2e-4, rtol=1e-3), (full - want).abs().max()
+    (full.float() * wgt).sum().backward()
+    gx = xs.grad  # the split after the embeddings gathers the token gradients of all ranks in its backward pass
+    err, ref_max = (gx - xr.grad).abs().max().item(), xr.grad.abs().max().item()
+    assert ref_max > 0 and err <= 2e-3 * ref_max, (err, ref_max)
+
+
+def _worker2(rank, world, family):
+    big = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=224, patch_size=14)
+    from cornstarch_b200.models import vision as V
+    from cornstarch_b200.models import vision_extra as X
+    from cornstarch_b200.models import whisper as W
+
+    def build():
+        if family == "siglip":
+            return V.SiglipVisionModel(V.SiglipVisionConfig(**big)), "image"
+        if family == "clip":
+            return V.CLIPVisionModel(V.CLIPVisionConfig(**big)), "image"
+        if family == "vit":
+            return V.ViTModel(V.ViTConfig(**big)), "image"
+        if family == "dinov2":
+            return X.Dinov2Model(X.Dinov2Config(**big)), "image"
+        if family == "evaclip":
+            return X.EvaCLIPVisionModel(X.EvaCLIPVisionConfig(**big)), "image"
+        if family == "pixtral":
+            return X.PixtralVisionModel(X.PixtralVisionConfig(**big, head_dim=16)), "image"
+        cfg = dict(num_mel_bins=8, d_model=64, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=128, max_source_positions=300)
+        if family == "whisper":
+            return W.WhisperEncoder(W.WhisperConfig(**cfg)), "audio"
+        return W.Qwen2AudioEncoder(W.Qwen2AudioEncoderConfig(**cfg)), "audio"
+
+    torch.manual_seed(0)
+    ref, kind = build()
+    torch.manual_seed(0)
+    model, _ = build()
+    model.load_state_dict(ref.state_dict())
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 3, 224, 224, generator=g) if kind == "image" else torch.randn(2, 8, 600, generator=g)
+    _check(ref, model, kind, x, world)
+
+
+@pytest.mark.parametrize("family", FAMILIES)
+def test_encoder_ring_attn_matches_unsharded(family):
+    run_distributed(_worker2, 2, family)
