@@ -152,3 +152,44 @@ def test_llama_ring_attn_matches_single_device(dist_mode):
 
 def test_llama_ulysses_matches_single_device():
     run_distributed(_llama_sp_worker, 2, "all_to_all", "uniform")
+
+
+def _family_sp_worker(rank, world, family, sp_mode):
+    """Other decoder families through the same two sequence-parallel modes as Llama above."""
+    from cornstarch_b200.shardformer.shard.shard_config import ShardConfig
+    from cornstarch_b200.shardformer.shard.shardformer import ShardFormer
+    from tests.test_policy_tp_numerics import _build
+
+    torch.manual_seed(0)
+    ref, _ = _build(family)
+    torch.manual_seed(0)
+    model, _ = _build(family)
+    model.load_state_dict(ref.state_dict())
+    S = 512
+    ids = torch.randint(0, 128, (2, S), generator=torch.Generator().manual_seed(3))
+    ref.config.max_position_embeddings = model.config.max_position_embeddings = S
+    ref_out = ref(input_ids=ids, labels=ids)
+    ref_out.loss.backward()
+    sc = ShardConfig(sequence_parallel_process_group=dist.group.WORLD, enable_sequence_parallelism=True,
+                     sequence_parallelism_mode=sp_mode, context_parallel_distribution_mode="uniform",
+                     enable_tensor_parallelism=False, extra_kwargs={"device": "cpu"})
+    ShardFormer(sc).optimize(model)
+    out = model(input_ids=ids, labels=ids)
+    out.loss.backward()
+    tot = out.loss.detach().clone()
+    dist.all_reduce(tot)
+    assert abs(tot.item() / world - ref_out.loss.item()) < 2e-4 * max(1.0, abs(ref_out.loss.item())), (tot.item() / world, ref_out.loss.item())
+    for (n, p), (_, rp) in zip(model.named_parameters(), ref.named_parameters()):
+        if p.grad is None and rp.grad is None:
+            continue
+        g = p.grad.clone()
+        dist.all_reduce(g)
+        g /= world
+        err, scale = (g - rp.grad).abs().max().item(), rp.grad.abs().max().item()
+        assert err <= 2e-3 * scale + 1e-6, (family, sp_mode, n, err, scale)
+
+
+@pytest.mark.parametrize("sp_mode", ["ring_attn", "all_to_all"])
+@pytest.mark.parametrize("family", ["mistral", "qwen3", "gemma", "phi3", "mixtral"])
+def test_decoder_families_sequence_parallel(family, sp_mode):
+    run_distributed(_family_sp_worker, 2, family, sp_mode)
