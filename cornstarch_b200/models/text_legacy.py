@@ -90,15 +90,47 @@ class _Conv1DFn(torch.autograd.Function):
 
 
 class Conv1D(nn.Module):
+    """GPT-2's linear layer with the weight stored ``[in, out]``.  ``shard`` makes the tensor-parallel variants: ``"col"``
+    keeps a slice of the output features (per fused part when ``split_sizes`` is given), ``"row"`` a slice of the input
+    features with the partial results summed over the group."""
+
     def __init__(self, nf: int, nx: int):
         super().__init__()
         self.nf, self.nx = nf, nx
         self.weight = nn.Parameter(torch.empty(nx, nf).normal_(std=0.02))
         self.bias = nn.Parameter(torch.zeros(nf))
+        self.process_group, self.parallel, self.split_sizes = None, None, None
+
+    @classmethod
+    def shard(cls, module: "Conv1D", process_group, kind: str, split_sizes: list[int] | None = None) -> "Conv1D":
+        import torch.distributed as dist
+
+        tp, r = dist.get_world_size(process_group), dist.get_rank(process_group)
+        w, b = module.weight.data, module.bias.data
+        if kind == "col":
+            lw = cnn.shard_rows(w.t(), tp, r, split_sizes).t().contiguous()
+            lb = cnn.shard_rows(b, tp, r, split_sizes).clone()
+        else:
+            lw, lb = cnn.shard_rows(w, tp, r).clone(), b.clone()
+        new = cls.__new__(cls)
+        nn.Module.__init__(new)
+        new.nx, new.nf = lw.shape
+        new.weight = nn.Parameter(lw, requires_grad=module.weight.requires_grad)
+        new.bias = nn.Parameter(lb, requires_grad=module.bias.requires_grad)
+        new.process_group, new.parallel, new.split_sizes = process_group, kind, split_sizes
+        return new
 
     def forward(self, x):
-        y = _Conv1DFn.apply(x.reshape(-1, self.nx), self.weight, self.bias)
-        return y.view(*x.shape[:-1], self.nf)
+        from ..parallel import comm
+
+        if self.parallel == "col":
+            x = comm.reduce_backward(x, self.process_group)
+        row = self.parallel == "row"
+        y = _Conv1DFn.apply(x.reshape(-1, self.nx), self.weight, None if row else self.bias)
+        y = y.view(*x.shape[:-1], self.nf)
+        if row:
+            y = comm.reduce_forward(y, self.process_group) + self.bias.to(y.dtype)
+        return y
 
 
 class _GPT2Attention(nn.Module):
@@ -130,7 +162,7 @@ class GPT2Block(nn.Module):
         B, S, H = x.shape
         qkv = self.attn.c_attn(self.ln_1(x)).view(B, S, 3, self.num_heads, self.head_dim)
         a = A.attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], mask)
-        a = self.attn.c_proj(a.reshape(B, S, H))
+        a = self.attn.c_proj(a.reshape(B, S, self.num_heads * self.head_dim))
         h2, x = self.ln_2(a, x)
         return x + self.mlp.c_proj(E.activation(self.mlp.c_fc(h2), self.act))
 

@@ -48,6 +48,11 @@ def _tp_info(module: nn.Module) -> dict[str, tuple]:
             info[pre + "weight"] = ("row", mod)
         elif isinstance(mod, cnn.VocabParallelEmbedding):
             info[pre + "weight"] = ("vocab", mod)
+        elif getattr(mod, "parallel", None) == "col" and hasattr(mod, "nx"):  # GPT-2 Conv1D, weight stored [in, out]
+            info[pre + "weight"] = ("col_t", mod)
+            info[pre + "bias"] = ("col", mod)
+        elif getattr(mod, "parallel", None) == "row" and hasattr(mod, "nx"):
+            info[pre + "weight"] = ("row_t", mod)
     return info
 
 
@@ -64,6 +69,10 @@ def gather_full_tensor(name: str, t: torch.Tensor, info: dict, tp_group) -> torc
         return t
     kind, mod = info[name]
     parts = _gather(t, tp_group)
+    if kind == "col_t":
+        return cnn.unshard_rows([p.t() for p in parts], getattr(mod, "split_sizes", None)).t().contiguous()
+    if kind == "row_t":
+        return torch.cat(parts, dim=0)
     if kind == "col":
         full = cnn.unshard_rows(parts, getattr(mod, "split_sizes", None))
         v = getattr(mod, "full_vocab_size", None)
@@ -79,6 +88,10 @@ def shard_full_tensor(name: str, full: torch.Tensor, info: dict, tp_group) -> to
         return full
     kind, mod = info[name]
     tp, r = dist.get_world_size(tp_group), dist.get_rank(tp_group)
+    if kind == "col_t":
+        return cnn.shard_rows(full.t(), tp, r, getattr(mod, "split_sizes", None)).t().contiguous()
+    if kind == "row_t":
+        return full.chunk(tp, dim=0)[r]
     if kind == "col":
         v = getattr(mod, "full_vocab_size", None)
         if v is not None:

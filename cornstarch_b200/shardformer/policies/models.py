@@ -241,19 +241,24 @@ class Qwen2VisionTransformerPolicy(ModelPolicy):
 
 
 class GPT2ModelPolicy(ModelPolicy):
-    """Pipeline parallel only: GPT-2 stores its projection weights transposed (``Conv1D``)
-    (module list cornstarch/shardformer/policies/gpt2.py:44-55)."""
+    """GPT-2 stores its projection weights transposed (``Conv1D``): ``c_attn`` (fused q, k, v) and ``c_fc`` are split
+    over their output features, the two ``c_proj`` over their input features (module list
+    cornstarch/shardformer/policies/gpt2.py:44-55).  Embeddings and the LM head stay replicated."""
 
     model_cls = T.GPT2Model
     first_stage_modules = ["wte", "wpe", "drop"]
     last_stage_modules = ["ln_f"]
-    tp_rules = []
+    head_modules = r"(transformer\.)?h\.\d+"
+    tp_rules = [
+        TPRule(r"(transformer\.)?h\.\d+\.attn\.c_attn", "col", "qkv"),
+        TPRule(r"(transformer\.)?h\.\d+\.attn\.c_proj", "row"),
+        TPRule(r"(transformer\.)?h\.\d+\.mlp\.c_fc", "col"),
+        TPRule(r"(transformer\.)?h\.\d+\.mlp\.c_proj", "row"),
+    ]
 
-    def config_sanity_check(self):
-        super().config_sanity_check()
-        sc = self.shard_config
-        if sc is not None and sc.tensor_parallel_size > 1:
-            raise ValueError("GPT-2 (Conv1D weights) supports pipeline and data parallelism only")
+    def split_sizes(self, path, module):
+        H = self.model.config.n_embd
+        return [H, H, H] if path.endswith("c_attn") else None
 
 
 class GPT2LMHeadModelPolicy(GPT2ModelPolicy):

@@ -83,7 +83,15 @@ class ModelSharder:
         if tp <= 1:
             return
         rules = [(re.compile(r.pattern), r) for r in self.policy.tp_rules]
+        from ...models.text_legacy import Conv1D
+
         for path, mod in list(self.model.named_modules()):
+            if isinstance(mod, Conv1D) and mod.parallel is None:
+                for rx, rule in rules:
+                    if rx.fullmatch(path):
+                        _set_submodule(self.model, path, Conv1D.shard(mod, tp_group, rule.kind, self.policy.split_sizes(path, mod)))
+                        break
+                continue
             if not isinstance(mod, (cnn.Linear, cnn.Embedding)) or isinstance(
                     mod, (cnn.ColumnParallelLinear, cnn.RowParallelLinear, cnn.VocabParallelEmbedding)):
                 continue

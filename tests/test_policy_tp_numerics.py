@@ -129,8 +129,38 @@ def _worker(rank, world, family):
     assert checked > 0
 
 
-@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "phi3", "mixtral", "opt", "bert",
+@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "phi3", "mixtral", "gpt2", "opt", "bert",
                                     "siglip", "clip", "vit", "dinov2", "whisper", "gemma3", "qwen3_moe", "llama4", "internvit",
                                     "evaclip", "qwen2_audio", "pixtral"])
 def test_tp2_matches_unsharded(family):
     run_distributed(_worker, 2, family)
+
+
+def _gather_worker(rank, world, family):
+    """Checkpoint view of a tensor-parallel model: every sharded parameter gathers back to the unsharded tensor, and the
+    unsharded tensor shards to what the rank holds."""
+    from cornstarch_b200.plugin.checkpoint_io import _tp_info, gather_full_tensor, shard_full_tensor
+    from cornstarch_b200.shardformer.shard.shard_config import ShardConfig
+    from cornstarch_b200.shardformer.shard.shardformer import ShardFormer
+
+    torch.manual_seed(0)
+    ref, _ = _build(family)
+    torch.manual_seed(0)
+    model, _ = _build(family)
+    model.load_state_dict(ref.state_dict())
+    sc = ShardConfig(tensor_parallel_process_group=dist.group.WORLD, enable_tensor_parallelism=True, extra_kwargs={"device": "cpu"})
+    ShardFormer(sc).optimize(model)
+    info = _tp_info(model)
+    assert info, "no tensor-parallel parameter found"
+    full = dict(ref.named_parameters())
+    for name, p in model.named_parameters():
+        if name not in info:
+            continue
+        back = gather_full_tensor(name, p.data, info, dist.group.WORLD)
+        assert back.shape == full[name].shape and torch.equal(back, full[name].data), name
+        assert torch.equal(shard_full_tensor(name, full[name].data, info, dist.group.WORLD), p.data), name
+
+
+@pytest.mark.parametrize("family", ["llama", "phi3", "gpt2", "mixtral", "siglip"])
+def test_tp_parameters_gather_to_unsharded(family):
+    run_distributed(_gather_worker, 2, family)
