@@ -24,7 +24,6 @@ import os
 import subprocess
 import sys
 import threading
-import time
 
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)

@@ -11,11 +11,9 @@ lists of cornstarch/shardformer/policies/{siglip,clip,vit}.py (names returned by
 
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 from ..utils.recompute import checkpoint_layer
 
 from .. import nn as cnn

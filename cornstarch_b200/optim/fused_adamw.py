@@ -23,7 +23,6 @@ used at cornstarch/plugin/multimodal_parallel_plugin/multimodal_parallel_plugin.
 
 from __future__ import annotations
 
-import math
 from typing import Iterable
 
 import torch

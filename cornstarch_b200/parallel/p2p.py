@@ -12,7 +12,6 @@ Tensors go through ``batch_isend_irecv`` (NCCL groups them into one launch; gloo
 
 from __future__ import annotations
 
-import io
 import pickle
 from dataclasses import dataclass
 from typing import Any

@@ -12,7 +12,6 @@ from __future__ import annotations
 
 import itertools
 
-import numpy as np
 
 from ..pipeline_template import PipelineTemplate
 from .mesh import MultiModalProcessGroupMesh

@@ -11,7 +11,6 @@ natively, so a policy is data, not code.
 
 from __future__ import annotations
 
-import re
 from dataclasses import dataclass, field
 
 from .pipeline_template_policy import PipelineTemplatePolicyBase, check_template_covers

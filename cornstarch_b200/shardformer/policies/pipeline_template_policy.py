@@ -4,7 +4,6 @@
 from __future__ import annotations
 
 import itertools
-import re
 from abc import ABC, abstractmethod
 
 

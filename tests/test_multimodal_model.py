@@ -179,3 +179,22 @@ def test_recompute_keep_last_layers_same_gradients():
         assert g.keys() == grads[0].keys()
         for n in g:
             assert torch.allclose(g[n], grads[0][n], atol=1e-6), n
+
+
+def test_generate_is_greedy_over_the_merged_sequence():
+    """Every generated token is the arg-max of the model's next-token logits for the prefix (image features merged in)."""
+    from cornstarch_b200 import zoo
+
+    torch.manual_seed(0)
+    model = zoo.build_model("tiny", device="cpu", dtype=torch.float32).eval()
+    batch = zoo.synthetic_batch("tiny", 2, seed=1)
+    prompt = batch["input_ids"][:, :40]
+    out = model.generate(prompt, max_new_tokens=3, pixel_values=batch["pixel_values"])
+    assert out.shape == (2, 43) and torch.equal(out[:, :40], prompt)
+    for t in range(40, 43):
+        logits = model(input_ids=out[:, :t], pixel_values=batch["pixel_values"]).logits
+        assert torch.equal(logits[:, -1].argmax(-1), out[:, t])
+    # with an end-of-sequence id the finished rows keep emitting it
+    eos = int(out[0, 40])
+    out2 = model.generate(prompt, max_new_tokens=3, eos_token_id=eos, pixel_values=batch["pixel_values"])
+    assert bool((out2[0, 40:] == eos).all())
