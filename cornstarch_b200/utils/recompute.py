@@ -14,6 +14,7 @@ only top-level tensor arguments are differentiated.  The layer may return a tens
 from __future__ import annotations
 
 import torch
+import torch.distributed as dist
 
 from ..ops.attention import attention_tape
 
@@ -63,3 +64,39 @@ def checkpoint_layer(fn, *args):
     outs = list(_Recompute.apply(run, anchor, *tensors))
     seq = [None if is_none else outs.pop(0) for is_none in layout["none"]]
     return seq[0] if layout["single"] else tuple(seq)
+
+
+def activation_bytes_per_layer(cfg, tokens: int, tp: int = 1) -> int:
+    """Upper estimate of what one dense decoder layer keeps for backward when it is not recomputed (bf16 activations):
+    the inputs of both norms, the normed inputs of the projections, q / k / v after RoPE, the attention output, the
+    gate-up output and the SwiGLU output."""
+    H, I = cfg.hidden_size, cfg.intermediate_size
+    D = getattr(cfg, "head_dim", None) or H // cfg.num_attention_heads
+    qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * D
+    return int(1.15 * tokens * 2 * (8 * H + (3 * qkv + 3 * I) / tp))
+
+
+def tune_recompute(model, tokens: int, tp: int, in_flight: int, group=None, safety_bytes: int = 6 << 30) -> int:
+    """After one fully recomputed step: how many decoder layers can keep their activations in the memory that step left
+    free (what the driver still reports free; the caching allocator holds on to its peak).  The same number on every
+    rank of ``group`` - the tensor-parallel peers replay the same collectives in a recomputed forward.  Returns the
+    number of layers kept (0 for models this estimate does not cover)."""
+    lm = getattr(model, "language_model", model)
+    inner = getattr(lm, "model", None)
+    cfg = getattr(lm, "config", None)
+    keep = 0
+    if torch.cuda.is_available() and inner is not None and hasattr(inner, "layers") and not getattr(cfg, "num_local_experts", 0):
+        from ..models.base import is_released
+
+        held = sum(not is_released(l) for l in inner.layers)
+        torch.cuda.synchronize()
+        free, _ = torch.cuda.mem_get_info()
+        per_layer = activation_bytes_per_layer(cfg, tokens, tp) * max(in_flight, 1)
+        keep = max(0, min(held, int((free - safety_bytes) // per_layer)))
+    if group is not None and dist.get_world_size(group) > 1:
+        t = torch.tensor([keep], device="cuda" if torch.cuda.is_available() else "cpu")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+        keep = int(t)
+    if inner is not None and hasattr(lm, "gradient_checkpointing_enable"):
+        lm.gradient_checkpointing_enable({"keep_last_layers": keep})
+    return keep
