@@ -247,6 +247,12 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": args.impl, "benchmark_config": args.config,
         }
         print(json.dumps(out))
+    if nat.KERNEL_TIMES and rank == 0:
+        # in-situ breakdown (CORNSTARCH_B200_KERNEL_TIMES=1): device time per native entry point since the process started
+        times = nat.kernel_times()  # {entry point: (calls, total ms)}
+        rows = sorted(times.items(), key=lambda kv: -kv[1][1])
+        print(json.dumps({"kernel_times": {k: {"calls": c, "ms": round(ms, 2)} for k, (c, ms) in rows[:20]},
+                          "sum_ms": round(sum(ms for _, ms in times.values()), 1)}))
     if world > 1:
         dist.destroy_process_group()
 
