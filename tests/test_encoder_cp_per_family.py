@@ -72,6 +72,15 @@ def _worker2(rank, world, family):
     _check(ref, model, kind, x, world)
 
 
-@pytest.mark.parametrize("family", FAMILIES)
-def test_encoder_ring_attn_matches_unsharded(family):
-    run_distributed(_worker2, 2, family)
+def _group_worker(rank, world, families):
+    for family in families:
+        try:
+            _worker2(rank, world, family)
+        except Exception as e:  # noqa: BLE001
+            raise AssertionError(f"family {family}: {e}") from e
+        dist.barrier()
+
+
+@pytest.mark.parametrize("families", [FAMILIES[:4], FAMILIES[4:]], ids=["vision_a", "vision_b_and_audio"])
+def test_encoder_ring_attn_matches_unsharded(families):
+    run_distributed(_group_worker, 2, families)
