@@ -148,10 +148,43 @@ def grad_reduce(args):
     nat.check_status()
 
 
+def moe_exchange(args):
+    """MoE token dispatch: ``--seq`` (token, expert) rows of 4096 bf16 per rank, gathered through a sorted index and sent
+    to the expert owners in equal shares.  The peer-memory push kernel (gather fused into the stores, counters instead
+    of a collective) against an index gather followed by NCCL ``all_to_all_single``."""
+    from ..parallel.ep import all_to_all_uneven
+    from ..parallel.ep_fused import FusedExpertExchange
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    rows, H = args.seq, 4096
+    per = rows // world
+    rows = per * world
+    x = torch.randn(rows, H, device="cuda").bfloat16()
+    index = torch.randperm(rows, device="cuda")
+    counts = [[per] * world for _ in range(world)]
+    ex = FusedExpertExchange.get(dist.group.WORLD)
+    ex.ensure(rows, H)
+    got = ex.exchange(x, index, counts)
+    want = all_to_all_uneven(x[index], [per] * world, [per] * world, dist.group.WORLD)
+    same = bool(torch.equal(got, want))
+    ms_f = timeit(lambda: ex.exchange(x, index, counts), iters=10, warmup=3)
+    ms_b = timeit(lambda: all_to_all_uneven(x[index], [per] * world, [per] * world, dist.group.WORLD), iters=10, warmup=3)
+    link_bytes = (world - 1) * per * H * 2  # rows that leave this GPU (as many arrive)
+    roof_ms = link_bytes / NVLINK_BPS * 1e3
+    if rank == 0:
+        print(json.dumps({"op": "moe dispatch (gather + all-to-all)", "world": world, "rows_per_rank": rows, "H": H,
+                          "fused_ms": round(ms_f, 4), "gather_then_nccl_all_to_all_ms": round(ms_b, 4),
+                          "roofline_ms": round(roof_ms, 4), "frac_of_roofline": round(roof_ms / ms_f, 3),
+                          "speedup_vs_nccl": round(ms_b / ms_f, 3), "same_rows": same}), flush=True)
+    from ..ops import _native as nat
+
+    nat.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm_allreduce", "cp_attention", "grad_reduce"])
-    ap.add_argument("--seq", type=int, default=8192, help="cp_attention: tokens per rank")
+    ap.add_argument("what", choices=["gemm_allreduce", "cp_attention", "grad_reduce", "moe_exchange"])
+    ap.add_argument("--seq", type=int, default=8192, help="cp_attention: tokens per rank; moe_exchange: rows per rank")
     ap.add_argument("--mb", type=int, default=1024, help="grad_reduce: buffer size in MiB")
     ap.add_argument("--reducers", type=int, nargs="+", default=[16])
     args = ap.parse_args()
@@ -159,7 +192,8 @@ def main():
     torch.cuda.set_device(local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    {"gemm_allreduce": gemm_allreduce, "cp_attention": cp_attention, "grad_reduce": grad_reduce}[args.what](args)
+    {"gemm_allreduce": gemm_allreduce, "cp_attention": cp_attention, "grad_reduce": grad_reduce,
+     "moe_exchange": moe_exchange}[args.what](args)
     dist.barrier()
     dist.destroy_process_group()
 
