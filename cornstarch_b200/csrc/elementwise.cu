@@ -166,13 +166,18 @@ __global__ void act_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_b
 // grad_scale (device scalar, optional) carries 1/loss_scale * clip factor; `skip` (device int,
 // optional) non-zero turns the whole update into a no-op (inf/nan step under dynamic loss scaling).
 constexpr int ADAMW_UNROLL = 4;
-template <typename GradT>
+// SPLIT: the fp32 master weight is not stored as such.  Its upper half is the bf16 parameter itself (rounded half away
+// from zero, so that the remainder always fits), its lower half a signed 16-bit remainder in `master_v` (an int16 array):
+// master bits = (bf16 bits << 16) + remainder, exactly.  Same update, 2 bytes per parameter less.
+template <typename GradT, bool SPLIT>
 __global__ void __launch_bounds__(256)
-adamw_kernel(__nv_bfloat16* __restrict__ param, float* __restrict__ master, float* __restrict__ m,
+adamw_kernel(__nv_bfloat16* __restrict__ param, void* __restrict__ master_v, float* __restrict__ m,
              float* __restrict__ v, GradT* __restrict__ grad, long n, float lr, float b1, float b2,
              float eps, float wd, float bc1, float bc2, const float* __restrict__ grad_scale,
              const int* __restrict__ skip, int zero_grad) {
   if (skip && *skip) return;
+  float* __restrict__ master = reinterpret_cast<float*>(master_v);
+  uint2* __restrict__ resid = reinterpret_cast<uint2*>(master_v);  // 4 x int16 per vector
   const float gs = grad_scale ? *grad_scale : 1.f;
   const float inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2, decay = 1.f - lr * wd;
   const long n4 = n / 4;
@@ -187,7 +192,19 @@ adamw_kernel(__nv_bfloat16* __restrict__ param, float* __restrict__ master, floa
     for (int u = 0; u < ADAMW_UNROLL; ++u) {
       const long i = base + u * blockDim.x + threadIdx.x;
       if (i < n4) {
-        w[u] = __ldcs(reinterpret_cast<const float4*>(master) + i);
+        if constexpr (SPLIT) {
+          const uint2 pb = __ldcs(reinterpret_cast<const uint2*>(param) + i);
+          const uint2 rb = __ldcs(resid + i);
+          const uint32_t hi[4] = {pb.x & 0xffffu, pb.x >> 16, pb.y & 0xffffu, pb.y >> 16};
+          const uint32_t lo[4] = {rb.x & 0xffffu, rb.x >> 16, rb.y & 0xffffu, rb.y >> 16};
+          float f[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            f[j] = __uint_as_float((hi[j] << 16) + static_cast<uint32_t>(static_cast<int32_t>(static_cast<int16_t>(lo[j]))));
+          w[u] = make_float4(f[0], f[1], f[2], f[3]);
+        } else {
+          w[u] = __ldcs(reinterpret_cast<const float4*>(master) + i);
+        }
         mm[u] = __ldcs(reinterpret_cast<const float4*>(m) + i);
         vv[u] = __ldcs(reinterpret_cast<const float4*>(v) + i);
         if constexpr (sizeof(GradT) == 4) {
@@ -215,12 +232,25 @@ adamw_kernel(__nv_bfloat16* __restrict__ param, float* __restrict__ master, floa
         const float denom = sqrtf(sv[j] * inv_bc2) + eps;
         wv[j] = wv[j] * decay - lr * (mv[j] * inv_bc1) / denom;
       }
-      __stcs(reinterpret_cast<float4*>(master) + i, make_float4(wv[0], wv[1], wv[2], wv[3]));
       __stcs(reinterpret_cast<float4*>(m) + i, make_float4(mv[0], mv[1], mv[2], mv[3]));
       __stcs(reinterpret_cast<float4*>(v) + i, make_float4(sv[0], sv[1], sv[2], sv[3]));
       uint2 o;
-      o.x = pack_bf16x2(wv[0], wv[1]);
-      o.y = pack_bf16x2(wv[2], wv[3]);
+      if constexpr (SPLIT) {
+        uint32_t hb[4], lb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t bits = __float_as_uint(wv[j]);
+          hb[j] = (bits + 0x8000u) >> 16;  // round half away from zero: the remainder is in [-32768, 32767]
+          lb[j] = (bits - (hb[j] << 16)) & 0xffffu;
+        }
+        o.x = hb[0] | (hb[1] << 16);
+        o.y = hb[2] | (hb[3] << 16);
+        __stcs(resid + i, make_uint2(lb[0] | (lb[1] << 16), lb[2] | (lb[3] << 16)));
+      } else {
+        __stcs(reinterpret_cast<float4*>(master) + i, make_float4(wv[0], wv[1], wv[2], wv[3]));
+        o.x = pack_bf16x2(wv[0], wv[1]);
+        o.y = pack_bf16x2(wv[2], wv[3]);
+      }
       reinterpret_cast<uint2*>(param)[i] = o;
       if (zero_grad) {
         if constexpr (sizeof(GradT) == 4) __stcs(reinterpret_cast<float4*>(grad) + i, make_float4(0.f, 0.f, 0.f, 0.f));
@@ -509,13 +539,31 @@ CSB_API int csb_adamw(void* param, float* master, float* m, float* v, void* grad
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int grid = ew_grid(n / 4 / ADAMW_UNROLL + 1, 256);
   if (grad_fp32)
-    adamw_kernel<float><<<grid, 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(param), master, m, v,
-                                             reinterpret_cast<float*>(grad), n, lr, b1, b2, eps, wd, bc1, bc2,
-                                             grad_scale, skip, zero_grad);
+    adamw_kernel<float, false><<<grid, 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(param), master, m, v,
+                                                    reinterpret_cast<float*>(grad), n, lr, b1, b2, eps, wd, bc1, bc2,
+                                                    grad_scale, skip, zero_grad);
   else
-    adamw_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(param), master, m, v,
-                                                     reinterpret_cast<__nv_bfloat16*>(grad), n, lr, b1, b2, eps, wd,
-                                                     bc1, bc2, grad_scale, skip, zero_grad);
+    adamw_kernel<__nv_bfloat16, false><<<grid, 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(param), master, m, v,
+                                                            reinterpret_cast<__nv_bfloat16*>(grad), n, lr, b1, b2, eps,
+                                                            wd, bc1, bc2, grad_scale, skip, zero_grad);
+  return launch_result();
+}
+// Same update with the master weight kept as bf16 parameter + int16 remainder (`resid`, n entries, zero when the master
+// equals the parameter).
+CSB_API int csb_adamw_split(void* param, short* resid, float* m, float* v, void* grad, int grad_fp32, long n, float lr,
+                            float b1, float b2, float eps, float wd, float bc1, float bc2, const float* grad_scale,
+                            const int* skip, int zero_grad, void* stream) {
+  if (n % 4) return CSB_ERR_BAD_ARG;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = ew_grid(n / 4 / ADAMW_UNROLL + 1, 256);
+  if (grad_fp32)
+    adamw_kernel<float, true><<<grid, 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(param), resid, m, v,
+                                                   reinterpret_cast<float*>(grad), n, lr, b1, b2, eps, wd, bc1, bc2,
+                                                   grad_scale, skip, zero_grad);
+  else
+    adamw_kernel<__nv_bfloat16, true><<<grid, 256, 0, s>>>(reinterpret_cast<__nv_bfloat16*>(param), resid, m, v,
+                                                           reinterpret_cast<__nv_bfloat16*>(grad), n, lr, b1, b2, eps,
+                                                           wd, bc1, bc2, grad_scale, skip, zero_grad);
   return launch_result();
 }
 CSB_API int csb_sumsq(const void* g, int grad_fp32, long n, float* out, void* stream) {

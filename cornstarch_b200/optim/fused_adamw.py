@@ -23,6 +23,7 @@ used at cornstarch/plugin/multimodal_parallel_plugin/multimodal_parallel_plugin.
 
 from __future__ import annotations
 
+import os
 from typing import Iterable
 
 import torch
@@ -37,7 +38,7 @@ class _Region:
     """One weight-decay group laid out flat."""
 
     def __init__(self, params: list[torch.nn.Parameter], grad_dtype: torch.dtype, shard: tuple[int, int] | None,
-                 grad_alloc=None):
+                 grad_alloc=None, split_master: bool = False):
         dev = params[0].device
         self.params = params
         self.offsets = []
@@ -64,18 +65,55 @@ class _Region:
         else:
             self.lo, self.hi = 0, self.numel
         k = self.hi - self.lo
-        self.master = self.flat_param[self.lo : self.hi].float()
+        # fp32 master weights, or (split_master) only their lower 16 bits: the bf16 parameter is the upper half, so
+        # master bits = (parameter bits << 16) + remainder and 2 bytes per parameter are saved
+        self.split_master = split_master
+        if split_master:
+            self.master = None
+            self.resid = torch.zeros(k, dtype=torch.int16, device=dev)
+        else:
+            self.master = self.flat_param[self.lo : self.hi].float()
+            self.resid = None
         self.exp_avg = torch.zeros(k, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(k, dtype=torch.float32, device=dev)
+
+    def master_weights(self) -> torch.Tensor:
+        """The fp32 master weights of this rank's slice (a new tensor when they are stored split)."""
+        if not self.split_master:
+            return self.master
+        hi = self.flat_param[self.lo : self.hi].view(torch.int16).to(torch.int32) << 16
+        return (hi + self.resid.to(torch.int32)).view(torch.float32)
+
+    def set_master_weights(self, sl: slice, master: torch.Tensor) -> None:
+        """Write fp32 master weights for ``sl`` of this rank's slice (and, stored split, the bf16 parameters they imply)."""
+        master = master.reshape(-1).to(device=self.flat_param.device, dtype=torch.float32)
+        if not self.split_master:
+            self.master[sl].copy_(master)
+            return
+        bits = master.view(torch.int32)
+        hi = (bits + 0x8000) >> 16  # round half away from zero; as int32 its low 16 bits are the bf16 pattern
+        self.resid[sl].copy_((bits - (hi << 16)).to(torch.int16))
+        self.flat_param[self.lo : self.hi][sl].view(torch.int16).copy_(hi.to(torch.int16))
+
+    def reset_master_weights(self) -> None:
+        """Master weights := the current bf16 parameters."""
+        if self.split_master:
+            self.resid.zero_()
+        else:
+            self.master.copy_(self.flat_param[self.lo : self.hi].float())
 
 
 class FusedAdamW(torch.optim.Optimizer):
     def __init__(self, params: Iterable, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
                  weight_decay: float = 0.01, max_norm: float = 0.0, grad_dtype: torch.dtype = torch.bfloat16,
                  zero_stage: int = 0, dp_group=None, norm_groups: list | None = None, use_arena: bool | None = None,
-                 expert_group=None, fused_dp: bool = True):
+                 expert_group=None, fused_dp: bool = True, split_master: bool | None = None):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
+        # split_master: keep only the lower 16 bits of each fp32 master weight next to the bf16 parameter (which is its
+        # upper half): the same fp32 update with 2 bytes per parameter less.  Default on; CORNSTARCH_B200_FP32_MASTER=1
+        # (or split_master=False) stores whole fp32 master weights.
+        self.split_master = (os.environ.get("CORNSTARCH_B200_FP32_MASTER", "0") != "1") if split_master is None else split_master
         self.max_norm = max_norm
         self.grad_dtype = grad_dtype
         self.zero_stage = zero_stage
@@ -109,7 +147,8 @@ class FusedAdamW(torch.optim.Optimizer):
             ps = [p for p in g["params"] if p.requires_grad]
             if ps:
                 alloc = self.reducer.allocate if (self.reducer is not None and not g.get("expert_parallel")) else None
-                region = _Region(ps, self.grad_dtype, None if g.get("expert_parallel") else shard, alloc)
+                region = _Region(ps, self.grad_dtype, None if g.get("expert_parallel") else shard, alloc,
+                                 split_master=self.split_master)
                 region.sharded = shard is not None and not g.get("expert_parallel")
                 region.expert = bool(g.get("expert_parallel"))
                 self._regions.append((g, region))
@@ -220,8 +259,9 @@ class FusedAdamW(torch.optim.Optimizer):
             bc2 = 1.0 - b2 ** self._step
             grad = r.flat_grad[r.lo : r.hi]
             param = r.flat_param[r.lo : r.hi]
+            step_fn = lib.csb_adamw_split if r.split_master else lib.csb_adamw
             nat.check(
-                lib.csb_adamw(param.data_ptr(), r.master.data_ptr(), r.exp_avg.data_ptr(), r.exp_avg_sq.data_ptr(),
+                step_fn(param.data_ptr(), (r.resid if r.split_master else r.master).data_ptr(), r.exp_avg.data_ptr(), r.exp_avg_sq.data_ptr(),
                               grad.data_ptr(), int(grad.dtype == torch.float32), grad.numel(), float(g["lr"]), b1, b2,
                               float(g["eps"]), float(g["weight_decay"]), bc1, bc2,
                               self._scale.data_ptr() if need_norm else None, self._skip.data_ptr() if need_norm else None,
@@ -322,13 +362,14 @@ class FusedAdamW(torch.optim.Optimizer):
             for p in g["params"]:
                 index_of[id(p)] = idx
                 idx += 1
+        masters = {id(r): r.master_weights() for _, r in self._regions}
         for _, r in self._regions:
             for p, off in zip(r.params, r.offsets):
                 lo, hi = off, off + p.numel()
                 if lo >= r.lo and hi <= r.hi:
                     s = slice(lo - r.lo, hi - r.lo)
                     state[index_of[id(p)]] = {
-                        "master": r.master[s].view(p.shape).clone(),
+                        "master": masters[id(r)][s].view(p.shape).clone(),
                         "exp_avg": r.exp_avg[s].view(p.shape).clone(),
                         "exp_avg_sq": r.exp_avg_sq[s].view(p.shape).clone(),
                     }
@@ -363,14 +404,14 @@ class FusedAdamW(torch.optim.Optimizer):
                 lo, hi = off, off + p.numel()
                 if lo >= r.lo and hi <= r.hi:
                     s = slice(lo - r.lo, hi - r.lo)
-                    r.master[s].copy_(st["master"].reshape(-1))
+                    r.set_master_weights(s, st["master"])
                     r.exp_avg[s].copy_(st["exp_avg"].reshape(-1))
                     r.exp_avg_sq[s].copy_(st["exp_avg_sq"].reshape(-1))
 
     def update_master_params(self):
         """Re-read master weights from the (just loaded) bf16 parameters."""
         for _, r in self._regions:
-            r.master.copy_(r.flat_param[r.lo : r.hi].float())
+            r.reset_master_weights()
 
 
 def split_decay_groups(model: torch.nn.Module, weight_decay: float = 0.01) -> list[dict]:

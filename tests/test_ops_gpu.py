@@ -188,3 +188,28 @@ def test_smoke_entry():
     import __graft_entry__ as g
 
     g.smoke()
+
+
+def test_fused_adamw_split_master_equals_fp32_master():
+    """Master weights kept as bf16 parameter + 16-bit remainder follow exactly the trajectory of whole fp32 master
+    weights; the bf16 parameters agree except where the master sits exactly between two bf16 values."""
+    torch.manual_seed(1)
+    init = torch.randn(1 << 18, device="cuda").bfloat16()
+    runs = {}
+    for split in (False, True):
+        p = torch.nn.Parameter(init.clone())
+        opt = FusedAdamW([{"params": [p], "weight_decay": 0.05}], lr=3e-3, max_norm=1.0, split_master=split)
+        assert opt.use_arena and opt._regions[0][1].split_master == split
+        g = torch.Generator(device="cuda").manual_seed(7)
+        for _ in range(5):
+            p.main_grad.copy_(torch.randn(init.shape, device="cuda", generator=g).bfloat16())
+            opt.step()
+        runs[split] = (opt._regions[0][1].master_weights().clone(), p.detach().clone(), opt.state_dict())
+    assert torch.equal(runs[True][0], runs[False][0])
+    diff = runs[True][1].float() - runs[False][1].float()
+    assert int((diff != 0).sum()) <= 64 and float(diff.abs().max()) <= float(init.float().abs().max()) * 2.0 ** -7
+    # a state dict written by one representation loads into the other
+    p2 = torch.nn.Parameter(init.clone())
+    opt2 = FusedAdamW([{"params": [p2], "weight_decay": 0.05}], lr=3e-3, max_norm=1.0, split_master=True)
+    opt2.load_state_dict(runs[False][2])
+    assert torch.equal(opt2._regions[0][1].master_weights(), runs[False][0])

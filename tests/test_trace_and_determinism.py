@@ -87,3 +87,29 @@ def test_norm_and_glu_are_deterministic():
     for a, b in zip(*res):
         assert torch.isfinite(a.float()).all()
         assert torch.equal(a, b)
+
+
+def test_split_master_weights_are_exact():
+    """fp32 master weights kept as bf16 parameter + int16 remainder: any fp32 value survives the split exactly, and the
+    parameter is the master rounded to bf16 (half away from zero)."""
+    from cornstarch_b200.optim.fused_adamw import _Region
+
+    torch.manual_seed(0)
+    p = torch.nn.Parameter(torch.randn(4096).bfloat16())
+    region = _Region([p], torch.bfloat16, None, None, split_master=True)
+    assert region.master is None and region.resid.dtype == torch.int16
+    assert torch.equal(region.master_weights(), p.data.float())  # starts as the parameter itself
+    vals = torch.cat([torch.randn(4000) * 3, torch.tensor([0.0, -0.0, 1.0, -1.0, 1e-30, -1e-30, 3.0e38, -3.0e38]),
+                      torch.randn(88) * 1e-6])
+    # exact ties of the rounding (lower half == 0x8000), both signs
+    ties = ((torch.randn(64).bfloat16().view(torch.int16).to(torch.int32) << 16) + 0x8000).view(torch.float32)
+    vals[:64] = ties
+    region.set_master_weights(slice(0, 4096), vals)
+    assert torch.equal(region.master_weights().view(torch.int32), vals.view(torch.int32))
+    err = (p.data.float() - vals).abs()
+    assert bool((err <= vals.abs() * 2.0 ** -8).all())  # half a unit in the last place of bf16 (8 significant bits)
+    not_tie = torch.ones(4096, dtype=torch.bool)
+    not_tie[:64] = False
+    assert torch.equal(p.data[not_tie], vals.bfloat16()[not_tie])  # same as round-to-nearest-even away from ties
+    region.reset_master_weights()
+    assert torch.equal(region.master_weights(), p.data.float())
