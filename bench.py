@@ -174,9 +174,10 @@ def main():
     # ---- device-timed region: inputs already on the device
     for i in range(W):
         trainer.step_device()
-        if i == 0 and args.recompute == "auto" and hasattr(trainer, "tune_recompute"):
+        if i < 2 and args.recompute == "auto" and hasattr(trainer, "tune_recompute"):
             # the first step ran with every layer recomputed and shows how much memory is left: layers that fit stop
-            # being recomputed; the remaining (>= 2) warm-up steps run with the final setting
+            # being recomputed; the second step shows what a kept layer really costs and may add more.  The remaining
+            # warm-up steps run with the final setting.
             trainer.tune_recompute()
     sync()
     sampler = ClockSampler(local_rank)

@@ -86,17 +86,19 @@ class PipelineTrainer:
     recompute = "every layer"
 
     def tune_recompute(self):
-        """Call after one step: decoder layers that fit in the memory left over stop being recomputed (per stage; the
+        """Call after each of the first two steps: decoder layers that fit in the memory left over stop being recomputed (per stage; the
         tensor-parallel peers agree on the number)."""
-        from .bench_support import tune_recompute
+        from .utils.recompute import RecomputeTuner
 
         sm = self.plugin.stage_manager
         is_llm = self.model.my_modal_name == "language_model"
         llm_stages = self.plugin.language_model_plugin.pipeline_template.num_stages
         in_flight = llm_stages - sm.stage_in_modal if is_llm else 1
         tp = self.plugin.language_model_plugin.tp_size
-        keep = tune_recompute(self.model.module, self.microbatch * self.seq_len, tp, in_flight,
-                              self.plugin.tp_group if tp > 1 else None) if is_llm else 0
+        if getattr(self, "_tuner", None) is None:
+            self._tuner = RecomputeTuner(self.model.module, self.microbatch * self.seq_len, tp, in_flight,
+                                         self.plugin.tp_group if tp > 1 else None)
+        keep = self._tuner.after_step() if is_llm else 0
         counts = [None] * dist.get_world_size()
         dist.all_gather_object(counts, (is_llm, keep))
         kept = [k for llm, k in counts if llm]

@@ -11,7 +11,7 @@ import torch
 import torch.distributed as dist
 
 from .optim.fused_adamw import FusedAdamW, split_decay_groups
-from .utils.recompute import activation_bytes_per_layer, tune_recompute  # noqa: F401  (also imported from here)
+from .utils.recompute import RecomputeTuner, activation_bytes_per_layer, tune_recompute  # noqa: F401  (also imported from here)
 from .zoo import SHAPES, build_model, synthetic_batch
 
 
@@ -86,10 +86,12 @@ class SingleDeviceTrainer:
     overlap_reduce = True
 
     def tune_recompute(self):
-        """Call after one step: layers that fit in the memory left over stop being recomputed."""
+        """Call after each of the first two steps: layers that fit in the memory left over stop being recomputed."""
         from .ops import _native as nat
 
-        keep = tune_recompute(self.model, self.microbatch * self.seq_len, 1, 1, self.dp_group)
+        if getattr(self, "_tuner", None) is None:
+            self._tuner = RecomputeTuner(self.model, self.microbatch * self.seq_len, 1, 1, self.dp_group)
+        keep = self._tuner.after_step()
         n = len(self.model.language_model.model.layers)
         self.recompute = f"{n - keep} of {n} decoder layers (the other {keep} fit in free memory), encoder layers"
         return keep

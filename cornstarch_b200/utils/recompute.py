@@ -100,3 +100,47 @@ def tune_recompute(model, tokens: int, tp: int, in_flight: int, group=None, safe
     if inner is not None and hasattr(lm, "gradient_checkpointing_enable"):
         lm.gradient_checkpointing_enable({"keep_last_layers": keep})
     return keep
+
+
+class RecomputeTuner:
+    """Two passes of :func:`tune_recompute`, one after each of the first two steps.  The first uses the upper estimate of a
+    layer's activations; the second replaces it by what the layers kept in step two actually cost (growth of the
+    allocator's reservation per kept layer, plus 10 %, and never less than half the estimate) and keeps more layers if
+    the memory the driver still reports free allows it."""
+
+    def __init__(self, model, tokens: int, tp: int, in_flight: int, group=None, safety_bytes: int = 6 << 30):
+        self.model, self.tokens, self.tp, self.in_flight = model, tokens, tp, max(in_flight, 1)
+        self.group, self.safety = group, safety_bytes
+        self.passes, self.keep, self.reserved0 = 0, 0, 0
+
+    def after_step(self) -> int:
+        self.passes += 1
+        if self.passes == 1:
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+                self.reserved0 = torch.cuda.memory_reserved()
+            self.keep = tune_recompute(self.model, self.tokens, self.tp, self.in_flight, self.group, self.safety)
+            return self.keep
+        if self.passes > 2:
+            return self.keep
+        lm = getattr(self.model, "language_model", self.model)
+        inner = getattr(lm, "model", None)
+        extra = 0
+        if torch.cuda.is_available() and inner is not None and self.keep > 0:
+            from ..models.base import is_released
+
+            held = sum(not is_released(l) for l in inner.layers)
+            torch.cuda.synchronize()
+            free, _ = torch.cuda.mem_get_info()
+            estimate = activation_bytes_per_layer(lm.config, self.tokens, self.tp) * self.in_flight
+            measured = (torch.cuda.memory_reserved() - self.reserved0) / self.keep
+            per_layer = max(1.1 * measured, 0.5 * estimate)
+            extra = max(0, min(held - self.keep, int((free - self.safety) // per_layer)))
+        if self.group is not None and dist.get_world_size(self.group) > 1:
+            t = torch.tensor([extra], device="cuda" if torch.cuda.is_available() else "cpu")
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+            extra = int(t)
+        if extra > 0:
+            self.keep += extra
+            lm.gradient_checkpointing_enable({"keep_last_layers": self.keep})
+        return self.keep
