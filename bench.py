@@ -241,7 +241,7 @@ def main():
             "config": {"model": trainer.model_name, "global_batch": trainer.global_batch, "seq_len": trainer.seq_len,
                        "parallelism": trainer.parallelism, "microbatch": args.microbatch,
                        "l2": "no flush needed: every step streams >16 GB of weights and activations, far above the 126 MB L2",
-                       "optimizer": ("fused AdamW, fp32 master + moments, bf16 grads" if args.impl == "native"
+                       "optimizer": ("fused AdamW, fp32 master weights (stored as bf16 parameter + 16-bit remainder) + fp32 moments, bf16 grads" if args.impl == "native"
                                      else "torch.optim.AdamW(fused=True) on bf16 parameters, clip_grad_norm_"),
                        "kernels": ("this package (sm_100a)" if args.impl == "native" else "library: cuBLAS, PyTorch SDPA, PyTorch elementwise, NCCL"), "activation_checkpointing": getattr(trainer, "recompute", "every layer"),
                        "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1)},
