@@ -198,3 +198,27 @@ def test_generate_is_greedy_over_the_merged_sequence():
     eos = int(out[0, 40])
     out2 = model.generate(prompt, max_new_tokens=3, eos_token_id=eos, pixel_values=batch["pixel_values"])
     assert bool((out2[0, 40:] == eos).all())
+
+
+def test_recompute_tuner_two_passes(monkeypatch):
+    """Pass one keeps what the upper estimate allows; pass two re-measures what a kept layer cost and keeps more."""
+    from cornstarch_b200 import zoo
+    from cornstarch_b200.utils import recompute as R
+
+    model = zoo.build_model("tiny", device="cpu", dtype=torch.float32)
+    model.gradient_checkpointing_enable()
+    n_layers = len(model.language_model.model.layers)
+    est = R.activation_bytes_per_layer(model.language_model.config, 256, 1)
+    mem = {"free": 6 * 2**30 + int(1.5 * est), "reserved": 10 * 2**30}
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "synchronize", lambda *a, **k: None)
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda *a, **k: (mem["free"], 180 * 2**30))
+    monkeypatch.setattr(torch.cuda, "memory_reserved", lambda *a, **k: mem["reserved"])
+    tuner = R.RecomputeTuner(model, 256, 1, 1)
+    assert tuner.after_step() == 1  # room for one estimated layer above the safety margin
+    assert model.language_model.model.recompute_keep_layers == 1
+    # the kept layer turned out to cost 0.6 of the estimate; the driver still reports room for one more such layer
+    mem["reserved"] += int(0.6 * est)
+    mem["free"] = 6 * 2**30 + int(0.7 * est)
+    assert tuner.after_step() == min(n_layers, 2)
+    assert tuner.after_step() == min(n_layers, 2)  # further calls change nothing
