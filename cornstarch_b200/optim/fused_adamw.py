@@ -95,6 +95,30 @@ class _Region:
         self.resid[sl].copy_((bits - (hi << 16)).to(torch.int16))
         self.flat_param[self.lo : self.hi][sl].view(torch.int16).copy_(hi.to(torch.int16))
 
+    def gathered_states(self, group=None) -> dict[str, torch.Tensor]:
+        """``master`` / ``exp_avg`` / ``exp_avg_sq`` over the WHOLE region (length ``numel``).  When the region is sharded
+        over ``group`` (ZeRO-1) the slices of all ranks are all-gathered: a collective call."""
+        local = {"master": self.master_weights(), "exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq}
+        if self.hi - self.lo == self.numel:
+            return local
+        assert group is not None, "a sharded region needs its data-parallel group to assemble the full state"
+        out = {}
+        for k, v in local.items():
+            full = torch.empty(self.numel, dtype=torch.float32, device=v.device)
+            dist.all_gather_into_tensor(full, v.contiguous(), group=group)
+            out[k] = full
+        return out
+
+    def import_param_state(self, off: int, numel: int, st: dict) -> None:
+        """Copy the part of one parameter's (whole) state that falls into this rank's slice."""
+        lo, hi = max(off, self.lo), min(off + numel, self.hi)
+        if lo >= hi:
+            return
+        src, dst = slice(lo - off, hi - off), slice(lo - self.lo, hi - self.lo)
+        self.set_master_weights(dst, st["master"].reshape(-1)[src])
+        self.exp_avg[dst].copy_(st["exp_avg"].reshape(-1)[src])
+        self.exp_avg_sq[dst].copy_(st["exp_avg_sq"].reshape(-1)[src])
+
     def reset_master_weights(self) -> None:
         """Master weights := the current bf16 parameters."""
         if self.split_master:
@@ -362,17 +386,13 @@ class FusedAdamW(torch.optim.Optimizer):
             for p in g["params"]:
                 index_of[id(p)] = idx
                 idx += 1
-        masters = {id(r): r.master_weights() for _, r in self._regions}
+        # ZeRO-1: every rank assembles the whole state (a collective over the data-parallel group), so that the file a
+        # single rank writes is complete and parameters that straddle a slice boundary are whole
         for _, r in self._regions:
+            full = r.gathered_states(self.dp_group)
             for p, off in zip(r.params, r.offsets):
-                lo, hi = off, off + p.numel()
-                if lo >= r.lo and hi <= r.hi:
-                    s = slice(lo - r.lo, hi - r.lo)
-                    state[index_of[id(p)]] = {
-                        "master": masters[id(r)][s].view(p.shape).clone(),
-                        "exp_avg": r.exp_avg[s].view(p.shape).clone(),
-                        "exp_avg_sq": r.exp_avg_sq[s].view(p.shape).clone(),
-                    }
+                s = slice(off, off + p.numel())
+                state[index_of[id(p)]] = {k: v[s].view(p.shape).clone() for k, v in full.items()}
         groups = []
         start = 0
         for g in self.param_groups:
@@ -401,12 +421,7 @@ class FusedAdamW(torch.optim.Optimizer):
                 st = sd["state"].get(index_of[id(p)])
                 if st is None:
                     continue
-                lo, hi = off, off + p.numel()
-                if lo >= r.lo and hi <= r.hi:
-                    s = slice(lo - r.lo, hi - r.lo)
-                    r.set_master_weights(s, st["master"])
-                    r.exp_avg[s].copy_(st["exp_avg"].reshape(-1))
-                    r.exp_avg_sq[s].copy_(st["exp_avg_sq"].reshape(-1))
+                r.import_param_state(off, p.numel(), st)
 
     def update_master_params(self):
         """Re-read master weights from the (just loaded) bf16 parameters."""

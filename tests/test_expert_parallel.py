@@ -81,3 +81,31 @@ def _ckpt_worker(rank, world):
 
 def test_expert_sharded_state_dict_round_trip():
     run_distributed(_ckpt_worker, 2)
+
+
+def _zero_state_worker(rank, world):
+    """ZeRO-1 optimizer state: every rank holds a slice of the flat state; the gathered view is whole on every rank and
+    loading a whole per-parameter state fills exactly the local slice - also for a parameter that straddles the boundary."""
+    from cornstarch_b200.optim.fused_adamw import _Region
+
+    torch.manual_seed(0)
+    params = [torch.nn.Parameter(torch.randn(n).bfloat16()) for n in (192, 64, 320)]  # 576 elements: the cut at 288 is inside the last one
+    for split in (False, True):
+        region = _Region([torch.nn.Parameter(p.data.clone()) for p in params], torch.bfloat16, (rank, world), None, split_master=split)
+        assert region.hi - region.lo == region.numel // world
+        whole = {k: torch.randn(region.numel, generator=torch.Generator().manual_seed(5 + i))
+                 for i, k in enumerate(("master", "exp_avg", "exp_avg_sq"))}
+        for p, off in zip(region.params, region.offsets):
+            region.import_param_state(off, p.numel(), {k: v[off : off + p.numel()] for k, v in whole.items()})
+        got = region.gathered_states(dist.group.WORLD)
+        covered = torch.zeros(region.numel, dtype=torch.bool)
+        for p, off in zip(region.params, region.offsets):
+            covered[off : off + p.numel()] = True
+        for k in whole:
+            assert torch.equal(got[k][covered], whole[k][covered]), (split, k)
+        # the local slice holds exactly its part
+        assert torch.equal(region.exp_avg, whole["exp_avg"][region.lo : region.hi].where(covered[region.lo : region.hi], region.exp_avg))
+
+
+def test_zero1_state_gathers_whole_and_loads_by_overlap():
+    run_distributed(_zero_state_worker, 2)
