@@ -198,7 +198,8 @@ def test_fused_adamw_split_master_equals_fp32_master():
     runs = {}
     for split in (False, True):
         p = torch.nn.Parameter(init.clone())
-        opt = FusedAdamW([{"params": [p], "weight_decay": 0.05}], lr=3e-3, max_norm=1.0, split_master=split)
+        # no clipping: the gradient norm is summed with atomics, so two runs may differ in its last bit
+        opt = FusedAdamW([{"params": [p], "weight_decay": 0.05}], lr=3e-3, max_norm=0.0, split_master=split)
         assert opt.use_arena and opt._regions[0][1].split_master == split
         g = torch.Generator(device="cuda").manual_seed(7)
         for _ in range(5):
@@ -210,6 +211,6 @@ def test_fused_adamw_split_master_equals_fp32_master():
     assert int((diff != 0).sum()) <= 64 and float(diff.abs().max()) <= float(init.float().abs().max()) * 2.0 ** -7
     # a state dict written by one representation loads into the other
     p2 = torch.nn.Parameter(init.clone())
-    opt2 = FusedAdamW([{"params": [p2], "weight_decay": 0.05}], lr=3e-3, max_norm=1.0, split_master=True)
+    opt2 = FusedAdamW([{"params": [p2], "weight_decay": 0.05}], lr=3e-3, max_norm=0.0, split_master=True)
     opt2.load_state_dict(runs[False][2])
     assert torch.equal(opt2._regions[0][1].master_weights(), runs[False][0])
