@@ -142,3 +142,23 @@ def test_whisper_encoder_matches_hf():
     with torch.no_grad():
         a, b = hf(x).last_hidden_state, mine(input_features=x).last_hidden_state
     assert torch.allclose(b, a, atol=1e-4), (a - b).abs().max()
+
+
+def test_qwen2_audio_encoder_matches_hf():
+    from transformers.models.qwen2_audio.configuration_qwen2_audio import Qwen2AudioEncoderConfig as HC
+    from transformers.models.qwen2_audio.modeling_qwen2_audio import Qwen2AudioEncoder as HM
+
+    from cornstarch_b200.models import whisper as W
+
+    torch.manual_seed(0)
+    kw = dict(num_mel_bins=16, d_model=64, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=128, max_source_positions=50)
+    hfc = HC(**kw)
+    hfc._attn_implementation = "eager"
+    hf = HM(hfc).eval()
+    mine = W.Qwen2AudioEncoder(W.Qwen2AudioEncoderConfig(**kw)).eval()
+    missing, unexpected = mine.load_state_dict(hf.state_dict(), strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    x = torch.randn(2, 16, 100)
+    with torch.no_grad():
+        a, b = hf(x).last_hidden_state, mine(input_features=x).last_hidden_state
+    assert a.shape == b.shape and torch.allclose(b, a, atol=1e-4), (a.shape, b.shape, (a - b).abs().max())
