@@ -30,5 +30,12 @@ def shard_fully(model: nn.Module, mesh=None, reshard_after_forward: bool | None 
             for layer in module:
                 if any(p.requires_grad for p in layer.parameters()):
                     fully_shard(layer, **kw)
+    # projectors recompute their forward in the backward pass (gradient checkpointing): as units of their own they are
+    # gathered again when that forward runs, which parameters left to the root unit are not
+    from ..multimodal.modeling import MultimodalProjector
+
+    for module in list(model.modules()):
+        if isinstance(module, MultimodalProjector) and any(p.requires_grad for p in module.parameters()):
+            fully_shard(module.projection, **kw)  # the inner module returns a plain tensor, which FSDP2 can hook
     fully_shard(model, **kw)
     return model

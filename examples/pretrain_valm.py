@@ -21,13 +21,15 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=3)
     a = ap.parse_args()
-    dev = torch.device("cuda")
-    model = build_model("valm", device=dev, dtype=torch.bfloat16)
+    cuda = torch.cuda.is_available()
+    dev = torch.device("cuda" if cuda else "cpu")
+    shape, dtype = ("valm", torch.bfloat16) if cuda else ("valm_tiny", torch.float32)  # CPU: a toy shape of the same structure
+    model = build_model(shape, device=dev, dtype=dtype)
     model.gradient_checkpointing_enable()
     model.train(encoders_mode={"vision": (False, True), "audio": (False, True)}, llm_mode=True)  # train projectors + LLM
     opt = FusedAdamW(split_decay_groups(model, 0.01), lr=1e-4, max_norm=1.0)
     for step in range(a.steps):
-        batch = synthetic_batch("valm", 1, seed=step, device=dev, dtype=torch.bfloat16)
+        batch = synthetic_batch(shape, 1, seed=step, device=dev, dtype=dtype)
         loss = model(**batch).loss
         loss.backward()
         opt.step()

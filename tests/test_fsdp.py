@@ -15,6 +15,8 @@ def _worker(rank, world):
     ref = zoo.build_model("tiny", device="cpu", dtype=torch.float32)
     torch.manual_seed(0)
     model = zoo.build_model("tiny", device="cpu", dtype=torch.float32)
+    model.gradient_checkpointing_enable()  # layers and projector recompute their forward while parameters are sharded
+    model.train()
     shard_fully(model)
     opt = torch.optim.SGD(model.parameters(), lr=0.1)
     ref_opt = torch.optim.SGD(ref.parameters(), lr=0.1)
