@@ -42,7 +42,7 @@ def test_batch_sampler_example():
         S(range(20), pipeline_index=2, microbatch_size=2, num_microbatches=[2, 3])
 
 
-def _train_worker(rank, world):
+def _train_worker(rank, world, tp=1):
     from cornstarch_b200.booster import Booster
     from cornstarch_b200.models.llama import DecoderConfig, DecoderForCausalLM
     from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
@@ -66,7 +66,7 @@ def _train_worker(rank, world):
         ref_loss += l.item()
     ref_grads = {n: p.grad.clone() for n, p in ref.named_parameters()}
 
-    plugin = HeterogeneousParallelPlugin(tp_size=1, microbatch_size=2, device=torch.device("cpu"))
+    plugin = HeterogeneousParallelPlugin(tp_size=tp, microbatch_size=2, device=torch.device("cpu"))
     one = PipelineTemplate.even_split(model, 1)
     two = PipelineTemplate.even_split(model, 2)
     plugin.set_pipelines([one, two], {one: 1, two: 2})
@@ -79,11 +79,19 @@ def _train_worker(rank, world):
     # weighted partial losses add up to the global mean
     part = out["loss"].clone() if out["loss"] is not None else torch.zeros(())
     dist.all_reduce(part)
-    assert abs(part.item() - ref_loss) < 1e-5, (part.item(), ref_loss)
+    assert abs(part.item() / tp - ref_loss) < 1e-5, (part.item(), ref_loss)  # every tensor-parallel rank of a last stage reports the loss
+    checked = 0
     for n, p in pmodel.module.named_parameters():
+        if p.shape != ref_grads[n].shape:
+            continue  # tensor-parallel shard: covered by the replicated parameters around it and by the loss
         assert torch.allclose(p.grad, ref_grads[n], atol=1e-5), (rank, n, (p.grad - ref_grads[n]).abs().max())
-    assert plugin.train_batch_size == 6
+        checked += 1
+    assert checked > 0 and plugin.train_batch_size == 6
 
 
 def test_two_heterogeneous_pipelines_match_single_process():
     run_distributed(_train_worker, 3)
+
+
+def test_two_heterogeneous_pipelines_with_tensor_parallelism():
+    run_distributed(_train_worker, 6, 2)
