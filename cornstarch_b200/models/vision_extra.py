@@ -547,7 +547,10 @@ class _QwenPatchMerger(nn.Module):
         self.mlp = nn.Sequential(cnn.Linear(self.width, self.width), nn.GELU(), cnn.Linear(self.width, config.hidden_size))
 
     def forward(self, x):
-        return self.mlp(self.ln_q(x).reshape(-1, self.width))
+        h = self.ln_q(x)
+        if h.dim() == 3:  # [images, tokens, C] (context parallelism keeps the image dimension): merge inside each image
+            return self.mlp(h.reshape(h.shape[0], -1, self.width))
+        return self.mlp(h.reshape(-1, self.width))
 
 
 class _QwenVisionRotary(nn.Module):
@@ -604,7 +607,25 @@ class Qwen2VisionTransformerPretrainedModel(_VisionBase):
         ang = self.rot_angles(grid_thw)
         rope = (ang.cos().contiguous(), ang.sin().contiguous())
         pos = torch.arange(n_img * per, device=x.device, dtype=torch.int32).view(n_img, per)
-        x = x.view(n_img, per, -1)
+        group = getattr(self, "_cp_group", None)
+        if group is not None:
+            # Context parallelism: every image's tokens are split over the ranks in whole merge groups (2 x 2 patches
+            # are consecutive tokens), so that the merger can work on a rank's own tokens.  The image dimension is kept
+            # in the output, [images, local tokens / merge, hidden], for the sequence gather that follows the projector.
+            import torch.distributed as dist
+
+            from ..parallel import comm
+
+            ws, r = dist.get_world_size(group), dist.get_rank(group)
+            unit = self.spatial_merge_size ** 2
+            bounds = torch.tensor_split(torch.arange(per // unit), ws)[r]
+            lo, hi = (int(bounds[0]) * unit, (int(bounds[-1]) + 1) * unit) if bounds.numel() else (0, 0)
+            pos = pos[:, lo:hi].contiguous()
+            if embedded is None:
+                x = x.view(n_img, per // unit, -1)
+                x = comm.split_forward_gather_backward(x, 1, group)
+            per = hi - lo
+        x = x.reshape(n_img, per, -1)
         mask = self._attn_mask(x.device)
         for blk in self.blocks:
             if is_released(blk):
@@ -613,10 +634,11 @@ class Qwen2VisionTransformerPretrainedModel(_VisionBase):
                 x = checkpoint_layer(blk, x, mask, rope, pos)
             else:
                 x = blk(x, mask, rope, pos)
-        x = x.reshape(n_img * per, -1)
         if is_released(self.merger):
-            return ModelOutput(hidden_states=x, embedded=True)
-        return ModelOutput(last_hidden_state=self.merger(x))
+            return ModelOutput(hidden_states=x.reshape(n_img * per, -1), embedded=True)
+        if group is not None:
+            return ModelOutput(last_hidden_state=self.merger(x))  # [images, local tokens / merge, hidden]
+        return ModelOutput(last_hidden_state=self.merger(x.reshape(n_img * per, -1)))
 
 
 register_model("dinov2", Dinov2Config, Dinov2Model)

@@ -224,9 +224,7 @@ class Qwen2VisionTransformerPolicy(ModelPolicy):
     model_cls = X.Qwen2VisionTransformerPretrainedModel
     first_stage_modules = ["patch_embed", "rotary_pos_emb"]
     last_stage_modules = ["merger"]
-    # no context parallelism: the merger joins 2 x 2 neighbouring patches, so a token split would have to follow the
-    # patch groups of every image and the flattened [tokens, hidden] output has no per-image dimension to gather along
-    supported_sp_modes = ()
+    supported_sp_modes = ("ring_attn",)  # tokens are split per image in whole 2 x 2 merge groups
     head_modules = r"blocks\.\d+"
     tp_rules = [
         TPRule(r"blocks\.\d+\.attn\.qkv", "col", "qkv"),

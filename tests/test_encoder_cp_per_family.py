@@ -84,3 +84,40 @@ def _group_worker(rank, world, families):
 @pytest.mark.parametrize("families", [FAMILIES[:4], FAMILIES[4:]], ids=["vision_a", "vision_b_and_audio"])
 def test_encoder_ring_attn_matches_unsharded(families):
     run_distributed(_group_worker, 2, families)
+
+
+def _qwen2_vl_worker(rank, world):
+    """The Qwen2-VL tower splits every image's tokens in whole 2 x 2 merge groups and keeps the image dimension in its
+    output; gathered along the token dimension it equals the unsharded tower's (flattened) output."""
+    from cornstarch_b200.models import vision_extra as X
+    from cornstarch_b200.parallel import comm
+    from cornstarch_b200.shardformer.shard.shard_config import ShardConfig
+    from cornstarch_b200.shardformer.shard.shardformer import ShardFormer
+
+    cfg = dict(depth=2, embed_dim=64, hidden_size=48, num_heads=4, mlp_ratio=2, patch_size=14, spatial_merge_size=2, temporal_patch_size=2)
+    torch.manual_seed(0)
+    ref = X.Qwen2VisionTransformerPretrainedModel(X.Qwen2VLVisionConfig(**cfg))
+    torch.manual_seed(0)
+    model = X.Qwen2VisionTransformerPretrainedModel(X.Qwen2VLVisionConfig(**cfg))
+    model.load_state_dict(ref.state_dict())
+    grid = torch.tensor([[1, 16, 16], [1, 16, 16]])
+    x = torch.randn(2 * 256, 3 * 2 * 14 * 14, generator=torch.Generator().manual_seed(5))
+    xr = x.clone().requires_grad_(True)
+    want = ref(hidden_states=xr, grid_thw=grid).last_hidden_state  # [2 * 64, 48]
+    wgt = torch.randn(want.shape, generator=torch.Generator().manual_seed(9))
+    (want.float() * wgt).sum().backward()
+    sc = ShardConfig(sequence_parallel_process_group=dist.group.WORLD, enable_sequence_parallelism=True,
+                     sequence_parallelism_mode="ring_attn", enable_tensor_parallelism=False, extra_kwargs={"device": "cpu"})
+    ShardFormer(sc).optimize(model)
+    xs = x.clone().requires_grad_(True)
+    local = model(hidden_states=xs, grid_thw=grid).last_hidden_state
+    assert local.shape == (2, 64 // world, 48), local.shape
+    full = comm.gather_forward_split_backward(local, 1, dist.group.WORLD).reshape(want.shape)
+    assert torch.allclose(full, want, atol=2e-4, rtol=1e-3), (full - want).abs().max()
+    (full.float() * wgt).sum().backward()
+    err, ref_max = (xs.grad - xr.grad).abs().max().item(), xr.grad.abs().max().item()
+    assert err <= 2e-3 * ref_max, (err, ref_max)
+
+
+def test_qwen2_vl_tower_ring_attn_matches_unsharded():
+    run_distributed(_qwen2_vl_worker, 2)
