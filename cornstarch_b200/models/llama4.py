@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from .. import nn as cnn
 from ..ops import attention as A
@@ -149,6 +150,7 @@ class Llama4TextAttention(nn.Module):
         self.qk_norm = bool(config.use_qk_norm) and self.use_rope
         self.temperature = bool(config.attn_temperature_tuning) and not self.use_rope
         self.floor_scale, self.attn_scale, self.eps = config.floor_scale, config.attn_scale, config.rms_norm_eps
+        self.chunk = int(config.attention_chunk_size)  # RoPE layers attend causally inside chunks of this many tokens
         bias = bool(config.attention_bias)
         self.q_proj = cnn.Linear(H, self.num_heads * D, bias=bias)
         self.k_proj = cnn.Linear(H, self.num_kv_heads * D, bias=bias)
@@ -175,7 +177,19 @@ class Llama4TextAttention(nn.Module):
             scales = torch.log1p(torch.floor((p + 1.0) / self.floor_scale)) * self.attn_scale + 1.0
             q = (q * scales.view(1, S, 1, 1)).to(x.dtype)
         fn = self.attn_impl or A.attention
-        o = fn(q.contiguous(), k.contiguous(), v.contiguous(), mask, None)
+        if self.use_rope and S > self.chunk:
+            # chunked attention: chunks are independent causal sequences, i.e. further batch entries (the tail is padded
+            # with keys that no real query can see, because they come after every real token of their chunk)
+            assert mask is None or mask.mode == A.MASK_CAUSAL, "chunked attention supports the plain causal mask"
+            C = self.chunk
+            pad = (-S) % C
+            if pad:
+                q, k, v = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (q, k, v))
+            n = (S + pad) // C
+            q, k, v = (t.reshape(B * n, C, t.shape[2], D).contiguous() for t in (q, k, v))
+            o = fn(q, k, v, A.AttnMask.causal(), None).reshape(B, n * C, Hq, D)[:, :S]
+        else:
+            o = fn(q.contiguous(), k.contiguous(), v.contiguous(), mask, None)
         return self.o_proj(o.reshape(B, S, Hq * D))
 
 
@@ -231,7 +245,6 @@ class Llama4TextModel(PreTrainedModel):
         if hidden_states is None:
             hidden_states = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
         B, S, _ = hidden_states.shape
-        assert S <= self.config.attention_chunk_size, "sequences longer than attention_chunk_size need chunked attention"
         mask = as_attn_mask(attention_mask, B, S, hidden_states.device)
         rope = self.rotary_emb.tables(S, hidden_states.device)
         x, router = hidden_states, []

@@ -113,3 +113,26 @@ def test_llama4_text_matches_hf():
     assert torch.allclose(ours(input_ids=ids).logits, want.logits, atol=2e-3)
     assert Llama4ForCausalLM.module_names(ours.config)[:3] == ["model.embed_tokens", "model.rotary_emb", "model.layers.0"]
     assert ours.config.moe_layers == [1, 3] and ours.config.no_rope_layers == [1, 1, 1, 0]
+
+
+def test_llama4_chunked_attention_matches_hf():
+    """Sequences longer than ``attention_chunk_size``: RoPE layers attend causally inside chunks, NoPE layers over everything."""
+    from transformers import Llama4TextConfig as HC
+    from transformers.models.llama4.modeling_llama4 import Llama4ForCausalLM as HM
+
+    from cornstarch_b200.models.llama4 import Llama4ForCausalLM, Llama4TextConfig
+
+    kw = dict(vocab_size=100, hidden_size=32, intermediate_size=48, intermediate_size_mlp=64, num_hidden_layers=4,
+              num_attention_heads=4, num_key_value_heads=2, head_dim=8, num_local_experts=4, num_experts_per_tok=1,
+              interleave_moe_layer_step=2, max_position_embeddings=128, attention_chunk_size=16)
+    torch.manual_seed(0)
+    hfc = HC(**kw)
+    hfc._attn_implementation = "eager"
+    hf = HM(hfc).eval()
+    ours = Llama4ForCausalLM(Llama4TextConfig(**kw, rope_theta=hfc.rope_parameters["rope_theta"] if getattr(hfc, "rope_parameters", None) else 500000.0)).eval()
+    _load(ours, hf)
+    ids = torch.randint(0, 100, (2, 40))  # 2.5 chunks
+    with torch.no_grad():
+        want = hf(input_ids=ids).logits
+        got = ours(input_ids=ids).logits
+    assert torch.allclose(got, want, atol=2e-3), (got - want).abs().max()
