@@ -164,9 +164,15 @@ class Llama4TextAttention(nn.Module):
         qkv = multi_linear(self.q_proj.input_hook(x), [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight],
                            [self.q_proj.bias, self.k_proj.bias, self.v_proj.bias] if self.q_proj.bias is not None else None,
                            tp=self.q_proj.tp_spec(x))
-        q = qkv[..., : Hq * D].reshape(B, S, Hq, D)
-        k = qkv[..., Hq * D : (Hq + Hk) * D].reshape(B, S, Hk, D)
-        v = qkv[..., (Hq + Hk) * D :].reshape(B, S, Hk, D)
+        q, k, v = qkv[..., : Hq * D], qkv[..., Hq * D : (Hq + Hk) * D], qkv[..., (Hq + Hk) * D :]
+        pc = getattr(self, "pc", None)
+        ulysses = pc is not None and pc.sp_mode == "all_to_all" and pc.sp_size > 1
+        if ulysses:
+            # [B, S/sp, heads * D] -> [B, S, heads/sp * D]: from here to the output projection every rank sees the whole
+            # sequence for its share of the heads, so rotary positions, temperature and chunking need no bookkeeping
+            q, k, v = (comm.all_to_all_comm(t.contiguous(), pc.sp_group, 2, 1) for t in (q, k, v))
+            Hq, Hk, S = Hq // pc.sp_size, Hk // pc.sp_size, q.shape[1]
+        q, k, v = q.reshape(B, S, Hq, D), k.reshape(B, S, Hk, D), v.reshape(B, S, Hk, D)
         if self.use_rope:
             q, k = rope_interleaved(q, rope[0][:S], rope[1][:S]), rope_interleaved(k, rope[0][:S], rope[1][:S])
         if self.qk_norm:
@@ -190,7 +196,10 @@ class Llama4TextAttention(nn.Module):
             o = fn(q, k, v, A.AttnMask.causal(), None).reshape(B, n * C, Hq, D)[:, :S]
         else:
             o = fn(q.contiguous(), k.contiguous(), v.contiguous(), mask, None)
-        return self.o_proj(o.reshape(B, S, Hq * D))
+        o = o.reshape(B, S, Hq * D)
+        if ulysses:
+            o = comm.all_to_all_comm(o, pc.sp_group, 1, 2)  # back to [B, S/sp, all heads * D]
+        return self.o_proj(o)
 
 
 class Llama4TextDecoderLayer(nn.Module):
@@ -239,14 +248,27 @@ class Llama4TextModel(PreTrainedModel):
     def get_input_embeddings(self):
         return self.embed_tokens
 
+    def set_parallel_context(self, pc):
+        self.pc = pc
+        for layer in self.layers:
+            if not is_released(layer):
+                layer.self_attn.pc = pc
+
     def forward(self, input_ids=None, inputs_embeds=None, attention_mask=None, hidden_states=None, **kw):
         from .llama import as_attn_mask
 
         if hidden_states is None:
             hidden_states = inputs_embeds if inputs_embeds is not None else self.embed_tokens(input_ids)
+        pc = getattr(self, "pc", None)
+        ulysses = pc is not None and pc.sp_mode == "all_to_all" and pc.sp_size > 1
+        if ulysses:
+            assert attention_mask is None, "Ulysses for Llama-4 supports the plain causal mask"
+            if self.holds("embed_tokens"):
+                # every rank keeps a contiguous 1/sp slice of the sequence between attention layers
+                hidden_states = comm.split_forward_gather_backward(hidden_states, 1, pc.sp_group, 1.0 / pc.sp_size)
         B, S, _ = hidden_states.shape
         mask = as_attn_mask(attention_mask, B, S, hidden_states.device)
-        rope = self.rotary_emb.tables(S, hidden_states.device)
+        rope = self.rotary_emb.tables(S * (pc.sp_size if ulysses else 1), hidden_states.device)
         x, router = hidden_states, []
         for layer in self.layers:
             if is_released(layer):
@@ -259,7 +281,11 @@ class Llama4TextModel(PreTrainedModel):
                 router.append(lg)
         if is_released(self.norm):
             return ModelOutput(hidden_states=x, router_logits=tuple(router) or None)
-        return ModelOutput(last_hidden_state=self.norm(x), router_logits=tuple(router) or None)
+        out = self.norm(x)
+        if ulysses:
+            # back to the full sequence for the LM head (the loss is then the same on every sequence-parallel rank)
+            out = comm.gather_forward_split_backward(out, 1, pc.sp_group, float(pc.sp_size))
+        return ModelOutput(last_hidden_state=out, router_logits=tuple(router) or None)
 
 
 class Llama4ForCausalLM(PreTrainedModel):
