@@ -42,6 +42,8 @@ _ALIASES = {
     "cornstarch.shardformer.layers": "cornstarch_b200.shardformer.layers",
     "cornstarch.shardformer.layers.utils": "cornstarch_b200.shardformer.layers.utils",
     "cornstarch.shardformer.layers.operation": "cornstarch_b200.shardformer.layers.operation",
+    "cornstarch.shardformer.layers.context_parallel_bitfield_attention": "cornstarch_b200.shardformer.layers.context_parallel_bitfield_attention",
+    "cornstarch.shardformer.layers.context_parallel_attention": "cornstarch_b200.shardformer.layers.context_parallel_attention",
     "cornstarch.testing": "cornstarch_b200.testing",
     "cornstarch.testing.timer": "cornstarch_b200.testing.timer",
     "cornstarch.testing.dcgm": "cornstarch_b200.testing.dcgm",

@@ -104,6 +104,22 @@ def _cp_attention_worker(rank, world):
         assert torch.allclose(lv.grad, ref_v.grad.index_select(1, st.mine), atol=1e-5), mode
 
 
+    # the entry points at the reference's import paths ([B, heads, S, D] in, [B, S, heads, D] out)
+    from cornstarch_b200.shardformer.layers.context_parallel_attention import context_parallel_flash_attention_forward
+    from cornstarch_b200.shardformer.layers.context_parallel_bitfield_attention import context_parallel_bitfield_attention_forward
+
+    offsets = U.create_context_parallel_split(bits, group, "makespan_min")
+    mine = offsets[rank]
+    out, _ = context_parallel_bitfield_attention_forward(
+        None, *(t.index_select(1, mine).transpose(1, 2) for t in (q, k, v)), bits, offsets_per_rank=offsets, sp_group=group)
+    assert torch.allclose(out, ref.index_select(1, mine), atol=1e-5)
+    chunk = torch.tensor_split(torch.arange(S), world)[rank]
+    full_ref, _ = A.attention_reference(q, k, v, A.AttnMask.full())
+    out, _ = context_parallel_flash_attention_forward(
+        None, *(t.index_select(1, chunk).transpose(1, 2) for t in (q, k, v)), sp_group=group)
+    assert torch.allclose(out, full_ref.index_select(1, chunk), atol=1e-5)
+
+
 def test_context_parallel_attention_matches_single_device():
     run_distributed(_cp_attention_worker, 2)
 
