@@ -30,6 +30,13 @@ _ALIASES = {
     "cornstarch.kernel.attention": "cornstarch_b200.kernel.attention",
     "cornstarch.plugin": "cornstarch_b200.plugin",
     "cornstarch.plugin.multimodal_parallel_plugin": "cornstarch_b200.plugin.multimodal_api",
+    # the sub-modules of that package: every one resolves to the module that exports all of the package's names
+    "cornstarch.plugin.multimodal_parallel_plugin.modal_parallel_plugin": "cornstarch_b200.plugin.modal_parallel_plugin",
+    "cornstarch.plugin.multimodal_parallel_plugin.multimodal_parallel_plugin": "cornstarch_b200.plugin.multimodal_parallel_plugin",
+    "cornstarch.plugin.multimodal_parallel_plugin.modal_process_group_mesh": "cornstarch_b200.parallel.mesh",
+    "cornstarch.plugin.multimodal_parallel_plugin.multimodal_stage_manager": "cornstarch_b200.parallel.stage_manager",
+    "cornstarch.plugin.multimodal_parallel_plugin.multimodal_1f1b": "cornstarch_b200.plugin.multimodal_api",
+    "cornstarch.plugin.multimodal_parallel_plugin.multimodal_parallel_checkpoint_io": "cornstarch_b200.plugin.checkpoint_io",
     "cornstarch.plugin.encoders_colocated_plugin": "cornstarch_b200.plugin.encoders_colocated_plugin",
     "cornstarch.plugin.encoders_colocated_plugin.encoders_colocated_plugin": "cornstarch_b200.plugin.encoders_colocated_plugin",
     "cornstarch.plugin.heterogeneous_parallel_plugin": "cornstarch_b200.plugin.heterogeneous_parallel_plugin",
