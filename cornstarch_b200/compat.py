@@ -40,6 +40,11 @@ _ALIASES = {
     "cornstarch.plugin.encoders_colocated_plugin": "cornstarch_b200.plugin.encoders_colocated_plugin",
     "cornstarch.plugin.encoders_colocated_plugin.encoders_colocated_plugin": "cornstarch_b200.plugin.encoders_colocated_plugin",
     "cornstarch.plugin.heterogeneous_parallel_plugin": "cornstarch_b200.plugin.heterogeneous_parallel_plugin",
+    **{f"cornstarch.plugin.heterogeneous_parallel_plugin.{m}": "cornstarch_b200.plugin.heterogeneous_parallel_plugin"
+       for m in ("heterogeneous_dataloader", "heterogeneous_parallel_module", "heterogeneous_parallel_plugin",
+                 "heterogeneous_process_group_mesh", "heterogeneous_stage_manager")},
+    **{f"cornstarch.plugin.encoders_colocated_plugin.{m}": "cornstarch_b200.plugin.encoders_colocated_plugin"
+       for m in ("encoders_colocated_stage_manager", "process_group_mesh")},
     "cornstarch.shardformer": "cornstarch_b200.shardformer",
     "cornstarch.shardformer.shard": "cornstarch_b200.shardformer.shard",
     "cornstarch.shardformer.shard.shard_config": "cornstarch_b200.shardformer.shard.shard_config",
