@@ -57,6 +57,12 @@ _ALIASES = {
     "cornstarch.shardformer.shard.shardformer": "cornstarch_b200.shardformer.shard.shardformer",
     "cornstarch.shardformer.policies": "cornstarch_b200.shardformer.policies",
     "cornstarch.shardformer.policies.auto_policy": "cornstarch_b200.shardformer.policies.auto_policy",
+    "cornstarch.shardformer.policies.pipeline_template_policy": "cornstarch_b200.shardformer.policies.pipeline_template_policy",
+    "cornstarch.shardformer.policies.multimodal": "cornstarch_b200.shardformer.policies.families",
+    **{f"cornstarch.shardformer.policies.{m}": "cornstarch_b200.shardformer.policies.families"
+       for m in ("bert", "clip", "dinov2", "evaclip", "gemma", "gemma2", "gemma3", "gpt2", "intern_vit", "llama", "llama4",
+                 "mistral", "mixtral", "opt", "phi3", "phi4_multimodal", "pixtral", "qwen2", "qwen2_audio", "qwen2_vision",
+                 "qwen3", "qwen3_moe", "siglip", "vit", "whisper")},
     "cornstarch.shardformer.layers": "cornstarch_b200.shardformer.layers",
     "cornstarch.shardformer.layers.utils": "cornstarch_b200.shardformer.layers.utils",
     "cornstarch.shardformer.layers.operation": "cornstarch_b200.shardformer.layers.operation",
