@@ -133,6 +133,24 @@ def test_reference_import_paths_resolve():
     assert hasattr(m, "MultimodalModel") and hasattr(m, "ModalEncoderModule")
     p = importlib.import_module("cornstarch.plugin.multimodal_parallel_plugin")
     assert hasattr(p, "MultimodalParallelPlugin")
+    for path, names in {
+        "cornstarch.plugin.multimodal_parallel_plugin.multimodal_1f1b": ["MultimodalEncoderTrainingOneForwardOneBackwardSchedule", "MultimodalPipelineP2PCommunication"],
+        "cornstarch.plugin.multimodal_parallel_plugin.modal_process_group_mesh": ["MultiModalProcessGroupMesh"],
+        "cornstarch.plugin.multimodal_parallel_plugin.multimodal_parallel_checkpoint_io": ["MultimodalParallelCheckpointIO"],
+        "cornstarch.plugin.encoders_colocated_plugin.encoders_colocated_plugin": ["EncodersColocatedMultimodalParallelPlugin"],
+        "cornstarch.plugin.heterogeneous_parallel_plugin.heterogeneous_dataloader": ["HeterogeneousDataLoader"],
+        "cornstarch.shardformer.policies.llama": ["LlamaForCausalLMPolicy", "LlamaModelPolicy"],
+        "cornstarch.shardformer.policies.siglip": ["SiglipVisionModelPolicy"],
+        "cornstarch.shardformer.layers.context_parallel_bitfield_attention": ["context_parallel_bitfield_attention_forward"],
+        "cornstarch.shardformer.layers.utils": ["ContextParallelBatchSplitUtils"],
+        "cornstarch.models.evaclip": ["EvaCLIPVisionModel", "EvaCLIPVisionConfig"],
+        "cornstarch.models.intern_vit": ["InternVisionModel"],
+        "cornstarch.kernel.bitfield_attention": ["bitfield_attn_func", "BitfieldUtils"],
+        "cornstarch.testing.timer": ["TimerContextManager"],
+        "colossalai.booster": ["Booster"],
+    }.items():
+        mod = importlib.import_module(path)
+        assert all(hasattr(mod, n) for n in names), (path, [n for n in names if not hasattr(mod, n)])
 
 
 def test_lora_adapters_train_only_low_rank_and_merge():
