@@ -173,7 +173,16 @@ def main():
 
     # ---- device-timed region: inputs already on the device
     for i in range(W):
-        trainer.step_device()
+        try:
+            trainer.step_device()
+        except torch.cuda.OutOfMemoryError:
+            # a kept layer cost more than measured: on one GPU (no peer is waiting in a collective) fall back to
+            # recomputing every layer and carry on with the warm-up
+            if world > 1 or not hasattr(trainer, "recompute_everything"):
+                raise
+            trainer.recompute_everything()
+            args.recompute = "full"
+            trainer.step_device()
         if i < 2 and args.recompute == "auto" and hasattr(trainer, "tune_recompute"):
             # the first step ran with every layer recomputed and shows how much memory is left: layers that fit stop
             # being recomputed; the second step shows what a kept layer really costs and may add more.  The remaining

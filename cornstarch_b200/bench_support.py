@@ -96,6 +96,15 @@ class SingleDeviceTrainer:
         self.recompute = f"{n - keep} of {n} decoder layers (the other {keep} fit in free memory), encoder layers"
         return keep
 
+    def recompute_everything(self):
+        """Back to recomputing every layer (after an out-of-memory error): drops half-accumulated gradients too."""
+        self.model.gradient_checkpointing_enable({"keep_last_layers": 0})
+        self.recompute = "every layer (a step with kept layers ran out of memory)"
+        self.opt.zero_grad()
+        if getattr(self.opt, "use_arena", False):
+            self.opt.clear_main_grads()
+        torch.cuda.empty_cache()
+
     def step_device(self):
         return self._run(self.dev)
 
