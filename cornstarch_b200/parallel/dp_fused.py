@@ -163,6 +163,18 @@ class OverlappedGradReduce:
         self.done[bi].append((lo, hi))
         self.launches += 1
 
+    @staticmethod
+    def gaps(done: list[tuple[int, int]], numel: int) -> list[tuple[int, int]]:
+        """The ranges of ``[0, numel)`` that no entry of ``done`` covers, in order."""
+        out, pos = [], 0
+        for lo, hi in sorted(done):
+            if lo > pos:
+                out.append((pos, lo))
+            pos = max(pos, hi)
+        if pos < numel:
+            out.append((pos, numel))
+        return out
+
     def finish(self) -> None:
         """Reduce every range no layer hook covered, then wait until all ranks' pushes have landed here."""
         r = self.reducer
@@ -172,13 +184,8 @@ class OverlappedGradReduce:
             self.side.wait_event(ev)
             saved, self.max_ctas = self.max_ctas, 0  # the backward pass is over: use the whole GPU
             for bi, flat in enumerate(self.flat_grads):
-                pos = 0
-                for lo, hi in sorted(self.done[bi]):
-                    if lo > pos:
-                        self._reduce_range(bi, pos, lo)
-                    pos = max(pos, hi)
-                if pos < flat.numel():
-                    self._reduce_range(bi, pos, flat.numel())
+                for lo, hi in self.gaps(self.done[bi], flat.numel()):
+                    self._reduce_range(bi, lo, hi)
             self.max_ctas = saved
             lib, st = nat.lib(), nat.stream()
             status = nat.status_word(self.flat_grads[0].device)

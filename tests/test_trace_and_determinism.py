@@ -113,3 +113,15 @@ def test_split_master_weights_are_exact():
     assert torch.equal(p.data[not_tie], vals.bfloat16()[not_tie])  # same as round-to-nearest-even away from ties
     region.reset_master_weights()
     assert torch.equal(region.master_weights(), p.data.float())
+
+
+def test_overlapped_reduce_covers_every_element_once():
+    """What the layer hooks reduced plus what ``finish`` adds is a partition of the flat buffer."""
+    from cornstarch_b200.parallel.dp_fused import OverlappedGradReduce as O
+
+    assert O.gaps([], 640) == [(0, 640)]
+    assert O.gaps([(128, 256), (0, 64)], 640) == [(64, 128), (256, 640)]
+    assert O.gaps([(0, 640)], 640) == []
+    done = [(320, 448), (448, 576), (64, 320)]
+    pieces = sorted(done + O.gaps(done, 640))
+    assert pieces[0][0] == 0 and pieces[-1][1] == 640 and all(a[1] == b[0] for a, b in zip(pieces, pieces[1:]))
