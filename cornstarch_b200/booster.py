@@ -15,8 +15,10 @@ class Booster:
         self.plugin = plugin
         self.checkpoint_io = None
 
-    def boost(self, model, optimizer=None, criterion=None, dataloader=None, lr_scheduler=None):
-        out = self.plugin.configure(model, optimizer, criterion, dataloader, lr_scheduler)
+    def boost(self, model, optimizer=None, criterion=None, dataloader=None, lr_scheduler=None, **plugin_kwargs):
+        """``plugin_kwargs`` go to the plugin's ``configure`` (``forced=True`` re-plans an already boosted model with the
+        heterogeneous plugin)."""
+        out = self.plugin.configure(model, optimizer, criterion, dataloader, lr_scheduler, **plugin_kwargs)
         self.checkpoint_io = self.plugin.get_checkpoint_io()
         return out
 

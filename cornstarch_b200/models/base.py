@@ -115,24 +115,36 @@ class PreTrainedModel(nn.Module):
         return self._held is None or name in self._held
 
     def hold_only(self, names: list[str]) -> None:
-        """Release every pipeline unit that is not in ``names`` (its parameters are freed)."""
+        """Release every pipeline unit that is not in ``names``: its parameters are freed, the module itself is kept on
+        the meta device inside the placeholder.  A unit in ``names`` that an earlier call released comes back from there
+        with meta parameters, to be materialised (``materialize_meta``) and filled from a checkpoint - what re-planning
+        the pipelines of a running job needs."""
         all_names = self.module_names(self.config)
         unknown = set(names) - set(all_names)
         assert not unknown, f"unknown module names {sorted(unknown)}"
         self._held = set(names)
         for n in all_names:
-            if n in self._held:
-                continue
             parent, attr = self._resolve_parent(n)
             if parent is None:
                 continue
-            target = parent[int(attr)] if isinstance(parent, (nn.ModuleList, nn.Sequential)) else getattr(parent, attr)
+            in_list = isinstance(parent, (nn.ModuleList, nn.Sequential))
+            target = parent[int(attr)] if in_list else getattr(parent, attr)
+
+            def put(m):
+                if in_list:
+                    parent[int(attr)] = m
+                else:
+                    setattr(parent, attr, m)
+
+            if n in self._held:
+                if isinstance(target, _Released) and target.stash is not None:
+                    put(target.stash)
+                continue
+            if isinstance(target, _Released):
+                continue
             if isinstance(target, nn.Module) and not any(True for _ in target.parameters()):
                 continue  # stateless helpers (rotary tables, activations, poolers) cost nothing to keep
-            if isinstance(parent, (nn.ModuleList, nn.Sequential)):
-                parent[int(attr)] = _Released()
-            else:
-                setattr(parent, attr, _Released())
+            put(_Released(target.to("meta") if isinstance(target, nn.Module) else None))
 
     def _resolve_parent(self, dotted: str):
         obj = self
@@ -208,7 +220,12 @@ class PreTrainedModel(nn.Module):
 
 
 class _Released(nn.Module):
-    """Placeholder left where a pipeline unit was released; calling it is a bug in the stage plan."""
+    """Placeholder left where a pipeline unit was released; calling it is a bug in the stage plan.  The released module
+    itself (parameters on the meta device: shapes and dtypes, no storage) waits in ``stash`` for a later re-plan."""
+
+    def __init__(self, stash: nn.Module | None = None):
+        super().__init__()
+        object.__setattr__(self, "stash", stash)  # not a sub-module: invisible to parameters() and state_dict()
 
     def forward(self, *a, **k):
         raise RuntimeError("this module is not held by the current pipeline stage")
