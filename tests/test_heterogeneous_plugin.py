@@ -150,12 +150,14 @@ def _replan_worker(rank, world, tmp):
     popt.zero_grad()
     ckpt = os.path.join(tmp, "model")
     booster.save_model(pmodel, ckpt, shard=True)
+    booster.save_optimizer(popt, os.path.join(tmp, "optim"), shard=True)
     dist.barrier()
 
     # membership "changed": the deep pipeline now comes first
     plugin.set_pipelines([two, one], {two: 2, one: 1})
     pmodel, popt, crit, *_ = booster.boost(pmodel, popt, criterion=crit, forced=True)
     booster.load_model(pmodel, ckpt)
+    booster.load_optimizer(popt, os.path.join(tmp, "optim"))  # Adam moments of the units this rank holds NOW, by name
     ref_sd = ref.state_dict()
     held = 0
     for n, p in pmodel.module.named_parameters():
@@ -167,6 +169,11 @@ def _replan_worker(rank, world, tmp):
     dist.all_reduce(part)
     want = ref_step(ref_opt)
     assert abs(part.item() - want) < 1e-4, (part.item(), want)
+    # with the restored moments the second update lands on the single-process weights as well
+    popt.step()
+    ref_sd = ref.state_dict()
+    for n, p in pmodel.module.named_parameters():
+        assert torch.allclose(p, ref_sd[n], atol=2e-4), (rank, n, (p - ref_sd[n]).abs().max())  # 2 % of one update (lr 1e-2)
 
 
 def test_replan_restores_released_units_and_continues(tmp_path):
