@@ -191,7 +191,16 @@ class PreTrainedModel(nn.Module):
         from ..checkpoint.io import load_state_dict_any
 
         if config is None:
-            config = cls.config_class.from_pretrained(path)
+            # several families share one model class (the decoder): the checkpoint's ``model_type`` picks the config
+            # class, and with it the family's details (q/k norms, fused projections, biases, experts)
+            with open(os.path.join(path, CONFIG_NAME)) as f:
+                reg = registered(json.load(f).get("model_type", ""))
+            if reg is not None and (issubclass(reg[1], cls) or issubclass(cls, reg[1])):
+                config = reg[0].from_pretrained(path)
+                if issubclass(reg[1], cls):
+                    cls = reg[1]  # e.g. the MoE subclass for a Mixtral checkpoint
+            else:
+                config = cls.config_class.from_pretrained(path)
         model = cls(config, **kwargs)
         sd = load_state_dict_any(path)
         missing, unexpected = model.load_state_dict(sd, strict=False)

@@ -1,0 +1,73 @@
+"""Checkpoint format: a directory written by ``save_pretrained`` here loads in Hugging Face ``transformers`` and gives the
+same outputs, and a directory written by ``transformers`` loads here."""
+
+import pytest
+import torch
+
+tf = pytest.importorskip("transformers")
+
+KW = dict(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+          num_key_value_heads=2, max_position_embeddings=64)
+
+
+def _decoder(family):
+    from cornstarch_b200.models import llama as L
+    from cornstarch_b200.models import moe as M
+
+    if family == "mixtral":
+        return M.MoeForCausalLM(M.MixtralConfig(**KW, num_local_experts=4, num_experts_per_tok=2)), tf.MixtralForCausalLM
+    cfg_cls, hf_cls, extra = {
+        "llama": (L.LlamaConfig, tf.LlamaForCausalLM, {}),
+        "mistral": (L.MistralConfig, tf.MistralForCausalLM, {}),
+        "qwen2": (L.Qwen2Config, tf.Qwen2ForCausalLM, {}),
+        "qwen3": (L.Qwen3Config, tf.Qwen3ForCausalLM, dict(head_dim=16)),
+        "phi3": (L.Phi3Config, tf.Phi3ForCausalLM, dict(pad_token_id=0)),
+    }[family]
+    return L.DecoderForCausalLM(cfg_cls(**KW, **extra)), hf_cls
+
+
+@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "qwen3", "phi3", "mixtral"])
+def test_decoder_checkpoints_round_trip_through_transformers(family, tmp_path):
+    torch.manual_seed(0)
+    mine, hf_cls = _decoder(family)
+    mine.eval()
+    mine.save_pretrained(str(tmp_path / "ours"))
+    hf = hf_cls.from_pretrained(str(tmp_path / "ours")).eval()
+    ids = torch.randint(0, 128, (2, 16))
+    with torch.no_grad():
+        want = mine(input_ids=ids).logits
+        assert torch.allclose(hf(input_ids=ids).logits, want, atol=1e-4)
+    hf.save_pretrained(str(tmp_path / "theirs"))
+    back = type(mine).from_pretrained(str(tmp_path / "theirs")).eval()
+    with torch.no_grad():
+        assert torch.allclose(back(input_ids=ids).logits, want, atol=1e-5)
+
+
+def test_vision_checkpoints_round_trip_through_transformers(tmp_path):
+    from cornstarch_b200.models import vision as V
+
+    torch.manual_seed(0)
+    common = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=28, patch_size=14)
+    px = torch.randn(2, 3, 28, 28)
+    for name, mine, hf_cls in (("siglip", V.SiglipVisionModel(V.SiglipVisionConfig(**common)), tf.SiglipVisionModel),
+                               ("clip", V.CLIPVisionModel(V.CLIPVisionConfig(**common)), tf.CLIPVisionModel),
+                               ("vit", V.ViTModel(V.ViTConfig(**common)), tf.ViTModel)):
+        mine.eval()
+        mine.save_pretrained(str(tmp_path / name))
+        hf = hf_cls.from_pretrained(str(tmp_path / name)).eval()
+        with torch.no_grad():
+            a, b = hf(pixel_values=px).last_hidden_state, mine(pixel_values=px).last_hidden_state
+        assert torch.allclose(a, b, atol=1e-4), (name, (a - b).abs().max())
+
+
+def test_auto_model_picks_the_family_from_the_checkpoint(tmp_path):
+    from cornstarch_b200.models import AutoModel
+
+    torch.manual_seed(0)
+    hf = tf.Qwen3ForCausalLM(tf.Qwen3Config(**KW, head_dim=16)).eval()
+    hf.save_pretrained(str(tmp_path))
+    mine = AutoModel.from_pretrained(str(tmp_path)).eval()
+    assert hasattr(mine.model.layers[0].self_attn, "q_norm")
+    ids = torch.randint(0, 128, (1, 12))
+    with torch.no_grad():
+        assert torch.allclose(mine(input_ids=ids).logits, hf(input_ids=ids).logits, atol=1e-4)
