@@ -204,6 +204,9 @@ class PreTrainedModel(nn.Module):
         model = cls(config, **kwargs)
         sd = load_state_dict_any(path)
         missing, unexpected = model.load_state_dict(sd, strict=False)
+        if getattr(config, "tie_word_embeddings", False):
+            # tied output embeddings are stored once: the head shares the input embedding's tensor
+            missing = [k for k in missing if not k.endswith("lm_head.weight") and "decoder.weight" not in k]
         if strict and (missing or unexpected):
             raise RuntimeError(f"from_pretrained: missing={missing} unexpected={unexpected}")
         if dtype is not None or device is not None:

@@ -42,8 +42,10 @@ class Qwen3MoeConfig(DecoderConfig):
     model_type = "qwen3_moe"
 
     def __init__(self, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=768, norm_topk_prob=True,
-                 decoder_sparse_step=1, mlp_only_layers=None, router_aux_loss_coef=0.001, **kw):
-        self.num_experts = num_experts
+                 decoder_sparse_step=1, mlp_only_layers=None, router_aux_loss_coef=0.001, num_local_experts=None, **kw):
+        if num_local_experts is not None:
+            num_experts = num_local_experts  # the name newer ``transformers`` releases write into config.json
+        self.num_experts = self.num_local_experts = num_experts
         self.num_experts_per_tok = num_experts_per_tok
         self.moe_intermediate_size = moe_intermediate_size
         self.norm_topk_prob = norm_topk_prob

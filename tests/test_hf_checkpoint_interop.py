@@ -71,3 +71,38 @@ def test_auto_model_picks_the_family_from_the_checkpoint(tmp_path):
     ids = torch.randint(0, 128, (1, 12))
     with torch.no_grad():
         assert torch.allclose(mine(input_ids=ids).logits, hf(input_ids=ids).logits, atol=1e-4)
+
+
+@pytest.mark.parametrize("family", ["gemma", "gemma2", "qwen3_moe", "gpt2", "opt", "dinov2"])
+def test_auto_model_loads_transformers_checkpoints(family, tmp_path):
+    """A directory written by ``transformers`` loads through ``AutoModel`` without missing or unexpected tensors and gives
+    the same output."""
+    from cornstarch_b200.models import AutoModel
+
+    torch.manual_seed(0)
+    ids = torch.randint(0, 128, (2, 12))
+    if family == "gemma":
+        hf = tf.GemmaForCausalLM(tf.GemmaConfig(**KW, head_dim=16, hidden_activation="gelu_pytorch_tanh"))
+    elif family == "gemma2":
+        hf = tf.Gemma2ForCausalLM(tf.Gemma2Config(**KW, head_dim=16, query_pre_attn_scalar=16, attn_logit_softcapping=None,
+                                                  final_logit_softcapping=None, sliding_window=4096))
+    elif family == "qwen3_moe":
+        hf = tf.Qwen3MoeForCausalLM(tf.Qwen3MoeConfig(**KW, head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
+                                                      decoder_sparse_step=1, mlp_only_layers=[]))
+    elif family == "gpt2":
+        hf = tf.GPT2LMHeadModel(tf.GPT2Config(n_layer=2, n_embd=64, n_head=4, vocab_size=128, n_positions=64))
+    elif family == "opt":
+        hf = tf.OPTForCausalLM(tf.OPTConfig(vocab_size=128, hidden_size=64, ffn_dim=128, num_hidden_layers=2, num_attention_heads=4,
+                                            max_position_embeddings=64, word_embed_proj_dim=64))
+    else:
+        hf = tf.Dinov2Model(tf.Dinov2Config(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, image_size=28, patch_size=14))
+    hf.eval()
+    hf.save_pretrained(str(tmp_path))
+    mine = AutoModel.from_pretrained(str(tmp_path)).eval()
+    with torch.no_grad():
+        if family == "dinov2":
+            px = torch.randn(2, 3, 28, 28)
+            a, b = hf(pixel_values=px).last_hidden_state, mine(pixel_values=px).last_hidden_state
+        else:
+            a, b = hf(input_ids=ids).logits, mine(input_ids=ids).logits
+    assert torch.allclose(a, b, atol=2e-4), (family, (a - b).abs().max())
