@@ -36,6 +36,25 @@ def registered(model_type: str):
     return _MODEL_REGISTRY.get(model_type)
 
 
+_CHECKPOINT_PREFIXES = ("", "model.", "encoder.", "model.encoder.", "vision_tower.", "model.vision_tower.", "visual.",
+                        "model.visual.", "audio_tower.", "model.audio_tower.", "language_model.", "model.language_model.",
+                        "transformer.", "bert.")
+
+
+def _strip_checkpoint_prefix(sd: dict, wanted: set) -> dict:
+    """A sub-model is often loaded from the checkpoint of a larger one (the Whisper encoder from a full Whisper model, a
+    vision tower from a vision-language model): find the key prefix under which most of the wanted tensors live and
+    return that part of the state dict without it (the counterpart of ``base_model_prefix`` handling in ``transformers``)."""
+    best, best_hits = "", sum(k in sd for k in wanted)
+    for p in _CHECKPOINT_PREFIXES[1:]:
+        hits = sum((p + k) in sd for k in wanted)
+        if hits > best_hits:
+            best, best_hits = p, hits
+    if not best:
+        return sd
+    return {k[len(best):]: v for k, v in sd.items() if k.startswith(best)}
+
+
 class PretrainedConfig:
     """Attribute bag with HF ``config.json`` round-tripping.  Subclasses set ``model_type`` and defaults."""
 
@@ -83,6 +102,9 @@ class PretrainedConfig:
             reg = registered(d.get("model_type", ""))
             if reg is not None:
                 return reg[0].from_dict(d)
+        sub = getattr(cls, "composite_key", None)
+        if sub and isinstance(d.get(sub), dict) and d.get("model_type") != cls.model_type:
+            d = d[sub]  # the config of a composite model (CLIP / SigLIP with both towers, a vision-language model)
         return cls.from_dict(d)
 
     def __repr__(self):
@@ -202,13 +224,18 @@ class PreTrainedModel(nn.Module):
             else:
                 config = cls.config_class.from_pretrained(path)
         model = cls(config, **kwargs)
-        sd = load_state_dict_any(path)
+        sd = _strip_checkpoint_prefix(load_state_dict_any(path), set(model.state_dict().keys()))
         missing, unexpected = model.load_state_dict(sd, strict=False)
         if getattr(config, "tie_word_embeddings", False):
             # tied output embeddings are stored once: the head shares the input embedding's tensor
             missing = [k for k in missing if not k.endswith("lm_head.weight") and "decoder.weight" not in k]
-        if strict and (missing or unexpected):
-            raise RuntimeError(f"from_pretrained: missing={missing} unexpected={unexpected}")
+        if strict and missing:
+            raise RuntimeError(f"from_pretrained: missing={missing} unexpected={list(unexpected)[:8]}")
+        if unexpected:
+            # tensors of other parts of a larger checkpoint (a text tower, a decoder): ignored, as ``transformers`` does
+            import logging
+
+            logging.getLogger(__name__).info("from_pretrained(%s): %d tensors of the checkpoint are not used", path, len(unexpected))
         if dtype is not None or device is not None:
             model = model.to(device=device, dtype=dtype)
         return model

@@ -33,6 +33,7 @@ from .base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, r
 
 class DecoderConfig(PretrainedConfig):
     model_type = "llama"
+    composite_key = "text_config"
 
     def __init__(self, vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
                  num_attention_heads=32, num_key_value_heads=None, head_dim=None, hidden_act="silu",

@@ -24,6 +24,8 @@ from .base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, r
 
 
 class VisionConfig(PretrainedConfig):
+    composite_key = "vision_config"
+
     model_type = "siglip_vision_model"
 
     def __init__(self, hidden_size=768, intermediate_size=3072, num_hidden_layers=12, num_attention_heads=12,

@@ -106,3 +106,30 @@ def test_auto_model_loads_transformers_checkpoints(family, tmp_path):
         else:
             a, b = hf(input_ids=ids).logits, mine(input_ids=ids).logits
     assert torch.allclose(a, b, atol=2e-4), (family, (a - b).abs().max())
+
+
+def test_sub_models_load_from_composite_checkpoints(tmp_path):
+    """The Whisper encoder from a full Whisper checkpoint, the SigLIP vision tower from a two-tower SigLIP checkpoint: the
+    key prefix and the nested config are found, the other tensors are ignored."""
+    from cornstarch_b200.models import vision as V
+    from cornstarch_b200.models import whisper as W
+
+    torch.manual_seed(0)
+    kw = dict(num_mel_bins=16, d_model=64, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=128, max_source_positions=50)
+    hf = tf.WhisperForConditionalGeneration(tf.WhisperConfig(
+        **kw, decoder_layers=1, decoder_attention_heads=4, decoder_ffn_dim=64, vocab_size=100, pad_token_id=0, bos_token_id=1,
+        eos_token_id=2, decoder_start_token_id=1)).eval()
+    hf.save_pretrained(str(tmp_path / "whisper"))
+    enc = W.WhisperEncoder.from_pretrained(str(tmp_path / "whisper")).eval()
+    x = torch.randn(2, 16, 100)
+    with torch.no_grad():
+        assert torch.allclose(enc(input_features=x).last_hidden_state, hf.model.encoder(x).last_hidden_state, atol=1e-4)
+
+    common = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=28, patch_size=14)
+    two = tf.SiglipModel(tf.SiglipConfig(vision_config=common, text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=1,
+                                                                                num_attention_heads=4, vocab_size=100))).eval()
+    two.save_pretrained(str(tmp_path / "siglip"))
+    tower = V.SiglipVisionModel.from_pretrained(str(tmp_path / "siglip")).eval()
+    px = torch.randn(2, 3, 28, 28)
+    with torch.no_grad():
+        assert torch.allclose(tower(pixel_values=px).last_hidden_state, two.vision_model(pixel_values=px).last_hidden_state, atol=1e-4)
