@@ -38,7 +38,7 @@ def registered(model_type: str):
 
 _CHECKPOINT_PREFIXES = ("", "model.", "encoder.", "model.encoder.", "vision_tower.", "model.vision_tower.", "visual.",
                         "model.visual.", "audio_tower.", "model.audio_tower.", "language_model.", "model.language_model.",
-                        "transformer.", "bert.")
+                        "transformer.", "bert.", "vit.", "dinov2.", "model.decoder.")
 
 
 def _strip_checkpoint_prefix(sd: dict, wanted: set) -> dict:
