@@ -102,6 +102,19 @@ def _roundtrip_worker(rank, world, tp, llm_stages):
                 assert set(j) == {"metadata", "weight_map"} and "total_size" in j["metadata"]
             assert not os.path.isdir(os.path.join(d, "tmp_index_files"))
         assert os.path.isdir(os.path.join(root, "optim", "language_model"))
+        # the language-model directory is a Hugging Face checkpoint: ``transformers`` loads it and computes the same logits
+        try:
+            import transformers as tf
+        except ImportError:
+            tf = None
+        if tf is not None:
+            from cornstarch_b200.models import AutoModel
+
+            d = os.path.join(root, "model", "language_model")
+            ours, theirs = AutoModel.from_pretrained(d).eval(), tf.AutoModelForCausalLM.from_pretrained(d).eval()
+            ids = torch.randint(0, 900, (2, 16))
+            with torch.no_grad():
+                assert torch.allclose(ours(input_ids=ids).logits, theirs(input_ids=ids).logits, atol=1e-4)
 
 
 @pytest.mark.parametrize("tp,llm_stages,world", [(1, 2, 3), (2, 1, 4)])
