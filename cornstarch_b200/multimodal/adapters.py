@@ -36,20 +36,33 @@ def _strip(sd: dict, prefix: str) -> dict:
     return OrderedDict((k[len(prefix):], v) for k, v in sd.items() if k.startswith(prefix))
 
 
+def _norm_composite_keys(sd: dict) -> dict:
+    """Keys of a composite checkpoint without the optional leading ``model.``: releases of ``transformers`` differ in where
+    they put it (``model.language_model...`` next to ``language_model.lm_head.weight`` in one and the same file)."""
+    return OrderedDict((k[len("model."):] if k.startswith("model.") else k, v) for k, v in sd.items())
+
+
+def _language_model_part(body: dict) -> dict:
+    """``language_model.*`` (and a top-level ``lm_head.*``) -> the state dict of a causal LM (``model.*`` + ``lm_head.*``)."""
+    llm = OrderedDict()
+    for k, v in body.items():
+        if k.startswith("lm_head."):
+            llm[k] = v
+        elif k.startswith("language_model.lm_head."):
+            llm[k[len("language_model."):]] = v
+        elif k.startswith("language_model.model."):
+            llm[k[len("language_model."):]] = v
+        elif k.startswith("language_model."):
+            llm["model." + k[len("language_model."):]] = v
+    return llm
+
+
 def split_llava_next_state_dict(sd: dict) -> dict[str, dict]:
-    """Keys of ``LlavaNextForConditionalGeneration`` (with or without the ``model.`` level) -> per-module state dicts."""
-    if any(k.startswith("model.vision_tower.") for k in sd):
-        body = _strip(sd, "model.")
-    else:
-        body = dict(sd)
+    """Keys of ``LlavaNextForConditionalGeneration`` (any of the layouts ``transformers`` has written) -> per-module state dicts."""
+    body = _norm_composite_keys(sd)
     vision = _strip(body, "vision_tower.")
     proj = _strip(body, "multi_modal_projector.")
-    llm = OrderedDict(("model." + k, v) for k, v in _strip(body, "language_model.").items() if not k.startswith("lm_head."))
-    if any(k.startswith("language_model.model.") for k in body):  # older layout: language_model.{model.*, lm_head.*}
-        llm = _strip(body, "language_model.")
-    for k in ("lm_head.weight",):
-        if k in sd:
-            llm[k] = sd[k]
+    llm = _language_model_part(body)
     projector = OrderedDict()
     for name, new in (("linear_1", "in_proj"), ("linear_2", "out_proj")):
         for p in ("weight", "bias"):
@@ -60,16 +73,16 @@ def split_llava_next_state_dict(sd: dict) -> dict[str, dict]:
 
 
 def split_qwen2_vl_state_dict(sd: dict) -> dict[str, dict]:
-    body = _strip(sd, "model.") if any(k.startswith("model.visual.") for k in sd) else dict(sd)
+    body = _norm_composite_keys(sd)
     visual = _strip(body, "visual.")
     merger = OrderedDict((k, v) for k, v in visual.items() if k.startswith("merger."))
     vision = OrderedDict((k, v) for k, v in visual.items() if not k.startswith("merger."))
-    if any(k.startswith("language_model.") for k in body):
-        llm = OrderedDict(("model." + k, v) for k, v in _strip(body, "language_model.").items())
-    else:
+    llm = _language_model_part(body)
+    if not any(k.startswith("model.") for k in llm):
+        # oldest layout: the decoder's tensors sit directly under ``model.`` next to ``model.visual.``
         llm = OrderedDict((k, v) for k, v in sd.items() if k.startswith("model.") and not k.startswith("model.visual."))
-    if "lm_head.weight" in sd:
-        llm["lm_head.weight"] = sd["lm_head.weight"]
+        if "lm_head.weight" in sd:
+            llm["lm_head.weight"] = sd["lm_head.weight"]
     projector = OrderedDict(("projection." + k[len("merger."):], v) for k, v in merger.items())
     return {"vision": vision, "projector": projector, "language_model": llm, "extras": {}}
 

@@ -67,3 +67,55 @@ def test_qwen2_vl_split():
         got = model.vision_encoder(hidden_states=x, grid_thw=grid)
     got = got["hidden_states"] if isinstance(got, dict) else got[0]
     assert torch.allclose(got.reshape(want.shape), want, atol=1e-4), (got.reshape(want.shape) - want).abs().max()
+
+
+def test_llava_next_from_a_checkpoint_directory(tmp_path):
+    """``MultimodalModel.from_pretrained_multimodal_model(dir)`` on a directory written by ``transformers``."""
+    from transformers import CLIPVisionConfig, LlamaConfig, LlavaNextConfig, LlavaNextForConditionalGeneration
+
+    from cornstarch_b200.multimodal import MultimodalModel
+
+    torch.manual_seed(0)
+    cfg = LlavaNextConfig(
+        vision_config=CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4, image_size=28,
+                                       patch_size=14).to_dict(),
+        text_config=LlamaConfig(vocab_size=200, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                num_key_value_heads=2).to_dict(),
+        image_token_index=199, image_grid_pinpoints=[[28, 28]])
+    hf = LlavaNextForConditionalGeneration(cfg).eval()
+    hf.save_pretrained(str(tmp_path))
+    model = MultimodalModel.from_pretrained_multimodal_model(str(tmp_path)).eval()
+    assert model.token_ids == {"vision": 199}
+    ids = torch.randint(0, 198, (2, 12))
+    with torch.no_grad():
+        a = hf.lm_head(hf.model.language_model(input_ids=ids).last_hidden_state)
+        b = model.language_model(input_ids=ids).logits
+    assert torch.allclose(a, b, atol=1e-4)
+
+
+def test_qwen2_vl_from_a_checkpoint_directory(tmp_path):
+    from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+
+    from cornstarch_b200.multimodal import MultimodalModel
+
+    torch.manual_seed(0)
+    vc = dict(depth=2, embed_dim=32, hidden_size=48, num_heads=4, mlp_ratio=2, patch_size=14, spatial_merge_size=2, temporal_patch_size=2)
+    tc = dict(vocab_size=200, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              rope_scaling={"type": "mrope", "mrope_section": [2, 2, 2]})
+    try:
+        cfg = Qwen2VLConfig(vision_config=vc, text_config=tc, image_token_id=199)
+    except TypeError:
+        cfg = Qwen2VLConfig(vision_config=vc, image_token_id=199, **tc)
+    hf = Qwen2VLForConditionalGeneration(cfg).eval()
+    hf.save_pretrained(str(tmp_path))
+    model = MultimodalModel.from_pretrained_multimodal_model(str(tmp_path)).eval()
+    assert model.token_ids == {"vision": 199}
+    grid = torch.tensor([[1, 4, 4]])
+    x = torch.randn(16, 3 * 2 * 14 * 14)
+    with torch.no_grad():
+        visual = hf.model.visual if hasattr(hf.model, "visual") else hf.visual
+        want = visual(x, grid_thw=grid)
+        want = want if isinstance(want, torch.Tensor) else (want.pooler_output if getattr(want, "pooler_output", None) is not None else want[0])
+        got = model.vision_encoder(hidden_states=x, grid_thw=grid)
+    got = got["hidden_states"] if isinstance(got, dict) else got[0]
+    assert torch.allclose(got.reshape(want.shape), want, atol=1e-4)
