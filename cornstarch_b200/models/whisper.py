@@ -52,6 +52,7 @@ class WhisperConfig(PretrainedConfig):
 
 
 class Qwen2AudioEncoderConfig(WhisperConfig):
+    composite_key = "audio_config"  # nested under this name in a Qwen2-Audio checkpoint's config.json
     model_type = "qwen2_audio_encoder"
 
 

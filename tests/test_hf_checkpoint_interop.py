@@ -133,3 +133,32 @@ def test_sub_models_load_from_composite_checkpoints(tmp_path):
     px = torch.randn(2, 3, 28, 28)
     with torch.no_grad():
         assert torch.allclose(tower(pixel_values=px).last_hidden_state, two.vision_model(pixel_values=px).last_hidden_state, atol=1e-4)
+
+
+def test_more_sub_models_from_composite_checkpoints(tmp_path):
+    """CLIP's vision tower from a two-tower CLIP checkpoint; the audio tower of a Qwen2-Audio checkpoint."""
+    from transformers import Qwen2AudioConfig, Qwen2AudioForConditionalGeneration
+
+    from cornstarch_b200.models import vision as V
+    from cornstarch_b200.models import whisper as W
+
+    torch.manual_seed(0)
+    common = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=28, patch_size=14)
+    clip = tf.CLIPModel(tf.CLIPConfig(vision_config=common, projection_dim=32,
+                                      text_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+                                                       vocab_size=100))).eval()
+    clip.save_pretrained(str(tmp_path / "clip"))
+    tower = V.CLIPVisionModel.from_pretrained(str(tmp_path / "clip")).eval()
+    px = torch.randn(2, 3, 28, 28)
+    with torch.no_grad():
+        assert torch.allclose(tower(pixel_values=px).last_hidden_state, clip.vision_model(pixel_values=px).last_hidden_state, atol=1e-4)
+
+    ac = dict(num_mel_bins=16, d_model=64, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=128, max_source_positions=50)
+    tc = dict(vocab_size=200, hidden_size=48, intermediate_size=96, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2,
+              model_type="qwen2")
+    qa = Qwen2AudioForConditionalGeneration(Qwen2AudioConfig(audio_config=ac, text_config=tc)).eval()
+    qa.save_pretrained(str(tmp_path / "qwen2_audio"))
+    enc = W.Qwen2AudioEncoder.from_pretrained(str(tmp_path / "qwen2_audio")).eval()
+    x = torch.randn(2, 16, 100)
+    with torch.no_grad():
+        assert torch.allclose(enc(input_features=x).last_hidden_state, qa.audio_tower(x).last_hidden_state, atol=1e-4)
