@@ -103,7 +103,7 @@ class PretrainedConfig:
             if reg is not None:
                 return reg[0].from_dict(d)
         sub = getattr(cls, "composite_key", None)
-        if sub and isinstance(d.get(sub), dict) and d.get("model_type") != cls.model_type:
+        if sub and isinstance(d.get(sub), dict):
             d = d[sub]  # the config of a composite model (CLIP / SigLIP with both towers, a vision-language model)
         return cls.from_dict(d)
 

@@ -29,6 +29,7 @@ from .base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, r
 
 class Phi4MultimodalAudioConfig(PretrainedConfig):
     model_type = "phi4_multimodal_audio"
+    composite_key = "audio_config"
 
     def __init__(self, hidden_size=1024, intermediate_size=1536, num_blocks=24, num_attention_heads=16, activation="swish",
                  chunk_size=-1, left_chunk=18, conv_activation="swish", conv_glu_type="swish", depthwise_multiplier=1,

@@ -487,6 +487,7 @@ class PixtralVisionModel(_VisionBase):
 # ------------------------------------------------------------------------------------------------ Qwen2-VL vision
 class Qwen2VLVisionConfig(PretrainedConfig):
     model_type = "qwen2_vl"
+    composite_key = "vision_config"
 
     def __init__(self, depth=32, embed_dim=1280, hidden_size=3584, hidden_act="quick_gelu", mlp_ratio=4, num_heads=16,
                  in_channels=3, patch_size=14, spatial_merge_size=2, temporal_patch_size=2, **kw):
