@@ -199,6 +199,33 @@ class PreTrainedModel(nn.Module):
             if m is not self and isinstance(m, PreTrainedModel):
                 m.gradient_checkpointing = False
 
+    def resize_token_embeddings(self, new_num_tokens: int):
+        """Grow (or shrink) the input embedding table and, when present, the output head to ``new_num_tokens`` rows; new
+        rows start at the mean of the existing ones.  Tied tables stay tied.  Returns the input embedding module."""
+        emb = self.get_input_embeddings()
+        head = self.get_output_embeddings() if hasattr(self, "get_output_embeddings") else None
+        tied = head is not None and head.weight is emb.weight
+
+        def grown(w: torch.Tensor) -> nn.Parameter:
+            new = w.new_empty(new_num_tokens, w.shape[1])
+            n = min(w.shape[0], new_num_tokens)
+            new[:n] = w.data[:n]
+            if new_num_tokens > n:
+                new[n:] = w.data.float().mean(0, keepdim=True).to(w.dtype)
+            return nn.Parameter(new, requires_grad=w.requires_grad)
+
+        if emb.weight.shape[0] != new_num_tokens:
+            emb.weight = grown(emb.weight)
+            if hasattr(emb, "num_embeddings"):
+                emb.num_embeddings = new_num_tokens
+            if head is not None:
+                head.weight = emb.weight if tied else grown(head.weight)
+                if hasattr(head, "out_features"):
+                    head.out_features = new_num_tokens
+            if hasattr(self.config, "vocab_size"):
+                self.config.vocab_size = new_num_tokens
+        return emb
+
     # ---- (de)serialisation ---------------------------------------------------------------------
     def save_pretrained(self, path: str, max_shard_size: int | None = None, safe_serialization: bool = True):
         from ..checkpoint.io import save_state_dict_sharded

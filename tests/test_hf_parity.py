@@ -162,3 +162,20 @@ def test_qwen2_audio_encoder_matches_hf():
     with torch.no_grad():
         a, b = hf(x).last_hidden_state, mine(input_features=x).last_hidden_state
     assert a.shape == b.shape and torch.allclose(b, a, atol=1e-4), (a.shape, b.shape, (a - b).abs().max())
+
+
+def test_resize_token_embeddings_keeps_old_rows_and_ties():
+    from cornstarch_b200.models import llama as L
+
+    torch.manual_seed(0)
+    kw = dict(vocab_size=100, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=4, num_key_value_heads=2)
+    m = L.DecoderForCausalLM(L.LlamaConfig(**kw)).eval()
+    ids = torch.randint(0, 100, (1, 8))
+    before = m(input_ids=ids).logits
+    m.resize_token_embeddings(120)
+    after = m(input_ids=ids).logits
+    assert after.shape[-1] == 120 and m.config.vocab_size == 120 and torch.allclose(before, after[..., :100], atol=1e-6)
+    assert torch.isfinite(m(input_ids=torch.tensor([[119, 3]]), labels=torch.tensor([[119, 3]])).loss)
+    tied = L.DecoderForCausalLM(L.GemmaConfig(**kw, head_dim=8))
+    tied.resize_token_embeddings(110)
+    assert tied.lm_head.weight is tied.model.embed_tokens.weight and tied.lm_head.weight.shape == (110, 32)

@@ -48,3 +48,33 @@ def test_image_and_audio_processors_from_transformers():
     assert tuple(batch["pixel_values"].shape) == (2, 3, 28, 28) and tuple(batch["input_features"].shape) == (2, 16, 100)
     out = model(input_ids=ids, pixel_values=batch["pixel_values"].float(), input_features=batch["input_features"].float(), labels=ids)
     assert torch.isfinite(out.loss)
+
+
+def test_hugging_face_fast_tokenizer():
+    """A ``PreTrainedTokenizerFast`` (word-level, built in memory): the modality token becomes an added special token and its
+    id goes to the model.  The id may lie beyond the embedding table: placeholder positions are filled with encoder features
+    and never looked up (nor used as labels), as in the reference."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+
+    from cornstarch_b200 import zoo
+    from cornstarch_b200.multimodal import MultimodalProcessor
+
+    words = ["<pad>", "<unk>", "look", "listen"] + [f"w{i}" for i in range(996)]  # exactly the model's 1000 embeddings
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    hf_tok = tf.PreTrainedTokenizerFast(tokenizer_object=tok, pad_token="<pad>", unk_token="<unk>")
+    model = zoo.build_model("tiny", dtype=torch.float32)
+
+    class Images:
+        def __call__(self, images=None, return_tensors="pt"):
+            return {"pixel_values": torch.stack(images)}
+
+    proc = MultimodalProcessor({"vision": Images()}, hf_tok, model, predefined_tokens={"vision": "<image>"},
+                               num_feature_calculation_funcs={"vision": lambda i, o: [16] * len(o["pixel_values"])})
+    assert model.token_ids == {"vision": 1000} and len(hf_tok) == 1001
+    assert model.language_model.get_input_embeddings().weight.shape[0] == 1000
+    batch = proc(encoder_inputs={"vision": {"images": [torch.randn(3, 56, 56)] * 2}},
+                 llm_inputs={"text": ["<image> look w1 w2", "listen <image>"], "padding": True})
+    assert (batch["input_ids"] == 1000).sum(dim=1).tolist() == [16, 16]
+    out = model(input_ids=batch["input_ids"], pixel_values=batch["pixel_values"], labels=batch["input_ids"])
+    assert torch.isfinite(out.loss)
