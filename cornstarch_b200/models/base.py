@@ -52,7 +52,14 @@ def _strip_checkpoint_prefix(sd: dict, wanted: set) -> dict:
             best, best_hits = p, hits
     if not best:
         return sd
-    return {k[len(best):]: v for k, v in sd.items() if k.startswith(best)}
+    out = {k[len(best):]: v for k, v in sd.items() if k.startswith(best)}
+    for k in wanted - set(out):
+        # a checkpoint may keep a few tensors elsewhere (``language_model.lm_head.weight`` next to ``model.language_model.*``)
+        for p in _CHECKPOINT_PREFIXES:
+            if (p + k) in sd:
+                out[k] = sd[p + k]
+                break
+    return out
 
 
 class PretrainedConfig:

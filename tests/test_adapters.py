@@ -119,3 +119,26 @@ def test_qwen2_vl_from_a_checkpoint_directory(tmp_path):
         got = model.vision_encoder(hidden_states=x, grid_thw=grid)
     got = got["hidden_states"] if isinstance(got, dict) else got[0]
     assert torch.allclose(got.reshape(want.shape), want, atol=1e-4)
+
+
+def test_language_model_alone_from_a_llava_checkpoint(tmp_path):
+    """The decoder of a vision-language checkpoint loads on its own: nested ``text_config``, the ``model.language_model.``
+    prefix, and the head that the same file keeps under ``language_model.lm_head``."""
+    from transformers import CLIPVisionConfig, LlamaConfig, LlavaNextConfig, LlavaNextForConditionalGeneration
+
+    from cornstarch_b200.models.llama import DecoderForCausalLM
+
+    torch.manual_seed(0)
+    cfg = LlavaNextConfig(
+        vision_config=CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, image_size=28,
+                                       patch_size=14).to_dict(),
+        text_config=LlamaConfig(vocab_size=200, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                num_key_value_heads=2).to_dict(),
+        image_token_index=199, image_grid_pinpoints=[[28, 28]])
+    hf = LlavaNextForConditionalGeneration(cfg).eval()
+    hf.save_pretrained(str(tmp_path))
+    llm = DecoderForCausalLM.from_pretrained(str(tmp_path)).eval()
+    ids = torch.randint(0, 198, (2, 12))
+    with torch.no_grad():
+        want = hf.lm_head(hf.model.language_model(input_ids=ids).last_hidden_state)
+        assert torch.allclose(llm(input_ids=ids).logits, want, atol=1e-4)
