@@ -22,6 +22,7 @@ import torch.nn.functional as F
 
 from .. import nn as cnn
 from ..ops import elementwise as E
+from ..parallel import comm
 from ..ops.linear import multi_linear
 from ..utils.recompute import checkpoint_layer
 from .base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, register_model
@@ -91,12 +92,19 @@ class _RelativeAttentionBias(nn.Module):
         self.max_distance, self.symmetric = config.bias_max_distance, config.bias_symmetric
         self.num_buckets = self.max_distance * (1 if self.symmetric else 2)
         self.bias_values = nn.Embedding(self.num_buckets, config.num_attention_heads)
+        self.tp_group = None  # set under tensor parallelism: this rank then returns the bias of its own heads only
 
     def forward(self, T: int, device):
         pos = torch.arange(T, device=device)
         rel = (pos[None, :] - pos[:, None]).clamp(-self.max_distance, self.max_distance - 1)
         idx = rel.abs() if self.symmetric else rel + self.num_buckets // 2
-        return self.bias_values(idx).permute(2, 0, 1).unsqueeze(0)  # [1, heads, T, T]
+        w = self.bias_values.weight
+        if self.tp_group is not None and comm._world(self.tp_group) > 1:
+            # the table stays replicated; each rank reads the columns of its heads, so the gradient is summed over ranks
+            tp, r = comm._world(self.tp_group), torch.distributed.get_rank(self.tp_group)
+            per = w.shape[1] // tp
+            w = comm.reduce_backward(w, self.tp_group)[:, r * per : (r + 1) * per]
+        return F.embedding(idx, w).permute(2, 0, 1).unsqueeze(0)  # [1, local heads, T, T]
 
 
 class _AudioMLP(nn.Module):
@@ -209,12 +217,19 @@ class Phi4MultimodalAudioModel(PreTrainedModel):
     def module_names(cls, config):
         return ["encoder_embedding", "embed", "relative_attention_bias_layer"] + [f"encoders.{i}" for i in range(config.num_blocks)]
 
-    def forward(self, audio_input_features=None, hidden_states=None, **kw):
+    def set_parallel_context(self, pc):
+        self.pc = pc
+        if not is_released(self.relative_attention_bias_layer):
+            self.relative_attention_bias_layer.tp_group = pc.tp_group if pc is not None else None
+
+    def forward(self, audio_input_features=None, hidden_states=None, attention_bias=None, **kw):
+        """A later pipeline stage gets ``hidden_states`` and the ``attention_bias`` the first stage computed (the
+        reference hands its ``attention_mask`` on the same way, cornstarch/shardformer/modeling/phi4_multimodal.py:148-189)."""
         if hidden_states is None:
             x = self.embed(self.encoder_embedding(audio_input_features))
         else:
             x = hidden_states
-        bias = self.relative_attention_bias_layer(x.shape[1], x.device)
+        bias = attention_bias if attention_bias is not None else self.relative_attention_bias_layer(x.shape[1], x.device)
         for layer in self.encoders:
             if is_released(layer):
                 continue
@@ -223,7 +238,7 @@ class Phi4MultimodalAudioModel(PreTrainedModel):
             else:
                 x = layer(x, bias)
         if is_released(self.encoders[-1]):
-            return ModelOutput(hidden_states=x)
+            return ModelOutput(hidden_states=x, attention_bias=bias)
         return ModelOutput(last_hidden_state=x)
 
 

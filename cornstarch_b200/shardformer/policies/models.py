@@ -344,10 +344,10 @@ class Phi4MultimodalAudioModelPolicy(ModelPolicy):
     tp_rules = [
         TPRule(r"encoders\.\d+\.self_attn\.(q_proj|k_proj|v_proj)", "col"),
         TPRule(r"encoders\.\d+\.self_attn\.o_proj", "row"),
+        TPRule(r"encoders\.\d+\.feed_forward_(in|out)\.gate_up_proj", "col"),
+        TPRule(r"encoders\.\d+\.feed_forward_(in|out)\.down_proj", "row"),
     ]
 
-    def config_sanity_check(self):
-        super().config_sanity_check()
-        sc = self.shard_config
-        if sc is not None and sc.tensor_parallel_size > 1:
-            raise ValueError("the relative attention bias is indexed by global head: tensor parallelism is not supported for this encoder")
+    def split_sizes(self, path, module):
+        I = self.model.config.intermediate_size
+        return [I, I] if path.endswith("gate_up_proj") else None

@@ -11,7 +11,7 @@ from cornstarch_b200.pipeline_template import PipelineTemplate
 from tests.test_policy_tp_numerics import _build, _run
 
 FAMILIES = ["llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "phi3", "mixtral", "qwen3_moe", "llama4", "gpt2",
-            "opt", "bert", "siglip", "clip", "vit", "dinov2", "internvit", "evaclip", "pixtral", "whisper", "qwen2_audio"]
+            "opt", "bert", "siglip", "clip", "vit", "dinov2", "internvit", "evaclip", "pixtral", "whisper", "qwen2_audio", "phi4_audio", "qwen2_vl"]
 
 
 def _build_any(family):
@@ -31,6 +31,10 @@ def _input(kind):
         return torch.randn(2, 3, 28, 28, generator=g)
     if kind == "image56":
         return torch.randn(2, 3, 56, 56, generator=g)
+    if kind == "phi4":
+        return torch.randn(2, 64, 16, generator=g)
+    if kind == "qwen2vl":
+        return torch.randn(32, 3 * 2 * 14 * 14, generator=g)
     return torch.randn(2, 8, 20, generator=g)
 
 
@@ -51,15 +55,17 @@ def test_two_stage_split_matches_whole_model(family):
         stages.append(m)
     assert sum(p.numel() for p in stages[0].parameters()) < sum(p.numel() for p in whole.parameters())
 
-    key = {"text": "input_ids", "image": "pixel_values", "image56": "pixel_values", "audio": "input_features"}[kind]
-    first = stages[0](**{key: x})
+    key = {"text": "input_ids", "image": "pixel_values", "image56": "pixel_values", "audio": "input_features",
+           "phi4": "audio_input_features", "qwen2vl": "hidden_states"}[kind]
+    extra = {"grid_thw": torch.tensor([[1, 4, 4], [1, 4, 4]])} if kind == "qwen2vl" else {}
+    first = stages[0](**{key: x}, **extra)
     passed = {k: v for k, v in first.items() if v is not None} if isinstance(first, dict) else {"hidden_states": first}
     assert "hidden_states" in passed, list(passed)
     if kind == "text":
         out = stages[1](labels=x, **passed)
         got = out.loss
     else:
-        out = stages[1](**passed)
+        out = stages[1](**passed, **extra)
         h = out["last_hidden_state"] if isinstance(out, dict) else out[0]
         got = h.float().square().mean()
     assert abs(got.item() - ref.item()) < 1e-4 * max(1.0, abs(ref.item())), (family, got.item(), ref.item())

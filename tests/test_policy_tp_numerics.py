@@ -68,6 +68,15 @@ def _build(family):
     if family == "pixtral":
         return X.PixtralVisionModel(X.PixtralVisionConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2,
                                                           num_attention_heads=4, image_size=56, patch_size=14, head_dim=16)), "image56"
+    if family == "phi4_audio":
+        from cornstarch_b200.models.phi4_audio import Phi4MultimodalAudioConfig, Phi4MultimodalAudioModel
+
+        return Phi4MultimodalAudioModel(Phi4MultimodalAudioConfig(
+            hidden_size=64, intermediate_size=96, num_blocks=2, num_attention_heads=4, input_size=16, nemo_conv_channels=32,
+            ext_pw_out_channel=64, kernel_size=3, time_reduction=8, depthwise_separable_out_channel=64)), "phi4"
+    if family == "qwen2_vl":
+        return X.Qwen2VisionTransformerPretrainedModel(X.Qwen2VLVisionConfig(
+            depth=2, embed_dim=64, hidden_size=48, num_heads=4, mlp_ratio=2, patch_size=14, spatial_merge_size=2, temporal_patch_size=2)), "qwen2vl"
     if family == "qwen2_audio":
         return W.Qwen2AudioEncoder(W.Qwen2AudioEncoderConfig(num_mel_bins=8, d_model=64, encoder_layers=2, encoder_attention_heads=4,
                                                              encoder_ffn_dim=128, max_source_positions=10)), "audio"
@@ -78,7 +87,11 @@ def _run(model, kind, x):
     if kind == "text":
         out = model(input_ids=x, labels=x)
         return out.loss
-    if kind in ("image", "image56"):
+    if kind == "phi4":
+        out = model(audio_input_features=x)
+    elif kind == "qwen2vl":
+        out = model(hidden_states=x, grid_thw=torch.tensor([[1, 4, 4], [1, 4, 4]]))
+    elif kind in ("image", "image56"):
         out = model(pixel_values=x)
     else:
         out = model(input_features=x)
@@ -102,6 +115,10 @@ def _worker(rank, world, family):
         x = torch.randn(2, 3, 28, 28, generator=g, requires_grad=True)
     elif kind == "image56":
         x = torch.randn(2, 3, 56, 56, generator=g, requires_grad=True)
+    elif kind == "phi4":
+        x = torch.randn(2, 64, 16, generator=g, requires_grad=True)
+    elif kind == "qwen2vl":
+        x = torch.randn(32, 3 * 2 * 14 * 14, generator=g, requires_grad=True)
     else:
         x = torch.randn(2, 8, 20, generator=g, requires_grad=True)
     xr = x.detach().clone().requires_grad_(x.requires_grad) if x.is_floating_point() else x
@@ -132,8 +149,8 @@ def _worker(rank, world, family):
 GROUPS = {
     "dense_decoders": ["llama", "mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "phi3"],
     "moe_and_legacy": ["mixtral", "qwen3_moe", "llama4", "gpt2", "opt", "bert"],
-    "vision": ["siglip", "clip", "vit", "dinov2", "internvit", "evaclip", "pixtral"],
-    "audio": ["whisper", "qwen2_audio"],
+    "vision": ["siglip", "clip", "vit", "dinov2", "internvit", "evaclip", "pixtral", "qwen2_vl"],
+    "audio": ["whisper", "qwen2_audio", "phi4_audio"],
 }
 
 
