@@ -66,9 +66,14 @@ class EncodersColocatedMultimodalParallelModule(MultimodalParallelModule):
                 inputs = kwargs
                 if name not in kwargs:
                     continue
-                res = enc.module(hidden_states=kwargs[name])
+                params = enc.forward_arg_names()
+                side = {k: v for k, v in kwargs.items() if k in params[1:] and k != "hidden_states" and v is not None}
+                side.update({k[len(name) + 1 :]: v for k, v in kwargs.items() if k.startswith(name + ".")})
+                res = enc.module(hidden_states=kwargs[name], **side)
             if not last:
                 out[name] = res["hidden_states"]
+                # what else the stage hands on (a relative-position bias, say) travels under "<name>.<key>"
+                out.update({f"{name}.{k}": v for k, v in res.items() if k != "hidden_states" and isinstance(v, torch.Tensor)})
                 continue
             res = enc.postprocess_module_callback(inputs=inputs, output=res)
             proj = enc.projector(_first_tensor(res), return_dict=True)

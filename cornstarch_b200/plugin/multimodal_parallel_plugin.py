@@ -86,9 +86,13 @@ class MultimodalParallelModule(nn.Module):
             inputs = kwargs
             if isinstance(hidden_states, (list, tuple)):
                 hidden_states = hidden_states[0]
-            out = enc.module(hidden_states=hidden_states)
+            # besides the hidden states a later stage gets what the stage before it handed on (a relative-position
+            # bias, say) and the per-sample arguments of the micro-batch (an image grid), never the raw main input
+            params = enc.forward_arg_names()
+            side = {k: v for k, v in kwargs.items() if k in params[1:] and k != "hidden_states" and v is not None}
+            out = enc.module(hidden_states=hidden_states, **side)
         if not last:
-            return {"hidden_states": out["hidden_states"]}
+            return {k: v for k, v in out.items() if isinstance(v, torch.Tensor)}
         out = enc.postprocess_module_callback(inputs=inputs, output=out)
         proj = enc.projector(_first_tensor(out), return_dict=True)
         proj = enc.postprocess_projector_callback(inputs=inputs, output=proj)

@@ -196,3 +196,66 @@ def _valm_worker(rank, world):
 
 def test_two_encoder_branches_match_single_process():
     run_distributed(_valm_worker, 3)
+
+
+def _phi4_audio_lm(seed=0):
+    """Phi-4 audio encoder (its attention bias is computed once, on the encoder's first stage) + a tiny Llama."""
+    from cornstarch_b200.models.llama import DecoderConfig, DecoderForCausalLM
+    from cornstarch_b200.models.phi4_audio import Phi4MultimodalAudioConfig, Phi4MultimodalAudioModel
+    from cornstarch_b200.multimodal.modeling import ModalEncoderModule, MultimodalModel
+    from cornstarch_b200.multimodal.modeling import MultimodalProjector, MultimodalProjectorConfig
+
+    torch.manual_seed(seed)
+    acfg = Phi4MultimodalAudioConfig(hidden_size=64, intermediate_size=96, num_blocks=2, num_attention_heads=4, input_size=16,
+                                     nemo_conv_channels=32, ext_pw_out_channel=64, kernel_size=3, time_reduction=8,
+                                     depthwise_separable_out_channel=64)
+    lcfg = DecoderConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, max_position_embeddings=128)
+    pcfg = MultimodalProjectorConfig(encoder_config=acfg, text_config=lcfg, projection_type="linear")
+    model = MultimodalModel(encoders={"audio": ModalEncoderModule(Phi4MultimodalAudioModel(acfg), MultimodalProjector(pcfg))},
+                            language_model=DecoderForCausalLM(lcfg))
+    model.set_modality_token_ids({"audio": 127})
+    model.train()
+    g = torch.Generator().manual_seed(3)
+    feats = torch.randn(4, 64, 16, generator=g)  # 64 frames / time_reduction 8 = 8 audio tokens per sample
+    ids = torch.randint(0, 127, (4, 32), generator=g)
+    ids[:, 2:10] = 127
+    return model, {"audio_input_features": feats, "input_ids": ids, "labels": ids.clone()}
+
+
+def _two_stage_encoder_worker(rank, world, tp):
+    from cornstarch_b200.booster import Booster
+    from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
+    from cornstarch_b200.pipeline_template import PipelineTemplate
+    from cornstarch_b200.plugin.modal_parallel_plugin import ModalParallelPlugin
+    from cornstarch_b200.plugin.multimodal_parallel_plugin import MultimodalParallelPlugin
+
+    n_micro = 2
+    ref, batch = _phi4_audio_lm()
+    ref_loss = 0.0
+    for i in range(n_micro):
+        loss = ref(**{k: v[2 * i : 2 * i + 2] for k, v in batch.items()}).loss / n_micro
+        loss.backward()
+        ref_loss += loss.item()
+    model, _ = _phi4_audio_lm()
+    plugin = MultimodalParallelPlugin(
+        encoder_plugins={"audio": ModalParallelPlugin(tp_size=tp, pipeline_template=PipelineTemplate.even_split(model.audio_encoder, 2))},
+        language_model_plugin=ModalParallelPlugin(tp_size=tp, pipeline_template=PipelineTemplate.even_split(model.language_model, 1)),
+        num_microbatches=n_micro, precision=None, device=torch.device("cpu"))
+    booster = Booster(plugin=plugin)
+    opt = FusedAdamW(split_decay_groups(model, 0.0), lr=1e-2)
+    pmodel, popt, criterion, *_ = booster.boost(model, opt, criterion=lambda out, b: out.loss)
+    out = booster.execute_pipeline(iter([batch]), pmodel, criterion, popt, return_loss=True)
+    sm = plugin.stage_manager
+    if sm.is_last_stage(check_only_in_modal=False):
+        assert abs(out["loss"].item() - ref_loss) < 1e-4, (out["loss"].item(), ref_loss)
+    if pmodel.my_modal_name == "audio_encoder" and sm.is_first_stage(check_only_in_modal=True):
+        # the bias table sits on the first encoder stage; its gradient comes back through the second stage's attention
+        got = pmodel.module.audio_encoder.module.relative_attention_bias_layer.bias_values.weight.grad
+        want = ref.audio_encoder.module.relative_attention_bias_layer.bias_values.weight.grad
+        assert got is not None and torch.allclose(got, want, atol=1e-5, rtol=1e-3), (got - want).abs().max()
+
+
+@pytest.mark.parametrize("tp,world", [(1, 3), (2, 6)])
+def test_two_stage_encoder_hands_on_its_attention_bias(tp, world):
+    run_distributed(_two_stage_encoder_worker, world, tp)
