@@ -10,6 +10,12 @@ Linear layers, LayerNorms and the GLU run on this package's kernels.  The attent
 bias to the scores, which the flash-attention kernels of this package do not take, so it goes through PyTorch's
 scaled-dot-product attention; the audio sequences are short (T = frames / time_reduction), and the 1-D / 2-D
 convolutions use cuDNN through PyTorch like the other front-ends.
+
+Parallel forms: tensor parallelism splits the heads and both feed-forwards (every rank reads its heads' columns of the
+replicated bias table); under context parallelism ("ring_attn") the tokens are split in contiguous chunks after the
+sub-sampling front-end, keys / values are gathered, each rank keeps the bias rows of its own queries and the causal
+depth-wise convolutions fetch their ``kernel_size - 1`` left neighbours from the previous rank; a later pipeline stage
+receives the bias together with the hidden states.
 """
 
 from __future__ import annotations
@@ -94,9 +100,11 @@ class _RelativeAttentionBias(nn.Module):
         self.bias_values = nn.Embedding(self.num_buckets, config.num_attention_heads)
         self.tp_group = None  # set under tensor parallelism: this rank then returns the bias of its own heads only
 
-    def forward(self, T: int, device):
+    def forward(self, T: int, device, rows: tuple[int, int] | None = None):
+        """``rows = (start, end)``: only the bias of those query positions (a context-parallel rank's tokens)."""
         pos = torch.arange(T, device=device)
-        rel = (pos[None, :] - pos[:, None]).clamp(-self.max_distance, self.max_distance - 1)
+        q_pos = pos if rows is None else pos[rows[0] : rows[1]]
+        rel = (pos[None, :] - q_pos[:, None]).clamp(-self.max_distance, self.max_distance - 1)
         idx = rel.abs() if self.symmetric else rel + self.num_buckets // 2
         w = self.bias_values.weight
         if self.tp_group is not None and comm._world(self.tp_group) > 1:
@@ -104,7 +112,7 @@ class _RelativeAttentionBias(nn.Module):
             tp, r = comm._world(self.tp_group), torch.distributed.get_rank(self.tp_group)
             per = w.shape[1] // tp
             w = comm.reduce_backward(w, self.tp_group)[:, r * per : (r + 1) * per]
-        return F.embedding(idx, w).permute(2, 0, 1).unsqueeze(0)  # [1, local heads, T, T]
+        return F.embedding(idx, w).permute(2, 0, 1).unsqueeze(0)  # [1, local heads, T or rows, T]
 
 
 class _AudioMLP(nn.Module):
@@ -120,12 +128,18 @@ class _AudioMLP(nn.Module):
         return self.down_proj(E.glu(torch.cat([gate, up], dim=-1), self.act))
 
 
+def _cp_sizes(T: int, world: int) -> list[int]:
+    """Tokens per rank of ``torch.tensor_split(T tokens, world)``."""
+    return [T // world + (1 if r < T % world else 0) for r in range(world)]
+
+
 class _AudioAttention(nn.Module):
     def __init__(self, config):
         super().__init__()
         H = config.hidden_size
         self.num_heads, self.head_dim = config.num_attention_heads, H // config.num_attention_heads
         self.q_proj, self.k_proj, self.v_proj, self.o_proj = cnn.Linear(H, H), cnn.Linear(H, H), cnn.Linear(H, H), cnn.Linear(H, H)
+        self.cp_group = None  # context parallelism: x holds this rank's tokens, the bias its rows against all keys
 
     def forward(self, x, bias):
         B, T, _ = x.shape
@@ -133,6 +147,10 @@ class _AudioAttention(nn.Module):
         qkv = multi_linear(self.q_proj.input_hook(x), [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight],
                            [self.q_proj.bias, self.k_proj.bias, self.v_proj.bias])
         q, k, v = (qkv[..., i * W : (i + 1) * W].view(B, T, self.num_heads, self.head_dim).transpose(1, 2) for i in range(3))
+        if self.cp_group is not None and comm._world(self.cp_group) > 1:
+            kv = comm.gather_forward_reduce_scatter_backward(torch.stack([k, v]), 3, self.cp_group,
+                                                             _cp_sizes(bias.shape[-1], comm._world(self.cp_group)))
+            k, v = kv[0], kv[1]
         o = F.scaled_dot_product_attention(q, k, v, attn_mask=bias.to(q.dtype))
         return self.o_proj(o.transpose(1, 2).reshape(B, T, W))
 
@@ -174,12 +192,22 @@ class _ConvModule(nn.Module):
         self.dw_sep_conv_1d = _DepthWiseSeparableConv1d(config, padding=config.kernel_size - 1)
         self.ext_pw_conv_1d = nn.Conv1d(config.hidden_size, config.ext_pw_out_channel, 1)
         self.act = _ACT[config.conv_activation]
+        self.cp_group = None
 
     def forward(self, x):
         h = self.glu(self.layer_norm(x)).permute(0, 2, 1)
-        h = self.dw_sep_conv_1d(h.to(self.dw_sep_conv_1d.dw_conv.weight.dtype))
-        if self.kernel_size > 1:
-            h = h[:, :, : -(self.kernel_size - 1)]  # causal: drop the look-ahead the symmetric padding added
+        conv = self.dw_sep_conv_1d
+        h = h.to(conv.dw_conv.weight.dtype)
+        if self.cp_group is not None and comm._world(self.cp_group) > 1 and self.kernel_size > 1:
+            # the causal convolution looks kernel_size - 1 tokens back: they come from the previous rank, and the
+            # depth-wise convolution then runs without padding
+            h = comm.halo_from_previous(h, 2, self.kernel_size - 1, self.cp_group)
+            dw = conv.dw_conv
+            h = conv.pw_conv(F.conv1d(h, dw.weight, dw.bias, 1, 0, 1, dw.groups))
+        else:
+            h = conv(h)
+            if self.kernel_size > 1:
+                h = h[:, :, : -(self.kernel_size - 1)]  # causal: drop the look-ahead the symmetric padding added
         h = E.activation(h.permute(0, 2, 1).contiguous(), self.act)
         return cnn.linear(h, self.ext_pw_conv_1d.weight.squeeze(-1), self.ext_pw_conv_1d.bias)
 
@@ -219,6 +247,11 @@ class Phi4MultimodalAudioModel(PreTrainedModel):
 
     def set_parallel_context(self, pc):
         self.pc = pc
+        cp = pc.sp_group if pc is not None and pc.sp_mode == "ring_attn" and pc.sp_size > 1 else None
+        self._cp_group = cp
+        for layer in self.encoders:
+            if not is_released(layer):
+                layer.self_attn.cp_group = layer.conv.cp_group = cp
         if not is_released(self.relative_attention_bias_layer):
             self.relative_attention_bias_layer.tp_group = pc.tp_group if pc is not None else None
 
@@ -229,7 +262,17 @@ class Phi4MultimodalAudioModel(PreTrainedModel):
             x = self.embed(self.encoder_embedding(audio_input_features))
         else:
             x = hidden_states
-        bias = attention_bias if attention_bias is not None else self.relative_attention_bias_layer(x.shape[1], x.device)
+        bias = attention_bias
+        if bias is None:
+            cp, T = getattr(self, "_cp_group", None), x.shape[1]
+            if cp is None:
+                bias = self.relative_attention_bias_layer(T, x.device)
+            else:
+                # context parallelism: contiguous token chunks in rank order (the causal convolutions need their left
+                # neighbours), every rank keeps the bias rows of its own tokens
+                sizes, r = _cp_sizes(T, comm._world(cp)), torch.distributed.get_rank(cp)
+                x = comm.split_forward_gather_backward(x, 1, cp)
+                bias = self.relative_attention_bias_layer(T, x.device, rows=(sum(sizes[:r]), sum(sizes[: r + 1])))
         for layer in self.encoders:
             if is_released(layer):
                 continue

@@ -224,3 +224,56 @@ class _GatherFwdReduceScatterBwd(torch.autograd.Function):
 
 def gather_forward_reduce_scatter_backward(x, dim: int, group, sizes: list[int] | None = None):
     return x if _world(group) == 1 else _GatherFwdReduceScatterBwd.apply(x, dim, group, sizes)
+
+
+def _shift(send: torch.Tensor | None, recv: torch.Tensor | None, group, to_next: bool) -> None:
+    """One neighbour exchange along the group's rank order: ``send`` goes to the next (previous) rank, ``recv`` is filled
+    by the previous (next) one.  Ranks at the ends pass ``None`` for the side they do not have."""
+    rank = dist.get_rank(group)
+    ops = []
+    if send is not None:
+        ops.append(dist.P2POp(dist.isend, send, dist.get_global_rank(group, rank + (1 if to_next else -1)), group))
+    if recv is not None:
+        ops.append(dist.P2POp(dist.irecv, recv, dist.get_global_rank(group, rank - (1 if to_next else -1)), group))
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+
+
+class _HaloFromPrevious(torch.autograd.Function):
+    """Prepend the last ``width`` entries (along ``dim``) of the previous rank's tensor; rank 0 prepends zeros.
+    Backward returns the halo's gradient to the rank it came from, which adds it to its tail."""
+
+    @staticmethod
+    def forward(ctx, x, dim, width, group):
+        ws, rank = dist.get_world_size(group), dist.get_rank(group)
+        assert x.shape[dim] >= width, "a sequence shard is shorter than the halo of the convolution"
+        ctx.dim, ctx.width, ctx.group = dim, width, group
+        shape = list(x.shape)
+        shape[dim] = width
+        halo = x.new_zeros(shape)
+        tail = x.narrow(dim, x.shape[dim] - width, width).contiguous() if rank < ws - 1 else None
+        _shift(tail, halo if rank > 0 else None, group, to_next=True)
+        return torch.cat([halo, x], dim=dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        dim, width, group = ctx.dim, ctx.width, ctx.group
+        ws, rank = dist.get_world_size(group), dist.get_rank(group)
+        gx = g.narrow(dim, width, g.shape[dim] - width).clone()
+        g_halo = g.narrow(dim, 0, width).contiguous() if rank > 0 else None
+        from_next = torch.empty_like(g.narrow(dim, 0, width)).contiguous() if rank < ws - 1 else None
+        _shift(g_halo, from_next, group, to_next=False)
+        if from_next is not None:
+            gx.narrow(dim, gx.shape[dim] - width, width).add_(from_next)
+        return gx, None, None, None
+
+
+def halo_from_previous(x, dim: int, width: int, group):
+    """``[previous rank's last width entries | x]`` along ``dim``: the left context of a causal convolution over a
+    sequence that is split in contiguous chunks in rank order."""
+    if _world(group) == 1 or width == 0:
+        shape = list(x.shape)
+        shape[dim] = width
+        return torch.cat([x.new_zeros(shape), x], dim=dim)
+    return _HaloFromPrevious.apply(x, dim, width, group)

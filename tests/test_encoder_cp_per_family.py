@@ -7,11 +7,14 @@ import torch.distributed as dist
 
 from tests.dist_utils import run_distributed
 
-FAMILIES = ["siglip", "clip", "vit", "dinov2", "evaclip", "pixtral", "whisper", "qwen2_audio"]
+FAMILIES = ["siglip", "clip", "vit", "dinov2", "evaclip", "pixtral", "whisper", "qwen2_audio", "phi4_audio"]
 
 
 def _features(model, kind, x):
-    out = model(pixel_values=x) if kind.startswith("image") else model(input_features=x)
+    if kind == "phi4":
+        out = model(audio_input_features=x)
+    else:
+        out = model(pixel_values=x) if kind.startswith("image") else model(input_features=x)
     return out["last_hidden_state"] if isinstance(out, dict) else out[0]
 
 
@@ -57,6 +60,13 @@ def _worker2(rank, world, family):
             return X.EvaCLIPVisionModel(X.EvaCLIPVisionConfig(**big)), "image"
         if family == "pixtral":
             return X.PixtralVisionModel(X.PixtralVisionConfig(**big, head_dim=16)), "image"
+        if family == "phi4_audio":
+            # the conformer's causal convolutions (kernel 3) need the two tokens before a rank's chunk; 65 tokens split 33 / 32
+            from cornstarch_b200.models.phi4_audio import Phi4MultimodalAudioConfig, Phi4MultimodalAudioModel
+
+            return Phi4MultimodalAudioModel(Phi4MultimodalAudioConfig(
+                hidden_size=64, intermediate_size=96, num_blocks=2, num_attention_heads=4, input_size=16, nemo_conv_channels=32,
+                ext_pw_out_channel=64, kernel_size=3, time_reduction=8, depthwise_separable_out_channel=64)), "phi4"
         cfg = dict(num_mel_bins=8, d_model=64, encoder_layers=2, encoder_attention_heads=4, encoder_ffn_dim=128, max_source_positions=300)
         if family == "whisper":
             return W.WhisperEncoder(W.WhisperConfig(**cfg)), "audio"
@@ -68,7 +78,10 @@ def _worker2(rank, world, family):
     model, _ = build()
     model.load_state_dict(ref.state_dict())
     g = torch.Generator().manual_seed(5)
-    x = torch.randn(2, 3, 224, 224, generator=g) if kind == "image" else torch.randn(2, 8, 600, generator=g)
+    if kind == "phi4":
+        x = torch.randn(2, 520, 16, generator=g)
+    else:
+        x = torch.randn(2, 3, 224, 224, generator=g) if kind == "image" else torch.randn(2, 8, 600, generator=g)
     _check(ref, model, kind, x, world)
 
 
