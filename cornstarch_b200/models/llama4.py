@@ -173,17 +173,19 @@ class Llama4TextAttention(nn.Module):
             q, k, v = (comm.all_to_all_comm(t.contiguous(), pc.sp_group, 2, 1) for t in (q, k, v))
             Hq, Hk, S = Hq // pc.sp_size, Hk // pc.sp_size, q.shape[1]
         q, k, v = q.reshape(B, S, Hq, D), k.reshape(B, S, Hk, D), v.reshape(B, S, Hk, D)
+        ring = getattr(mask, "_cp_state", None) is not None  # this rank holds the tokens at global positions `pos`
         if self.use_rope:
-            q, k = rope_interleaved(q, rope[0][:S], rope[1][:S]), rope_interleaved(k, rope[0][:S], rope[1][:S])
+            cos, sin = (rope[0][:S], rope[1][:S]) if pos is None else (rope[0].index_select(0, pos), rope[1].index_select(0, pos))
+            q, k = rope_interleaved(q, cos, sin), rope_interleaved(k, cos, sin)
         if self.qk_norm:
             q = (q.float() * torch.rsqrt(q.float().pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype)
             k = (k.float() * torch.rsqrt(k.float().pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype)
         if self.temperature:
-            p = torch.arange(S, device=x.device, dtype=torch.float32)
+            p = torch.arange(S, device=x.device, dtype=torch.float32) if pos is None else pos.float()
             scales = torch.log1p(torch.floor((p + 1.0) / self.floor_scale)) * self.attn_scale + 1.0
             q = (q * scales.view(1, S, 1, 1)).to(x.dtype)
         fn = self.attn_impl or A.attention
-        if self.use_rope and S > self.chunk:
+        if self.use_rope and S > self.chunk and not ring:
             # chunked attention: chunks are independent causal sequences, i.e. further batch entries (the tail is padded
             # with keys that no real query can see, because they come after every real token of their chunk)
             assert mask is None or mask.mode == A.MASK_CAUSAL, "chunked attention supports the plain causal mask"
@@ -268,24 +270,58 @@ class Llama4TextModel(PreTrainedModel):
                 hidden_states = comm.split_forward_gather_backward(hidden_states, 1, pc.sp_group, 1.0 / pc.sp_size)
         B, S, _ = hidden_states.shape
         mask = as_attn_mask(attention_mask, B, S, hidden_states.device)
-        rope = self.rotary_emb.tables(S * (pc.sp_size if ulysses else 1), hidden_states.device)
+        pos, chunk_mask, cp_state, S_full = None, None, None, S
+        if pc is not None and pc.sp_mode == "ring_attn" and pc.sp_size > 1:
+            assert attention_mask is None, "ring attention for Llama-4 supports the plain causal mask"
+            hidden_states, pos, mask, chunk_mask, cp_state, S_full = self._context_parallel_split(hidden_states, kw)
+            S = hidden_states.shape[1]
+        rope = self.rotary_emb.tables(S_full * (pc.sp_size if ulysses else 1), hidden_states.device)
         x, router = hidden_states, []
         for layer in self.layers:
             if is_released(layer):
                 continue
+            m = chunk_mask if (chunk_mask is not None and layer.self_attn.use_rope) else mask
             if self.gradient_checkpointing and self.training and torch.is_grad_enabled():
-                x, lg = checkpoint_layer(layer, x, rope, None, mask)
+                x, lg = checkpoint_layer(layer, x, rope, pos, m)
             else:
-                x, lg = layer(x, rope, None, mask)
+                x, lg = layer(x, rope, pos, m)
             if lg is not None:
                 router.append(lg)
         if is_released(self.norm):
-            return ModelOutput(hidden_states=x, router_logits=tuple(router) or None)
+            return ModelOutput(hidden_states=x, router_logits=tuple(router) or None, cp_state=cp_state)
         out = self.norm(x)
         if ulysses:
             # back to the full sequence for the LM head (the loss is then the same on every sequence-parallel rank)
             out = comm.gather_forward_split_backward(out, 1, pc.sp_group, float(pc.sp_size))
-        return ModelOutput(last_hidden_state=out, router_logits=tuple(router) or None)
+        return ModelOutput(last_hidden_state=out, router_logits=tuple(router) or None, cp_state=cp_state)
+
+    def _context_parallel_split(self, hidden_states, kw):
+        """Ring attention: pick this rank's tokens (on the first stage) and state both masks through global positions.
+
+        The global (NoPE) layers use the causal mask.  The chunked layers use a bitfield mask: a query carries the text
+        bit and the bit of its chunk, a key only the bit of its chunk, so a query sees the earlier keys of its own chunk.
+        One bit per chunk limits a sequence to 60 chunks.  The reference runs this model under ring attention too
+        (cornstarch/shardformer/modeling/llama4.py:148-200)."""
+        from ..parallel.cp import ContextParallelBatchSplitUtils as U, ContextParallelState
+
+        pc, dev = self.pc, hidden_states.device
+        B, S, _ = hidden_states.shape
+        first = self.holds("embed_tokens")
+        S_full = int(kw.get("full_seq_len") or (S if first else S * pc.sp_size))
+        offsets = U.create_context_parallel_split(None, pc.sp_group, pc.cp_dist_mode, seq_len=S_full, batch=B, device=dev)
+        if offsets is None:  # too short to split: every rank computes the whole sequence
+            return hidden_states, None, A.AttnMask.causal(), None, None, S_full
+        state = ContextParallelState(pc.sp_group, offsets, A.AttnMask.causal(), dev)
+        chunk_mask, C = None, int(self.config.attention_chunk_size)
+        if S_full > C:
+            n_chunks = (S_full + C - 1) // C
+            assert n_chunks <= 60, f"{n_chunks} attention chunks: ring attention for Llama-4 encodes at most 60 in its mask"
+            chunk_bit = torch.ones(B, S_full, dtype=torch.int64, device=dev) << (1 + torch.arange(S_full, device=dev) // C)
+            chunk_state = ContextParallelState(pc.sp_group, offsets, A.AttnMask.bitfield(chunk_bit | 1, k_bits=chunk_bit), dev)
+            chunk_mask = chunk_state.local_mask
+        if S == S_full and first:
+            hidden_states = hidden_states.index_select(1, state.mine)
+        return hidden_states, state.mine.int(), state.local_mask, chunk_mask, state, S_full
 
 
 class Llama4ForCausalLM(PreTrainedModel):
@@ -326,7 +362,20 @@ class Llama4ForCausalLM(PreTrainedModel):
                 w = w[: self.valid_vocab]
             tp = self.tp_group if (self.tp_group is not None and comm._world(self.tp_group) > 1) else None
             h_in = comm.reduce_backward(h, tp) if tp is not None else h  # each vocabulary shard yields a partial dh
-            res["loss"] = linear_cross_entropy(h_in, w, tgt, tp_group=tp, vocab_start=self.vocab_start)
+            cp_state = out.get("cp_state")
+            if cp_state is not None:
+                # this rank holds a token subset: normalise by the global token count, pre-multiplied by sp so that
+                # the gradient average over the dp x sp group yields d(sum / count)
+                tgt = tgt.index_select(1, cp_state.mine)
+                loss_sum, n_valid = linear_cross_entropy(h_in, w, tgt, tp_group=tp, vocab_start=self.vocab_start,
+                                                         reduction="sum_and_count")
+                total = n_valid.clone().float()
+                torch.distributed.all_reduce(total, group=cp_state.group)
+                sp = torch.distributed.get_world_size(cp_state.group)
+                res["loss_sum"], res["num_valid"] = loss_sum, total
+                res["loss"] = loss_sum * sp / total.clamp(min=1).to(loss_sum.dtype)
+            else:
+                res["loss"] = linear_cross_entropy(h_in, w, tgt, tp_group=tp, vocab_start=self.vocab_start)
         else:
             tp = self.tp_group if (self.tp_group is not None and comm._world(self.tp_group) > 1) else None
             logits = linear(comm.reduce_backward(h, tp) if tp is not None else h, self.lm_head.weight)

@@ -318,7 +318,7 @@ class Llama4TextModelPolicy(ModelPolicy):
     model_cls = L4.Llama4TextModel
     first_stage_modules = ["embed_tokens", "rotary_emb"]
     last_stage_modules = ["norm"]
-    supported_sp_modes = ("all_to_all",)  # Ulysses; ring attention is not built for this model
+    supported_sp_modes = ("all_to_all", "ring_attn")  # both with the plain causal mask
     head_modules = _L4_LAYER + r"self_attn"
     tp_rules = [
         TPRule(_L4_LAYER + r"self_attn\.(q_proj|k_proj|v_proj)", "col"),

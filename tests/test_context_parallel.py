@@ -206,7 +206,7 @@ def _family_sp_worker(rank, world, family, sp_mode):
 
 
 def _family_group_worker(rank, world, sp_mode):
-    families = ["mistral", "qwen3", "gemma", "phi3", "mixtral"] + (["llama4"] if sp_mode == "all_to_all" else [])
+    families = ["mistral", "qwen3", "gemma", "phi3", "mixtral", "llama4"]
     for family in families:
         _family_sp_worker(rank, world, family, sp_mode)
         dist.barrier()
