@@ -77,14 +77,11 @@ class DecoderForCausalLMPolicy(DecoderModelPolicy):
 
 
 class MoeForCausalLMPolicy(DecoderForCausalLMPolicy):
-    model_cls = M.MoeForCausalLM
+    """Mixtral and Qwen3-MoE.  Both run under Ulysses and ring attention (the reference refuses sequence parallelism
+    for Qwen3-MoE, cornstarch/shardformer/policies/qwen3_moe.py:107-111; here the expert block works on whatever token
+    subset a rank holds, so nothing stands in the way)."""
 
-    def config_sanity_check(self):
-        super().config_sanity_check()
-        if getattr(self.model.config, "model_type", "") == "qwen3_moe":
-            sc = self.shard_config
-            if sc is not None and sc.enable_sequence_parallelism and sc.sequence_parallel_size > 1:
-                raise ValueError("Qwen3-MoE does not support sequence parallelism")
+    model_cls = M.MoeForCausalLM
 
 
 _ENC_ATTN_COL = r"(q_proj|k_proj|v_proj|query|key|value)"

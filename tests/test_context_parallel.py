@@ -206,7 +206,7 @@ def _family_sp_worker(rank, world, family, sp_mode):
 
 
 def _family_group_worker(rank, world, sp_mode):
-    families = ["mistral", "qwen3", "gemma", "phi3", "mixtral", "llama4"]
+    families = ["mistral", "qwen2", "qwen3", "gemma", "gemma2", "gemma3", "phi3", "mixtral", "qwen3_moe", "llama4"]
     for family in families:
         _family_sp_worker(rank, world, family, sp_mode)
         dist.barrier()
