@@ -12,7 +12,8 @@ scaled-dot-product attention; the audio sequences are short (T = frames / time_r
 convolutions use cuDNN through PyTorch like the other front-ends.
 
 Parallel forms: tensor parallelism splits the heads and both feed-forwards (every rank reads its heads' columns of the
-replicated bias table); under context parallelism ("ring_attn") the tokens are split in contiguous chunks after the
+replicated bias table); Ulysses ("all_to_all") splits the tokens between the attention layers and the heads inside
+them; under context parallelism ("ring_attn") the tokens are split in contiguous chunks after the
 sub-sampling front-end, keys / values are gathered, each rank keeps the bias rows of its own queries and the causal
 depth-wise convolutions fetch their ``kernel_size - 1`` left neighbours from the previous rank; a later pipeline stage
 receives the bias together with the hidden states.
@@ -98,7 +99,10 @@ class _RelativeAttentionBias(nn.Module):
         self.max_distance, self.symmetric = config.bias_max_distance, config.bias_symmetric
         self.num_buckets = self.max_distance * (1 if self.symmetric else 2)
         self.bias_values = nn.Embedding(self.num_buckets, config.num_attention_heads)
-        self.tp_group = None  # set under tensor parallelism: this rank then returns the bias of its own heads only
+        # groups that split the heads, outermost first, as (group, sum_gradient): tensor parallelism (the table is
+        # replicated and its gradient summed over the ranks) and then Ulysses sequence parallelism (no sum: the
+        # gradients of sequence-parallel ranks are partial sums like those of every other parameter)
+        self.head_splits: list = []
 
     def forward(self, T: int, device, rows: tuple[int, int] | None = None):
         """``rows = (start, end)``: only the bias of those query positions (a context-parallel rank's tokens)."""
@@ -107,11 +111,10 @@ class _RelativeAttentionBias(nn.Module):
         rel = (pos[None, :] - q_pos[:, None]).clamp(-self.max_distance, self.max_distance - 1)
         idx = rel.abs() if self.symmetric else rel + self.num_buckets // 2
         w = self.bias_values.weight
-        if self.tp_group is not None and comm._world(self.tp_group) > 1:
-            # the table stays replicated; each rank reads the columns of its heads, so the gradient is summed over ranks
-            tp, r = comm._world(self.tp_group), torch.distributed.get_rank(self.tp_group)
-            per = w.shape[1] // tp
-            w = comm.reduce_backward(w, self.tp_group)[:, r * per : (r + 1) * per]
+        for group, sum_gradient in self.head_splits:
+            n, r = comm._world(group), torch.distributed.get_rank(group)
+            per = w.shape[1] // n
+            w = (comm.reduce_backward(w, group) if sum_gradient else w)[:, r * per : (r + 1) * per]
         return F.embedding(idx, w).permute(2, 0, 1).unsqueeze(0)  # [1, local heads, T or rows, T]
 
 
@@ -140,19 +143,28 @@ class _AudioAttention(nn.Module):
         self.num_heads, self.head_dim = config.num_attention_heads, H // config.num_attention_heads
         self.q_proj, self.k_proj, self.v_proj, self.o_proj = cnn.Linear(H, H), cnn.Linear(H, H), cnn.Linear(H, H), cnn.Linear(H, H)
         self.cp_group = None  # context parallelism: x holds this rank's tokens, the bias its rows against all keys
+        self.ulysses_group = None  # Ulysses: x holds this rank's tokens; attention sees all tokens for a share of the heads
 
     def forward(self, x, bias):
         B, T, _ = x.shape
-        W = self.num_heads * self.head_dim
+        W, heads = self.num_heads * self.head_dim, self.num_heads
         qkv = multi_linear(self.q_proj.input_hook(x), [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight],
                            [self.q_proj.bias, self.k_proj.bias, self.v_proj.bias])
-        q, k, v = (qkv[..., i * W : (i + 1) * W].view(B, T, self.num_heads, self.head_dim).transpose(1, 2) for i in range(3))
+        q, k, v = (qkv[..., i * W : (i + 1) * W] for i in range(3))
+        ulysses = self.ulysses_group is not None and comm._world(self.ulysses_group) > 1
+        if ulysses:
+            q, k, v = (comm.all_to_all_comm(t.contiguous(), self.ulysses_group, 2, 1) for t in (q, k, v))  # [B, T_all, W / sp]
+            heads, T = heads // comm._world(self.ulysses_group), q.shape[1]
+        q, k, v = (t.reshape(B, T, heads, self.head_dim).transpose(1, 2) for t in (q, k, v))
         if self.cp_group is not None and comm._world(self.cp_group) > 1:
             kv = comm.gather_forward_reduce_scatter_backward(torch.stack([k, v]), 3, self.cp_group,
                                                              _cp_sizes(bias.shape[-1], comm._world(self.cp_group)))
             k, v = kv[0], kv[1]
         o = F.scaled_dot_product_attention(q, k, v, attn_mask=bias.to(q.dtype))
-        return self.o_proj(o.transpose(1, 2).reshape(B, T, W))
+        o = o.transpose(1, 2).reshape(B, T, heads * self.head_dim)
+        if ulysses:
+            o = comm.all_to_all_comm(o, self.ulysses_group, 1, 2)  # back to [B, T_local, W]
+        return self.o_proj(o)
 
 
 class _GluPointWiseConv(nn.Module):
@@ -247,13 +259,17 @@ class Phi4MultimodalAudioModel(PreTrainedModel):
 
     def set_parallel_context(self, pc):
         self.pc = pc
-        cp = pc.sp_group if pc is not None and pc.sp_mode == "ring_attn" and pc.sp_size > 1 else None
-        self._cp_group = cp
+        sp = pc.sp_group if pc is not None and pc.sp_mode in ("ring_attn", "all_to_all") and pc.sp_size > 1 else None
+        ring = sp if pc is not None and pc.sp_mode == "ring_attn" else None
+        ulysses = sp if pc is not None and pc.sp_mode == "all_to_all" else None
+        self._cp_group, self._ulysses_group = ring, ulysses
         for layer in self.encoders:
             if not is_released(layer):
-                layer.self_attn.cp_group = layer.conv.cp_group = cp
+                layer.self_attn.cp_group, layer.self_attn.ulysses_group = ring, ulysses
+                layer.conv.cp_group = sp  # the tokens are split in contiguous chunks in both modes
         if not is_released(self.relative_attention_bias_layer):
-            self.relative_attention_bias_layer.tp_group = pc.tp_group if pc is not None else None
+            splits = [(pc.tp_group, True)] if pc is not None and pc.tp_size > 1 else []
+            self.relative_attention_bias_layer.head_splits = splits + ([(ulysses, False)] if ulysses is not None else [])
 
     def forward(self, audio_input_features=None, hidden_states=None, attention_bias=None, **kw):
         """A later pipeline stage gets ``hidden_states`` and the ``attention_bias`` the first stage computed (the
@@ -264,8 +280,14 @@ class Phi4MultimodalAudioModel(PreTrainedModel):
             x = hidden_states
         bias = attention_bias
         if bias is None:
-            cp, T = getattr(self, "_cp_group", None), x.shape[1]
-            if cp is None:
+            cp, ul, T = getattr(self, "_cp_group", None), getattr(self, "_ulysses_group", None), x.shape[1]
+            if ul is not None:
+                # Ulysses: equal contiguous chunks between the attention layers; attention sees every token, so the bias
+                # keeps all rows (of this rank's heads)
+                assert T % comm._world(ul) == 0, f"{T} audio tokens do not divide over {comm._world(ul)} sequence-parallel ranks"
+                x = comm.split_forward_gather_backward(x, 1, ul)
+                bias = self.relative_attention_bias_layer(T, x.device)
+            elif cp is None:
                 bias = self.relative_attention_bias_layer(T, x.device)
             else:
                 # context parallelism: contiguous token chunks in rank order (the causal convolutions need their left

@@ -338,7 +338,7 @@ class Phi4MultimodalAudioModelPolicy(ModelPolicy):
     first_stage_modules = ["encoder_embedding", "embed", "relative_attention_bias_layer"]
     last_stage_modules = []
     head_modules = r"encoders\.\d+\.self_attn"
-    supported_sp_modes = ("ring_attn",)  # contiguous chunks; K/V gathered, the causal convolutions exchange a halo
+    supported_sp_modes = ("ring_attn", "all_to_all")  # contiguous chunks; the causal convolutions exchange a halo
     tp_rules = [
         TPRule(r"encoders\.\d+\.self_attn\.(q_proj|k_proj|v_proj)", "col"),
         TPRule(r"encoders\.\d+\.self_attn\.o_proj", "row"),

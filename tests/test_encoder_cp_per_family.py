@@ -18,7 +18,7 @@ def _features(model, kind, x):
     return out["last_hidden_state"] if isinstance(out, dict) else out[0]
 
 
-def _check(ref, model, kind, x, world):
+def _check(ref, model, kind, x, world, sp_mode="ring_attn"):
     from cornstarch_b200.parallel import comm
     from cornstarch_b200.shardformer.shard.shard_config import ShardConfig
     from cornstarch_b200.shardformer.shard.shardformer import ShardFormer
@@ -28,7 +28,7 @@ def _check(ref, model, kind, x, world):
     wgt = torch.randn(want.shape, generator=torch.Generator().manual_seed(9))
     (want.float() * wgt).sum().backward()
     sc = ShardConfig(sequence_parallel_process_group=dist.group.WORLD, enable_sequence_parallelism=True,
-                     sequence_parallelism_mode="ring_attn", enable_tensor_parallelism=False, extra_kwargs={"device": "cpu"})
+                     sequence_parallelism_mode=sp_mode, enable_tensor_parallelism=False, extra_kwargs={"device": "cpu"})
     ShardFormer(sc).optimize(model)
     xs = x.clone().requires_grad_(True)
     local = _features(model, kind, xs)
@@ -41,7 +41,7 @@ def _check(ref, model, kind, x, world):
     assert ref_max > 0 and err <= 2e-3 * ref_max, (err, ref_max)
 
 
-def _worker2(rank, world, family):
+def _worker2(rank, world, family, sp_mode="ring_attn"):
     big = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=224, patch_size=14)
     from cornstarch_b200.models import vision as V
     from cornstarch_b200.models import vision_extra as X
@@ -79,10 +79,10 @@ def _worker2(rank, world, family):
     model.load_state_dict(ref.state_dict())
     g = torch.Generator().manual_seed(5)
     if kind == "phi4":
-        x = torch.randn(2, 520, 16, generator=g)
+        x = torch.randn(2, 520 if sp_mode == "ring_attn" else 512, 16, generator=g)  # Ulysses wants equal shards
     else:
         x = torch.randn(2, 3, 224, 224, generator=g) if kind == "image" else torch.randn(2, 8, 600, generator=g)
-    _check(ref, model, kind, x, world)
+    _check(ref, model, kind, x, world, sp_mode)
 
 
 def _group_worker(rank, world, families):
@@ -97,6 +97,11 @@ def _group_worker(rank, world, families):
 @pytest.mark.parametrize("families", [FAMILIES[:4], FAMILIES[4:]], ids=["vision_a", "vision_b_and_audio"])
 def test_encoder_ring_attn_matches_unsharded(families):
     run_distributed(_group_worker, 2, families)
+
+
+def test_phi4_audio_ulysses_matches_unsharded():
+    """Tokens split between the conformer's attention layers (halo for the causal convolutions), heads inside them."""
+    run_distributed(_worker2, 2, "phi4_audio", "all_to_all")
 
 
 def _qwen2_vl_worker(rank, world):
