@@ -182,6 +182,7 @@ class InternVisionModelPolicy(ModelPolicy):
     fused qkv is column parallel (cornstarch/shardformer/policies/intern_vit.py:35-45)."""
 
     model_cls = X.InternVisionModel
+    supported_sp_modes = ("ring_attn",)  # the reference switches sequence parallelism off for this model (intern_vit.py:82-83)
     first_stage_modules = ["embeddings"]
     last_stage_modules = []
     head_modules = r"encoder\.layers\.\d+"

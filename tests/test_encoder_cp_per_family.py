@@ -7,7 +7,7 @@ import torch.distributed as dist
 
 from tests.dist_utils import run_distributed
 
-FAMILIES = ["siglip", "clip", "vit", "dinov2", "evaclip", "pixtral", "whisper", "qwen2_audio", "phi4_audio"]
+FAMILIES = ["siglip", "clip", "vit", "dinov2", "evaclip", "pixtral", "whisper", "qwen2_audio", "phi4_audio", "internvit"]
 
 
 def _features(model, kind, x):
@@ -58,6 +58,8 @@ def _worker2(rank, world, family, sp_mode="ring_attn"):
             return X.Dinov2Model(X.Dinov2Config(**big)), "image"
         if family == "evaclip":
             return X.EvaCLIPVisionModel(X.EvaCLIPVisionConfig(**big)), "image"
+        if family == "internvit":
+            return X.InternVisionModel(X.InternVisionConfig(**big)), "image"  # q / k normalised over the full width, per token
         if family == "pixtral":
             return X.PixtralVisionModel(X.PixtralVisionConfig(**big, head_dim=16)), "image"
         if family == "phi4_audio":
