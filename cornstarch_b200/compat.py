@@ -34,6 +34,7 @@ _ALIASES = {
     "cornstarch.kernel.interface": "cornstarch_b200.kernel.interface",
     "cornstarch.kernel.bitfield_attention": "cornstarch_b200.kernel.bitfield_attention",
     "cornstarch.kernel.attention": "cornstarch_b200.kernel.attention",
+    "cornstarch.models.intern_vit.flash_attention": "cornstarch_b200.kernel.attention",  # FlashAttention module
     "cornstarch.plugin": "cornstarch_b200.plugin",
     "cornstarch.plugin.multimodal_parallel_plugin": "cornstarch_b200.plugin.multimodal_api",
     # the sub-modules of that package: every one resolves to the module that exports all of the package's names
