@@ -259,3 +259,31 @@ def _two_stage_encoder_worker(rank, world, tp):
 @pytest.mark.parametrize("tp,world", [(1, 3), (2, 6)])
 def test_two_stage_encoder_hands_on_its_attention_bias(tp, world):
     run_distributed(_two_stage_encoder_worker, world, tp)
+
+
+def _colocated_two_stage_encoder_worker(rank, world):
+    """The colocated plugin with a two-stage audio encoder: the attention bias travels beside the encoder's hidden states."""
+    from cornstarch_b200.booster import Booster
+    from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
+    from cornstarch_b200.pipeline_template import PipelineTemplate
+    from cornstarch_b200.plugin.encoders_colocated_plugin import EncodersColocatedMultimodalParallelPlugin
+    from cornstarch_b200.plugin.modal_parallel_plugin import ModalParallelPlugin
+
+    n_micro = 2
+    ref, batch = _phi4_audio_lm()
+    ref_loss = sum((ref(**{k: v[2 * i : 2 * i + 2] for k, v in batch.items()}).loss / n_micro).item() for i in range(n_micro))
+    model, _ = _phi4_audio_lm()
+    plugin = EncodersColocatedMultimodalParallelPlugin(
+        encoder_plugins={"audio": ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.audio_encoder, 2))},
+        language_model_plugin=ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.language_model, 1)),
+        num_microbatches=n_micro, device=torch.device("cpu"))
+    booster = Booster(plugin=plugin)
+    opt = FusedAdamW(split_decay_groups(model, 0.0), lr=1e-2)
+    pmodel, popt, criterion, *_ = booster.boost(model, opt, criterion=lambda out, b: out.loss)
+    out = booster.execute_pipeline(iter([batch]), pmodel, criterion, popt, return_loss=True)
+    if plugin.stage_manager.is_last_stage(check_only_in_modal=False):
+        assert abs(out["loss"].item() - ref_loss) < 1e-4, (out["loss"].item(), ref_loss)
+
+
+def test_colocated_two_stage_encoder():
+    run_distributed(_colocated_two_stage_encoder_worker, 3)
