@@ -420,6 +420,18 @@ class DecoderModel(PreTrainedModel):
         return hidden_states, pos, state.local_mask, state, S_full
 
 
+def _full_seq_len(kwargs, input_ids, labels) -> int:
+    """Length of the whole sequence as a later pipeline stage can know it under context parallelism: its hidden states
+    hold this rank's tokens only, but the micro-batch still carries the full ``input_ids`` / ``labels``."""
+    n = kwargs.get("full_seq_len")
+    if n:
+        return int(n)
+    for t in (input_ids, labels):
+        if t is not None:
+            return int(t.shape[1])
+    return 0
+
+
 def as_attn_mask(attention_mask, B: int, S: int, device) -> A.AttnMask:
     """Accept ``None`` (causal), an :class:`AttnMask`, an int64 bitfield ``[B,S]`` or a 0/1 padding mask ``[B,S]``."""
     if attention_mask is None:
@@ -475,7 +487,8 @@ class DecoderForCausalLM(PreTrainedModel):
     def forward(self, input_ids=None, inputs_embeds=None, attention_mask=None, position_ids=None, labels=None,
                 hidden_states=None, return_logits: bool | None = None, shift_labels: bool = True, **kwargs):
         out = self.model(input_ids=input_ids, inputs_embeds=inputs_embeds, attention_mask=attention_mask,
-                         position_ids=position_ids, hidden_states=hidden_states, rope_len=kwargs.get("rope_len", 0))
+                         position_ids=position_ids, hidden_states=hidden_states, rope_len=kwargs.get("rope_len", 0),
+                         full_seq_len=_full_seq_len(kwargs, input_ids, labels))
         h = out.last_hidden_state
         if not self.holds("lm_head"):
             return ModelOutput(hidden_states=h, router_logits=out.router_logits)

@@ -349,7 +349,10 @@ class Llama4ForCausalLM(PreTrainedModel):
 
     def forward(self, input_ids=None, inputs_embeds=None, attention_mask=None, labels=None, hidden_states=None, **kw):
         self.model.gradient_checkpointing = self.gradient_checkpointing
-        out = self.model(input_ids=input_ids, inputs_embeds=inputs_embeds, attention_mask=attention_mask, hidden_states=hidden_states)
+        from .llama import _full_seq_len
+
+        out = self.model(input_ids=input_ids, inputs_embeds=inputs_embeds, attention_mask=attention_mask, hidden_states=hidden_states,
+                         full_seq_len=_full_seq_len(kw, input_ids, labels))
         if "last_hidden_state" not in out or not self.holds("lm_head"):
             return ModelOutput(hidden_states=out.get("hidden_states", out.get("last_hidden_state")), router_logits=out.router_logits)
         h = out.last_hidden_state

@@ -215,3 +215,43 @@ def _family_group_worker(rank, world, sp_mode):
 @pytest.mark.parametrize("sp_mode", ["ring_attn", "all_to_all"])
 def test_decoder_families_sequence_parallel(sp_mode):
     run_distributed(_family_group_worker, 2, sp_mode)
+
+
+def _two_stage_ring_worker(rank, world):
+    """Ring attention across a pipeline cut: the second stage gets this rank's tokens only and recovers the length of
+    the whole sequence (and with it the token-to-rank map) from the micro-batch's ``input_ids``."""
+    import copy
+
+    from cornstarch_b200.pipeline_template import PipelineTemplate
+    from cornstarch_b200.shardformer.shard.shard_config import ShardConfig
+    from cornstarch_b200.shardformer.shard.shardformer import ShardFormer
+    from tests.test_policy_tp_numerics import _build
+
+    for family in ("llama", "llama4"):
+        torch.manual_seed(0)
+        whole, _ = _build(family)
+        S = 512
+        whole.config.max_position_embeddings = S
+        ids = torch.randint(0, 128, (2, S), generator=torch.Generator().manual_seed(3))
+        want = whole(input_ids=ids, labels=ids).loss
+        stages = []
+        for names in PipelineTemplate.even_split(whole, 2).modules_per_stage:
+            m = copy.deepcopy(whole)
+            m.hold_only(list(names))
+            sc = ShardConfig(sequence_parallel_process_group=dist.group.WORLD, enable_sequence_parallelism=True,
+                             sequence_parallelism_mode="ring_attn", context_parallel_distribution_mode="zigzag",
+                             enable_tensor_parallelism=False, extra_kwargs={"device": "cpu"})
+            ShardFormer(sc).optimize(m)
+            stages.append(m)
+        first = stages[0](input_ids=ids)
+        assert first["hidden_states"].shape[1] == S // world
+        passed = {k: v for k, v in first.items() if isinstance(v, torch.Tensor)}
+        out = stages[1](input_ids=ids, labels=ids, **passed)
+        tot = out.loss.detach().clone()
+        dist.all_reduce(tot)
+        assert abs(tot.item() / world - want.item()) < 2e-4 * max(1.0, abs(want.item())), (family, tot.item() / world, want.item())
+        dist.barrier()
+
+
+def test_ring_attention_across_a_pipeline_cut():
+    run_distributed(_two_stage_ring_worker, 2)
