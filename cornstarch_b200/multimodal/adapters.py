@@ -108,18 +108,27 @@ class _PassThroughMerger(nn.Module):
 
 
 def multimodal_from_state_dict(model_type: str, config: dict, state_dict: dict, dtype=None, device=None) -> MultimodalModel:
-    if model_type == "llava_next":
+    if model_type in ("llava_next", "llava"):
+        # LLaVA-1.5 has the modules and key names of LLaVA-NeXT without ``image_newline``; every image is one base tile
         parts = split_llava_next_state_dict(state_dict)
         vcfg = dict(config["vision_config"])
         layer = config.get("vision_feature_layer", -2)
         assert isinstance(layer, int) and layer < 0, "a single negative vision_feature_layer is supported"
         keep = vcfg["num_hidden_layers"] + layer + 1  # -1 keeps all layers, -2 drops the last one, ...
         vcfg["num_hidden_layers"] = keep
-        vcfg.pop("model_type", None)
-        vision = V.CLIPVisionModel(V.CLIPVisionConfig(**{k: v for k, v in vcfg.items() if k in (
+        tower = vcfg.pop("model_type", None) or "clip_vision_model"
+        vkw = {k: v for k, v in vcfg.items() if k in (
             "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads", "num_channels", "image_size",
-            "patch_size", "hidden_act", "layer_norm_eps")}))
+            "patch_size", "hidden_act", "layer_norm_eps")}
+        if tower.startswith("siglip"):
+            vision = V.SiglipVisionModel(V.SiglipVisionConfig(**vkw, vision_use_head=False))
+        else:
+            vision = V.CLIPVisionModel(V.CLIPVisionConfig(**vkw))
         vsd = {k: v for k, v in parts["vision"].items() if not _layer_index_at_least(k, keep)}
+        if tower.startswith("siglip"):
+            # the feature layer's output is taken before SigLIP's final LayerNorm and pooling head
+            vision.hold_only([n for n in vision.module_names(vision.config) if n not in ("vision_model.post_layernorm", "vision_model.head")])
+            vsd = {k: v for k, v in vsd.items() if not k.startswith(("vision_model.post_layernorm.", "vision_model.head."))}
         llm = _text_model(config["text_config"])
         pc = MultimodalProjectorConfig(encoder_config=vision.config, text_config=llm.config, projection_type="mlp",
                                        activation=config.get("projector_hidden_act", "gelu"))
@@ -151,7 +160,7 @@ def multimodal_from_state_dict(model_type: str, config: dict, state_dict: dict, 
         enc = ModalEncoderModule(vision, projector, additional_args=["grid_thw"])
         token_id = config.get("image_token_id", config.get("image_token_index"))
     else:
-        raise NotImplementedError(f"from_pretrained_multimodal_model supports llava_next and qwen2_vl, not '{model_type}'")
+        raise NotImplementedError(f"from_pretrained_multimodal_model supports llava, llava_next and qwen2_vl, not '{model_type}'")
 
     _load(vision, vsd, "vision tower")
     _load(projector, parts["projector"], "projector")
@@ -166,7 +175,10 @@ def multimodal_from_state_dict(model_type: str, config: dict, state_dict: dict, 
 
 
 def _keep_all(inputs, output):
-    h = output["last_hidden_state"] if isinstance(output, dict) else output[0]
+    if isinstance(output, dict):
+        h = output["last_hidden_state"] if "last_hidden_state" in output else output["hidden_states"]
+    else:
+        h = output[0]
     return (h,)
 
 

@@ -226,7 +226,8 @@ class MultimodalModel(nn.Module):
         self.language_model = language_model
         self.preprocess_llm_callback = preprocess_llm_callback
         self.token_ids: dict[str, int] | None = None
-        # "modality": one bit per modality (reference rule); "instance": one bit per image/audio instance + prefix-causal
+        # "modality": one bit per modality (reference rule); "instance": one bit per image/audio instance + prefix-causal;
+        # "causal": modality tokens are ordinary causal tokens
         self.mask_mode = mask_mode
         self.check_counts = False
 
@@ -295,9 +296,17 @@ class MultimodalModel(nn.Module):
             return create_instance_bitfield_attention_mask(input_ids, ordered, padding_mask)
         return create_bitfield_attention_mask(input_ids, ordered, padding_mask)
 
+    def _mask_from_bits(self, bits: torch.Tensor) -> A.AttnMask:
+        if self.mask_mode == "causal":
+            # every real token is a text token: the plain causal mask (plus padding) Hugging Face's own multimodal models
+            # use, and the reference under any attention implementation but its bitfield one
+            text = torch.full_like(bits, (1 << 62) | 1)
+            return A.AttnMask.bitfield(torch.where(bits != 0, text, torch.zeros_like(bits)))
+        return A.AttnMask.bitfield(bits, prefix_causal=(self.mask_mode == "instance"))
+
     def build_attn_mask(self, input_ids, padding_mask=None) -> A.AttnMask:
         bits = self.create_bitfield_attention_mask(input_ids, padding_mask)
-        return A.AttnMask.bitfield(bits, prefix_causal=(self.mask_mode == "instance"))
+        return self._mask_from_bits(bits)
 
     def merge_source_index(self, input_ids: torch.Tensor, feature_counts: dict[str, int]) -> torch.Tensor:
         """int32 ``[B*S]``: ``>= 0`` = embedding row (token id), ``< 0`` = ``-(row of the concatenated features) - 1``."""
@@ -383,7 +392,7 @@ class MultimodalModel(nn.Module):
             labels = torch.where(ignore, torch.full_like(labels, -100), labels)
         if self.token_ids:
             embeds, bits = self.merge_encoder_outputs(have, input_ids, inputs_embeds, attention_mask)
-            mask = A.AttnMask.bitfield(bits, prefix_causal=(self.mask_mode == "instance"))
+            mask = self._mask_from_bits(bits)
         else:
             embeds = inputs_embeds if inputs_embeds is not None else self.language_model.get_input_embeddings()(input_ids)
             mask = attention_mask
@@ -409,7 +418,7 @@ class MultimodalModel(nn.Module):
         for _ in range(max_new_tokens):
             if self.token_ids:
                 embeds, bits = self.merge_encoder_outputs(enc_out, ids, None, None)
-                mask = A.AttnMask.bitfield(bits, prefix_causal=(self.mask_mode == "instance"))
+                mask = self._mask_from_bits(bits)
             else:
                 embeds, mask = self.language_model.get_input_embeddings()(ids), None
             out = self.language_model(inputs_embeds=embeds, attention_mask=mask)

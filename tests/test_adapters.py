@@ -142,3 +142,30 @@ def test_language_model_alone_from_a_llava_checkpoint(tmp_path):
     with torch.no_grad():
         want = hf.lm_head(hf.model.language_model(input_ids=ids).last_hidden_state)
         assert torch.allclose(llm(input_ids=ids).logits, want, atol=1e-4)
+
+
+@pytest.mark.parametrize("tower", ["clip", "siglip"])
+def test_llava_full_forward_matches_hf(tower):
+    """LLaVA-1.5 (CLIP tower, CLS dropped) and its SigLIP variant (all patch tokens): logits of the whole multimodal
+    forward equal those of ``LlavaForConditionalGeneration`` with the same weights."""
+    from transformers import CLIPVisionConfig, LlamaConfig, LlavaConfig, LlavaForConditionalGeneration, SiglipVisionConfig
+
+    from cornstarch_b200.multimodal.adapters import multimodal_from_state_dict
+
+    torch.manual_seed(0)
+    vkw = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4, image_size=28, patch_size=14)
+    vision = CLIPVisionConfig(**vkw) if tower == "clip" else SiglipVisionConfig(**vkw)
+    cfg = LlavaConfig(
+        vision_config=vision.to_dict(),
+        text_config=LlamaConfig(vocab_size=200, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                                num_key_value_heads=2).to_dict(),
+        image_token_index=199, vision_feature_layer=-2, vision_feature_select_strategy="default" if tower == "clip" else "full")
+    hf = LlavaForConditionalGeneration(cfg).eval()
+    model = multimodal_from_state_dict("llava", cfg.to_dict(), hf.state_dict()).eval()
+    model.mask_mode = "causal"  # image tokens attend causally in Hugging Face's LLaVA
+    px = torch.randn(2, 3, 28, 28)
+    ids = torch.cat([torch.randint(0, 198, (2, 3)), torch.full((2, 4), 199), torch.randint(0, 198, (2, 9))], dim=1)
+    with torch.no_grad():
+        want = hf(input_ids=ids, pixel_values=px).logits
+        got = model(input_ids=ids, pixel_values=px).logits
+    assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
