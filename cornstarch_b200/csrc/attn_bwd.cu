@@ -55,7 +55,6 @@ struct AttnBwdParams {
   long dk_stride_b[CSB_MAX_SEG], dk_stride_s[CSB_MAX_SEG], dv_stride_b[CSB_MAX_SEG], dv_stride_s[CSB_MAX_SEG];
   int* status;
   int kj_slowest;  // block order: 1 = key block slowest (masks that leave key blocks unequal work), 0 = key block fastest
-  int dbg;  // timing experiments only (results are wrong when set): bit 0 no reduce-add, 1 no dQ staging, 2 no exp, 3 no dS^T store, 4 no P^T store
   SegInfo seg;
 };
 
@@ -94,7 +93,7 @@ __device__ __forceinline__ bool bw_wait(uint64_t* bar, uint32_t phase, volatile 
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > CSB_WAIT_NS) return false;
+      else if (now - t0 > wait_limit_ns()) return false;
     }
   }
   return false;
@@ -398,13 +397,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (lane == 0) tma_store_wait_read<0>();  // the previous block has left the staging buffer
       __syncwarp();
       float* stage = reinterpret_cast<float*>(smem + L::DQ_OFF + cw * (COLS * 128));
-      if (!(p.dbg & 2)) {
 #pragma unroll
-        for (int c = 0; c < COLS; ++c) stage[c * 32 + lane] = __uint_as_float(v[c]);
-      }
+      for (int c = 0; c < COLS; ++c) stage[c * 32 + lane] = __uint_as_float(v[c]);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0 && quarter * 32 < p.D && !(p.dbg & 3)) {
+      if (lane == 0 && quarter * 32 < p.D) {
         tma_reduce_add_4d(&tm_dq, stage, quarter * 32, ph, pi * BW_BQ + col0, b);  // box: 32 d x COLS q
         tma_store_commit();
       }
@@ -451,8 +448,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
 #pragma unroll
         for (int y = 0; y < 4; ++y)
-          pv[x4 * 4 + y] = (p.dbg & 4) ? fmaf(__uint_as_float(sv[x4 * 4 + y]), p.scale_log2, -ls[y])
-                                       : fast_exp2(fmaf(__uint_as_float(sv[x4 * 4 + y]), p.scale_log2, -ls[y]));
+          pv[x4 * 4 + y] = fast_exp2(fmaf(__uint_as_float(sv[x4 * 4 + y]), p.scale_log2, -ls[y]));
       }
       if (c == 1) {
 #pragma unroll
@@ -484,7 +480,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint32_t pk[COLS / 2];
 #pragma unroll
         for (int x = 0; x < COLS / 2; ++x) pk[x] = pack_bf16x2(pv[2 * x], pv[2 * x + 1]);
-        if (!(p.dbg & 16)) tmem_st_cols<COLS / 2>(tmem_base + (it & 1) * 64 + col0 + lane_addr, pk);
+        tmem_st_cols<COLS / 2>(tmem_base + (it & 1) * 64 + col0 + lane_addr, pk);
       }
 #pragma unroll
       for (int pc = 0; pc < COLS / 8; ++pc) {
@@ -493,7 +489,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         w.y = pack_bf16x2(ds[pc * 8 + 2], ds[pc * 8 + 3]);
         w.z = pack_bf16x2(ds[pc * 8 + 4], ds[pc * 8 + 5]);
         w.w = pack_bf16x2(ds[pc * 8 + 6], ds[pc * 8 + 7]);
-        if (!(p.dbg & 8)) *reinterpret_cast<uint4*>(smem + L::DST_OFF + sw128_offset(r, half * (COLS / 8) + pc)) = w;
+        *reinterpret_cast<uint4*>(smem + L::DST_OFF + sw128_offset(r, half * (COLS / 8) + pc)) = w;
       }
       tmem_st_wait();
       fence_proxy_async_smem();
@@ -586,6 +582,7 @@ CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void*
     attn_delta_kernel<<<(unsigned)blocks, threads, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(out),
                                                            reinterpret_cast<const __nv_bfloat16*>(dout), delta, B, Sq, Hq,
                                                            D, o_sb, o_ss, do_sb, do_ss);
+    if (int e = launch_result()) return e;
   }
   AttnBwdParams p;
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hk = Hk; p.D = D;
@@ -602,8 +599,6 @@ CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void*
   p.cls = reinterpret_cast<const int8_t*>(cls);
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
   p.status = status;
-  static const int dbg = []() { const char* e = getenv("CORNSTARCH_B200_ATTN_BWD_DEBUG"); return e ? atoi(e) : 0; }();
-  p.dbg = dbg;
   p.kj_slowest = mask_mode != MASK_FULL;
   fill_seg_info(&p.seg, kv, BW_BKV);
   if (p.seg.tile_start[kv->n_seg] != p.nK) return CSB_ERR_BAD_ARG;
@@ -773,3 +768,5 @@ CSB_API int csb_cp_reduce(const void* const* src, int world, const int* flags, i
   cp_reduce_kernel<<<(unsigned)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p, reinterpret_cast<__nv_bfloat16*>(out), n8);
   return launch_result();
 }
+
+CSB_WAIT_LIMIT_SETTER(attn_bwd)

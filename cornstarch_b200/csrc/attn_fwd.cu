@@ -118,7 +118,7 @@ __device__ __forceinline__ bool at_wait(uint64_t* bar, uint32_t phase, volatile 
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > CSB_WAIT_NS) return false;
+      else if (now - t0 > wait_limit_ns()) return false;
     }
   }
   return false;
@@ -596,3 +596,5 @@ CSB_API int csb_attn_fwd(const void* q, const void* k, const void* v, void* out,
   return csb_attn_fwd_seg(q, &kv, out, lse, B, Sq, Sk, Hq, Hk, D, q_stride_s, q_stride_b, o_stride_s, o_stride_b, scale,
                           mask_mode, q_bits, k_bits, q_pos, k_pos, cls, status, stream);
 }
+
+CSB_WAIT_LIMIT_SETTER(attn_fwd)

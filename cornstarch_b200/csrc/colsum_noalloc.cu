@@ -80,6 +80,9 @@ extern "C" __attribute__((visibility("default"))) int csb_colsum_noalloc(const v
                                                                           void* stream) {
   using namespace csb;
   if (x == nullptr || out == nullptr || rows <= 0 || H <= 0 || (H % 8) != 0) return CSB_ERR_BAD_ARG;
+  // x is read with 16-byte loads, out with its element size: a misaligned pointer would fault on the GPU
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return CSB_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(out) & (out_fp32 ? 3 : 1)) != 0) return CSB_ERR_BAD_ARG;
   if (H > CSB_COLSUM_NOALLOC_MAX_H) {
     fprintf(stderr,
             "[cornstarch_b200] csb_colsum_noalloc: H=%d exceeds the built-in scratch (max %d columns); "
@@ -95,6 +98,7 @@ extern "C" __attribute__((visibility("default"))) int csb_colsum_noalloc(const v
   if (parts > rows) parts = rows;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   colsum_noalloc_partial_kernel<<<parts, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), scratch, rows, H);
+  if (int e = launch_result()) return e;
   colsum_noalloc_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, out, parts, H, out_fp32, accumulate);
   return launch_result();
 }

@@ -303,15 +303,18 @@ __global__ void sumsq_kernel(const GradT* __restrict__ g, long n, float* __restr
     if (l == 0) atomicAdd(out, t);
   }
 }
-// scale_out = inv_loss_scale * min(1, max_norm / (sqrt(sumsq) * inv_loss_scale + 1e-6)); skip = !finite
+// scale_out = inv_loss_scale * min(1, max_norm / (sqrt(sumsq) * inv_loss_scale + 1e-6)); skip = !finite.
+// `status` (optional) is the device's bounded-wait status word: when a wait ran out earlier in the step the sums this
+// step produced are incomplete, so the update is skipped as well (the host raises at its next status poll).
 __global__ void clip_scale_kernel(const float* __restrict__ sumsq, float max_norm, float inv_loss_scale,
-                                  float* __restrict__ scale_out, float* __restrict__ norm_out, int* __restrict__ skip) {
+                                  float* __restrict__ scale_out, float* __restrict__ norm_out, int* __restrict__ skip,
+                                  const int* __restrict__ status) {
   const float norm = sqrtf(*sumsq) * inv_loss_scale;
   float s = inv_loss_scale;
   if (max_norm > 0.f) s *= fminf(1.f, max_norm / (norm + 1e-6f));
   *scale_out = s;
   if (norm_out) *norm_out = norm;
-  if (skip) *skip = isfinite(norm) ? 0 : 1;
+  if (skip) *skip = (isfinite(norm) && (status == nullptr || *status == 0)) ? 0 : 1;
 }
 
 // ------------------------------------------------------------------------------------ cross entropy
@@ -576,9 +579,9 @@ CSB_API int csb_sumsq(const void* g, int grad_fp32, long n, float* out, void* st
   return launch_result();
 }
 CSB_API int csb_clip_scale(const float* sumsq, float max_norm, float inv_loss_scale, float* scale_out,
-                           float* norm_out, int* skip, void* stream) {
+                           float* norm_out, int* skip, const int* status, void* stream) {
   clip_scale_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(sumsq, max_norm, inv_loss_scale, scale_out,
-                                                                          norm_out, skip);
+                                                                          norm_out, skip, status);
   return launch_result();
 }
 

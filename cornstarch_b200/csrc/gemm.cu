@@ -86,7 +86,7 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t phase, vol
       if (*abort_flag) return false;
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > CSB_WAIT_NS) return false;
+      else if (now - t0 > wait_limit_ns()) return false;
     }
   }
   return false;
@@ -120,7 +120,7 @@ __device__ __forceinline__ bool spin_until_ge(const int* addr, int target) {
     if ((i & 63u) == 63u) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > CSB_WAIT_NS) return false;
+      else if (now - t0 > wait_limit_ns()) return false;
     }
   }
   return false;
@@ -655,7 +655,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
   int grid = tiles < sm_count() ? tiles : sm_count();
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   GemmParams q = p;
-  static EpiMaps em;
+  EpiMaps em = {};  // filled per launch and passed by value: no state shared between host threads
   const int eb = q.out_fp32 ? 4 : 2;
   const int cps = 128 / eb;
   q.tma_epi = ((reinterpret_cast<uintptr_t>(q.C) & 15) == 0 && ((size_t)q.ldc * eb) % 16 == 0) ? 1 : 0;
@@ -777,3 +777,5 @@ CSB_API int csb_ar_layout(int M, int N, int world, int rank, int tile_n, int* ro
   *num_n_blocks = (N + bn - 1) / bn;
   return 0;
 }
+
+CSB_WAIT_LIMIT_SETTER(gemm)

@@ -95,3 +95,5 @@ CSB_API int csb_grad_reduce(void* const* bufs, int world, int rank, long n, floa
   grad_reduce_kernel<<<(unsigned)blocks, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   return launch_result();
 }
+
+CSB_WAIT_LIMIT_SETTER(grad_reduce)

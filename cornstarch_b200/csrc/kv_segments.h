@@ -73,7 +73,7 @@ __device__ __forceinline__ bool wait_peer_flag(const int* flag, int value) {
     if ((i & 63u) == 63u) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > CSB_WAIT_NS) return false;
+      else if (now - t0 > wait_limit_ns()) return false;
     }
   }
   return false;
@@ -89,7 +89,7 @@ __device__ __forceinline__ bool wait_local_count(const int* counter, int value) 
     if ((i & 63u) == 63u) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > CSB_WAIT_NS) return false;
+      else if (now - t0 > wait_limit_ns()) return false;
     }
   }
   return false;

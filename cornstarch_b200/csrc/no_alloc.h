@@ -10,7 +10,9 @@
 //
 //   out[c] (+)= sum over rows of x[r][c]        x: bf16 [rows][H] row-major, out: fp32 or bf16 [H]
 //
-// Limits: H must be a multiple of 8 and at most CSB_COLSUM_NOALLOC_MAX_H; any number of rows.
+// Limits: H must be a multiple of 8 and at most CSB_COLSUM_NOALLOC_MAX_H; any number of rows.  x must be
+// 16-byte aligned (it is read in 16-byte pieces; with H a multiple of 8 every row then is), out aligned
+// to its element size.  A misaligned pointer is refused with CSB_ERR_BAD_ARG (-1); nothing is launched.
 // Larger H is refused with CSB_ERR_TOO_LARGE (-4) and a message on stderr; nothing is launched.
 //
 // Things to know before using it:

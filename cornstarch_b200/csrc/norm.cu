@@ -369,9 +369,11 @@ CSB_API int csb_colsum_parts(int rows) {
 CSB_API int csb_colsum(const void* x, float* partial, void* out, int out_fp32, int accumulate, int rows, int H,
                        void* stream) {
   if (H % 8 != 0 || rows <= 0) return CSB_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0) return CSB_ERR_BAD_ARG;  // 16-byte loads
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int grid = csb_colsum_parts(rows);
   colsum_partial_kernel<<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(x), partial, rows, H);
+  if (int e = launch_result()) return e;
   reduce_partials_kernel<<<(H + 31) / 32, 256, 0, s>>>(partial, out, grid, H, out_fp32, accumulate);
   return launch_result();
 }

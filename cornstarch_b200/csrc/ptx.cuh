@@ -22,13 +22,22 @@ enum : int {
   ST_TIMEOUT_MISC = 6,
 };
 
-// Waits are bounded in wall time: after CSB_WAIT_NS nanoseconds a wait gives up.
+// Waits are bounded in wall time: after the wait limit (CSB_WAIT_NS nanoseconds unless csb_set_wait_ns changed it) a
+// wait gives up.  The limit lives in a device variable of each translation unit (no relocatable device code), read only
+// on the slow path of a spin; CSB_WAIT_LIMIT_SETTER(tu) defines the host function that updates this unit's copy on the
+// current device, and csb_set_wait_ns (symm.cu) calls all of them.
 #ifndef CSB_WAIT_NS
 #define CSB_WAIT_NS 2000000000ull
 #endif
 #ifndef CSB_SPIN_LIMIT
 #define CSB_SPIN_LIMIT (1u << 30)
 #endif
+static __device__ unsigned long long g_wait_ns = CSB_WAIT_NS;
+__device__ __forceinline__ uint64_t wait_limit_ns() { return *reinterpret_cast<volatile unsigned long long*>(&g_wait_ns); }
+#define CSB_WAIT_LIMIT_SETTER(tu)                                                  \
+  extern "C" int csb_set_wait_ns_##tu(unsigned long long ns) {                     \
+    return (int)cudaMemcpyToSymbol(csb::g_wait_ns, &ns, sizeof(ns));               \
+  }
 
 // 2^x on the special-function unit (one MUFU.EX2; -inf -> 0, flushes denormals).
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -97,7 +106,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t phase) {
     if ((i & 511u) == 511u) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > CSB_WAIT_NS) return false;
+      else if (now - t0 > wait_limit_ns()) return false;
     }
   }
   return false;
@@ -225,15 +234,6 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
-// 2-CTA commit: arrive on the barrier at this smem offset in every CTA of `cta_mask`
-// (a signal between the two SMs of a pair; no data is copied).
-__device__ __forceinline__ void umma_commit_2cta_mask(uint64_t* bar, uint16_t cta_mask) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-      ::"r"(smem_u32(bar)), "h"(cta_mask)
-      : "memory");
-}
-
 // TMEM -> registers, 32 lanes x 32 consecutive fp32 columns; thread i of the warp gets lane
 // (lane_base + i), register j holds column (col + j).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {

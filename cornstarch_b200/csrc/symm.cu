@@ -44,3 +44,18 @@ CSB_API int csb_ipc_import(const void* handle64, void** out) {
 }
 CSB_API int csb_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 CSB_API int csb_ipc_handle_size() { return (int)sizeof(cudaIpcMemHandle_t); }
+
+// Wait limit of every bounded device-side wait of this library on the CURRENT device, in nanoseconds (0 = back to the
+// built-in 2 s).  Stream-ordered with respect to nothing: call it while no kernel of this library is running.
+extern "C" int csb_set_wait_ns_attn_fwd(unsigned long long);
+extern "C" int csb_set_wait_ns_attn_bwd(unsigned long long);
+extern "C" int csb_set_wait_ns_gemm(unsigned long long);
+extern "C" int csb_set_wait_ns_grad_reduce(unsigned long long);
+CSB_API int csb_set_wait_ns(unsigned long long ns) {
+  if (ns == 0) ns = 2000000000ull;
+  int e;
+  if ((e = csb_set_wait_ns_attn_fwd(ns))) return e;
+  if ((e = csb_set_wait_ns_attn_bwd(ns))) return e;
+  if ((e = csb_set_wait_ns_gemm(ns))) return e;
+  return csb_set_wait_ns_grad_reduce(ns);
+}

@@ -523,8 +523,14 @@ class DecoderForCausalLM(PreTrainedModel):
                 result["loss"] = loss_sum / n_valid.clamp(min=1).to(loss_sum.dtype)
         if return_logits or (labels is None) or softcap:
             logits = linear(comm.reduce_backward(h, tp_group) if tp_group is not None else h, self.lm_head.weight)
-            if tp_group is not None and comm._world(tp_group) > 1 and not (self.pc and self.pc.parallel_output and labels is not None):
+            tp_sharded = tp_group is not None and comm._world(tp_group) > 1
+            # the soft-capped loss below is a plain cross-entropy over the whole vocabulary: gather the shards for it
+            keep_sharded = tp_sharded and bool(self.pc and self.pc.parallel_output and labels is not None) and not softcap
+            if tp_sharded and not keep_sharded:
                 logits = comm.gather_forward_split_backward(logits, logits.dim() - 1, tp_group)
+                full_v = getattr(self.lm_head, "full_vocab_size", None)
+                if full_v is not None and full_v < logits.shape[-1]:
+                    logits = logits[..., :full_v]  # drop the padding rows of the vocab-parallel shards
             if softcap:
                 logits = torch.tanh(logits / softcap) * softcap
                 if labels is not None:
@@ -532,11 +538,20 @@ class DecoderForCausalLM(PreTrainedModel):
                     if shift_labels:
                         tgt = torch.full_like(labels, -100)
                         tgt[:, :-1] = labels[:, 1:]
+                    if cp_state is not None and cp_state.mine is not None and tgt.shape[1] != h.shape[1]:
+                        tgt = tgt.index_select(1, cp_state.mine)
                     lf = logits.float().view(-1, logits.shape[-1])
                     loss_sum = torch.nn.functional.cross_entropy(lf, tgt.reshape(-1), ignore_index=-100, reduction="sum")
                     n_valid = (tgt != -100).sum()
-                    result["loss_sum"], result["num_valid"] = loss_sum, n_valid
-                    result["loss"] = loss_sum / n_valid.clamp(min=1)
+                    if cp_state is not None:
+                        total = n_valid.clone().float()
+                        torch.distributed.all_reduce(total, group=cp_state.group)
+                        sp = torch.distributed.get_world_size(cp_state.group)
+                        result["loss_sum"], result["num_valid"] = loss_sum, total
+                        result["loss"] = loss_sum * sp / total.clamp(min=1).to(loss_sum.dtype)
+                    else:
+                        result["loss_sum"], result["num_valid"] = loss_sum, n_valid
+                        result["loss"] = loss_sum / n_valid.clamp(min=1)
             result["logits"] = logits
         return result
 

@@ -38,7 +38,7 @@ _PROTOS = {
     "csb_adamw": [vp, vp, vp, vp, vp, i32, i64, f32, f32, f32, f32, f32, f32, f32, vp, vp, i32, vp],
     "csb_adamw_split": [vp, vp, vp, vp, vp, i32, i64, f32, f32, f32, f32, f32, f32, f32, vp, vp, i32, vp],
     "csb_sumsq": [vp, i32, i64, vp, vp],
-    "csb_clip_scale": [vp, f32, f32, vp, vp, vp, vp],
+    "csb_clip_scale": [vp, f32, f32, vp, vp, vp, vp, vp],
     "csb_ce_stats": [vp, i64, vp, i32, i32, vp, vp, vp, i64, vp],
     "csb_ce_grad": [vp, i64, vp, i32, i32, vp, vp, vp, vp, vp, i64, i64, vp],
     "csb_gather_merge": [vp, vp, vp, vp, i64, i32, vp],
@@ -162,10 +162,62 @@ def status_word(device: torch.device | None = None) -> torch.Tensor:
     return t
 
 
+def status_in_use(device: torch.device | None = None) -> bool:
+    """True once a kernel with bounded waits has been given this device's status word."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    return idx in _STATUS
+
+
+_STATUS_NAMES = {1: "TMA stage never arrived", 2: "shared-memory slot never came back", 3: "accumulator never became ready",
+                 4: "accumulator never drained", 5: "a peer's flag or counter never reached its value", 6: "internal hand-over"}
+
+
+def _raise_status(v: int, device) -> None:
+    status_word(device).zero_()
+    raise RuntimeError(f"a device-side bounded wait ran out (status {v}: {_STATUS_NAMES.get(v, 'unknown')}); "
+                       "the results of that step are incomplete; see csrc/ptx.cuh for codes")
+
+
 def check_status(device: torch.device | None = None) -> int:
     """Synchronising read of the status word (call it between steps, not per kernel)."""
     v = int(status_word(device).item())
     if v != 0:
-        status_word(device).zero_()
-        raise RuntimeError(f"a device-side bounded wait ran out (status {v}); see csrc/ptx.cuh for codes")
+        _raise_status(v, device)
     return v
+
+
+def set_wait_limit(seconds: float = 0.0) -> None:
+    """Limit of every bounded device-side wait of the library on the current device (0 = the built-in 2 s).  Call it
+    while no kernel of the library is running; tests use a few milliseconds to make a wait run out quickly."""
+    raw = lib()._raw
+    raw.csb_set_wait_ns.argtypes = [C.c_ulonglong]
+    raw.csb_set_wait_ns.restype = C.c_int
+    torch.cuda.synchronize()
+    check(raw.csb_set_wait_ns(int(seconds * 1e9)), "csb_set_wait_ns")
+
+
+_POLLS: dict[int, list] = {}
+
+
+def poll_status(device: torch.device | None = None) -> None:
+    """Check the status word WITHOUT synchronising: enqueue an asynchronous copy of it to pinned host memory and look
+    at the copies enqueued by earlier calls whose events have completed.  Called once per step by the optimizer and the
+    pipeline schedule, so a wait that ran out surfaces as an exception one step later at the latest (the optimizer has
+    already skipped the update of the affected step on the device, see ``csb_clip_scale``).  Does nothing until a
+    kernel with bounded waits has used the status word."""
+    if not status_in_use(device):
+        return
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    pending = _POLLS.setdefault(idx, [])
+    while pending and pending[0][1].query():
+        host, _ = pending.pop(0)
+        v = int(host[0])
+        if v != 0:
+            pending.clear()
+            _raise_status(v, device)
+    if len(pending) < 4:
+        host = torch.empty(1, dtype=torch.int32, pin_memory=True)
+        host.copy_(_STATUS[idx], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        pending.append((host, ev))

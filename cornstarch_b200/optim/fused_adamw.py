@@ -210,10 +210,15 @@ class FusedAdamW(torch.optim.Optimizer):
         here (no group, ZeRO-1 reduces inside ``step``, or the plain per-parameter path is in use)."""
         if not self.use_arena or self.dp_group is None or dist.get_world_size(self.dp_group) == 1 or self._sharded:
             return False
+        # gradients that autograd left in ``.grad`` (embedding lookups, norm weights behind a tensor-parallel reduction,
+        # sliced views, PyTorch fallbacks) must be part of what is averaged: fold them in before anything is reduced
+        folded = self._fold_stray_grads()
         bufs = self.flat_grads()
         if self.reducer is not None:
             if self._overlap is not None and self._overlap_used:
-                self._overlap.finish()  # part of the buffers was reduced during the backward pass
+                # part of the buffers was reduced during the backward pass; a range that a fold touched afterwards
+                # holds mean + local remainder and is averaged once more (the mean of that is the full mean)
+                self._overlap.finish(redo=self._spans_in_flat_grads(folded, bufs))
                 self._overlap_used = False
             else:
                 self.reducer.reduce(bufs)
@@ -227,13 +232,32 @@ class FusedAdamW(torch.optim.Optimizer):
     def flat_params(self) -> list[torch.Tensor]:
         return [r.flat_param for _, r in self._regions]
 
-    def _fold_stray_grads(self):
-        """Gradients autograd left in ``.grad`` (ops without main_grad fusion) are added to ``main_grad``."""
+    def _fold_stray_grads(self) -> list:
+        """Gradients autograd left in ``.grad`` (ops without main_grad fusion) are added to ``main_grad``.  Returns the
+        parameters that had one.  A parameter that had a stray gradient once is reported on every later call too, so
+        that all data-parallel ranks agree on the set even when one of them happens to see no gradient in a step."""
+        sticky = self.__dict__.setdefault("_stray_params", {})
         for _, r in self._regions:
             for p in r.params:
                 if p.grad is not None:
                     p.main_grad.add_(p.grad.to(p.main_grad.dtype))
                     p.grad = None
+                    sticky[id(p)] = p
+        return list(sticky.values())
+
+    @staticmethod
+    def _spans_in_flat_grads(params: list, bufs: list[torch.Tensor]) -> list[tuple[int, int, int]]:
+        """``(buffer index, lo, hi)`` element ranges (64-element aligned, as the arena lays parameters out) of the
+        ``main_grad`` views of ``params`` inside the flat gradient buffers ``bufs``."""
+        out = []
+        for p in params:
+            g = p.main_grad
+            for bi, flat in enumerate(bufs):
+                off = (g.data_ptr() - flat.data_ptr()) // flat.element_size()
+                if g.data_ptr() >= flat.data_ptr() and off < flat.numel():
+                    out.append((bi, off // ALIGN * ALIGN, min(flat.numel(), (off + g.numel() + ALIGN - 1) // ALIGN * ALIGN)))
+                    break
+        return sorted(out)
 
     def _step_arena(self):
         lib = nat.lib()
@@ -255,7 +279,10 @@ class FusedAdamW(torch.optim.Optimizer):
                     out = r.flat_grad[r.lo : r.hi]
                     dist.reduce_scatter_tensor(out, r.flat_grad, op=dist.ReduceOp.AVG, group=self.dp_group)
         inv_scale = 1.0 / self.loss_scale
-        need_norm = self.max_norm > 0 or self.loss_scale != 1.0
+        # kernels with bounded waits (peer-memory reductions, fused TP / CP / EP) report a wait that ran out in the
+        # device's status word; the update is then skipped on the device, and the host learns of it without a sync
+        gate = nat.status_word(self._sumsq.device) if nat.status_in_use(self._sumsq.device) else None
+        need_norm = self.max_norm > 0 or self.loss_scale != 1.0 or gate is not None
         if need_norm:
             self._sumsq.zero_()
             self._sumsq_expert.zero_()
@@ -275,7 +302,8 @@ class FusedAdamW(torch.optim.Optimizer):
                 if grp is not None and dist.get_world_size(grp) > 1:
                     dist.all_reduce(self._sumsq, group=grp)
             nat.check(lib.csb_clip_scale(self._sumsq.data_ptr(), float(self.max_norm), inv_scale, self._scale.data_ptr(),
-                                         self._norm.data_ptr(), self._skip.data_ptr(), st), "csb_clip_scale")
+                                         self._norm.data_ptr(), self._skip.data_ptr(), nat.ptr(gate), st), "csb_clip_scale")
+            nat.poll_status(self._sumsq.device)
         self._step += 1
         for g, r in self._regions:
             b1, b2 = g["betas"]

@@ -175,8 +175,12 @@ class OverlappedGradReduce:
             out.append((pos, numel))
         return out
 
-    def finish(self) -> None:
-        """Reduce every range no layer hook covered, then wait until all ranks' pushes have landed here."""
+    def finish(self, redo: list[tuple[int, int, int]] | None = None) -> None:
+        """Reduce every range no layer hook covered, then wait until all ranks' pushes have landed here.
+
+        ``redo``: ``(buffer, lo, hi)`` ranges that received a local contribution AFTER a hook may already have averaged
+        them (gradients folded in from ``.grad``).  Such a range holds mean + local part; averaging it once more gives
+        the full mean.  Ranges that fall into a gap are reduced once, by the gap."""
         r = self.reducer
         ev = torch.cuda.Event()
         ev.record()
@@ -184,8 +188,17 @@ class OverlappedGradReduce:
             self.side.wait_event(ev)
             saved, self.max_ctas = self.max_ctas, 0  # the backward pass is over: use the whole GPU
             for bi, flat in enumerate(self.flat_grads):
-                for lo, hi in self.gaps(self.done[bi], flat.numel()):
+                gaps = self.gaps(self.done[bi], flat.numel())
+                for lo, hi in gaps:
                     self._reduce_range(bi, lo, hi)
+                for rb, lo, hi in redo or []:
+                    if rb != bi:
+                        continue
+                    # the part of [lo, hi) that lies in hooked (already averaged) ranges
+                    for dlo, dhi in self.gaps(gaps, flat.numel()):
+                        a, b = max(lo, dlo), min(hi, dhi)
+                        if a < b:
+                            self._reduce_range(bi, a, b)
             self.max_ctas = saved
             lib, st = nat.lib(), nat.stream()
             status = nat.status_word(self.flat_grads[0].device)

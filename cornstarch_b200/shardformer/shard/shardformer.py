@@ -85,6 +85,15 @@ class ModelSharder:
         rules = [(re.compile(r.pattern), r) for r in self.policy.tp_rules]
         from ...models.text_legacy import Conv1D
 
+        # parameters that several modules share (tie_word_embeddings: embed_tokens.weight is lm_head.weight): each
+        # tensor-parallel layer below takes its own copy of its shard, so the ties are restored afterwards
+        owners: dict[int, list[tuple[str, str]]] = {}
+        for path, mod in self.model.named_modules():
+            for pn, prm in mod._parameters.items():
+                if prm is not None:
+                    owners.setdefault(id(prm), []).append((path, pn))
+        tied = [v for v in owners.values() if len(v) > 1]
+
         for path, mod in list(self.model.named_modules()):
             if isinstance(mod, Conv1D) and mod.parallel is None:
                 for rx, rule in rules:
@@ -111,6 +120,16 @@ class ModelSharder:
                     raise ValueError(rule.kind)
                 _set_submodule(self.model, path, new)
                 break
+        for group in tied:
+            # the vocabulary padding and the row split of the embedding and the LM head are identical, so the shards
+            # of a tied pair have the same shape and hold the same rows: one Parameter again
+            (path0, pn0), rest = group[0], group[1:]
+            first = _get_submodule(self.model, path0)._parameters.get(pn0) if path0 else self.model._parameters.get(pn0)
+            for path, pn in rest:
+                mod = _get_submodule(self.model, path) if path else self.model
+                other = mod._parameters.get(pn)
+                if first is not None and other is not None and other is not first and other.shape == first.shape:
+                    mod._parameters[pn] = first
         if self.policy.head_modules:
             rx = re.compile(self.policy.head_modules)
             for path, mod in self.model.named_modules():

@@ -98,3 +98,54 @@ def test_step_logger_json_lines(tmp_path):
     rows = [json.loads(x) for x in p.read_text().splitlines()]
     assert [r["step"] for r in rows] == [0, 1, 2] and rows[2]["loss"] < rows[0]["loss"]
     assert rows[0]["tokens_per_s"] > 0 and rows[0]["config"] == "unit"
+
+
+# ------------------------------------------------------------------------------------------------ on the device
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_device_wait_runs_out_sets_status_and_optimizer_skips():
+    """A bounded device-side wait really runs out: ``csb_cp_wait`` on a local counter that nothing advances, with the
+    wait limit set to a few milliseconds.  The kernel gives up by itself, stores ST_TIMEOUT_PEER_FLAG (5) in the status
+    word and returns; the context stays usable; the optimizer skips the update of that step on the device;
+    ``poll_status`` (no sync) and ``check_status`` (sync) raise."""
+    from cornstarch_b200.ops import _native as nat
+    from cornstarch_b200.optim.fused_adamw import FusedAdamW
+    from cornstarch_b200.parallel import cp_fused  # noqa: F401  (declares csb_cp_wait)
+
+    lib = nat.lib()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    st = nat.status_word(dev)
+    st.zero_()
+    w = torch.nn.Parameter(torch.randn(256, 64, device=dev).bfloat16())
+    opt = FusedAdamW([w], lr=1e-2, max_norm=1.0)
+    before = w.detach().clone()
+    w.main_grad.fill_(0.5)
+    nat.set_wait_limit(0.005)
+    try:
+        flags = torch.zeros(8, dtype=torch.int32, device=dev)  # counters of two "ranks"; nobody ever writes them
+        t0 = time.monotonic()
+        nat.check(lib.csb_cp_wait(flags.data_ptr(), 2, 1, st.data_ptr(), nat.stream()), "csb_cp_wait")
+        torch.cuda.synchronize()
+        assert time.monotonic() - t0 < 1.0  # gave up after ~5 ms, not after the built-in 2 s
+        assert int(st.item()) == 5
+        opt.step()  # reads the status word on the device: update skipped
+        torch.cuda.synchronize()
+        assert torch.equal(w.detach(), before)
+        with pytest.raises(RuntimeError, match="status 5"):
+            for _ in range(50):  # the asynchronous copy enqueued by step() completes within a few polls
+                nat.poll_status(dev)
+                time.sleep(0.01)
+        assert nat.check_status(dev) == 0  # cleared by the raise
+        # the context is intact: the next step updates the weights
+        nat._POLLS.clear()
+        w.main_grad.fill_(0.5)
+        opt.step()
+        torch.cuda.synchronize()
+        assert not torch.equal(w.detach(), before)
+        assert nat.check_status(dev) == 0
+    finally:
+        nat.set_wait_limit(0.0)
+        st.zero_()
+        nat._POLLS.clear()

@@ -83,3 +83,18 @@ def test_noalloc_colsum_refuses_oversized_width():
     rc = lib.csb_colsum_noalloc(x.data_ptr(), out.data_ptr(), 1, 0, 4, H, torch.cuda.current_stream().cuda_stream)
     assert rc == -4
     torch.cuda.synchronize()
+
+
+def test_noalloc_colsum_refuses_misaligned_input():
+    """x is read in 16-byte pieces: a pointer off that boundary (a sliced view handed over as a raw address) is
+    refused with CSB_ERR_BAD_ARG before anything is launched, instead of faulting on the GPU."""
+    lib = _lib()
+    H = 256
+    buf = torch.zeros(4 * H + 8, device="cuda", dtype=torch.bfloat16)
+    out = torch.full((H,), 7.0, device="cuda")
+    rc = lib.csb_colsum_noalloc(buf.data_ptr() + 2, out.data_ptr(), 1, 0, 4, H, torch.cuda.current_stream().cuda_stream)
+    assert rc == -1
+    rc = lib.csb_colsum_noalloc(buf.data_ptr(), out.data_ptr() + 2, 1, 0, 4, H, torch.cuda.current_stream().cuda_stream)
+    assert rc == -1
+    torch.cuda.synchronize()
+    assert bool((out == 7.0).all())  # nothing ran
