@@ -87,23 +87,89 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------ reference arm
+REF_CHAIN = ("cornstarch", "cornstarch.kernel.bitfield_attention", "cornstarch.kernel.attention",
+             "cornstarch.models.multimodal_language_model", "cornstarch.plugin.multimodal_parallel_plugin")
+
+
 def run_reference(args) -> None:
-    """The unmodified reference from baseline/_ref through its own public API, or the `unavailable` line."""
+    """The unmodified reference from baseline/_ref through its own public API, or the `unavailable` line.
+
+    The import chain of the reference is tried module by module and the first one that fails is reported.  The
+    end-to-end training metric needs the model layer and the plugin (colossalai, peft, timm and transformers-4.5x
+    internals, none of which is installed here), so that metric is `unavailable`; what the reference owns as GPU code -
+    its Triton attention kernels - imports with torch + triton alone and is timed on this GPU next to this package's
+    kernels (`reference_kernels`, rank 0 only), unmodified and through the reference's own `bitfield_attn_func`."""
     ref = os.path.join(REPO, "baseline", "_ref")
-    why = None
+    rank0 = int(os.environ.get("RANK", "0")) == 0
+    out = {"impl": "reference"}
     if not os.path.isdir(os.path.join(ref, "cornstarch")):
-        why = "baseline/_ref is empty (offline pip install of the reference was not possible)"
-    else:
-        sys.path.insert(0, ref)
+        out["unavailable"] = "baseline/_ref is empty (offline pip install of the reference was not possible)"
+        if rank0:
+            print(json.dumps(out))
+        return
+    sys.path.insert(0, ref)
+    import importlib
+
+    imported, first_fail = [], None
+    for mod in REF_CHAIN:
         try:
-            import cornstarch  # noqa: F401
-            from cornstarch.models.multimodal_language_model import MultimodalModel  # noqa: F401
-        except Exception as e:  # missing third-party packages of the reference
-            why = f"reference import fails offline: {type(e).__name__}: {e}".replace("\n", " ")[:200]
-    if why is None:
-        why = "reference imports but its plugins need colossalai 0.4.6 and transformers 4.5x internals, absent here"
-    if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+            importlib.import_module(mod)
+            imported.append(mod)
+        except Exception as e:  # missing third-party packages / removed transformers internals
+            first_fail = f"{mod}: {type(e).__name__}: {e}".replace("\n", " ")[:240]
+            break
+    out["imports_ok"] = imported
+    out["unavailable"] = ("end-to-end training through the reference's MultimodalModel + MultimodalParallelPlugin cannot run here: "
+                          + (f"first failing import {first_fail}" if first_fail else
+                             "the modules import but the plugin needs colossalai 0.4.6 and transformers 4.5x internals"))
+    if rank0 and "cornstarch.kernel.bitfield_attention" in imported and not args.no_ref_kernels:
+        try:
+            from cornstarch_b200.utils.reference_kernels import compare_attention
+
+            out["reference_kernels"] = compare_attention(quick=True)
+        except Exception as e:  # noqa: BLE001  (a Triton compile error on this GPU is a result, not a crash)
+            out["reference_kernels"] = {"error": f"{type(e).__name__}: {e}".replace("\n", " ")[:400]}
+    if rank0:
+        print(json.dumps(out))
+
+
+# ------------------------------------------------------------------------------------------------ library baseline arm
+def run_baseline_child(args, rank: int, world: int) -> dict | None:
+    """Run `bench.py --impl baseline` (same plan, same data, library kernels) as a child process of every rank BEFORE this
+    process touches the GPU, and return its JSON record (rank 0).  The children form their own process group on another
+    port; when they have exited, all of their memory is free again."""
+    env = dict(os.environ)
+    env.pop("TORCHELASTIC_USE_AGENT_STORE", None)  # the child group hosts its own store on its own port
+    env["MASTER_ADDR"] = "127.0.0.1"
+    env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29500")) + 23)
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "baseline", "--gpus", str(world), "--steps", str(args.baseline_steps),
+           "--warmup", "3", "--config", str(args.config), "--recompute", args.recompute, "--microbatch", str(args.microbatch)]
+    for flag, val, default in (("--shape", args.shape, None), ("--samples-per-gpu", args.samples_per_gpu, None),
+                               ("--parallelism", args.parallelism, None)):
+        cmd += [flag, str(val)]
+    try:
+        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=args.baseline_timeout)
+    except subprocess.TimeoutExpired:
+        return {"error": f"baseline arm did not finish within {args.baseline_timeout} s"} if rank == 0 else None
+    if rank != 0:
+        return None
+    rec = None
+    for line in res.stdout.splitlines():
+        line = line.strip()
+        if line.startswith("{") and '"metric"' in line:
+            try:
+                rec = json.loads(line)
+            except ValueError:
+                pass
+    if rec is None:
+        return {"error": f"baseline arm exited {res.returncode}: " + (res.stderr or res.stdout)[-300:].replace("\n", " ")}
+    keep = {k: rec.get(k) for k in ("value", "unit", "ms_per_step", "steps", "warmup", "e2e", "gpu_launches")}
+    keep["what"] = ("same models, plan, schedule and data with library kernels at every call site (cuBLAS, PyTorch SDPA / norms / "
+                    "cross-entropy, torch fused AdamW, NCCL): bench.py --impl baseline, run on this box right before the native steps")
+    keep["activation_checkpointing"] = rec.get("config", {}).get("activation_checkpointing")
+    keep["peak_memory_gb"] = rec.get("config", {}).get("peak_memory_gb")
+    keep["clocks"] = rec.get("clocks")
+    return keep
 
 
 # ------------------------------------------------------------------------------------------------ native arm
@@ -120,6 +186,10 @@ def parse_args():
     ap.add_argument("--microbatch", type=int, default=1)
     ap.add_argument("--parallelism", default="auto", help="auto | dp | e.g. 'pp4xtp2'")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-baseline", action="store_true", help="native arm: skip the library-baseline child run (vs_baseline stays null)")
+    ap.add_argument("--baseline-steps", type=int, default=5)
+    ap.add_argument("--baseline-timeout", type=int, default=420)
+    ap.add_argument("--no-ref-kernels", action="store_true", help="reference arm: skip timing the reference's Triton kernels")
     ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
                     help="benchmark configuration: 1 VLM (headline), 2 vision+audio VALM, 3 long-context CP, 4 MoE EP+ZeRO-1")
     args = ap.parse_args()
@@ -147,15 +217,18 @@ def main():
         # same models, plans and schedule with library kernels at every call site (cuBLAS GEMMs, PyTorch SDPA, PyTorch norms /
         # activations / cross-entropy, torch fused AdamW, NCCL collectives): the in-repo stand-in for the reference's stack
         os.environ["CORNSTARCH_B200_LIBRARY_OPS"] = "1"
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    baseline = None
+    if args.impl == "native" and not args.no_baseline:
+        baseline = run_baseline_child(args, rank, world)
     import torch
     import torch.distributed as dist
 
     from cornstarch_b200.bench_support import build_trainer
 
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
     torch.cuda.set_device(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
@@ -228,6 +301,24 @@ def main():
         dist.all_reduce(lc)
         launches = int(lc[0])
     nat.check_status()
+    peak_gb = torch.cuda.max_memory_allocated() / 2**30
+    checks = None
+    if world > 1:
+        pk = torch.tensor([peak_gb], device="cuda", dtype=torch.float64)
+        dist.all_reduce(pk, op=dist.ReduceOp.MAX)
+        peak_gb = float(pk[0])
+        # replicated parameters must agree bit for bit inside every data-parallel / tensor-parallel group
+        mine = trainer.checks() if hasattr(trainer, "checks") else {}
+        everyone = [None] * world
+        dist.all_gather_object(everyone, mine)
+        checks = {}
+        for c in everyone:
+            for k, v in (c or {}).items():
+                agg = checks.setdefault(k, {"ranks": v["ranks"], "params_compared": 0, "mismatched": 0})
+                agg["params_compared"] += v["params"]
+                agg["mismatched"] += v["mismatched"]
+        checks["ok"] = all(v["mismatched"] == 0 for v in checks.values() if isinstance(v, dict))
+        checks["last_loss_finite"] = bool(last is None or (last == last and abs(last) < 1e30))
     if world > 1:
         # report the clocks of the busiest GPU (pipeline stages differ a lot in load), with every rank's throttle reasons
         everyone = [None] * world
@@ -245,7 +336,8 @@ def main():
     if rank == 0:
         out = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": (value / baseline["value"]) if (baseline and baseline.get("value")) else None, "dtype": "bf16",
             "data": "synthetic (pixels ~N(0,1), token ids uniform), random-init weights",
             "config": {"model": trainer.model_name, "global_batch": trainer.global_batch, "seq_len": trainer.seq_len,
                        "parallelism": trainer.parallelism, "microbatch": args.microbatch,
@@ -253,9 +345,16 @@ def main():
                        "optimizer": ("fused AdamW, fp32 master weights (stored as bf16 parameter + 16-bit remainder) + fp32 moments, bf16 grads" if args.impl == "native"
                                      else "torch.optim.AdamW(fused=True) on bf16 parameters, clip_grad_norm_"),
                        "kernels": ("this package (sm_100a)" if args.impl == "native" else "library: cuBLAS, PyTorch SDPA, PyTorch elementwise, NCCL"), "activation_checkpointing": getattr(trainer, "recompute", "every layer"),
-                       "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 2**30, 1)},
+                       "peak_memory_gb": round(peak_gb, 1), "peak_memory_is": "max over ranks"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "impl": args.impl, "benchmark_config": args.config,
         }
+        if baseline is not None:
+            out["baseline"] = baseline
+            out["vs_baseline_is"] = "native value / library-baseline value measured in this run (the reference publishes no number)"
+            if e2e and isinstance(baseline.get("e2e"), dict) and baseline["e2e"].get("value"):
+                out["e2e"]["vs_baseline"] = e2e["value"] / baseline["e2e"]["value"]
+        if checks is not None:
+            out["checks"] = checks
         print(json.dumps(out))
     if nat.KERNEL_TIMES and rank == 0:
         # in-situ breakdown (CORNSTARCH_B200_KERNEL_TIMES=1): device time per native entry point since the process started

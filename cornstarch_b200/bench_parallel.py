@@ -85,6 +85,18 @@ class PipelineTrainer:
 
     recompute = "every layer"
 
+    def checks(self) -> dict:
+        """Agreement of replicated parameters inside this rank's data-parallel and tensor-parallel groups after the timed
+        steps; every rank reports, the values are combined over all ranks by the caller."""
+        from .bench_support import replica_checks
+        from .plugin.checkpoint_io import _tp_info
+
+        inner = getattr(self.model.module, self.model.my_modal_name)
+        tp = self.plugin.tp_group[0] if isinstance(self.plugin.tp_group, list) else self.plugin.tp_group
+        tp = tp if (tp is not None and dist.get_world_size(tp) > 1) else None
+        return replica_checks(list(inner.named_parameters()), dp_group=self.model.dp_group, tp_group=tp,
+                              tp_sharded=set(_tp_info(inner)))
+
     def tune_recompute(self):
         """Call after each of the first two steps: decoder layers that fit in the memory left over stop being recomputed (per stage; the
         tensor-parallel peers agree on the number)."""

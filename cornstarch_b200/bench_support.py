@@ -15,8 +15,43 @@ from .utils.recompute import RecomputeTuner, activation_bytes_per_layer, tune_re
 from .zoo import SHAPES, build_model, synthetic_batch
 
 
+def replica_checks(named_params, dp_group=None, tp_group=None, tp_sharded: set | None = None) -> dict:
+    """Bit-level agreement of parameters that must be identical on several ranks, after the timed steps.
+
+    Every parameter is reduced to a 64-bit checksum of its bit pattern (sum of its 16-bit words as integers) on the
+    device; the checksum vectors are gathered and compared.  ``dp``: all parameters over the data-parallel group;
+    ``tp_replicated``: the parameters that tensor parallelism does not shard (norm weights, biases of row-parallel
+    layers) over the tensor-parallel group.  Values: number of parameters compared and how many of them differ."""
+    named = [(n, p) for n, p in named_params if p is not None and p.numel() > 0]
+    out = {}
+
+    def sums(items):
+        if not items:
+            return torch.zeros(0, dtype=torch.int64, device="cuda" if torch.cuda.is_available() else "cpu")
+        return torch.stack([p.detach().contiguous().view(torch.int16 if p.element_size() == 2 else torch.int32)
+                            .to(torch.int64).sum() for _, p in items])
+
+    for key, group, items in (("dp", dp_group, named),
+                              ("tp_replicated", tp_group, [(n, p) for n, p in named if n not in (tp_sharded or set())])):
+        if group is None or dist.get_world_size(group) < 2:
+            continue
+        mine = sums(items)
+        everyone = [torch.empty_like(mine) for _ in range(dist.get_world_size(group))]
+        dist.all_gather(everyone, mine, group=group)
+        bad = int(sum((e != everyone[0]).sum() for e in everyone[1:]))
+        out[key] = {"ranks": dist.get_world_size(group), "params": len(items), "mismatched": bad}
+    return out
+
+
 class SingleDeviceTrainer:
     parallelism = "single"
+
+    def checks(self) -> dict:
+        """Replica agreement after the timed steps (see :func:`replica_checks`); expert-parallel parameters differ by design."""
+        if self.world < 2:
+            return {}
+        named = [(n, p) for n, p in self.model.named_parameters() if not getattr(p, "expert_parallel", False)]
+        return replica_checks(named, dp_group=self.dp_group)
 
     def __init__(self, shape: str, samples_per_step: int, microbatch: int, device, lr: float = 1e-4, seed: int = 0,
                  dp_group=None, mask_mode: str = "modality", dtype=torch.bfloat16):

@@ -27,9 +27,10 @@ _ALIASES = {
     **{f"cornstarch.models.multimodal_language_model.{m}": "cornstarch_b200.models.multimodal_language_model"
        for m in ("modeling_multimodal_language_model", "processing_multimodal_language_model",
                  "configuration_multimodal_language_model")},
+    **{f"cornstarch.models.{m}": "cornstarch_b200.models.evaclip"
+       for m in ("evaclip", "evaclip.modeling_evaclip", "evaclip.configuration_evaclip")},
     **{f"cornstarch.models.{m}": "cornstarch_b200.models.vision_extra"
-       for m in ("evaclip", "evaclip.modeling_evaclip", "evaclip.configuration_evaclip", "intern_vit",
-                 "intern_vit.modeling_intern_vit", "intern_vit.configuration_intern_vit")},
+       for m in ("intern_vit", "intern_vit.modeling_intern_vit", "intern_vit.configuration_intern_vit")},
     "cornstarch.kernel": "cornstarch_b200.kernel",
     "cornstarch.kernel.interface": "cornstarch_b200.kernel.interface",
     "cornstarch.kernel.bitfield_attention": "cornstarch_b200.kernel.bitfield_attention",

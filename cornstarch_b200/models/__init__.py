@@ -1,10 +1,10 @@
 """Model families with Hugging Face parameter names: ``llama`` (Llama, Mistral, Qwen2/3, Gemma 1-3, Phi3), ``moe`` (Mixtral,
-Qwen3-MoE), ``llama4``, ``text_legacy`` (GPT-2, BERT, OPT), ``vision`` (SigLIP, CLIP, ViT), ``vision_extra`` (DINOv2, EvaCLIP,
-InternViT, Pixtral, Qwen2-VL vision), ``whisper`` (Whisper, Qwen2-Audio encoders), ``phi4_audio``.  Every module registers its
+Qwen3-MoE), ``llama4``, ``text_legacy`` (GPT-2, BERT, OPT), ``vision`` (SigLIP, CLIP, ViT), ``vision_extra`` (DINOv2, EvaCLIP vision,
+InternViT, Pixtral, Qwen2-VL vision), ``evaclip`` (EvaCLIP text tower and joint model), ``whisper`` (Whisper, Qwen2-Audio encoders), ``phi4_audio``.  Every module registers its
 classes by ``model_type`` (the reference registers EvaCLIP and InternViT with the HF Auto classes,
 cornstarch/models/__init__.py:1-15); :class:`AutoModel` looks a checkpoint's ``model_type`` up there."""
 
-_FAMILY_MODULES = ("llama", "moe", "llama4", "text_legacy", "vision", "vision_extra", "whisper", "phi4_audio")
+_FAMILY_MODULES = ("llama", "moe", "llama4", "text_legacy", "vision", "vision_extra", "evaclip", "whisper", "phi4_audio")
 
 
 class AutoModel:

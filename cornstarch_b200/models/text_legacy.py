@@ -327,6 +327,7 @@ class BertModel(PreTrainedModel):
         self.encoder = _BertEncoder(config)
         self.pooler = _BertPooler(config) if add_pooling_layer else None
         self._has_pooler = add_pooling_layer
+        self.causal = bool(getattr(config, "is_decoder", False))  # BertLMHeadModel as a decoder attends causally
 
     @classmethod
     def module_names(cls, config, add_pooling_layer=True):
@@ -335,7 +336,7 @@ class BertModel(PreTrainedModel):
     def forward(self, input_ids=None, attention_mask=None, token_type_ids=None, hidden_states=None, **kw):
         if hidden_states is None:
             hidden_states = self.embeddings(input_ids, token_type_ids)
-        x = _run_layers(self.encoder.layer, hidden_states, _padding_mask(attention_mask, False),
+        x = _run_layers(self.encoder.layer, hidden_states, _padding_mask(attention_mask, self.causal),
                         self.gradient_checkpointing and self.training)
         last_held = not is_released(self.encoder.layer[-1])
         if not last_held:

@@ -70,37 +70,9 @@ class ModalParallelPlugin:
 
     def _configure_modal_module(self, modal: ModalModuleBase, sc: ShardConfig, former: ShardFormer, held: list[str] | None):
         """Encoder units are named ``module.<unit>``; the projector's ``projector.<unit>`` (last stage only)."""
-        import copy
+        from ..shardformer.policies.multimodal import ModalModulePolicy
 
-        enc_held = None if held is None else [h[len("module."):] for h in held if h.startswith("module.")]
-        proj_held = None if held is None else [h for h in held if h.startswith("projector.")]
-        enc_sc = copy.copy(sc)
-        if enc_held is not None:
-            enc_sc.pipeline_stage_manager = _FixedHeld(enc_held)
-            enc_sc.pipeline_template = None
-        ShardFormer(enc_sc).optimize(modal.module, policy_for_model(modal.module))
-        if modal.projector is not None:
-            if proj_held is not None and not proj_held:
-                modal.projector = None  # the projector lives on the encoder's last stage only
-            else:
-                proj_sc = copy.copy(sc)
-                proj_sc.pipeline_stage_manager = None
-                proj_sc.pipeline_template = None
-                proj_sc.enable_sequence_parallelism = False
-                proj_sc.sequence_parallelism_mode = None
-                ShardFormer(proj_sc).optimize(modal.projector, policy_for_model(modal.projector))
-                if sc.enable_sequence_parallelism and sc.sequence_parallel_size > 1:
-                    from ..parallel.comm import gather_forward_split_backward
-
-                    sp_group, sp = sc.sequence_parallel_process_group, sc.sequence_parallel_size
-                    modal.projector.post_projection = lambda x: gather_forward_split_backward(x, 1, sp_group, float(sp))
-
-
-class _FixedHeld:
-    """Minimal stage-manager stand-in that reports a fixed list of held units."""
-
-    def __init__(self, names):
-        self._names = list(names)
-
-    def held_module_names(self):
-        return self._names
+        pol = ModalModulePolicy()
+        pol.set_model(modal)
+        pol.set_shard_config(sc)
+        pol.shard(sc, held)

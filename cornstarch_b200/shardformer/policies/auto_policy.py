@@ -8,6 +8,14 @@ reference registers (cornstarch/shardformer/policies/auto_policy.py:12-248), so 
 from __future__ import annotations
 
 from . import models as P
+from .multimodal import ModalModulePolicy
+
+# task-head classes whose policy is named <class>Policy, here and (as transformers.models.<family>.modeling_<family>.<class>)
+# in the reference's registry
+_HEADS = ("BertForPreTraining", "BertLMHeadModel", "BertForSequenceClassification", "BertForTokenClassification",
+          "BertForNextSentencePrediction", "BertForMultipleChoice", "BertForQuestionAnswering", "GPT2DoubleHeadsModel",
+          "GPT2ForQuestionAnswering", "GPT2ForTokenClassification", "GPT2ForSequenceClassification",
+          "OPTForSequenceClassification", "OPTForQuestionAnswering")
 
 _NATIVE = {
     "cornstarch_b200.models.llama.DecoderModel": P.DecoderModelPolicy,
@@ -33,6 +41,12 @@ _NATIVE = {
     "cornstarch_b200.models.text_legacy.BertForMaskedLM": P.BertForMaskedLMPolicy,
     "cornstarch_b200.models.text_legacy.OPTModel": P.OPTModelPolicy,
     "cornstarch_b200.models.text_legacy.OPTForCausalLM": P.OPTForCausalLMPolicy,
+    "cornstarch_b200.multimodal.modeling.ModalEncoderModule": ModalModulePolicy,
+    "cornstarch_b200.multimodal.modeling.ModalDecoderModule": ModalModulePolicy,
+    "cornstarch_b200.models.task_heads.DecoderForSequenceClassification": P.DecoderForSequenceClassificationPolicy,
+    "cornstarch_b200.models.task_heads.Dinov2Backbone": P.Dinov2BackbonePolicy,
+    "cornstarch_b200.models.task_heads.Dinov2ForImageClassification": P.Dinov2ForImageClassificationPolicy,
+    **{f"cornstarch_b200.models.task_heads.{n}": getattr(P, n + "Policy") for n in _HEADS},
 }
 
 
@@ -72,6 +86,14 @@ _HF_ALIASES.update({
     "transformers.models.bert.modeling_bert.BertForMaskedLM": P.BertForMaskedLMPolicy,
     "transformers.models.opt.modeling_opt.OPTModel": P.OPTModelPolicy,
     "transformers.models.opt.modeling_opt.OPTForCausalLM": P.OPTForCausalLMPolicy,
+    **{f"transformers.models.{n[:4].lower().rstrip('f')}.modeling_{n[:4].lower().rstrip('f')}.{n}": getattr(P, n + "Policy") for n in _HEADS},
+    "transformers.models.llama.modeling_llama.LlamaForSequenceClassification": P.DecoderForSequenceClassificationPolicy,
+    "transformers.models.dinov2.modeling_dinov2.Dinov2Backbone": P.Dinov2BackbonePolicy,
+    "transformers.models.dinov2.modeling_dinov2.Dinov2ForImageClassification": P.Dinov2ForImageClassificationPolicy,
+    # the language model of Qwen2-VL is a Qwen2 decoder (the reference maps the class to its Qwen2 causal-LM policy)
+    "transformers.models.qwen2_vl.modeling_qwen2_vl.Qwen2VLForConditionalGeneration": P.DecoderForCausalLMPolicy,
+    "cornstarch.models.multimodal_language_model.modeling_multimodal_language_model.ModalEncoderModule": ModalModulePolicy,
+    "cornstarch.models.multimodal_language_model.modeling_multimodal_language_model.ModalDecoderModule": ModalModulePolicy,
 })
 
 _POLICY_LIST = {**_NATIVE, **_HF_ALIASES}

@@ -2,7 +2,24 @@
 cornstarch/shardformer/policies/<family>.py).  The decoder families share one implementation here: the differences between
 them are in the model's spec, not in how it is sharded."""
 
+from .multimodal import ModalModulePolicy  # noqa: F401
 from .models import (  # noqa: F401
+    BertForMultipleChoicePolicy,
+    BertForNextSentencePredictionPolicy,
+    BertForPreTrainingPolicy,
+    BertForQuestionAnsweringPolicy,
+    BertForSequenceClassificationPolicy,
+    BertForTokenClassificationPolicy,
+    BertLMHeadModelPolicy,
+    DecoderForSequenceClassificationPolicy,
+    Dinov2BackbonePolicy,
+    Dinov2ForImageClassificationPolicy,
+    GPT2DoubleHeadsModelPolicy,
+    GPT2ForQuestionAnsweringPolicy,
+    GPT2ForSequenceClassificationPolicy,
+    GPT2ForTokenClassificationPolicy,
+    OPTForQuestionAnsweringPolicy,
+    OPTForSequenceClassificationPolicy,
     BertForMaskedLMPolicy,
     BertModelPolicy,
     CLIPVisionModelPolicy,
@@ -43,3 +60,4 @@ GPT2Policy = GPT2ModelPolicy
 BertPolicy = BertModelPolicy
 OPTPolicy = OPTModelPolicy
 Phi4MultimodalAudioPolicy = Phi4MultimodalAudioModelPolicy
+LlamaForSequenceClassificationPolicy = DecoderForSequenceClassificationPolicy

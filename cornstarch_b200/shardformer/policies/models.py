@@ -11,6 +11,7 @@ from __future__ import annotations
 from ...models import llama as L
 from ...models import llama4 as L4
 from ...models import phi4_audio as PA
+from ...models import task_heads as H
 from ...models import text_legacy as T
 from ...models import vision_extra as X
 from ...models import moe as M
@@ -350,3 +351,91 @@ class Phi4MultimodalAudioModelPolicy(ModelPolicy):
     def split_sizes(self, path, module):
         I = self.model.config.intermediate_size
         return [I, I] if path.endswith("gate_up_proj") else None
+
+
+# ------------------------------------------------------------------------------------------------ task heads
+# Pipeline units of the head classes: the backbone's units under its prefix plus the head units, which must sit on the
+# last stage (cornstarch/shardformer/policies/bert.py:106-260, gpt2.py:97-180, opt.py:99-135, dinov2.py:254-259).
+class BertForPreTrainingPolicy(BertModelPolicy):
+    model_cls = H.BertForPreTraining
+    first_stage_modules = ["bert.embeddings"]
+    last_stage_modules = ["cls"]
+
+
+class BertLMHeadModelPolicy(BertForPreTrainingPolicy):
+    model_cls = H.BertLMHeadModel
+
+
+class BertForNextSentencePredictionPolicy(BertForPreTrainingPolicy):
+    model_cls = H.BertForNextSentencePrediction
+
+
+class BertForSequenceClassificationPolicy(BertModelPolicy):
+    model_cls = H.BertForSequenceClassification
+    first_stage_modules = ["bert.embeddings"]
+    last_stage_modules = ["dropout", "classifier"]
+
+
+class BertForTokenClassificationPolicy(BertForSequenceClassificationPolicy):
+    model_cls = H.BertForTokenClassification
+
+
+class BertForMultipleChoicePolicy(BertForSequenceClassificationPolicy):
+    model_cls = H.BertForMultipleChoice
+
+
+class BertForQuestionAnsweringPolicy(BertModelPolicy):
+    model_cls = H.BertForQuestionAnswering
+    first_stage_modules = ["bert.embeddings"]
+    last_stage_modules = ["qa_outputs"]
+
+
+class GPT2DoubleHeadsModelPolicy(GPT2LMHeadModelPolicy):
+    model_cls = H.GPT2DoubleHeadsModel
+    last_stage_modules = ["transformer.ln_f", "lm_head", "multiple_choice_head"]
+
+
+class GPT2ForQuestionAnsweringPolicy(GPT2ModelPolicy):
+    model_cls = H.GPT2ForQuestionAnswering
+    first_stage_modules = ["transformer.wte", "transformer.wpe", "transformer.drop"]
+    last_stage_modules = ["transformer.ln_f", "qa_outputs"]
+
+
+class GPT2ForTokenClassificationPolicy(GPT2ForQuestionAnsweringPolicy):
+    model_cls = H.GPT2ForTokenClassification
+    last_stage_modules = ["transformer.ln_f", "dropout", "classifier"]
+
+
+class GPT2ForSequenceClassificationPolicy(GPT2ForQuestionAnsweringPolicy):
+    model_cls = H.GPT2ForSequenceClassification
+    last_stage_modules = ["transformer.ln_f", "score"]
+
+
+class OPTForSequenceClassificationPolicy(OPTForCausalLMPolicy):
+    model_cls = H.OPTForSequenceClassification
+    last_stage_modules = ["model.decoder.final_layer_norm", "model.decoder.project_out", "score"]
+
+
+class OPTForQuestionAnsweringPolicy(OPTForCausalLMPolicy):
+    model_cls = H.OPTForQuestionAnswering
+    last_stage_modules = ["model.decoder.final_layer_norm", "model.decoder.project_out", "qa_outputs"]
+
+
+class DecoderForSequenceClassificationPolicy(DecoderModelPolicy):
+    """``LlamaForSequenceClassification``: the decoder's units under ``model.`` plus ``score`` on the last stage."""
+
+    model_cls = H.DecoderForSequenceClassification
+    first_stage_modules = ["model.embed_tokens", "model.rotary_emb", "model.rotary_emb_local"]
+    last_stage_modules = ["model.norm", "score"]
+
+
+class Dinov2BackbonePolicy(Dinov2ModelPolicy):
+    model_cls = H.Dinov2Backbone
+
+
+class Dinov2ForImageClassificationPolicy(Dinov2ModelPolicy):
+    model_cls = H.Dinov2ForImageClassification
+    first_stage_modules = ["dinov2.embeddings"]
+    last_stage_modules = ["dinov2.layernorm", "classifier"]
+    head_modules = r"dinov2\.encoder\.layer\.\d+"
+    tp_rules = [TPRule(r"dinov2\." + r.pattern, r.kind, r.split_sizes_attr) for r in Dinov2ModelPolicy.tp_rules]

@@ -216,6 +216,12 @@ class ShardFormer:
             from ..policies.auto_policy import policy_for_model
 
             policy = policy_for_model(model)
+        if getattr(policy, "is_modal_module_policy", False):
+            # a modality wrapper (encoder / decoder + projector): its parts are sharded by their own policies
+            policy.set_model(model)
+            policy.set_shard_config(self.shard_config)
+            policy.shard(self.shard_config)
+            return model, []
         sharder = ModelSharder(model, policy, self.shard_config)
         shared = sharder.shard()
         model._sharder_placeholders = sharder.placeholders
