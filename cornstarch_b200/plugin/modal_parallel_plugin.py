@@ -76,3 +76,6 @@ class ModalParallelPlugin:
         pol.set_model(modal)
         pol.set_shard_config(sc)
         pol.shard(sc, held)
+
+
+from ..shardformer.policies.multimodal import _FixedHeld  # noqa: E402,F401  (used by the colocated plugin)
