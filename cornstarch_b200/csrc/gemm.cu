@@ -15,8 +15,14 @@
 //
 // This file replaces the cuBLAS calls behind nn.Linear / Linear1D_Col / Linear1D_Row in the
 // reference (cornstarch/shardformer/policies/llama.py:192-249).
+#include <stdlib.h>
+
 #include "host.h"
 #include "ptx.cuh"
+
+#ifndef CSB_GEMM_DEFAULT_CG
+#define CSB_GEMM_DEFAULT_CG 1
+#endif
 
 namespace csb {
 
@@ -64,12 +70,15 @@ __host__ __device__ __forceinline__ int ar_owner(int m_blk, int num_m, int world
   return o;
 }
 
-template <int BN>
+// CG = CTAs per MMA (tcgen05 cta_group): 1 = every thread block computes its own 128 x BN tile; 2 = a cluster of two
+// thread blocks computes one 256 x BN tile: each block stages its own 128 rows of A and HALF of the B tile (BN / 2
+// rows), the leader block issues the MMAs, which read both blocks' shared memory and write both blocks' tensor memory.
+template <int BN, int CG = 1>
 struct SmemLayout {
   static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int B_BYTES = (BN / CG) * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int STAGES = (CG == 2) ? 6 : ((BN == 256) ? 4 : 6);
   static constexpr int EPI_OFFSET = STAGES * STAGE_BYTES;  // two 16 KB output slabs (128 rows x 128 B, swizzled)
   static constexpr int EPI_SLAB_BYTES = 128 * 128;
   static constexpr int BAR_OFFSET = EPI_OFFSET + 2 * EPI_SLAB_BYTES;
@@ -153,11 +162,17 @@ struct EpiMaps {
 // Epilogue of one tile through shared memory: every thread owns one accumulator row; 128-byte row pieces
 // (64 bf16 or 32 fp32 columns) are staged in a swizzled slab and written with ONE TMA store per slab and
 // destination, so global and NVLink writes are full 128-byte lines.  `accumulate` uses the TMA reduce-add.
-template <int BN>
+// Arrive on an accumulator-drained barrier: the block's own, or (second block of a pair) the leader's.
+__device__ __forceinline__ void arrive_tmem_empty(uint64_t* bar, bool remote_leader) {
+  if (remote_leader) mbar_arrive_cluster(bar, 0);
+  else mbar_arrive(bar);
+}
+
+template <int BN, int EPI_OFF_BYTES_SLAB = 128 * 128>
 __device__ __forceinline__ void epilogue_tile_tma(const GemmParams& p, const EpiMaps& maps, uint8_t* epi_smem,
                                                   uint32_t t_row, int m_blk, int n_blk, int quarter, int lane, int warp,
                                                   uint32_t& slab_ctr, uint64_t* tmem_empty_bar, bool ar, int owner,
-                                                  bool mine) {
+                                                  bool mine, bool remote_leader = false) {
   const int r = quarter * 32 + lane;
   const int row = m_blk * BM + r;
   const bool e0 = (warp == 2 && lane == 0);
@@ -182,7 +197,7 @@ __device__ __forceinline__ void epilogue_tile_tma(const GemmParams& p, const Epi
     }
     if (last) {
       tc_fence_before();
-      mbar_arrive(tmem_empty_bar);  // the accumulator buffer can be overwritten by the next tile's MMAs
+      arrive_tmem_empty(tmem_empty_bar, remote_leader);  // the accumulator buffer can be overwritten by the next tile's MMAs
     }
     if (p.bias) {
       const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(p.bias) + col0;
@@ -221,7 +236,7 @@ __device__ __forceinline__ void epilogue_tile_tma(const GemmParams& p, const Epi
         }
       }
     }
-    uint8_t* buf = epi_smem + (slab_ctr & 1) * SmemLayout<BN>::EPI_SLAB_BYTES;
+    uint8_t* buf = epi_smem + (slab_ctr & 1) * EPI_OFF_BYTES_SLAB;
     if (e0) tma_store_wait_read<1>();  // the store that last used this slab has finished reading it
     asm volatile("bar.sync 2, 128;" ::: "memory");
     if (p.out_fp32) {
@@ -281,11 +296,12 @@ __device__ __forceinline__ void epilogue_tile_tma(const GemmParams& p, const Epi
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int CG>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ EpiMaps epi_maps, const GemmParams p) {
-  using L = SmemLayout<BN>;
+  using L = SmemLayout<BN, CG>;
+  constexpr int BNH = BN / CG;  // rows of B this thread block stages
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::BAR_OFFSET);
@@ -297,7 +313,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  // A pair of thread blocks (CG == 2) walks the tiles together: `unit` rows of 128 * CG; block `cta_rank` of the pair
+  // owns rows [cta_rank * 128, +128) of a tile and rows [cta_rank * BNH, +BNH) of the B tile.
+  const int cta_rank = CG == 2 ? (int)cluster_ctarank() : 0;
+  const bool leader = cta_rank == 0;
+  const int num_m_units = (p.num_m_blocks + CG - 1) / CG;
+  const int num_tiles = num_m_units * p.num_n_blocks;
+  const int work_first = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int work_step = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   const int rot = p.ar_world > 1 ? ar_range_start((p.ar_rank + 1) % p.ar_world, p.num_m_blocks, p.ar_world) : 0;
 
   if (threadIdx.x == 0) {
@@ -307,7 +330,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tmem_full[i], 1);
-      mbar_init(&tmem_empty[i], 128);
+      mbar_init(&tmem_empty[i], 128 * CG);  // CG == 2: the epilogue threads of both blocks arrive on the leader's barrier
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -317,11 +340,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     tma_prefetch_desc(&tma_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_addr_slot, 2 * BN);
-    tmem_relinquish();
+    if constexpr (CG == 2) {
+      tmem_alloc_2cta(tmem_addr_slot, 2 * BN);  // the same warp of both blocks: the columns are allocated in both
+      tmem_relinquish_2cta();
+    } else {
+      tmem_alloc(tmem_addr_slot, 2 * BN);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // the peer's barriers are initialised before anything signals them
+  else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_addr_slot;
 
@@ -330,9 +359,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      // CG == 2: both blocks' loads report their bytes to the LEADER's barrier (its address in the cluster window is
+      // this block's address with the pair bit cleared); only the leader announces the expected byte count
+      constexpr uint32_t LEADER_MASK = CG == 2 ? 0xFEFFFFFFu : 0xFFFFFFFFu;
+      for (int tile = work_first; tile < num_tiles && ok; tile += work_step) {
         int m_blk, n_blk;
-        tile_coords_rot(tile, p.num_m_blocks, p.num_n_blocks, rot, m_blk, n_blk);
+        tile_coords_rot(tile, num_m_units, p.num_n_blocks, rot, m_blk, n_blk);
+        m_blk = m_blk * CG + cta_rank;
+        const int n_row0 = n_blk * BN + cta_rank * BNH;
         for (int kb = 0; kb < p.num_k_blocks; ++kb, ++it) {
           const int s = it % L::STAGES;
           const uint32_t ph = (it / L::STAGES) & 1;
@@ -344,20 +378,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           }
           uint8_t* sa = smem + s * L::STAGE_BYTES;
           uint8_t* sb = sa + L::A_BYTES;
-          mbar_expect_tx(&full_bar[s], L::STAGE_BYTES);
+          const uint32_t full_addr_s = smem_u32(&full_bar[s]) & LEADER_MASK;
+          if (leader) mbar_expect_tx(&full_bar[s], L::STAGE_BYTES * CG);
           if constexpr (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d(sa + j * (64 * BK * 2), &tma_a, &full_bar[s], m_blk * BM + j * 64, kb * BK);
+              tma_load_2d_to<CG>(sa + j * (64 * BK * 2), &tma_a, full_addr_s, m_blk * BM + j * 64, kb * BK);
           } else {
-            tma_load_2d(sa, &tma_a, &full_bar[s], kb * BK, m_blk * BM);
+            tma_load_2d_to<CG>(sa, &tma_a, full_addr_s, kb * BK, m_blk * BM);
           }
           if constexpr (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (64 * BK * 2), &tma_b, &full_bar[s], n_blk * BN + j * 64, kb * BK);
+            for (int j = 0; j < BNH / 64; ++j)
+              tma_load_2d_to<CG>(sb + j * (64 * BK * 2), &tma_b, full_addr_s, n_row0 + j * 64, kb * BK);
           } else {
-            tma_load_2d(sb, &tma_b, &full_bar[s], kb * BK, n_blk * BN);
+            tma_load_2d_to<CG>(sb, &tma_b, full_addr_s, kb * BK, n_row0);
           }
         }
       }
@@ -365,12 +400,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM * CG, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t it = 0;
       uint32_t local_tile = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+      for (int tile = work_first; tile < num_tiles && ok; tile += work_step, ++local_tile) {
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!wait_or_abort(&tmem_empty[acc], acc_ph ^ 1, abort_flag)) {
@@ -399,11 +434,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             // K-major: 16 elements = 32 bytes along the swizzled row; MN-major: 16 rows of 128 bytes.
             const uint64_t a_adv = A_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : (uint64_t)((k * UMMA_K * 2) >> 4);
             const uint64_t b_adv = B_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : (uint64_t)((k * UMMA_K * 2) >> 4);
-            umma_f16(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (CG == 2) umma_f16_2cta(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else umma_f16(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit(&empty_bar[s]);  // smem slot is free once these MMAs retire
+          umma_commit_cg<CG>(&empty_bar[s]);  // smem slot (of both blocks) is free once these MMAs retire
         }
-        if (ok) umma_commit(&tmem_full[acc]);
+        if (ok) umma_commit_cg<CG>(&tmem_full[acc]);
       }
     }
     __syncwarp();
@@ -413,9 +449,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t local_tile = 0;
     uint32_t slab_ctr = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+    for (int tile = work_first; tile < num_tiles && ok; tile += work_step, ++local_tile) {
       int m_blk, n_blk;
-      tile_coords_rot(tile, p.num_m_blocks, p.num_n_blocks, rot, m_blk, n_blk);
+      tile_coords_rot(tile, num_m_units, p.num_n_blocks, rot, m_blk, n_blk);
+      m_blk = m_blk * CG + cta_rank;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
       if (!wait_or_abort(&tmem_full[acc], acc_ph, abort_flag)) {
@@ -438,8 +475,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             arrived = spin_until_ge(p.ar_cnt_part[p.ar_rank] + lane * AR_MAX_ROWS + m_blk, p.ar_base + p.num_n_blocks);
           if (!__all_sync(0xffffffffu, arrived) && lane == 0) atomicExch(p.status, ST_TIMEOUT_PEER_FLAG);
         }
-        epilogue_tile_tma<BN>(p, epi_maps, smem + L::EPI_OFFSET, t_row, m_blk, n_blk, quarter, lane, warp, slab_ctr,
-                              &tmem_empty[acc], ar, owner, mine);
+        epilogue_tile_tma<BN, L::EPI_SLAB_BYTES>(p, epi_maps, smem + L::EPI_OFFSET, t_row, m_blk, n_blk, quarter, lane, warp, slab_ctr,
+                                                 &tmem_empty[acc], ar, owner, mine, !leader);
         continue;
       }
       if (mine) {
@@ -587,7 +624,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         }
       }
       tc_fence_before();
-      mbar_arrive(&tmem_empty[acc]);
+      arrive_tmem_empty(&tmem_empty[acc], !leader);
       if (ar) {
         // all 128 epilogue threads have issued their stores for this tile: make them visible, then count the tile
         asm volatile("bar.sync 2, 128;" ::: "memory");
@@ -621,14 +658,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   // ------------------------------------------------------------------ teardown
   tc_fence_before();
-  __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();  // both blocks are done with tensor memory and with each other's barriers
+  else __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    if constexpr (CG == 2) tmem_dealloc_2cta(tmem_base, 2 * BN);
+    else tmem_dealloc(tmem_base, 2 * BN);
   }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int CG = 1>
 static int launch_gemm(const void* A, const void* B, const GemmParams& p, int lda, int ldb, int max_ctas,
                        cudaStream_t stream) {
   CUtensorMap ta, tb;
@@ -641,19 +680,20 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
   if (B_MN)
     r = make_tmap_2d_bf16(&tb, B, p.K, p.N, ldb, 64, BK);
   else
-    r = make_tmap_2d_bf16(&tb, B, p.N, p.K, ldb, BK, BN);
+    r = make_tmap_2d_bf16(&tb, B, p.N, p.K, ldb, BK, BN / CG);
   if (r) return r;
-  using L = SmemLayout<BN>;
-  auto kfn = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  using L = SmemLayout<BN, CG>;
+  auto kfn = gemm_bf16_kernel<BN, A_MN, B_MN, CG>;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN_BYTES);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  int tiles = p.num_m_blocks * p.num_n_blocks;
-  int grid = tiles < sm_count() ? tiles : sm_count();
-  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  int tiles = ((p.num_m_blocks + CG - 1) / CG) * p.num_n_blocks;
+  int grid = tiles < sm_count() / CG ? tiles : sm_count() / CG;  // thread blocks (CG == 1) or pairs (CG == 2)
+  if (max_ctas > 0 && grid > max_ctas / CG) grid = max_ctas / CG > 0 ? max_ctas / CG : 1;
+  grid *= CG;
   GemmParams q = p;
   EpiMaps em = {};  // filled per launch and passed by value: no state shared between host threads
   const int eb = q.out_fp32 ? 4 : 2;
@@ -670,8 +710,29 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
       if (r) return r;
     }
   }
-  kfn<<<grid, 192, L::DYN_BYTES, stream>>>(ta, tb, em, q);
-  return launch_result();
+  if constexpr (CG == 2) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = L::DYN_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, ta, tb, em, q);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "[cornstarch_b200] cluster launch of the GEMM failed: %s\n", cudaGetErrorString(e));
+      return (int)e;
+    }
+    return launch_result();
+  } else {
+    kfn<<<grid, 192, L::DYN_BYTES, stream>>>(ta, tb, em, q);
+    return launch_result();
+  }
 }
 
 }  // namespace csb
@@ -713,6 +774,16 @@ CSB_API int csb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   if (!a_mn_major && b_mn_major) return launch_gemm<BNV, false, true>(A, B, p, lda, ldb, max_ctas, s);   \
   if (a_mn_major && !b_mn_major) return launch_gemm<BNV, true, false>(A, B, p, lda, ldb, max_ctas, s);   \
   return launch_gemm<BNV, true, true>(A, B, p, lda, ldb, max_ctas, s);
+  // Pairs of thread blocks on one 256 x 256 tile (cta_group::2) when the problem has at least two tile rows and the
+  // caller did not restrict the number of thread blocks (a restricted launch shares the GPU with another kernel).
+  static const int cg_env = []() { const char* e = getenv("CORNSTARCH_B200_GEMM_CG"); return e ? atoi(e) : 0; }();
+  const int cg = (cg_env == 1 || cg_env == 2) ? cg_env : CSB_GEMM_DEFAULT_CG;
+  if (bn == 256 && cg == 2 && p.num_m_blocks >= 2 && max_ctas <= 0) {
+    if (!a_mn_major && !b_mn_major) return launch_gemm<256, false, false, 2>(A, B, p, lda, ldb, 0, s);
+    if (!a_mn_major && b_mn_major) return launch_gemm<256, false, true, 2>(A, B, p, lda, ldb, 0, s);
+    if (a_mn_major && !b_mn_major) return launch_gemm<256, true, false, 2>(A, B, p, lda, ldb, 0, s);
+    return launch_gemm<256, true, true, 2>(A, B, p, lda, ldb, 0, s);
+  }
   if (bn == 256) { CSB_DISPATCH(256) }
   CSB_DISPATCH(128)
 #undef CSB_DISPATCH

@@ -56,6 +56,7 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+__device__ __forceinline__ uint32_t cluster_ctarank();
 __device__ __forceinline__ uint32_t elect_one() {
   uint32_t pred = 0;
   asm volatile(
@@ -141,6 +142,24 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
       " [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
+}
+// 2-D tiled load whose completion is reported to the mbarrier at `bar_addr`, a shared::cluster address.  CG == 2: the
+// barrier may belong to the other thread block of a CTA pair (the data still lands in this block's shared memory).
+template <int CG>
+__device__ __forceinline__ void tma_load_2d_to(void* smem_dst, const CUtensorMap* m, uint32_t bar_addr, int x, int y) {
+  if constexpr (CG == 2) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_addr), "r"(x), "r"(y)
+        : "memory");
+  } else {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_addr), "r"(x), "r"(y)
+        : "memory");
+  }
 }
 // 2-D tiled store smem -> global (bulk group completion).
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int x, int y) {
@@ -234,6 +253,21 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
+// CG == 2: the MMAs were issued for a CTA pair; the barrier at this shared-memory offset is signalled in BOTH thread
+// blocks of the pair (one commit per block: the own barrier, then the peer's through its cluster address).
+template <int CG>
+__device__ __forceinline__ void umma_commit_cg(uint64_t* bar) {
+  if constexpr (CG == 2) {
+    const uint32_t own = smem_u32(bar);
+    uint32_t peer;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(own), "r"(cluster_ctarank() ^ 1u));
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(own) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(peer) : "memory");
+  } else {
+    umma_commit(bar);
+  }
+}
+
 // TMEM -> registers, 32 lanes x 32 consecutive fp32 columns; thread i of the warp gets lane
 // (lane_base + i), register j holds column (col + j).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -292,6 +326,8 @@ template <>
 __device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, uint32_t (&r)[16]) { tmem_ld_32x16(taddr, r); }
 template <int N>
 __device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&r)[N]);
+template <>
+__device__ __forceinline__ void tmem_st_cols<32>(uint32_t taddr, const uint32_t (&r)[32]) { tmem_st_32x32(taddr, r); }
 template <>
 __device__ __forceinline__ void tmem_st_cols<16>(uint32_t taddr, const uint32_t (&r)[16]) { tmem_st_32x16(taddr, r); }
 template <>

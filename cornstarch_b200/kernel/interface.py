@@ -21,11 +21,34 @@ TEXT_BITS = (1 << 62) | 1
 MAX_MODALITY_BITS = 61
 
 
+def _native_mask(input_ids: torch.Tensor, ids: list[int], padding_mask, instance: bool) -> torch.Tensor | None:
+    """The mask built by one launch of ``csb_bitfield_mask`` for int64 CUDA ids; ``None`` = use the PyTorch statement."""
+    import ctypes as C
+
+    from ..ops import _native as nat
+
+    if not (input_ids.is_cuda and input_ids.dtype == torch.int64 and input_ids.dim() == 2) or nat.LIBRARY_MODE:
+        return None
+    nat.declare("csb_bitfield_mask", [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p])
+    x = input_ids.contiguous()
+    pad = None
+    if padding_mask is not None:
+        pad = padding_mask.to(device=x.device).ne(0).to(torch.uint8).contiguous()
+    out = torch.empty_like(x)
+    arr = (C.c_long * max(1, len(ids)))(*[int(i) for i in ids])
+    nat.check(nat.lib().csb_bitfield_mask(x.data_ptr(), C.cast(arr, C.c_void_p), len(ids), nat.ptr(pad), out.data_ptr(),
+                                          x.shape[0], x.shape[1], int(instance), nat.stream()), "csb_bitfield_mask")
+    return out
+
+
 def create_bitfield_attention_mask(input_ids: torch.Tensor, token_ids: dict[str, int] | list[int],
                                    padding_mask: torch.Tensor | None = None) -> torch.Tensor:
     """int64 ``[B, S]`` bitfield mask from placeholder token ids (dict order = bit order)."""
     ids = list(token_ids.values()) if isinstance(token_ids, dict) else list(token_ids)
     assert len(ids) <= MAX_MODALITY_BITS, "at most 61 modalities fit the bitfield"
+    native = _native_mask(input_ids, ids, padding_mask, instance=False)
+    if native is not None:
+        return native
     text = TEXT_BITS
     for i in range(len(ids)):
         text |= 1 << (i + 1)
@@ -41,6 +64,9 @@ def create_instance_bitfield_attention_mask(input_ids: torch.Tensor, token_ids: 
                                             padding_mask: torch.Tensor | None = None) -> torch.Tensor:
     """One bit per contiguous run of modality placeholder tokens (bits are reused modulo 61)."""
     ids = list(token_ids.values()) if isinstance(token_ids, dict) else list(token_ids)
+    native = _native_mask(input_ids, ids, padding_mask, instance=True) if len(ids) <= MAX_MODALITY_BITS else None
+    if native is not None:
+        return native
     is_modal = torch.zeros_like(input_ids, dtype=torch.bool)
     for tid in ids:
         is_modal |= input_ids == tid

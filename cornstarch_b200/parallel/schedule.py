@@ -40,11 +40,13 @@ def _to_device(batch: Any, device) -> Any:
 
 class MultimodalEncoderTrainingOneForwardOneBackwardSchedule:
     def __init__(self, stage_manager, num_microbatches: int | None = None, microbatch_size: int | None = None,
-                 device=None, p2p_group=None, assume_static_shapes: bool = True):
+                 device=None, p2p_group=None, assume_static_shapes: bool = True, overlap_p2p: bool = False,
+                 p2p_edge_groups: dict | None = None):
         assert num_microbatches is not None or microbatch_size is not None, "Either num_microbatches or microbatch_size should be provided"
         self.stage_manager = stage_manager
-        self.comm = MultimodalPipelineP2PCommunication(stage_manager, device=device, group=p2p_group,
-                                                       assume_static=assume_static_shapes)
+        self.comm = MultimodalPipelineP2PCommunication(stage_manager, overlap_p2p=overlap_p2p, device=device, group=p2p_group,
+                                                       assume_static=assume_static_shapes, edge_groups=p2p_edge_groups)
+        self.overlapped_steps = 0  # steps that ran with asynchronous sends and pre-posted receives
         self.num_microbatches = num_microbatches
         self.microbatch_size = microbatch_size
         self.batch = None
@@ -204,6 +206,71 @@ class MultimodalEncoderTrainingOneForwardOneBackwardSchedule:
             w = sm.num_stages_in_modal - sm.stage_in_modal - 1
         return min(self.num_microbatches, w)
 
+    def _run_overlapped(self, model, criterion, optimizer, accum_loss, outputs) -> None:
+        """The same 1F1B order with asynchronous P2P: the receive of the NEXT forward input (and of the next gradient) is
+        posted before the current micro-batch is computed, sends are posted and not waited for, and the compute stream
+        waits only where it consumes a received tensor.  Runs from the second step on (the first step negotiates the
+        message layouts synchronously)."""
+        sm, comm = self.stage_manager, self.comm
+        first, last = sm.is_first_stage(check_only_in_modal=False), sm.is_last_stage(check_only_in_modal=False)
+        M, warmup = self.num_microbatches, self.num_warmup()
+        remaining = M - warmup
+        n_prev = 0 if first else len(sm.get_prev_ranks())
+        input_objs, output_objs = [], []
+        fwd_posted = bwd_posted = 0
+        fwd_h = bwd_h = None
+
+        def post_fwd():
+            nonlocal fwd_h, fwd_posted
+            fwd_h = comm.post_recv_forward() if (not first and fwd_posted < M) else None
+            fwd_posted += 1
+
+        def post_bwd():
+            nonlocal bwd_h, bwd_posted
+            bwd_h = comm.post_recv_backward() if (not last and bwd_posted < M) else None
+            bwd_posted += 1
+
+        def take_fwd():
+            h = fwd_h
+            inp = self.merge_inputs(comm.wait_all(h)) if h is not None else None
+            post_fwd()  # the next input travels while this micro-batch is computed
+            return inp
+
+        def take_bwd():
+            h = bwd_h
+            grad = comm.wait_all(h)[0] if h is not None else None
+            post_bwd()
+            return grad
+
+        def backward_and_send(grad):
+            inp0, out0 = input_objs.pop(0), output_objs.pop(0)
+            self.backward_step(optimizer, inp0, out0, grad)
+            if not first and inp0 is not None:
+                comm.isend_backward(self.split_input_grads(inp0, n_prev))
+
+        post_fwd()
+        for _ in range(warmup):
+            inp = take_fwd()
+            out = self.forward_step(model, inp, criterion, accum_loss, outputs)
+            if not last:
+                comm.isend_forward(out)
+            input_objs.append(inp)
+            output_objs.append(out)
+        post_bwd()
+        for _ in range(remaining):
+            inp = take_fwd()
+            out = self.forward_step(model, inp, criterion, accum_loss, outputs)
+            if not last:
+                comm.isend_forward(out)
+            input_objs.append(inp)
+            output_objs.append(out)
+            backward_and_send(take_bwd())
+        for _ in range(warmup):
+            backward_and_send(take_bwd())
+        comm.flush_sends()
+        assert not input_objs and not output_objs
+        self.overlapped_steps += 1
+
     def run_forward_backward(self, model, data_iter, criterion, optimizer=None, return_loss=False, return_outputs=False) -> dict:
         sm = self.stage_manager
         self.load_batch(data_iter, self.device)
@@ -216,6 +283,9 @@ class MultimodalEncoderTrainingOneForwardOneBackwardSchedule:
             accum_loss = torch.zeros((), device=self.device if self.device is not None else "cpu")
         outputs = [] if return_outputs and last else None
         train = torch.is_grad_enabled() and optimizer is not False
+        if train and self.comm.overlap_ready():
+            self._run_overlapped(model, criterion, optimizer, accum_loss, outputs)
+            return {"loss": accum_loss, "outputs": outputs}
 
         for _ in range(warmup):
             inp = self.recv_forward()

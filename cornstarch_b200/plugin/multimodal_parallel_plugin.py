@@ -178,8 +178,12 @@ class MultimodalParallelPlugin:
                  initial_scale: float = 2**16, min_scale: float = 1, growth_factor: float = 2, backoff_factor: float = 0.5,
                  growth_interval: int = 1000, hysteresis: int = 2, max_scale: float = 2**32, max_norm: float = 0,
                  parallel_output: bool = True, make_vocab_size_divisible_by: int = 64, zero_stage: int = 0,
-                 grad_dtype: torch.dtype = torch.bfloat16, device=None):
+                 grad_dtype: torch.dtype = torch.bfloat16, device=None, overlap_p2p: bool | None = None):
         assert language_model_plugin is not None, "a language model plugin is required"
+        # Pipeline messages posted asynchronously (sends not waited for, receives posted ahead of the compute they
+        # overlap with).  None = on for NCCL (every pipeline edge gets one two-rank process group per message
+        # direction), off for gloo; CORNSTARCH_B200_OVERLAP_P2P=0/1 overrides.
+        self.overlap_p2p = overlap_p2p
         for name, pl in {**(encoder_plugins or {}), "language_model": language_model_plugin}.items():
             assert pl.pipeline_template is not None, f"A pipeline template must be specified for {name} (the plugin always pipelines)."
         self.encoder_plugins = dict(encoder_plugins or {})
@@ -222,8 +226,24 @@ class MultimodalParallelPlugin:
         self.dp_size = M.dp_size
         if self.device is None:
             self.device = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl" else torch.device("cpu")
+        import os
+
+        overlap = self.overlap_p2p
+        env = os.environ.get("CORNSTARCH_B200_OVERLAP_P2P")
+        if env is not None:
+            overlap = env == "1"
+        if overlap is None:
+            overlap = dist.get_backend() == "nccl"
+        edge_groups = None
+        if overlap:
+            from ..parallel.p2p import make_edge_groups
+
+            sm = self.stage_manager
+            nxt = [] if sm.is_last_stage(check_only_in_modal=False) else sm.get_next_ranks()
+            edge_groups = make_edge_groups(nxt)  # collective over all ranks: two groups per pipeline edge
         self.schedule = MultimodalEncoderTrainingOneForwardOneBackwardSchedule(
-            self.stage_manager, self.num_microbatches, self.microbatch_size, device=self.device)
+            self.stage_manager, self.num_microbatches, self.microbatch_size, device=self.device, overlap_p2p=bool(overlap),
+            p2p_edge_groups=edge_groups)
         self.distributed_initialized = True
 
     def my_modal_name(self) -> str:

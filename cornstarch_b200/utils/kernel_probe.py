@@ -82,6 +82,38 @@ def probe_gemm(a, flush):
         report(f"gemm[{tag}]", ms, flops=2.0 * M * N * K, M=M, N=N, K=K)
 
 
+def probe_gemm_sustained(a, flush):
+    """Back-to-back launches for ``--seconds`` (default 3) of this package's GEMM and of ``torch.matmul`` (cuBLAS) on the
+    same operands: the throughput both settle at under the power cap, which is what a long training step sees."""
+    import time
+
+    M, N, K = a.m, a.n, a.k
+    A_ = torch.randn(M, K, device="cuda").bfloat16()
+    B_ = torch.randn(N, K, device="cuda").bfloat16()
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    Bt = B_.t()
+
+    def loop(fn):
+        fn()
+        torch.cuda.synchronize()
+        n, t0 = 0, time.monotonic()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        while time.monotonic() - t0 < a.seconds:
+            for _ in range(20):
+                fn()
+            n += 20
+            torch.cuda.synchronize()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    for tag, fn in (("cublas", lambda: torch.matmul(A_, Bt, out=out)), ("native", lambda: gemm(A_, B_, False, False, out=out)),
+                    ("cublas", lambda: torch.matmul(A_, Bt, out=out)), ("native", lambda: gemm(A_, B_, False, False, out=out))):
+        ms = loop(fn)
+        report(f"gemm_sustained[{tag}]", ms, flops=2.0 * M * N * K, M=M, N=N, K=K, seconds=a.seconds)
+
+
 def _qkv(a):
     B, S, Hq, Hk, D = a.batch, a.seq, a.heads, a.kv_heads, a.head_dim
     q = torch.randn(B, S, Hq, D, device="cuda").bfloat16()
@@ -265,7 +297,8 @@ def probe_attn_fwd_pulled(a, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "elementwise", "gemm_ar_local", "adamw", "grad_reduce_local",
+    ap.add_argument("--seconds", type=float, default=3.0)
+    ap.add_argument("what", choices=["gemm", "gemm_sustained", "attn_fwd", "attn_bwd", "elementwise", "gemm_ar_local", "adamw", "grad_reduce_local",
                                      "moe_push_local", "attn_fwd_pulled", "all"])
     ap.add_argument("--reducers", type=int, default=16)
     ap.add_argument("--m", type=int, default=8192)
@@ -284,7 +317,7 @@ def main():
     flush = Flusher(not a.no_flush)
     todo = ["gemm", "attn_fwd", "attn_bwd", "elementwise"] if a.what == "all" else [a.what]
     for t in todo:
-        {"gemm": probe_gemm, "attn_fwd": probe_attn_fwd, "attn_bwd": probe_attn_bwd, "elementwise": probe_elementwise,
+        {"gemm": probe_gemm, "gemm_sustained": probe_gemm_sustained, "attn_fwd": probe_attn_fwd, "attn_bwd": probe_attn_bwd, "elementwise": probe_elementwise,
          "gemm_ar_local": probe_gemm_ar_local, "adamw": probe_adamw, "grad_reduce_local": probe_grad_reduce_local,
          "moe_push_local": probe_moe_push_local, "attn_fwd_pulled": probe_attn_fwd_pulled}[t](a, flush)
     from ..ops import _native as nat

@@ -5,7 +5,8 @@ autograd class at :1202-1266; ``cornstarch/kernel/attention.py``: ``flash_attn_f
 torch + triton alone, so they can run here even though the rest of the reference (model layer, plugins) cannot.  This
 module imports them from an installed copy of the reference (``baseline/_ref`` of a checkout, or any ``cornstarch`` on
 ``sys.path``), runs forward and backward on the shapes of the benchmark workloads, cross-checks outputs and gradients
-against this package's kernels, and reports device times.
+against this package's kernels and both against an fp32 PyTorch oracle (one KV head and the query heads sharing it; errors are
+max |x - oracle| / max |oracle|, the reference's own tolerance is 5e-3), and reports device times.
 
     python -m cornstarch_b200.utils.reference_kernels            # all cases, one JSON line per case
     python -m cornstarch_b200.utils.reference_kernels --quick    # the two headline shapes only
@@ -102,8 +103,22 @@ def _case(name, B, S, Hq, Hk, D, bits, iters, warmup, flush, ref_bf, ref_fa):
     out["native"] = {"fwd_ms": round(ms_f, 4), "bwd_ms": round(ms_b, 4), "fwd_tflops": round(fwd_flops / ms_f / 1e9, 1),
                      "bwd_tflops": round(2.5 * fwd_flops / ms_b / 1e9, 1)}
 
+    # ---- fp32 oracle (plain PyTorch, dense mask) on the first KV head and the query heads that share it
+    g_sz = Hq // Hk
+    qo, ko, vo = (t.float().clone().requires_grad_() for t in (q[:, :, :g_sz], k[:, :, :1], v[:, :, :1]))
+    o_o, _ = A.attention_reference(qo, ko, vo, mask)
+    o_o.backward(do[:, :, :g_sz].float())
+    oracle = {"o": o_o.detach(), "dq": qo.grad, "dk": ko.grad, "dv": vo.grad}
+    del o_o
+    sub = lambda o_, dq_, dk_, dv_: {"o": o_[:, :, :g_sz], "dq": dq_[:, :, :g_sz], "dk": dk_[:, :, :1], "dv": dv_[:, :, :1]}  # noqa: E731
+    err_n = {k_: _rel(v_, oracle[k_]) for k_, v_ in sub(o_n, dq_n, dk_n, dv_n).items()}
+    out["native"]["max_rel_err_vs_fp32_oracle"] = {k_: round(v_, 5) for k_, v_ in err_n.items()}
+    out["native"]["within_5e-3_of_oracle"] = bool(all(v_ <= TOL for v_ in err_n.values()))
+
     # ---- the reference's Triton kernels through its own autograd function
     try:
+        if hasattr(ref_bf, "BitfieldUtils"):
+            ref_bf.BitfieldUtils.clear_cache()  # the reference caches ONE compressed mask globally; a new mask needs a clear
         qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
         if bits is None:
             fwd = lambda: ref_fa.flash_attn_func(qr, kr, vr)  # noqa: E731
@@ -131,7 +146,9 @@ def _case(name, B, S, Hq, Hk, D, bits, iters, warmup, flush, ref_bf, ref_fa):
                           "fwd_plus_bwd": round(ms_rfb / (ms_f + ms_b), 2)}
         err = {"o": _rel(o_n, o_r), "dq": _rel(dq_n, dq_r), "dk": _rel(dk_n, dk_r), "dv": _rel(dv_n, dv_r)}
         out["max_rel_diff_native_vs_reference"] = {k_: round(v_, 5) for k_, v_ in err.items()}
-        out["within_5e-3"] = bool(all(v_ <= TOL for v_ in err.values()))
+        err_r = {k_: _rel(v_, oracle[k_]) for k_, v_ in sub(o_r, dq_r, dk_r, dv_r).items()}
+        out["reference_triton"]["max_rel_err_vs_fp32_oracle"] = {k_: round(v_, 5) for k_, v_ in err_r.items()}
+        out["reference_triton"]["within_5e-3_of_oracle"] = bool(all(v_ <= TOL for v_ in err_r.values()))
     except Exception as e:  # noqa: BLE001  (e.g. a Triton compile error for this GPU: reported, not raised)
         out["reference_triton"] = {"error": f"{type(e).__name__}: {e}".replace("\n", " ")[:400]}
     return out

@@ -237,3 +237,30 @@ def test_kv_segments_pulled(sizes, my_seg, pull):
     torch.cuda.synchronize()
     assert torch.equal(o, ro)
     assert torch.equal(lse, rlse)
+
+
+@pytest.mark.parametrize("instance", [False, True])
+def test_bitfield_mask_builder_kernel_matches_pytorch_statement(instance):
+    """The int64 bitfield mask built by one kernel launch equals the PyTorch statement of the same builder (CPU path):
+    several modalities, runs that straddle the 1024-token scan chunks, adjacent runs of different ids, padding."""
+    from cornstarch_b200.kernel import interface as I
+
+    g = torch.Generator().manual_seed(5)
+    B, S = 3, 5000
+    ids = torch.randint(0, 900, (B, S), generator=g)
+    tok = {"vision": 998, "audio": 999}
+    for b in range(B):
+        pos = 3
+        for run in range(70 if instance else 9):  # more than 61 runs: the instance bits wrap around
+            n = int(torch.randint(1, 90, (1,), generator=g))
+            if pos + n >= S:
+                break
+            ids[b, pos : pos + n] = 998 if (run + b) % 3 else 999
+            pos += n + int(torch.randint(0, 40, (1,), generator=g))  # gap 0: two runs of different ids touch
+    pad = torch.ones(B, S, dtype=torch.long)
+    pad[1, 4700:] = 0
+    build = I.create_instance_bitfield_attention_mask if instance else I.create_bitfield_attention_mask
+    want = build(ids, tok, pad)
+    got = build(ids.cuda(), tok, pad.cuda())
+    assert got.dtype == torch.int64 and torch.equal(got.cpu(), want)
+    assert torch.equal(build(ids.cuda(), tok).cpu(), build(ids, tok))

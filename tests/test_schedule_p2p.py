@@ -142,3 +142,40 @@ def _p2p_worker(rank, world):
 
 def test_p2p_protocol():
     run_distributed(_p2p_worker, 3)
+
+
+def _overlap_worker(rank, world, enc_stages, llm_stages, M):
+    """Overlapped P2P (asynchronous sends, receives posted ahead): the first step negotiates the message layouts with the
+    synchronous protocol, the following steps run overlapped; order, loss and gradients equal the synchronous schedule."""
+    from cornstarch_b200.parallel.p2p import make_edge_groups
+
+    sm, Sched = _setup(world, rank, enc_stages, llm_stages)
+    last = sm.is_last_stage(check_only_in_modal=False)
+    edges = make_edge_groups([] if last else sm.get_next_ranks())
+    n_edges = (0 if last else len(sm.get_next_ranks())) + (0 if sm.is_first_stage(check_only_in_modal=False) else len(sm.get_prev_ranks()))
+    assert len(edges) == 2 * n_edges
+    x = torch.randn(M * 2, 8, generator=torch.Generator().manual_seed(2))
+    results = {}
+    for mode in ("sync", "overlap"):
+        sched = Sched(sm, num_microbatches=M, device=torch.device("cpu"), overlap_p2p=(mode == "overlap"), p2p_edge_groups=edges)
+        model = ToyStage(rank, last)
+        grads, losses, orders = [], [], []
+        for step in range(3):
+            model.zero_grad()
+            sched.order_log = []
+            out = sched.forward_backward_step(model, iter([{"x": x * (step + 1)}]), lambda o, mb: o.pow(2).mean(), None, return_loss=True)
+            grads.append(model.lin.weight.grad.clone())
+            losses.append(out["loss"].item() if last else None)
+            orders.append("".join(sched.order_log))
+        results[mode] = (grads, losses, orders)
+        assert sched.overlapped_steps == (2 if mode == "overlap" else 0), (mode, sched.overlapped_steps)
+        dist.barrier()
+    for a, b in zip(results["sync"][0], results["overlap"][0]):
+        assert torch.equal(a, b)
+    assert results["sync"][1] == results["overlap"][1]
+    assert results["sync"][2] == results["overlap"][2]
+
+
+@pytest.mark.parametrize("enc_stages,llm_stages,M", [((1,), 3, 6), ((1, 2), 2, 4), ((1,), 2, 1)])
+def test_overlapped_p2p_matches_synchronous(enc_stages, llm_stages, M):
+    run_distributed(_overlap_worker, sum(enc_stages) + llm_stages, enc_stages, llm_stages, M)
