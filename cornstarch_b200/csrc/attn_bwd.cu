@@ -55,6 +55,12 @@ struct AttnBwdParams {
   long dk_stride_b[CSB_MAX_SEG], dk_stride_s[CSB_MAX_SEG], dv_stride_b[CSB_MAX_SEG], dv_stride_s[CSB_MAX_SEG];
   int* status;
   int kj_slowest;  // block order: 1 = key block slowest (masks that leave key blocks unequal work), 0 = key block fastest
+  // dense boolean mask (MASK_DENSE) and additive bias, as in the forward kernel
+  const uint8_t* dmask;
+  long dm_sb, dm_sq;
+  const float* bias;
+  long bias_sb, bias_sh, bias_sq;
+  float inv_scale;
   SegInfo seg;
 };
 
@@ -442,6 +448,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_cols<COLS>(tmem_dPT + col0 + lane_addr, dv);
       tmem_ld_wait();
       float pv[COLS], ds[COLS];
+      const int q_base = tile_idx[it % n_valid] * BW_BQ + col0;  // first query row of this thread's columns
+      if (p.bias != nullptr && k_valid) {
+        const int hh = hk * group + it / n_valid;
+        const float* bcol = p.bias + (long)b * p.bias_sb + (long)hh * p.bias_sh + kidx;
+#pragma unroll
+        for (int x = 0; x < COLS; ++x)
+          if (q_base + x < p.Sq)
+            sv[x] = __float_as_uint(fmaf(__ldg(bcol + (long)(q_base + x) * p.bias_sq), p.inv_scale, __uint_as_float(sv[x])));
+      }
 #pragma unroll
       for (int x4 = 0; x4 < COLS / 4; ++x4) {
         const float4 l4 = *reinterpret_cast<const float4*>(m_lse + col0 + x4 * 4);
@@ -451,11 +466,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           pv[x4 * 4 + y] = fast_exp2(fmaf(__uint_as_float(sv[x4 * 4 + y]), p.scale_log2, -ls[y]));
       }
       if (c == 1) {
+        if (p.mask_mode == MASK_DENSE) {
+          const uint8_t* mcol = p.dmask + (long)b * p.dm_sb + kidx;
 #pragma unroll
-        for (int x = 0; x < COLS; ++x) {
-          const int col = col0 + x;
-          const bool allow = k_valid && m_qpos[col] >= 0 && mask_allowed(p.mask_mode, m_qbits[col], kb, m_qpos[col], kpos);
-          pv[x] = allow ? pv[x] : 0.f;
+          for (int x = 0; x < COLS; ++x) {
+            const bool allow = k_valid && m_qpos[col0 + x] >= 0 && __ldg(mcol + (long)(q_base + x) * p.dm_sq) != 0;
+            pv[x] = allow ? pv[x] : 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int x = 0; x < COLS; ++x) {
+            const int col = col0 + x;
+            const bool allow = k_valid && m_qpos[col] >= 0 && mask_allowed(p.mask_mode, m_qbits[col], kb, m_qpos[col], kpos);
+            pv[x] = allow ? pv[x] : 0.f;
+          }
         }
       }
 #pragma unroll
@@ -565,12 +589,21 @@ using namespace csb;
 // come as segments (kv_segments.h) and the dK / dV tiles of segment r are written to kv->dk[r] / kv->dv[r].
 // lse: fp32 [B][Hq][Sq] from the forward; delta: fp32 [B][Hq][Sq] scratch; dq_acc: fp32 dense [B][Sq][Hq][D] scratch
 // that the caller has zeroed.  Sk = padded gathered length; cls: tile classes for 128x128 tiles.
-CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void* out, const void* dout, const float* lse,
+// Optional inputs of the dense-mask / bias form (same layout as in attn_fwd.cu).
+struct CsbAttnExtras {
+  const unsigned char* dmask;
+  long dm_sb, dm_sq;
+  const float* bias;
+  long bias_sb, bias_sh, bias_sq;
+};
+
+static int attn_bwd_seg_impl(const void* q, const CsbKvSegments* kv, const void* out, const void* dout, const float* lse,
                              float* delta, float* dq_acc, void* dq, int B, int Sq, int Sk, int Hq, int Hk, int D, long q_ss,
                              long q_sb, long o_ss, long o_sb, long do_ss, long do_sb, long dq_ss, long dq_sb, float scale,
                              int mask_mode, const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
-                             const signed char* cls, int* status, void* stream) {
+                             const signed char* cls, int* status, void* stream, const CsbAttnExtras* ex) {
   if (D % 8 || D > 128 || D < 16 || Hq % Hk) return CSB_ERR_BAD_ARG;
+  if (mask_mode == MASK_DENSE && (ex == nullptr || ex->dmask == nullptr)) return CSB_ERR_BAD_ARG;
   if (kv == nullptr || kv->n_seg < 1 || kv->n_seg > CSB_MAX_SEG) return CSB_ERR_BAD_ARG;
   if ((Sq + BW_BQ - 1) / BW_BQ > BwdSmem::MAX_TILES) return CSB_ERR_TOO_LARGE;
   if ((q_ss % 8) || (do_ss % 8) || (dq_ss % 4)) return CSB_ERR_BAD_ARG;
@@ -599,6 +632,11 @@ CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void*
   p.cls = reinterpret_cast<const int8_t*>(cls);
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
   p.status = status;
+  p.dmask = ex ? ex->dmask : nullptr;
+  p.dm_sb = ex ? ex->dm_sb : 0; p.dm_sq = ex ? ex->dm_sq : 0;
+  p.bias = ex ? ex->bias : nullptr;
+  p.bias_sb = ex ? ex->bias_sb : 0; p.bias_sh = ex ? ex->bias_sh : 0; p.bias_sq = ex ? ex->bias_sq : 0;
+  p.inv_scale = scale != 0.f ? 1.f / scale : 0.f;
   p.kj_slowest = mask_mode != MASK_FULL;
   fill_seg_info(&p.seg, kv, BW_BKV);
   if (p.seg.tile_start[kv->n_seg] != p.nK) return CSB_ERR_BAD_ARG;
@@ -652,6 +690,35 @@ CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void*
   int blocks = (int)((work + 255) / 256 < (long)sm_count() * 16 ? (work + 255) / 256 : (long)sm_count() * 16);
   attn_dq_convert_kernel<<<blocks, 256, 0, s>>>(dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), n_rows, Sq, HD, dq_sb, dq_ss);
   return launch_result();
+}
+
+CSB_API int csb_attn_bwd_seg(const void* q, const CsbKvSegments* kv, const void* out, const void* dout, const float* lse,
+                             float* delta, float* dq_acc, void* dq, int B, int Sq, int Sk, int Hq, int Hk, int D, long q_ss,
+                             long q_sb, long o_ss, long o_sb, long do_ss, long do_sb, long dq_ss, long dq_sb, float scale,
+                             int mask_mode, const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
+                             const signed char* cls, int* status, void* stream) {
+  return attn_bwd_seg_impl(q, kv, out, dout, lse, delta, dq_acc, dq, B, Sq, Sk, Hq, Hk, D, q_ss, q_sb, o_ss, o_sb, do_ss, do_sb,
+                           dq_ss, dq_sb, scale, mask_mode, q_bits, k_bits, q_pos, k_pos, cls, status, stream, nullptr);
+}
+
+// One local K/V tensor with a dense boolean mask (mask_mode = MASK_DENSE) and / or an additive bias (no bias gradient).
+CSB_API int csb_attn_bwd_dense(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                               const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq,
+                               int Sk, int Hq, int Hk, int D, long q_ss, long q_sb, long k_ss, long k_sb, long v_ss, long v_sb,
+                               long o_ss, long o_sb, long do_ss, long do_sb, long dq_ss, long dq_sb, long dk_ss, long dk_sb,
+                               long dv_ss, long dv_sb, float scale, int mask_mode, const signed char* cls,
+                               const CsbAttnExtras* ex, int* status, void* stream) {
+  CsbKvSegments kv = {};
+  kv.n_seg = 1;
+  kv.my_seg = 0;
+  kv.rows[0] = Sk;
+  kv.k[0] = k; kv.v[0] = v;
+  kv.k_stride_s[0] = k_ss; kv.k_stride_b[0] = k_sb; kv.v_stride_s[0] = v_ss; kv.v_stride_b[0] = v_sb;
+  kv.dk[0] = dk; kv.dv[0] = dv;
+  kv.dk_stride_s[0] = dk_ss; kv.dk_stride_b[0] = dk_sb; kv.dv_stride_s[0] = dv_ss; kv.dv_stride_b[0] = dv_sb;
+  kv.ready_flags = nullptr;
+  return attn_bwd_seg_impl(q, &kv, out, dout, lse, delta, dq_acc, dq, B, Sq, Sk, Hq, Hk, D, q_ss, q_sb, o_ss, o_sb, do_ss, do_sb,
+                           dq_ss, dq_sb, scale, mask_mode, nullptr, nullptr, nullptr, nullptr, cls, status, stream, ex);
 }
 
 // One local K/V tensor ([B][Sk][Hk][D] views) with dK / dV of the same shape.

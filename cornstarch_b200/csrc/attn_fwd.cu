@@ -44,6 +44,13 @@ struct AttnFwdParams {
   float* lse;                   // [B][Hq][Sq]
   int* status;
   int j_start;  // key tiles are visited in rotated order starting here (own segment first)
+  // dense boolean mask (MASK_DENSE): bytes [B][Sq][Sk], key index contiguous, strides in bytes
+  const uint8_t* dmask;
+  long dm_sb, dm_sq;
+  // additive bias (optional, any mode): fp32, key index contiguous; strides in elements, 0 for broadcast dimensions
+  const float* bias;
+  long bias_sb, bias_sh, bias_sq;
+  float inv_scale;
   SegInfo seg;
 };
 
@@ -87,6 +94,35 @@ mask_classify_kernel(int mode, const int64_t* __restrict__ q_bits, const int64_t
     else if (total == valid_rows * bn) c = 2;
     cls[((long)b * nQ + qi) * nK + kj] = c;
     // per query block: number of non-empty key blocks (the context-parallel partitioner's workload)
+    if (row_work && c != 0) atomicAdd(&row_work[(long)b * nQ + qi], 1);
+  }
+}
+
+// Tile classes of a dense boolean mask (bytes [B][Sq][Sk]): one thread block per 128 x 128 tile counts the allowed pairs.
+__global__ void __launch_bounds__(128)
+mask_classify_dense_kernel(const uint8_t* __restrict__ dmask, long sb, long sq, int Sq, int Sk, int bm, int bn, int nQ, int nK,
+                           int8_t* __restrict__ cls, int* __restrict__ row_work) {
+  const int kj = blockIdx.x, qi = blockIdx.y, b = blockIdx.z;
+  const int k0 = kj * bn, k1 = min(Sk, k0 + bn);
+  int cnt = 0;
+  for (int r = threadIdx.x; r < bm; r += blockDim.x) {
+    const int q = qi * bm + r;
+    if (q >= Sq) continue;
+    const uint8_t* row = dmask + (long)b * sb + (long)q * sq;
+    for (int k = k0; k < k1; ++k) cnt += row[k] ? 1 : 0;
+  }
+  __shared__ int red[4];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = cnt;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int total = red[0] + red[1] + red[2] + red[3];
+    const int valid_rows = min(bm, Sq - qi * bm);
+    int8_t c = 1;
+    if (total == 0) c = 0;
+    else if (total == valid_rows * bn) c = 2;  // only tiles that lie fully inside Sk can be "all allowed"
+    cls[((long)b * nQ + qi) * nK + kj] = c;
     if (row_work && c != 0) atomicAdd(&row_work[(long)b * nQ + qi], 1);
   }
 }
@@ -357,14 +393,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           s[32 + i] = __uint_as_float(v1[i]);
         }
       }
+      if (p.bias != nullptr && row_valid) {
+        // additive bias in score units: folded in as bias / scale so that the scaled exponent below stays one FMA
+        const int kc0 = j * AT_BN + half * 64;
+        const float* brow = p.bias + (long)b * p.bias_sb + (long)h * p.bias_sh + (long)q * p.bias_sq + kc0;
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (kc0 + i < p.Sk) s[i] = fmaf(__ldg(brow + i), p.inv_scale, s[i]);
+      }
       if (c == 1) {
         const int64_t* kb = kb_s + buf * 128 + half * 64;
         const int* kp = kp_s + buf * 128 + half * 64;
+        if (p.mask_mode == MASK_DENSE) {
+          const int kc0 = j * AT_BN + half * 64;
+          const uint8_t* mrow = p.dmask + (long)b * p.dm_sb + (long)(row_valid ? q : 0) * p.dm_sq + kc0;
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const int kpos = kp[i];
-          const bool allow = row_valid && kpos >= 0 && mask_allowed(p.mask_mode, qb, kb[i], qpos, kpos);
-          s[i] = allow ? s[i] : -INFINITY;
+          for (int i = 0; i < 64; ++i) {
+            const bool allow = row_valid && kp[i] >= 0 && __ldg(mrow + i) != 0;
+            s[i] = allow ? s[i] : -INFINITY;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int kpos = kp[i];
+            const bool allow = row_valid && kpos >= 0 && mask_allowed(p.mask_mode, qb, kb[i], qpos, kpos);
+            s[i] = allow ? s[i] : -INFINITY;
+          }
         }
       }
       float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
@@ -517,11 +571,20 @@ CSB_API int csb_mask_classify(int mode, const long* q_bits, const long* k_bits, 
 // token / batch strides in elements); Sk = sum of the segments' rows rounded up to 128 each (the padded gathered
 // length that k_bits / k_pos / cls are indexed by); out: [B][Sq][Hq][D] view; lse: fp32 [B][Hq][Sq]; cls from
 // csb_mask_classify with bm = bn = 128.
-CSB_API int csb_attn_fwd_seg(const void* q, const CsbKvSegments* kv, void* out, float* lse, int B, int Sq, int Sk, int Hq,
+// Optional inputs of the dense-mask / bias form (flash attention with a boolean mask or an additive bias).
+struct CsbAttnExtras {
+  const unsigned char* dmask;  // bytes [B][Sq][Sk] (nonzero = attend), key index contiguous; used when mask_mode = MASK_DENSE
+  long dm_sb, dm_sq;           // byte strides of batch and query index
+  const float* bias;           // fp32, key index contiguous; null = none
+  long bias_sb, bias_sh, bias_sq;  // element strides (0 = broadcast)
+};
+
+static int attn_fwd_seg_impl(const void* q, const CsbKvSegments* kv, void* out, float* lse, int B, int Sq, int Sk, int Hq,
                              int Hk, int D, long q_stride_s, long q_stride_b, long o_stride_s, long o_stride_b, float scale,
                              int mask_mode, const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
-                             const signed char* cls, int* status, void* stream) {
+                             const signed char* cls, int* status, void* stream, const CsbAttnExtras* ex) {
   if (D % 8 || D > 128 || D < 16 || Hq % Hk) return CSB_ERR_BAD_ARG;
+  if (mask_mode == MASK_DENSE && (ex == nullptr || ex->dmask == nullptr)) return CSB_ERR_BAD_ARG;
   if (kv == nullptr || kv->n_seg < 1 || kv->n_seg > CSB_MAX_SEG) return CSB_ERR_BAD_ARG;
   if ((Sk + AT_BN - 1) / AT_BN > AttnSmem<2>::MAX_NK) return CSB_ERR_TOO_LARGE;
   if ((q_stride_s % 8) || (o_stride_s % 8)) return CSB_ERR_BAD_ARG;
@@ -541,6 +604,11 @@ CSB_API int csb_attn_fwd_seg(const void* q, const CsbKvSegments* kv, void* out, 
   p.o_stride_b = o_stride_b; p.o_stride_s = o_stride_s;
   p.lse = lse;
   p.status = status;
+  p.dmask = ex ? ex->dmask : nullptr;
+  p.dm_sb = ex ? ex->dm_sb : 0; p.dm_sq = ex ? ex->dm_sq : 0;
+  p.bias = ex ? ex->bias : nullptr;
+  p.bias_sb = ex ? ex->bias_sb : 0; p.bias_sh = ex ? ex->bias_sh : 0; p.bias_sq = ex ? ex->bias_sq : 0;
+  p.inv_scale = scale != 0.f ? 1.f / scale : 0.f;
   fill_seg_info(&p.seg, kv, AT_BN);
   if (p.seg.tile_start[kv->n_seg] != p.nK) return CSB_ERR_BAD_ARG;  // Sk must be the padded gathered length
   p.j_start = (kv->my_seg >= 0 && kv->my_seg < kv->n_seg) ? p.seg.tile_start[kv->my_seg] : 0;
@@ -576,6 +644,41 @@ CSB_API int csb_attn_fwd_seg(const void* q, const CsbKvSegments* kv, void* out, 
     kfn<<<grid, 320, AttnSmem<2>::DYN_BYTES, s>>>(tq, kvm, p);
   }
   return launch_result();
+}
+
+CSB_API int csb_attn_fwd_seg(const void* q, const CsbKvSegments* kv, void* out, float* lse, int B, int Sq, int Sk, int Hq,
+                             int Hk, int D, long q_stride_s, long q_stride_b, long o_stride_s, long o_stride_b, float scale,
+                             int mask_mode, const long* q_bits, const long* k_bits, const int* q_pos, const int* k_pos,
+                             const signed char* cls, int* status, void* stream) {
+  return attn_fwd_seg_impl(q, kv, out, lse, B, Sq, Sk, Hq, Hk, D, q_stride_s, q_stride_b, o_stride_s, o_stride_b, scale,
+                           mask_mode, q_bits, k_bits, q_pos, k_pos, cls, status, stream, nullptr);
+}
+
+// Tile classes (128 x 128) of a dense boolean mask: bytes [B][Sq][Sk] with byte strides sb / sq.
+CSB_API int csb_mask_classify_dense(const unsigned char* dmask, long sb, long sq, int B, int Sq, int Sk, signed char* cls,
+                                    int* row_work, void* stream) {
+  const int nQ = (Sq + 127) / 128, nK = (Sk + 127) / 128;
+  dim3 grid(nK, nQ, B);
+  mask_classify_dense_kernel<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(dmask, sb, sq, Sq, Sk, 128, 128, nQ, nK,
+                                                                                      reinterpret_cast<int8_t*>(cls), row_work);
+  return launch_result();
+}
+
+// One local K/V tensor with a dense boolean mask (mask_mode = MASK_DENSE) and / or an additive bias.
+CSB_API int csb_attn_fwd_dense(const void* q, const void* k, const void* v, void* out, float* lse, int B, int Sq, int Sk,
+                               int Hq, int Hk, int D, long q_stride_s, long q_stride_b, long k_stride_s, long k_stride_b,
+                               long v_stride_s, long v_stride_b, long o_stride_s, long o_stride_b, float scale, int mask_mode,
+                               const signed char* cls, const CsbAttnExtras* ex, int* status, void* stream) {
+  CsbKvSegments kv = {};
+  kv.n_seg = 1;
+  kv.my_seg = 0;
+  kv.rows[0] = Sk;
+  kv.k[0] = k; kv.v[0] = v;
+  kv.k_stride_s[0] = k_stride_s; kv.k_stride_b[0] = k_stride_b;
+  kv.v_stride_s[0] = v_stride_s; kv.v_stride_b[0] = v_stride_b;
+  kv.ready_flags = nullptr;
+  return attn_fwd_seg_impl(q, &kv, out, lse, B, Sq, Sk, Hq, Hk, D, q_stride_s, q_stride_b, o_stride_s, o_stride_b, scale,
+                           mask_mode, nullptr, nullptr, nullptr, nullptr, cls, status, stream, ex);
 }
 
 // One local K/V tensor: q: [B][Sq][Hq][D], k/v: [B][Sk][Hk][D] bf16 views.

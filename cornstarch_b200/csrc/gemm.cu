@@ -56,6 +56,21 @@ struct GemmParams {
   __nv_bfloat16* ar_final[8];  // final buffer [M][N] of every rank (peer-mapped): rows owned by others land here
   int* ar_cnt_part[8];         // per rank: int32 [world][512 tile rows], bumped by the sender of a partial tile
   int* ar_cnt_final[8];        // per rank: int32 [world][512 tile rows], bumped by the owner after pushing a final tile
+  // Reduce-scatter form of the above (ar_scatter = 1): the owner keeps the sum of its rows and nothing is pushed back;
+  // C then holds ONLY the owner's rows, stored from row 0 (ar_row_offset = first owned row).
+  int ar_scatter;
+  int ar_row_offset;
+  // ---- fused all-gather of A (ag_world > 1): A is sharded by rows over the ranks (contiguous ranges of 128-row tile
+  // rows, range r on rank r, as above).  The first ag_pull_ctas thread blocks copy every shard - the peers' through
+  // their peer mappings, once - into the local full-size A that the tensor map covers; the other blocks compute tiles,
+  // own rows first, and wait (bounded) for a range's copy before they load its first tile.
+  int ag_world, ag_rank, ag_pull_ctas;
+  const uint4* ag_src[8];   // shard of every rank (peer-mapped; [rows of range r][K] bf16, row pitch K)
+  uint4* ag_dst;            // local full A [M][K], row pitch K
+  const int* ag_ready;      // local int[world]: rank r's counter >= ag_ready_value once its shard is staged
+  int ag_ready_value;
+  int* ag_pulled;           // local int[world]: every pulling block adds 1 per finished range
+  int ag_pull_target;       // ag_pulled[r] reaches this once range r is complete for this call
 };
 
 constexpr int AR_MAX_ROWS = 512;
@@ -133,6 +148,57 @@ __device__ __forceinline__ bool spin_until_ge(const int* addr, int target) {
     }
   }
   return false;
+}
+
+__device__ __forceinline__ bool spin_local_ge(const int* addr, int target) {
+  uint64_t t0 = 0;
+  for (uint32_t i = 0; i < CSB_SPIN_LIMIT; ++i) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    if (v >= target) return true;
+    if ((i & 63u) == 63u) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > wait_limit_ns()) return false;
+    }
+  }
+  return false;
+}
+
+// One pulling thread block of the fused all-gather: its share of every rank's shard (own first, then the next
+// ranks) goes from the (peer-mapped) source into the local full-size A; the range is then counted as done.
+__device__ __forceinline__ bool ag_pull(const GemmParams& p, int block, int n_blocks, int* ok_smem) {
+  const long stride = (long)n_blocks * blockDim.x;
+  const long row_vecs = p.K / 8;  // 16-byte vectors per row
+  for (int d = 0; d < p.ag_world; ++d) {
+    const int r = (p.ag_rank + d) % p.ag_world;
+    if (r != p.ag_rank) {
+      if (threadIdx.x == 0) *ok_smem = spin_until_ge(p.ag_ready + r, p.ag_ready_value) ? 1 : 0;
+      __syncthreads();
+      const bool ok = *ok_smem != 0;
+      __syncthreads();
+      if (!ok) return false;
+    }
+    const long row0 = (long)ar_range_start(r, p.num_m_blocks, p.ag_world) * BM;
+    long row1 = (long)ar_range_start(r + 1, p.num_m_blocks, p.ag_world) * BM;
+    if (row1 > p.M) row1 = p.M;
+    const long n = (row1 - row0) * row_vecs;
+    const uint4* __restrict__ src = p.ag_src[r];
+    uint4* __restrict__ dst = p.ag_dst + row0 * row_vecs;
+    for (long i = (long)block * blockDim.x + threadIdx.x; i < n; i += 4 * stride) {
+      uint4 x[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i + u * stride < n) x[u] = __ldcg(src + i + u * stride);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i + u * stride < n) dst[i + u * stride] = x[u];
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.ag_pulled + r) : "memory");
+  }
+  return true;
 }
 
 __device__ __forceinline__ float apply_act(float x, int act) {
@@ -266,6 +332,8 @@ __device__ __forceinline__ void epilogue_tile_tma(const GemmParams& p, const Epi
         else tma_store_2d(&maps.c, buf, col0, y);
       } else if (!mine) {
         tma_store_2d(&maps.inbox[owner], buf, col0, y);
+      } else if (p.ar_scatter) {
+        tma_store_2d(&maps.c, buf, col0, y - p.ar_row_offset);  // C holds the owned rows only
       } else {
         tma_store_2d(&maps.c, buf, col0, y);
         for (int d = 0; d < p.ar_world; ++d)
@@ -286,7 +354,7 @@ __device__ __forceinline__ void epilogue_tile_tma(const GemmParams& p, const Epi
     if (!mine) {
       int* cnt = p.ar_cnt_part[owner] + p.ar_rank * AR_MAX_ROWS + m_blk;
       asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(cnt) : "memory");
-    } else {
+    } else if (!p.ar_scatter) {
       for (int d = 0; d < p.ar_world; ++d) {
         if (d == p.ar_rank) continue;
         int* cnt = p.ar_cnt_final[d] + p.ar_rank * AR_MAX_ROWS + m_blk;
@@ -313,15 +381,26 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // The grid is one-dimensional so that thread blocks start in index order: the pulling blocks of a fused all-gather
+  // come first and are resident before any block that waits for their counters.
+  const int n_pull = (CG == 1 && p.ag_world > 1) ? p.ag_pull_ctas : 0;
+  if ((int)blockIdx.x < n_pull) {
+    if (!ag_pull(p, blockIdx.x, n_pull, reinterpret_cast<int*>(smem)) && threadIdx.x == 0)
+      atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG);
+    return;
+  }
   // A pair of thread blocks (CG == 2) walks the tiles together: `unit` rows of 128 * CG; block `cta_rank` of the pair
   // owns rows [cta_rank * 128, +128) of a tile and rows [cta_rank * BNH, +BNH) of the B tile.
   const int cta_rank = CG == 2 ? (int)cluster_ctarank() : 0;
   const bool leader = cta_rank == 0;
   const int num_m_units = (p.num_m_blocks + CG - 1) / CG;
   const int num_tiles = num_m_units * p.num_n_blocks;
-  const int work_first = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
-  const int work_step = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
-  const int rot = p.ar_world > 1 ? ar_range_start((p.ar_rank + 1) % p.ar_world, p.num_m_blocks, p.ar_world) : 0;
+  const int work_first = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x - n_pull;
+  const int work_step = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x - n_pull;
+  // tile rows are walked in rotated order: fused all-reduce / reduce-scatter - the rows of the next rank first, the own
+  // last; fused all-gather - the own rows (already local) first
+  const int rot = p.ar_world > 1 ? ar_range_start((p.ar_rank + 1) % p.ar_world, p.num_m_blocks, p.ar_world)
+                                 : (p.ag_world > 1 ? ar_range_start(p.ag_rank, p.num_m_blocks, p.ag_world) : 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; ++s) {
@@ -358,6 +437,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
+      uint32_t ag_opened = 0;
       bool ok = true;
       // CG == 2: both blocks' loads report their bytes to the LEADER's barrier (its address in the cluster window is
       // this block's address with the pair bit cleared); only the leader announces the expected byte count
@@ -367,6 +447,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tile_coords_rot(tile, num_m_units, p.num_n_blocks, rot, m_blk, n_blk);
         m_blk = m_blk * CG + cta_rank;
         const int n_row0 = n_blk * BN + cta_rank * BNH;
+        if (n_pull > 0) {
+          // first tile of a range: its rows must have been copied into the local A (bounded wait on the pull counter);
+          // the copy was written with ordinary stores by other blocks, the loads below go through the async proxy
+          const int o = ar_owner(m_blk, p.num_m_blocks, p.ag_world);
+          if (!((ag_opened >> o) & 1u)) {
+            if (!spin_local_ge(p.ag_pulled + o, p.ag_pull_target)) {
+              atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            ag_opened |= 1u << o;
+          }
+        }
         for (int kb = 0; kb < p.num_k_blocks; ++kb, ++it) {
           const int s = it % L::STAGES;
           const uint32_t ph = (it / L::STAGES) & 1;
@@ -642,7 +737,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       }
     }
     if (p.tma_epi && warp == 2 && lane == 0) tma_store_wait<0>();  // shared memory must outlive the bulk stores
-    if (p.ar_world > 1 && ok && blockIdx.x == 0) {
+    if (p.ar_world > 1 && !p.ar_scatter && ok && work_first == 0) {
       // before the launch completes, the final tiles that the other owners push into my `final` buffer must have
       // landed: each epilogue thread of CTA 0 checks a share of the (tile row, owner) counters
       const int t = (warp - 2) * 32 + lane;
@@ -694,6 +789,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
   int grid = tiles < sm_count() / CG ? tiles : sm_count() / CG;  // thread blocks (CG == 1) or pairs (CG == 2)
   if (max_ctas > 0 && grid > max_ctas / CG) grid = max_ctas / CG > 0 ? max_ctas / CG : 1;
   grid *= CG;
+  if (CG == 1 && p.ag_world > 1) grid += p.ag_pull_ctas;  // the pulling blocks come first and leave when they are done
   GemmParams q = p;
   EpiMaps em = {};  // filled per launch and passed by value: no state shared between host threads
   const int eb = q.out_fp32 ? 4 : 2;
@@ -737,6 +833,15 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
 
 }  // namespace csb
 
+namespace csb {
+static void no_collective(GemmParams& p) {
+  p.ar_scatter = 0; p.ar_row_offset = 0;
+  p.ag_world = 1; p.ag_rank = 0; p.ag_pull_ctas = 0;
+  for (int i = 0; i < 8; ++i) p.ag_src[i] = nullptr;
+  p.ag_dst = nullptr; p.ag_ready = nullptr; p.ag_ready_value = 0; p.ag_pulled = nullptr; p.ag_pull_target = 0;
+}
+}  // namespace csb
+
 // C[M,N] (+)= act(op(A) * op(B)^T + bias).  a_mn_major=0: A is [M][K] with row stride lda;
 // a_mn_major=1: A is [K][M] with row stride lda.  Same for B with N in place of M.
 // Leading dimensions are in elements and must be multiples of 8 (16-byte TMA strides).
@@ -768,6 +873,7 @@ CSB_API int csb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   p.tma_epi = 0;
   p.ar_world = 1; p.ar_rank = 0; p.ar_base = 0; p.ar_slot_elems = 0;
   for (int i = 0; i < 8; ++i) { p.ar_inbox[i] = nullptr; p.ar_final[i] = nullptr; p.ar_cnt_part[i] = nullptr; p.ar_cnt_final[i] = nullptr; }
+  no_collective(p);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define CSB_DISPATCH(BNV)                                                                       \
   if (!a_mn_major && !b_mn_major) return launch_gemm<BNV, false, false>(A, B, p, lda, ldb, max_ctas, s); \
@@ -801,10 +907,10 @@ CSB_API int csb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
 // all four arrays hold `world` device pointers valid on THIS rank (own buffers + peer mappings).
 // `base` = num_n_blocks(of this shape) * number of earlier calls on this set of buffers; a set of buffers serves one
 // (M, N, tile_n) shape, and callers alternate between two sets so a rank never overwrites data a slower peer still reads.
-CSB_API int csb_gemm_allreduce_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
-                                    int a_mn_major, int b_mn_major, int world, int rank, void* const* inbox_ptrs,
-                                    void* const* final_ptrs, void* const* cnt_part_ptrs, void* const* cnt_final_ptrs,
-                                    long slot_elems, int base, int tile_n, int* status, void* stream) {
+static int gemm_allreduce_impl(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                               int a_mn_major, int b_mn_major, int world, int rank, void* const* inbox_ptrs,
+                               void* const* final_ptrs, void* const* cnt_part_ptrs, void* const* cnt_final_ptrs,
+                               long slot_elems, int base, int tile_n, int* status, void* stream, int scatter) {
   using namespace csb;
   if (M <= 0 || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) || (N & 7) || world < 2 || world > 8) return CSB_ERR_BAD_ARG;
   int bn = (tile_n == 128 || tile_n == 256) ? tile_n : ((N >= 256) ? 256 : 128);
@@ -825,6 +931,13 @@ CSB_API int csb_gemm_allreduce_bf16(const void* A, const void* B, void* C, int M
     p.ar_cnt_part[i] = i < world ? reinterpret_cast<int*>(cnt_part_ptrs[i]) : nullptr;
     p.ar_cnt_final[i] = i < world ? reinterpret_cast<int*>(cnt_final_ptrs[i]) : nullptr;
   }
+  no_collective(p);
+  if (scatter) {
+    p.ar_scatter = 1;
+    p.ar_row_offset = ar_range_start(rank, p.num_m_blocks, world) * BM;
+    // the C tensor map covers the owned rows only
+    p.M = M;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
 #define CSB_DISPATCH_AR(BNV)                                                                       \
   if (!a_mn_major && !b_mn_major) return launch_gemm<BNV, false, false>(A, B, p, lda, ldb, 0, s); \
@@ -834,6 +947,64 @@ CSB_API int csb_gemm_allreduce_bf16(const void* A, const void* B, void* C, int M
   if (bn == 256) { CSB_DISPATCH_AR(256) }
   CSB_DISPATCH_AR(128)
 #undef CSB_DISPATCH_AR
+}
+
+CSB_API int csb_gemm_allreduce_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                    int a_mn_major, int b_mn_major, int world, int rank, void* const* inbox_ptrs,
+                                    void* const* final_ptrs, void* const* cnt_part_ptrs, void* const* cnt_final_ptrs,
+                                    long slot_elems, int base, int tile_n, int* status, void* stream) {
+  return gemm_allreduce_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, world, rank, inbox_ptrs, final_ptrs,
+                             cnt_part_ptrs, cnt_final_ptrs, slot_elems, base, tile_n, status, stream, 0);
+}
+
+// Fused GEMM + reduce-scatter: like csb_gemm_allreduce_bf16, but every rank keeps only the sum of the rows it owns
+// (rows [row_begin, row_end) of csb_ar_layout) and nothing is sent back.  C is the OWNED part: [row_end - row_begin][N].
+// final_ptrs / cnt_final_ptrs are not used (pass the same arrays).
+CSB_API int csb_gemm_reducescatter_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                        int a_mn_major, int b_mn_major, int world, int rank, void* const* inbox_ptrs,
+                                        void* const* final_ptrs, void* const* cnt_part_ptrs, void* const* cnt_final_ptrs,
+                                        long slot_elems, int base, int tile_n, int* status, void* stream) {
+  return gemm_allreduce_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, world, rank, inbox_ptrs, final_ptrs,
+                             cnt_part_ptrs, cnt_final_ptrs, slot_elems, base, tile_n, status, stream, 1);
+}
+
+// Fused all-gather + GEMM: C[M,N] = A_full * op(B)^T where A_full [M][K] (K-major) is sharded by rows over `world`
+// ranks (range r of csb_ar_layout on rank r).  shard_ptrs[r] = rank r's shard (peer-mapped, row pitch K); a_full = local
+// [M][K] buffer that the kernel fills (and that the caller may keep, e.g. for the weight gradient); ready = local
+// int[world] counters (rank r stores ready_value there once its shard is staged); pulled = local int[world] counters,
+// zero at start, advanced by pull_ctas per call: pass pull_target = pull_ctas * (number of calls so far, this one included).
+CSB_API int csb_ag_gemm_bf16(void* const* shard_ptrs, void* a_full, const void* B, void* C, int M, int N, int K, int ldb,
+                             int ldc, int b_mn_major, int world, int rank, const int* ready, int ready_value, int* pulled,
+                             int pull_target, int pull_ctas, int tile_n, int* status, void* stream) {
+  using namespace csb;
+  if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || (ldb & 7) || world < 2 || world > 8 || pull_ctas < 1 || pull_ctas > 64)
+    return CSB_ERR_BAD_ARG;
+  if ((reinterpret_cast<uintptr_t>(a_full) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return CSB_ERR_BAD_ARG;
+  int bn = (tile_n == 128 || tile_n == 256) ? tile_n : ((N >= 256) ? 256 : 128);
+  GemmParams p;
+  p.C = C; p.bias = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc;
+  p.out_fp32 = 0; p.accumulate = 0; p.act = 0;
+  p.num_m_blocks = (M + BM - 1) / BM;
+  p.num_n_blocks = (N + bn - 1) / bn;
+  p.num_k_blocks = (K + BK - 1) / BK;
+  if (p.num_m_blocks < world) return CSB_ERR_TOO_LARGE;
+  p.status = status;
+  p.tma_epi = 0;
+  p.ar_world = 1; p.ar_rank = 0; p.ar_base = 0; p.ar_slot_elems = 0;
+  for (int i = 0; i < 8; ++i) { p.ar_inbox[i] = nullptr; p.ar_final[i] = nullptr; p.ar_cnt_part[i] = nullptr; p.ar_cnt_final[i] = nullptr; }
+  no_collective(p);
+  p.ag_world = world; p.ag_rank = rank; p.ag_pull_ctas = pull_ctas;
+  for (int i = 0; i < 8; ++i) p.ag_src[i] = reinterpret_cast<const uint4*>(shard_ptrs[i < world ? i : 0]);
+  p.ag_dst = reinterpret_cast<uint4*>(a_full);
+  p.ag_ready = ready; p.ag_ready_value = ready_value; p.ag_pulled = pulled; p.ag_pull_target = pull_target;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 256) {
+    if (b_mn_major) return launch_gemm<256, false, true>(a_full, B, p, K, ldb, 0, s);
+    return launch_gemm<256, false, false>(a_full, B, p, K, ldb, 0, s);
+  }
+  if (b_mn_major) return launch_gemm<128, false, true>(a_full, B, p, K, ldb, 0, s);
+  return launch_gemm<128, false, false>(a_full, B, p, K, ldb, 0, s);
 }
 
 // Rows [row_begin, row_end) of an M-row output that rank `rank` of `world` owns in the fused all-reduce,

@@ -13,7 +13,9 @@
 
 namespace csb {
 
-enum MaskMode : int { MASK_FULL = 0, MASK_CAUSAL = 1, MASK_BITFIELD = 2, MASK_BITFIELD_PREFIX_CAUSAL = 3 };
+// MASK_DENSE: a boolean [B][Sq][Sk] byte matrix decides (read by the kernels for tiles of class 1); the predicate below
+// is not used for it.
+enum MaskMode : int { MASK_FULL = 0, MASK_CAUSAL = 1, MASK_BITFIELD = 2, MASK_BITFIELD_PREFIX_CAUSAL = 3, MASK_DENSE = 4 };
 
 constexpr int64_t BITFIELD_LOW62 = (int64_t(1) << 62) - 1;
 

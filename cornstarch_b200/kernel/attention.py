@@ -1,14 +1,12 @@
 """``flash_attn_func`` with a dense boolean mask (the reference's cornstarch/kernel/attention.py:1126-1147), and the
 packed variable-length entry points.
 
-A dense ``[B, Sq, Sk]`` mask cannot be expressed as a bitfield in general, so this entry point runs the
-math in PyTorch (fp32 softmax) when a mask is given; with ``mask=None`` it is full attention on the
-tcgen05 kernel.  Multimodal training uses the bitfield path, which is the fused one.
+A dense ``[B, Sq, Sk]`` mask cannot be expressed as a bitfield in general: the kernels take it as a byte matrix
+(mask mode ``MASK_DENSE``), classify its 128 x 128 tiles once and read it only inside tiles that mix allowed and
+masked pairs; an additive bias is added to the scores in the kernel.  Multimodal training uses the bitfield path.
 """
 
 from __future__ import annotations
-
-import math
 
 import torch
 
@@ -16,25 +14,13 @@ from ..ops import attention as A
 
 
 def flash_attn_func(q, k, v, bias=None, mask=None, softmax_scale=None):
-    """``q, k, v``: ``[B, S, H, D]``; ``mask``: bool ``[B, Sq, Sk]`` (True = attend); ``bias`` broadcastable to ``[B, H, Sq, Sk]``."""
+    """``q, k, v``: ``[B, S, H, D]``; ``mask``: bool ``[B, Sq, Sk]`` (True = attend); ``bias`` broadcastable to ``[B, H, Sq, Sk]``
+    (no gradient flows to it, as in the reference).  Runs on the attention kernels: the dense mask is read tile by tile
+    (tiles without an allowed pair are skipped, tiles with every pair allowed skip the mask), the bias is added to the
+    scores inside the kernel."""
     if mask is None and bias is None:
         return A.attention(q, k, v, A.AttnMask.full(), softmax_scale)
-    scale = softmax_scale or 1.0 / math.sqrt(q.shape[-1])
-    g = q.shape[2] // k.shape[2]
-    qf = q.permute(0, 2, 1, 3).float()
-    kf = k.permute(0, 2, 1, 3).float().repeat_interleave(g, dim=1)
-    vf = v.permute(0, 2, 1, 3).float().repeat_interleave(g, dim=1)
-    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
-    if bias is not None:
-        s = s + bias.float()
-    if mask is not None:
-        m = mask[:, None].bool()
-        s = s.masked_fill(~m, float("-inf"))
-    lse = torch.logsumexp(s, dim=-1, keepdim=True)
-    p = torch.exp(s - torch.where(torch.isinf(lse), torch.zeros_like(lse), lse))
-    if mask is not None:
-        p = torch.where(m, p, torch.zeros_like(p))
-    return torch.matmul(p, vf).permute(0, 2, 1, 3).to(q.dtype)
+    return A.attention(q, k, v, A.AttnMask.from_dense(mask, bias), softmax_scale)
 
 
 _MAX_PACKED_SEQUENCES = 60  # one mask bit per packed sequence; bit 0 is the text (causal) bit

@@ -27,7 +27,7 @@ import torch.nn.functional as F
 
 from . import _native as nat
 
-MASK_FULL, MASK_CAUSAL, MASK_BITFIELD, MASK_BITFIELD_PREFIX_CAUSAL = 0, 1, 2, 3
+MASK_FULL, MASK_CAUSAL, MASK_BITFIELD, MASK_BITFIELD_PREFIX_CAUSAL, MASK_DENSE = 0, 1, 2, 3, 4
 _LOW62 = (1 << 62) - 1
 BLOCK = 128
 
@@ -42,6 +42,15 @@ nat.declare(
     "csb_attn_bwd",
     [vp] * 11 + [i32] * 6 + [i64] * 16 + [f32, i32, vp, vp, vp, vp, vp, vp, vp],
 )
+nat.declare("csb_mask_classify_dense", [vp, i64, i64, i32, i32, i32, vp, vp, vp])
+nat.declare("csb_attn_fwd_dense", [vp] * 5 + [i32] * 6 + [i64] * 8 + [f32, i32, vp, vp, vp, vp])
+nat.declare("csb_attn_bwd_dense", [vp] * 11 + [i32] * 6 + [i64] * 16 + [f32, i32, vp, vp, vp, vp])
+
+
+class _Extras(C.Structure):
+    """``CsbAttnExtras`` of the native library: dense boolean mask and additive bias of one attention call."""
+
+    _fields_ = [("dmask", vp), ("dm_sb", i64), ("dm_sq", i64), ("bias", vp), ("bias_sb", i64), ("bias_sh", i64), ("bias_sq", i64)]
 
 
 @dataclass
@@ -53,6 +62,8 @@ class AttnMask:
     k_bits: torch.Tensor | None = None  # int64 [B, Sk]
     q_pos: torch.Tensor | None = None  # int32 [B, Sq] global positions of the local query rows
     k_pos: torch.Tensor | None = None  # int32 [B, Sk]
+    dense: torch.Tensor | None = None  # bool / uint8 [B, Sq, Sk] (True = attend), mode MASK_DENSE
+    bias: torch.Tensor | None = None  # additive, broadcastable to [B, H, Sq, Sk] (no gradient), with MASK_FULL or MASK_DENSE
     _cls: dict = field(default_factory=dict, repr=False)
 
     @staticmethod
@@ -71,6 +82,48 @@ class AttnMask:
             q_bits=bits, k_bits=bits if k_bits is None else k_bits, q_pos=q_pos, k_pos=k_pos,
         )
 
+    @staticmethod
+    def from_dense(mask: torch.Tensor | None, bias: torch.Tensor | None = None) -> "AttnMask":
+        """Flash attention with a dense boolean mask ``[B, Sq, Sk]`` and / or an additive bias (the reference's
+        ``flash_attn_func(q, k, v, bias, mask)``, cornstarch/kernel/attention.py:1126-1147)."""
+        if mask is None:
+            return AttnMask(mode=MASK_FULL, bias=bias)
+        if mask.dim() == 4:
+            assert mask.shape[1] == 1, "a dense mask is shared by all heads"
+            mask = mask[:, 0]
+        return AttnMask(mode=MASK_DENSE, dense=mask, bias=bias)
+
+    def extras(self, B: int, H: int, Sq: int, Sk: int, device, with_bias: bool = True):
+        """ctypes ``CsbAttnExtras`` (plus the tensors it points to, which the caller keeps alive) or ``(None, ())``."""
+        if self.dense is None and (self.bias is None or not with_bias):
+            return None, ()
+        keep = []
+        ex = _Extras()
+        if self.dense is not None:
+            m = self._cls.get("dense_u8")
+            if m is None:
+                m = self.dense.to(device=device).ne(0).to(torch.uint8)
+                if m.shape[0] == 1 and B > 1:
+                    m = m.expand(B, -1, -1)
+                m = m.contiguous()
+                self._cls["dense_u8"] = m
+            assert m.shape == (B, Sq, Sk), f"dense mask {tuple(m.shape)} does not match {(B, Sq, Sk)}"
+            ex.dmask, ex.dm_sb, ex.dm_sq = m.data_ptr(), m.stride(0), m.stride(1)
+            keep.append(m)
+        if self.bias is not None and with_bias:
+            bz = self._cls.get("bias_f32")
+            if bz is None:
+                bz = self.bias.to(device=device, dtype=torch.float32)
+                while bz.dim() < 4:
+                    bz = bz.unsqueeze(0)
+                if bz.stride(-1) != 1:
+                    bz = bz.contiguous()
+                self._cls["bias_f32"] = bz
+            e = bz.expand(B, H, Sq, Sk)
+            ex.bias, ex.bias_sb, ex.bias_sh, ex.bias_sq = bz.data_ptr(), e.stride(0), e.stride(1), e.stride(2)
+            keep.append(bz)
+        return ex, tuple(keep)
+
     def classes(self, B: int, Sq: int, Sk: int, device) -> torch.Tensor:
         """int8 ``[B, nQ, nK]`` tile classes for 128x128 tiles (0 skip, 1 mixed, 2 all allowed); cached."""
         key = (B, Sq, Sk, str(device))
@@ -88,6 +141,8 @@ def dense_mask(mask: AttnMask, B: int, Sq: int, Sk: int, device="cpu") -> torch.
     qp, kp = qp[:, :, None], kp[:, None, :]
     if mask.mode == MASK_FULL:
         return torch.ones(B, Sq, Sk, dtype=torch.bool, device=device)
+    if mask.mode == MASK_DENSE:
+        return mask.dense.to(device).ne(0).expand(B, Sq, Sk)
     if mask.mode == MASK_CAUSAL:
         return (kp <= qp).expand(B, Sq, Sk).clone()
     qb = (mask.q_bits.to(device) & _LOW62)[:, :, None]
@@ -120,6 +175,12 @@ def classify_mask(mask: AttnMask, B: int, Sq: int, Sk: int, device, bm: int = BL
         return cls
     cls = torch.empty(B, nQ, nK, dtype=torch.int8, device=dev)
     work = torch.zeros(B, nQ, dtype=torch.int32, device=dev) if with_work else None
+    if mask.mode == MASK_DENSE:
+        assert bm == BLOCK and bn == BLOCK, "dense masks are classified in 128 x 128 tiles"
+        ex, keep = mask.extras(B, 1, Sq, Sk, dev, with_bias=False)
+        nat.check(nat.lib().csb_mask_classify_dense(ex.dmask, ex.dm_sb, ex.dm_sq, B, Sq, Sk, cls.data_ptr(), nat.ptr(work),
+                                                    nat.stream()), "csb_mask_classify_dense")
+        return (cls, work) if with_work else cls
     qb, kb, qp, kp = _mask_ptrs(mask, B)
     nat.check(
         nat.lib().csb_mask_classify(mask.mode, nat.ptr(qb), nat.ptr(kb), nat.ptr(qp), nat.ptr(kp), B, Sq, Sk, bm, bn,
@@ -139,6 +200,8 @@ def attention_reference(q, k, v, mask: AttnMask, scale: float | None = None):
     kf = k.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
     vf = v.float().permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if mask.bias is not None:
+        s = s + mask.bias.to(device=q.device, dtype=torch.float32)
     m = dense_mask(mask, B, Sq, Sk, q.device)[:, None]
     s = s.masked_fill(~m, float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
@@ -178,8 +241,19 @@ def attention_forward(q, k, v, mask: AttnMask, scale: float | None = None):
     out = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
     cls = mask.classes(B, Sq, Sk, q.device)
-    qb, kb, qp, kp = _mask_ptrs(mask, B)
     st = nat.status_word(q.device)
+    ex, keep = mask.extras(B, Hq, Sq, Sk, q.device)
+    if ex is not None:
+        nat.check(
+            nat.lib().csb_attn_fwd_dense(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), B, Sq, Sk, Hq, Hk, D,
+                q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0), out.stride(1), out.stride(0),
+                scale, mask.mode, cls.data_ptr(), C.addressof(ex), st.data_ptr(), nat.stream(),
+            ),
+            "csb_attn_fwd_dense",
+        )
+        return out, lse
+    qb, kb, qp, kp = _mask_ptrs(mask, B)
     nat.check(
         nat.lib().csb_attn_fwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), B, Sq, Sk, Hq, Hk, D,
@@ -205,8 +279,21 @@ def attention_backward(do, q, k, v, out, lse, mask: AttnMask, scale: float | Non
     dq_acc = torch.zeros((B, Sq, Hq, D), dtype=torch.float32, device=q.device)
     delta = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
     cls = mask.classes(B, Sq, Sk, q.device)
-    qb, kb, qp, kp = _mask_ptrs(mask, B)
     st = nat.status_word(q.device)
+    ex, keep = mask.extras(B, Hq, Sq, Sk, q.device)
+    if ex is not None:
+        nat.check(
+            nat.lib().csb_attn_bwd_dense(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                dq_acc.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, Sq, Sk, Hq, Hk, D,
+                q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0), out.stride(1), out.stride(0),
+                do.stride(1), do.stride(0), dq.stride(1), dq.stride(0), dk.stride(1), dk.stride(0), dv.stride(1),
+                dv.stride(0), scale, mask.mode, cls.data_ptr(), C.addressof(ex), st.data_ptr(), nat.stream(),
+            ),
+            "csb_attn_bwd_dense",
+        )
+        return dq, dk, dv
+    qb, kb, qp, kp = _mask_ptrs(mask, B)
     nat.check(
         nat.lib().csb_attn_bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), do.data_ptr(), lse.data_ptr(), delta.data_ptr(),
@@ -287,6 +374,13 @@ def attention_library(q, k, v, mask: AttnMask, scale=None) -> torch.Tensor:
     qh, kh, vh = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
     gqa = q.shape[2] != k.shape[2]
     plain = mask.q_pos is None and mask.k_pos is None
+    if mask.bias is not None or mask.mode == MASK_DENSE:
+        am = mask.bias.to(q.dtype) if mask.bias is not None else None
+        if mask.mode == MASK_DENSE:
+            keep = dense_mask(mask, B, Sq, Sk, q.device)[:, None]
+            am = keep if am is None else am.masked_fill(~keep, float("-inf"))
+        o = torch.nan_to_num(F.scaled_dot_product_attention(qh, kh, vh, attn_mask=am, scale=scale, enable_gqa=gqa))
+        return o.transpose(1, 2)
     if mask.mode == MASK_CAUSAL and plain and Sq == Sk:
         o = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, scale=scale, enable_gqa=gqa)
     elif mask.mode == MASK_FULL:
