@@ -36,7 +36,7 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 // sign = +1 forward, -1 backward (the transpose of a rotation).
 __global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const float* __restrict__ cos_t,
                             const float* __restrict__ sin_t, const int* __restrict__ pos_ids, long T, int S,
-                            int row_stride, int n_heads, int D, int rot_dim, float sign) {
+                            int row_stride, int n_heads, int D, int rot_dim, float sign, int table_rows) {
   const int half = rot_dim / 2;
   const int vec_per_head = half / 8;
   const long total = T * n_heads * vec_per_head;
@@ -46,6 +46,7 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const float* __rest
     const int hd = th % n_heads;
     const long t = th / n_heads;
     const int pos = pos_ids ? pos_ids[t] : static_cast<int>(t % S);
+    if (!CSB_IN_BOUNDS(pos, table_rows, BND_ROPE_POS)) continue;
     __nv_bfloat16* p = buf + t * row_stride + hd * D + vc * 8;
     uint4 u1 = *reinterpret_cast<uint4*>(p);
     uint4 u2 = *reinterpret_cast<uint4*>(p + half);
@@ -429,12 +430,14 @@ __global__ void __launch_bounds__(512) ce_grad_kernel(__nv_bfloat16* __restrict_
 // ------------------------------------------------------------------------------------ embedding + modality merge
 // out[t] = src[t] >= 0 ? embed[src[t]] : feats[-src[t] - 1]
 __global__ void gather_merge_kernel(const __nv_bfloat16* __restrict__ embed, const __nv_bfloat16* __restrict__ feats,
-                                    const int* __restrict__ src, __nv_bfloat16* __restrict__ out, long T, int H) {
+                                    const int* __restrict__ src, __nv_bfloat16* __restrict__ out, long T, int H,
+                                    long n_embed, long n_feats) {
   const int vec = H / 8;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < T * vec; i += (long)gridDim.x * blockDim.x) {
     const long t = i / vec;
     const int c = (i % vec) * 8;
     const int s = src[t];
+    if (s >= 0 ? !CSB_IN_BOUNDS(s, n_embed, BND_EMBED_ROW) : !CSB_IN_BOUNDS(-(long)s - 1, n_feats, BND_FEAT_ROW)) continue;
     const __nv_bfloat16* p = s >= 0 ? embed + static_cast<size_t>(s) * H : feats + static_cast<size_t>(-s - 1) * H;
     *reinterpret_cast<uint4*>(out + t * H + c) = *reinterpret_cast<const uint4*>(p + c);
   }
@@ -443,12 +446,13 @@ __global__ void gather_merge_kernel(const __nv_bfloat16* __restrict__ embed, con
 template <typename GradT>
 __global__ void scatter_merge_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const int* __restrict__ src,
                                          GradT* __restrict__ d_embed, __nv_bfloat16* __restrict__ d_feats, long T,
-                                         int H) {
+                                         int H, long n_embed, long n_feats) {
   const int vec = H / 8;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < T * vec; i += (long)gridDim.x * blockDim.x) {
     const long t = i / vec;
     const int c = (i % vec) * 8;
     const int s = src[t];
+    if (s >= 0 ? !CSB_IN_BOUNDS(s, n_embed, BND_EMBED_ROW) : !CSB_IN_BOUNDS(-(long)s - 1, n_feats, BND_FEAT_ROW)) continue;
     const uint4 u = *reinterpret_cast<const uint4*>(dout + t * H + c);
     if (s < 0) {
       if (d_feats) *reinterpret_cast<uint4*>(d_feats + static_cast<size_t>(-s - 1) * H + c) = u;
@@ -492,12 +496,14 @@ static inline int ew_grid(long work, int threads) {
   return (int)(g < cap ? (g > 0 ? g : 1) : cap);
 }
 
+// table_rows: rows of the cos / sin tables (what positions are checked against in the bounds-checked build).
 CSB_API int csb_rope(void* buf, const float* cos_t, const float* sin_t, const int* pos_ids, long T, int S,
-                     int row_stride, int n_heads, int D, int rot_dim, float sign, void* stream) {
+                     int row_stride, int n_heads, int D, int rot_dim, float sign, int table_rows, void* stream) {
   if (rot_dim % 16 != 0 || rot_dim > D || (row_stride % 8) || (D % 8)) return CSB_ERR_BAD_ARG;
+  if (pos_ids == nullptr && S > table_rows) return CSB_ERR_BAD_ARG;  // implicit positions 0..S-1 must fit the tables
   const long work = T * n_heads * (rot_dim / 16);
   rope_kernel<<<ew_grid(work, 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<__nv_bfloat16*>(buf), cos_t, sin_t, pos_ids, T, S, row_stride, n_heads, D, rot_dim, sign);
+      reinterpret_cast<__nv_bfloat16*>(buf), cos_t, sin_t, pos_ids, T, S, row_stride, n_heads, D, rot_dim, sign, table_rows);
   return launch_result();
 }
 
@@ -604,26 +610,30 @@ CSB_API int csb_ce_grad(void* logits, long ld, const long* labels, int V, int vo
   return launch_result();
 }
 
+// n_embed / n_feats: rows of the embedding table and of the feature matrix (what the indices in src are checked against
+// in the bounds-checked build).
 CSB_API int csb_gather_merge(const void* embed, const void* feats, const int* src, void* out, long T, int H,
-                             void* stream) {
+                             long n_embed, long n_feats, void* stream) {
   if (H % 8) return CSB_ERR_BAD_ARG;
   gather_merge_kernel<<<ew_grid(T * (H / 8), 256), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(embed), reinterpret_cast<const __nv_bfloat16*>(feats), src,
-      reinterpret_cast<__nv_bfloat16*>(out), T, H);
+      reinterpret_cast<__nv_bfloat16*>(out), T, H, n_embed, n_feats);
   return launch_result();
 }
 CSB_API int csb_scatter_merge_bwd(const void* dout, const int* src, void* d_embed, int embed_fp32, void* d_feats,
-                                  long T, int H, void* stream) {
+                                  long T, int H, long n_embed, long n_feats, void* stream) {
   if (H % 8) return CSB_ERR_BAD_ARG;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int grid = ew_grid(T * (H / 8), 256);
   if (embed_fp32)
     scatter_merge_bwd_kernel<float><<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(dout), src,
                                                          reinterpret_cast<float*>(d_embed),
-                                                         reinterpret_cast<__nv_bfloat16*>(d_feats), T, H);
+                                                         reinterpret_cast<__nv_bfloat16*>(d_feats), T, H, n_embed, n_feats);
   else
     scatter_merge_bwd_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(dout), src,
                                                                  reinterpret_cast<__nv_bfloat16*>(d_embed),
-                                                                 reinterpret_cast<__nv_bfloat16*>(d_feats), T, H);
+                                                                 reinterpret_cast<__nv_bfloat16*>(d_feats), T, H, n_embed, n_feats);
   return launch_result();
 }
+
+CSB_BOUNDS_STATUS_GETTER(elementwise)

@@ -21,7 +21,7 @@
 #include "ptx.cuh"
 
 #ifndef CSB_GEMM_DEFAULT_CG
-#define CSB_GEMM_DEFAULT_CG 1
+#define CSB_GEMM_DEFAULT_CG 2
 #endif
 
 namespace csb {
@@ -116,8 +116,11 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t phase, vol
   return false;
 }
 
+// Tiles are walked in groups of GROUP_M tile rows (all columns of a group before the next group), so that the thread
+// blocks running at one time share few rows of A and few columns of B (L2 reuse).  16 rows of 128 measured 2.7 % faster
+// than 8 at 8192 x 8192 x 4096 with one thread block per tile; pairs (rows of 256) keep 8.
+template <int GROUP_M>
 __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& m_blk, int& n_blk) {
-  constexpr int GROUP_M = 8;
   const int per_group = GROUP_M * num_n;
   const int group = tile / per_group;
   const int first_m = group * GROUP_M;
@@ -129,8 +132,9 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 
 // Rotated order for the fused all-reduce: the tile-row index is shifted so that a rank starts with the
 // rows owned by the next rank and finishes with its own.
+template <int GROUP_M>
 __device__ __forceinline__ void tile_coords_rot(int tile, int num_m, int num_n, int rot, int& m_blk, int& n_blk) {
-  tile_coords(tile, num_m, num_n, m_blk, n_blk);
+  tile_coords<GROUP_M>(tile, num_m, num_n, m_blk, n_blk);
   m_blk += rot;
   if (m_blk >= num_m) m_blk -= num_m;
 }
@@ -444,7 +448,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       constexpr uint32_t LEADER_MASK = CG == 2 ? 0xFEFFFFFFu : 0xFFFFFFFFu;
       for (int tile = work_first; tile < num_tiles && ok; tile += work_step) {
         int m_blk, n_blk;
-        tile_coords_rot(tile, num_m_units, p.num_n_blocks, rot, m_blk, n_blk);
+        tile_coords_rot<(CG == 2 ? 8 : 16)>(tile, num_m_units, p.num_n_blocks, rot, m_blk, n_blk);
         m_blk = m_blk * CG + cta_rank;
         const int n_row0 = n_blk * BN + cta_rank * BNH;
         if (n_pull > 0) {
@@ -546,7 +550,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     bool ok = true;
     for (int tile = work_first; tile < num_tiles && ok; tile += work_step, ++local_tile) {
       int m_blk, n_blk;
-      tile_coords_rot(tile, num_m_units, p.num_n_blocks, rot, m_blk, n_blk);
+      tile_coords_rot<(CG == 2 ? 8 : 16)>(tile, num_m_units, p.num_n_blocks, rot, m_blk, n_blk);
       m_blk = m_blk * CG + cta_rank;
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;

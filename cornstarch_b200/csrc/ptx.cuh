@@ -39,6 +39,29 @@ __device__ __forceinline__ uint64_t wait_limit_ns() { return *reinterpret_cast<v
     return (int)cudaMemcpyToSymbol(csb::g_wait_ns, &ns, sizeof(ns));               \
   }
 
+// Bounds-checked debug build (-DCSB_BOUNDS_CHECK, `python -m cornstarch_b200.csrc.build --bounds-check`): every index
+// that a kernel takes from DATA (token ids, source rows, positions) is compared with the extent its entry point was
+// given.  A violation records a code (first one wins) and the access is skipped, so a bad index never reaches memory;
+// the host reads and clears the record with csb_bounds_status().  The release build compiles the checks away.
+#ifdef CSB_BOUNDS_CHECK
+static __device__ int g_bounds_status = 0;
+#define CSB_IN_BOUNDS(idx, extent, code) \
+  (((long)(idx) >= 0 && (long)(idx) < (long)(extent)) ? true : (atomicCAS(&csb::g_bounds_status, 0, (code)), false))
+#define CSB_BOUNDS_STATUS_GETTER(tu)                                                        \
+  extern "C" int csb_bounds_status_##tu() {                                                 \
+    int v = 0, z = 0;                                                                       \
+    if (cudaMemcpyFromSymbol(&v, csb::g_bounds_status, sizeof(v)) != cudaSuccess) return -1; \
+    cudaMemcpyToSymbol(csb::g_bounds_status, &z, sizeof(z));                                \
+    return v;                                                                               \
+  }
+#else
+#define CSB_IN_BOUNDS(idx, extent, code) true
+#define CSB_BOUNDS_STATUS_GETTER(tu) \
+  extern "C" int csb_bounds_status_##tu() { return 0; }
+#endif
+// violation codes
+enum : int { BND_EMBED_ROW = 101, BND_FEAT_ROW = 102, BND_ROPE_POS = 103, BND_MOE_SRC_ROW = 104 };
+
 // 2^x on the special-function unit (one MUFU.EX2; -inf -> 0, flushes denormals).
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -254,15 +277,15 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
                : "memory");
 }
 // CG == 2: the MMAs were issued for a CTA pair; the barrier at this shared-memory offset is signalled in BOTH thread
-// blocks of the pair (one commit per block: the own barrier, then the peer's through its cluster address).
+// blocks of the pair by ONE commit whose arrival is multicast to the two blocks (cta mask 0b11).  This is a barrier
+// signal between the two SMs of the pair - no data is copied and no load is involved.  (Two separate commits, one per
+// block, cost 12 % of the MMA rate in a measurement without loads: 1.69 against 1.90 PFLOP/s.)
 template <int CG>
 __device__ __forceinline__ void umma_commit_cg(uint64_t* bar) {
   if constexpr (CG == 2) {
-    const uint32_t own = smem_u32(bar);
-    uint32_t peer;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(own), "r"(cluster_ctarank() ^ 1u));
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(own) : "memory");
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(peer) : "memory");
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(static_cast<uint16_t>(3))
+                 : "memory");
   } else {
     umma_commit(bar);
   }

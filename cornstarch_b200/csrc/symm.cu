@@ -59,3 +59,22 @@ CSB_API int csb_set_wait_ns(unsigned long long ns) {
   if ((e = csb_set_wait_ns_gemm(ns))) return e;
   return csb_set_wait_ns_grad_reduce(ns);
 }
+
+// Bounds-checked build: first index violation recorded by a kernel since the last call on the CURRENT device
+// (0 = none; codes in ptx.cuh), cleared by the call.  The release build always answers 0; csb_bounds_check_enabled()
+// tells which build this is.  Both calls synchronise the device.
+extern "C" int csb_bounds_status_elementwise();
+extern "C" int csb_bounds_status_moe_dispatch();
+CSB_API int csb_bounds_status() {
+  cudaDeviceSynchronize();
+  const int a = csb_bounds_status_elementwise();
+  const int b = csb_bounds_status_moe_dispatch();
+  return a ? a : b;
+}
+CSB_API int csb_bounds_check_enabled() {
+#ifdef CSB_BOUNDS_CHECK
+  return 1;
+#else
+  return 0;
+#endif
+}

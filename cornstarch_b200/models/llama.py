@@ -25,7 +25,8 @@ from .. import nn as cnn
 from ..ops import attention as A
 from ..ops import elementwise as E
 from ..ops.cross_entropy import linear_cross_entropy
-from ..ops.linear import add_adapter_deltas, linear, multi_linear
+from ..nn import _fused_tp
+from ..ops.linear import add_adapter_deltas, ag_linear, linear, multi_linear, rs_linear
 from ..parallel import comm
 from ..parallel.dp_fused import layer_input as grad_sync_layer_input
 from .base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, register_model
@@ -126,12 +127,27 @@ def decoder_spec(config) -> DecoderSpec:
 class ParallelContext:
     """Process groups a model shard works with (all optional)."""
 
-    def __init__(self, tp_group=None, sp_group=None, sp_mode: str | None = None, cp_dist_mode=None, parallel_output=True):
+    def __init__(self, tp_group=None, sp_group=None, sp_mode: str | None = None, cp_dist_mode=None, parallel_output=True,
+                 tp_seq_shard: bool | None = None):
         self.tp_group = tp_group
         self.sp_group = sp_group
         self.sp_mode = sp_mode  # None | "ring_attn" | "all_to_all"
         self.cp_dist_mode = cp_dist_mode
         self.parallel_output = parallel_output
+        if tp_seq_shard is None:
+            import os
+
+            tp_seq_shard = os.environ.get("CORNSTARCH_B200_TP_SEQ_SHARD", "0") == "1"
+        # token-sharded activations between the tensor-parallel blocks (see ops/linear.py: ag_linear / rs_linear)
+        self.tp_seq_shard = bool(tp_seq_shard)
+
+    def seq_shard_group(self, tokens: int, hidden_like: torch.Tensor):
+        """The tensor-parallel group when a ``tokens``-row activation can be token-sharded over it (whole 128-row tiles
+        per rank on CUDA, an even split elsewhere), else ``None``: the layer then keeps replicated activations."""
+        if not self.tp_seq_shard or self.tp_group is None or self.tp_size < 2 or (self.sp_mode and self.sp_size > 1):
+            return None
+        unit = 128 * self.tp_size if hidden_like.is_cuda else self.tp_size
+        return self.tp_group if tokens % unit == 0 else None
 
     @property
     def tp_size(self):
@@ -185,10 +201,17 @@ class Attention(nn.Module):
         self.pc: ParallelContext | None = None
         self.attn_impl = None  # set by context parallelism
 
-    def forward(self, x, rope, pos, mask: A.AttnMask):
+    def forward(self, x, rope, pos, mask: A.AttnMask, full_shape=None):
+        """``full_shape = (B, S, group)``: ``x`` holds this rank's token rows of a ``[B, S]`` batch (token-sharded tensor
+        parallelism); the q|k|v projection gathers the rows inside its GEMM, ``o_proj`` scatters them again."""
         B, S, _ = x.shape
         D, Hq, Hk = self.head_dim, self.num_heads, self.num_kv_heads
-        if self.spec.fused_names:
+        sharded = full_shape is not None
+        if sharded:
+            B, S, tp_group = full_shape
+            ws = [self.qkv_proj.weight] if self.spec.fused_names else [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight]
+            qkv = ag_linear(x, ws, tp_group, _fused_tp(tp_group, x)).view(B, S, -1)
+        elif self.spec.fused_names:
             qkv = self.qkv_proj(x)
         else:
             xin = self.q_proj.input_hook(x)
@@ -221,6 +244,8 @@ class Attention(nn.Module):
         o = o.reshape(B, S, Hq * D)
         if ulysses:
             o = comm.all_to_all_comm(o, self.pc.sp_group, 1, 2)
+        if sharded:
+            return rs_linear(o, self.o_proj.weight, tp_group, _fused_tp(tp_group, o)).unsqueeze(0)
         return self.o_proj(o)
 
 
@@ -238,7 +263,12 @@ class MLP(nn.Module):
             self.up_proj = cnn.Linear(H, I, bias=bias)
         self.down_proj = cnn.Linear(I, H, bias=bias)
 
-    def forward(self, x):
+    def forward(self, x, tp_group=None):
+        if tp_group is not None:
+            # token-sharded input: gather inside the gate|up GEMM, scatter inside the down GEMM
+            ws = [self.gate_up_proj.weight] if self.fused else [self.gate_proj.weight, self.up_proj.weight]
+            gu = ag_linear(x, ws, tp_group, _fused_tp(tp_group, x))
+            return rs_linear(E.glu(gu, self.act), self.down_proj.weight, tp_group, _fused_tp(tp_group, gu)).unsqueeze(0)
         if self.fused:
             gu = self.gate_up_proj(x)
         else:
@@ -273,19 +303,34 @@ class DecoderLayer(nn.Module):
             self.pre_feedforward_layernorm = cnn.RMSNorm(config.hidden_size, eps, off)
             self.post_feedforward_layernorm = cnn.RMSNorm(config.hidden_size, eps, off)
 
-    def _ffn(self, x):
+    def _ffn(self, x, tp_group=None):
         if self.spec.moe == "mixtral":
             return self.block_sparse_moe(x)
-        out = self.mlp(x)
+        out = self.mlp(x, tp_group) if tp_group is not None else self.mlp(x)
         return out if isinstance(out, tuple) else (out, None)
 
-    def forward(self, delta, residual, rope, pos, mask):
-        """``delta`` is the previous sub-layer output still to be added to the stream ``residual`` (None at a stage start)."""
+    def supports_seq_shard(self) -> bool:
+        """Token-sharded tensor parallelism covers dense blocks whose projections carry no bias."""
+        a = self.self_attn
+        if self.spec.moe or not isinstance(getattr(self, "mlp", None), MLP):
+            return False
+        lins = [a.o_proj, self.mlp.down_proj] + ([a.qkv_proj] if self.spec.fused_names else [a.q_proj, a.k_proj, a.v_proj])
+        lins += [self.mlp.gate_up_proj] if self.mlp.fused else [self.mlp.gate_proj, self.mlp.up_proj]
+        return all(l.bias is None and not hasattr(l, "delta") for l in lins)
+
+    def forward(self, delta, residual, rope, pos, mask, full_shape=None):
+        """``delta`` is the previous sub-layer output still to be added to the stream ``residual`` (None at a stage start).
+        ``full_shape = (B, S, group)``: ``delta`` / ``residual`` hold this rank's token rows only (``[1, B*S/tp, H]``)."""
         if residual is None:
             residual = delta
             x = self.input_layernorm(delta)
         else:
             x, residual = self.input_layernorm(delta, residual)
+        if full_shape is not None:
+            a = self.self_attn(x, rope, pos, mask, full_shape)
+            x, residual = self.post_attention_layernorm(a, residual)
+            m, aux = self._ffn(x, full_shape[2])
+            return m, residual, aux
         a = self.self_attn(x, rope, pos, mask)
         if self.spec.sandwich_norm:
             a = self.post_attention_layernorm(a)
@@ -343,6 +388,19 @@ class DecoderModel(PreTrainedModel):
                     layer.self_attn.q_norm.grad_sum_group = pc.tp_group
                     layer.self_attn.k_norm.grad_sum_group = pc.tp_group
 
+    def _mark_partial_grad_norms(self, group) -> None:
+        """Under token-sharded tensor parallelism a norm weight sees 1/tp of the tokens on each rank: its gradient is a
+        partial sum.  The optimizer adds the parts over ``group`` once per step (``FusedAdamW._reduce_partial_grads``)."""
+        if getattr(self, "_partial_marked", None) is group:
+            return
+        norms = [self.norm] if self.holds("norm") else []
+        for layer in self.layers:
+            if not is_released(layer):
+                norms += [layer.input_layernorm, layer.post_attention_layernorm]
+        for n in norms:
+            n.weight.tp_partial_grad_group = group
+        self._partial_marked = group
+
     def embed(self, input_ids, feats=None, src=None):
         h = self.embed_tokens(input_ids, feats, src)
         if self.spec.embed_scale:
@@ -358,6 +416,25 @@ class DecoderModel(PreTrainedModel):
                 inputs_embeds = self.embed(input_ids)
             hidden_states = inputs_embeds
         B, S, _ = hidden_states.shape
+        # Token-sharded tensor parallelism: between the parallel blocks every rank holds the rows [r T/tp, (r+1) T/tp) of
+        # the flattened [B*S, H] activations.  The first stage takes its rows of the (replicated) embeddings; a later
+        # stage receives its rows from the same tensor-parallel rank of the stage before it.
+        tp_shard = None
+        if self.pc is not None and self.pc.tp_seq_shard:
+            from ..ops import _native as nat
+
+            Bf, Sf = kwargs.get("full_shape") or (B, S)
+            incoming_shard = B * S != Bf * Sf
+            grp = None if nat.LIBRARY_MODE else self.pc.seq_shard_group(Bf * Sf, hidden_states)
+            if grp is not None and not all(l.supports_seq_shard() for l in self.layers if not is_released(l)):
+                grp = None
+            assert grp is not None or not incoming_shard, "received token-sharded activations but this stage cannot shard"
+            if grp is not None:
+                if not incoming_shard:
+                    hidden_states = comm.split_forward_gather_backward(hidden_states.reshape(1, B * S, -1), 1, grp)
+                tp_shard = (Bf, Sf, grp)
+                B, S = Bf, Sf
+                self._mark_partial_grad_norms(grp)
         mask = as_attn_mask(attention_mask, B, S, hidden_states.device)
         pos = position_ids
         cp_state = None
@@ -386,9 +463,9 @@ class DecoderModel(PreTrainedModel):
                     lrope = self.rotary_emb_local(hidden_states.device, max_pos)
             grad_sync_layer_input(layer, delta)
             if recompute and seen <= n_recompute:
-                delta, residual, aux = checkpoint_layer(layer, delta, residual, lrope, pos, mask)
+                delta, residual, aux = checkpoint_layer(layer, delta, residual, lrope, pos, mask, tp_shard)
             else:
-                delta, residual, aux = layer(delta, residual, lrope, pos, mask)
+                delta, residual, aux = layer(delta, residual, lrope, pos, mask, tp_shard)
             if aux is not None:
                 aux_losses.append(aux)
         if self.holds("norm"):
@@ -399,6 +476,9 @@ class DecoderModel(PreTrainedModel):
             if self.pc is not None and self.pc.sp_mode == "all_to_all" and self.pc.sp_size > 1:
                 # Ulysses: back to the full sequence for the LM head (the loss is computed identically on every sp rank)
                 out = comm.gather_forward_split_backward(out, 1, self.pc.sp_group, float(self.pc.sp_size))
+            if tp_shard is not None:
+                # the LM head (vocab-parallel, or replicated) works on all tokens again
+                out = comm.gather_forward_split_backward(out, 1, tp_shard[2]).view(B, S, -1)
         else:
             out = delta if residual is None else delta + residual
         return ModelOutput(last_hidden_state=out, router_logits=tuple(aux_losses) if aux_losses else None, cp_state=cp_state)
@@ -430,6 +510,18 @@ def _full_seq_len(kwargs, input_ids, labels) -> int:
         if t is not None:
             return int(t.shape[1])
     return 0
+
+
+def _full_shape(kwargs, input_ids, labels):
+    """``(batch, sequence length)`` of the whole micro-batch as a later pipeline stage can know it when its hidden states
+    hold only this rank's token rows (token-sharded tensor parallelism): given explicitly, or from ``input_ids`` / ``labels``."""
+    fs = kwargs.get("full_shape")
+    if fs:
+        return tuple(int(v) for v in fs)
+    for t in (input_ids, labels):
+        if t is not None and t.dim() == 2:
+            return int(t.shape[0]), int(t.shape[1])
+    return None
 
 
 def as_attn_mask(attention_mask, B: int, S: int, device) -> A.AttnMask:
@@ -488,7 +580,7 @@ class DecoderForCausalLM(PreTrainedModel):
                 hidden_states=None, return_logits: bool | None = None, shift_labels: bool = True, **kwargs):
         out = self.model(input_ids=input_ids, inputs_embeds=inputs_embeds, attention_mask=attention_mask,
                          position_ids=position_ids, hidden_states=hidden_states, rope_len=kwargs.get("rope_len", 0),
-                         full_seq_len=_full_seq_len(kwargs, input_ids, labels))
+                         full_seq_len=_full_seq_len(kwargs, input_ids, labels), full_shape=_full_shape(kwargs, input_ids, labels))
         h = out.last_hidden_state
         if not self.holds("lm_head"):
             return ModelOutput(hidden_states=h, router_logits=out.router_logits)

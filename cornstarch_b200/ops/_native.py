@@ -29,7 +29,7 @@ _PROTOS = {
     "csb_norm_bwd": [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, vp],
     "csb_colsum_parts": [i32],
     "csb_colsum": [vp, vp, vp, i32, i32, i32, i32, vp],
-    "csb_rope": [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, f32, vp],
+    "csb_rope": [vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, f32, i32, vp],
     "csb_glu_fwd": [vp, vp, i64, i32, i32, vp],
     "csb_glu_bwd": [vp, vp, vp, i64, i32, i32, vp],
     "csb_act_fwd": [vp, vp, i64, i32, vp],
@@ -41,8 +41,8 @@ _PROTOS = {
     "csb_clip_scale": [vp, f32, f32, vp, vp, vp, vp, vp],
     "csb_ce_stats": [vp, i64, vp, i32, i32, vp, vp, vp, i64, vp],
     "csb_ce_grad": [vp, i64, vp, i32, i32, vp, vp, vp, vp, vp, i64, i64, vp],
-    "csb_gather_merge": [vp, vp, vp, vp, i64, i32, vp],
-    "csb_scatter_merge_bwd": [vp, vp, vp, i32, vp, i64, i32, vp],
+    "csb_gather_merge": [vp, vp, vp, vp, i64, i32, i64, i64, vp],
+    "csb_scatter_merge_bwd": [vp, vp, vp, i32, vp, i64, i32, i64, i64, vp],
 }
 
 
@@ -134,6 +134,15 @@ def declare(name: str, argtypes: list) -> None:
         fn = getattr(_LIB._raw, name)
         fn.argtypes = argtypes
         fn.restype = C.c_int
+
+
+def bounds_status() -> int:
+    """Bounds-checked build of the library (``python -m cornstarch_b200.csrc.build --bounds-check``, loaded through
+    ``CORNSTARCH_B200_LIB``): the first index violation a kernel recorded since the last call (0 = none), cleared by the
+    call.  Always 0 with the release build.  Synchronises the device."""
+    raw = lib()._raw
+    raw.csb_bounds_status.restype = C.c_int
+    return int(raw.csb_bounds_status())
 
 
 def ptr(t: torch.Tensor | None):

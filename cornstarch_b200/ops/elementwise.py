@@ -180,7 +180,7 @@ class _RopeFn(torch.autograd.Function):
         p = pos.int().contiguous() if pos is not None else None
         nat.check(
             nat.lib().csb_rope(buf.data_ptr(), cos.data_ptr(), sin.data_ptr(), nat.ptr(p), B * S, S, buf.stride(1),
-                               n_heads, D, rot_dim, 1.0, nat.stream()),
+                               n_heads, D, rot_dim, 1.0, cos.shape[0], nat.stream()),
             "csb_rope",
         )
         ctx.save_for_backward(cos, sin, p)
@@ -196,7 +196,7 @@ class _RopeFn(torch.autograd.Function):
         B, S, W = g.shape
         nat.check(
             nat.lib().csb_rope(g.data_ptr(), cos.data_ptr(), sin.data_ptr(), nat.ptr(p), B * S, S, g.stride(1), n_heads,
-                               D, rot_dim, -1.0, nat.stream()),
+                               D, rot_dim, -1.0, cos.shape[0], nat.stream()),
             "csb_rope(bwd)",
         )
         return g, None, None, None, None, None, None
@@ -300,8 +300,10 @@ class _EmbedMergeFn(torch.autograd.Function):
         H = weight.shape[1]
         out = torch.empty((T, H), dtype=weight.dtype, device=weight.device)
         f = feats if feats is not None else weight
-        nat.check(nat.lib().csb_gather_merge(weight.data_ptr(), f.data_ptr(), src.data_ptr(), out.data_ptr(), T, H, nat.stream()),
+        nat.check(nat.lib().csb_gather_merge(weight.data_ptr(), f.data_ptr(), src.data_ptr(), out.data_ptr(), T, H,
+                                             weight.shape[0], feats.shape[0] if feats is not None else 0, nat.stream()),
                   "csb_gather_merge")
+        ctx.n_embed = weight.shape[0]
         ctx.save_for_backward(src)
         ctx.w_ref = weight
         ctx.n_feats = feats.shape[0] if feats is not None else 0
@@ -326,7 +328,7 @@ class _EmbedMergeFn(torch.autograd.Function):
         nat.check(
             nat.lib().csb_scatter_merge_bwd(d.data_ptr(), src.data_ptr(), nat.ptr(demb),
                                             int(demb is not None and demb.dtype == torch.float32), nat.ptr(dfe), T, H,
-                                            nat.stream()),
+                                            ctx.n_embed, ctx.n_feats, nat.stream()),
             "csb_scatter_merge_bwd",
         )
         if demb is not None and getattr(w, "main_grad", None) is None:

@@ -207,6 +207,142 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     return multi_linear(x, [weight], [bias], tp)
 
 
+# ------------------------------------------------------------------------------------------------ sequence-sharded TP
+# Activations between the tensor-parallel blocks are sharded by token rows (rank r holds a contiguous range of whole
+# 128-row tiles): norms, residual adds and everything token-wise run on 1/tp of the tokens.  A column-parallel
+# projection gathers its input inside the GEMM (all-gather -> GEMM), a row-parallel one scatters its output inside
+# the GEMM (GEMM -> reduce-scatter); the backward passes use the same two kernels with the roles swapped.  On CUDA both
+# are single kernels over peer memory (parallel/symm.py); elsewhere torch.distributed collectives state the same math.
+def _gather_rows(x2: torch.Tensor, group) -> torch.Tensor:
+    import torch.distributed as dist
+
+    ws = dist.get_world_size(group)
+    parts = [torch.empty_like(x2) for _ in range(ws)]
+    dist.all_gather(parts, x2.contiguous(), group=group)
+    return torch.cat(parts, dim=0)
+
+
+def _scatter_rows_sum(y2: torch.Tensor, group) -> torch.Tensor:
+    import torch.distributed as dist
+
+    ws, r = dist.get_world_size(group), dist.get_rank(group)
+    y2 = y2.contiguous()
+    dist.all_reduce(y2, group=group)
+    rows = y2.shape[0] // ws
+    return y2[r * rows : (r + 1) * rows].clone()
+
+
+class _AgLinearFn(torch.autograd.Function):
+    """``y = all_gather_rows(x_shard) [W_0; W_1; ...]^T``: column-parallel projections of a row-sharded input."""
+
+    @staticmethod
+    def forward(ctx, x_shard, group, ftp, n_w, *weights):
+        x2 = _as_2d(x_shard)
+        fused_w = fuse_adjacent(weights) if n_w > 1 else weights[0]
+        if ftp is not None and fused_w is not None:
+            y, x_full = ftp.ag_gemm(x2, fused_w)
+        else:
+            x_full = _gather_rows(x2, group)
+            if _use_native(x_full) and fused_w is not None:
+                y = gemm(x_full, fused_w)
+            else:
+                y = torch.cat([F.linear(x_full, w) for w in weights], dim=-1)
+        ctx.save_for_backward(x_full, *weights)
+        ctx.group, ctx.ftp, ctx.n_w, ctx.x_shape = group, ftp, n_w, x_shard.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_full, *weights = ctx.saved_tensors
+        n_w = ctx.n_w
+        dy2 = _as_2d(dy)
+        fused_w = fuse_adjacent(weights) if n_w > 1 else weights[0]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            if ctx.ftp is not None and fused_w is not None:
+                dx = ctx.ftp.gemm_reducescatter(dy2, fused_w, b_mn_major=True)  # partial sums over the output shards
+            else:
+                full = dy2.float() @ torch.cat([w.float() for w in weights], dim=0)
+                dx = _scatter_rows_sum(full.to(dy.dtype), ctx.group)
+            dx = dx.view(ctx.x_shape)
+        dws = _weight_grads(dy2, x_full, weights, [ctx.needs_input_grad[4 + i] for i in range(n_w)])
+        return (dx, None, None, None, *dws)
+
+
+class _RsLinearFn(torch.autograd.Function):
+    """``y_shard = reduce_scatter_rows(x W^T)``: a row-parallel projection whose output is row-sharded."""
+
+    @staticmethod
+    def forward(ctx, x, group, ftp, weight):
+        x2 = _as_2d(x)
+        if ftp is not None:
+            y = ftp.gemm_reducescatter(x2, weight)
+        else:
+            y = _scatter_rows_sum(gemm(x2, weight) if _use_native(x2) else F.linear(x2, weight), group)
+        ctx.save_for_backward(x2, weight)
+        ctx.group, ctx.ftp, ctx.x_shape = group, ftp, x.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy_shard):
+        x2, weight = ctx.saved_tensors
+        dy2 = _as_2d(dy_shard)
+        if ctx.ftp is not None:
+            dx, dy_full = ctx.ftp.ag_gemm(dy2, weight, b_mn_major=True)  # dx = all_gather(dy) W
+        else:
+            dy_full = _gather_rows(dy2, ctx.group)
+            dx = gemm(dy_full, weight, b_mn_major=True) if _use_native(dy_full) else dy_full @ weight
+        dws = _weight_grads(dy_full, x2, [weight], [ctx.needs_input_grad[3]])
+        return dx.view(ctx.x_shape) if ctx.needs_input_grad[0] else None, None, None, dws[0]
+
+
+def _offsets(weights):
+    o = 0
+    for w in weights:
+        yield o, w
+        o += w.shape[0]
+
+
+def _weight_grads(dy2, x2, weights, need):
+    """``dW_i = dy_i^T x`` for every weight: accumulated into ``main_grad`` when the weight has one (autograd then gets
+    ``None``), returned otherwise."""
+    dws = [None] * len(weights)
+    if not any(need):
+        return dws
+    native = _use_native(dy2)
+    mains = [getattr(w, "main_grad", None) for w in weights]
+    fused_main = None
+    if native and all(m is not None for m in mains):
+        fused_main = fuse_adjacent(mains) if len(weights) > 1 else mains[0]
+    if fused_main is not None and (len(weights) == 1 or fuse_adjacent(weights) is not None):
+        gemm(dy2, x2, a_mn_major=True, b_mn_major=True, out=fused_main, accumulate=True)
+        for w in weights:
+            w.grad_added_to_main_grad = True
+        return dws
+    for i, (o, w) in enumerate(_offsets(weights)):
+        if not need[i]:
+            continue
+        seg = dy2[:, o : o + w.shape[0]]
+        if native and mains[i] is not None:
+            gemm(seg, x2, a_mn_major=True, b_mn_major=True, out=mains[i], accumulate=True)
+            w.grad_added_to_main_grad = True
+        elif native:
+            dws[i] = gemm(seg, x2, a_mn_major=True, b_mn_major=True)
+        else:
+            dws[i] = (seg.float().t() @ x2.float()).to(w.dtype)
+    return dws
+
+
+def ag_linear(x_shard: torch.Tensor, weights: Sequence[torch.Tensor], group, ftp=None) -> torch.Tensor:
+    """Column-parallel projections (no bias) of a row-sharded input: returns ``[rows * tp, sum of local widths]``."""
+    return _AgLinearFn.apply(x_shard, group, ftp, len(weights), *weights)
+
+
+def rs_linear(x: torch.Tensor, weight: torch.Tensor, group, ftp=None) -> torch.Tensor:
+    """Row-parallel projection (no bias) with a row-sharded output: returns ``[rows / tp, out]``."""
+    return _RsLinearFn.apply(x, group, ftp, weight)
+
+
 def add_adapter_deltas(y: torch.Tensor, x: torch.Tensor, projections) -> torch.Tensor:
     """``y`` = fused output of several projections of ``x`` (concatenated on the last dim).  Projections that carry an
     adapter (a ``delta(x)`` method returning their additive update, e.g. LoRA) get it added to their slice."""

@@ -259,10 +259,23 @@ class FusedAdamW(torch.optim.Optimizer):
                     break
         return sorted(out)
 
+    def _reduce_partial_grads(self):
+        """Parameters whose gradient is a partial sum on every rank of a group (norm weights under token-sharded tensor
+        parallelism carry ``tp_partial_grad_group``): add the parts, once per step."""
+        for g in self.param_groups:
+            for p in g["params"]:
+                grp = getattr(p, "tp_partial_grad_group", None)
+                if grp is None or dist.get_world_size(grp) < 2:
+                    continue
+                t = p.main_grad if self.use_arena else p.grad
+                if t is not None:
+                    dist.all_reduce(t, group=grp)
+
     def _step_arena(self):
         lib = nat.lib()
         st = nat.stream()
         self._fold_stray_grads()
+        self._reduce_partial_grads()
         if self.dp_group is not None and dist.get_world_size(self.dp_group) > 1:
             # expert gradients hold the contributions of every data-parallel rank's tokens, each taken from that
             # rank's own mean loss: the mean over ranks is 1/dp of the sum
@@ -332,6 +345,7 @@ class FusedAdamW(torch.optim.Optimizer):
     # ------------------------------------------------------------------ plain path (CPU / fp32)
     @torch.no_grad()
     def _step_plain(self):
+        self._reduce_partial_grads()
         params = [p for g in self.param_groups for p in g["params"] if p.grad is not None]
         inv_scale = 1.0 / self.loss_scale
         scale = inv_scale

@@ -23,7 +23,7 @@ from . import cp_fused  # noqa: F401  (declares csb_cp_signal / csb_cp_wait)
 from .symm import SymmetricMemory
 
 vp, i32, i64 = C.c_void_p, C.c_int, C.c_long
-nat.declare("csb_moe_push", [vp, vp, i64, i32, vp, vp, i32, vp])
+nat.declare("csb_moe_push", [vp, vp, i64, i32, vp, vp, i32, i64, vp])
 MAX = 8
 
 
@@ -87,7 +87,7 @@ class FusedExpertExchange:
         dst_arr = (vp * ws)(*dst)
         idx = index.int().contiguous() if index is not None else None
         srcc = src.contiguous()
-        nat.check(lib.csb_moe_push(srcc.data_ptr(), nat.ptr(idx), seg[-1], H, C.cast(seg_arr, vp), C.cast(dst_arr, vp), ws, st), "csb_moe_push")
+        nat.check(lib.csb_moe_push(srcc.data_ptr(), nat.ptr(idx), seg[-1], H, C.cast(seg_arr, vp), C.cast(dst_arr, vp), ws, srcc.shape[0], st), "csb_moe_push")
         self.events += 1
         nat.check(lib.csb_cp_signal(self.flag_ptrs.data_ptr(), ws, me, self.events, st), "csb_cp_signal")
         nat.check(lib.csb_cp_wait(self.flags.data_ptr(), ws, self.events, status.data_ptr(), st), "csb_cp_wait")

@@ -36,6 +36,11 @@ nat.declare(
     [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, i64, i32, i32, vp, vp],
 )
 nat.declare("csb_ar_layout", [i32, i32, i32, i32, i32, vp, vp, vp])
+nat.declare(
+    "csb_gemm_reducescatter_bf16",
+    [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, i64, i32, i32, vp, vp],
+)
+nat.declare("csb_ag_gemm_bf16", [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, i32, i32, i32, vp, vp])
 
 
 class _RawCudaBuffer:
@@ -123,6 +128,32 @@ class _ARContext:
         self.calls = 0
 
 
+class _AGContext:
+    """Symmetric staging of one sharded operand shape ``[M / world, K]``: two staging buffers (a rank may already stage
+    call i + 1 while a slower peer still copies call i), the "shard staged" counters the peers write, and the local
+    counters of the pulling thread blocks."""
+
+    PULL_CTAS = 16
+
+    def __init__(self, group, M: int, K: int):
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.M, self.K = M, K
+        assert M % (128 * self.world) == 0, "the row count must split into whole 128-row tiles per rank"
+        self.rows = M // self.world
+        self.bytes = self.rows * K * 2
+        self.mem = SymmetricMemory(2 * self.bytes + 256, group)
+        self.stage = [self.mem.local_tensor(torch.bfloat16, i * self.bytes, self.rows * K).view(self.rows, K) for i in range(2)]
+        self.shards = [self.mem.offset_ptr_array(i * self.bytes) for i in range(2)]
+        flag_off = 2 * self.bytes
+        self.flags = self.mem.local_tensor(torch.int32, flag_off, 64)
+        self.flags.zero_()
+        self.flag_ptrs = torch.tensor([p + flag_off for p in self.mem.ptrs], dtype=torch.int64, device="cuda")
+        self.pulled = torch.zeros(64, dtype=torch.int32, device="cuda")
+        self.calls = 0
+        torch.cuda.synchronize()
+        dist.barrier(group)
+
+
 class FusedTensorParallel:
     """GEMM + all-reduce through peer memory for one tensor-parallel group (world size 2..8, one node)."""
 
@@ -177,3 +208,70 @@ class FusedTensorParallel:
         if ctx.row_end < M:
             out[ctx.row_end :].copy_(ctx.final_local[ctx.row_end :])
         return out
+
+    # ------------------------------------------------------------------ sequence-sharded activations (Megatron "SP")
+    def shard_rows(self, M: int) -> tuple[int, int]:
+        """Rows ``[begin, end)`` of an ``M``-row activation that this rank owns (whole 128-row tiles, contiguous ranges)."""
+        tiles = (M + 127) // 128
+        b = (self.rank * tiles) // self.world * 128
+        e = min(M, ((self.rank + 1) * tiles) // self.world * 128)
+        return b, e
+
+    def gemm_reducescatter(self, a: torch.Tensor, b: torch.Tensor, a_mn_major=False, b_mn_major=False, tile_n: int = 0) -> torch.Tensor:
+        """``sum_ranks op(a) @ op(b).T`` restricted to the rows this rank owns: GEMM with the reduce-scatter in its
+        epilogue (a partial tile of a foreign row range is pushed to its owner, the owner adds what arrived to its own
+        accumulator; nothing is sent back).  Returns ``[rows owned, N]``."""
+        if a_mn_major:
+            K, M = a.shape
+        else:
+            M, K = a.shape
+        N = b.shape[1] if b_mn_major else b.shape[0]
+        key = ("rs", M, N, tile_n)
+        pair = self.contexts.get(key)
+        if pair is None:
+            # two inbox sets: a rank that runs ahead pushes the partials of call i + 1 while a peer still reads call i
+            pair = self.contexts[key] = [_ARContext(self.group, M, N, tile_n), _ARContext(self.group, M, N, tile_n), 0]
+        ctx = pair[pair[2] & 1]
+        pair[2] += 1
+        out = torch.empty((ctx.row_end - ctx.row_begin, N), dtype=torch.bfloat16, device=a.device)
+        st = nat.status_word(a.device)
+        nat.check(
+            nat.lib().csb_gemm_reducescatter_bf16(
+                a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+                int(a_mn_major), int(b_mn_major), self.world, self.rank, C.cast(ctx.inbox, vp), C.cast(ctx.final, vp),
+                C.cast(ctx.cnt_part, vp), C.cast(ctx.cnt_final, vp), ctx.slot, ctx.calls * ctx.num_n, tile_n,
+                st.data_ptr(), nat.stream()),
+            "csb_gemm_reducescatter_bf16",
+        )
+        ctx.calls += 1
+        return out
+
+    def ag_gemm(self, a_shard: torch.Tensor, b: torch.Tensor, b_mn_major=False, tile_n: int = 0):
+        """``all_gather(a_shard) @ op(b).T``: the first thread blocks of the GEMM copy the peers' shards once into a local
+        full-size operand while the other blocks already compute the tiles of the own rows.  ``a_shard``: this rank's
+        ``[M / world, K]`` rows.  Returns ``(out [M, N], a_full [M, K])``; ``a_full`` is a fresh tensor the caller may keep."""
+        from . import cp_fused  # noqa: F401  (declares csb_cp_signal)
+
+        rows, K = a_shard.shape
+        M = rows * self.world
+        N = b.shape[1] if b_mn_major else b.shape[0]
+        key = ("ag", M, K)
+        ctx = self.contexts.get(key)
+        if ctx is None:
+            ctx = self.contexts[key] = _AGContext(self.group, M, K)
+        cur = ctx.calls & 1
+        ctx.calls += 1
+        ctx.stage[cur].copy_(a_shard)
+        lib, st = nat.lib(), nat.stream()
+        nat.check(lib.csb_cp_signal(ctx.flag_ptrs.data_ptr(), self.world, self.rank, ctx.calls, st), "csb_cp_signal")
+        a_full = torch.empty((M, K), dtype=torch.bfloat16, device=a_shard.device)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a_shard.device)
+        status = nat.status_word(a_shard.device)
+        nat.check(
+            lib.csb_ag_gemm_bf16(C.cast(ctx.shards[cur], vp), a_full.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K,
+                                 b.stride(0), out.stride(0), int(b_mn_major), self.world, self.rank, ctx.flags.data_ptr(),
+                                 ctx.calls, ctx.pulled.data_ptr(), ctx.PULL_CTAS * ctx.calls, ctx.PULL_CTAS, tile_n,
+                                 status.data_ptr(), st),
+            "csb_ag_gemm_bf16",
+        )
+        return out, a_full

@@ -106,6 +106,8 @@ class MultimodalParallelModule(nn.Module):
         last = sm is None or sm.is_last_stage(check_only_in_modal=True)
         mask = mm.build_attn_mask(input_ids, attention_mask) if mm.token_ids else attention_mask
         llm_kwargs = dict(attention_mask=mask, position_ids=position_ids)
+        if input_ids is not None:
+            llm_kwargs["full_shape"] = tuple(input_ids.shape)  # later stages may hold token-sharded hidden states
         if first:
             enc_outs = {}
             if hidden_states is not None:

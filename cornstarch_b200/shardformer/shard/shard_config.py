@@ -39,6 +39,10 @@ class ShardConfig:
     make_vocab_size_divisible_by: int = 64
     gradient_checkpoint_config: Optional[Any] = None
     expert_parallel_process_group: Optional[Any] = None
+    # Tensor parallelism with token-sharded activations between the parallel blocks (norms, residuals and the other
+    # token-wise work run on 1/tp of the tokens; the projections gather / scatter inside their GEMMs).  None = decided
+    # by the environment variable CORNSTARCH_B200_TP_SEQ_SHARD (default off); decoders without projection biases only.
+    tensor_parallel_sequence_sharding: Optional[bool] = None
     extra_kwargs: dict = field(default_factory=dict)
 
     def __post_init__(self):

@@ -168,7 +168,8 @@ class ModelSharder:
             tp_group=sc.tensor_parallel_process_group if sc.enable_tensor_parallelism else None,
             sp_group=sc.sequence_parallel_process_group if sc.enable_sequence_parallelism else None,
             sp_mode=sc.sequence_parallelism_mode if sc.enable_sequence_parallelism else None,
-            cp_dist_mode=sc.context_parallel_distribution_mode, parallel_output=sc.parallel_output)
+            cp_dist_mode=sc.context_parallel_distribution_mode, parallel_output=sc.parallel_output,
+            tp_seq_shard=sc.tensor_parallel_sequence_sharding)
         if hasattr(self.model, "set_parallel_context"):
             self.model.set_parallel_context(pc)
         else:

@@ -264,7 +264,7 @@ def probe_moe_push_local(a, flush):
 
     def run():
         nat.check(nat.lib().csb_moe_push(src.data_ptr(), index.data_ptr(), rows, H, C.cast(seg_arr, C.c_void_p),
-                                         C.cast(dst_arr, C.c_void_p), ws, nat.stream()), "csb_moe_push")
+                                         C.cast(dst_arr, C.c_void_p), ws, rows, nat.stream()), "csb_moe_push")
 
     run()
     torch.cuda.synchronize()

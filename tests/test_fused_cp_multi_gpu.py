@@ -36,6 +36,7 @@ def _worker(rank, world, port, q):
         B, Hq, Hk, D = 2, 8, 2, 128
         for it, (S, mode, dist_mode) in enumerate([(1024, "causal", "zigzag"), (1536, "bitfield", "makespan_min"),
                                                    (1200, "bitfield", "uniform"), (2048, "causal", "uniform")]):
+            S *= max(1, world // 2)  # the same number of tokens per rank at every world size
             g = torch.Generator().manual_seed(7 + it)  # same tensors on both ranks; each keeps its shard
             q_full = torch.randn(B, S, Hq, D, generator=g).cuda().bfloat16()
             k_full = torch.randn(B, S, Hk, D, generator=g).cuda().bfloat16()

@@ -21,7 +21,7 @@ def _worker(rank, world, port, q):
         from cornstarch_b200.parallel import ep as EP
 
         cfg = MixtralConfig(vocab_size=64, hidden_size=256, intermediate_size=512, num_hidden_layers=1, num_attention_heads=4,
-                            num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2)
+                            num_key_value_heads=2, num_local_experts=max(4, world), num_experts_per_tok=2)
         torch.manual_seed(0)
         blocks = []
         for _ in range(2):

@@ -23,6 +23,7 @@ def _worker(rank, world, port, q):
         assert ftp is not None
         for it, (M, N, K, amn, bmn) in enumerate([(512, 1024, 256, 0, 0), (1000, 776, 520, 0, 1), (2048, 4096, 1024, 0, 0),
                                                   (512, 1024, 256, 0, 0), (384, 512, 640, 1, 1)]):
+            M *= max(1, world // 2)  # every rank owns at least one 128-row tile row
             g = torch.Generator().manual_seed(100 * it + rank)
             a = torch.randn((K, M) if amn else (M, K), generator=g).cuda().bfloat16()
             b = torch.randn((K, N) if bmn else (N, K), generator=g).cuda().bfloat16()

@@ -129,6 +129,13 @@ def test_modality_parallel_pipeline_matches_single_process(llm_stages, tp, n_mic
     run_distributed(_pp_worker, world, llm_stages, tp, n_micro)
 
 
+def test_pipeline_with_token_sharded_tensor_parallelism(monkeypatch):
+    """Encoder stage + 2 LLM stages x TP 2 with token-sharded activations between the tensor-parallel blocks: the LLM
+    stages hand only their rank's token rows to the next stage, and loss / weights still match the single process."""
+    monkeypatch.setenv("CORNSTARCH_B200_TP_SEQ_SHARD", "1")
+    run_distributed(_pp_worker, 6, 2, 2, 4)
+
+
 def _colocated_worker(rank, world):
     from cornstarch_b200.booster import Booster
     from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
