@@ -263,7 +263,7 @@ adamw_kernel(__nv_bfloat16* __restrict__ param, void* __restrict__ master_v, flo
 
 // sum of squares of a flat gradient buffer -> out[0] (atomic add of per-CTA sums; caller zeroes out).
 template <typename GradT>
-__global__ void sumsq_kernel(const GradT* __restrict__ g, long n, float* __restrict__ out) {
+__global__ void sumsq_kernel(const GradT* __restrict__ g, long n, float* __restrict__ out, float* __restrict__ scratch) {
   float acc = 0.f;
   // 16-byte streaming loads, two per thread and pass (the base pointer is 16-byte aligned: arena slices and torch
   // allocations are); the tail that does not fill a vector is read element-wise
@@ -301,7 +301,28 @@ __global__ void sumsq_kernel(const GradT* __restrict__ g, long n, float* __restr
     float t = (l < (blockDim.x >> 5)) ? sh[l] : 0.f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (l == 0) atomicAdd(out, t);
+    // The block sums are added in block order by whichever block finishes last (scratch[0] is the ticket counter,
+    // scratch[1 + b] block b's sum): the result does not depend on the order in which the blocks ran, so data-parallel
+    // replicas that hold the same gradients compute the same norm, bit for bit.
+    __shared__ bool last;
+    if (l == 0) {
+      scratch[1 + blockIdx.x] = t;
+      __threadfence();
+      const unsigned ticket = atomicAdd(reinterpret_cast<unsigned*>(scratch), 1u);
+      last = ticket == gridDim.x - 1;
+    }
+    __syncwarp();
+    if (last) {
+      __threadfence();
+      float tot = 0.f;
+      for (unsigned b = l; b < gridDim.x; b += 32) tot += __ldcg(scratch + 1 + b);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+      if (l == 0) {
+        *out += tot;  // launches that add into the same `out` are ordered by their stream
+        *reinterpret_cast<unsigned*>(scratch) = 0u;
+      }
+    }
   }
 }
 // scale_out = inv_loss_scale * min(1, max_norm / (sqrt(sumsq) * inv_loss_scale + 1e-6)); skip = !finite.
@@ -575,13 +596,17 @@ CSB_API int csb_adamw_split(void* param, short* resid, float* m, float* v, void*
                                                            wd, bc1, bc2, grad_scale, skip, zero_grad);
   return launch_result();
 }
-CSB_API int csb_sumsq(const void* g, int grad_fp32, long n, float* out, void* stream) {
+// Adds the sum of squares of g[0..n) to *out.  `scratch`: scratch_elems floats of device memory owned by the caller (zero
+// before the first call; the kernel leaves its ticket counter at zero again), used by one launch at a time.
+CSB_API int csb_sumsq(const void* g, int grad_fp32, long n, float* out, float* scratch, int scratch_elems, void* stream) {
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = ew_grid(n / 16 + 1, 512);
+  if (scratch == nullptr || scratch_elems < 2) return CSB_ERR_BAD_ARG;
+  int grid = ew_grid(n / 16 + 1, 512);
+  if (grid > scratch_elems - 1) grid = scratch_elems - 1;
   if (grad_fp32)
-    sumsq_kernel<float><<<grid, 512, 0, s>>>(reinterpret_cast<const float*>(g), n, out);
+    sumsq_kernel<float><<<grid, 512, 0, s>>>(reinterpret_cast<const float*>(g), n, out, scratch);
   else
-    sumsq_kernel<__nv_bfloat16><<<grid, 512, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(g), n, out);
+    sumsq_kernel<__nv_bfloat16><<<grid, 512, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(g), n, out, scratch);
   return launch_result();
 }
 CSB_API int csb_clip_scale(const float* sumsq, float max_norm, float inv_loss_scale, float* scale_out,

@@ -169,38 +169,61 @@ __device__ __forceinline__ bool spin_local_ge(const int* addr, int target) {
   return false;
 }
 
-// One pulling thread block of the fused all-gather: its share of every rank's shard (own first, then the next
-// ranks) goes from the (peer-mapped) source into the local full-size A; the range is then counted as done.
-__device__ __forceinline__ bool ag_pull(const GemmParams& p, int block, int n_blocks, int* ok_smem) {
-  const long stride = (long)n_blocks * blockDim.x;
-  const long row_vecs = p.K / 8;  // 16-byte vectors per row
-  for (int d = 0; d < p.ag_world; ++d) {
-    const int r = (p.ag_rank + d) % p.ag_world;
-    if (r != p.ag_rank) {
-      if (threadIdx.x == 0) *ok_smem = spin_until_ge(p.ag_ready + r, p.ag_ready_value) ? 1 : 0;
-      __syncthreads();
-      const bool ok = *ok_smem != 0;
-      __syncthreads();
-      if (!ok) return false;
-    }
+// One pulling thread block of the fused all-gather.  One thread moves the block's share of every shard from the
+// (peer-mapped) source into the local full-size A with bulk copies through a ring of shared-memory stages: the loads of
+// PULL_STAGES - 1 chunks are in flight while one chunk is written out, so a handful of blocks keep enough bytes on NVLink
+// to fill it.  The peers' shards come first (the tiles of the own rows read the own shard in place); each finished
+// range is counted.  The own shard follows last: only the caller, after the launch, reads those rows of the full A.
+constexpr int PULL_CHUNK = 16384;
+constexpr int PULL_STAGES = 8;
+__device__ __forceinline__ bool ag_pull(const GemmParams& p, int block, int n_blocks, uint8_t* stage_smem) {
+  __shared__ uint64_t pull_bar[PULL_STAGES];
+  if (threadIdx.x != 0) return true;
+  for (int s = 0; s < PULL_STAGES; ++s) mbar_init(&pull_bar[s], 1);
+  mbar_fence_init();
+  const long row_bytes = (long)p.K * 2;
+  uint32_t used = 0;  // chunks that went through the ring so far (stage = used % PULL_STAGES, phase from used / PULL_STAGES)
+  for (int d = 1; d <= p.ag_world; ++d) {
+    const int r = (p.ag_rank + d) % p.ag_world;  // d == world: the own shard
+    if (r != p.ag_rank && !spin_until_ge(p.ag_ready + r, p.ag_ready_value)) return false;
     const long row0 = (long)ar_range_start(r, p.num_m_blocks, p.ag_world) * BM;
     long row1 = (long)ar_range_start(r + 1, p.num_m_blocks, p.ag_world) * BM;
     if (row1 > p.M) row1 = p.M;
-    const long n = (row1 - row0) * row_vecs;
-    const uint4* __restrict__ src = p.ag_src[r];
-    uint4* __restrict__ dst = p.ag_dst + row0 * row_vecs;
-    for (long i = (long)block * blockDim.x + threadIdx.x; i < n; i += 4 * stride) {
-      uint4 x[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (i + u * stride < n) x[u] = __ldcg(src + i + u * stride);
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (i + u * stride < n) dst[i + u * stride] = x[u];
+    const long n = (row1 - row0) * row_bytes;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(p.ag_src[r]);
+    uint8_t* dst = reinterpret_cast<uint8_t*>(p.ag_dst) + row0 * row_bytes;
+    const long n_chunks = (n + PULL_CHUNK - 1) / PULL_CHUNK;
+    const long mine = block < n_chunks ? (n_chunks - block + n_blocks - 1) / n_blocks : 0;  // chunks block, block + n_blocks, ...
+    auto chunk_bytes = [&](long j) -> uint32_t {
+      const long off = (block + j * n_blocks) * (long)PULL_CHUNK;
+      return (uint32_t)(n - off < PULL_CHUNK ? n - off : PULL_CHUNK);
+    };
+    auto load = [&](long j) {
+      const uint32_t st = (used + (uint32_t)j) % PULL_STAGES;
+      const long off = (block + j * n_blocks) * (long)PULL_CHUNK;
+      mbar_expect_tx(&pull_bar[st], chunk_bytes(j));
+      bulk_load_g2s(stage_smem + st * PULL_CHUNK, src + off, chunk_bytes(j), &pull_bar[st]);
+    };
+    for (long j = 0; j < mine && j < PULL_STAGES - 1; ++j) load(j);
+    for (long j = 0; j < mine; ++j) {
+      const uint32_t u = used + (uint32_t)j;
+      if (!mbar_wait(&pull_bar[u % PULL_STAGES], (u / PULL_STAGES) & 1)) {
+        tma_store_wait<0>();
+        return false;
+      }
+      const long off = (block + j * n_blocks) * (long)PULL_CHUNK;
+      bulk_store_s2g(dst + off, stage_smem + (u % PULL_STAGES) * PULL_CHUNK, chunk_bytes(j));
+      tma_store_commit();
+      // the stage that the next load overwrites was read by the store before this one
+      tma_store_wait_read<1>();
+      if (j + PULL_STAGES - 1 < mine) load(j + PULL_STAGES - 1);
     }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.ag_pulled + r) : "memory");
+    used += (uint32_t)mine;
+    tma_store_wait<0>();  // the writes of this range are complete
+    if (r != p.ag_rank) {
+      __threadfence();
+      asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.ag_pulled + r) : "memory");
+    }
   }
   return true;
 }
@@ -224,6 +247,7 @@ __device__ __forceinline__ float apply_act(float x, int act) {
 // Tensor maps of the output side: C itself and, for the fused all-reduce, this rank's slot in every
 // rank's inbox and every rank's final buffer (128-byte swizzled boxes of 128 rows x 128 bytes).
 struct EpiMaps {
+  CUtensorMap a_own;  // fused all-gather: this rank's own shard of A, read in place by the tiles of the own rows
   CUtensorMap c;
   CUtensorMap inbox[8];
   CUtensorMap fin[8];
@@ -387,10 +411,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int lane = threadIdx.x & 31;
   // The grid is one-dimensional so that thread blocks start in index order: the pulling blocks of a fused all-gather
   // come first and are resident before any block that waits for their counters.
-  const int n_pull = (CG == 1 && p.ag_world > 1) ? p.ag_pull_ctas : 0;
+  const int n_pull = p.ag_world > 1 ? p.ag_pull_ctas : 0;  // CG == 2: an even number, so that a pair pulls or works as one
   if ((int)blockIdx.x < n_pull) {
-    if (!ag_pull(p, blockIdx.x, n_pull, reinterpret_cast<int*>(smem)) && threadIdx.x == 0)
-      atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG);
+    if (!ag_pull(p, blockIdx.x, n_pull, smem)) atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG);
     return;
   }
   // A pair of thread blocks (CG == 2) walks the tiles together: `unit` rows of 128 * CG; block `cta_rank` of the pair
@@ -399,12 +422,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const bool leader = cta_rank == 0;
   const int num_m_units = (p.num_m_blocks + CG - 1) / CG;
   const int num_tiles = num_m_units * p.num_n_blocks;
-  const int work_first = CG == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x - n_pull;
-  const int work_step = CG == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x - n_pull;
+  const int work_first = ((int)blockIdx.x - n_pull) / CG;
+  const int work_step = ((int)gridDim.x - n_pull) / CG;
   // tile rows are walked in rotated order: fused all-reduce / reduce-scatter - the rows of the next rank first, the own
   // last; fused all-gather - the own rows (already local) first
-  const int rot = p.ar_world > 1 ? ar_range_start((p.ar_rank + 1) % p.ar_world, p.num_m_blocks, p.ar_world)
-                                 : (p.ag_world > 1 ? ar_range_start(p.ag_rank, p.num_m_blocks, p.ag_world) : 0);
+  // (CG == 2: the host picks pairs only when every range starts on an even tile row, so a pair never straddles two)
+  const int rot = (p.ar_world > 1 ? ar_range_start((p.ar_rank + 1) % p.ar_world, p.num_m_blocks, p.ar_world)
+                                  : (p.ag_world > 1 ? ar_range_start(p.ag_rank, p.num_m_blocks, p.ag_world) : 0)) / CG;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::STAGES; ++s) {
@@ -451,11 +475,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tile_coords_rot<(CG == 2 ? 8 : 16)>(tile, num_m_units, p.num_n_blocks, rot, m_blk, n_blk);
         m_blk = m_blk * CG + cta_rank;
         const int n_row0 = n_blk * BN + cta_rank * BNH;
+        const CUtensorMap* map_a = &tma_a;
+        int a_row0 = m_blk * BM;
         if (n_pull > 0) {
-          // first tile of a range: its rows must have been copied into the local A (bounded wait on the pull counter);
-          // the copy was written with ordinary stores by other blocks, the loads below go through the async proxy
           const int o = ar_owner(m_blk, p.num_m_blocks, p.ag_world);
-          if (!((ag_opened >> o) & 1u)) {
+          if (o == p.ag_rank) {
+            // own rows: read from the shard in place (the full A receives them last, for the caller)
+            map_a = &epi_maps.a_own;
+            a_row0 -= ar_range_start(o, p.num_m_blocks, p.ag_world) * BM;
+          } else if (!((ag_opened >> o) & 1u)) {
+            // first tile of a peer's range: its rows must have been copied into the local A (bounded wait on the pull
+            // counter); the copy was written by other blocks, the loads below go through the async proxy
             if (!spin_local_ge(p.ag_pulled + o, p.ag_pull_target)) {
               atomicCAS(p.status, 0, ST_TIMEOUT_PEER_FLAG);
               *abort_flag = 1;
@@ -482,9 +512,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if constexpr (A_MN) {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j)
-              tma_load_2d_to<CG>(sa + j * (64 * BK * 2), &tma_a, full_addr_s, m_blk * BM + j * 64, kb * BK);
+              tma_load_2d_to<CG>(sa + j * (64 * BK * 2), map_a, full_addr_s, a_row0 + j * 64, kb * BK);
           } else {
-            tma_load_2d_to<CG>(sa, &tma_a, full_addr_s, kb * BK, m_blk * BM);
+            tma_load_2d_to<CG>(sa, map_a, full_addr_s, kb * BK, a_row0);
           }
           if constexpr (B_MN) {
 #pragma unroll
@@ -793,13 +823,21 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
   int grid = tiles < sm_count() / CG ? tiles : sm_count() / CG;  // thread blocks (CG == 1) or pairs (CG == 2)
   if (max_ctas > 0 && grid > max_ctas / CG) grid = max_ctas / CG > 0 ? max_ctas / CG : 1;
   grid *= CG;
-  if (CG == 1 && p.ag_world > 1) grid += p.ag_pull_ctas;  // the pulling blocks come first and leave when they are done
+  if (p.ag_world > 1) grid += p.ag_pull_ctas;  // the pulling blocks come first and leave when they are done
   GemmParams q = p;
   EpiMaps em = {};  // filled per launch and passed by value: no state shared between host threads
   const int eb = q.out_fp32 ? 4 : 2;
   const int cps = 128 / eb;
   q.tma_epi = ((reinterpret_cast<uintptr_t>(q.C) & 15) == 0 && ((size_t)q.ldc * eb) % 16 == 0) ? 1 : 0;
   if (q.ar_world > 1 && !q.tma_epi) return CSB_ERR_BAD_ARG;
+  if (q.ag_world > 1) {
+    if (A_MN) return CSB_ERR_BAD_ARG;
+    const int own0 = ar_range_start(q.ag_rank, q.num_m_blocks, q.ag_world) * BM;
+    int own1 = ar_range_start(q.ag_rank + 1, q.num_m_blocks, q.ag_world) * BM;
+    if (own1 > q.M) own1 = q.M;
+    r = make_tmap_2d_bf16(&em.a_own, q.ag_src[q.ag_rank], own1 - own0, q.K, q.K, BK, BM);
+    if (r) return r;
+  }
   if (q.tma_epi) {
     r = make_tmap_2d_out(&em.c, q.C, q.M, q.N, q.ldc, q.out_fp32, cps, BM);
     if (r) return r;
@@ -838,6 +876,13 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
 }  // namespace csb
 
 namespace csb {
+static int gemm_cg_choice() {
+  static const int cg_env = []() { const char* e = getenv("CORNSTARCH_B200_GEMM_CG"); return e ? atoi(e) : 0; }();
+  return (cg_env == 1 || cg_env == 2) ? cg_env : CSB_GEMM_DEFAULT_CG;
+}
+// Pairs of thread blocks serve a fused collective when every rank's range of tile rows starts on an even tile row:
+// both blocks of a pair then work for the same owner.
+static bool pairs_fit_ranges(int num_m_blocks, int world) { return num_m_blocks % (2 * world) == 0; }
 static void no_collective(GemmParams& p) {
   p.ar_scatter = 0; p.ar_row_offset = 0;
   p.ag_world = 1; p.ag_rank = 0; p.ag_pull_ctas = 0;
@@ -886,8 +931,7 @@ CSB_API int csb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   return launch_gemm<BNV, true, true>(A, B, p, lda, ldb, max_ctas, s);
   // Pairs of thread blocks on one 256 x 256 tile (cta_group::2) when the problem has at least two tile rows and the
   // caller did not restrict the number of thread blocks (a restricted launch shares the GPU with another kernel).
-  static const int cg_env = []() { const char* e = getenv("CORNSTARCH_B200_GEMM_CG"); return e ? atoi(e) : 0; }();
-  const int cg = (cg_env == 1 || cg_env == 2) ? cg_env : CSB_GEMM_DEFAULT_CG;
+  const int cg = gemm_cg_choice();
   if (bn == 256 && cg == 2 && p.num_m_blocks >= 2 && max_ctas <= 0) {
     if (!a_mn_major && !b_mn_major) return launch_gemm<256, false, false, 2>(A, B, p, lda, ldb, 0, s);
     if (!a_mn_major && b_mn_major) return launch_gemm<256, false, true, 2>(A, B, p, lda, ldb, 0, s);
@@ -948,6 +992,12 @@ static int gemm_allreduce_impl(const void* A, const void* B, void* C, int M, int
   if (!a_mn_major && b_mn_major) return launch_gemm<BNV, false, true>(A, B, p, lda, ldb, 0, s);   \
   if (a_mn_major && !b_mn_major) return launch_gemm<BNV, true, false>(A, B, p, lda, ldb, 0, s);   \
   return launch_gemm<BNV, true, true>(A, B, p, lda, ldb, 0, s);
+  if (bn == 256 && gemm_cg_choice() == 2 && pairs_fit_ranges(p.num_m_blocks, world)) {
+    if (!a_mn_major && !b_mn_major) return launch_gemm<256, false, false, 2>(A, B, p, lda, ldb, 0, s);
+    if (!a_mn_major && b_mn_major) return launch_gemm<256, false, true, 2>(A, B, p, lda, ldb, 0, s);
+    if (a_mn_major && !b_mn_major) return launch_gemm<256, true, false, 2>(A, B, p, lda, ldb, 0, s);
+    return launch_gemm<256, true, true, 2>(A, B, p, lda, ldb, 0, s);
+  }
   if (bn == 256) { CSB_DISPATCH_AR(256) }
   CSB_DISPATCH_AR(128)
 #undef CSB_DISPATCH_AR
@@ -1003,6 +1053,10 @@ CSB_API int csb_ag_gemm_bf16(void* const* shard_ptrs, void* a_full, const void* 
   p.ag_dst = reinterpret_cast<uint4*>(a_full);
   p.ag_ready = ready; p.ag_ready_value = ready_value; p.ag_pulled = pulled; p.ag_pull_target = pull_target;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (bn == 256 && gemm_cg_choice() == 2 && pairs_fit_ranges(p.num_m_blocks, world) && (pull_ctas & 1) == 0) {
+    if (b_mn_major) return launch_gemm<256, false, true, 2>(a_full, B, p, K, ldb, 0, s);
+    return launch_gemm<256, false, false, 2>(a_full, B, p, K, ldb, 0, s);
+  }
   if (bn == 256) {
     if (b_mn_major) return launch_gemm<256, false, true>(a_full, B, p, K, ldb, 0, s);
     return launch_gemm<256, false, false>(a_full, B, p, K, ldb, 0, s);

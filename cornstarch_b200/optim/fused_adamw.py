@@ -178,6 +178,8 @@ class FusedAdamW(torch.optim.Optimizer):
                 self._regions.append((g, region))
         dev = self._regions[0][1].flat_param.device
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        # block sums of the norm kernel, added in block order so that replicas with equal gradients get equal norms
+        self._sumsq_scratch = torch.zeros(4096, dtype=torch.float32, device=dev)
         self._scale = torch.ones(1, dtype=torch.float32, device=dev)
         self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
         self._skip = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -304,7 +306,8 @@ class FusedAdamW(torch.optim.Optimizer):
                 g = r.flat_grad[r.lo : r.hi]
                 acc = self._sumsq_expert if r.expert else self._sumsq
                 any_expert |= r.expert
-                nat.check(lib.csb_sumsq(g.data_ptr(), int(g.dtype == torch.float32), g.numel(), acc.data_ptr(), st), "csb_sumsq")
+                nat.check(lib.csb_sumsq(g.data_ptr(), int(g.dtype == torch.float32), g.numel(), acc.data_ptr(),
+                                        self._sumsq_scratch.data_ptr(), self._sumsq_scratch.numel(), st), "csb_sumsq")
             if self._sharded and dist.get_world_size(self.dp_group) > 1:
                 dist.all_reduce(self._sumsq, group=self.dp_group)  # every rank summed its slice only
             if any_expert:

@@ -75,6 +75,58 @@ def gemm_allreduce(args):
     nat.check_status()
 
 
+def sp_linear(args):
+    """Token-sharded tensor parallelism: all-gather -> GEMM (column-parallel forward) and GEMM -> reduce-scatter
+    (row-parallel forward) as one kernel each, against NCCL all-gather / reduce-scatter around the same GEMM kernel.
+    Roofline: the slower of FLOPs / measured GEMM peak and (world-1)/world of the gathered (or scattered) matrix / 770 GB/s."""
+    from ..parallel.symm import FusedTensorParallel
+
+    ftp = FusedTensorParallel.get(dist.group.WORLD)
+    world, rank = dist.get_world_size(), dist.get_rank()
+    _, flops_peak, src = peaks()
+    T, H, I, QKV = 8192, 4096, 14336, 6144
+    for name, N, K in [("all-gather -> qkv", QKV // world, H), ("all-gather -> gate_up", 2 * I // world, H)]:
+        shard = torch.randn(T // world, K, device="cuda").bfloat16()
+        w = torch.randn(N, K, device="cuda").bfloat16()
+        full = torch.empty(T, K, device="cuda", dtype=torch.bfloat16)
+        ms_f = timeit(lambda: ftp.ag_gemm(shard, w))
+
+        def base():
+            dist.all_gather_into_tensor(full, shard)
+            gemm(full, w)
+
+        ms_b = timeit(base)
+        ms_g = timeit(lambda: gemm(full, w))
+        roof_ms = max(2.0 * T * N * K / flops_peak, (world - 1) / world * T * K * 2 / NVLINK_BPS) * 1e3
+        if rank == 0:
+            print(json.dumps({"op": name, "M": T, "N": N, "K": K, "world": world, "fused_ms": round(ms_f, 4),
+                              "nccl_then_gemm_ms": round(ms_b, 4), "gemm_only_ms": round(ms_g, 4), "roofline_ms": round(roof_ms, 4),
+                              f"frac_of_roofline_{src}": round(roof_ms / ms_f, 3), "speedup_vs_nccl": round(ms_b / ms_f, 3)}), flush=True)
+    for name, N, K in [("o_proj -> reduce-scatter", H, H // world), ("down_proj -> reduce-scatter", H, I // world)]:
+        a = torch.randn(T, K, device="cuda").bfloat16()
+        w = torch.randn(N, K, device="cuda").bfloat16()
+        part = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+        mine = torch.empty(T // world, N, device="cuda", dtype=torch.bfloat16)
+        ms_f = timeit(lambda: ftp.gemm_reducescatter(a, w))
+
+        def base():
+            gemm(a, w, out=part)
+            dist.reduce_scatter_tensor(mine, part)
+
+        ms_b = timeit(base)
+        ms_g = timeit(lambda: gemm(a, w, out=part))
+        ms_ar = timeit(lambda: ftp.gemm_allreduce(a, w, False, False, out=part))
+        roof_ms = max(2.0 * T * N * K / flops_peak, (world - 1) / world * T * N * 2 / NVLINK_BPS) * 1e3
+        if rank == 0:
+            print(json.dumps({"op": name, "M": T, "N": N, "K": K, "world": world, "fused_ms": round(ms_f, 4),
+                              "gemm_then_nccl_ms": round(ms_b, 4), "gemm_only_ms": round(ms_g, 4),
+                              "fused_allreduce_ms": round(ms_ar, 4), "roofline_ms": round(roof_ms, 4),
+                              f"frac_of_roofline_{src}": round(roof_ms / ms_f, 3), "speedup_vs_nccl": round(ms_b / ms_f, 3)}), flush=True)
+    from ..ops import _native as nat
+
+    nat.check_status()
+
+
 def cp_attention(args):
     """Context-parallel attention forward + backward: K/V streamed from the peers inside the kernels against
     NCCL all-gather / reduce-scatter around the local kernels.  Llama-8B heads, ``--seq`` tokens per rank."""
@@ -183,7 +235,7 @@ def moe_exchange(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm_allreduce", "cp_attention", "grad_reduce", "moe_exchange"])
+    ap.add_argument("what", choices=["gemm_allreduce", "sp_linear", "cp_attention", "grad_reduce", "moe_exchange"])
     ap.add_argument("--seq", type=int, default=8192, help="cp_attention: tokens per rank; moe_exchange: rows per rank")
     ap.add_argument("--mb", type=int, default=1024, help="grad_reduce: buffer size in MiB")
     ap.add_argument("--reducers", type=int, nargs="+", default=[16])
@@ -192,7 +244,7 @@ def main():
     torch.cuda.set_device(local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    {"gemm_allreduce": gemm_allreduce, "cp_attention": cp_attention, "grad_reduce": grad_reduce,
+    {"gemm_allreduce": gemm_allreduce, "sp_linear": sp_linear, "cp_attention": cp_attention, "grad_reduce": grad_reduce,
      "moe_exchange": moe_exchange}[args.what](args)
     dist.barrier()
     dist.destroy_process_group()

@@ -89,6 +89,37 @@ def test_norm_and_glu_are_deterministic():
         assert torch.equal(a, b)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gradient_norm_is_bitwise_repeatable(dtype):
+    """The sum of squares behind gradient clipping is the same bit pattern on every launch (block sums are added in block
+    order): data-parallel replicas that hold equal gradients must scale them by equal factors, else they drift apart."""
+    from cornstarch_b200.ops import _native as nat
+
+    lib = nat.lib()
+    torch.manual_seed(0)
+    g = (torch.randn(50_000_003, device="cuda") * 1e-2).to(dtype)
+    scratch = torch.zeros(4096, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    outs = []
+    for _ in range(8):
+        out = torch.zeros(1, device="cuda")
+        nat.check(lib.csb_sumsq(g.data_ptr(), int(dtype == torch.float32), g.numel(), out.data_ptr(), scratch.data_ptr(),
+                                scratch.numel(), st), "csb_sumsq")
+        outs.append(out)
+    torch.cuda.synchronize()
+    assert all(torch.equal(o, outs[0]) for o in outs[1:])
+    ref = g.double().pow(2).sum().item()
+    assert abs(outs[0].item() - ref) <= 1e-5 * ref
+    # two launches into the same accumulator add up; the ticket counter is back at zero for the next launch
+    out = torch.zeros(1, device="cuda")
+    for _ in range(2):
+        nat.check(lib.csb_sumsq(g.data_ptr(), int(dtype == torch.float32), g.numel(), out.data_ptr(), scratch.data_ptr(),
+                                scratch.numel(), st), "csb_sumsq")
+    assert abs(out.item() - 2 * ref) <= 1e-5 * 2 * ref
+    assert scratch.view(torch.int32)[0].item() == 0
+
+
 def test_split_master_weights_are_exact():
     """fp32 master weights kept as bf16 parameter + int16 remainder: any fp32 value survives the split exactly, and the
     parameter is the master rounded to bf16 (half away from zero)."""
