@@ -169,11 +169,11 @@ __device__ __forceinline__ bool spin_local_ge(const int* addr, int target) {
   return false;
 }
 
-// One pulling thread block of the fused all-gather.  One thread moves the block's share of every shard from the
-// (peer-mapped) source into the local full-size A with bulk copies through a ring of shared-memory stages: the loads of
+// One pulling thread block of the fused all-gather.  One thread moves the block's share of every peer's shard from the
+// peer-mapped source into the local full-size A with bulk copies through a ring of shared-memory stages: the loads of
 // PULL_STAGES - 1 chunks are in flight while one chunk is written out, so a handful of blocks keep enough bytes on NVLink
-// to fill it.  The peers' shards come first (the tiles of the own rows read the own shard in place); each finished
-// range is counted.  The own shard follows last: only the caller, after the launch, reads those rows of the full A.
+// to fill it.  Each finished range is counted.  The tiles of the own rows read the own shard in place; the caller copies
+// that shard into the full A (a local copy, outside this kernel).
 constexpr int PULL_CHUNK = 16384;
 constexpr int PULL_STAGES = 8;
 __device__ __forceinline__ bool ag_pull(const GemmParams& p, int block, int n_blocks, uint8_t* stage_smem) {
@@ -183,9 +183,9 @@ __device__ __forceinline__ bool ag_pull(const GemmParams& p, int block, int n_bl
   mbar_fence_init();
   const long row_bytes = (long)p.K * 2;
   uint32_t used = 0;  // chunks that went through the ring so far (stage = used % PULL_STAGES, phase from used / PULL_STAGES)
-  for (int d = 1; d <= p.ag_world; ++d) {
-    const int r = (p.ag_rank + d) % p.ag_world;  // d == world: the own shard
-    if (r != p.ag_rank && !spin_until_ge(p.ag_ready + r, p.ag_ready_value)) return false;
+  for (int d = 1; d < p.ag_world; ++d) {
+    const int r = (p.ag_rank + d) % p.ag_world;
+    if (!spin_until_ge(p.ag_ready + r, p.ag_ready_value)) return false;
     const long row0 = (long)ar_range_start(r, p.num_m_blocks, p.ag_world) * BM;
     long row1 = (long)ar_range_start(r + 1, p.num_m_blocks, p.ag_world) * BM;
     if (row1 > p.M) row1 = p.M;
@@ -220,10 +220,8 @@ __device__ __forceinline__ bool ag_pull(const GemmParams& p, int block, int n_bl
     }
     used += (uint32_t)mine;
     tma_store_wait<0>();  // the writes of this range are complete
-    if (r != p.ag_rank) {
-      __threadfence();
-      asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.ag_pulled + r) : "memory");
-    }
+    __threadfence();
+    asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.ag_pulled + r) : "memory");
   }
   return true;
 }
@@ -820,7 +818,10 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
     attr_set = true;
   }
   int tiles = ((p.num_m_blocks + CG - 1) / CG) * p.num_n_blocks;
-  int grid = tiles < sm_count() / CG ? tiles : sm_count() / CG;  // thread blocks (CG == 1) or pairs (CG == 2)
+  // thread blocks (CG == 1) or pairs (CG == 2); with a fused all-gather the pulling blocks keep their SMs, so that every
+  // working block is resident from the start (tiles are dealt out round-robin: a block that started late would finish late)
+  const int slots = (sm_count() - (p.ag_world > 1 ? p.ag_pull_ctas : 0)) / CG;
+  int grid = tiles < slots ? tiles : slots;
   if (max_ctas > 0 && grid > max_ctas / CG) grid = max_ctas / CG > 0 ? max_ctas / CG : 1;
   grid *= CG;
   if (p.ag_world > 1) grid += p.ag_pull_ctas;  // the pulling blocks come first and leave when they are done
@@ -1024,7 +1025,8 @@ CSB_API int csb_gemm_reducescatter_bf16(const void* A, const void* B, void* C, i
 
 // Fused all-gather + GEMM: C[M,N] = A_full * op(B)^T where A_full [M][K] (K-major) is sharded by rows over `world`
 // ranks (range r of csb_ar_layout on rank r).  shard_ptrs[r] = rank r's shard (peer-mapped, row pitch K); a_full = local
-// [M][K] buffer that the kernel fills (and that the caller may keep, e.g. for the weight gradient); ready = local
+// [M][K] buffer whose PEER rows the kernel fills (the caller copies its own shard in; it may keep the buffer, e.g. for
+// the weight gradient); ready = local
 // int[world] counters (rank r stores ready_value there once its shard is staged); pulled = local int[world] counters,
 // zero at start, advanced by pull_ctas per call: pass pull_target = pull_ctas * (number of calls so far, this one included).
 CSB_API int csb_ag_gemm_bf16(void* const* shard_ptrs, void* a_full, const void* B, void* C, int M, int N, int K, int ldb,

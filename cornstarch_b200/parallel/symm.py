@@ -133,10 +133,11 @@ class _AGContext:
     call i + 1 while a slower peer still copies call i), the "shard staged" counters the peers write, and the local
     counters of the pulling thread blocks."""
 
-    PULL_CTAS = 16
-
     def __init__(self, group, M: int, K: int):
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        # thread blocks of the GEMM launch that pull the peers' shards (each keeps 112 KB in flight); they hold their SMs
+        # for the whole launch, so no more than the links need
+        self.PULL_CTAS = 8 if self.world == 2 else 16
         self.M, self.K = M, K
         assert M % (128 * self.world) == 0, "the row count must split into whole 128-row tiles per rank"
         self.rows = M // self.world
@@ -265,6 +266,7 @@ class FusedTensorParallel:
         lib, st = nat.lib(), nat.stream()
         nat.check(lib.csb_cp_signal(ctx.flag_ptrs.data_ptr(), self.world, self.rank, ctx.calls, st), "csb_cp_signal")
         a_full = torch.empty((M, K), dtype=torch.bfloat16, device=a_shard.device)
+        a_full[self.rank * rows : (self.rank + 1) * rows].copy_(a_shard)  # the kernel reads these rows from the shard in place
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a_shard.device)
         status = nat.status_word(a_shard.device)
         nat.check(
