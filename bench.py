@@ -290,6 +290,31 @@ def main():
         ms_e2e = t0.elapsed_time(t1)
     else:
         ms_e2e, last = ms, None
+    timeline_path = os.environ.get("CORNSTARCH_B200_TIMELINE")
+    if timeline_path:
+        # untimed extra steps with CUDA events around every schedule range: where each rank's device time goes
+        from cornstarch_b200.utils import trace
+
+        sync()
+        trace.timeline(True)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(2):
+            trainer.step_device()
+        b.record()
+        totals = trace.timeline_totals()
+        trace.timeline(False)
+        rec = {"rank": rank, "role": getattr(trainer, "role", trainer.parallelism), "step_ms": round(a.elapsed_time(b) / 2, 2),
+               "ranges": {k: {"count": c // 2, "ms_per_step": round(t / 2, 2)} for k, (c, t) in sorted(totals.items())}}
+        covered = sum(v["ms_per_step"] for k, v in rec["ranges"].items())
+        rec["other_ms_per_step"] = round(rec["step_ms"] - covered, 2)
+        everyone = [rec]
+        if world > 1:
+            everyone = [None] * world
+            dist.all_gather_object(everyone, rec)
+        if rank == 0:
+            with open(timeline_path, "w") as f:
+                json.dump(everyone, f, indent=1)
     if world > 1:
         t = torch.tensor([ms, ms_e2e], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

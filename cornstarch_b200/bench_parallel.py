@@ -76,6 +76,8 @@ class PipelineTrainer:
         self.h2d_bytes_per_step = sum(v.numel() * v.element_size() for v in self.host.values())
         self.d2h_bytes_per_step = 4
         self.is_last = self.plugin.stage_manager.is_last_stage(check_only_in_modal=False)
+        sm = self.plugin.stage_manager
+        self.role = f"{self.model.my_modal_name} stage {sm.stage_in_modal + 1}/{sm.num_stages_in_modal}, tp rank {M.coords[0][M.tp_axis]}"
 
     def _step(self, batch):
         out = self.booster.execute_pipeline(iter([batch]), self.model, self.criterion, self.opt, return_loss=True)

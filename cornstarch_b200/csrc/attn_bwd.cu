@@ -278,41 +278,42 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks this code in step (every lane waits on the barriers; one elected lane issues each MMA and
+    // commit): see umma_f16_w.  A 16-wide slice of a tile is the tile's descriptor plus the slice's byte offset / 16.
+    {
       const uint32_t idesc_s = make_idesc_bf16(128, BW_BQ, 0, 0);
       const uint32_t idesc_dkv = make_idesc_bf16(128, p.dk16, 0, 1);
       const uint32_t idesc_dq = make_idesc_bf16(128, BW_BQ, 1, 1);
-      const uint32_t k_s = smem_u32(smem + L::K_OFF);
-      const uint32_t v_s = smem_u32(smem + L::V_OFF);
-      const uint32_t dst_s = smem_u32(smem + L::DST_OFF);
+      const uint64_t k_km = make_desc_kmajor_sw128(smem_u32(smem + L::K_OFF));
+      const uint64_t v_km = make_desc_kmajor_sw128(smem_u32(smem + L::V_OFF));
+      const uint64_t k_mn = make_desc_mnmajor_sw128(smem_u32(smem + L::K_OFF), KV_CHUNK);
+      const uint64_t dst_km = make_desc_kmajor_sw128(smem_u32(smem + L::DST_OFF));
+      const uint64_t dst_mn = make_desc_mnmajor_sw128(smem_u32(smem + L::DST_OFF), KV_CHUNK);
       const int ksteps_d = p.dk16 / 16;
       bool ok = bw_wait(kv_full, 0, abort_flag);
       if (!ok) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; }
+      auto kslice = [](int kk, int chunk_bytes) -> uint64_t {
+        return static_cast<uint64_t>(((kk >> 2) * chunk_bytes + (kk & 3) * 32) >> 4);
+      };
 
       // S^T(it) = K Q^T into ST[it & 1]; waits for the Q/dO stage of that iteration
       auto issue_st = [&](int it) -> bool {
         const int st = it % QS;
         if (!bw_wait(&q_full[st], (it / QS) & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
         tc_fence_after();
-        const uint32_t q_s = smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK);
+        const uint64_t q_km = make_desc_kmajor_sw128(smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK));
         const uint32_t t_st = tmem_base + (it & 1) * 64;
-        for (int kk = 0; kk < ksteps_d; ++kk) {
-          const uint32_t a_off = (kk >> 2) * KV_CHUNK + (kk & 3) * 32;
-          const uint32_t b_off = (kk >> 2) * Q_CHUNK + (kk & 3) * 32;
-          umma_f16(t_st, make_desc_kmajor_sw128(k_s + a_off), make_desc_kmajor_sw128(q_s + b_off), idesc_s, kk > 0);
-        }
+        for (int kk = 0; kk < ksteps_d; ++kk)
+          umma_f16_w(t_st, k_km + kslice(kk, KV_CHUNK), q_km + kslice(kk, Q_CHUNK), idesc_s, kk > 0);
         return true;
       };
       // dP^T(it) = V dO^T; its commit also covers S^T(it), issued earlier
       auto issue_dpt = [&](int it) {
         const int st = it % QS;
-        const uint32_t do_s = smem_u32(smem + L::DO_OFF + st * 2 * Q_CHUNK);
-        for (int kk = 0; kk < ksteps_d; ++kk) {
-          const uint32_t a_off = (kk >> 2) * KV_CHUNK + (kk & 3) * 32;
-          const uint32_t b_off = (kk >> 2) * Q_CHUNK + (kk & 3) * 32;
-          umma_f16(tmem_dPT, make_desc_kmajor_sw128(v_s + a_off), make_desc_kmajor_sw128(do_s + b_off), idesc_s, kk > 0);
-        }
-        umma_commit(sdp_full);
+        const uint64_t do_km = make_desc_kmajor_sw128(smem_u32(smem + L::DO_OFF + st * 2 * Q_CHUNK));
+        for (int kk = 0; kk < ksteps_d; ++kk)
+          umma_f16_w(tmem_dPT, v_km + kslice(kk, KV_CHUNK), do_km + kslice(kk, Q_CHUNK), idesc_s, kk > 0);
+        umma_commit_w(sdp_full);
       };
 
       if (ok && n_iter > 0) {
@@ -325,18 +326,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!bw_wait(pds_full, it & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
         tc_fence_after();
         if (it + 1 < n_iter) issue_dpt(it + 1);  // dP^T columns were read before pds_full(it)
-        const uint32_t q_s = smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK);
-        const uint32_t do_s = smem_u32(smem + L::DO_OFF + st * 2 * Q_CHUNK);
+        const uint64_t q_mn = make_desc_mnmajor_sw128(smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK), Q_CHUNK);
+        const uint64_t do_mn = make_desc_mnmajor_sw128(smem_u32(smem + L::DO_OFF + st * 2 * Q_CHUNK), Q_CHUNK);
         // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows)
 #pragma unroll
         for (int kk = 0; kk < BW_BQ / 16; ++kk)
-          umma_f16_ts(tmem_dV, tmem_base + (it & 1) * 64 + (kk / (COLS / 16)) * COLS + (kk % (COLS / 16)) * 8,
-                      make_desc_mnmajor_sw128(do_s + kk * 2048, Q_CHUNK), idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_f16_ts_w(tmem_dV, tmem_base + (it & 1) * 64 + (kk / (COLS / 16)) * COLS + (kk % (COLS / 16)) * 8,
+                        do_mn + static_cast<uint64_t>((kk * 2048) >> 4), idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < BW_BQ / 16; ++kk)
-          umma_f16(tmem_dK, make_desc_kmajor_sw128(dst_s + kk * 32), make_desc_mnmajor_sw128(q_s + kk * 2048, Q_CHUNK),
-                   idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&q_empty[st]);
+          umma_f16_w(tmem_dK, dst_km + static_cast<uint64_t>((kk * 32) >> 4), q_mn + static_cast<uint64_t>((kk * 2048) >> 4),
+                     idesc_dkv, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit_w(&q_empty[st]);
         if (it > 0) {
           if (!bw_wait(dq_free, (it - 1) & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_TMEM_EMPTY); *abort_flag = 1; break; }
           tc_fence_after();
@@ -344,10 +345,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // dQ^T = K^T dS^T  (contraction over the 128 key rows)
 #pragma unroll
         for (int kk = 0; kk < BW_BKV / 16; ++kk)
-          umma_f16(tmem_dQT, make_desc_mnmajor_sw128(k_s + kk * 2048, KV_CHUNK),
-                   make_desc_mnmajor_sw128(dst_s + kk * 2048, KV_CHUNK), idesc_dq, kk > 0 ? 1u : 0u);
-        umma_commit(pds_empty);
-        umma_commit(dq_full);
+          umma_f16_w(tmem_dQT, k_mn + static_cast<uint64_t>((kk * 2048) >> 4), dst_mn + static_cast<uint64_t>((kk * 2048) >> 4),
+                     idesc_dq, kk > 0 ? 1u : 0u);
+        umma_commit_w(pds_empty);
+        umma_commit_w(dq_full);
         if (it + 2 < n_iter) ok = issue_st(it + 2);  // ST[it & 1] was read before pds_full(it)
       }
     }

@@ -280,10 +280,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks this code in step (every lane waits on the barriers; one elected lane issues each MMA and
+    // commit): see umma_f16_w.
+    {
       const uint32_t idesc_s = make_idesc_bf16(AT_BM, AT_BN, 0, 0);
       const uint32_t idesc_o = make_idesc_bf16(AT_BM, p.dk16, 0, 1);
-      const uint32_t q_s = smem_u32(smem + L::Q_OFF);
+      const uint64_t q_desc = make_desc_kmajor_sw128(smem_u32(smem + L::Q_OFF));
       const int ksteps_s = p.dk16 / 16;
       bool ok = at_wait(q_full, 0, abort_flag);
       if (!ok) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; }
@@ -299,14 +301,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint32_t ph = (it >> 1) & 1;
         if (!at_wait(&k_full[st], ph, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; return false; }
         tc_fence_after();
-        const uint32_t k_s = smem_u32(smem + L::K_OFF + st * L::KV_BYTES);
+        // descriptors of the k-th 16-wide slice: the tile's descriptor plus the slice's byte offset / 16
+        const uint64_t k_desc = make_desc_kmajor_sw128(smem_u32(smem + L::K_OFF + st * L::KV_BYTES));
         for (int kk = 0; kk < ksteps_s; ++kk) {
-          const uint32_t off = (kk >> 2) * CHUNK_BYTES + (kk & 3) * 32;
-          umma_f16(tmem_S + st * 128, make_desc_kmajor_sw128(q_s + off), make_desc_kmajor_sw128(k_s + off), idesc_s,
-                   kk > 0 ? 1u : 0u);
+          const uint64_t off = static_cast<uint64_t>(((kk >> 2) * CHUNK_BYTES + (kk & 3) * 32) >> 4);
+          umma_f16_w(tmem_S + st * 128, q_desc + off, k_desc + off, idesc_s, kk > 0 ? 1u : 0u);
         }
-        umma_commit(&k_empty[st]);
-        umma_commit(&s_full[st]);
+        umma_commit_w(&k_empty[st]);
+        umma_commit_w(&s_full[st]);
         return true;
       };
       if (ok && n > 0) ok = issue_s(0);
@@ -320,15 +322,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (!at_wait(&v_full[st], ph, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
         if (!at_wait(p_full, it & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
         tc_fence_after();
-        const uint32_t v_s = smem_u32(smem + L::V_OFF + st * L::KV_BYTES);
+        const uint64_t v_desc = make_desc_mnmajor_sw128(smem_u32(smem + L::V_OFF + st * L::KV_BYTES), CHUNK_BYTES);
         // O += P V with P read from tensor memory: 16 keys of a row = 8 packed 32-bit columns per step
 #pragma unroll
         for (int kk = 0; kk < AT_BN / 16; ++kk)
-          umma_f16_ts(tmem_O, tmem_S + st * 128 + kk * 8, make_desc_mnmajor_sw128(v_s + kk * 2048, CHUNK_BYTES), idesc_o,
-                      (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&v_empty[st]);
-        umma_commit(pv_done);
-        if (it + 1 == (uint32_t)n) umma_commit(o_done);
+          umma_f16_ts_w(tmem_O, tmem_S + st * 128 + kk * 8, v_desc + static_cast<uint64_t>((kk * 2048) >> 4), idesc_o,
+                        (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit_w(&v_empty[st]);
+        umma_commit_w(pv_done);
+        if (it + 1 == (uint32_t)n) umma_commit_w(o_done);
       }
     }
     __syncwarp();

@@ -527,7 +527,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0 && leader) {
+    // the whole warp walks this code in step; one elected lane issues each MMA and commit (see umma_f16_w)
+    if (leader) {
       constexpr uint32_t idesc = make_idesc_bf16(BM * CG, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t it = 0;
       uint32_t local_tile = 0;
@@ -561,12 +562,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             // K-major: 16 elements = 32 bytes along the swizzled row; MN-major: 16 rows of 128 bytes.
             const uint64_t a_adv = A_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : (uint64_t)((k * UMMA_K * 2) >> 4);
             const uint64_t b_adv = B_MN ? (uint64_t)((k * UMMA_K * 128) >> 4) : (uint64_t)((k * UMMA_K * 2) >> 4);
-            if constexpr (CG == 2) umma_f16_2cta(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-            else umma_f16(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            if constexpr (CG == 2) umma_f16_2cta_w(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            else umma_f16_w(d_tmem, adesc + a_adv, bdesc + b_adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
-          umma_commit_cg<CG>(&empty_bar[s]);  // smem slot (of both blocks) is free once these MMAs retire
+          umma_commit_cg_w<CG>(&empty_bar[s]);  // smem slot (of both blocks) is free once these MMAs retire
         }
-        if (ok) umma_commit_cg<CG>(&tmem_full[acc]);
+        if (ok) umma_commit_cg_w<CG>(&tmem_full[acc]);
       }
     }
     __syncwarp();

@@ -232,13 +232,15 @@ class MultimodalEncoderTrainingOneForwardOneBackwardSchedule:
 
         def take_fwd():
             h = fwd_h
-            inp = self.merge_inputs(comm.wait_all(h)) if h is not None else None
+            with nvtx_range("pipeline/wait_recv_forward"):
+                inp = self.merge_inputs(comm.wait_all(h)) if h is not None else None
             post_fwd()  # the next input travels while this micro-batch is computed
             return inp
 
         def take_bwd():
             h = bwd_h
-            grad = comm.wait_all(h)[0] if h is not None else None
+            with nvtx_range("pipeline/wait_recv_backward"):
+                grad = comm.wait_all(h)[0] if h is not None else None
             post_bwd()
             return grad
 
