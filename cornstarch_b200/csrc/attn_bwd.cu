@@ -77,7 +77,7 @@ struct BwdSmem {
   static constexpr int LIST_OFF = META_OFF + 2 * META_STAGE;  // valid 64-row query tiles of this key block: int16 index, int8 class
   static constexpr int MAX_TILES = 1024;                      // sequences up to 65536 tokens
   static constexpr int BAR_OFF = LIST_OFF + MAX_TILES * 4;
-  static constexpr int NBAR = 1 + QSTAGES + QSTAGES + 1 + 1 + 1 + 1 + 1 + 1;
+  static constexpr int NBAR = 1 + QSTAGES + QSTAGES + 1 + 1 + 1 + 1 + 1 + 1 + 1;
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 32;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
@@ -168,6 +168,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* dq_full = pds_empty + 1;      //       dQ^T ready in TMEM
   uint64_t* dq_free = dq_full + 1;        //       dQ^T drained (256 arrivals)
   uint64_t* meta_full = dq_free + 1;      //       per-iteration query metadata staged (256 arrivals)
+  uint64_t* dp_read = meta_full + 1;      //       S^T and dP^T of an iteration are in registers (256 arrivals): dP^T may be overwritten
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* n_valid_slot = reinterpret_cast<int*>(tmem_slot + 2);
@@ -200,6 +201,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(dq_full, 1);
     mbar_init(dq_free, CFG::COMPUTE_THREADS);
     mbar_init(meta_full, CFG::COMPUTE_THREADS);
+    mbar_init(dp_read, CFG::COMPUTE_THREADS);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -323,9 +325,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       for (int it = 0; ok && it < n_iter; ++it) {
         const int st = it % QS;
+        // dP^T(it+1) is issued as soon as the compute warps hold dP^T(it) in registers, long before they are done with
+        // the iteration: S^T(it+1) and dP^T(it+1) are then ready when they come back for the next one
+        if (it + 1 < n_iter) {
+          if (!bw_wait(dp_read, it & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
+          tc_fence_after();
+          issue_dpt(it + 1);
+        }
         if (!bw_wait(pds_full, it & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
         tc_fence_after();
-        if (it + 1 < n_iter) issue_dpt(it + 1);  // dP^T columns were read before pds_full(it)
         const uint64_t q_mn = make_desc_mnmajor_sw128(smem_u32(smem + L::Q_OFF + st * 2 * Q_CHUNK), Q_CHUNK);
         const uint64_t do_mn = make_desc_mnmajor_sw128(smem_u32(smem + L::DO_OFF + st * 2 * Q_CHUNK), Q_CHUNK);
         // dV += P^T dO ; dK += dS^T Q   (contraction over the 64 query rows)
@@ -448,6 +456,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_cols<COLS>(tmem_base + (it & 1) * 64 + col0 + lane_addr, sv);
       tmem_ld_cols<COLS>(tmem_dPT + col0 + lane_addr, dv);
       tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(dp_read);
       float pv[COLS], ds[COLS];
       const int q_base = tile_idx[it % n_valid] * BW_BQ + col0;  // first query row of this thread's columns
       if (p.bias != nullptr && k_valid) {

@@ -3,13 +3,16 @@
 //   O = softmax(scale * Q K^T + mask) V,   LSE = log sum exp   (per query row)
 //
 // One CTA = one 128-row query tile of one head.  Both GEMMs run on tcgen05 with TMEM accumulators:
-//   S = Q K^T   : A = Q tile (K-major smem), B = K tile (K-major smem)      -> TMEM S[2] (double buffer)
-//   O += P V    : A = P tile in TMEM (bf16 pairs written by the softmax threads over the columns of S), B = V tile
-//                 (MN-major smem)
-// Warp roles: warp 0 = TMA producer (Q once, K/V ring of 2 stages), warp 1 = MMA issuer,
-// warps 2..9 = softmax: two threads per query row (one TMEM lane), each owning 64 of a tile's 128 key
-// columns; the pair exchanges its row maximum through shared memory.  The running maximum is only refreshed when it grows by more than 2^8 (lazy rescale),
-// which keeps the TMEM read-modify-write of O off the common path.
+//   S = Q K^T    : A = Q tile (K-major smem), B = K tile (K-major smem)      -> TMEM S[2] (double buffer)
+//   O[h] += P V  : A = P tile in TMEM (bf16 pairs written by the softmax threads over the columns of S), B = V tile
+//                  (MN-major smem)                                            -> TMEM O[2]
+// Warp roles: warp 0 = TMA producer (Q once, K/V ring of 2 stages), warp 1 = MMA issuer (the whole warp walks the code,
+// one elected lane issues), warps 2..9 = softmax: two threads per query row (one TMEM lane), thread (r, h) owning key
+// columns [64 h, 64 h + 64) of every tile.  Each thread is an independent online softmax over ITS columns (own running
+// maximum and row sum), and the keys of column half h accumulate into their own output O[h]: no exchange between the two
+// threads of a row inside the loop, and the P V of a half is issued as soon as that half's threads are done.  The epilogue
+// merges the two partial results of a row.  The running maximum is only refreshed when it grows by more than 2^8 (lazy
+// rescale), which keeps the TMEM read-modify-write of O off the common path.
 //
 // Mask handling: a [B][nQ][nK] int8 class map (0 = skip tile, 1 = evaluate the predicate per element,
 // 2 = all allowed) is produced once per step by csb_mask_classify and shared by all layers, heads, the
@@ -141,7 +144,7 @@ struct AttnSmem {
   static constexpr int CLS_OFF = XM_OFF + 6 * 128 * 4;        // + row-sum exchange [2 halves][128]; then the tile classes
   static constexpr int MAX_NK = 1024;                         // key blocks per row of the class map (131072 keys)
   static constexpr int BAR_OFF = CLS_OFF + MAX_NK;
-  static constexpr int NBAR = 1 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 1 + 4 + 1;
+  static constexpr int NBAR = 1 + 2 + 2 + 2 + 2 + 2 + 2 + 1 + 1 + 4 + 1;
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 16;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
@@ -173,11 +176,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* v_full = bars + 5;
   uint64_t* v_empty = bars + 7;
   uint64_t* s_full = bars + 9;
-  uint64_t* p_full = bars + 11;
-  uint64_t* pv_done = bars + 12;
-  uint64_t* kb_full = bars + 13;  // key bits / positions of a partial tile staged by the softmax threads
-  uint64_t* pair_bar = bars + 14; // [4] one per lane quarter: the two warps that share its query rows
-  uint64_t* o_done = bars + 18;   // the last P V has retired: O is final
+  uint64_t* p_full = bars + 11;   // [2] the threads of one column half have written their part of P
+  uint64_t* pv_done = bars + 13;
+  uint64_t* kb_full = bars + 14;  // key bits / positions of a partial tile staged by the softmax threads
+  uint64_t* pair_bar = bars + 15; // [4] one per lane quarter: the two warps that share its query rows (epilogue)
+  uint64_t* o_done = bars + 19;   // the last P V has retired: both O accumulators are final
   float* xm_s = reinterpret_cast<float*>(smem + L::XM_OFF);
   int8_t* cls_s = reinterpret_cast<int8_t*>(smem + L::CLS_OFF);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBAR);
@@ -218,7 +221,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
     }
-    mbar_init(p_full, 256);
+    mbar_init(&p_full[0], 128);
+    mbar_init(&p_full[1], 128);
     mbar_init(pv_done, 1);
     mbar_init(o_done, 1);
     mbar_init(kb_full, 256);
@@ -235,7 +239,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base;        // 2 x 128 columns
-  const uint32_t tmem_O = tmem_base + 256;  // up to 128 columns
+  const uint32_t tmem_O = tmem_base + 256;  // 2 x (up to 128) columns: O[h] accumulates the keys of column half h of every tile
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -320,14 +324,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
         if (!at_wait(&v_full[st], ph, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_FULL); *abort_flag = 1; break; }
-        if (!at_wait(p_full, it & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_MISC); *abort_flag = 1; break; }
-        tc_fence_after();
         const uint64_t v_desc = make_desc_mnmajor_sw128(smem_u32(smem + L::V_OFF + st * L::KV_BYTES), CHUNK_BYTES);
-        // O += P V with P read from tensor memory: 16 keys of a row = 8 packed 32-bit columns per step
+        // O[h] += P_h V_h for the two column halves of the tile, each as soon as its threads have written P_h (packed
+        // bf16 pairs in the first 32 columns of that half of the S buffer: 16 keys of a row = 8 columns per step)
 #pragma unroll
-        for (int kk = 0; kk < AT_BN / 16; ++kk)
-          umma_f16_ts_w(tmem_O, tmem_S + st * 128 + kk * 8, v_desc + static_cast<uint64_t>((kk * 2048) >> 4), idesc_o,
-                        (it > 0 || kk > 0) ? 1u : 0u);
+        for (int hh = 0; hh < 2; ++hh) {
+          if (!at_wait(&p_full[hh], it & 1, abort_flag)) { atomicCAS(p.status, 0, ST_TIMEOUT_MISC); *abort_flag = 1; ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < AT_BN / 32; ++kk)
+            umma_f16_ts_w(tmem_O + hh * 128, tmem_S + st * 128 + hh * 64 + kk * 8,
+                          v_desc + static_cast<uint64_t>(((hh * 4 + kk) * 2048) >> 4), idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        if (!ok) break;
         umma_commit_w(&v_empty[st]);
         umma_commit_w(pv_done);
         if (it + 1 == (uint32_t)n) umma_commit_w(o_done);
@@ -351,7 +360,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (p.q_pos) qpos = p.q_pos[(long)b * p.Sq + q];
     }
     float m_used = -INFINITY, l_sum = 0.f;
-    uint32_t it = 0, n_partial = 0, n_pair = 0;
+    uint32_t it = 0, n_partial = 0;
     bool ok = true;
     auto fail = [&](int code) {
       if (lane == 0) atomicCAS(p.status, 0, code);
@@ -431,37 +440,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mx2 = fmaxf(mx2, s[i + 2]);
         mx3 = fmaxf(mx3, s[i + 3]);
       }
-      float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      // exchange with the thread that holds the other 64 columns of this row
-      xm_s[(buf * 2 + half) * 128 + r] = mx;
-      mbar_arrive(&pair_bar[quarter]);
-      if (!at_wait(&pair_bar[quarter], n_pair & 1, abort_flag)) { fail(ST_TIMEOUT_MISC); break; }
-      ++n_pair;
-      mx = fmaxf(mx, xm_s[(buf * 2 + (half ^ 1)) * 128 + r]);
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));  // of this thread's half of the row only
       const float m_new = fmaxf(m_used, mx);
       const bool need = (m_new - m_used) * p.scale_log2 > 8.f;  // also true when m_used is -inf and m_new is finite
       if (it > 0 && __any_sync(0xffffffffu, need)) {
-        // rare (lazy rescale): O is only touched once the previous P V has retired
+        // rare (lazy rescale): O[half] is only touched once the previous P V has retired
         if (!at_wait(pv_done, (it - 1) & 1, abort_flag)) { fail(ST_TIMEOUT_MISC); break; }
         tc_fence_after();
         float alpha = 1.f;
         if (need) alpha = (m_used == -INFINITY) ? 0.f : fast_exp2((m_used - m_new) * p.scale_log2);
-#pragma unroll
-        for (int cc = 0; cc < NCH; ++cc) {
+#pragma unroll 1
+        for (int cc = 0; cc < 2 * NCH; ++cc) {
           uint32_t v[32];
-          tmem_ld_32x32(tmem_O + (half * NCH + cc) * 32 + lane_addr, v);
+          tmem_ld_32x32(tmem_O + half * 128 + cc * 32 + lane_addr, v);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-          tmem_st_32x32(tmem_O + (half * NCH + cc) * 32 + lane_addr, v);
+          tmem_st_32x32(tmem_O + half * 128 + cc * 32 + lane_addr, v);
         }
         tmem_st_wait();
         l_sum *= alpha;
       }
       if (need) m_used = m_new;
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used * p.scale_log2;
-      // probabilities -> packed bf16 pairs -> tensor memory, over the first 64 columns of this tile's S buffer (the
-      // partner's S values there were read before the pair barrier above): thread (r, half) writes keys 64*half.. of row r
+      // probabilities -> packed bf16 pairs -> tensor memory, over the first 32 of this thread's own 64 columns of the
+      // tile's S buffer (its scores are in registers by now)
       uint32_t pk[32];
       float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
 #pragma unroll
@@ -477,7 +480,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         pk[i / 2] = pack_bf16x2(e0, e1);
         pk[i / 2 + 1] = pack_bf16x2(e2, e3);
       }
-      tmem_st_32x32(tmem_S + buf * 128 + half * 32 + lane_addr, pk);
+      tmem_st_32x32(tmem_S + buf * 128 + half * 64 + lane_addr, pk);
       tmem_st_wait();
       l_sum += (ls0 + ls1) + (ls2 + ls3);
       // Arrive for tile `it` only once P V(it-1) has retired.  Without this, nothing bounds how far the softmax threads
@@ -486,7 +489,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // twice within one phase.  The exponentials above are already done, so the wait is normally free.
       if (it > 0 && !at_wait(pv_done, (it - 1) & 1, abort_flag)) { fail(ST_TIMEOUT_MISC); break; }
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(&p_full[half]);
       ++it;
     }
     // ---- epilogue
@@ -495,26 +498,38 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (!at_wait(o_done, 0, abort_flag)) fail(ST_TIMEOUT_MISC);
     }
     if (ok) {
-      // total row sum = this thread's columns + the partner's
-      xm_s[(4 + half) * 128 + r] = l_sum;
+      // merge the two halves' partial softmax results (running maximum, row sum, accumulator) of this row
+      xm_s[half * 128 + r] = m_used;
+      xm_s[(2 + half) * 128 + r] = l_sum;
       mbar_arrive(&pair_bar[quarter]);
-      if (!at_wait(&pair_bar[quarter], n_pair & 1, abort_flag)) fail(ST_TIMEOUT_MISC);
+      if (!at_wait(&pair_bar[quarter], 0, abort_flag)) fail(ST_TIMEOUT_MISC);
     }
     if (ok) {
-      l_sum += xm_s[(4 + (half ^ 1)) * 128 + r];
       tc_fence_after();
-      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      const float m0 = xm_s[r], m1 = xm_s[128 + r];
+      const float l0 = xm_s[256 + r], l1 = xm_s[384 + r];
+      const float m = fmaxf(m0, m1);
+      const float a0 = (m0 == -INFINITY) ? 0.f : fast_exp2((m0 - m) * p.scale_log2);
+      const float a1 = (m1 == -INFINITY) ? 0.f : fast_exp2((m1 - m) * p.scale_log2);
+      const float l = l0 * a0 + l1 * a1;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const float w0 = a0 * inv, w1 = a1 * inv;
       __nv_bfloat16* o_row = p.O + (long)b * p.o_stride_b + (long)q * p.o_stride_s + (long)h * p.D;
+      // thread (r, half) writes output columns [half * NCH * 32, +NCH * 32) of row r
 #pragma unroll
       for (int cc = 0; cc < NCH; ++cc) {
         const int col0 = (half * NCH + cc) * 32;
-        uint32_t v[32];
+        float o[32];
         if (it > 0) {
-          tmem_ld_32x32(tmem_O + col0 + lane_addr, v);
+          uint32_t v0[32], v1[32];
+          tmem_ld_32x32(tmem_O + col0 + lane_addr, v0);
+          tmem_ld_32x32(tmem_O + 128 + col0 + lane_addr, v1);
           tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v0[i]) * w0 + __uint_as_float(v1[i]) * w1;
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = 0u;
+          for (int i = 0; i < 32; ++i) o[i] = 0.f;
         }
         if (row_valid) {
 #pragma unroll
@@ -522,17 +537,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const int col = col0 + g * 8;
             if (col + 8 <= p.D) {
               uint4 u;
-              u.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
-              u.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
-              u.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
-              u.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+              u.x = pack_bf16x2(o[g * 8 + 0], o[g * 8 + 1]);
+              u.y = pack_bf16x2(o[g * 8 + 2], o[g * 8 + 3]);
+              u.z = pack_bf16x2(o[g * 8 + 4], o[g * 8 + 5]);
+              u.w = pack_bf16x2(o[g * 8 + 6], o[g * 8 + 7]);
               *reinterpret_cast<uint4*>(o_row + col) = u;
             }
           }
         }
       }
       if (row_valid && half == 0)
-        p.lse[((long)b * p.Hq + h) * p.Sq + q] = l_sum > 0.f ? m_used * p.scale + logf(l_sum) : -INFINITY;
+        p.lse[((long)b * p.Hq + h) * p.Sq + q] = l > 0.f ? m * p.scale + logf(l) : -INFINITY;
     }
   }
 
