@@ -39,6 +39,7 @@ _PROTOS = {
     "csb_adamw_split": [vp, vp, vp, vp, vp, i32, i64, f32, f32, f32, f32, f32, f32, f32, vp, vp, i32, vp],
     "csb_sumsq": [vp, i32, i64, vp, vp, i32, vp],
     "csb_clip_scale": [vp, f32, f32, vp, vp, vp, vp, vp],
+    "csb_mma_issue_probe": [i32, i32, i32, i32, vp, vp],
     "csb_ce_stats": [vp, i64, vp, i32, i32, vp, vp, vp, i64, vp],
     "csb_ce_grad": [vp, i64, vp, i32, i32, vp, vp, vp, vp, vp, i64, i64, vp],
     "csb_gather_merge": [vp, vp, vp, vp, i64, i32, i64, i64, vp],

@@ -235,7 +235,16 @@ class MultimodalParallelPlugin:
         if env is not None:
             overlap = env == "1"
         if overlap is None:
-            overlap = dist.get_backend() == "nccl"
+            # A receive that was posted ahead is an NCCL kernel that stays on the GPU until its sender has sent.  The fused
+            # tensor- / context- / expert-parallel kernels are persistent (one thread block per SM) and wait for their peers
+            # inside the kernel: they need every thread block resident at once.  With a pending receive holding SMs on
+            # both ranks of a pair, each rank's late blocks wait for an SM that the other rank's waiting blocks hold, and
+            # every such launch runs into its bounded wait (measured: 2 s per fused GEMM on 4 GPUs).  So the overlap is on
+            # by default only where no such kernel runs: every modality without tensor, context or expert parallelism.
+            plugins = list(self.encoder_plugins.values()) + [self.language_model_plugin]
+            peer_kernels = any(getattr(pl, "tp_size", 1) > 1 or getattr(pl, "sp_size", 1) > 1 or getattr(pl, "ep_size", 1) > 1
+                               for pl in plugins if pl is not None)
+            overlap = dist.get_backend() == "nccl" and not peer_kernels
         edge_groups = None
         if overlap:
             from ..parallel.p2p import make_edge_groups

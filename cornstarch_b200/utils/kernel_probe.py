@@ -295,11 +295,34 @@ def probe_attn_fwd_pulled(a, flush):
            direct_ms=round(ms_direct, 4))
 
 
+def probe_mma_issue(a, flush):
+    """Cycles per tcgen05.mma (128 x N x 16) for a run of 512 issued by one warp: a single lane in a divergent branch
+    against the whole converged warp with an elected lane, with idle and with busy (dense FMA) neighbour warps."""
+    from ..ops import _native as nat
+
+    lib = nat.lib()
+    out = torch.zeros(4, dtype=torch.int64, device="cuda")
+    reps = 64
+    for busy in (0, 1):
+        for n in (64, 128, 256):
+            row = {"kernel": "mma_issue", "tile": f"128x{n}x16", "neighbour_warps": "dense FMAs" if busy else "idle",
+                   "cycles_at_tensor_peak": 128 * n * 16 * 2 // 8192}
+            for whole in (0, 1):
+                for _ in range(3):
+                    nat.check(lib.csb_mma_issue_probe(n, whole, busy, reps, out.data_ptr(), nat.stream()), "csb_mma_issue_probe")
+                torch.cuda.synchronize()
+                issued, retired, ok = out[:3].tolist()
+                assert ok == 1
+                row["one_lane" if whole == 0 else "whole_warp_elected"] = {"issue_cycles_per_mma": round(issued / (reps * 8), 1),
+                                                                             "retire_cycles_per_mma": round(retired / (reps * 8), 1)}
+            print(json.dumps(row), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--seconds", type=float, default=3.0)
     ap.add_argument("what", choices=["gemm", "gemm_sustained", "attn_fwd", "attn_bwd", "elementwise", "gemm_ar_local", "adamw", "grad_reduce_local",
-                                     "moe_push_local", "attn_fwd_pulled", "all"])
+                                     "moe_push_local", "attn_fwd_pulled", "mma_issue", "all"])
     ap.add_argument("--reducers", type=int, default=16)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
@@ -319,7 +342,7 @@ def main():
     for t in todo:
         {"gemm": probe_gemm, "gemm_sustained": probe_gemm_sustained, "attn_fwd": probe_attn_fwd, "attn_bwd": probe_attn_bwd, "elementwise": probe_elementwise,
          "gemm_ar_local": probe_gemm_ar_local, "adamw": probe_adamw, "grad_reduce_local": probe_grad_reduce_local,
-         "moe_push_local": probe_moe_push_local, "attn_fwd_pulled": probe_attn_fwd_pulled}[t](a, flush)
+         "moe_push_local": probe_moe_push_local, "attn_fwd_pulled": probe_attn_fwd_pulled, "mma_issue": probe_mma_issue}[t](a, flush)
     from ..ops import _native as nat
 
     nat.check_status()
