@@ -9,6 +9,10 @@ import torch
 from cornstarch_b200.ops import attention as A
 
 pytestmark = pytest.mark.gpu
+# Bound on max|kernel - oracle| / max(1, max|oracle|).  The outputs are bf16: one unit in the last place at the largest
+# magnitude is 2^-8 = 3.9e-3 of it, and P is rounded to bf16 before P V (and dS before dK / dQ), so a few such roundings
+# add up on the small, short cases here (10 of 120 cases exceed 5e-3).  At the benchmark shapes, where sums run
+# over thousands of keys, the kernels stay inside the reference's 5e-3 (tests/test_benchmark_shapes.py).
 TOL = 5e-3 * 4
 
 
