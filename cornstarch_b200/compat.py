@@ -24,7 +24,7 @@ _ALIASES = {
     "cornstarch.pipeline_template": "cornstarch_b200.pipeline_template",
     "cornstarch.models": "cornstarch_b200.models",
     "cornstarch.models.multimodal_language_model": "cornstarch_b200.multimodal",
-    **{f"cornstarch.models.multimodal_language_model.{m}": "cornstarch_b200.models.multimodal_language_model"
+    **{f"cornstarch.models.multimodal_language_model.{m}": "cornstarch_b200.multimodal"
        for m in ("modeling_multimodal_language_model", "processing_multimodal_language_model",
                  "configuration_multimodal_language_model")},
     **{f"cornstarch.models.{m}": "cornstarch_b200.models.evaclip"
@@ -37,13 +37,13 @@ _ALIASES = {
     "cornstarch.kernel.attention": "cornstarch_b200.kernel.attention",
     "cornstarch.models.intern_vit.flash_attention": "cornstarch_b200.kernel.attention",  # FlashAttention module
     "cornstarch.plugin": "cornstarch_b200.plugin",
-    "cornstarch.plugin.multimodal_parallel_plugin": "cornstarch_b200.plugin.multimodal_api",
+    "cornstarch.plugin.multimodal_parallel_plugin": "cornstarch_b200.plugin.multimodal_parallel_plugin",
     # the sub-modules of that package: every one resolves to the module that exports all of the package's names
     "cornstarch.plugin.multimodal_parallel_plugin.modal_parallel_plugin": "cornstarch_b200.plugin.modal_parallel_plugin",
     "cornstarch.plugin.multimodal_parallel_plugin.multimodal_parallel_plugin": "cornstarch_b200.plugin.multimodal_parallel_plugin",
     "cornstarch.plugin.multimodal_parallel_plugin.modal_process_group_mesh": "cornstarch_b200.parallel.mesh",
     "cornstarch.plugin.multimodal_parallel_plugin.multimodal_stage_manager": "cornstarch_b200.parallel.stage_manager",
-    "cornstarch.plugin.multimodal_parallel_plugin.multimodal_1f1b": "cornstarch_b200.plugin.multimodal_api",
+    "cornstarch.plugin.multimodal_parallel_plugin.multimodal_1f1b": "cornstarch_b200.parallel.schedule",
     "cornstarch.plugin.multimodal_parallel_plugin.multimodal_parallel_checkpoint_io": "cornstarch_b200.plugin.checkpoint_io",
     "cornstarch.plugin.encoders_colocated_plugin": "cornstarch_b200.plugin.encoders_colocated_plugin",
     "cornstarch.plugin.encoders_colocated_plugin.encoders_colocated_plugin": "cornstarch_b200.plugin.encoders_colocated_plugin",
@@ -60,14 +60,14 @@ _ALIASES = {
     "cornstarch.shardformer.policies": "cornstarch_b200.shardformer.policies",
     "cornstarch.shardformer.policies.auto_policy": "cornstarch_b200.shardformer.policies.auto_policy",
     "cornstarch.shardformer.policies.pipeline_template_policy": "cornstarch_b200.shardformer.policies.pipeline_template_policy",
-    "cornstarch.shardformer.policies.multimodal": "cornstarch_b200.shardformer.policies.families",
-    **{f"cornstarch.shardformer.policies.{m}": "cornstarch_b200.shardformer.policies.families"
+    "cornstarch.shardformer.policies.multimodal": "cornstarch_b200.shardformer.policies.multimodal",
+    **{f"cornstarch.shardformer.policies.{m}": "cornstarch_b200.shardformer.policies.models"
        for m in ("bert", "clip", "dinov2", "evaclip", "gemma", "gemma2", "gemma3", "gpt2", "intern_vit", "llama", "llama4",
                  "mistral", "mixtral", "opt", "phi3", "phi4_multimodal", "pixtral", "qwen2", "qwen2_audio", "qwen2_vision",
                  "qwen3", "qwen3_moe", "siglip", "vit", "whisper")},
     "cornstarch.shardformer.layers": "cornstarch_b200.shardformer.layers",
-    "cornstarch.shardformer.layers.utils": "cornstarch_b200.shardformer.layers.utils",
-    "cornstarch.shardformer.layers.operation": "cornstarch_b200.shardformer.layers.operation",
+    "cornstarch.shardformer.layers.utils": "cornstarch_b200.parallel.cp",
+    "cornstarch.shardformer.layers.operation": "cornstarch_b200.parallel.comm",
     "cornstarch.shardformer.layers.context_parallel_bitfield_attention": "cornstarch_b200.shardformer.layers.context_parallel_bitfield_attention",
     "cornstarch.shardformer.layers.context_parallel_attention": "cornstarch_b200.shardformer.layers.context_parallel_attention",
     "cornstarch.testing": "cornstarch_b200.testing",

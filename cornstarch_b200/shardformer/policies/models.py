@@ -439,3 +439,24 @@ class Dinov2ForImageClassificationPolicy(Dinov2ModelPolicy):
     last_stage_modules = ["dinov2.layernorm", "classifier"]
     head_modules = r"dinov2\.encoder\.layer\.\d+"
     tp_rules = [TPRule(r"dinov2\." + r.pattern, r.kind, r.split_sizes_attr) for r in Dinov2ModelPolicy.tp_rules]
+
+
+# The per-family names the reference uses (``LlamaForCausalLMPolicy``, ``MixtralModelPolicy``, ...;
+# cornstarch/shardformer/policies/<family>.py).  The decoder families share one implementation here: the differences
+# between them are in the model's spec, not in how it is sharded.
+for _family in ("Llama", "Mistral", "Qwen2", "Qwen3", "Gemma", "Gemma2", "Gemma3", "Phi3"):
+    globals()[f"{_family}Policy"] = DecoderModelPolicy
+    globals()[f"{_family}ModelPolicy"] = DecoderModelPolicy
+    globals()[f"{_family}ForCausalLMPolicy"] = DecoderForCausalLMPolicy
+for _family in ("Mixtral", "Qwen3Moe"):
+    globals()[f"{_family}Policy"] = MoeForCausalLMPolicy
+    globals()[f"{_family}ModelPolicy"] = MoeForCausalLMPolicy
+    globals()[f"{_family}ForCausalLMPolicy"] = MoeForCausalLMPolicy
+Llama4Policy = Llama4TextModelPolicy
+SiglipVisionTransformerPolicy = SiglipVisionModelPolicy
+CLIPVisionTransformerPolicy = CLIPVisionModelPolicy
+GPT2Policy = GPT2ModelPolicy
+BertPolicy = BertModelPolicy
+OPTPolicy = OPTModelPolicy
+Phi4MultimodalAudioPolicy = Phi4MultimodalAudioModelPolicy
+LlamaForSequenceClassificationPolicy = DecoderForSequenceClassificationPolicy
