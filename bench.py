@@ -333,7 +333,11 @@ def main():
         dist.all_reduce(pk, op=dist.ReduceOp.MAX)
         peak_gb = float(pk[0])
         # replicated parameters must agree bit for bit inside every data-parallel / tensor-parallel group
-        mine = trainer.checks() if hasattr(trainer, "checks") else {}
+        # (a failure inside the comparison itself is reported in the record instead of costing the timed result)
+        try:
+            mine = trainer.checks() if hasattr(trainer, "checks") else {}
+        except Exception as e:  # noqa: BLE001
+            mine = {"error": {"ranks": 0, "params": 0, "mismatched": 1, "what": f"{type(e).__name__}: {e}"[:200]}}
         everyone = [None] * world
         dist.all_gather_object(everyone, mine)
         checks = {}
@@ -342,6 +346,8 @@ def main():
                 agg = checks.setdefault(k, {"ranks": v["ranks"], "params_compared": 0, "mismatched": 0})
                 agg["params_compared"] += v["params"]
                 agg["mismatched"] += v["mismatched"]
+                if "what" in v:
+                    agg["what"] = v["what"]
         checks["ok"] = all(v["mismatched"] == 0 for v in checks.values() if isinstance(v, dict))
         checks["last_loss_finite"] = bool(last is None or (last == last and abs(last) < 1e30))
     if world > 1:

@@ -72,12 +72,12 @@ struct BwdSmem {
   static constexpr int DO_OFF = Q_OFF + QSTAGES * 2 * Q_CHUNK;
   static constexpr int DST_OFF = DO_OFF + QSTAGES * 2 * Q_CHUNK;  // dS^T [128 kv][64 q] bf16
   static constexpr int DQ_OFF = DST_OFF + KV_CHUNK;           // dQ staging: 8 warps x [32 q][32 d] fp32 (row-major, 4 KB each)
-  static constexpr int META_OFF = DQ_OFF + 8 * 4096;          // per buffer: lse2[64] f32, delta*scale[64] f32, qpos[64] i32, qbits[64] i64
+  static constexpr int META_OFF = DQ_OFF + 8 * 4096;          // three buffers of: lse2[64] f32, delta*scale[64] f32, qpos[64] i32, qbits[64] i64
   static constexpr int META_STAGE = 64 * 4 * 3 + 64 * 8;
-  static constexpr int LIST_OFF = META_OFF + 2 * META_STAGE;  // valid 64-row query tiles of this key block: int16 index, int8 class
+  static constexpr int LIST_OFF = META_OFF + 3 * META_STAGE;  // valid 64-row query tiles of this key block: int16 index, int8 class
   static constexpr int MAX_TILES = 1024;                      // sequences up to 65536 tokens
   static constexpr int BAR_OFF = LIST_OFF + MAX_TILES * 4;
-  static constexpr int NBAR = 1 + QSTAGES + QSTAGES + 1 + 1 + 1 + 1 + 1 + 1 + 1;
+  static constexpr int NBAR = 1 + QSTAGES + QSTAGES + 1 + 1 + 1 + 1 + 1 + 1;
   static constexpr int TOTAL = BAR_OFF + NBAR * 8 + 32;
   static constexpr int DYN_BYTES = TOTAL + 1024;
 };
@@ -167,8 +167,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* pds_empty = pds_full + 1;     //       ... and consumed by the MMAs
   uint64_t* dq_full = pds_empty + 1;      //       dQ^T ready in TMEM
   uint64_t* dq_free = dq_full + 1;        //       dQ^T drained (256 arrivals)
-  uint64_t* meta_full = dq_free + 1;      //       per-iteration query metadata staged (256 arrivals)
-  uint64_t* dp_read = meta_full + 1;      //       S^T and dP^T of an iteration are in registers (256 arrivals): dP^T may be overwritten
+  uint64_t* dp_read = dq_free + 1;      //       S^T and dP^T of an iteration are in registers (256 arrivals): dP^T may be overwritten
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBAR);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* n_valid_slot = reinterpret_cast<int*>(tmem_slot + 2);
@@ -200,7 +199,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(pds_empty, 1);
     mbar_init(dq_full, 1);
     mbar_init(dq_free, CFG::COMPUTE_THREADS);
-    mbar_init(meta_full, CFG::COMPUTE_THREADS);
     mbar_init(dp_read, CFG::COMPUTE_THREADS);
     *abort_flag = 0;
     mbar_fence_init();
@@ -423,28 +421,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       return true;
     };
 
+    // Query metadata of iteration it lives in buffer it % 3.  The stagers write the metadata of iteration it + 1 right
+    // after they hold S^T / dP^T of iteration it in registers and BEFORE they arrive on dp_read(it); the MMA warp issues
+    // dP^T(it + 1) only after dp_read(it) is complete, so sdp_full(it + 1) also tells every thread that the metadata is
+    // staged.  Three buffers: whoever stages it + 1 has seen sdp_full(it), i.e. every thread is past its loads of it - 1
+    // and therefore done with the metadata of it - 2, the previous tenant of that buffer.
+    auto stage_meta = [&](int it) {
+      if (!stager || it >= n_iter) return;
+      float* m = reinterpret_cast<float*>(smem + L::META_OFF + (it % 3) * L::META_STAGE);
+      m[r] = pf_lse;
+      m[64 + r] = pf_delta;
+      reinterpret_cast<int*>(m + 128)[r] = pf_qpos;
+      reinterpret_cast<int64_t*>(m + 192)[r] = pf_qbits;
+    };
     prefetch_meta(0);
+    stage_meta(0);
+    prefetch_meta(1);
+    // the metadata of iteration 0 is ordered by a barrier of its own (named barrier 1 over the compute threads)
+    asm volatile("bar.sync 1, %0;" ::"n"(CFG::COMPUTE_THREADS) : "memory");
     for (int it = 0; it < n_iter && ok; ++it) {
       const int c = tile_cls[it % n_valid];
-      const int mb = it & 1;
-      float* m_lse = reinterpret_cast<float*>(smem + L::META_OFF + mb * L::META_STAGE);
+      float* m_lse = reinterpret_cast<float*>(smem + L::META_OFF + (it % 3) * L::META_STAGE);
       float* m_delta = m_lse + 64;
       int* m_qpos = reinterpret_cast<int*>(m_delta + 64);
       int64_t* m_qbits = reinterpret_cast<int64_t*>(m_qpos + 64);
-      if (stager) {
-        m_lse[r] = pf_lse;
-        m_delta[r] = pf_delta;
-        m_qpos[r] = pf_qpos;
-        m_qbits[r] = pf_qbits;
-      }
-      mbar_arrive(meta_full);
-      prefetch_meta(it + 1);  // global loads for the next tile fly while this one is processed
-      if (!bw_wait(meta_full, it & 1, abort_flag)) {
-        if (lane == 0) atomicCAS(p.status, 0, ST_TIMEOUT_MISC);
-        *abort_flag = 1;
-        ok = false;
-        break;
-      }
       if (!bw_wait(sdp_full, it & 1, abort_flag)) {
         if (lane == 0) atomicCAS(p.status, 0, ST_TIMEOUT_TMEM_FULL);
         *abort_flag = 1;
@@ -456,6 +456,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_ld_cols<COLS>(tmem_base + (it & 1) * 64 + col0 + lane_addr, sv);
       tmem_ld_cols<COLS>(tmem_dPT + col0 + lane_addr, dv);
       tmem_ld_wait();
+      stage_meta(it + 1);
+      prefetch_meta(it + 2);  // global loads for the tile after next fly while this one is processed
       tc_fence_before();
       mbar_arrive(dp_read);
       float pv[COLS], ds[COLS];
