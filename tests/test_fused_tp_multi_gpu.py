@@ -94,6 +94,11 @@ def _tp_model_worker(rank, world, port, q):
         nat.check_status()
         l0, g0 = results[False]
         l1, g1 = results[True]
+        # Two bf16 computations are compared with each other here, not with an fp32 oracle (the kernel-level test above does
+        # that): the fused path rounds every rank's partial tile to bf16 before the sum, NCCL sums in another order, and the
+        # difference passes through two decoder layers, a 2048-way softmax and the backward pass.  The loss bound is two bf16
+        # units at its magnitude (7.6); a direction (cosine) bound on each gradient tensor is what survives such noise
+        # on tensors whose largest element is 1e-3.
         assert abs(l0 - l1) < 2e-2, (l0, l1)
         for n in g0:
             d = (g0[n] - g1[n]).abs().max().item()
