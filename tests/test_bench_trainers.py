@@ -69,6 +69,11 @@ def _pipeline_worker(rank, world):
     if tr.is_last:
         assert torch.isfinite(l1) and torch.isfinite(l2)
     assert tr.global_batch == world
+    # what bench.py asks of a trainer after the timed steps: replicated parameters agree inside the tensor-parallel pair
+    assert "stage" in tr.role and "tp rank" in tr.role
+    c = tr.checks()
+    assert c["tp_replicated"]["ranks"] == 2 and c["tp_replicated"]["params"] > 0
+    assert c["tp_replicated"]["mismatched"] == 0, c
 
 
 def test_pipeline_trainer_with_recompute_tuning():
