@@ -116,14 +116,16 @@ def test_embed_merge_fwd_bwd():
     close(feats.grad, ff.grad)
 
 
+@pytest.mark.parametrize("keep", [False, True])
 @pytest.mark.parametrize("V", [1000, 128256])
-def test_linear_cross_entropy(V):
+def test_linear_cross_entropy(V, keep):
+    """``keep``: the logits stay resident for the backward pass (what small problems do by default) or are recomputed."""
     T, H = 700, 256
     h = torch.randn(T, H, device="cuda").bfloat16().requires_grad_(True)
     w = (0.05 * torch.randn(V, H, device="cuda")).bfloat16().requires_grad_(True)
     labels = torch.randint(0, V, (T,), device="cuda")
     labels[::7] = -100
-    loss = linear_cross_entropy(h, w, labels, chunk=256)
+    loss = linear_cross_entropy(h, w, labels, chunk=256, keep_logits=keep)
     hf, wf = h.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
     ref = F.cross_entropy(F.linear(hf, wf), labels, ignore_index=-100)
     assert abs(loss.item() - ref.item()) < 2e-2 * max(1.0, abs(ref.item()))
