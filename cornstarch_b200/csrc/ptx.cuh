@@ -80,15 +80,6 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 }
 
 __device__ __forceinline__ uint32_t cluster_ctarank();
-__device__ __forceinline__ uint32_t elect_one() {
-  uint32_t pred = 0;
-  asm volatile(
-      "{\n\t.reg .pred P;\n\t"
-      "elect.sync _|P, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, P;\n\t}"
-      : "=r"(pred));
-  return pred;
-}
 
 // ----------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -142,22 +133,6 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
 }
 // 2-D tiled load, completion on an mbarrier of this CTA.  x is the innermost coordinate and
 // must keep x * elem_size a multiple of 16 bytes.
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m, uint64_t* bar,
-                                            int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m, uint64_t* bar,
-                                            int x, int y, int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar,
                                             int x, int y, int z, int w) {
   asm volatile(
@@ -263,25 +238,6 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-// A operand from TMEM (used for P*V with P kept in tensor memory).
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_f16_2cta(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                              uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 // Make the mbarrier track completion of all tcgen05 ops this thread issued so far.
 // Whole-warp forms: every lane of a CONVERGED warp executes the call with the same arguments and one elected lane (always
 // the same one) issues the instruction.  Warp-uniform control flow lets the compiler keep descriptors and addresses in the
@@ -325,6 +281,10 @@ __device__ __forceinline__ void umma_commit_w(uint64_t* bar) {
       "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar))
       : "memory");
 }
+// CG == 2: the MMAs were issued for a CTA pair; the barrier at this shared-memory offset is signalled in BOTH thread
+// blocks of the pair by ONE commit whose arrival is multicast to the two blocks (cta mask 0b11).  This is a barrier
+// signal between the two SMs of the pair - no data is copied and no load is involved.  (Two separate commits, one per
+// block, cost 12 % of the MMA rate in a measurement without loads: 1.69 against 1.90 PFLOP/s.)
 template <int CG>
 __device__ __forceinline__ void umma_commit_cg_w(uint64_t* bar) {
   if constexpr (CG == 2) {
@@ -341,20 +301,6 @@ __device__ __forceinline__ void umma_commit_cg_w(uint64_t* bar) {
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
-}
-// CG == 2: the MMAs were issued for a CTA pair; the barrier at this shared-memory offset is signalled in BOTH thread
-// blocks of the pair by ONE commit whose arrival is multicast to the two blocks (cta mask 0b11).  This is a barrier
-// signal between the two SMs of the pair - no data is copied and no load is involved.  (Two separate commits, one per
-// block, cost 12 % of the MMA rate in a measurement without loads: 1.69 against 1.90 PFLOP/s.)
-template <int CG>
-__device__ __forceinline__ void umma_commit_cg(uint64_t* bar) {
-  if constexpr (CG == 2) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 ::"r"(smem_u32(bar)), "h"(static_cast<uint16_t>(3))
-                 : "memory");
-  } else {
-    umma_commit(bar);
-  }
 }
 
 // TMEM -> registers, 32 lanes x 32 consecutive fp32 columns; thread i of the warp gets lane
