@@ -148,7 +148,8 @@ class PipelineP2PCommunication:
             same = _same_layout(self._sent.get(key), meta)
             if self.assume_static and key in self._sent:
                 if not same:
-                    raise RuntimeError(f"p2p edge {key}: message layout changed although shapes were declared static")
+                    raise RuntimeError(f"p2p edge {key}: message layout changed although shapes were declared static "
+                                       "(build the schedule with assume_static_shapes=False for batches of varying shape)")
                 prepared.append((dst, None, None, tensors))
                 continue
             payload = None

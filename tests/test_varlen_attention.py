@@ -43,7 +43,8 @@ def _case(device, dtype, limit, causal, tol):
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("limit", [60, 2], ids=["one_masked_sequence", "padded_batch"])
 def test_varlen_matches_per_sequence_attention(limit, causal):
-    _case("cpu", torch.float32, limit, causal, 1e-5)
+    # fp32 on the CPU: the packed and the per-sequence products sum in different orders (1e-5 failed once on a many-core host)
+    _case("cpu", torch.float32, limit, causal, 1e-4)
 
 
 @pytest.mark.gpu
