@@ -230,6 +230,47 @@ class ContextParallelTrainer(SingleDeviceTrainer):
         super().reduce_grads()
 
 
+class TensorParallelTrainer(SingleDeviceTrainer):
+    """One replica over all ranks: the language model is tensor parallel over the group (replicated activations, or
+    token-sharded ones with ``CORNSTARCH_B200_TP_SEQ_SHARD=1``), the small encoder and the projector are replicated and
+    see the same data on every rank.  Used to measure the two tensor-parallel layouts inside a whole training step
+    (``bench.py --parallelism tp``)."""
+
+    def __init__(self, shape, samples_per_step, microbatch, device, group, **kw):
+        self.group = group
+        super().__init__(shape, samples_per_step, microbatch, device, dp_group=None, **kw)
+        self.world = dist.get_world_size(group)
+        self.global_batch = samples_per_step  # all ranks work on the same samples
+        self.tokens_per_step = self.global_batch * self.seq_len
+        import os
+
+        sharded = os.environ.get("CORNSTARCH_B200_TP_SEQ_SHARD", "0") == "1"
+        self.parallelism = f"tp{self.world} ({'token-sharded' if sharded else 'replicated'} activations), encoder replicated"
+
+    def data_rank(self) -> int:
+        return 0  # same data on every rank
+
+    def make_optimizer(self, lr):
+        from .ops import _native as nat
+        from .shardformer.shard.shard_config import ShardConfig
+        from .shardformer.shard.shardformer import ShardFormer
+
+        sc = ShardConfig(tensor_parallel_process_group=self.group, enable_tensor_parallelism=True, extra_kwargs={"device": self.device})
+        ShardFormer(sc).optimize(self.model.language_model)
+        if nat.LIBRARY_MODE:
+            return _TorchAdamW(self.model, lr)
+        return FusedAdamW(split_decay_groups(self.model, 0.01), lr=lr, max_norm=1.0, norm_groups=[self.group])
+
+    def reduce_grads(self):
+        return  # no data parallelism: replicated parts see identical data, sharded parts are reduced inside the layers
+
+    def checks(self) -> dict:
+        from .plugin.checkpoint_io import _tp_info
+
+        return replica_checks(list(self.model.named_parameters()), tp_group=self.group,
+                              tp_sharded={"language_model." + n for n in _tp_info(self.model.language_model)})
+
+
 def _model_name(shape: str) -> str:
     return {
         "vlm": "SigLIP-so400m-shape (27L,h1152) + MLP projector + Llama-3.1-8B-shape (32L,h4096,vocab 128256)",
@@ -248,6 +289,8 @@ def build_trainer(args, rank: int, world: int, local_rank: int):
         return ExpertParallelTrainer(args.shape, args.samples_per_gpu, args.microbatch, device, dist.group.WORLD)
     if plan == "cp" or (plan == "auto" and SHAPES[args.shape].images_per_sample > 1):
         return ContextParallelTrainer(args.shape, args.samples_per_gpu, args.microbatch, device, dist.group.WORLD)
+    if plan == "tp":
+        return TensorParallelTrainer(args.shape, args.samples_per_gpu, args.microbatch, device, dist.group.WORLD)
     if plan == "auto" and world in (2, 4):
         plan = "dp"
     if plan == "dp":

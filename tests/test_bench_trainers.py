@@ -1,6 +1,7 @@
 """The benchmark's expert-parallel and context-parallel trainers on CPU-sized shapes: loss of the first step equals
 the single-process model on the same data, and a step updates the weights."""
 
+import pytest
 import torch
 import torch.distributed as dist
 
@@ -78,3 +79,29 @@ def _pipeline_worker(rank, world):
 
 def test_pipeline_trainer_with_recompute_tuning():
     run_distributed(_pipeline_worker, 4)
+
+
+def _tp_worker(rank, world, seq_shard):
+    """The benchmark's tensor-parallel trainer (language model over both ranks, encoder replicated) in both activation
+    layouts: two steps, finite loss, replicated parameters still equal on both ranks."""
+    import os
+
+    os.environ["CORNSTARCH_B200_TP_SEQ_SHARD"] = "1" if seq_shard else "0"
+    from cornstarch_b200.bench_support import TensorParallelTrainer
+
+    tr = TensorParallelTrainer("tiny", 2, 1, torch.device("cpu"), dist.group.WORLD, dtype=torch.float32)
+    l1 = tr.step_device()
+    l2 = tr.step_device()
+    assert torch.isfinite(l1) and torch.isfinite(l2)
+    assert ("token-sharded" in tr.parallelism) == seq_shard
+    c = tr.checks()
+    assert c["tp_replicated"]["params"] > 0 and c["tp_replicated"]["mismatched"] == 0, c
+    # both layouts compute the same function: the loss of the first step is the single-process loss
+    everyone = [None, None]
+    dist.all_gather_object(everyone, float(l1))
+    assert abs(everyone[0] - everyone[1]) < 1e-5
+
+
+@pytest.mark.parametrize("seq_shard", [False, True])
+def test_tensor_parallel_trainer(seq_shard):
+    run_distributed(_tp_worker, 2, seq_shard)
