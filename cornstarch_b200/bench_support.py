@@ -232,8 +232,8 @@ class ContextParallelTrainer(SingleDeviceTrainer):
 
 class TensorParallelTrainer(SingleDeviceTrainer):
     """One replica over all ranks: the language model is tensor parallel over the group (replicated activations, or
-    token-sharded ones with ``CORNSTARCH_B200_TP_SEQ_SHARD=1``), the small encoder and the projector are replicated and
-    see the same data on every rank.  Used to measure the two tensor-parallel layouts inside a whole training step
+    token-sharded ones with ``CORNSTARCH_B200_TP_SEQ_SHARD=1``) and so are the encoder and its projector; every rank
+    sees the same data.  Used to measure the two tensor-parallel layouts inside a whole training step
     (``bench.py --parallelism tp``)."""
 
     def __init__(self, shape, samples_per_step, microbatch, device, group, **kw):
@@ -245,7 +245,7 @@ class TensorParallelTrainer(SingleDeviceTrainer):
         import os
 
         sharded = os.environ.get("CORNSTARCH_B200_TP_SEQ_SHARD", "0") == "1"
-        self.parallelism = f"tp{self.world} ({'token-sharded' if sharded else 'replicated'} activations), encoder replicated"
+        self.parallelism = f"tp{self.world} ({'token-sharded' if sharded else 'replicated'} activations)"
 
     def data_rank(self) -> int:
         return 0  # same data on every rank
@@ -257,6 +257,10 @@ class TensorParallelTrainer(SingleDeviceTrainer):
 
         sc = ShardConfig(tensor_parallel_process_group=self.group, enable_tensor_parallelism=True, extra_kwargs={"device": self.device})
         ShardFormer(sc).optimize(self.model.language_model)
+        # the encoders (with their projectors) are tensor parallel as well: replicas that compute the same gradients
+        # independently would drift apart in the last bit (dQ of the attention backward is summed in no fixed order)
+        for key in self.model.encoders_keys:
+            ShardFormer(sc).optimize(getattr(self.model, f"{key}_encoder"))
         if nat.LIBRARY_MODE:
             return _TorchAdamW(self.model, lr)
         return FusedAdamW(split_decay_groups(self.model, 0.01), lr=lr, max_norm=1.0, norm_groups=[self.group])
@@ -267,8 +271,7 @@ class TensorParallelTrainer(SingleDeviceTrainer):
     def checks(self) -> dict:
         from .plugin.checkpoint_io import _tp_info
 
-        return replica_checks(list(self.model.named_parameters()), tp_group=self.group,
-                              tp_sharded={"language_model." + n for n in _tp_info(self.model.language_model)})
+        return replica_checks(list(self.model.named_parameters()), tp_group=self.group, tp_sharded=set(_tp_info(self.model)))
 
 
 def _model_name(shape: str) -> str:
