@@ -236,7 +236,10 @@ class VocabParallelEmbedding(Embedding):
             return super().forward(ids, feats, src)
         assert src is None, "modality merge happens after the vocab-parallel reduce"
         inside = (ids >= self.vocab_start) & (ids < self.vocab_end)
-        local = (ids - self.vocab_start).clamp(0, self.num_embeddings - 1)
+        # Tokens of other ranks' shards look up SOME local row and are zeroed below.  They are spread over the rows
+        # (modulo) instead of clamped onto the first / last one: thousands of tokens on one row made the embedding's
+        # backward pass (a segmented sum per row) take about 10 ms per 8192-token micro-batch on the first pipeline stage.
+        local = torch.remainder(ids - self.vocab_start, self.num_embeddings)
         out = F.embedding(local, self.weight)
         out = out * inside.unsqueeze(-1).to(out.dtype)
         return comm.reduce_forward(out, self.process_group)
