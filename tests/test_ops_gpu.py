@@ -116,6 +116,29 @@ def test_embed_merge_fwd_bwd():
     close(feats.grad, ff.grad)
 
 
+def test_merge_features_into_given_embeddings():
+    """The merge kernel with already embedded tokens as its table (what a vocabulary-parallel model does after its
+    embedding all-reduce): row t keeps ``flat[t]`` or takes a feature row; both inputs get their gradients."""
+    from cornstarch_b200.ops.elementwise import embed_merge
+
+    T, H, NF = 1000, 256, 37
+    flat = torch.randn(T, H, device="cuda").bfloat16().requires_grad_(True)
+    feats = torch.randn(NF, H, device="cuda").bfloat16().requires_grad_(True)
+    src = torch.arange(T, device="cuda", dtype=torch.int32)
+    where = torch.randperm(T, device="cuda")[:NF].sort().values
+    src[where] = -(torch.arange(NF, device="cuda", dtype=torch.int32)) - 1
+    out = embed_merge(flat, src, feats)
+    ff, fe = flat.detach().float().requires_grad_(True), feats.detach().float().requires_grad_(True)
+    ref = ff.clone()
+    ref[where] = fe
+    close(out, ref)
+    g = torch.randn_like(out)
+    out.backward(g)
+    ref.backward(g.float())
+    close(flat.grad, ff.grad)
+    close(feats.grad, fe.grad)
+
+
 @pytest.mark.parametrize("keep", [False, True])
 @pytest.mark.parametrize("V", [1000, 128256])
 def test_linear_cross_entropy(V, keep):
