@@ -371,7 +371,7 @@ class MultimodalModel(nn.Module):
                     merged = E.embed_merge(flat.contiguous(), torch.where(src < 0, src, own_row), allf.to(flat.dtype)).view(B, S, -1)
                 else:
                     is_f = (src < 0)[:, None]
-                    merged = torch.where(is_f, allf.to(flat.dtype)[(-src.long() - 1).clamp(min=0)], flat).view(B, S, -1)
+                    merged = torch.where(is_f, allf.to(flat.dtype)[torch.remainder(-src.long() - 1, allf.shape[0])], flat).view(B, S, -1)
         else:
             merged = inputs_embeds if inputs_embeds is not None else emb(input_ids)
         bits = self.create_bitfield_attention_mask(input_ids, attention_mask)

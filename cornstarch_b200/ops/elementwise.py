@@ -345,5 +345,7 @@ def embed_merge(weight: torch.Tensor, src: torch.Tensor, feats: torch.Tensor | N
     if feats is None:
         return emb
     is_feat = s < 0
-    picked = feats[(-s - 1).clamp(min=0)]
+    # rows that keep their embedding still gather SOME feature row; spread them over the rows (a clamp would put them all
+    # on row 0 and make the gather's backward pass a sum of thousands of zero rows into one)
+    picked = feats[torch.remainder(-s - 1, feats.shape[0])]
     return torch.where(is_feat[:, None], picked.to(emb.dtype), emb)
