@@ -349,7 +349,8 @@ def main():
                 if "what" in v:
                     agg["what"] = v["what"]
         checks["ok"] = all(v["mismatched"] == 0 for v in checks.values() if isinstance(v, dict))
-        checks["last_loss_finite"] = bool(last is None or (last == last and abs(last) < 1e30))
+        # (without the end-to-end steps no loss is read back)
+        checks["last_loss_finite"] = None if args.no_e2e else bool(last is not None and last == last and abs(last) < 1e30)
     if world > 1:
         # report the clocks of the busiest GPU (pipeline stages differ a lot in load), with every rank's throttle reasons
         everyone = [None] * world
