@@ -184,7 +184,7 @@ def parse_args():
     ap.add_argument("--shape", default="vlm", help="named shape from cornstarch_b200.zoo (default: the headline VLM)")
     ap.add_argument("--samples-per-gpu", type=int, default=SAMPLES_PER_GPU)
     ap.add_argument("--microbatch", type=int, default=1)
-    ap.add_argument("--parallelism", default="auto", help="auto | dp | e.g. 'pp4xtp2'")
+    ap.add_argument("--parallelism", default="auto", help="auto | dp | tp | cp | ep | enc<E>+llm<L>xtp<T> (e.g. enc1+llm3xtp2)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-baseline", action="store_true", help="native arm: skip the library-baseline child run (vs_baseline stays null)")
     ap.add_argument("--baseline-steps", type=int, default=5)
