@@ -41,6 +41,8 @@ def timeline(on: bool = True) -> None:
 
 def timeline_totals() -> dict[str, tuple[int, float]]:
     """``{range name: (count, total device milliseconds)}`` of the ranges recorded since ``timeline(True)``; synchronises."""
+    if not _events:
+        return {}
     torch.cuda.synchronize()
     out = {name: (len(pairs), sum(a.elapsed_time(b) for a, b in pairs)) for name, pairs in _events.items()}
     _events.clear()

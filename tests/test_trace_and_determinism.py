@@ -22,6 +22,30 @@ def test_nvtx_ranges_wrap_optimizer_step():
     assert names == ["optimizer/fused_adamw_step"]
 
 
+def test_timeline_is_inert_without_a_gpu():
+    """``timeline(True)`` records CUDA events around the ranges; without CUDA it stays off and the ranges do nothing."""
+    if torch.cuda.is_available():
+        pytest.skip("covers the CPU behaviour")
+    trace.timeline(True)
+    with trace.nvtx_range("pipeline/forward_microbatch"):
+        pass
+    assert trace.timeline_totals() == {}
+    trace.timeline(False)
+
+
+@pytest.mark.gpu
+def test_timeline_sums_device_time_per_range():
+    trace.timeline(True)
+    x = torch.randn(4096, 4096, device="cuda")
+    for _ in range(3):
+        with trace.nvtx_range("work"):
+            x = x @ x.t() * 1e-4
+    totals = trace.timeline_totals()
+    trace.timeline(False)
+    assert totals["work"][0] == 3 and totals["work"][1] > 0
+    assert trace.timeline_totals() == {}
+
+
 def _poisoned_allocations():
     """Fill the caching allocator's free blocks with NaN bit patterns so that ``torch.empty`` outputs start poisoned."""
     junk = [torch.full((n,), float("nan"), device="cuda", dtype=torch.float32) for n in (1 << 24, 1 << 22, 1 << 20, 1 << 18)]
