@@ -176,11 +176,17 @@ class ExpertParallelTrainer(SingleDeviceTrainer):
         self.group = group
         super().__init__(shape, samples_per_step, microbatch, device, dp_group=group, **kw)
         self.parallelism = f"dp{self.world} + ep{self.world} (expert all-to-all) + ZeRO-1"
+        if self.ep_capacity:
+            self.parallelism += f", capacity factor {self.ep_capacity} (static shapes, no host synchronisation)"
 
     def make_optimizer(self, lr):
         from .parallel.ep import shard_experts
 
-        shard_experts(self.model.language_model, self.group)
+        import os
+
+        cap = os.environ.get("CORNSTARCH_B200_EP_CAPACITY")  # e.g. 1.25: static-shape dispatch without host reads
+        self.ep_capacity = float(cap) if cap else None
+        shard_experts(self.model.language_model, self.group, capacity_factor=self.ep_capacity)
         if torch.cuda.is_available():
             torch.cuda.empty_cache()
         return FusedAdamW(split_decay_groups(self.model, 0.01), lr=lr, max_norm=1.0, zero_stage=1, dp_group=self.group,

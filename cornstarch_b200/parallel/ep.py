@@ -17,6 +17,13 @@ Data movement per MoE layer::
 
 Both all-to-alls are autograd functions whose backward is the reverse exchange.  On NCCL they are
 ``all_to_all_single`` with split sizes; on gloo (CPU tests) they are emulated with a padded all-gather.
+
+Capacity mode (``ExpertParallel(..., capacity_factor=f)`` / ``shard_experts(..., capacity_factor=f)``) is the same layer
+with STATIC shapes: every rank sends exactly ``C = ceil(f * tokens * k / num_experts)`` rows per expert (unused slots are
+zero rows, pairs beyond an expert's capacity are dropped and counted in ``dropped_pairs``), so both exchanges are
+all-to-alls with equal splits and nothing is read back to the host: no count exchange, no synchronisation, every tensor
+shape fixed from step to step.  The price is the padding (``f - 1`` of the expert GEMM rows at balanced load) and, like the
+capacity factor of GShard / Switch layers, dropped pairs when one expert receives more than ``f`` times its share.
 """
 
 from __future__ import annotations
@@ -69,7 +76,9 @@ FUSED_EP_ENABLED = True  # exchange tokens with this package's peer-memory kerne
 class ExpertParallel:
     """Attached to a sparse MoE block as ``block.ep``; the block then holds only this rank's experts."""
 
-    def __init__(self, group, num_experts: int):
+    def __init__(self, group, num_experts: int, capacity_factor: float | None = None):
+        self.capacity_factor = capacity_factor
+        self.dropped_pairs = None  # capacity mode: device scalar, pairs dropped in the last call (read it when convenient)
         self.group = group
         self.ws = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -96,6 +105,8 @@ class ExpertParallel:
     def forward(self, x2: torch.Tensor, weights: torch.Tensor, experts_idx: torch.Tensor, experts, act: str) -> torch.Tensor:
         T, H = x2.shape
         k = experts_idx.shape[1]
+        if self.capacity_factor is not None:
+            return self._forward_capacity(x2, weights, experts_idx, experts, act)
         flat_e = experts_idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         token_of = torch.div(order, k, rounding_mode="floor")
@@ -141,6 +152,68 @@ class ExpertParallel:
         out = torch.zeros_like(x2)
         out.index_add_(0, token_of, back)
         return out
+
+
+def _a2a_equal(x: torch.Tensor, group) -> torch.Tensor:
+    """All-to-all with equal splits: ``x`` is ``[world, n, ...]``, slice ``d`` goes to rank ``d``."""
+    if dist.get_backend(group) != "gloo":
+        out = torch.empty_like(x)
+        dist.all_to_all_single(out, x.contiguous(), group=group)
+        return out
+    ws, rank = dist.get_world_size(group), dist.get_rank(group)
+    everyone = [torch.empty_like(x) for _ in range(ws)]
+    dist.all_gather(everyone, x.contiguous(), group=group)
+    return torch.stack([e[rank] for e in everyone], dim=0)
+
+
+class _AllToAllEqual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _a2a_equal(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _a2a_equal(g.contiguous(), ctx.group), None
+
+
+def _capacity_methods():
+    def _forward_capacity(self, x2, weights, experts_idx, experts, act):
+        """Static-shape dispatch / combine (see the module docstring): no host reads, equal-split all-to-alls."""
+        import math
+
+        T, H = x2.shape
+        k = experts_idx.shape[1]
+        E, ws, L = self.num_experts, self.ws, self.local
+        C = max(1, math.ceil(self.capacity_factor * T * k / E))
+        flat_e = experts_idx.reshape(-1)
+        order = torch.argsort(flat_e, stable=True)
+        sorted_e = flat_e[order]
+        token_of = torch.div(order, k, rounding_mode="floor")
+        counts = torch.bincount(flat_e, minlength=E)
+        starts = torch.cumsum(counts, 0) - counts
+        pos = torch.arange(T * k, device=x2.device) - starts[sorted_e]  # rank of a pair among its expert's pairs
+        keep = pos < C
+        self.dropped_pairs = (~keep).sum()
+        dump = E * C  # one extra row that collects every dropped pair
+        slot = torch.where(keep, sorted_e * C + pos, torch.full_like(pos, dump))
+        send = x2.new_zeros((E * C + 1, H)).index_copy(0, slot, x2[token_of])[:dump]
+        recv = _AllToAllEqual.apply(send.view(ws, L * C, H), self.group)  # [src, (local expert, slot), H]
+        self.last_recv_tokens = ws * L * C
+        per_expert = recv.view(ws, L, C, H).transpose(0, 1).reshape(L, ws * C, H)
+        outs = [experts[e](per_expert[e], act) for e in range(L)]  # zero rows stay zero through a bias-free gated MLP
+        y = torch.stack(outs, dim=0).view(L, ws, C, H).transpose(0, 1).reshape(ws, L * C, H)
+        back = _AllToAllEqual.apply(y, self.group).reshape(dump, H)
+        back = torch.cat([back, back.new_zeros((1, H))], dim=0)[slot]  # dropped pairs read the zero row
+        back = back * weights.reshape(-1)[order].unsqueeze(-1).to(back.dtype)
+        out = torch.zeros_like(x2)
+        out.index_add_(0, token_of, back)
+        return out
+
+    ExpertParallel._forward_capacity = _forward_capacity
+
+
+_capacity_methods()
 
 
 def _replayed_counts():
@@ -228,7 +301,7 @@ def _ep_fused_methods():
 _ep_fused_methods()
 
 
-def shard_experts(model, group) -> list[torch.nn.Parameter]:
+def shard_experts(model, group, capacity_factor: float | None = None) -> list[torch.nn.Parameter]:
     """Keep only this rank's experts in every sparse MoE block of ``model`` and attach the exchange.
 
     Returns the expert parameters (they are NOT replicated over the group: no data-parallel reduction, and an
@@ -240,7 +313,7 @@ def shard_experts(model, group) -> list[torch.nn.Parameter]:
         if hasattr(m, "experts") and hasattr(m, "ep") and isinstance(m.experts, nn.ModuleList):
             if m.ep is not None:
                 continue
-            ep = ExpertParallel(group, len(m.experts))
+            ep = ExpertParallel(group, len(m.experts), capacity_factor)
             m.experts = nn.ModuleList([m.experts[i] for i in ep.local_expert_ids()])
             m.ep = ep
             expert_params += list(m.experts.parameters())

@@ -50,6 +50,58 @@ def test_ep4_four_experts():
     run_distributed(_worker, 4, 4)
 
 
+def _capacity_worker(rank, world, factor):
+    """Static-shape (capacity) dispatch: with room for every pair it equals the local MoE block exactly, in outputs and in
+    every gradient; with too little room the surplus pairs are dropped, counted, and contribute nothing."""
+    from cornstarch_b200.models.moe import MixtralConfig, MixtralSparseMoeBlock
+    from cornstarch_b200.parallel.ep import shard_experts
+
+    cfg = MixtralConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=4,
+                        num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2)
+    torch.manual_seed(0)
+    full = MixtralSparseMoeBlock(cfg)
+    torch.manual_seed(0)
+    sharded = MixtralSparseMoeBlock(cfg)
+    shard_experts(sharded, dist.group.WORLD, capacity_factor=factor)
+    g = torch.Generator().manual_seed(10 + rank)
+    x = torch.randn(2, 12, 32, generator=g)  # equal token counts on every rank: the shapes of the exchange are static
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya, _ = full(xa)
+    yb, _ = sharded(xb)
+    dropped = int(sharded.ep.dropped_pairs)
+    if factor >= 4.0:  # capacity = every pair of the rank: nothing can be dropped
+        assert dropped == 0
+        assert torch.allclose(ya, yb, atol=1e-5), (ya - yb).abs().max()
+        ya.square().sum().backward()
+        yb.square().sum().backward()
+        assert torch.allclose(xa.grad, xb.grad, atol=1e-5)
+        assert torch.allclose(full.gate.weight.grad, sharded.gate.weight.grad, atol=1e-5)
+        per = 4 // world
+        zero = torch.zeros_like(full.experts[0].w1.weight)
+        mine = torch.stack([e.w1.weight.grad if e.w1.weight.grad is not None else zero for e in full.experts])
+        everyone = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        total = sum(everyone)
+        for j in range(per):
+            assert torch.allclose(sharded.experts[j].w1.weight.grad, total[rank * per + j], atol=1e-4)
+    else:
+        assert dropped > 0
+        assert torch.isfinite(yb).all()
+        yb.square().sum().backward()
+        assert torch.isfinite(xb.grad).all()
+        # a token whose pairs were all kept is computed exactly
+        same = (ya - yb).abs().amax(dim=-1) < 1e-5
+        assert same.any() and not same.all()
+
+
+def test_ep2_capacity_mode_is_exact_with_room_for_every_pair():
+    run_distributed(_capacity_worker, 2, 4.0)
+
+
+def test_ep2_capacity_mode_drops_and_counts_the_surplus():
+    run_distributed(_capacity_worker, 2, 0.5)
+
+
 def _ckpt_worker(rank, world):
     from cornstarch_b200.models.moe import MixtralConfig, MoeForCausalLM
     from cornstarch_b200.parallel.ep import gather_full_state_dict, shard_experts
