@@ -1,5 +1,6 @@
 """Expert parallelism: dispatch / combine all-to-all with experts sharded over ranks equals the local MoE block."""
 
+import pytest
 import torch
 import torch.distributed as dist
 
@@ -100,6 +101,37 @@ def test_ep2_capacity_mode_is_exact_with_room_for_every_pair():
 
 def test_ep2_capacity_mode_drops_and_counts_the_surplus():
     run_distributed(_capacity_worker, 2, 0.5)
+
+
+def _capacity_gpu_worker(rank, world):
+    from cornstarch_b200.models.moe import MixtralConfig, MixtralSparseMoeBlock
+    from cornstarch_b200.parallel.ep import shard_experts
+
+    cfg = MixtralConfig(vocab_size=64, hidden_size=256, intermediate_size=512, num_hidden_layers=1, num_attention_heads=4,
+                        num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2)
+    torch.manual_seed(0)
+    full = MixtralSparseMoeBlock(cfg).cuda().bfloat16()
+    torch.manual_seed(0)
+    sharded = MixtralSparseMoeBlock(cfg).cuda().bfloat16()
+    shard_experts(sharded, dist.group.WORLD, capacity_factor=4.0)  # room for every pair: nothing dropped
+    x = torch.randn(2, 384, 256, generator=torch.Generator().manual_seed(3)).cuda().bfloat16()
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya, _ = full(xa)
+    yb, _ = sharded(xb)
+    ya.float().square().sum().backward()
+    yb.float().square().sum().backward()
+    assert int(sharded.ep.dropped_pairs) == 0
+    for name, a, b in (("y", yb, ya), ("dx", xb.grad, xa.grad), ("dgate", sharded.gate.weight.grad, full.gate.weight.grad),
+                       ("dw1", sharded.experts[1].w1.weight.grad, full.experts[1].w1.weight.grad)):
+        err = (a.float() - b.float()).abs().max().item()
+        assert err <= 2e-2 * max(1.0, b.float().abs().max().item()), (name, err)
+
+
+@pytest.mark.gpu
+def test_capacity_mode_on_the_device_equals_the_local_block():
+    from tests.dist_utils import run_gpu_ranks
+
+    run_gpu_ranks(_capacity_gpu_worker, 1)
 
 
 def _ckpt_worker(rank, world):
