@@ -190,7 +190,8 @@ def _capacity_methods():
         order = torch.argsort(flat_e, stable=True)
         sorted_e = flat_e[order]
         token_of = torch.div(order, k, rounding_mode="floor")
-        counts = torch.bincount(flat_e, minlength=E)
+        # not torch.bincount: on a device it reads the largest value on the host to size its result
+        counts = torch.zeros(E, dtype=torch.long, device=x2.device).scatter_add_(0, flat_e, torch.ones_like(flat_e))
         starts = torch.cumsum(counts, 0) - counts
         pos = torch.arange(T * k, device=x2.device) - starts[sorted_e]  # rank of a pair among its expert's pairs
         keep = pos < C

@@ -14,6 +14,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 
 import torch
 import torch.distributed as dist
@@ -233,9 +234,72 @@ def moe_exchange(args):
     nat.check_status()
 
 
+def moe_layer(args):
+    """One Mixtral-8x7B-shape MoE block (hidden 4096, intermediate 14336, 8 experts, top 2), experts sharded over the
+    ranks, forward + backward on ``--seq`` tokens per rank: exact dispatch (per-expert counts read on the host; NCCL
+    all-to-all, and the peer-memory push kernel when there is more than one rank) against capacity mode (static shapes,
+    no host read) at two capacity factors.  Device time between two events around the iterations, so launch gaps
+    behind a host read are part of it; works on a single GPU too (all exchanges are local then)."""
+    import time
+    import warnings
+
+    from ..models.moe import MixtralConfig, MixtralSparseMoeBlock
+    from ..parallel import ep as EP
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    cfg = MixtralConfig(vocab_size=64, hidden_size=4096, intermediate_size=14336, num_hidden_layers=1, num_attention_heads=32,
+                        num_key_value_heads=8, num_local_experts=8, num_experts_per_tok=2)
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        block = MixtralSparseMoeBlock(cfg).bfloat16()
+    EP.shard_experts(block, dist.group.WORLD)
+    x = torch.randn(1, args.seq, 4096, device="cuda", generator=torch.Generator("cuda").manual_seed(rank)).bfloat16()
+    gy = torch.randn_like(x)
+
+    def step():
+        xi = x.detach().requires_grad_()
+        y, _ = block(xi)
+        y.backward(gy)
+
+    arms = [("exact, NCCL all-to-all", False, None)]
+    if world > 1:
+        arms.append(("exact, peer-memory push", True, None))
+    arms += [("capacity 1.25", False, 1.25), ("capacity 2.0", False, 2.0)]
+    rows = []
+    for name, fused, cap in arms:
+        EP.FUSED_EP_ENABLED = fused
+        block.ep.capacity_factor = cap
+        ms = timeit(step, iters=10, warmup=3)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(10):
+            step()
+        host_ms = (time.perf_counter() - t0) * 100  # time the host needs to ENQUEUE one step (it blocks at host reads)
+        torch.cuda.synchronize()
+        dropped = int(block.ep.dropped_pairs) if cap is not None else 0
+        with warnings.catch_warnings(record=True) as seen:  # PyTorch reports every call that makes the host wait
+            warnings.simplefilter("always")
+            torch.cuda.set_sync_debug_mode("warn")
+            step()
+            torch.cuda.set_sync_debug_mode("default")
+        torch.cuda.synchronize()
+        if rank == 0 and cap is not None:
+            for w in seen[:4]:
+                print(f"[{name}] host wait: {w.filename}:{w.lineno}", file=sys.stderr, flush=True)
+        rows.append({"arm": name, "device_ms": round(ms, 3), "host_enqueue_ms": round(host_ms, 3),
+                     "host_waits_per_step": len(seen),
+                     "rows_into_local_experts": int(block.ep.last_recv_tokens), "dropped_pairs": dropped})
+    if rank == 0:
+        print(json.dumps({"op": "MoE block forward + backward", "world": world, "tokens_per_rank": args.seq,
+                          "pairs_per_rank": args.seq * 2, "arms": rows}), flush=True)
+    from ..ops import _native as nat
+
+    nat.check_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm_allreduce", "sp_linear", "cp_attention", "grad_reduce", "moe_exchange"])
+    ap.add_argument("what", choices=["gemm_allreduce", "sp_linear", "cp_attention", "grad_reduce", "moe_exchange", "moe_layer"])
     ap.add_argument("--seq", type=int, default=8192, help="cp_attention: tokens per rank; moe_exchange: rows per rank")
     ap.add_argument("--mb", type=int, default=1024, help="grad_reduce: buffer size in MiB")
     ap.add_argument("--reducers", type=int, nargs="+", default=[16])
@@ -243,9 +307,12 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if "RANK" not in os.environ:  # plain ``python -m``: a group of one on this GPU
+        os.environ.update(RANK="0", WORLD_SIZE="1")
+        os.environ.setdefault("MASTER_PORT", "29541")
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     {"gemm_allreduce": gemm_allreduce, "sp_linear": sp_linear, "cp_attention": cp_attention, "grad_reduce": grad_reduce,
-     "moe_exchange": moe_exchange}[args.what](args)
+     "moe_exchange": moe_exchange, "moe_layer": moe_layer}[args.what](args)
     dist.barrier()
     dist.destroy_process_group()
 
