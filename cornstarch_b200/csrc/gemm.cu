@@ -71,6 +71,10 @@ struct GemmParams {
   int ag_ready_value;
   int* ag_pulled;           // local int[world]: every pulling block adds 1 per finished range
   int ag_pull_target;       // ag_pulled[r] reaches this once range r is complete for this call
+  // ---- grouped form (group_rows > 0): rows [g * group_rows, (g + 1) * group_rows) of A and C belong to group g and are
+  // multiplied with that group's own B (the local experts of a MoE layer in ONE launch).  group_rows is a multiple of
+  // the tile height, so a tile never straddles two groups; the B tensor maps travel in EpiMaps (see group_b_map).
+  int group_rows;
 };
 
 constexpr int AR_MAX_ROWS = 512;
@@ -250,6 +254,13 @@ struct EpiMaps {
   CUtensorMap inbox[8];
   CUtensorMap fin[8];
 };
+
+// The grouped form never runs together with the fused all-reduce, so its per-group B maps use the sixteen slots of the
+// all-reduce maps: the kernel's parameter block keeps its size.
+constexpr int MAX_GROUPS = 16;
+__host__ __device__ __forceinline__ const CUtensorMap* group_b_map(const EpiMaps& m, int g) {
+  return g < 8 ? &m.inbox[g] : &m.fin[g - 8];
+}
 
 // Epilogue of one tile through shared memory: every thread owns one accumulator row; 128-byte row pieces
 // (64 bf16 or 32 fp32 columns) are staged in a swizzled slab and written with ONE TMA store per slab and
@@ -475,6 +486,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         const int n_row0 = n_blk * BN + cta_rank * BNH;
         const CUtensorMap* map_a = &tma_a;
         int a_row0 = m_blk * BM;
+        const CUtensorMap* map_b = p.group_rows > 0 ? group_b_map(epi_maps, a_row0 / p.group_rows) : &tma_b;
         if (n_pull > 0) {
           const int o = ar_owner(m_blk, p.num_m_blocks, p.ag_world);
           if (o == p.ag_rank) {
@@ -517,9 +529,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if constexpr (B_MN) {
 #pragma unroll
             for (int j = 0; j < BNH / 64; ++j)
-              tma_load_2d_to<CG>(sb + j * (64 * BK * 2), &tma_b, full_addr_s, n_row0 + j * 64, kb * BK);
+              tma_load_2d_to<CG>(sb + j * (64 * BK * 2), map_b, full_addr_s, n_row0 + j * 64, kb * BK);
           } else {
-            tma_load_2d_to<CG>(sb, &tma_b, full_addr_s, kb * BK, n_row0);
+            tma_load_2d_to<CG>(sb, map_b, full_addr_s, kb * BK, n_row0);
           }
         }
       }
@@ -797,7 +809,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 
 template <int BN, bool A_MN, bool B_MN, int CG = 1>
 static int launch_gemm(const void* A, const void* B, const GemmParams& p, int lda, int ldb, int max_ctas,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const void* const* group_b = nullptr, int groups = 0) {
   CUtensorMap ta, tb;
   int r;
   if (A_MN)
@@ -832,6 +844,21 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p, int ld
   const int cps = 128 / eb;
   q.tma_epi = ((reinterpret_cast<uintptr_t>(q.C) & 15) == 0 && ((size_t)q.ldc * eb) % 16 == 0) ? 1 : 0;
   if (q.ar_world > 1 && !q.tma_epi) return CSB_ERR_BAD_ARG;
+  if (q.group_rows > 0) {
+    // grouped form: one B per group, same shape and row pitch (B above is group 0's and only serves the prefetch)
+    if (A_MN || q.ar_world > 1 || q.ag_world > 1 || groups < 1 || groups > MAX_GROUPS || group_b == nullptr ||
+        q.group_rows % (BM * CG) != 0 || (long)groups * q.group_rows != q.M)
+      return CSB_ERR_BAD_ARG;
+    for (int g = 0; g < groups; ++g) {
+      CUtensorMap* dst = const_cast<CUtensorMap*>(group_b_map(em, g));
+      if (reinterpret_cast<uintptr_t>(group_b[g]) & 15) return CSB_ERR_BAD_ARG;
+      if (B_MN)
+        r = make_tmap_2d_bf16(dst, group_b[g], q.K, q.N, ldb, 64, BK);
+      else
+        r = make_tmap_2d_bf16(dst, group_b[g], q.N, q.K, ldb, BK, BN / CG);
+      if (r) return r;
+    }
+  }
   if (q.ag_world > 1) {
     if (A_MN) return CSB_ERR_BAD_ARG;
     const int own0 = ar_range_start(q.ag_rank, q.num_m_blocks, q.ag_world) * BM;
@@ -886,6 +913,7 @@ static int gemm_cg_choice() {
 // both blocks of a pair then work for the same owner.
 static bool pairs_fit_ranges(int num_m_blocks, int world) { return num_m_blocks % (2 * world) == 0; }
 static void no_collective(GemmParams& p) {
+  p.group_rows = 0;
   p.ar_scatter = 0; p.ar_row_offset = 0;
   p.ag_world = 1; p.ag_rank = 0; p.ag_pull_ctas = 0;
   for (int i = 0; i < 8; ++i) p.ag_src[i] = nullptr;
@@ -943,6 +971,59 @@ CSB_API int csb_gemm_bf16(const void* A, const void* B, void* C, const void* bia
   if (bn == 256) { CSB_DISPATCH(256) }
   CSB_DISPATCH(128)
 #undef CSB_DISPATCH
+}
+
+
+// Grouped GEMM: `groups` problems of the same shape in ONE launch.  A is [groups * group_rows][K] (K-major) and C is
+// [groups * group_rows][N]; rows [g * group_rows, (g + 1) * group_rows) use B_ptrs[g] (a HOST array of `groups` device
+// pointers): [N][K] (b_mn_major = 0) or [K][N] (b_mn_major = 1), all with row pitch ldb.
+//   C[g] (+)= A[g] * op(B[g])^T
+// group_rows must be a multiple of 256 (the height of a tile of a pair of thread blocks); groups <= 16.  This is the
+// expert MLP of a MoE layer whose experts all receive the same number of rows (capacity dispatch): the forward GEMMs
+// (b_mn_major = 0) and the input-gradient GEMMs (b_mn_major = 1) of all local experts.
+CSB_API int csb_gemm_grouped_bf16(const void* A, const void* const* B_ptrs, void* C, int groups, int group_rows, int N, int K,
+                                  int lda, int ldb, int ldc, int b_mn_major, int out_fp32, int accumulate, int tile_n,
+                                  int* status, void* stream) {
+  using namespace csb;
+  if (groups < 1 || groups > MAX_GROUPS || group_rows <= 0 || group_rows % 256 || N <= 0 || K <= 0 || (lda & 7) || (ldb & 7) ||
+      B_ptrs == nullptr)
+    return CSB_ERR_BAD_ARG;
+  if (reinterpret_cast<uintptr_t>(A) & 15) return CSB_ERR_BAD_ARG;
+  const int M = groups * group_rows;
+  int bn = tile_n;
+  if (bn != 128 && bn != 256) {
+    long t256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256);
+    bn = (N >= 256 && t256 >= sm_count()) ? 256 : 128;
+  }
+  GemmParams p;
+  p.C = C;
+  p.bias = nullptr;
+  p.M = M; p.N = N; p.K = K;
+  p.ldc = ldc;
+  p.out_fp32 = out_fp32;
+  p.accumulate = accumulate;
+  p.act = 0;
+  p.num_m_blocks = (M + BM - 1) / BM;
+  p.num_n_blocks = (N + bn - 1) / bn;
+  p.num_k_blocks = (K + BK - 1) / BK;
+  p.status = status;
+  p.tma_epi = 0;
+  p.ar_world = 1; p.ar_rank = 0; p.ar_base = 0; p.ar_slot_elems = 0;
+  for (int i = 0; i < 8; ++i) { p.ar_inbox[i] = nullptr; p.ar_final[i] = nullptr; p.ar_cnt_part[i] = nullptr; p.ar_cnt_final[i] = nullptr; }
+  no_collective(p);
+  p.group_rows = group_rows;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const void* B0 = B_ptrs[0];
+  if (bn == 256 && gemm_cg_choice() == 2) {
+    if (b_mn_major) return launch_gemm<256, false, true, 2>(A, B0, p, lda, ldb, 0, s, B_ptrs, groups);
+    return launch_gemm<256, false, false, 2>(A, B0, p, lda, ldb, 0, s, B_ptrs, groups);
+  }
+  if (bn == 256) {
+    if (b_mn_major) return launch_gemm<256, false, true>(A, B0, p, lda, ldb, 0, s, B_ptrs, groups);
+    return launch_gemm<256, false, false>(A, B0, p, lda, ldb, 0, s, B_ptrs, groups);
+  }
+  if (b_mn_major) return launch_gemm<128, false, true>(A, B0, p, lda, ldb, 0, s, B_ptrs, groups);
+  return launch_gemm<128, false, false>(A, B0, p, lda, ldb, 0, s, B_ptrs, groups);
 }
 
 

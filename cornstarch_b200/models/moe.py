@@ -71,6 +71,22 @@ class _SwiGLUExpert(nn.Module):
         return d(E.glu(gu, act))
 
 
+def experts_forward_grouped(experts, x3: torch.Tensor, act: str) -> torch.Tensor:
+    """``experts[e](x3[e])`` for every local expert, ``x3`` being ``[experts, rows, hidden]`` with the same number of rows
+    for each: the gate / up projections of all experts run as one grouped GEMM, the GLU once over all rows, the down
+    projections as one grouped GEMM (``ops.linear.grouped_multi_linear``).  Experts whose linears are wrapped or
+    tensor-parallel run one after the other."""
+    L, R, H = x3.shape
+    if L == 1 or not all(type(getattr(e, n)) is cnn.Linear for e in experts for n in e.names):
+        return torch.stack([experts[e](x3[e], act) for e in range(L)], dim=0)
+    from ..ops.linear import grouped_multi_linear
+
+    gate_up = [[getattr(e, e.names[0]).weight, getattr(e, e.names[1]).weight] for e in experts]
+    down = [[getattr(e, e.names[2]).weight] for e in experts]
+    gu = grouped_multi_linear(x3.reshape(L * R, H), gate_up, R)
+    return grouped_multi_linear(E.glu(gu, act), down, R).view(L, R, H)
+
+
 def route_topk(router_logits: torch.Tensor, top_k: int, renormalize: bool = True):
     """softmax over experts -> top-k -> (optionally) renormalise.  Returns ``(weights [T,k], experts [T,k])``."""
     probs = F.softmax(router_logits.float(), dim=-1)

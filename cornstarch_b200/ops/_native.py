@@ -24,6 +24,7 @@ vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_long, C.c_float
 
 _PROTOS = {
     "csb_gemm_bf16": [vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
+    "csb_gemm_grouped_bf16": [vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "csb_norm_bwd_parts": [i32],
     "csb_norm_fwd": [i32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, f32, vp],
     "csb_norm_bwd": [i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, f32, vp],

@@ -125,6 +125,52 @@ def gemm(
     return out
 
 
+GROUP_ROW_MULTIPLE = 256  # rows per group of the native grouped GEMM: whole tiles of a pair of thread blocks
+MAX_GROUPS = 16
+
+
+def grouped_gemm_supported(a: torch.Tensor, bs, group_rows: int) -> bool:
+    """Whether ``grouped_gemm`` runs these operands as ONE native launch."""
+    b0 = bs[0]
+    return (a.is_cuda and not nat.LIBRARY_MODE and a.dtype == torch.bfloat16 and a.dim() == 2 and a.stride(1) == 1
+            and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and 1 <= len(bs) <= MAX_GROUPS
+            and group_rows > 0 and group_rows % GROUP_ROW_MULTIPLE == 0 and a.shape[0] == len(bs) * group_rows
+            and all(b.dtype == torch.bfloat16 and b.dim() == 2 and b.shape == b0.shape and b.stride() == b0.stride()
+                    and b.stride(1) == 1 and b.stride(0) % 8 == 0 and b.data_ptr() % 16 == 0 for b in bs))
+
+
+def grouped_gemm(a: torch.Tensor, bs, group_rows: int, b_mn_major: bool = False, out: torch.Tensor | None = None,
+                 accumulate: bool = False) -> torch.Tensor:
+    """``out[g] (+)= a[g] @ op(bs[g]).T`` for every group ``g``: rows ``[g * group_rows, (g + 1) * group_rows)`` of ``a`` and
+    ``out`` belong to group ``g``, ``bs[g]`` is ``[N, K]`` (``b_mn_major=False``) or ``[K, N]`` (``True``).  One launch of
+    the GEMM kernel for all groups when ``grouped_gemm_supported``; one GEMM per group otherwise.  This is the expert MLP
+    of a MoE layer whose experts all receive the same number of rows (Mixtral's experts in the reference run one after
+    another, cornstarch/shardformer/modeling/mixtral.py:419-430)."""
+    G = len(bs)
+    assert a.dim() == 2 and a.shape[0] == G * group_rows, (a.shape, G, group_rows)
+    N = bs[0].shape[1] if b_mn_major else bs[0].shape[0]
+    K = bs[0].shape[0] if b_mn_major else bs[0].shape[1]
+    assert a.shape[1] == K, f"contraction mismatch {a.shape[1]} vs {K}"
+    if out is None:
+        out = torch.empty((a.shape[0], N), dtype=a.dtype, device=a.device)
+        accumulate = False
+    if not grouped_gemm_supported(a, bs, group_rows) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+        for g in range(G):
+            rows = slice(g * group_rows, (g + 1) * group_rows)
+            gemm(a[rows], bs[g], b_mn_major=b_mn_major, out=out[rows], accumulate=accumulate)
+        return out
+    import ctypes
+
+    ptrs = (ctypes.c_void_p * G)(*[b.data_ptr() for b in bs])
+    st = nat.status_word(a.device)
+    code = nat.lib().csb_gemm_grouped_bf16(
+        a.data_ptr(), ctypes.cast(ptrs, ctypes.c_void_p), out.data_ptr(), G, group_rows, N, K, a.stride(0), bs[0].stride(0),
+        out.stride(0), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate), 0, st.data_ptr(), nat.stream(),
+    )
+    nat.check(code, "csb_gemm_grouped_bf16")
+    return out
+
+
 def _pad_rows(t: torch.Tensor) -> torch.Tensor:
     """Copy a 2-D tensor into storage whose row stride is a multiple of 8 elements (16 bytes)."""
     r, c = t.shape

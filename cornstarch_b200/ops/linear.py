@@ -207,6 +207,77 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
     return multi_linear(x, [weight], [bias], tp)
 
 
+# ------------------------------------------------------------------------------------------------ grouped (per-expert) linears
+class _GroupedLinearFn(torch.autograd.Function):
+    """``y[g] = x[g] [W_g0 | W_g1 | ...]^T`` for every group ``g`` of ``group_rows`` rows: the forward GEMMs of all groups are
+    one launch and so are the input-gradient GEMMs (``ops.gemm.grouped_gemm``); the weight gradients are one GEMM per
+    group, accumulated into ``main_grad`` where the weight has one."""
+
+    @staticmethod
+    def forward(ctx, x2, group_rows, n_w, *weights):
+        G = len(weights) // n_w
+        groups = [weights[g * n_w : (g + 1) * n_w] for g in range(G)]
+        from .gemm import grouped_gemm
+
+        widths = [w.shape[0] for w in groups[0]]
+        out = torch.empty((x2.shape[0], sum(widths)), dtype=x2.dtype, device=x2.device)
+        fused = [fuse_adjacent(ws) if n_w > 1 else ws[0] for ws in groups]
+        if all(f is not None for f in fused):
+            grouped_gemm(x2, fused, group_rows, out=out)
+        else:
+            o = 0
+            for j, n in enumerate(widths):
+                grouped_gemm(x2, [ws[j] for ws in groups], group_rows, out=out[:, o : o + n])
+                o += n
+        ctx.save_for_backward(x2, *weights)
+        ctx.group_rows, ctx.n_w, ctx.widths = group_rows, n_w, widths
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        from .gemm import grouped_gemm
+
+        x2, *weights = ctx.saved_tensors
+        R, n_w, widths = ctx.group_rows, ctx.n_w, ctx.widths
+        G = len(weights) // n_w
+        groups = [weights[g * n_w : (g + 1) * n_w] for g in range(G)]
+        dy2 = _as_2d(dy)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            fused = [fuse_adjacent(ws) if n_w > 1 else ws[0] for ws in groups]
+            if all(f is not None for f in fused):
+                dx = grouped_gemm(dy2, fused, R, b_mn_major=True)
+            else:
+                dx = torch.empty_like(x2)
+                o = 0
+                for j, n in enumerate(widths):
+                    grouped_gemm(dy2[:, o : o + n], [ws[j] for ws in groups], R, b_mn_major=True, out=dx, accumulate=j > 0)
+                    o += n
+        dws: list = []
+        for g, ws in enumerate(groups):
+            rows = slice(g * R, (g + 1) * R)
+            need = [ctx.needs_input_grad[3 + g * n_w + j] for j in range(n_w)]
+            dws += _weight_grads(dy2[rows], x2[rows], ws, need)
+        return (dx, None, None, *dws)
+
+
+def grouped_multi_linear(x2: torch.Tensor, weight_groups: Sequence[Sequence[torch.Tensor]], group_rows: int) -> torch.Tensor:
+    """Bias-free projections of a row-grouped input: rows ``[g * group_rows, (g + 1) * group_rows)`` of ``x2`` are
+    multiplied with the weights of group ``g`` (``weight_groups[g]``, e.g. ``[w1, w3]`` of expert ``g``; every group has
+    the same shapes), outputs concatenated along the last dimension as ``multi_linear`` does."""
+    G = len(weight_groups)
+    assert x2.dim() == 2 and x2.shape[0] == G * group_rows
+    n_w = len(weight_groups[0])
+    if not _use_native(x2):
+        outs = []
+        for g, ws in enumerate(weight_groups):
+            seg = x2[g * group_rows : (g + 1) * group_rows]
+            outs.append(torch.cat([F.linear(seg, w) for w in ws], dim=-1) if n_w > 1 else F.linear(seg, ws[0]))
+        return torch.cat(outs, dim=0)
+    flat = [w for ws in weight_groups for w in ws]
+    return _GroupedLinearFn.apply(_as_2d(x2), group_rows, n_w, *flat)
+
+
 # ------------------------------------------------------------------------------------------------ sequence-sharded TP
 # Activations between the tensor-parallel blocks are sharded by token rows (rank r holds a contiguous range of whole
 # 128-row tiles): norms, residual adds and everything token-wise run on 1/tp of the tokens.  A column-parallel

@@ -186,6 +186,10 @@ def _capacity_methods():
         k = experts_idx.shape[1]
         E, ws, L = self.num_experts, self.ws, self.local
         C = max(1, math.ceil(self.capacity_factor * T * k / E))
+        if x2.is_cuda:
+            # every expert then holds a multiple of 256 rows: whole tiles of the grouped GEMM that runs all local experts
+            step = 256 // math.gcd(256, ws)
+            C = (C + step - 1) // step * step
         flat_e = experts_idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         sorted_e = flat_e[order]
@@ -202,8 +206,10 @@ def _capacity_methods():
         recv = _AllToAllEqual.apply(send.view(ws, L * C, H), self.group)  # [src, (local expert, slot), H]
         self.last_recv_tokens = ws * L * C
         per_expert = recv.view(ws, L, C, H).transpose(0, 1).reshape(L, ws * C, H)
-        outs = [experts[e](per_expert[e], act) for e in range(L)]  # zero rows stay zero through a bias-free gated MLP
-        y = torch.stack(outs, dim=0).view(L, ws, C, H).transpose(0, 1).reshape(ws, L * C, H)
+        from ..models.moe import experts_forward_grouped
+
+        y = experts_forward_grouped(experts, per_expert, act)  # zero rows stay zero through a bias-free gated MLP
+        y = y.view(L, ws, C, H).transpose(0, 1).reshape(ws, L * C, H)
         back = _AllToAllEqual.apply(y, self.group).reshape(dump, H)
         back = torch.cat([back, back.new_zeros((1, H))], dim=0)[slot]  # dropped pairs read the zero row
         back = back * weights.reshape(-1)[order].unsqueeze(-1).to(back.dtype)
