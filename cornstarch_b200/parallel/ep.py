@@ -154,30 +154,6 @@ class ExpertParallel:
         return out
 
 
-def _a2a_equal(x: torch.Tensor, group) -> torch.Tensor:
-    """All-to-all with equal splits: ``x`` is ``[world, n, ...]``, slice ``d`` goes to rank ``d``."""
-    if dist.get_backend(group) != "gloo":
-        out = torch.empty_like(x)
-        dist.all_to_all_single(out, x.contiguous(), group=group)
-        return out
-    ws, rank = dist.get_world_size(group), dist.get_rank(group)
-    everyone = [torch.empty_like(x) for _ in range(ws)]
-    dist.all_gather(everyone, x.contiguous(), group=group)
-    return torch.stack([e[rank] for e in everyone], dim=0)
-
-
-class _AllToAllEqual(torch.autograd.Function):
-    @staticmethod
-    def forward(ctx, x, group):
-        ctx.group = group
-        return _a2a_equal(x, group)
-
-    @staticmethod
-    def backward(ctx, g):
-        return _a2a_equal(g.contiguous(), ctx.group), None
-
-
-def _capacity_methods():
     def _forward_capacity(self, x2, weights, experts_idx, experts, act):
         """Static-shape dispatch / combine (see the module docstring): no host reads, equal-split all-to-alls."""
         import math
@@ -217,34 +193,6 @@ def _capacity_methods():
         out.index_add_(0, token_of, back)
         return out
 
-    ExpertParallel._forward_capacity = _forward_capacity
-
-
-_capacity_methods()
-
-
-def _replayed_counts():
-    """Inside the recomputation of a layer the routing is the one of the first forward pass: the token counts that pass
-    exchanged (a collective plus a host read) are taken from the recomputation tape instead of being exchanged again."""
-    from ..ops.attention import _TAPE
-
-    tape = getattr(_TAPE, "cur", None)
-    if tape is None or tape.mode != "replay":
-        return None
-    tag, value = tape.items.pop(0)
-    assert tag == "ep_counts", "recomputation tape out of order"
-    return value
-
-
-def _record_counts(value) -> None:
-    from ..ops.attention import _TAPE
-
-    tape = getattr(_TAPE, "cur", None)
-    if tape is not None and tape.mode == "record":
-        tape.items.append(("ep_counts", value))
-
-
-def _ep_fused_methods():
     def _fused(self, x2):
         from ..ops import _native as nat
 
@@ -301,11 +249,49 @@ def _ep_fused_methods():
         out.index_add_(0, token_of, back)
         return out
 
-    ExpertParallel._fused = _fused
-    ExpertParallel._forward_fused = _forward_fused
+
+def _a2a_equal(x: torch.Tensor, group) -> torch.Tensor:
+    """All-to-all with equal splits: ``x`` is ``[world, n, ...]``, slice ``d`` goes to rank ``d``."""
+    if dist.get_backend(group) != "gloo":
+        out = torch.empty_like(x)
+        dist.all_to_all_single(out, x.contiguous(), group=group)
+        return out
+    ws, rank = dist.get_world_size(group), dist.get_rank(group)
+    everyone = [torch.empty_like(x) for _ in range(ws)]
+    dist.all_gather(everyone, x.contiguous(), group=group)
+    return torch.stack([e[rank] for e in everyone], dim=0)
 
 
-_ep_fused_methods()
+class _AllToAllEqual(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _a2a_equal(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _a2a_equal(g.contiguous(), ctx.group), None
+
+
+def _replayed_counts():
+    """Inside the recomputation of a layer the routing is the one of the first forward pass: the token counts that pass
+    exchanged (a collective plus a host read) are taken from the recomputation tape instead of being exchanged again."""
+    from ..ops.attention import _TAPE
+
+    tape = getattr(_TAPE, "cur", None)
+    if tape is None or tape.mode != "replay":
+        return None
+    tag, value = tape.items.pop(0)
+    assert tag == "ep_counts", "recomputation tape out of order"
+    return value
+
+
+def _record_counts(value) -> None:
+    from ..ops.attention import _TAPE
+
+    tape = getattr(_TAPE, "cur", None)
+    if tape is not None and tape.mode == "record":
+        tape.items.append(("ep_counts", value))
 
 
 def shard_experts(model, group, capacity_factor: float | None = None) -> list[torch.nn.Parameter]:
