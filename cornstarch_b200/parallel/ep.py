@@ -153,7 +153,6 @@ class ExpertParallel:
         out.index_add_(0, token_of, back)
         return out
 
-
     def _forward_capacity(self, x2, weights, experts_idx, experts, act):
         """Static-shape dispatch / combine (see the module docstring): no host reads, equal-split all-to-alls."""
         import math
