@@ -70,6 +70,21 @@ def all_to_all_uneven(x, send_splits: list[int], recv_splits: list[int], group):
     return _AllToAllUneven.apply(x, send_splits, recv_splits, group)
 
 
+def expert_counts(flat_e: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Pairs per expert.  Not ``torch.bincount``: on a device that reads the smallest and largest value on the host."""
+    return torch.zeros(num_experts, dtype=torch.long, device=flat_e.device).scatter_add_(0, flat_e, torch.ones_like(flat_e))
+
+
+def by_expert_order(recv_counts: torch.Tensor, total: int) -> torch.Tensor:
+    """Permutation that takes received rows from (source rank, local expert) order to (local expert, source rank) order.
+    ``recv_counts[src, local]`` stays on its device; ``total`` (their sum, known on the host) sizes the result, so nothing
+    is read back and nothing is copied in."""
+    ws, local = recv_counts.shape
+    expert_of_segment = torch.arange(local, device=recv_counts.device).repeat(ws)
+    keys = torch.repeat_interleave(expert_of_segment, recv_counts.reshape(-1), output_size=total)
+    return torch.argsort(keys, stable=True)
+
+
 FUSED_EP_ENABLED = True  # exchange tokens with this package's peer-memory kernel instead of NCCL all_to_all
 
 
@@ -110,30 +125,24 @@ class ExpertParallel:
         flat_e = experts_idx.reshape(-1)
         order = torch.argsort(flat_e, stable=True)
         token_of = torch.div(order, k, rounding_mode="floor")
-        counts = torch.bincount(flat_e, minlength=self.num_experts)
+        counts = expert_counts(flat_e, self.num_experts)
         fused = self._fused(x2)
         if fused is not None:
             return self._forward_fused(fused, x2, weights, order, token_of, counts, experts, act)
-        both = _replayed_counts()
-        if both is None:
+        rec = _replayed_counts()
+        if rec is None:
             recv_counts = self.exchange_counts(counts)
-            # one host read for both directions' split sizes
-            both = torch.cat([counts.view(self.ws, self.local).sum(1), recv_counts.reshape(-1)]).tolist()
-            _record_counts(both)
+            # one host read for both directions' split sizes: the only point of this path where the host waits
+            rec = (torch.cat([counts.view(self.ws, self.local).sum(1), recv_counts.reshape(-1)]).tolist(), recv_counts)
+            _record_counts(rec)
+        both, recv_counts = rec
         send_splits = both[: self.ws]
         rc = [both[self.ws + s * self.local : self.ws + (s + 1) * self.local] for s in range(self.ws)]
         recv_splits = [sum(r) for r in rc]
         rows = all_to_all_uneven(x2[token_of], send_splits, recv_splits, self.group)  # grouped by (src, local expert)
         self.last_recv_tokens = rows.shape[0]
         if self.local > 1:
-            # permutation to (local expert, src) order
-            starts, pos = [], 0
-            for s in range(self.ws):
-                for e in range(self.local):
-                    starts.append(pos)
-                    pos += rc[s][e]
-            perm = torch.cat([torch.arange(starts[s * self.local + e], starts[s * self.local + e] + rc[s][e])
-                              for e in range(self.local) for s in range(self.ws)]).to(rows.device)
+            perm = by_expert_order(recv_counts, rows.shape[0])
             rows = rows[perm]
         outs, start = [], 0
         for e in range(self.local):
@@ -169,8 +178,7 @@ class ExpertParallel:
         order = torch.argsort(flat_e, stable=True)
         sorted_e = flat_e[order]
         token_of = torch.div(order, k, rounding_mode="floor")
-        # not torch.bincount: on a device it reads the largest value on the host to size its result
-        counts = torch.zeros(E, dtype=torch.long, device=x2.device).scatter_add_(0, flat_e, torch.ones_like(flat_e))
+        counts = expert_counts(flat_e, E)
         starts = torch.cumsum(counts, 0) - counts
         pos = torch.arange(T * k, device=x2.device) - starts[sorted_e]  # rank of a pair among its expert's pairs
         keep = pos < C
@@ -207,12 +215,14 @@ class ExpertParallel:
 
         T, H = x2.shape
         k = order.numel() // T
-        mat = _replayed_counts()
-        if mat is None:
+        rec = _replayed_counts()
+        if rec is None:
             everyone = [torch.empty_like(counts) for _ in range(self.ws)]
             dist.all_gather(everyone, counts, group=self.group)  # counts[src][expert]: placement of every rank's rows
-            mat = torch.stack(everyone).view(self.ws, self.ws, self.local).tolist()  # [src][dst][local expert]
-            _record_counts(mat)
+            stacked = torch.stack(everyone).view(self.ws, self.ws, self.local)  # [src][dst][local expert]
+            rec = (stacked.tolist(), stacked[:, self.rank].contiguous())
+            _record_counts(rec)
+        mat, recv_counts = rec
         send = [[sum(mat[s][d]) for d in range(self.ws)] for s in range(self.ws)]
         # every rank may receive at most all (token, k) pairs of the group; sized once from the first call's total
         total_pairs = sum(sum(r) for r in send)
@@ -223,13 +233,7 @@ class ExpertParallel:
         self.last_recv_tokens = rows.shape[0]
         perm = None
         if self.local > 1:
-            starts, pos = [], 0
-            for s in range(self.ws):
-                for e in range(self.local):
-                    starts.append(pos)
-                    pos += rc[s][e]
-            perm = torch.cat([torch.arange(starts[s * self.local + e], starts[s * self.local + e] + rc[s][e])
-                              for e in range(self.local) for s in range(self.ws)]).to(rows.device)
+            perm = by_expert_order(recv_counts, rows.shape[0])
             rows = rows[perm]
         outs, start = [], 0
         for e in range(self.local):

@@ -51,6 +51,24 @@ def test_ep4_four_experts():
     run_distributed(_worker, 4, 4)
 
 
+def test_regroup_permutation_and_counts_without_host_values():
+    """The device-side helpers of the dispatch: pairs per expert, and the permutation from (source, local expert) to
+    (local expert, source) order, against their plain statements (segments of length zero included)."""
+    from cornstarch_b200.parallel.ep import by_expert_order, expert_counts
+
+    flat_e = torch.tensor([3, 0, 3, 1, 0, 3])
+    assert expert_counts(flat_e, 5).tolist() == [2, 1, 0, 3, 0]
+    rc = [[2, 0, 1], [0, 3, 1], [1, 1, 0]]  # [source][local expert]
+    ws, local = 3, 3
+    starts, pos = [], 0
+    for s in range(ws):
+        for e in range(local):
+            starts.append(pos)
+            pos += rc[s][e]
+    want = [i for e in range(local) for s in range(ws) for i in range(starts[s * local + e], starts[s * local + e] + rc[s][e])]
+    assert by_expert_order(torch.tensor(rc), pos).tolist() == want
+
+
 def _capacity_worker(rank, world, factor):
     """Static-shape (capacity) dispatch: with room for every pair it equals the local MoE block exactly, in outputs and in
     every gradient; with too little room the surplus pairs are dropped, counted, and contribute nothing."""
