@@ -354,8 +354,15 @@ class FusedAdamW(torch.optim.Optimizer):
         scale = inv_scale
         if self.max_norm > 0 or self.loss_scale != 1.0:
             sq = torch.zeros((), dtype=torch.float32, device=params[0].device if params else "cpu")
+            sq_expert = torch.zeros_like(sq)
             for p in params:
-                sq = sq + p.grad.float().pow(2).sum()
+                if getattr(p, "expert_parallel", False):
+                    sq_expert = sq_expert + p.grad.float().pow(2).sum()
+                else:
+                    sq = sq + p.grad.float().pow(2).sum()
+            if self.expert_group is not None and dist.get_world_size(self.expert_group) > 1:
+                dist.all_reduce(sq_expert, group=self.expert_group)  # every rank owns different experts
+            sq = sq + sq_expert
             for grp in self.norm_groups:
                 if grp is not None and dist.get_world_size(grp) > 1:
                     dist.all_reduce(sq, group=grp)

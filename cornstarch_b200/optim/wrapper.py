@@ -44,6 +44,7 @@ class OptimizerWrapper:
         self.model = model
         self.max_norm = max_norm
         self.tp_group, self.pp_group = tp_group, pp_group
+        self.expert_group = None  # set when experts are sharded over a group: their share of the norm is summed over it
         self.scaler = DynamicLossScaler(**(scaler_kwargs or {})) if precision == "fp16" else None
         if isinstance(optim, FusedAdamW):
             optim.max_norm = max_norm
@@ -72,9 +73,16 @@ class OptimizerWrapper:
         if not params:
             return None
         sq = torch.zeros((), dtype=torch.float32, device=params[0].device)
+        sq_expert = torch.zeros_like(sq)
         for p in params:
             # parameters replicated inside a tp group are counted once per rank; divide their share
-            sq = sq + p.grad.float().pow(2).sum()
+            if getattr(p, "expert_parallel", False):
+                sq_expert = sq_expert + p.grad.float().pow(2).sum()
+            else:
+                sq = sq + p.grad.float().pow(2).sum()
+        if self.expert_group is not None and dist.get_world_size(self.expert_group) > 1:
+            dist.all_reduce(sq_expert, group=self.expert_group)  # every rank owns different experts
+        sq = sq + sq_expert
         for grp in (self.tp_group, self.pp_group):
             if grp is not None and dist.get_world_size(grp) > 1:
                 dist.all_reduce(sq, group=grp)

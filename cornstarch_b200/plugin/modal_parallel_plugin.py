@@ -24,13 +24,18 @@ class ModalParallelPlugin:
     def __init__(self, tp_size: int = 1, sp_size: int = 1, sequence_parallelism_mode: Optional[str] = None,
                  pipeline_template: Optional[PipelineTemplate] = None,
                  context_parallel_distribution_mode: ContextParallelDistributionMode | str = ContextParallelDistributionMode.MAKESPAN_MIN,
-                 cpu_offload: bool = False, custom_policy=None, ep_size: int = 1):
+                 cpu_offload: bool = False, custom_policy=None, ep_size: int = 1,
+                 ep_capacity_factor: Optional[float] = None):
         if sp_size > 1:
             assert sequence_parallelism_mode in ("ring_attn", "all_to_all"), (
                 "sequence_parallelism_mode must be 'ring_attn' or 'all_to_all' when sp_size > 1")
         self.tp_size = tp_size
         self.sp_size = sp_size
+        # expert parallelism (MoE language models): the experts of every sparse block are sharded over the data-parallel
+        # ranks of the stage that holds the block, so ep_size must equal the data-parallel degree.  With a capacity factor
+        # the dispatch has static shapes and makes no host read (parallel/ep.py).
         self.ep_size = ep_size
+        self.ep_capacity_factor = ep_capacity_factor
         self.sequence_parallelism_mode = sequence_parallelism_mode if sp_size > 1 else None
         self.pipeline_template = pipeline_template
         self.context_parallel_distribution_mode = (

@@ -162,11 +162,14 @@ class MultimodalParallelModule(nn.Module):
                 opt.dp_group = g
             opt.reduce_dp_grads(bucket_bytes)  # peer-memory kernel when the buffers are peer-mapped, else NCCL buckets
             return
-        grads = [p.grad for p in getattr(self.module, self.my_modal_name).parameters() if p.grad is not None]
         ws = dist.get_world_size(g)
-        for gr in grads:
-            dist.all_reduce(gr, group=g)
-            gr.div_(ws)
+        for p in getattr(self.module, self.my_modal_name).parameters():
+            if p.grad is None:
+                continue
+            if not getattr(p, "expert_parallel", False):
+                dist.all_reduce(p.grad, group=g)
+            # an expert's gradient already holds every rank's tokens, each from that rank's own mean loss: only the 1 / dp
+            p.grad.div_(ws)
 
     def sync_sp_grads(self, grads=None):
         return None  # context-parallel ranks are part of the data-parallel reduction group
@@ -289,6 +292,8 @@ class MultimodalParallelPlugin:
                                       self.sp_group if plugin.sp_size > 1 else None,
                                       self.stage_manager, device=self.device, dtype=dtype, **self.flags)
         plugin.configure(getattr(model, name), sc, self.stage_manager)
+        if getattr(plugin, "ep_size", 1) > 1:
+            self._shard_experts(getattr(model, name), plugin)
         wrapped = MultimodalParallelModule(model, name, self.stage_manager, self.dp_group,
                                            self.tp_group if plugin.tp_size > 1 else None,
                                            self.sp_group if plugin.sp_size > 1 else None, self.precision, self.device)
@@ -296,6 +301,19 @@ class MultimodalParallelPlugin:
             optimizer = self._wrap_optimizer(optimizer, wrapped, plugin)
             wrapped.optimizer = optimizer
         return wrapped, optimizer, criterion, dataloader, lr_scheduler
+
+    def _shard_experts(self, module, plugin: ModalParallelPlugin) -> None:
+        """Expert parallelism of a MoE modality: every sparse block this rank holds keeps ``experts / ep`` experts, tokens
+        travel between the data-parallel ranks of this stage (``parallel/ep.py``).  The expert parameters are then not
+        replicated over that group: the gradient reduction skips them and the optimizer only rescales them."""
+        from ..parallel.ep import shard_experts
+
+        dp = dist.get_world_size(self.dp_group) if self.dp_group is not None else 1
+        assert plugin.ep_size == dp, (
+            f"ep_size {plugin.ep_size} must equal the data-parallel degree {dp}: experts are sharded over the data-parallel ranks")
+        assert plugin.sp_size == 1, "expert parallelism over ranks that also split the sequence is not supported"
+        params = shard_experts(module, self.dp_group, capacity_factor=plugin.ep_capacity_factor)
+        assert params or not any(hasattr(m, "experts") for m in module.modules()), "no sparse MoE block found to shard"
 
     def _wrap_optimizer(self, optimizer, wrapped: MultimodalParallelModule, plugin: ModalParallelPlugin):
         """Rebuild the optimizer over the parameters that survived sharding (same class and hyper-parameters)."""
@@ -310,14 +328,16 @@ class MultimodalParallelPlugin:
             kw = {k: defaults[k] for k in ("lr", "betas", "eps", "weight_decay") if k in defaults}
             wd = kw.pop("weight_decay", 0.01 if cls is not torch.optim.Adam else 0.0)
             inner = FusedAdamW(split_decay_groups(mine, wd), grad_dtype=self.grad_dtype, zero_stage=self.zero_stage,
-                               dp_group=self.dp_group, **kw)
+                               dp_group=self.dp_group, expert_group=self.dp_group if plugin.ep_size > 1 else None, **kw)
         else:
             defaults.pop("differentiable", None)
             keep = {k: v for k, v in defaults.items() if k in cls.__init__.__code__.co_varnames}
             inner = cls(params, **keep) if params else cls([torch.nn.Parameter(torch.zeros(1, device=self.device))], **keep)
         pp_group = self.pp_groups[0] if self.pp_groups else None
-        return OptimizerWrapper(inner, wrapped, self.max_norm, self.precision, self.tp_group if plugin.tp_size > 1 else None,
-                                pp_group, self.scaler_kwargs)
+        opt = OptimizerWrapper(inner, wrapped, self.max_norm, self.precision, self.tp_group if plugin.tp_size > 1 else None,
+                               pp_group, self.scaler_kwargs)
+        opt.expert_group = self.dp_group if plugin.ep_size > 1 else None
+        return opt
 
     # ------------------------------------------------------------------ data
     def prepare_dataloader(self, dataset, batch_size, shuffle=False, seed=1024, drop_last=False, pin_memory=False,

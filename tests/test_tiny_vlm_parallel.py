@@ -11,27 +11,27 @@ import torch.distributed as dist
 from tests.dist_utils import run_distributed
 
 
-def _build(seed=0):
+def _build(seed=0, shape="tiny"):
     from cornstarch_b200.zoo import build_model
 
     torch.manual_seed(seed)
-    m = build_model("tiny")
+    m = build_model(shape)
     m.train()
     return m
 
 
-def _batch(n, seed=1):
+def _batch(n, seed=1, shape="tiny"):
     from cornstarch_b200.zoo import synthetic_batch
 
-    return synthetic_batch("tiny", n, seed=seed)
+    return synthetic_batch(shape, n, seed=seed)
 
 
-def _single_process_reference(n_samples, n_micro, lr=1e-2, steps=2):
+def _single_process_reference(n_samples, n_micro, lr=1e-2, steps=2, shape="tiny", eps=1e-8, dense_grads=False):
     from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
 
-    model = _build()
-    opt = FusedAdamW(split_decay_groups(model, 0.0), lr=lr)
-    batch = _batch(n_samples)
+    model = _build(shape=shape)
+    opt = FusedAdamW(split_decay_groups(model, 0.0), lr=lr, eps=eps)
+    batch = _batch(n_samples, shape=shape)
     losses = []
     mb = n_samples // n_micro
     for _ in range(steps):
@@ -41,6 +41,12 @@ def _single_process_reference(n_samples, n_micro, lr=1e-2, steps=2):
             loss = model(**sub).loss / n_micro
             loss.backward()
             total += loss.item()
+        if dense_grads:
+            # an expert that received no token has no gradient here and would be skipped by the optimizer; with sharded
+            # experts (and in the flat gradient buffer on GPUs) it has a zero gradient and its momentum still moves it
+            for p in model.parameters():
+                if p.requires_grad and p.grad is None:
+                    p.grad = torch.zeros_like(p)
         opt.step()
         opt.zero_grad()
         losses.append(total)
@@ -294,3 +300,58 @@ def _colocated_two_stage_encoder_worker(rank, world):
 
 def test_colocated_two_stage_encoder():
     run_distributed(_colocated_two_stage_encoder_worker, 3)
+
+
+def _ep_plugin_worker(rank, world, capacity):
+    """Encoder stage + MoE language-model stage, two data-parallel replicas, the experts of every sparse block sharded over
+    the two replicas by the plugin (``ModalParallelPlugin(ep_size=2)``): loss and post-step weights equal the
+    single-process model with all experts local."""
+    from cornstarch_b200.booster import Booster
+    from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
+    from cornstarch_b200.pipeline_template import PipelineTemplate
+    from cornstarch_b200.plugin.modal_parallel_plugin import ModalParallelPlugin
+    from cornstarch_b200.plugin.multimodal_parallel_plugin import MultimodalParallelPlugin
+
+    # a larger epsilon than the default: with 1e-8 the first Adam steps move every weight by +-lr whatever the size of its
+    # gradient, so elements whose gradient is rounding noise (experts that saw few tokens) differ by whole steps
+    ref_losses, ref_sd = _single_process_reference(4, 4, shape="moe_tiny", eps=1e-4, dense_grads=True)
+    model = _build(shape="moe_tiny")
+    plugin = MultimodalParallelPlugin(
+        encoder_plugins={"vision": ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.vision_encoder, 1))},
+        language_model_plugin=ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.language_model, 1),
+                                                  ep_size=2, ep_capacity_factor=capacity),
+        num_microbatches=2, precision=None, device=torch.device("cpu"))
+    booster = Booster(plugin=plugin)
+    opt = FusedAdamW(split_decay_groups(model, 0.0), lr=1e-2, eps=1e-4)
+    pmodel, popt, criterion, *_ = booster.boost(model, opt, criterion=lambda out, batch: out.loss)
+    assert plugin.dp_size == 2
+    M = plugin.pg_mesh
+    replica = M.coords[0][M.dp_axis]
+    batch = {k: v[replica * 2 : (replica + 1) * 2] for k, v in _batch(4, shape="moe_tiny").items()}
+    sm = plugin.stage_manager
+    mine = getattr(pmodel.module, pmodel.my_modal_name)
+    if pmodel.my_modal_name == "language_model":
+        blocks = [m for m in mine.modules() if getattr(m, "ep", None) is not None]
+        assert blocks and all(len(b.experts) == 2 for b in blocks)  # 4 experts over 2 ranks
+    for step in range(2):
+        out = booster.execute_pipeline(iter([batch]), pmodel, criterion, popt, return_loss=True)
+        popt.step()
+        popt.zero_grad()
+        if sm.is_last_stage(check_only_in_modal=False):
+            mean = out["loss"].detach().clone()
+            dist.all_reduce(mean, group=plugin.dp_group)
+            assert abs(mean.item() / 2 - ref_losses[step]) < 1e-4, (mean.item() / 2, ref_losses[step])
+    prefix = pmodel.my_modal_name + "."
+    ep_rank = dist.get_rank(plugin.dp_group)
+    for name, p in mine.named_parameters():
+        key = prefix + name
+        if getattr(p, "expert_parallel", False):
+            # local expert j of this rank is expert ep_rank * 2 + j of the whole model
+            head, j, tail = name.partition(".experts.")[0], int(name.partition(".experts.")[2].split(".")[0]), name.partition(".experts.")[2].split(".", 1)[1]
+            key = f"{prefix}{head}.experts.{ep_rank * 2 + j}.{tail}"
+        assert torch.allclose(p.detach(), ref_sd[key], atol=2e-3, rtol=5e-3), (name, (p.detach() - ref_sd[key]).abs().max())
+
+
+@pytest.mark.parametrize("capacity", [None, 4.0])
+def test_plugin_expert_parallelism_matches_single_process(capacity):
+    run_distributed(_ep_plugin_worker, 4, capacity)
