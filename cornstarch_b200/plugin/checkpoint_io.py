@@ -109,6 +109,28 @@ def shard_full_tensor(name: str, full: torch.Tensor, info: dict, tp_group) -> to
     return full[mod.vocab_start : mod.vocab_end]
 
 
+def _expert_state_keys(model: nn.Module) -> list[str]:
+    """State-dict keys (global expert indices) of the parameters that expert parallelism shards over the data-parallel
+    group: every rank of that group holds different ones."""
+    ptrs = {p.data_ptr() for p in model.parameters() if getattr(p, "expert_parallel", False)}
+    if not ptrs:
+        return []
+    return [k for k, t in model.state_dict().items() if t.data_ptr() in ptrs]
+
+
+def _checkpoint_param_names(model: nn.Module) -> dict[int, str]:
+    """``id(parameter) -> name in the checkpoint``: the module path, except for expert-parallel parameters, whose
+    checkpoint name carries the expert's global index (``state_dict`` renames them, ``named_parameters`` does not)."""
+    names = {id(p): n for n, p in model.named_parameters()}
+    experts = {p.data_ptr(): p for p in model.parameters() if getattr(p, "expert_parallel", False)}
+    if experts:
+        for k, t in model.state_dict().items():
+            p = experts.get(t.data_ptr())
+            if p is not None:
+                names[id(p)] = k
+    return names
+
+
 class ModalParallelCheckpointIO:
     """Checkpoint IO of one modality's module on the groups that shard it."""
 
@@ -135,6 +157,7 @@ class ModalParallelCheckpointIO:
                 # tensor-parallel gathers are collective over the tp group: every tp rank takes part
                 sd[name] = gather_full_tensor(name, t.detach(), info, self.tp_group).cpu().contiguous()
         writer = self.dp_rank == 0 and self.tp_rank == 0
+        expert_keys = _expert_state_keys(model)
         if writer and sd:
             os.makedirs(path, exist_ok=True)
             os.makedirs(os.path.join(path, TMP_INDEX_DIR), exist_ok=True)
@@ -142,7 +165,17 @@ class ModalParallelCheckpointIO:
                                                  use_safetensors=use_safetensors, stage=self.stage, write_index=False)
             with open(os.path.join(path, TMP_INDEX_DIR, f"index-stage-{self.stage:05d}.json"), "w") as f:
                 json.dump(index, f)
+        elif expert_keys and sd and self.tp_rank == 0:
+            # expert parallelism: the other data-parallel ranks hold other experts; each writes its own (global names)
+            os.makedirs(os.path.join(path, TMP_INDEX_DIR), exist_ok=True)
+            index = ckio.save_state_dict_sharded({k: sd[k] for k in expert_keys}, path, max_shard_size=size_per_shard * 1024 * 1024,
+                                                 use_safetensors=use_safetensors, stage=self.stage,
+                                                 base=f"model-experts-{self.dp_rank:03d}", write_index=False)
+            with open(os.path.join(path, TMP_INDEX_DIR, f"index-stage-{self.stage:05d}-experts-{self.dp_rank:03d}.json"), "w") as f:
+                json.dump(index, f)
         if merge_on_first:
+            if expert_keys and self.dp_group is not None:
+                dist.barrier(self.dp_group)  # the merge below reads what every expert writer left
             self._barrier()
             first = self.stage_manager is None or self.stage_manager.is_first_stage(check_only_in_modal=True)
             tmp = os.path.join(path, TMP_INDEX_DIR)
@@ -176,7 +209,9 @@ class ModalParallelCheckpointIO:
     def save_sharded_optimizer(self, optimizer, model: nn.Module, path: str, size_per_shard: int = 1024) -> None:
         opt = optimizer.unwrap() if hasattr(optimizer, "unwrap") else optimizer
         info = _tp_info(model)
-        names = {id(p): n for n, p in model.named_parameters()}
+        names = _checkpoint_param_names(model)
+        expert_ids = {id(p) for p in model.parameters() if getattr(p, "expert_parallel", False)}
+        expert_flat = {}
         sd = opt.state_dict()
         flat = {}
         idx = 0
@@ -189,7 +224,15 @@ class ModalParallelCheckpointIO:
                         if isinstance(v, torch.Tensor) and v.dim() > 0 and v.shape == p.shape:
                             v = gather_full_tensor(n, v, info, self.tp_group)
                         flat[f"{n}::{k}"] = v.detach().cpu() if isinstance(v, torch.Tensor) else torch.tensor(v)
+                        if id(p) in expert_ids:
+                            expert_flat[f"{n}::{k}"] = flat[f"{n}::{k}"]
                 idx += 1
+        if self.dp_rank != 0 and self.tp_rank == 0 and expert_flat:
+            # expert parallelism: the state of the experts this data-parallel rank owns, in files of its own
+            os.makedirs(path, exist_ok=True)
+            ckio.save_state_dict_sharded(expert_flat, path, max_shard_size=size_per_shard * 1024 * 1024, use_safetensors=False,
+                                         base=f"pytorch_optim-stage-{self.stage + 1:05d}-experts-{self.dp_rank:03d}",
+                                         write_index=False)
         if self.dp_rank == 0 and self.tp_rank == 0:
             os.makedirs(path, exist_ok=True)
             ckio.save_state_dict_sharded(flat, path, max_shard_size=size_per_shard * 1024 * 1024, use_safetensors=False,
@@ -202,7 +245,7 @@ class ModalParallelCheckpointIO:
     def load_sharded_optimizer(self, optimizer, model: nn.Module, path: str) -> None:
         opt = optimizer.unwrap() if hasattr(optimizer, "unwrap") else optimizer
         info = _tp_info(model)
-        names = {id(p): n for n, p in model.named_parameters()}
+        names = _checkpoint_param_names(model)
         flat = {}
         for fn in sorted(os.listdir(path)):
             if fn.startswith("pytorch_optim-stage-") and fn.endswith(".bin"):

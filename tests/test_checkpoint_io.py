@@ -19,7 +19,7 @@ def _shared_tmpdir():
     return path[0]
 
 
-def _boost(tp, llm_stages, freeze_vision=False, seed=0):
+def _boost(tp, llm_stages, freeze_vision=False, seed=0, shape="tiny", ep=1):
     from cornstarch_b200.booster import Booster
     from cornstarch_b200.optim.fused_adamw import FusedAdamW, split_decay_groups
     from cornstarch_b200.pipeline_template import PipelineTemplate
@@ -28,12 +28,13 @@ def _boost(tp, llm_stages, freeze_vision=False, seed=0):
     from cornstarch_b200.zoo import build_model
 
     torch.manual_seed(seed)
-    model = build_model("tiny")
+    model = build_model(shape)
     if freeze_vision:
         model.train(encoders_mode={"vision": (False, True)}, llm_mode=True)
     plugin = MultimodalParallelPlugin(
         encoder_plugins={"vision": ModalParallelPlugin(tp_size=tp, pipeline_template=PipelineTemplate.even_split(model.vision_encoder, 1))},
-        language_model_plugin=ModalParallelPlugin(tp_size=tp, pipeline_template=PipelineTemplate.even_split(model.language_model, llm_stages)),
+        language_model_plugin=ModalParallelPlugin(tp_size=tp, pipeline_template=PipelineTemplate.even_split(model.language_model, llm_stages),
+                                                  ep_size=ep),
         num_microbatches=2, device=torch.device("cpu"))
     booster = Booster(plugin=plugin)
     opt = FusedAdamW(split_decay_groups(model, 0.0), lr=1e-2)
@@ -41,10 +42,10 @@ def _boost(tp, llm_stages, freeze_vision=False, seed=0):
     return booster, plugin, pmodel, popt, crit
 
 
-def _step(booster, pmodel, popt, crit, seed):
+def _step(booster, pmodel, popt, crit, seed, shape="tiny"):
     from cornstarch_b200.zoo import synthetic_batch
 
-    out = booster.execute_pipeline(iter([synthetic_batch("tiny", 4, seed=seed)]), pmodel, crit, popt, return_loss=True)
+    out = booster.execute_pipeline(iter([synthetic_batch(shape, 4, seed=seed)]), pmodel, crit, popt, return_loss=True)
     popt.step()
     popt.zero_grad()
     return out["loss"]
@@ -120,6 +121,43 @@ def _roundtrip_worker(rank, world, tp, llm_stages):
 @pytest.mark.parametrize("tp,llm_stages,world", [(1, 2, 3), (2, 1, 4)])
 def test_checkpoint_roundtrip(tp, llm_stages, world):
     run_distributed(_roundtrip_worker, world, tp, llm_stages, timeout=600)
+
+
+def _expert_parallel_worker(rank, world):
+    """Two replicas of (encoder stage + MoE stage) with the experts sharded over the replicas: every rank of the expert
+    group writes the experts it owns, the directory holds ALL experts under their global names, and a rebuilt model
+    with the same plan loads weights and optimizer state back and takes the same next step."""
+    kw = dict(shape="moe_tiny", ep=2)
+    booster, plugin, pmodel, popt, crit = _boost(1, 1, seed=0, **kw)
+    _step(booster, pmodel, popt, crit, 1, "moe_tiny")
+    root = _shared_tmpdir()
+    booster.save_model(pmodel, os.path.join(root, "model"), shard=True, size_per_shard=1)
+    booster.save_optimizer(popt, os.path.join(root, "optim"), shard=True, size_per_shard=1)
+    dist.barrier()
+    before = {k: v.detach().clone() for k, v in _mine(pmodel).state_dict().items()}
+    _step(booster, pmodel, popt, crit, 2, "moe_tiny")
+    after_a = {k: v.detach().clone() for k, v in _mine(pmodel).state_dict().items()}
+    booster2, plugin2, pmodel2, popt2, crit2 = _boost(1, 1, seed=123, **kw)
+    booster2.load_model(pmodel2, os.path.join(root, "model"))
+    booster2.load_optimizer(popt2, os.path.join(root, "optim"))
+    for k, v in _mine(pmodel2).state_dict().items():
+        assert torch.allclose(v, before[k], atol=1e-6), k
+    _step(booster2, pmodel2, popt2, crit2, 2, "moe_tiny")
+    for k, v in _mine(pmodel2).state_dict().items():
+        assert torch.allclose(v, after_a[k], atol=1e-5), (k, (v - after_a[k]).abs().max())
+    dist.barrier()
+    if rank == 0:
+        from cornstarch_b200.checkpoint.io import load_state_dict_any
+        from cornstarch_b200.zoo import build_model
+
+        want = build_model("moe_tiny").language_model.state_dict()
+        sd = load_state_dict_any(os.path.join(root, "model", "language_model"))
+        assert set(sd) == set(want), set(want) ^ set(sd)  # experts 0..3 of every layer, although no rank holds them all
+        assert any(".experts.3." in k for k in sd)
+
+
+def test_checkpoint_roundtrip_with_expert_parallelism():
+    run_distributed(_expert_parallel_worker, 4, timeout=600)
 
 
 def _frozen_worker(rank, world):
