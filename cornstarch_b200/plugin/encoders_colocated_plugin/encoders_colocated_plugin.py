@@ -150,6 +150,8 @@ class EncodersColocatedMultimodalParallelPlugin(MultimodalParallelPlugin):
                                           self.sp_group if plugin.sp_size > 1 else None, sm, device=self.device, dtype=dtype,
                                           **self.flags)
             plugin.configure(model.language_model, sc, sm)
+            if getattr(plugin, "ep_size", 1) > 1:
+                self._shard_experts(model.language_model, plugin)
             name = "language_model"
         wrapped = EncodersColocatedMultimodalParallelModule(model, name, sm, self.dp_group,
                                                             self.tp_group if plugin.tp_size > 1 else None,
