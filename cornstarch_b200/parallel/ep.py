@@ -319,6 +319,17 @@ def shard_experts(model, group, capacity_factor: float | None = None) -> list[to
     return expert_params
 
 
+def dropped_pairs(model) -> torch.Tensor | None:
+    """Capacity mode: (token, expert) pairs that the last forward pass of ``model`` dropped on this rank, summed over its
+    sparse blocks, as a device scalar (reading it is the caller's synchronisation).  ``None`` without capacity mode."""
+    total = None
+    for m in model.modules():
+        ep = getattr(m, "ep", None)
+        if isinstance(ep, ExpertParallel) and ep.dropped_pairs is not None:
+            total = ep.dropped_pairs if total is None else total + ep.dropped_pairs
+    return total
+
+
 def _install_global_expert_names(block, ep: ExpertParallel) -> None:
     """Checkpoints name experts by their global index: ``experts.<local>`` <-> ``experts.<first + local>`` on save / load."""
     import re

@@ -88,6 +88,9 @@ def _capacity_worker(rank, world, factor):
     ya, _ = full(xa)
     yb, _ = sharded(xb)
     dropped = int(sharded.ep.dropped_pairs)
+    from cornstarch_b200.parallel.ep import dropped_pairs
+
+    assert int(dropped_pairs(sharded)) == dropped and dropped_pairs(full) is None
     if factor >= 4.0:  # capacity = every pair of the rank: nothing can be dropped
         assert dropped == 0
         assert torch.allclose(ya, yb, atol=1e-5), (ya - yb).abs().max()
