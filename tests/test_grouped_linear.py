@@ -60,13 +60,11 @@ def test_grouped_linear_autograd_on_cpu(adjacent):
         assert torch.allclose(wa.grad, wb.grad, atol=1e-5)
 
 
-def test_grouped_linear_accumulates_into_main_grad_on_cpu():
+def test_grouped_multi_linear_without_the_native_path():
+    """On the CPU ``grouped_multi_linear`` is one ``F.linear`` per group: every weight sees only its group's rows."""
     G, R, K, widths = 2, 8, 16, [12]
     x, groups = _make(G, R, K, widths, torch.float32, "cpu")
     ws = [g[0].requires_grad_() for g in groups]
-    for w in ws:
-        w.main_grad = torch.ones_like(w)
-    # main_grad accumulation is the native path's contract; on the CPU the gradients are returned
     y = grouped_multi_linear(x, [[w] for w in ws], R)
     y.sum().backward()
     for g, w in enumerate(ws):
