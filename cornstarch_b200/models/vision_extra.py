@@ -19,7 +19,7 @@ from .. import nn as cnn
 from ..ops import attention as A
 from ..ops import elementwise as E
 from ..ops.linear import multi_linear
-from .base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, register_model
+from .base import ModelOutput, PretrainedConfig, is_released, register_model
 from .vision import VisionConfig, _Encoder, _VisionBase
 
 

@@ -28,7 +28,7 @@ from torch.utils.checkpoint import checkpoint
 
 from .. import nn as cnn
 from ..kernel.interface import create_bitfield_attention_mask, create_instance_bitfield_attention_mask
-from ..models.base import ModelOutput, PretrainedConfig, PreTrainedModel, is_released, register_model
+from ..models.base import ModelOutput, PretrainedConfig, PreTrainedModel, register_model
 from ..ops import attention as A
 from ..ops import elementwise as E
 

@@ -34,8 +34,6 @@ class PipelineTemplate:
     @staticmethod
     def get_modules(model: nn.Module) -> list[str]:
         from .multimodal.modeling import ModalModuleBase
-        from .shardformer.policies.auto_policy import get_policy_type
-
         from .shardformer.policies.auto_policy import policy_for_model
 
         if isinstance(model, ModalModuleBase):

@@ -19,7 +19,7 @@ from ...parallel.mesh import MultiModalProcessGroupMesh
 from ...parallel.schedule import MultimodalEncoderTrainingOneForwardOneBackwardSchedule
 from ...parallel.stage_manager import MultiModalPipelineStageManager
 from ...pipeline_template import PipelineTemplate
-from ..modal_parallel_plugin import ModalParallelPlugin, _FixedHeld
+from ..modal_parallel_plugin import _FixedHeld
 from ..multimodal_parallel_plugin import PRECISION, MultimodalParallelModule, MultimodalParallelPlugin, _Dropped, _DroppedLM
 
 

@@ -13,14 +13,13 @@ large buckets, instead of one blocking all-reduce per parameter (reference :362-
 from __future__ import annotations
 
 from contextlib import contextmanager
-from typing import Any, Callable, Iterator, Optional
+from typing import Any, Callable, Iterator
 
 import torch
 import torch.distributed as dist
 import torch.nn as nn
 from torch.utils.data import DataLoader, DistributedSampler
 
-from ..models.base import ModelOutput, is_released
 from ..multimodal.modeling import ModalEncoderModule, MultimodalModel, _first_tensor
 from ..ops import attention as A
 from ..optim.fused_adamw import FusedAdamW, split_decay_groups
@@ -29,7 +28,6 @@ from ..parallel.mesh import MultiModalProcessGroupMesh
 from ..parallel.p2p import MultimodalPipelineP2PCommunication  # noqa: F401  (part of this module's public names)
 from ..parallel.schedule import MultimodalEncoderTrainingOneForwardOneBackwardSchedule
 from ..parallel.stage_manager import MultiModalPipelineStageManager
-from ..pipeline_template import PipelineTemplate
 from .modal_parallel_plugin import ModalParallelPlugin
 
 PRECISION = {None: None, "fp32": torch.float32, "fp16": torch.float16, "bf16": torch.bfloat16}

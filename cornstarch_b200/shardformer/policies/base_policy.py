@@ -11,7 +11,7 @@ natively, so a policy is data, not code.
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 
 from .pipeline_template_policy import PipelineTemplatePolicyBase, check_template_covers
 

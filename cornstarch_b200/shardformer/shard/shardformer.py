@@ -15,7 +15,7 @@ import torch
 import torch.nn as nn
 
 from ... import nn as cnn
-from ...models.base import PreTrainedModel, is_released
+from ...models.base import PreTrainedModel
 from ...models.llama import ParallelContext
 from .placeholder import TensorPlaceholder
 from .shard_config import ShardConfig
