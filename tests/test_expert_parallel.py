@@ -214,3 +214,44 @@ def _zero_state_worker(rank, world):
 
 def test_zero1_state_gathers_whole_and_loads_by_overlap():
     run_distributed(_zero_state_worker, 2)
+
+
+def _tp_ep_worker(rank, world, capacity):
+    """Language model only, tensor parallel 2 inside every expert AND the experts sharded over 2 data-parallel replicas:
+    each replica's loss equals the single-process model's on the same samples, and an optimizer step goes through."""
+    from cornstarch_b200.booster import Booster
+    from cornstarch_b200.models.moe import MixtralConfig, MoeForCausalLM
+    from cornstarch_b200.multimodal import MultimodalModel
+    from cornstarch_b200.optim.fused_adamw import FusedAdamW
+    from cornstarch_b200.pipeline_template import PipelineTemplate
+    from cornstarch_b200.plugin.modal_parallel_plugin import ModalParallelPlugin
+    from cornstarch_b200.plugin.multimodal_parallel_plugin import MultimodalParallelPlugin
+
+    cfg = MixtralConfig(vocab_size=512, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2, max_position_embeddings=256)
+    torch.manual_seed(0)
+    ref = MoeForCausalLM(cfg)
+    torch.manual_seed(0)
+    llm = MoeForCausalLM(cfg)
+    ids = torch.randint(0, 512, (4, 64), generator=torch.Generator().manual_seed(1))
+    ref_losses = [ref(input_ids=ids[i : i + 1], labels=ids[i : i + 1]).loss.item() for i in range(4)]
+    model = MultimodalModel(encoders={}, language_model=llm)
+    plugin = MultimodalParallelPlugin(
+        encoder_plugins={},
+        language_model_plugin=ModalParallelPlugin(tp_size=2, pipeline_template=PipelineTemplate.even_split(llm, 1), ep_size=2,
+                                                  ep_capacity_factor=capacity),
+        precision=None, num_microbatches=2, device=torch.device("cpu"))
+    booster = Booster(plugin=plugin)
+    model, opt, criterion, *_ = booster.boost(model, FusedAdamW, criterion=lambda out, batch: out.loss)
+    replica = plugin.pg_mesh.coords[0][plugin.pg_mesh.dp_axis]
+    mine = ids[replica * 2 : (replica + 1) * 2]
+    out = booster.execute_pipeline(iter([{"input_ids": mine, "labels": mine}]), model, criterion, opt, return_loss=True)
+    want = sum(ref_losses[replica * 2 : (replica + 1) * 2]) / 2
+    assert abs(out["loss"].item() - want) < 1e-4, (out["loss"].item(), want)
+    opt.step()
+    opt.zero_grad()
+
+
+@pytest.mark.parametrize("capacity", [None, 4.0])
+def test_plugin_tensor_parallel_experts_sharded_over_replicas(capacity):
+    run_distributed(_tp_ep_worker, 4, capacity)
