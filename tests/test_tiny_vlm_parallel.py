@@ -302,7 +302,7 @@ def test_colocated_two_stage_encoder():
     run_distributed(_colocated_two_stage_encoder_worker, 3)
 
 
-def _ep_plugin_worker(rank, world, capacity):
+def _ep_plugin_worker(rank, world, capacity, llm_stages=1):
     """Encoder stage + MoE language-model stage, two data-parallel replicas, the experts of every sparse block sharded over
     the two replicas by the plugin (``ModalParallelPlugin(ep_size=2)``): loss and post-step weights equal the
     single-process model with all experts local."""
@@ -318,7 +318,7 @@ def _ep_plugin_worker(rank, world, capacity):
     model = _build(shape="moe_tiny")
     plugin = MultimodalParallelPlugin(
         encoder_plugins={"vision": ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.vision_encoder, 1))},
-        language_model_plugin=ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.language_model, 1),
+        language_model_plugin=ModalParallelPlugin(pipeline_template=PipelineTemplate.even_split(model.language_model, llm_stages),
                                                   ep_size=2, ep_capacity_factor=capacity),
         num_microbatches=2, precision=None, device=torch.device("cpu"))
     booster = Booster(plugin=plugin)
@@ -352,6 +352,6 @@ def _ep_plugin_worker(rank, world, capacity):
         assert torch.allclose(p.detach(), ref_sd[key], atol=2e-3, rtol=5e-3), (name, (p.detach() - ref_sd[key]).abs().max())
 
 
-@pytest.mark.parametrize("capacity", [None, 4.0])
-def test_plugin_expert_parallelism_matches_single_process(capacity):
-    run_distributed(_ep_plugin_worker, 4, capacity)
+@pytest.mark.parametrize("capacity,llm_stages,world", [(None, 1, 4), (4.0, 1, 4), (None, 2, 6)])
+def test_plugin_expert_parallelism_matches_single_process(capacity, llm_stages, world):
+    run_distributed(_ep_plugin_worker, world, capacity, llm_stages)
