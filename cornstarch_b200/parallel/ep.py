@@ -88,6 +88,9 @@ def by_expert_order(recv_counts: torch.Tensor, total: int) -> torch.Tensor:
 FUSED_EP_ENABLED = True  # exchange tokens with this package's peer-memory kernel instead of NCCL all_to_all
 
 
+ONE_PROCESS = "one process"  # in place of a process group: every expert is local and nothing is exchanged
+
+
 class ExpertParallel:
     """Attached to a sparse MoE block as ``block.ep``; the block then holds only this rank's experts."""
 
@@ -95,8 +98,11 @@ class ExpertParallel:
         self.capacity_factor = capacity_factor
         self.dropped_pairs = None  # capacity mode: device scalar, pairs dropped in the last call (read it when convenient)
         self.group = group
-        self.ws = dist.get_world_size(group)
-        self.rank = dist.get_rank(group)
+        # ONE_PROCESS: no process group at all (capacity mode of a single process: static shapes and the grouped GEMM
+        # without any exchange)
+        self.ws = 1 if group is ONE_PROCESS else dist.get_world_size(group)
+        self.rank = 0 if group is ONE_PROCESS else dist.get_rank(group)
+        assert group is not ONE_PROCESS or capacity_factor is not None, "a single process without a group runs the capacity form"
         assert num_experts % self.ws == 0, f"{num_experts} experts cannot be split over {self.ws} ranks"
         self.num_experts = num_experts
         self.local = num_experts // self.ws
@@ -255,6 +261,8 @@ class ExpertParallel:
 
 def _a2a_equal(x: torch.Tensor, group) -> torch.Tensor:
     """All-to-all with equal splits: ``x`` is ``[world, n, ...]``, slice ``d`` goes to rank ``d``."""
+    if group is ONE_PROCESS:
+        return x
     if dist.get_backend(group) != "gloo":
         out = torch.empty_like(x)
         dist.all_to_all_single(out, x.contiguous(), group=group)
@@ -317,6 +325,18 @@ def shard_experts(model, group, capacity_factor: float | None = None) -> list[to
     for p in expert_params:
         p.expert_parallel = True
     return expert_params
+
+
+def set_expert_capacity(model, capacity_factor: float) -> None:
+    """Capacity mode for a model whose experts all live in this process (no expert parallelism, no process group): every
+    sparse block routes with static shapes, reads nothing on the host and runs its experts through one grouped GEMM per
+    projection.  Pairs beyond ``capacity_factor`` times an expert's fair share are dropped (``dropped_pairs``)."""
+    import torch.nn as nn
+
+    for m in model.modules():
+        if hasattr(m, "experts") and hasattr(m, "ep") and isinstance(m.experts, nn.ModuleList):
+            assert m.ep is None or m.ep.group is ONE_PROCESS, "this block's experts are already sharded over a group"
+            m.ep = ExpertParallel(ONE_PROCESS, len(m.experts), capacity_factor)
 
 
 def dropped_pairs(model) -> torch.Tensor | None:

@@ -69,6 +69,36 @@ def test_regroup_permutation_and_counts_without_host_values():
     assert by_expert_order(torch.tensor(rc), pos).tolist() == want
 
 
+def test_capacity_mode_in_one_process_without_a_group():
+    """``set_expert_capacity``: the static-shape form with every expert local, no torch.distributed at all."""
+    from cornstarch_b200.models.moe import MixtralConfig, MixtralSparseMoeBlock
+    from cornstarch_b200.parallel.ep import dropped_pairs, set_expert_capacity
+
+    cfg = MixtralConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=4,
+                        num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2)
+    torch.manual_seed(0)
+    full = MixtralSparseMoeBlock(cfg)
+    torch.manual_seed(0)
+    capped = MixtralSparseMoeBlock(cfg)
+    set_expert_capacity(capped, 4.0)  # room for every pair
+    assert len(capped.experts) == 4 and not dist.is_initialized()
+    x = torch.randn(2, 12, 32)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya, _ = full(xa)
+    yb, _ = capped(xb)
+    assert int(dropped_pairs(capped)) == 0
+    assert torch.allclose(ya, yb, atol=1e-5)
+    ya.square().sum().backward()
+    yb.square().sum().backward()
+    assert torch.allclose(xa.grad, xb.grad, atol=1e-5)
+    for ea, eb in zip(full.experts, capped.experts):
+        ga, gb = ea.w1.weight.grad, eb.w1.weight.grad
+        assert torch.allclose(torch.zeros_like(gb) if ga is None else ga, gb, atol=1e-5)
+    set_expert_capacity(capped, 0.5)  # too little room: pairs are dropped and counted
+    capped(x)
+    assert int(dropped_pairs(capped)) > 0
+
+
 def _capacity_worker(rank, world, factor):
     """Static-shape (capacity) dispatch: with room for every pair it equals the local MoE block exactly, in outputs and in
     every gradient; with too little room the surplus pairs are dropped, counted, and contribute nothing."""
