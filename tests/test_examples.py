@@ -20,7 +20,6 @@ def test_example_runs(script):
 
 
 @pytest.mark.parametrize("script,procs,flags,lines", [
-    ("distributed/run_vlm_hybrid.py", 2, ["--backend", "gloo", "--steps", "2", "--microbatches", "2", "--shape", "tiny"], 2),
     ("distributed/run_vlm_hybrid.py", 4, ["--backend", "gloo", "--steps", "2", "--microbatches", "2", "--shape", "moe_tiny",
                                           "--ep", "2", "--ep-capacity", "1.5"], 4),
     ("distributed/run_vlm_ddp.py", 2, ["--backend", "gloo", "--steps", "2", "--shape", "tiny"], 2),

@@ -352,6 +352,6 @@ def _ep_plugin_worker(rank, world, capacity, llm_stages=1):
         assert torch.allclose(p.detach(), ref_sd[key], atol=2e-3, rtol=5e-3), (name, (p.detach() - ref_sd[key]).abs().max())
 
 
-@pytest.mark.parametrize("capacity,llm_stages,world", [(None, 1, 4), (4.0, 1, 4), (None, 2, 6)])
+@pytest.mark.parametrize("capacity,llm_stages,world", [(4.0, 1, 4), (None, 2, 6)])
 def test_plugin_expert_parallelism_matches_single_process(capacity, llm_stages, world):
     run_distributed(_ep_plugin_worker, world, capacity, llm_stages)
