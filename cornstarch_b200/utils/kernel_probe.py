@@ -82,6 +82,28 @@ def probe_gemm(a, flush):
         report(f"gemm[{tag}]", ms, flops=2.0 * M * N * K, M=M, N=N, K=K)
 
 
+def probe_gemm_grouped(a, flush):
+    """``--groups`` problems of ``--m`` rows each (``--n``, ``--k`` as given; default: the gate / up projection of eight
+    Mixtral experts at 2560 rows) as ONE grouped launch against one GEMM launch per group, forward and input-gradient
+    forms."""
+    from ..ops.gemm import grouped_gemm
+
+    G, R, N, K = a.groups, a.m, a.n, a.k
+    x = torch.randn(G * R, K, device="cuda").bfloat16()
+    for bmn, tag in ((False, "fwd y=xW^T"), (True, "dx=dyW")):
+        bs = [torch.randn((K, N) if bmn else (N, K), device="cuda").bfloat16() for _ in range(G)]
+        out = torch.empty(G * R, N, device="cuda", dtype=torch.bfloat16)
+
+        def one_by_one():
+            for g in range(G):
+                gemm(x[g * R : (g + 1) * R], bs[g], False, bmn, out=out[g * R : (g + 1) * R])
+
+        ms = timeit(lambda: grouped_gemm(x, bs, R, b_mn_major=bmn, out=out), a.iters, a.warmup, flush)
+        ms_loop = timeit(one_by_one, a.iters, a.warmup, flush)
+        report(f"gemm_grouped[{tag}]", ms, flops=2.0 * G * R * N * K, groups=G, rows_per_group=R, N=N, K=K,
+               one_launch_per_group_ms=round(ms_loop, 4), speedup=round(ms_loop / ms, 3))
+
+
 def probe_gemm_sustained(a, flush):
     """Back-to-back launches for ``--seconds`` (default 3) of this package's GEMM and of ``torch.matmul`` (cuBLAS) on the
     same operands: the throughput both settle at under the power cap, which is what a long training step sees."""
@@ -321,9 +343,10 @@ def probe_mma_issue(a, flush):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--seconds", type=float, default=3.0)
-    ap.add_argument("what", choices=["gemm", "gemm_sustained", "attn_fwd", "attn_bwd", "elementwise", "gemm_ar_local", "adamw", "grad_reduce_local",
+    ap.add_argument("what", choices=["gemm", "gemm_grouped", "gemm_sustained", "attn_fwd", "attn_bwd", "elementwise", "gemm_ar_local", "adamw", "grad_reduce_local",
                                      "moe_push_local", "attn_fwd_pulled", "mma_issue", "all"])
     ap.add_argument("--reducers", type=int, default=16)
+    ap.add_argument("--groups", type=int, default=8, help="gemm_grouped: number of groups (experts)")
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -340,7 +363,9 @@ def main():
     flush = Flusher(not a.no_flush)
     todo = ["gemm", "attn_fwd", "attn_bwd", "elementwise"] if a.what == "all" else [a.what]
     for t in todo:
-        {"gemm": probe_gemm, "gemm_sustained": probe_gemm_sustained, "attn_fwd": probe_attn_fwd, "attn_bwd": probe_attn_bwd, "elementwise": probe_elementwise,
+        if t == "gemm_grouped" and (a.m, a.n, a.k) == (8192, 4096, 4096):
+            a.m, a.n, a.k = 2560, 28672, 4096  # rows per expert at capacity 1.25 of 8192 tokens; gate | up of Mixtral-8x7B
+        {"gemm": probe_gemm, "gemm_grouped": probe_gemm_grouped, "gemm_sustained": probe_gemm_sustained, "attn_fwd": probe_attn_fwd, "attn_bwd": probe_attn_bwd, "elementwise": probe_elementwise,
          "gemm_ar_local": probe_gemm_ar_local, "adamw": probe_adamw, "grad_reduce_local": probe_grad_reduce_local,
          "moe_push_local": probe_moe_push_local, "attn_fwd_pulled": probe_attn_fwd_pulled, "mma_issue": probe_mma_issue}[t](a, flush)
     from ..ops import _native as nat

@@ -20,7 +20,7 @@ def _choices(module: str) -> set[str]:
 
 
 @pytest.mark.parametrize("module,named", [
-    ("cornstarch_b200.utils.kernel_probe", ["gemm", "gemm_sustained", "attn_fwd", "attn_bwd", "elementwise", "adamw", "mma_issue",
+    ("cornstarch_b200.utils.kernel_probe", ["gemm", "gemm_grouped", "gemm_sustained", "attn_fwd", "attn_bwd", "elementwise", "adamw", "mma_issue",
                                             "gemm_ar_local", "grad_reduce_local", "moe_push_local", "attn_fwd_pulled"]),
     ("cornstarch_b200.utils.comm_probe", ["gemm_allreduce", "sp_linear", "cp_attention", "grad_reduce", "moe_exchange", "moe_layer"]),
 ])
