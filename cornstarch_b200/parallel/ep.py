@@ -22,7 +22,8 @@ Capacity mode (``ExpertParallel(..., capacity_factor=f)`` / ``shard_experts(...,
 with STATIC shapes: every rank sends exactly ``C = ceil(f * tokens * k / num_experts)`` rows per expert (unused slots are
 zero rows, pairs beyond an expert's capacity are dropped and counted in ``dropped_pairs``), so both exchanges are
 all-to-alls with equal splits and nothing is read back to the host: no count exchange, no synchronisation, every tensor
-shape fixed from step to step.  The price is the padding (``f - 1`` of the expert GEMM rows at balanced load) and, like the
+shape fixed from step to step.  ``tokens`` is the token count of the call, which must then be equal on all ranks, or the
+fixed ``capacity_tokens`` (an upper bound) when ranks see batches of different lengths.  The price is the padding (``f - 1`` of the expert GEMM rows at balanced load) and, like the
 capacity factor of GShard / Switch layers, dropped pairs when one expert receives more than ``f`` times its share.
 """
 
@@ -94,8 +95,12 @@ ONE_PROCESS = "one process"  # in place of a process group: every expert is loca
 class ExpertParallel:
     """Attached to a sparse MoE block as ``block.ep``; the block then holds only this rank's experts."""
 
-    def __init__(self, group, num_experts: int, capacity_factor: float | None = None):
+    def __init__(self, group, num_experts: int, capacity_factor: float | None = None, capacity_tokens: int | None = None):
         self.capacity_factor = capacity_factor
+        # capacity mode sizes its exchange from the number of tokens of a call, which must then be the same on every rank.
+        # With capacity_tokens the size comes from this fixed number instead (an upper bound of the tokens per call and
+        # rank): batches of different lengths on different ranks still exchange buffers of one static shape.
+        self.capacity_tokens = capacity_tokens
         self.dropped_pairs = None  # capacity mode: device scalar, pairs dropped in the last call (read it when convenient)
         self.group = group
         # ONE_PROCESS: no process group at all (capacity mode of a single process: static shapes and the grouped GEMM
@@ -175,7 +180,7 @@ class ExpertParallel:
         T, H = x2.shape
         k = experts_idx.shape[1]
         E, ws, L = self.num_experts, self.ws, self.local
-        C = max(1, math.ceil(self.capacity_factor * T * k / E))
+        C = max(1, math.ceil(self.capacity_factor * (self.capacity_tokens or T) * k / E))
         if x2.is_cuda:
             # every expert then holds a multiple of 256 rows: whole tiles of the grouped GEMM that runs all local experts
             step = 256 // math.gcd(256, ws)
@@ -305,7 +310,8 @@ def _record_counts(value) -> None:
         tape.items.append(("ep_counts", value))
 
 
-def shard_experts(model, group, capacity_factor: float | None = None) -> list[torch.nn.Parameter]:
+def shard_experts(model, group, capacity_factor: float | None = None,
+                  capacity_tokens: int | None = None) -> list[torch.nn.Parameter]:
     """Keep only this rank's experts in every sparse MoE block of ``model`` and attach the exchange.
 
     Returns the expert parameters (they are NOT replicated over the group: no data-parallel reduction, and an
@@ -317,7 +323,7 @@ def shard_experts(model, group, capacity_factor: float | None = None) -> list[to
         if hasattr(m, "experts") and hasattr(m, "ep") and isinstance(m.experts, nn.ModuleList):
             if m.ep is not None:
                 continue
-            ep = ExpertParallel(group, len(m.experts), capacity_factor)
+            ep = ExpertParallel(group, len(m.experts), capacity_factor, capacity_tokens)
             m.experts = nn.ModuleList([m.experts[i] for i in ep.local_expert_ids()])
             m.ep = ep
             expert_params += list(m.experts.parameters())

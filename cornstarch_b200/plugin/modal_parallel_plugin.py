@@ -25,7 +25,7 @@ class ModalParallelPlugin:
                  pipeline_template: Optional[PipelineTemplate] = None,
                  context_parallel_distribution_mode: ContextParallelDistributionMode | str = ContextParallelDistributionMode.MAKESPAN_MIN,
                  cpu_offload: bool = False, custom_policy=None, ep_size: int = 1,
-                 ep_capacity_factor: Optional[float] = None):
+                 ep_capacity_factor: Optional[float] = None, ep_capacity_tokens: Optional[int] = None):
         if sp_size > 1:
             assert sequence_parallelism_mode in ("ring_attn", "all_to_all"), (
                 "sequence_parallelism_mode must be 'ring_attn' or 'all_to_all' when sp_size > 1")
@@ -36,6 +36,7 @@ class ModalParallelPlugin:
         # the dispatch has static shapes and makes no host read (parallel/ep.py).
         self.ep_size = ep_size
         self.ep_capacity_factor = ep_capacity_factor
+        self.ep_capacity_tokens = ep_capacity_tokens  # fixed token count that sizes the exchange (ranks with unequal batches)
         self.sequence_parallelism_mode = sequence_parallelism_mode if sp_size > 1 else None
         self.pipeline_template = pipeline_template
         self.context_parallel_distribution_mode = (

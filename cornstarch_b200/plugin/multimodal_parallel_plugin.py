@@ -310,7 +310,8 @@ class MultimodalParallelPlugin:
         assert plugin.ep_size == dp, (
             f"ep_size {plugin.ep_size} must equal the data-parallel degree {dp}: experts are sharded over the data-parallel ranks")
         assert plugin.sp_size == 1, "expert parallelism over ranks that also split the sequence is not supported"
-        params = shard_experts(module, self.dp_group, capacity_factor=plugin.ep_capacity_factor)
+        params = shard_experts(module, self.dp_group, capacity_factor=plugin.ep_capacity_factor,
+                               capacity_tokens=getattr(plugin, "ep_capacity_tokens", None))
         assert params or not any(hasattr(m, "experts") for m in module.modules()), "no sparse MoE block found to shard"
 
     def _wrap_optimizer(self, optimizer, wrapped: MultimodalParallelModule, plugin: ModalParallelPlugin):

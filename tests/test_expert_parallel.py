@@ -185,6 +185,34 @@ def test_capacity_mode_on_the_device_equals_the_local_block():
     run_gpu_ranks(_capacity_gpu_worker, 1)
 
 
+def _unequal_tokens_worker(rank, world):
+    """Capacity mode with a fixed ``capacity_tokens``: ranks with different numbers of tokens exchange buffers of one shape,
+    and with room for every pair the result is the local block's."""
+    from cornstarch_b200.models.moe import MixtralConfig, MixtralSparseMoeBlock
+    from cornstarch_b200.parallel.ep import shard_experts
+
+    cfg = MixtralConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=1, num_attention_heads=4,
+                        num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2)
+    torch.manual_seed(0)
+    full = MixtralSparseMoeBlock(cfg)
+    torch.manual_seed(0)
+    sharded = MixtralSparseMoeBlock(cfg)
+    shard_experts(sharded, dist.group.WORLD, capacity_factor=4.0, capacity_tokens=32)
+    x = torch.randn(2, 9 + 5 * rank, 32, generator=torch.Generator().manual_seed(10 + rank))  # 18 and 28 tokens
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    ya, _ = full(xa)
+    yb, _ = sharded(xb)
+    assert int(sharded.ep.dropped_pairs) == 0
+    assert torch.allclose(ya, yb, atol=1e-5), (ya - yb).abs().max()
+    ya.square().sum().backward()
+    yb.square().sum().backward()
+    assert torch.allclose(xa.grad, xb.grad, atol=1e-5)
+
+
+def test_ep2_capacity_mode_with_unequal_token_counts():
+    run_distributed(_unequal_tokens_worker, 2)
+
+
 def _ckpt_worker(rank, world):
     from cornstarch_b200.models.moe import MixtralConfig, MoeForCausalLM
     from cornstarch_b200.parallel.ep import gather_full_state_dict, shard_experts
