@@ -12,6 +12,7 @@ from __future__ import annotations
 import re
 
 import torch
+import torch.distributed as dist
 import torch.nn as nn
 
 from ... import nn as cnn
@@ -141,8 +142,6 @@ class ModelSharder:
 
     def _shard_lm_head(self, mod: cnn.Linear, tp_group, tp: int):
         """Vocab-parallel LM head: rows padded to a multiple of ``divisible_by * tp`` and split across ranks."""
-        import torch.distributed as dist
-
         V, H = mod.weight.shape
         mult = self.shard_config.make_vocab_size_divisible_by * tp
         Vp = (V + mult - 1) // mult * mult
@@ -226,4 +225,12 @@ class ShardFormer:
         sharder = ModelSharder(model, policy, self.shard_config)
         shared = sharder.shard()
         model._sharder_placeholders = sharder.placeholders
+        ep_group = self.shard_config.expert_parallel_process_group
+        if ep_group is not None and dist.get_world_size(ep_group) > 1:
+            # experts of the sparse blocks that survived the pipeline cut are sharded over the expert-parallel group
+            # (blocks that already are stay as they are); ``extra_kwargs["expert_capacity_factor"]`` selects capacity mode
+            from ...parallel.ep import shard_experts
+
+            shard_experts(model, ep_group, capacity_factor=self.shard_config.extra_kwargs.get("expert_capacity_factor"),
+                          capacity_tokens=self.shard_config.extra_kwargs.get("expert_capacity_tokens"))
         return model, shared

@@ -312,3 +312,29 @@ def _tp_ep_worker(rank, world, capacity):
 
 def test_plugin_tensor_parallel_experts_sharded_over_replicas():
     run_distributed(_tp_ep_worker, 4, None)  # (with a capacity factor the tensor-parallel experts run the same loop)
+
+
+def _shardformer_worker(rank, world):
+    """``ShardConfig(expert_parallel_process_group=...)``: ShardFormer shards the experts of a MoE decoder by itself."""
+    from cornstarch_b200.models.moe import MixtralConfig, MoeForCausalLM
+    from cornstarch_b200.shardformer.shard.shard_config import ShardConfig
+    from cornstarch_b200.shardformer.shard.shardformer import ShardFormer
+
+    cfg = MixtralConfig(vocab_size=64, hidden_size=32, intermediate_size=48, num_hidden_layers=2, num_attention_heads=4,
+                        num_key_value_heads=2, num_local_experts=4, num_experts_per_tok=2)
+    torch.manual_seed(0)
+    ref = MoeForCausalLM(cfg)
+    torch.manual_seed(0)
+    model = MoeForCausalLM(cfg)
+    sc = ShardConfig(enable_tensor_parallelism=False, expert_parallel_process_group=dist.group.WORLD)
+    ShardFormer(sc).optimize(model)
+    blocks = [m for m in model.modules() if getattr(m, "ep", None) is not None]
+    assert len(blocks) == 2 and all(len(b.experts) == 2 for b in blocks)
+    ids = torch.randint(0, 64, (2, 16), generator=torch.Generator().manual_seed(rank))
+    want = ref(input_ids=ids, labels=ids).loss
+    got = model(input_ids=ids, labels=ids).loss
+    assert abs(want.item() - got.item()) < 1e-5
+
+
+def test_shardformer_shards_experts_over_the_configured_group():
+    run_distributed(_shardformer_worker, 2)
