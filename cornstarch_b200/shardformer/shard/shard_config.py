@@ -31,6 +31,10 @@ class ShardConfig:
     enable_sequence_parallelism: bool = False
     sequence_parallelism_mode: Optional[str] = None  # "ring_attn" | "all_to_all"
     context_parallel_distribution_mode: ContextParallelDistributionMode = ContextParallelDistributionMode.MAKESPAN_MIN
+    # The next four switches and gradient_checkpoint_config exist so that the reference's constructor calls keep working
+    # (cornstarch/shardformer/shard/shard_config.py:35-38).  They change nothing here: fused norms and flash attention are
+    # the only GPU path of this package (CORNSTARCH_B200_LIBRARY_OPS=1 switches ALL ops to library kernels instead), and
+    # recomputation is switched on the model (gradient_checkpointing_enable).
     enable_fused_normalization: bool = True
     enable_flash_attention: bool = True
     enable_jit_fused: bool = False
